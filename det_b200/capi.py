@@ -1,0 +1,136 @@
+"""ctypes bindings of the two native libraries.
+
+  cuda()  libdet_b200.so — the C ABI of include/det_b200.h (loading it needs the CUDA runtime, not a GPU)
+  host()  libdet_host.so — the driver above it (backends, synthetic model, token loop)
+
+Nothing here falls back to a CPU implementation: a missing library raises, and the first call that needs a device
+aborts inside the library when none is present.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_DIR = Path(__file__).resolve().parent / "lib"
+
+c_void_p, c_int, c_size_t, c_float, c_char_p = C.c_void_p, C.c_int, C.c_size_t, C.c_float, C.c_char_p
+c_u64, c_i32 = C.c_uint64, C.c_int32
+
+
+class QLinear(C.Structure):
+    """det_qlinear (include/det_b200.h; kernels/cuda/det_cuda.h:26-32)."""
+    _fields_ = [("wq", c_void_p), ("c", c_void_p), ("m", c_void_p), ("N", c_int), ("K", c_int), ("bits", c_int)]
+
+
+class AttnLayer(C.Structure):
+    _fields_ = [("q_norm", c_void_p), ("k_norm", c_void_p), ("v_scale", c_void_p), ("v_inv_scale", c_void_p)]
+
+
+class KvCache(C.Structure):
+    _fields_ = [("kq", c_void_p), ("sk", c_void_p), ("vq", c_void_p), ("capacity", c_int), ("vlo", c_void_p),
+                ("vhi", c_void_p)]
+
+
+class GdnLayer(C.Structure):
+    _fields_ = [("conv", c_void_p), ("A", c_void_p), ("dt_bias", c_void_p), ("norm", c_void_p)]
+
+
+class GdnState(C.Structure):
+    _fields_ = [("conv_state", c_void_p), ("S", c_void_p)]
+
+
+DET_LAYOUT_STREAM = 0x100
+
+# every symbol include/det_b200.h declares: name -> (restype, argtypes)
+CUDA_ABI = {
+    "det_init": (c_int, []),
+    "det_device_name": (c_char_p, []),
+    "det_malloc": (c_void_p, [c_size_t]),
+    "det_free": (None, [c_void_p]),
+    "det_allocated_bytes": (c_size_t, []),
+    "det_sync": (None, []),
+    "det_flush": (None, []),
+    "det_memset": (None, [c_void_p, c_int, c_size_t, c_void_p]),
+    "det_memcpy": (None, [c_void_p, c_void_p, c_size_t, c_void_p]),
+    "det_cuda_stream": (c_void_p, []),
+    "det_rmsnorm_quant": (None, [c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "det_quant": (None, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "det_embed": (None, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "det_add": (None, [c_void_p, c_void_p, C.c_longlong, c_void_p]),
+    "det_silu_mul_quant": (None, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "det_argmax": (None, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "det_gemm": (None, [C.POINTER(QLinear), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "det_gemm_ex": (None, [C.POINTER(QLinear), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                           C.POINTER(c_int), C.POINTER(c_void_p), c_void_p]),
+    "det_gemm_scratch_bytes": (c_size_t, [c_int, c_int]),
+    "det_gemm_set_scratch": (None, [c_void_p, c_size_t]),
+    "det_attention": (None, [C.POINTER(AttnLayer), C.POINTER(KvCache), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "det_attn_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "det_attention_dev": (None, [C.POINTER(AttnLayer), C.POINTER(KvCache), c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_float, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                 c_void_p, c_void_p]),
+    "det_gdn": (None, [C.POINTER(GdnLayer), C.POINTER(GdnState), c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int,
+                       c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "det_gdn_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "det_gdn_ex": (None, [C.POINTER(GdnLayer), C.POINTER(GdnState), c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                          c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "det_sample": (None, [c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p]),
+    "det_sample_topkp": (None, [c_void_p, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "det_sample_scratch_bytes": (c_size_t, [c_int, c_int]),
+    "det_test_prim": (None, [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "det_linear_repack_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "det_linear_repack": (None, [C.POINTER(QLinear), c_void_p, c_void_p]),
+    "det_synth_linear": (None, [c_u64, c_u64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "det_synth_bf16": (None, [c_u64, c_u64, C.c_longlong, c_void_p, c_void_p]),
+    "det_last_error": (c_int, []),
+}
+
+HOST_API = {
+    "dh_last_error": (c_char_p, []),
+    "dh_cuda_backend_new": (c_void_p, [c_int, c_int]),
+    "dh_backend_free": (None, [c_void_p]),
+    "dh_backend_name": (c_int, [c_void_p, c_char_p, c_size_t]),
+    "dh_cuda_test_prim": (None, [c_int, c_void_p, c_size_t, c_size_t, c_size_t, c_void_p, c_size_t]),
+    "dh_model_new_synth": (c_void_p, [c_void_p, c_char_p, c_size_t, c_u64, c_size_t, c_size_t]),
+    "dh_model_free": (None, [c_void_p]),
+    "dh_model_vocab": (c_size_t, [c_void_p]),
+    "dh_model_pos": (c_size_t, [c_void_p]),
+    "dh_model_set_all_logits": (c_int, [c_void_p, c_int]),
+    "dh_model_reset": (c_int, [c_void_p]),
+    "dh_model_forward": (c_int, [c_void_p, c_void_p, c_size_t]),
+    "dh_model_prefill": (c_int, [c_void_p, c_void_p, c_size_t]),
+    "dh_model_logits": (c_size_t, [c_void_p, c_void_p, c_size_t]),
+    "dh_model_pick": (c_int, [c_void_p, c_int, c_float, c_size_t, c_float, C.POINTER(c_u64), C.POINTER(c_i32)]),
+    "dh_model_generate": (c_int, [c_void_p, c_void_p, c_size_t, c_size_t, c_int, c_float, c_size_t, c_float, c_u64,
+                                  c_void_p, C.POINTER(c_size_t)]),
+    "dh_synth_prompt": (None, [c_u64, c_size_t, c_size_t, c_void_p]),
+    "dh_synth_det_rows": (None, [c_u64, c_u64, c_size_t, c_size_t, c_int, c_void_p]),
+    "dh_det_row_bytes": (c_size_t, [c_int, c_size_t]),
+}
+
+_cache: dict[str, C.CDLL] = {}
+
+
+def _load(name: str, table: dict) -> C.CDLL:
+    if name in _cache:
+        return _cache[name]
+    path = LIB_DIR / name
+    if not path.exists():
+        raise RuntimeError(f"{path} is missing: run `python -m det_b200.build` (there is no fallback implementation)")
+    lib = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
+    for sym, (res, args) in table.items():
+        fn = getattr(lib, sym)   # AttributeError when the library does not export a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    _cache[name] = lib
+    return lib
+
+
+def cuda() -> C.CDLL:
+    return _load("libdet_b200.so", CUDA_ABI)
+
+
+def host() -> C.CDLL:
+    cuda()
+    return _load("libdet_host.so", HOST_API)

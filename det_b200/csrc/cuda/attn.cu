@@ -1,0 +1,404 @@
+// Gated full attention with an int8 K / int16 V cache (docs/SPEC.md §5.1, spec/layers.rs:5-87, cpu.rs:216-291).
+// Replaces kernels/cuda/attn.cu behind det_attention / det_attention_dev / det_attn_scratch_bytes.
+//
+//   prep   one warp per (token, head) row: RMSNorm -> RoPE -> (q: * 1/sqrt(hd)) -> per-row int8; k rows and int16 v rows
+//          go straight into the cache at position pos0 + t, q rows into scratch.
+//   max    pass 1 over the keys: the largest score ((float)dot * sq) * sk per (token, q head), order-free, merged across
+//          key splits with an integer atomicMax on an order-preserving key.
+//   acc    pass 2: pq = rint(exp_f(s - max) * 2^24), den = sum pq, num[d] = sum pq * vq[d] in int64.  Integer sums are
+//          exact in any order, so key ranges are split over CTAs and merged with 64-bit atomic adds.
+//   fin    o = (((float)num / (float)den) * v_scale) * sigmoid_f(gate)
+// All query heads that share a kv head are handled by the same CTA so K and V tiles are read once per group.
+#include "runtime.cuh"
+
+namespace detb {
+
+constexpr int KT = 64;           // keys per shared-memory tile
+constexpr int ATT_THREADS = 256;
+constexpr int MAX_REP = 8;       // q heads per kv head
+
+struct AttnArgs {
+    // layer / cache
+    const float *q_norm, *k_norm, *v_scale, *v_inv;
+    int8_t* kq;
+    float* sk;
+    int16_t* vq;
+    // inputs
+    const float *qg, *k, *v, *rope_cos, *rope_sin;
+    int rot;
+    float eps, qscale;
+    int M, n_h, n_kv, rep;
+    int pos0;                // used when pos0_dev == NULL
+    const int* pos0_dev;
+    float* o;
+    // scratch
+    int8_t* qq;              // [M][n_h][HD]
+    float* sq;               // [M][n_h]
+    unsigned* mxkey;         // [M][n_h]
+    long long* den;          // [M][n_h]
+    long long* num;          // [M][n_h][HD]
+    int nsplit, keys_per_split;
+};
+__device__ __forceinline__ int base_pos(const AttnArgs& a) { return a.pos0_dev ? *a.pos0_dev : a.pos0; }
+
+template <int HD>
+__global__ void __launch_bounds__(256) k_attn_prep(const AttnArgs a) {
+    constexpr int PER = HD / 32;
+    __shared__ float rowbuf[8][HD];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const long long row = (long long)blockIdx.x * 8 + wib;
+    const long long n_q = (long long)a.M * a.n_h, n_kvrows = (long long)a.M * a.n_kv;
+    if (row >= n_q + 2 * n_kvrows) return;
+    const int pos0 = base_pos(a);
+    if (row >= n_q + n_kvrows) {
+        // ---- v row -> int16 cache (spec/layers.rs:76-87)
+        const long long r = row - n_q - n_kvrows;
+        const int t = (int)(r / a.n_kv), h = (int)(r % a.n_kv);
+        const float inv = a.v_inv[h];
+        const float* src = a.v + ((size_t)t * a.n_kv + h) * HD;
+        int16_t* dst = a.vq + ((size_t)(pos0 + t) * a.n_kv + h) * HD;
+#pragma unroll
+        for (int i = 0; i < PER; i++) {
+            const int idx = lane * PER + i;
+            int q = f2i_sat(fmul(src[idx], inv));
+            dst[idx] = (int16_t)max(-32767, min(32767, q));
+        }
+        return;
+    }
+    const bool is_q = row < n_q;
+    int t, h;
+    const float *src, *wn;
+    if (is_q) {
+        t = (int)(row / a.n_h); h = (int)(row % a.n_h);
+        src = a.qg + ((size_t)t * a.n_h + h) * 2 * HD;
+        wn = a.q_norm;
+    } else {
+        const long long r = row - n_q;
+        t = (int)(r / a.n_kv); h = (int)(r % a.n_kv);
+        src = a.k + ((size_t)t * a.n_kv + h) * HD;
+        wn = a.k_norm;
+    }
+    // rmsnorm over hd (spec/prim.rs:176-185): lane owns PER consecutive values
+    float x[PER], sq[PER];
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        x[i] = src[lane * PER + i];
+        sq[i] = fmul(x[i], x[i]);
+    }
+    const float ss = fold_lanes<32>(fold_run<PER>(sq));
+    const float inv_rms = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)HD), a.eps)));
+    float* buf = rowbuf[wib];
+#pragma unroll
+    for (int i = 0; i < PER; i++) buf[lane * PER + i] = fmul(fmul(x[i], inv_rms), wn[lane * PER + i]);
+    __syncwarp();
+    // rope on the first `rot` dims, neox pairing (spec/layers.rs:5-13)
+    const int half = a.rot >> 1;
+    const float* rc = a.rope_cos + (size_t)(pos0 + t) * half;
+    const float* rs = a.rope_sin + (size_t)(pos0 + t) * half;
+    for (int p = lane; p < half; p += 32) {
+        const float u = buf[p], w = buf[p + half];
+        const float c = rc[p], s = rs[p];
+        buf[p] = fsub(fmul(u, c), fmul(w, s));
+        buf[p + half] = fadd(fmul(w, c), fmul(u, s));
+    }
+    __syncwarp();
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        float v = buf[lane * PER + i];
+        if (is_q) v = fmul(v, a.qscale);
+        x[i] = v;
+        amax = fmaxf(amax, fabsf(v));
+    }
+    amax = max_lanes(amax);
+    const float s = (amax == 0.0f) ? 1.0f : fdiv(amax, 127.0f);   // spec/quant.rs:7-16
+    const float inv = fdiv(1.0f, s);
+    int8_t* dst = is_q ? a.qq + ((size_t)t * a.n_h + h) * HD : a.kq + ((size_t)(pos0 + t) * a.n_kv + h) * HD;
+#pragma unroll
+    for (int i = 0; i < PER; i++) dst[lane * PER + i] = (int8_t)quant_code(x[i], inv);
+    if (lane == 0) {
+        if (is_q) a.sq[(size_t)t * a.n_h + h] = s;
+        else a.sk[(size_t)(pos0 + t) * a.n_kv + h] = s;
+    }
+}
+
+// Shared tile of KT keys with rows padded by 16 bytes: 128-bit reads by threads that own consecutive keys then fall into
+// distinct banks.
+template <int HD>
+struct KTile {
+    static constexpr int STRIDE = HD + 16;
+    __device__ static void load(int8_t* tile, float* sks, const AttnArgs& a, int kvh, int key0, int nkeys) {
+        constexpr int VEC = HD / 16;
+        for (int i = threadIdx.x; i < KT * VEC; i += ATT_THREADS) {
+            const int j = i / VEC, v = i % VEC;
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (j < nkeys)
+                val = *reinterpret_cast<const uint4*>(a.kq + ((size_t)(key0 + j) * a.n_kv + kvh) * HD + v * 16);
+            *reinterpret_cast<uint4*>(tile + j * STRIDE + v * 16) = val;
+        }
+        for (int j = threadIdx.x; j < KT; j += ATT_THREADS) sks[j] = j < nkeys ? a.sk[(size_t)(key0 + j) * a.n_kv + kvh] : 0.0f;
+    }
+    __device__ __forceinline__ static int dot(const int8_t* tile, int j, const int8_t* q) {
+        int acc = 0;
+#pragma unroll
+        for (int v = 0; v < HD / 16; v++) {
+            const uint4 kk = *reinterpret_cast<const uint4*>(tile + j * STRIDE + v * 16);
+            const uint4 qv = *reinterpret_cast<const uint4*>(q + v * 16);
+            acc = __dp4a((int)kk.x, (int)qv.x, acc);
+            acc = __dp4a((int)kk.y, (int)qv.y, acc);
+            acc = __dp4a((int)kk.z, (int)qv.z, acc);
+            acc = __dp4a((int)kk.w, (int)qv.w, acc);
+        }
+        return acc;
+    }
+};
+
+// key range of this CTA for token t: [k0, k1) within [0, pos0 + t]
+__device__ __forceinline__ void key_range(const AttnArgs& a, int t, int& k0, int& k1) {
+    const int total = base_pos(a) + t + 1;
+    k0 = blockIdx.x * a.keys_per_split;
+    k1 = min(total, k0 + a.keys_per_split);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS) k_attn_max(const AttnArgs a) {
+    __shared__ __align__(16) int8_t ktile[KT * KTile<HD>::STRIDE];
+    __shared__ __align__(16) int8_t qs[MAX_REP * HD];
+    __shared__ float sks[KT];
+    __shared__ float sqs[MAX_REP];
+    __shared__ unsigned best[MAX_REP];
+    const int kvh = blockIdx.y, t = blockIdx.z;
+    int k0, k1;
+    key_range(a, t, k0, k1);
+    if (k0 >= k1) return;
+    const int rep = a.rep;
+    for (int i = threadIdx.x; i < rep * HD / 16; i += ATT_THREADS)
+        reinterpret_cast<uint4*>(qs)[i] =
+            reinterpret_cast<const uint4*>(a.qq + ((size_t)t * a.n_h + (size_t)kvh * rep) * HD)[i];
+    if (threadIdx.x < rep) {
+        sqs[threadIdx.x] = a.sq[(size_t)t * a.n_h + kvh * rep + threadIdx.x];
+        best[threadIdx.x] = 0u;
+    }
+    const int j = threadIdx.x % KT, part = threadIdx.x / KT;   // 4 parts share the heads
+    unsigned mine[MAX_REP / 4 + 1];
+#pragma unroll
+    for (int i = 0; i < MAX_REP / 4 + 1; i++) mine[i] = 0u;
+    for (int key0 = k0; key0 < k1; key0 += KT) {
+        const int nkeys = min(KT, k1 - key0);
+        __syncthreads();
+        KTile<HD>::load(ktile, sks, a, kvh, key0, nkeys);
+        __syncthreads();
+        if (j < nkeys) {
+#pragma unroll
+            for (int i = 0; i < MAX_REP / 4 + 1; i++) {
+                const int r = part + 4 * i;
+                if (r < rep) {
+                    const int d = KTile<HD>::dot(ktile, j, qs + r * HD);
+                    const float s = fmul(fmul((float)d, sqs[r]), sks[j]);
+                    mine[i] = max(mine[i], f32_key(s));
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_REP / 4 + 1; i++) {
+        const int r = part + 4 * i;
+        if (r < rep && mine[i]) atomicMax(&best[r], mine[i]);
+    }
+    __syncthreads();
+    if (threadIdx.x < rep && best[threadIdx.x])
+        atomicMax(a.mxkey + (size_t)t * a.n_h + kvh * rep + threadIdx.x, best[threadIdx.x]);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
+    static_assert(HD <= ATT_THREADS, "one thread per value dimension");
+    __shared__ __align__(16) int8_t ktile[KT * KTile<HD>::STRIDE];
+    __shared__ __align__(16) int8_t qs[MAX_REP * HD];
+    __shared__ float sks[KT];
+    __shared__ float sqs[MAX_REP];
+    __shared__ float mxs[MAX_REP];
+    __shared__ int pq[MAX_REP][KT];
+    __shared__ long long den_sh[MAX_REP];
+    const int kvh = blockIdx.y, t = blockIdx.z;
+    int k0, k1;
+    key_range(a, t, k0, k1);
+    if (k0 >= k1) return;
+    const int rep = a.rep;
+    for (int i = threadIdx.x; i < rep * HD / 16; i += ATT_THREADS)
+        reinterpret_cast<uint4*>(qs)[i] =
+            reinterpret_cast<const uint4*>(a.qq + ((size_t)t * a.n_h + (size_t)kvh * rep) * HD)[i];
+    if (threadIdx.x < rep) {
+        const size_t hh = (size_t)t * a.n_h + kvh * rep + threadIdx.x;
+        sqs[threadIdx.x] = a.sq[hh];
+        mxs[threadIdx.x] = key_f32(a.mxkey[hh]);
+        den_sh[threadIdx.x] = 0;
+    }
+    const int j = threadIdx.x % KT, part = threadIdx.x / KT;
+    const int d = threadIdx.x;   // value dimension owned in the P.V phase
+    long long num[MAX_REP];
+#pragma unroll
+    for (int r = 0; r < MAX_REP; r++) num[r] = 0;
+    for (int key0 = k0; key0 < k1; key0 += KT) {
+        const int nkeys = min(KT, k1 - key0);
+        __syncthreads();
+        KTile<HD>::load(ktile, sks, a, kvh, key0, nkeys);
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < MAX_REP / 4 + 1; i++) {
+            const int r = part + 4 * i;
+            if (r < rep) {
+                int p = 0;
+                if (j < nkeys) {
+                    const int dt = KTile<HD>::dot(ktile, j, qs + r * HD);
+                    const float s = fmul(fmul((float)dt, sqs[r]), sks[j]);
+                    p = f2i_sat(fmul(exp_f(fsub(s, mxs[r])), 16777216.0f));
+                }
+                pq[r][j] = p;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < rep) {
+            long long s = 0;
+            for (int q = 0; q < nkeys; q++) s += pq[threadIdx.x][q];
+            den_sh[threadIdx.x] += s;
+        }
+        if (d < HD) {
+            const int16_t* vcol = a.vq + ((size_t)key0 * a.n_kv + kvh) * HD + d;
+            const size_t vstride = (size_t)a.n_kv * HD;
+            for (int q = 0; q < nkeys; q++) {
+                const int vv = vcol[q * vstride];
+#pragma unroll
+                for (int r = 0; r < MAX_REP; r++)
+                    if (r < rep) num[r] += (long long)pq[r][q] * (long long)vv;
+            }
+        }
+    }
+    __syncthreads();
+    if (a.nsplit == 1) {
+        if (d < HD) {
+            const float vs = a.v_scale[kvh];
+#pragma unroll
+            for (int r = 0; r < MAX_REP; r++) {
+                if (r < rep) {
+                    const int h = kvh * rep + r;
+                    const float gate = a.qg[((size_t)t * a.n_h + h) * 2 * HD + HD + d];
+                    const float val = fmul(fdiv(i64_to_f32(num[r]), i64_to_f32(den_sh[r])), vs);
+                    a.o[((size_t)t * a.n_h + h) * HD + d] = fmul(val, sigmoid_f(gate));
+                }
+            }
+        }
+    } else {
+        if (d < HD) {
+#pragma unroll
+            for (int r = 0; r < MAX_REP; r++)
+                if (r < rep)
+                    atomicAdd(reinterpret_cast<unsigned long long*>(a.num + ((size_t)t * a.n_h + kvh * rep + r) * HD + d),
+                              (unsigned long long)num[r]);
+        }
+        if (threadIdx.x < rep)
+            atomicAdd(reinterpret_cast<unsigned long long*>(a.den + (size_t)t * a.n_h + kvh * rep + threadIdx.x),
+                      (unsigned long long)den_sh[threadIdx.x]);
+    }
+}
+
+template <int HD>
+__global__ void k_attn_fin(const AttnArgs a) {
+    const size_t row = blockIdx.x;   // t * n_h + h
+    const int d = threadIdx.x;
+    const int t = (int)(row / a.n_h), h = (int)(row % a.n_h);
+    const float vs = a.v_scale[h / a.rep];
+    const float gate = a.qg[((size_t)t * a.n_h + h) * 2 * HD + HD + d];
+    const float val = fmul(fdiv(i64_to_f32(a.num[row * HD + d]), i64_to_f32(a.den[row])), vs);
+    a.o[row * HD + d] = fmul(val, sigmoid_f(gate));
+}
+
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+struct ScratchMap {
+    size_t qq, sq, mx, den, num, total;
+};
+static ScratchMap scratch_map(int M, int n_h, int hd) {
+    ScratchMap s;
+    const size_t rows = (size_t)M * n_h;
+    s.qq = 0;
+    s.sq = align256(rows * hd);
+    s.mx = s.sq + align256(rows * 4);
+    s.den = s.mx + align256(rows * 4);
+    s.num = s.den + align256(rows * 8);
+    s.total = s.num + align256(rows * hd * 8);
+    return s;
+}
+
+template <int HD>
+static void run_attention(AttnArgs a, void* scratch, int max_total_keys, cudaStream_t q) {
+    const ScratchMap sm = scratch_map(a.M, a.n_h, HD);
+    uint8_t* base = static_cast<uint8_t*>(scratch);
+    a.qq = reinterpret_cast<int8_t*>(base + sm.qq);
+    a.sq = reinterpret_cast<float*>(base + sm.sq);
+    a.mxkey = reinterpret_cast<unsigned*>(base + sm.mx);
+    a.den = reinterpret_cast<long long*>(base + sm.den);
+    a.num = reinterpret_cast<long long*>(base + sm.num);
+    // key split: aim at ~4 CTAs per SM in total, whole tiles per split (a choice by shape only)
+    const int tiles = (max_total_keys + KT - 1) / KT;
+    int want = (4 * sm_count()) / (a.n_kv * a.M);
+    int nsplit = want < 1 ? 1 : (want > tiles ? tiles : want);
+    const int tiles_per_split = (tiles + nsplit - 1) / nsplit;
+    nsplit = (tiles + tiles_per_split - 1) / tiles_per_split;
+    a.nsplit = nsplit;
+    a.keys_per_split = tiles_per_split * KT;
+
+    DETB_CUDA_OK(cudaMemsetAsync(base + sm.mx, 0, sm.den - sm.mx, q));
+    if (nsplit > 1) DETB_CUDA_OK(cudaMemsetAsync(base + sm.den, 0, sm.total - sm.den, q));
+    const long long rows = (long long)a.M * (a.n_h + 2 * a.n_kv);
+    k_attn_prep<HD><<<(unsigned)((rows + 7) / 8), 256, 0, q>>>(a);
+    const dim3 grid(nsplit, a.n_kv, a.M);
+    k_attn_max<HD><<<grid, ATT_THREADS, 0, q>>>(a);
+    k_attn_acc<HD><<<grid, ATT_THREADS, 0, q>>>(a);
+    if (nsplit > 1) k_attn_fin<HD><<<a.M * a.n_h, HD, 0, q>>>(a);
+    DETB_CUDA_OK(cudaGetLastError());
+}
+
+static void attention_entry(const det_attn_layer* L, const det_kv_cache* kv, const float* qg, const float* k,
+                            const float* v, const float* rope_cos, const float* rope_sin, int rot, float eps, int M,
+                            int pos0, const int* pos0_dev, int max_pos, int n_h, int n_kv, int hd, float* o,
+                            void* scratch, cudaStream_t st) {
+    if (M <= 0) return;
+    DETB_REQUIRE(n_kv > 0 && n_h % n_kv == 0 && n_h / n_kv <= MAX_REP, "n_h / n_kv must be an integer <= 8");
+    DETB_REQUIRE(hd == 64 || hd == 256, "head_dim must be 64 or 256 (1/sqrt(hd) has to be a power of two, cpu.rs:225-230)");
+    DETB_REQUIRE(rot >= 0 && rot <= hd && rot % 2 == 0, "bad rotary dimension");
+    DETB_REQUIRE(max_pos + M <= kv->capacity, "positions exceed the cache capacity");
+    AttnArgs a;
+    a.q_norm = L->q_norm; a.k_norm = L->k_norm; a.v_scale = L->v_scale; a.v_inv = L->v_inv_scale;
+    a.kq = kv->kq; a.sk = kv->sk; a.vq = kv->vq;
+    a.qg = qg; a.k = k; a.v = v; a.rope_cos = rope_cos; a.rope_sin = rope_sin;
+    a.rot = rot; a.eps = eps;
+    a.qscale = hd == 256 ? 0.0625f : 0.125f;   // fp32(1/sqrt(hd)), exact
+    a.M = M; a.n_h = n_h; a.n_kv = n_kv; a.rep = n_h / n_kv;
+    a.pos0 = pos0; a.pos0_dev = pos0_dev; a.o = o;
+    cudaStream_t q = queue_of(st);
+    if (hd == 256) run_attention<256>(a, scratch, max_pos + M, q);
+    else run_attention<64>(a, scratch, max_pos + M, q);
+}
+
+}  // namespace detb
+
+using namespace detb;
+
+extern "C" {
+
+size_t det_attn_scratch_bytes(int M, int n_h, int hd) { return scratch_map(M > 0 ? M : 1, n_h, hd).total; }
+
+void det_attention(const det_attn_layer* L, const det_kv_cache* kv, const float* qg, const float* k, const float* v,
+                   const float* rope_cos, const float* rope_sin, int rot, float eps, int M, int pos0, int n_h,
+                   int n_kv, int hd, float* o, void* scratch, cudaStream_t st) {
+    attention_entry(L, kv, qg, k, v, rope_cos, rope_sin, rot, eps, M, pos0, nullptr, pos0, n_h, n_kv, hd, o, scratch, st);
+}
+
+void det_attention_dev(const det_attn_layer* L, const det_kv_cache* kv, const float* qg, const float* k,
+                       const float* v, const float* rope_cos, const float* rope_sin, int rot, float eps, int M,
+                       const int* pos0_dev, int max_pos, int n_h, int n_kv, int hd, float* o, void* scratch,
+                       cudaStream_t st) {
+    attention_entry(L, kv, qg, k, v, rope_cos, rope_sin, rot, eps, M, 0, pos0_dev, max_pos, n_h, n_kv, hd, o, scratch, st);
+}
+
+}  // extern "C"

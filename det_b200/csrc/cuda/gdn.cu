@@ -1,0 +1,265 @@
+// Gated DeltaNet (docs/SPEC.md §5.2, spec/layers.rs:88-147, cpu.rs:293-391).  Replaces kernels/cuda/gdn.cu behind
+// det_gdn / det_gdn_ex / det_gdn_scratch_bytes.
+//
+//   prep    causal conv (4 taps) + silu per channel, l2norm of q and k per k head (q scaled by QSCALE),
+//           beta = sigmoid(b), decay = exp_f(-(A * softplus_f(a + dt_bias))); one warp per (token, 128-channel head).
+//   recur   the strictly sequential state update.  A CTA owns 16 columns of one v head's S[dk][dv]; a column's 128
+//           rows are spread over 8 consecutive lanes (16 rows each) and stay in registers for the whole call.  Both
+//           contractions over dk are the spec tree: fold of the lane's aligned run, then xor offsets 1, 2, 4 across the
+//           8 lanes.  State enters and leaves through a shared-memory slab so global traffic stays coalesced.
+//   out     on = rmsnorm(o, norm) * silu_f(z) per (token, v head); the last three raw inputs become the conv state.
+#include "runtime.cuh"
+
+namespace detb {
+
+constexpr int DK = 128, DV = 128;          // fixed by the model family (asserted at the entry points)
+constexpr unsigned QSCALE_BITS = 0x3DB504F3u;   // fp32(1/sqrt(128)), spec/layers.rs:147
+
+struct GdnArgs {
+    const float *conv, *A, *dt_bias, *norm;
+    float *conv_state, *S;
+    const float *qkv, *z, *a, *b;
+    float eps;
+    int M, n_k, n_v, rep, conv_dim;
+    float* on;
+    // scratch
+    float* y;        // [M][conv_dim]: q (normalised, scaled) | k (normalised) | v
+    float* beta;     // [M][n_v]
+    float* decay;    // [M][n_v]
+    float* o;        // [M][n_v][DV] mixer output (gout when exported)
+    float* gin;      // optional
+};
+
+// input of channel c at time tau (tau < 0 reaches into the conv state, which holds times -3, -2, -1)
+__device__ __forceinline__ float conv_in(const GdnArgs& g, int tau, int c) {
+    return tau < 0 ? g.conv_state[(size_t)(3 + tau) * g.conv_dim + c] : g.qkv[(size_t)tau * g.conv_dim + c];
+}
+
+__global__ void __launch_bounds__(128) k_gdn_prep(const GdnArgs g) {
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int t = blockIdx.y;
+    const int heads = 2 * g.n_k + g.n_v;     // 128-channel slices of conv_dim
+    const int head = blockIdx.x * 4 + wib;
+    if (head < heads) {
+        const int c0 = head * 128 + lane * 4;
+        float v[4], sq[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int c = c0 + e;
+            const float4 w = *reinterpret_cast<const float4*>(g.conv + (size_t)c * 4);
+            // ((w0*x[t-3] + w1*x[t-2]) + w2*x[t-1]) + w3*x[t]   (spec/layers.rs:135-140)
+            float acc = fadd(fmul(w.x, conv_in(g, t - 3, c)), fmul(w.y, conv_in(g, t - 2, c)));
+            acc = fadd(acc, fmul(w.z, conv_in(g, t - 1, c)));
+            acc = fadd(acc, fmul(w.w, conv_in(g, t, c)));
+            v[e] = silu_f(acc);
+            sq[e] = fmul(v[e], v[e]);
+        }
+        if (head < 2 * g.n_k) {
+            // l2norm over the head's 128 channels (spec/prim.rs:187-194)
+            const float ss = fold_lanes<32>(fold_run<4>(sq));
+            const float inv = fdiv(1.0f, fsqrt(fadd(ss, g.eps)));
+            const bool is_q = head < g.n_k;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                v[e] = fmul(v[e], inv);
+                if (is_q) v[e] = fmul(v[e], __uint_as_float(QSCALE_BITS));
+            }
+        }
+        *reinterpret_cast<float4*>(g.y + (size_t)t * g.conv_dim + c0) = make_float4(v[0], v[1], v[2], v[3]);
+        if (g.gin) {
+            // gin[t][kh]: q[128] | k[128] | v[rep][128] | beta[rep] | decay[rep]   (cpu.rs:345-357)
+            const int gw = 2 * DK + g.rep * DV + 2 * g.rep;
+            float* row;
+            if (head < g.n_k) row = g.gin + ((size_t)t * g.n_k + head) * gw;
+            else if (head < 2 * g.n_k) row = g.gin + ((size_t)t * g.n_k + (head - g.n_k)) * gw + DK;
+            else {
+                const int vh = head - 2 * g.n_k;
+                row = g.gin + ((size_t)t * g.n_k + vh / g.rep) * gw + 2 * DK + (vh % g.rep) * DV;
+            }
+#pragma unroll
+            for (int e = 0; e < 4; e++) row[lane * 4 + e] = v[e];
+        }
+    }
+    // the last CTA row of the grid also produces beta and decay for this token
+    if (blockIdx.x == gridDim.x - 1) {
+        for (int h = threadIdx.x; h < g.n_v; h += blockDim.x) {
+            const float be = sigmoid_f(g.b[(size_t)t * g.n_v + h]);
+            const float sp = softplus_f(fadd(g.a[(size_t)t * g.n_v + h], g.dt_bias[h]));
+            const float de = exp_f(-fmul(g.A[h], sp));
+            g.beta[(size_t)t * g.n_v + h] = be;
+            g.decay[(size_t)t * g.n_v + h] = de;
+            if (g.gin) {
+                const int gw = 2 * DK + g.rep * DV + 2 * g.rep;
+                float* row = g.gin + ((size_t)t * g.n_k + h / g.rep) * gw + 2 * DK + g.rep * DV;
+                row[h % g.rep] = be;
+                row[g.rep + h % g.rep] = de;
+            }
+        }
+    }
+}
+
+constexpr int RC = 16;    // columns per CTA
+constexpr int RL = 8;     // lanes per column
+constexpr int RR = DK / RL;   // rows per lane (16)
+
+__global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
+    __shared__ float slab[DK][RC + 1];
+    const int h = blockIdx.x / (DV / RC);
+    const int j0 = (blockIdx.x % (DV / RC)) * RC;
+    const int kh = h / g.rep;
+    const int p = threadIdx.x % RL, jj = threadIdx.x / RL;
+    float* Sh = g.S + (size_t)h * DK * DV;
+
+    for (int i = threadIdx.x; i < DK * RC; i += RC * RL) slab[i / RC][i % RC] = Sh[(size_t)(i / RC) * DV + j0 + (i % RC)];
+    __syncthreads();
+    float s[RR];
+#pragma unroll
+    for (int i = 0; i < RR; i++) s[i] = slab[p * RR + i][jj];
+
+    const size_t ystride = g.conv_dim;
+    const float* qrow = g.y + (size_t)kh * DK + p * RR;
+    const float* krow = g.y + (size_t)g.n_k * DK + (size_t)kh * DK + p * RR;
+    const float* vptr = g.y + (size_t)2 * g.n_k * DK + (size_t)h * DV + j0 + jj;
+
+    float kq[2][2 * RR];   // [buffer][k rows | q rows]
+    float vv[2], be[2], de[2];
+    auto fetch = [&](int t, int b) {
+#pragma unroll
+        for (int i = 0; i < RR; i += 4) {
+            const float4 kk = *reinterpret_cast<const float4*>(krow + (size_t)t * ystride + i);
+            const float4 qq = *reinterpret_cast<const float4*>(qrow + (size_t)t * ystride + i);
+            kq[b][i] = kk.x; kq[b][i + 1] = kk.y; kq[b][i + 2] = kk.z; kq[b][i + 3] = kk.w;
+            kq[b][RR + i] = qq.x; kq[b][RR + i + 1] = qq.y; kq[b][RR + i + 2] = qq.z; kq[b][RR + i + 3] = qq.w;
+        }
+        vv[b] = vptr[(size_t)t * ystride];
+        be[b] = g.beta[(size_t)t * g.n_v + h];
+        de[b] = g.decay[(size_t)t * g.n_v + h];
+    };
+    fetch(0, 0);
+#pragma unroll 1
+    for (int t = 0; t < g.M; t += 2) {
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const int tt = t + b;
+            if (tt < g.M) {
+                if (tt + 1 < g.M) fetch(tt + 1, b ^ 1);
+                float prod[RR];
+#pragma unroll
+                for (int i = 0; i < RR; i++) {
+                    s[i] = fmul(s[i], de[b]);
+                    prod[i] = fmul(s[i], kq[b][i]);
+                }
+                const float kv_mem = fold_lanes<RL>(fold_run<RR>(prod));
+                const float delta = fmul(fsub(vv[b], kv_mem), be[b]);
+#pragma unroll
+                for (int i = 0; i < RR; i++) {
+                    s[i] = fadd(s[i], fmul(kq[b][i], delta));
+                    prod[i] = fmul(s[i], kq[b][RR + i]);
+                }
+                const float ov = fold_lanes<RL>(fold_run<RR>(prod));
+                if (p == 0) g.o[((size_t)tt * g.n_v + h) * DV + j0 + jj] = ov;
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < RR; i++) slab[p * RR + i][jj] = s[i];
+    __syncthreads();
+    for (int i = threadIdx.x; i < DK * RC; i += RC * RL) Sh[(size_t)(i / RC) * DV + j0 + (i % RC)] = slab[i / RC][i % RC];
+}
+
+// on = rmsnorm(o, norm, eps) * silu_f(z): one warp per (token, v head).  Extra CTAs past the rows move the conv state.
+__global__ void __launch_bounds__(128) k_gdn_out(const GdnArgs g, int row_blocks) {
+    if ((int)blockIdx.x >= row_blocks) {
+        // conv state <- the last three raw inputs (times M-3 .. M-1); each channel is read fully before it is written
+        const int c = (blockIdx.x - row_blocks) * 128 + threadIdx.x;
+        if (c < g.conv_dim) {
+            float keep[3];
+#pragma unroll
+            for (int r = 0; r < 3; r++) keep[r] = conv_in(g, g.M - 3 + r, c);
+#pragma unroll
+            for (int r = 0; r < 3; r++) g.conv_state[(size_t)r * g.conv_dim + c] = keep[r];
+        }
+        return;
+    }
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const long long row = (long long)blockIdx.x * 4 + wib;   // t * n_v + h
+    if (row >= (long long)g.M * g.n_v) return;
+    const float* o = g.o + row * DV + lane * 4;
+    float v[4], sq[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        v[e] = o[e];
+        sq[e] = fmul(v[e], v[e]);
+    }
+    const float ss = fold_lanes<32>(fold_run<4>(sq));
+    const float inv = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)DV), g.eps)));
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const float yn = fmul(fmul(v[e], inv), g.norm[lane * 4 + e]);
+        g.on[row * DV + lane * 4 + e] = fmul(yn, silu_f(g.z[row * DV + lane * 4 + e]));
+    }
+}
+
+static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
+struct GdnScratch {
+    size_t y, beta, decay, o, total;
+};
+static GdnScratch gdn_scratch(int M, int n_k, int n_v) {
+    GdnScratch s;
+    const size_t conv_dim = (size_t)2 * n_k * DK + (size_t)n_v * DV;
+    s.y = 0;
+    s.beta = up256((size_t)M * conv_dim * 4);
+    s.decay = s.beta + up256((size_t)M * n_v * 4);
+    s.o = s.decay + up256((size_t)M * n_v * 4);
+    s.total = s.o + up256((size_t)M * n_v * DV * 4);
+    return s;
+}
+
+}  // namespace detb
+
+using namespace detb;
+
+extern "C" {
+
+size_t det_gdn_scratch_bytes(int M, int n_k, int n_v, int dk, int dv) {
+    (void)dk; (void)dv;
+    return gdn_scratch(M > 0 ? M : 1, n_k, n_v).total;
+}
+
+void det_gdn_ex(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a,
+                const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
+                float* gin, float* gout, cudaStream_t st) {
+    if (M <= 0) return;
+    DETB_REQUIRE(dk == DK && dv == DV, "Gated DeltaNet kernels are built for dk = dv = 128");
+    DETB_REQUIRE(n_k > 0 && n_v % n_k == 0, "n_v must be a multiple of n_k");
+    const GdnScratch sm = gdn_scratch(M, n_k, n_v);
+    uint8_t* base = static_cast<uint8_t*>(scratch);
+    GdnArgs g;
+    g.conv = L->conv; g.A = L->A; g.dt_bias = L->dt_bias; g.norm = L->norm;
+    g.conv_state = S->conv_state; g.S = S->S;
+    g.qkv = qkv; g.z = z; g.a = a; g.b = b;
+    g.eps = eps; g.M = M; g.n_k = n_k; g.n_v = n_v; g.rep = n_v / n_k;
+    g.conv_dim = 2 * n_k * DK + n_v * DV;
+    g.on = on;
+    g.y = reinterpret_cast<float*>(base + sm.y);
+    g.beta = reinterpret_cast<float*>(base + sm.beta);
+    g.decay = reinterpret_cast<float*>(base + sm.decay);
+    g.o = gout ? gout : reinterpret_cast<float*>(base + sm.o);
+    g.gin = gin;
+    cudaStream_t q = queue_of(st);
+    const int heads = 2 * n_k + n_v;
+    k_gdn_prep<<<dim3((heads + 3) / 4, M), 128, 0, q>>>(g);
+    k_gdn_recur<<<n_v * (DV / RC), RC * RL, 0, q>>>(g);
+    const int row_blocks = (int)(((long long)M * n_v + 3) / 4);
+    k_gdn_out<<<row_blocks + (g.conv_dim + 127) / 128, 128, 0, q>>>(g, row_blocks);
+    DETB_CUDA_OK(cudaGetLastError());
+}
+
+void det_gdn(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a,
+             const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
+             cudaStream_t st) {
+    det_gdn_ex(L, S, qkv, z, a, b, eps, M, n_k, n_v, dk, dv, on, scratch, nullptr, nullptr, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,273 @@
+// Deterministic sampling (docs/SPEC.md §5.5, spec/sample.rs:16-87).  Replaces kernels/cuda/sample.cu behind
+// det_sample / det_sample_topkp / det_sample_scratch_bytes.
+//
+// After w_i = rint(exp_f(l_i * inv_temp - max) * 2^32) everything is exact integer arithmetic, so any parallel
+// decomposition is legal.  The candidate order (weight descending, index ascending) is never materialised: the kept set
+// is a prefix of that order, i.e. "w > w*" plus the first e elements (by index) with w == w*.  (w*, e) comes from a
+// three-pass radix select on the 33-bit weights with per-digit (count, sum) histograms in shared memory, which finds the
+// element where the first of the two prefix conditions — k elements taken, or the integer mass reaching
+// ceil(p24 * total / 2^24) — becomes true.  The draw then walks the kept weights in index order.
+// One CTA of 1024 threads per row.
+#include "runtime.cuh"
+
+namespace detb {
+
+constexpr int ST = 1024;
+constexpr int SW = ST / 32;
+constexpr int DIGITS = 2048;
+typedef unsigned long long u64;
+
+__device__ __forceinline__ u64 shfl_u64(u64 v, int src) {
+    unsigned lo = (unsigned)v, hi = (unsigned)(v >> 32);
+    lo = __shfl_sync(FULL, lo, src);
+    hi = __shfl_sync(FULL, hi, src);
+    return ((u64)hi << 32) | lo;
+}
+__device__ __forceinline__ u64 shfl_up_u64(u64 v, int d) {
+    unsigned lo = (unsigned)v, hi = (unsigned)(v >> 32);
+    lo = __shfl_up_sync(FULL, lo, d);
+    hi = __shfl_up_sync(FULL, hi, d);
+    return ((u64)hi << 32) | lo;
+}
+__device__ __forceinline__ u64 warp_sum_u64(u64 v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        unsigned lo = (unsigned)v, hi = (unsigned)(v >> 32);
+        lo = __shfl_xor_sync(FULL, lo, off);
+        hi = __shfl_xor_sync(FULL, hi, off);
+        v += ((u64)hi << 32) | lo;
+    }
+    return v;
+}
+__device__ __forceinline__ u64 warp_incl_scan_u64(u64 v, int lane) {
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const u64 o = shfl_up_u64(v, d);
+        if (lane >= d) v += o;
+    }
+    return v;
+}
+// block-wide sum; every thread returns the total
+__device__ u64 block_sum_u64(u64 v, u64* sh /* [SW] */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum_u64(v);
+    __syncthreads();
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    u64 t = sh[lane];   // SW == 32
+    return warp_sum_u64(t);
+}
+
+__device__ __forceinline__ u64 weight_of(float logit, float inv_temp, float mx) {
+    return __float2ull_rn(fmul(exp_f(fsub(fmul(logit, inv_temp), mx)), 4294967296.0f));
+}
+
+struct Cut {
+    int filtered;   // 0: every token kept
+    u64 wstar;      // kept: w > wstar, plus the first `e` (by index) with w == wstar
+    u64 e;
+    u64 total;      // sum of kept weights
+};
+
+// The draw: smallest kept index whose inclusive prefix of kept weights exceeds u = z % total.
+// Warp `w` owns the contiguous index range [w * seg, (w + 1) * seg); W(i) returns the weight of index i.
+template <class WF>
+__device__ int walk(const WF& W, int V, const Cut& cut, u64 z, u64* sh64, unsigned* sh32) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int seg = (((V + SW - 1) / SW) + 31) & ~31;
+    const int lo = warp * seg, hi = min(V, lo + seg);
+    // equal-weight rank base per warp
+    unsigned eq = 0;
+    if (cut.filtered)
+        for (int i = lo + lane; i < hi; i += 32) eq += (W(i) == cut.wstar) ? 1u : 0u;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) eq += __shfl_xor_sync(FULL, eq, off);
+    __syncthreads();
+    if (lane == 0) sh32[warp] = eq;
+    __syncthreads();
+    u64 eq_base = 0;
+    for (int w = 0; w < warp; w++) eq_base += sh32[w];
+    // kept mass per warp
+    auto kept_weight = [&](int i, u64& eq_seen) -> u64 {
+        // called by all lanes of the warp for indices i = base + lane in lockstep
+        const bool in = i < hi;
+        const u64 wv = in ? W(i) : 0;
+        if (!cut.filtered) return wv;
+        const bool is_eq = in && wv == cut.wstar;
+        const unsigned mask = __ballot_sync(FULL, is_eq);
+        const u64 rank = eq_seen + __popc(mask & ((1u << lane) - 1u));
+        eq_seen += __popc(mask);
+        if (!in) return 0;
+        if (wv > cut.wstar) return wv;
+        return (is_eq && rank < cut.e) ? wv : 0;
+    };
+    u64 mass = 0, seen = eq_base;
+    for (int b = lo; b < lo + seg; b += 32) mass += kept_weight(b + lane, seen);
+    mass = warp_sum_u64(mass);
+    __syncthreads();
+    if (lane == 0) sh64[warp] = mass;
+    __syncthreads();
+    const u64 u = z % cut.total;
+    u64 before = 0;
+    int target = -1;
+    for (int w = 0; w < SW; w++) {
+        const u64 m = sh64[w];
+        if (target < 0 && before + m > u) target = w;
+        if (target < 0) before += m;
+    }
+    __syncthreads();
+    int result = -1;
+    if (warp == target) {
+        u64 run = before;
+        seen = eq_base;
+        for (int b = lo; b < lo + seg && result < 0; b += 32) {
+            const u64 kw = kept_weight(b + lane, seen);
+            const u64 incl = warp_incl_scan_u64(kw, lane) + run;
+            const unsigned hit = __ballot_sync(FULL, kw != 0 && incl > u);
+            if (hit) result = b + __ffs(hit) - 1;
+            run = shfl_u64(incl, 31);
+        }
+        if (lane == 0) sh32[0] = (unsigned)result;
+    }
+    __syncthreads();
+    return (int)sh32[0];
+}
+
+__global__ void __launch_bounds__(ST) k_sample_plain(const float* __restrict__ logits, int V, float inv_temp,
+                                                     const u64* __restrict__ z, int* __restrict__ out) {
+    __shared__ float shf[32];
+    __shared__ u64 sh64[SW];
+    __shared__ unsigned sh32[SW];
+    const float* row = logits + (size_t)blockIdx.x * V;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += ST) mx = fmaxf(mx, fmul(row[i], inv_temp));
+    mx = max_block<SW>(mx, shf);
+    u64 part = 0;
+    for (int i = threadIdx.x; i < V; i += ST) part += weight_of(row[i], inv_temp, mx);
+    Cut cut;
+    cut.filtered = 0; cut.wstar = 0; cut.e = 0;
+    cut.total = block_sum_u64(part, sh64);
+    auto W = [&](int i) { return weight_of(row[i], inv_temp, mx); };
+    const int r = walk(W, V, cut, z[blockIdx.x], sh64, sh32);
+    if (threadIdx.x == 0) out[blockIdx.x] = r;
+}
+
+__global__ void __launch_bounds__(ST) k_sample_topkp(const float* __restrict__ logits, int V, float inv_temp,
+                                                     int use_k, u64 top_k, int use_p, u64 p24,
+                                                     const u64* __restrict__ z, int* __restrict__ out,
+                                                     u64* __restrict__ wbuf_all) {
+    __shared__ float shf[32];
+    __shared__ u64 sh64[SW];
+    __shared__ unsigned sh32[SW];
+    __shared__ unsigned cnt[DIGITS];
+    __shared__ u64 sum[DIGITS];
+    __shared__ u64 sel[6];   // prefix value, k_left, s_left, sum_gt, cnt_sel, found
+    const float* row = logits + (size_t)blockIdx.x * V;
+    u64* wbuf = wbuf_all + (size_t)blockIdx.x * V;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += ST) mx = fmaxf(mx, fmul(row[i], inv_temp));
+    mx = max_block<SW>(mx, shf);
+    u64 part = 0;
+    for (int i = threadIdx.x; i < V; i += ST) {
+        const u64 wv = weight_of(row[i], inv_temp, mx);
+        wbuf[i] = wv;
+        part += wv;
+    }
+    const u64 total = block_sum_u64(part, sh64);
+    if (threadIdx.x == 0) {
+        // thresh = ceil(total * p24 / 2^24)  (spec/sample.rs:60-62), 128-bit intermediate
+        const unsigned __int128 prod = (unsigned __int128)total * p24 + ((((unsigned __int128)1) << 24) - 1);
+        sel[0] = 0;
+        sel[1] = use_k ? top_k : (u64)V;
+        sel[2] = (u64)(prod >> 24);
+        sel[3] = 0;
+    }
+    __syncthreads();
+    // three 11-bit digits, most significant first: bits [32:22], [21:11], [10:0]
+    for (int pass = 0; pass < 3; pass++) {
+        const int shift = 22 - 11 * pass;
+        for (int i = threadIdx.x; i < DIGITS; i += ST) { cnt[i] = 0; sum[i] = 0; }
+        __syncthreads();
+        const u64 prefix = sel[0];
+        for (int i = threadIdx.x; i < V; i += ST) {
+            const u64 wv = wbuf[i];
+            if (pass == 0 || (wv >> (shift + 11)) == prefix) {
+                const unsigned d = (unsigned)(wv >> shift) & (DIGITS - 1);
+                atomicAdd(&cnt[d], 1u);
+                atomicAdd(&sum[d], wv);
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            u64 k_left = sel[1], s_left = sel[2], sum_gt = sel[3];
+            int chosen = 0;
+            for (int d = DIGITS - 1; d >= 0; d--) {
+                const unsigned c = cnt[d];
+                if (!c) continue;
+                if ((u64)c >= k_left || (use_p && sum[d] >= s_left)) { chosen = d; break; }
+                k_left -= c;
+                s_left -= sum[d];
+                sum_gt += sum[d];
+                chosen = d;   // stays the lowest non-empty digit when nothing triggers (cannot happen for valid input)
+            }
+            sel[0] = (prefix << 11) | (u64)chosen;
+            sel[1] = k_left; sel[2] = s_left; sel[3] = sum_gt;
+            sel[4] = cnt[chosen];
+        }
+        __syncthreads();
+    }
+    Cut cut;
+    cut.filtered = 1;
+    cut.wstar = sel[0];
+    {
+        const u64 k_left = sel[1], s_left = sel[2], n_eq = sel[4];
+        u64 e = n_eq;
+        if (use_k && k_left < e) e = k_left;
+        if (use_p) {
+            u64 ep;
+            if (s_left == 0) ep = 1;
+            else if (cut.wstar == 0) ep = n_eq;
+            else ep = (s_left + cut.wstar - 1) / cut.wstar;
+            if (ep < e) e = ep;
+        }
+        cut.e = e;
+        cut.total = sel[3] + e * cut.wstar;
+    }
+    auto W = [&](int i) { return wbuf[i]; };
+    const int r = walk(W, V, cut, z[blockIdx.x], sh64, sh32);
+    if (threadIdx.x == 0) out[blockIdx.x] = r;
+}
+
+}  // namespace detb
+
+using namespace detb;
+
+extern "C" {
+
+size_t det_sample_scratch_bytes(int M, int V) { return (size_t)(M > 0 ? M : 1) * (size_t)V * sizeof(u64); }
+
+void det_sample(const float* logits, int M, int V, float inv_temp, const unsigned long long* z, int* out,
+                cudaStream_t st) {
+    if (M <= 0) return;
+    k_sample_plain<<<M, ST, 0, queue_of(st)>>>(logits, V, inv_temp, z, out);
+    DETB_CUDA_OK(cudaGetLastError());
+}
+
+void det_sample_topkp(const float* logits, int M, int V, float inv_temp, int top_k, float top_p,
+                      const unsigned long long* z, int* out, void* scratch, cudaStream_t st) {
+    if (M <= 0) return;
+    const int use_k = top_k > 0 && top_k < V;
+    const int use_p = top_p < 1.0f;
+    if (!use_k && !use_p) {
+        det_sample(logits, M, V, inv_temp, z, out, st);
+        return;
+    }
+    // p24 = rint(top_p * 2^24) in binary64; negative values (and NaN) become 0, as Rust's `as u128` does
+    double pr = __builtin_nearbyint((double)top_p * 16777216.0);
+    const u64 p24 = (pr != pr || pr <= 0.0) ? 0 : (u64)pr;
+    k_sample_topkp<<<M, ST, 0, queue_of(st)>>>(logits, V, inv_temp, use_k, (u64)(top_k > 0 ? top_k : 0), use_p, p24, z,
+                                                out, static_cast<u64*>(scratch));
+    DETB_CUDA_OK(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -1,0 +1,196 @@
+// The op set a backend implements and its buffer type — the C++ mirror of det's plugin boundary
+// (crates/det/src/backend.rs:13-302: Buf<T>, GemmOut, AttnLayer, KvCache, GdnLayer, GdnState, GdnExport, Shape,
+// GdnShape, trait Backend).  Names, argument order and meaning follow the trait so that the driver
+// (model.hpp, the mirror of qwen35.rs / model.rs) and the conformance suites read like the reference's.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <utility>
+#include <vector>
+
+namespace det {
+
+class Backend;
+
+// backend.rs:13-134 — a typed span owned by a backend (released through it) or a borrowed view.
+template <class T>
+class Buf {
+  public:
+    Buf() = default;
+    Buf(Backend* owner, T* p, size_t len) : owner_(owner), p_(p), len_(len) {}
+    static Buf view(T* p, size_t len) { return Buf(nullptr, p, len); }
+    Buf(const Buf&) = delete;
+    Buf& operator=(const Buf&) = delete;
+    Buf(Buf&& o) noexcept { steal(o); }
+    Buf& operator=(Buf&& o) noexcept {
+        if (this != &o) {
+            release();
+            steal(o);
+        }
+        return *this;
+    }
+    ~Buf() { release(); }
+    T* ptr() const { return p_; }
+    T* ptr_at(size_t off) const { return p_ + off; }
+    size_t len() const { return len_; }
+    size_t bytes() const { return len_ * sizeof(T); }
+    Backend* owner() const { return owner_; }
+
+  private:
+    void steal(Buf& o) {
+        owner_ = o.owner_; p_ = o.p_; len_ = o.len_;
+        o.owner_ = nullptr; o.p_ = nullptr; o.len_ = 0;
+    }
+    void release();
+    Backend* owner_ = nullptr;
+    T* p_ = nullptr;
+    size_t len_ = 0;
+};
+
+// A quantized linear, possibly several tensors fused along N (backend.rs:229-231).
+struct Linear {
+    virtual ~Linear() = default;
+    std::vector<size_t> widths;
+    size_t k = 0;
+    int bits = 0;
+    size_t n() const {
+        size_t s = 0;
+        for (size_t w : widths) s += w;
+        return s;
+    }
+};
+// One tensor of det rows in host memory: `n` rows of det_row_bytes(bits, k) bytes (spec/tensor.rs:43-55).
+struct LinearPart {
+    const uint8_t* rows;
+    size_t n;
+};
+// One tensor of a seeded synthetic model: rows are produced by the generator in synth.hpp from (seed, tensor_id).
+struct SynthPart {
+    uint64_t tensor_id;
+    size_t n;
+};
+
+// backend.rs:136-142
+struct GemmOut {
+    enum Kind { Write, Accumulate, Parts } kind;
+    std::vector<const Buf<float>*> dst;
+    static GemmOut write(const Buf<float>& y) { return GemmOut{Write, {&y}}; }
+    static GemmOut accumulate(const Buf<float>& y) { return GemmOut{Accumulate, {&y}}; }
+    static GemmOut parts(std::vector<const Buf<float>*> d) { return GemmOut{Parts, std::move(d)}; }
+};
+
+// backend.rs:144-151
+struct AttnLayer {
+    const Buf<float>*q_norm, *k_norm, *v_scale, *v_inv_scale, *rope_cos, *rope_sin;
+};
+// backend.rs:153-162 (the Metal-only V planes are not carried)
+struct KvCache {
+    Buf<int8_t> kq;
+    Buf<float> sk;
+    Buf<int16_t> vq;
+    size_t capacity = 0;
+};
+// backend.rs:164-169
+struct GdnLayer {
+    const Buf<float>*conv, *a, *dt_bias, *norm;
+};
+// backend.rs:171-175
+struct GdnState {
+    Buf<float> conv_state;
+    Buf<float> s;
+};
+// backend.rs:177-182
+struct GdnExport {
+    const Buf<float>* gin = nullptr;
+    const Buf<float>* gout = nullptr;
+};
+// backend.rs:184-192
+struct Shape {
+    size_t m, pos0, n_h, n_kv, hd, rot;
+    float eps;
+};
+// backend.rs:194-201
+struct GdnShape {
+    size_t m, n_k, n_v, dk, dv;
+    float eps;
+};
+
+// backend.rs:203-302
+class Backend {
+  public:
+    virtual ~Backend() = default;
+    virtual std::string name() const = 0;
+
+    // raw storage (typed helpers below)
+    virtual void* alloc_bytes(size_t bytes) = 0;   // zero-filled
+    virtual void free_bytes(void* p) = 0;
+    virtual void write_bytes(void* dst, const void* host_src, size_t bytes) = 0;
+    virtual void read_bytes(const void* src, void* host_dst, size_t bytes) = 0;   // waits for the producers
+    virtual void zero_bytes(void* p, size_t bytes) = 0;
+    virtual void sync() = 0;
+
+    virtual std::unique_ptr<Linear> linear(const std::vector<LinearPart>& parts, size_t k, int bits) = 0;
+    // A linear of the seeded synthetic model.  The default builds the det rows on the host and calls linear();
+    // a device backend may generate the identical rows in place.
+    virtual std::unique_ptr<Linear> linear_synth(uint64_t seed, const std::vector<SynthPart>& parts, size_t k, int bits);
+
+    virtual void rmsnorm_quant(const Buf<float>& x, const Buf<float>& w, float eps, size_t m, size_t n,
+                               const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx) = 0;
+    virtual void quant(const Buf<float>& x, size_t m, size_t n, const Buf<int8_t>& xq, const Buf<float>& sx,
+                       const Buf<uint16_t>& mx) = 0;
+    virtual void gemm(const Linear& lin, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx,
+                      size_t m, const GemmOut& out) = 0;
+    virtual void silu_mul_quant(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<int8_t>& hq,
+                                const Buf<float>& sh, const Buf<uint16_t>& mh) = 0;
+    virtual void attention(const AttnLayer& l, const KvCache& kv, const Shape& s, const Buf<float>& qg,
+                           const Buf<float>& k, const Buf<float>& v, const Buf<float>& o) = 0;
+    virtual void gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, const Buf<float>& qkv,
+                     const Buf<float>& z, const Buf<float>& a, const Buf<float>& b, const Buf<float>& on,
+                     const GdnExport& ex) = 0;
+    virtual int32_t argmax(const Buf<float>& logits, size_t v) = 0;
+    virtual int32_t sample(const Buf<float>& logits, size_t v, float inv_temp, size_t top_k, float top_p,
+                           uint64_t z) = 0;
+
+    // ---- typed helpers (backend.rs:209-227)
+    template <class T>
+    Buf<T> alloc(size_t len) {
+        return Buf<T>(this, static_cast<T*>(alloc_bytes((len ? len : 1) * sizeof(T))), len);
+    }
+    template <class T>
+    Buf<T> upload(const T* data, size_t len) {
+        Buf<T> b = alloc<T>(len);
+        write_bytes(b.ptr(), data, len * sizeof(T));
+        return b;
+    }
+    template <class T>
+    Buf<T> upload(const std::vector<T>& v) { return upload(v.data(), v.size()); }
+    template <class T>
+    void write(const Buf<T>& b, size_t offset, const T* data, size_t len) {
+        write_bytes(b.ptr_at(offset), data, len * sizeof(T));
+    }
+    template <class T>
+    void read(const Buf<T>& b, size_t offset, T* out, size_t len) {
+        read_bytes(b.ptr_at(offset), out, len * sizeof(T));
+    }
+    template <class T>
+    std::vector<T> download(const Buf<T>& b) {
+        std::vector<T> v(b.len());
+        read_bytes(b.ptr(), v.data(), b.bytes());
+        return v;
+    }
+    template <class T>
+    void zero(const Buf<T>& b) { zero_bytes(b.ptr(), b.bytes()); }
+};
+
+template <class T>
+void Buf<T>::release() {
+    if (owner_ && p_) owner_->free_bytes(p_);
+    owner_ = nullptr;
+    p_ = nullptr;
+    len_ = 0;
+}
+
+}  // namespace det

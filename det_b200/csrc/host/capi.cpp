@@ -1,0 +1,137 @@
+// C entry points of the host driver library for the Python package (ctypes): backend objects, the synthetic model,
+// the token loop.  Every function that can fail returns 0 on success and leaves a message for dh_last_error().
+#include "cuda_backend.hpp"
+#include "model.hpp"
+#include <cstring>
+#include <string>
+
+namespace {
+thread_local std::string g_err;
+int fail(const std::string& e) {
+    g_err = e;
+    return 1;
+}
+template <class F>
+int guarded(F&& f) {
+    try {
+        std::string e = f();
+        return e.empty() ? 0 : fail(e);
+    } catch (const std::exception& ex) {
+        return fail(ex.what());
+    }
+}
+}  // namespace
+
+extern "C" {
+
+const char* dh_last_error() { return g_err.c_str(); }
+
+// ---- backends.  A backend handle is a det::Backend*; the CUDA backend is created here, test code may pass handles of
+// other implementations of the same interface.
+void* dh_cuda_backend_new(int stream_layout, int keep_rowmajor) {
+    try {
+        auto* b = new det::CudaBackend();
+        b->stream_layout = stream_layout != 0;
+        b->keep_rowmajor = keep_rowmajor != 0;
+        return static_cast<det::Backend*>(b);
+    } catch (const std::exception& ex) {
+        g_err = ex.what();
+        return nullptr;
+    }
+}
+void dh_backend_free(void* b) { delete static_cast<det::Backend*>(b); }
+int dh_backend_name(void* b, char* out, size_t cap) {
+    return guarded([&] {
+        snprintf(out, cap, "%s", static_cast<det::Backend*>(b)->name().c_str());
+        return std::string();
+    });
+}
+// The primitive test hook of the CUDA backend (cuda.rs:474-490).
+void dh_cuda_test_prim(int op, const float* x, size_t len, size_t m, size_t n, float* out, size_t out_len) {
+    static det::CudaBackend* hook = new det::CudaBackend();
+    std::vector<float> r = hook->test_prim(op, std::vector<float>(x, x + len), m, n);
+    std::memcpy(out, r.data(), (out_len < r.size() ? out_len : r.size()) * sizeof(float));
+}
+
+// ---- model
+void* dh_model_new_synth(void* backend, const char* config, size_t layers, uint64_t seed, size_t max_ctx,
+                         size_t max_batch) {
+    try {
+        det::Config cfg = det::config_by_name(config, layers);
+        return det::Model::load_synthetic(cfg, seed, static_cast<det::Backend*>(backend), max_ctx, max_batch).release();
+    } catch (const std::exception& ex) {
+        g_err = ex.what();
+        return nullptr;
+    }
+}
+void dh_model_free(void* m) { delete static_cast<det::Model*>(m); }
+size_t dh_model_vocab(void* m) { return static_cast<det::Model*>(m)->cfg.vocab; }
+size_t dh_model_pos(void* m) { return static_cast<det::Model*>(m)->pos; }
+int dh_model_set_all_logits(void* m, int all) {
+    return guarded([&] {
+        static_cast<det::Model*>(m)->set_all_logits(all != 0);
+        return std::string();
+    });
+}
+int dh_model_reset(void* m) {
+    return guarded([&] {
+        static_cast<det::Model*>(m)->reset();
+        return std::string();
+    });
+}
+int dh_model_forward(void* m, const int32_t* ids, size_t t) {
+    return guarded([&] { return static_cast<det::Model*>(m)->forward(ids, t); });
+}
+int dh_model_prefill(void* m, const int32_t* ids, size_t n) {
+    return guarded([&] { return static_cast<det::Model*>(m)->prefill(ids, n); });
+}
+// Copies the logits of the last forward ([vocab], or [t][vocab] in all-logits mode); returns the element count.
+size_t dh_model_logits(void* m, float* out, size_t cap) {
+    std::vector<float> l = static_cast<det::Model*>(m)->logits();
+    const size_t n = l.size() < cap ? l.size() : cap;
+    std::memcpy(out, l.data(), n * sizeof(float));
+    return l.size();
+}
+// greedy != 0 ignores the sampling parameters.  `rng` is the splitmix64 state, advanced by every draw.
+int dh_model_pick(void* m, int greedy, float inv_temp, size_t top_k, float top_p, uint64_t* rng, int32_t* id) {
+    return guarded([&] {
+        det::Sampling s;
+        s.greedy = greedy != 0;
+        s.inv_temp = inv_temp;
+        s.top_k = top_k;
+        s.top_p = top_p;
+        s.rng = *rng;
+        std::string e = static_cast<det::Model*>(m)->pick(s, *id);
+        *rng = s.rng;
+        return e;
+    });
+}
+// Prefill + up to n_new tokens; writes the ids to `out` and their count to *n_out.
+int dh_model_generate(void* m, const int32_t* prompt, size_t n_prompt, size_t n_new, int greedy, float inv_temp,
+                      size_t top_k, float top_p, uint64_t rng, int32_t* out, size_t* n_out) {
+    return guarded([&] {
+        det::Sampling s;
+        s.greedy = greedy != 0;
+        s.inv_temp = inv_temp;
+        s.top_k = top_k;
+        s.top_p = top_p;
+        s.rng = rng;
+        std::vector<int32_t> ids;
+        std::string e = static_cast<det::Model*>(m)->generate(prompt, n_prompt, n_new, s, {}, ids);
+        std::memcpy(out, ids.data(), ids.size() * sizeof(int32_t));
+        *n_out = ids.size();
+        return e;
+    });
+}
+void dh_synth_prompt(uint64_t seed, size_t n, size_t vocab, int32_t* out) {
+    std::vector<int32_t> ids = det::synth_prompt(seed, n, vocab);
+    std::memcpy(out, ids.data(), n * sizeof(int32_t));
+}
+// Host twin of the synthetic generator: `n` det rows of tensor `tid` (for checking the device twin).
+void dh_synth_det_rows(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits, uint8_t* out) {
+    std::vector<uint8_t> rows = det::synth_det_rows(seed, tid, n, k, bits);
+    std::memcpy(out, rows.data(), rows.size());
+}
+size_t dh_det_row_bytes(int bits, size_t k) { return det::det_row_bytes(bits, k); }
+
+}  // extern "C"

@@ -1,0 +1,214 @@
+// The CUDA backend: device buffers and kernels reached through the C ABI of include/det_b200.h — the C++ mirror of
+// crates/det/src/cuda.rs:15-490 (Cuda, CudaLinear, impl Backend for Cuda, test_prim).  Like the reference glue it keeps
+// lazily grown scratch buffers for attention, GDN and sampling, builds the device weight layout in linear(), and reads
+// picks back through a one-element device buffer.  The B200-specific part is linear(): besides the reference layout
+// (kept for large-M GEMMs) it builds the streaming layout the decode GEMV reads (det_linear_repack).
+#include "cuda_backend.hpp"
+#include <cstdio>
+#include <cstdlib>
+#include <stdexcept>
+
+namespace det {
+
+namespace {
+constexpr cudaStream_t ST = nullptr;   // the library's own in-order queue (cuda.rs:13)
+
+size_t bytes_per_32(int bits) { return bits == 8 ? 32 : (bits == 6 ? 24 : 16); }
+}  // namespace
+
+CudaBackend::CudaBackend() {
+    if (det_init() != 0) throw std::runtime_error("CUDA runtime failed to initialize");
+    pick_ = alloc<int32_t>(1);
+    z_ = alloc<uint64_t>(1);
+}
+CudaBackend::~CudaBackend() = default;
+
+std::string CudaBackend::name() const { return det_device_name(); }
+void* CudaBackend::alloc_bytes(size_t bytes) {
+    void* p = det_malloc(bytes < 16 ? 16 : bytes);   // cuda.rs:39-44
+    if (!p) {
+        fprintf(stderr, "det_malloc(%zu) failed\n", bytes);
+        abort();
+    }
+    return p;
+}
+void CudaBackend::free_bytes(void* p) { det_free(p); }
+void CudaBackend::write_bytes(void* dst, const void* src, size_t bytes) { det_memcpy(dst, src, bytes, ST); }
+void CudaBackend::read_bytes(const void* src, void* dst, size_t bytes) {
+    det_memcpy(dst, src, bytes, ST);
+    det_sync();
+}
+void CudaBackend::zero_bytes(void* p, size_t bytes) { det_memset(p, 0, bytes, ST); }
+void CudaBackend::sync() { det_sync(); }
+
+void* CudaBackend::scratch(Buf<uint8_t>& slot, size_t bytes) {   // cuda.rs:81-87
+    if (slot.len() < bytes) slot = alloc<uint8_t>(bytes < 256 ? 256 : bytes);
+    return slot.ptr();
+}
+
+void CudaBackend::finish_linear(CudaLinear& l) {
+    if (!stream_layout) return;
+    det_qlinear src{l.wq.ptr(), l.c.ptr(), l.m.ptr(), (int)l.n(), (int)l.k, l.bits};
+    l.stream = alloc<uint8_t>(det_linear_repack_bytes((int)l.n(), (int)l.k, l.bits));
+    det_linear_repack(&src, l.stream.ptr(), ST);
+    if (!keep_rowmajor) {
+        det_sync();
+        l.wq = Buf<uint8_t>();
+    }
+}
+
+// cuda.rs:139-163 — codes row-major, c and m split out; then the streaming copy
+std::unique_ptr<Linear> CudaBackend::linear(const std::vector<LinearPart>& parts, size_t k, int bits) {
+    auto lin = std::make_unique<CudaLinear>();
+    lin->k = k;
+    lin->bits = bits;
+    size_t n = 0;
+    for (const LinearPart& p : parts) {
+        lin->widths.push_back(p.n);
+        n += p.n;
+    }
+    const size_t nc = k / 32 * bytes_per_32(bits), g = k / 128, rb = nc + 4 + 2 * g;
+    std::vector<uint8_t> wq(n * nc);
+    std::vector<float> c(n);
+    std::vector<uint16_t> m(n * g);
+    size_t r = 0;
+    for (const LinearPart& p : parts)
+        for (size_t i = 0; i < p.n; i++, r++) {
+            const uint8_t* row = p.rows + i * rb;
+            std::memcpy(wq.data() + r * nc, row, nc);
+            std::memcpy(&c[r], row + nc, 4);
+            std::memcpy(m.data() + r * g, row + nc + 4, 2 * g);
+        }
+    lin->wq = upload(wq);
+    lin->c = upload(c);
+    lin->m = upload(m);
+    det_sync();   // the staging vectors die here
+    finish_linear(*lin);
+    return lin;
+}
+
+std::unique_ptr<Linear> CudaBackend::linear_synth(uint64_t seed, const std::vector<SynthPart>& parts, size_t k,
+                                                  int bits) {
+    auto lin = std::make_unique<CudaLinear>();
+    lin->k = k;
+    lin->bits = bits;
+    size_t n = 0, nmax = 0;
+    for (const SynthPart& p : parts) {
+        lin->widths.push_back(p.n);
+        n += p.n;
+        nmax = p.n > nmax ? p.n : nmax;
+    }
+    const size_t nc = k / 32 * bytes_per_32(bits), g = k / 128;
+    lin->wq = alloc<uint8_t>(n * nc);
+    lin->c = alloc<float>(n);
+    lin->m = alloc<uint16_t>(n * g);
+    double* tmp = static_cast<double*>(scratch(synth_scratch_, nmax * g * sizeof(double)));
+    size_t row0 = 0;
+    for (const SynthPart& p : parts) {
+        det_synth_linear(seed, p.tensor_id, (int)p.n, (int)k, bits, (int)row0, lin->wq.ptr(), lin->c.ptr(),
+                         lin->m.ptr(), tmp, ST);
+        row0 += p.n;
+    }
+    finish_linear(*lin);
+    return lin;
+}
+
+void CudaBackend::rmsnorm_quant(const Buf<float>& x, const Buf<float>& w, float eps, size_t m, size_t n,
+                                const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx) {
+    det_rmsnorm_quant(x.ptr(), w.ptr(), eps, (int)m, (int)n, nullptr, xq.ptr(), sx.ptr(), mx.ptr(), ST);
+}
+void CudaBackend::quant(const Buf<float>& x, size_t m, size_t n, const Buf<int8_t>& xq, const Buf<float>& sx,
+                        const Buf<uint16_t>& mx) {
+    det_quant(x.ptr(), (int)m, (int)n, xq.ptr(), sx.ptr(), mx.ptr(), ST);
+}
+
+// cuda.rs:209-289
+void CudaBackend::gemm(const Linear& lin_, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx,
+                       size_t m, const GemmOut& out) {
+    const CudaLinear& lin = static_cast<const CudaLinear&>(lin_);
+    det_qlinear q;
+    const bool use_stream = lin.stream.ptr() && (m <= (size_t)stream_max_m || !lin.wq.ptr());
+    q.wq = use_stream ? lin.stream.ptr() : lin.wq.ptr();
+    q.c = lin.c.ptr();
+    q.m = lin.m.ptr();
+    q.N = (int)lin.n();
+    q.K = (int)lin.k;
+    q.bits = use_stream ? (lin.bits | DET_LAYOUT_STREAM) : lin.bits;
+    switch (out.kind) {
+        case GemmOut::Write:
+            det_gemm_ex(&q, xq.ptr(), sx.ptr(), mx.ptr(), (int)m, out.dst[0]->ptr(), 0, 0, nullptr, nullptr, ST);
+            break;
+        case GemmOut::Accumulate:
+            det_gemm_ex(&q, xq.ptr(), sx.ptr(), mx.ptr(), (int)m, out.dst[0]->ptr(), 1, 0, nullptr, nullptr, ST);
+            break;
+        case GemmOut::Parts: {
+            if (out.dst.size() != lin.widths.size()) throw std::logic_error("gemm: part count mismatch");
+            std::vector<int> offs;
+            std::vector<float*> ptrs;
+            int acc = 0;
+            for (size_t i = 0; i < lin.widths.size(); i++) {
+                offs.push_back(acc);
+                acc += (int)lin.widths[i];
+                ptrs.push_back(out.dst[i]->ptr());
+            }
+            det_gemm_ex(&q, xq.ptr(), sx.ptr(), mx.ptr(), (int)m, nullptr, 0, (int)offs.size(), offs.data(),
+                        ptrs.data(), ST);
+            break;
+        }
+    }
+}
+
+void CudaBackend::silu_mul_quant(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<int8_t>& hq,
+                                 const Buf<float>& sh, const Buf<uint16_t>& mh) {
+    det_silu_mul_quant(g.ptr(), u.ptr(), (int)m, (int)n, nullptr, hq.ptr(), sh.ptr(), mh.ptr(), ST);
+}
+
+// cuda.rs:316-364
+void CudaBackend::attention(const AttnLayer& l, const KvCache& kv, const Shape& s, const Buf<float>& qg,
+                            const Buf<float>& k, const Buf<float>& v, const Buf<float>& o) {
+    det_attn_layer layer{l.q_norm->ptr(), l.k_norm->ptr(), l.v_scale->ptr(), l.v_inv_scale->ptr()};
+    det_kv_cache cache{kv.kq.ptr(), kv.sk.ptr(), kv.vq.ptr(), (int)kv.capacity, nullptr, nullptr};
+    void* sc = scratch(attn_scratch_, det_attn_scratch_bytes((int)s.m, (int)s.n_h, (int)s.hd));
+    det_attention(&layer, &cache, qg.ptr(), k.ptr(), v.ptr(), l.rope_cos->ptr(), l.rope_sin->ptr(), (int)s.rot, s.eps,
+                  (int)s.m, (int)s.pos0, (int)s.n_h, (int)s.n_kv, (int)s.hd, o.ptr(), sc, ST);
+}
+
+// cuda.rs:366-423
+void CudaBackend::gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, const Buf<float>& qkv,
+                      const Buf<float>& z, const Buf<float>& a, const Buf<float>& b, const Buf<float>& on,
+                      const GdnExport& ex) {
+    det_gdn_layer layer{l.conv->ptr(), l.a->ptr(), l.dt_bias->ptr(), l.norm->ptr()};
+    det_gdn_state state{st.conv_state.ptr(), st.s.ptr()};
+    void* sc = scratch(gdn_scratch_, det_gdn_scratch_bytes((int)s.m, (int)s.n_k, (int)s.n_v, (int)s.dk, (int)s.dv));
+    det_gdn_ex(&layer, &state, qkv.ptr(), z.ptr(), a.ptr(), b.ptr(), s.eps, (int)s.m, (int)s.n_k, (int)s.n_v,
+               (int)s.dk, (int)s.dv, on.ptr(), sc, ex.gin ? ex.gin->ptr() : nullptr, ex.gout ? ex.gout->ptr() : nullptr,
+               ST);
+}
+
+// cuda.rs:425-471
+int32_t CudaBackend::argmax(const Buf<float>& logits, size_t v) {
+    det_argmax(logits.ptr(), 1, (int)v, pick_.ptr(), ST);
+    return download(pick_)[0];
+}
+int32_t CudaBackend::sample(const Buf<float>& logits, size_t v, float inv_temp, size_t top_k, float top_p,
+                            uint64_t z) {
+    write(z_, 0, &z, 1);
+    const unsigned long long* zp = reinterpret_cast<const unsigned long long*>(z_.ptr());
+    if (top_k == 0 && top_p >= 1.0f) {
+        det_sample(logits.ptr(), 1, (int)v, inv_temp, zp, pick_.ptr(), ST);
+    } else {
+        void* sc = scratch(sample_scratch_, det_sample_scratch_bytes(1, (int)v));
+        det_sample_topkp(logits.ptr(), 1, (int)v, inv_temp, (int)top_k, top_p, zp, pick_.ptr(), sc, ST);
+    }
+    return download(pick_)[0];
+}
+
+// cuda.rs:474-490
+std::vector<float> CudaBackend::test_prim(int op, const std::vector<float>& x, size_t m, size_t n) {
+    Buf<float> xb = upload(x);
+    Buf<float> out = alloc<float>(x.size() > m ? x.size() : m);
+    det_test_prim(op, xb.ptr(), (int)m, (int)n, out.ptr(), ST);
+    return download(out);
+}
+
+}  // namespace det

@@ -1,0 +1,61 @@
+// The CUDA backend over the C ABI (the mirror of `Cuda` / `CudaLinear`, crates/det/src/cuda.rs:15-33,96-472).
+#pragma once
+#include "backend.hpp"
+#include "det_b200.h"
+
+namespace det {
+
+// cuda.rs:24-33, plus the streaming copy of the same weights for the decode GEMV.
+struct CudaLinear : Linear {
+    Buf<uint8_t> wq;       // reference layout [N][K/32 * bytes_per_32] (empty when only the streaming copy is kept)
+    Buf<float> c;          // [N]
+    Buf<uint16_t> m;       // [N][K/128]
+    Buf<uint8_t> stream;   // det_linear_repack layout
+};
+
+class CudaBackend : public Backend {
+  public:
+    CudaBackend();
+    ~CudaBackend() override;
+    std::string name() const override;
+    void* alloc_bytes(size_t bytes) override;
+    void free_bytes(void* p) override;
+    void write_bytes(void* dst, const void* host_src, size_t bytes) override;
+    void read_bytes(const void* src, void* host_dst, size_t bytes) override;
+    void zero_bytes(void* p, size_t bytes) override;
+    void sync() override;
+    std::unique_ptr<Linear> linear(const std::vector<LinearPart>& parts, size_t k, int bits) override;
+    std::unique_ptr<Linear> linear_synth(uint64_t seed, const std::vector<SynthPart>& parts, size_t k,
+                                         int bits) override;
+    void rmsnorm_quant(const Buf<float>& x, const Buf<float>& w, float eps, size_t m, size_t n, const Buf<int8_t>& xq,
+                       const Buf<float>& sx, const Buf<uint16_t>& mx) override;
+    void quant(const Buf<float>& x, size_t m, size_t n, const Buf<int8_t>& xq, const Buf<float>& sx,
+               const Buf<uint16_t>& mx) override;
+    void gemm(const Linear& lin, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx, size_t m,
+              const GemmOut& out) override;
+    void silu_mul_quant(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<int8_t>& hq,
+                        const Buf<float>& sh, const Buf<uint16_t>& mh) override;
+    void attention(const AttnLayer& l, const KvCache& kv, const Shape& s, const Buf<float>& qg, const Buf<float>& k,
+                   const Buf<float>& v, const Buf<float>& o) override;
+    void gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, const Buf<float>& qkv, const Buf<float>& z,
+             const Buf<float>& a, const Buf<float>& b, const Buf<float>& on, const GdnExport& ex) override;
+    int32_t argmax(const Buf<float>& logits, size_t v) override;
+    int32_t sample(const Buf<float>& logits, size_t v, float inv_temp, size_t top_k, float top_p, uint64_t z) override;
+
+    // The primitive test hook (cuda.rs:474-490).
+    std::vector<float> test_prim(int op, const std::vector<float>& x, size_t m, size_t n);
+
+    // Weight-layout policy, fixed before the first linear() (a choice by configuration, never by timing):
+    bool stream_layout = true;    // build the streaming copy for the decode GEMV
+    bool keep_rowmajor = true;    // keep the reference layout too (needed by the large-M GEMM)
+    int stream_max_m = 8;         // batches up to this many tokens go through the streaming GEMV
+
+  private:
+    void* scratch(Buf<uint8_t>& slot, size_t bytes);
+    void finish_linear(CudaLinear& l);
+    Buf<uint8_t> attn_scratch_, gdn_scratch_, sample_scratch_, synth_scratch_;
+    Buf<int32_t> pick_;
+    Buf<uint64_t> z_;
+};
+
+}  // namespace det

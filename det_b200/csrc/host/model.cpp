@@ -1,0 +1,279 @@
+// Model loading (synthetic), the network's op sequence and the token loop.  See model.hpp for the reference map.
+#include "model.hpp"
+#include <algorithm>
+#include <cmath>
+#include <stdexcept>
+
+namespace det {
+
+// Default of Backend::linear_synth: det rows on the host, then the ordinary weight-ingestion path.
+std::unique_ptr<Linear> Backend::linear_synth(uint64_t seed, const std::vector<SynthPart>& parts, size_t k, int bits) {
+    std::vector<std::vector<uint8_t>> rows;
+    std::vector<LinearPart> lp;
+    for (const SynthPart& p : parts) {
+        rows.push_back(synth_det_rows(seed, p.tensor_id, p.n, k, bits));
+        lp.push_back(LinearPart{rows.back().data(), p.n});
+    }
+    return linear(lp, k, bits);
+}
+
+namespace {
+struct SynthTensor {
+    TensorKind kind;
+    size_t n, k;
+    int bits;
+};
+// model.rs:180-197 — consecutive tensors of equal type and K become one fused linear.
+Proj make_proj(Backend* bk, uint64_t seed, size_t layer, const std::vector<SynthTensor>& ts) {
+    Proj p;
+    size_t i = 0;
+    while (i < ts.size()) {
+        size_t j = i + 1;
+        while (j < ts.size() && ts[j].bits == ts[i].bits && ts[j].k == ts[i].k) j++;
+        std::vector<SynthPart> parts;
+        for (size_t q = i; q < j; q++) parts.push_back(SynthPart{tensor_id(layer, ts[q].kind), ts[q].n});
+        p.lins.push_back(bk->linear_synth(seed, parts, ts[i].k, ts[i].bits));
+        i = j;
+    }
+    return p;
+}
+Buf<float> ones(Backend* bk, size_t n) { return bk->upload(std::vector<float>(n, 1.0f)); }
+}  // namespace
+
+std::unique_ptr<Model> Model::load_synthetic(const Config& cfg, uint64_t seed, Backend* bk, size_t max_ctx,
+                                             size_t max_batch) {
+    auto mp = std::make_unique<Model>();
+    Model& m = *mp;
+    m.cfg = cfg;
+    m.backend = bk;
+    m.seed = seed;
+    m.max_ctx = max_ctx;
+    m.max_batch = max_batch;
+    const size_t h = cfg.hidden, inter = cfg.intermediate;
+    const size_t n_h = cfg.n_heads, n_kv = cfg.n_kv, hd = cfg.head_dim;
+    const size_t n_k = cfg.gdn_k_heads, n_v = cfg.gdn_v_heads, dk = cfg.gdn_dk, dv = cfg.gdn_dv;
+    const size_t conv_dim = cfg.conv_dim();
+    const int wb = cfg.bits_default;
+
+    m.final_norm = ones(bk, h);
+    std::vector<float> rc, rs;
+    rope_tables(cfg, max_ctx, rc, rs);
+    m.rope_cos = bk->upload(rc);
+    m.rope_sin = bk->upload(rs);
+    m.lm_head = make_proj(bk, seed, GLOBAL_LAYER, {{T_EMBED, cfg.vocab, h, 8}});
+
+    m.layers.resize(cfg.n_layers);
+    for (size_t i = 0; i < cfg.n_layers; i++) {
+        Layer& l = m.layers[i];
+        l.is_attn = cfg.is_attention(i);
+        if (l.is_attn) {
+            Attn& a = l.attn;
+            a.qkv = make_proj(bk, seed, i, {{T_ATTN_Q, n_h * 2 * hd, h, wb}, {T_ATTN_K, n_kv * hd, h, wb}, {T_ATTN_V, n_kv * hd, h, wb}});
+            a.o = make_proj(bk, seed, i, {{T_ATTN_OUT, h, n_h * hd, wb}});
+            a.q_norm = ones(bk, hd);
+            a.k_norm = ones(bk, hd);
+            std::vector<float> vs(n_kv, DEFAULT_V_SCALE), vis(n_kv);
+            for (size_t q = 0; q < n_kv; q++) vis[q] = 1.0f / vs[q];   // model.rs:258
+            a.v_scale = bk->upload(vs);
+            a.v_inv_scale = bk->upload(vis);
+            a.kv.kq = bk->alloc<int8_t>(max_ctx * n_kv * hd);
+            a.kv.sk = bk->alloc<float>(max_ctx * n_kv);
+            a.kv.vq = bk->alloc<int16_t>(max_ctx * n_kv * hd);
+            a.kv.capacity = max_ctx;
+        } else {
+            Gdn& g = l.gdn;
+            g.qkvz = make_proj(bk, seed, i, {{T_GDN_QKV, conv_dim, h, wb}, {T_GDN_GATE, n_v * dv, h, wb}});
+            g.ab = make_proj(bk, seed, i, {{T_GDN_ALPHA, n_v, h, 8}, {T_GDN_BETA, n_v, h, 8}});
+            g.out = make_proj(bk, seed, i, {{T_GDN_OUT, h, n_v * dv, wb}});
+            std::vector<float> conv(conv_dim * cfg.conv_k), dtb(n_v), av(n_v);
+            for (size_t q = 0; q < conv.size(); q++) conv[q] = draw_normal(seed, tensor_id(i, T_CONV), q, WEIGHT_STD);
+            for (size_t q = 0; q < n_v; q++) {
+                dtb[q] = draw_normal(seed, tensor_id(i, T_DT_BIAS), q, WEIGHT_STD);
+                // the file stores ssm_a = -(1 + 15 u); the model keeps a = -ssm_a (model.rs:281-293)
+                av[q] = 1.0f + 15.0f * draw_unit(seed, tensor_id(i, T_SSM_A), q);
+            }
+            g.conv = bk->upload(conv);
+            g.a = bk->upload(av);
+            g.dt_bias = bk->upload(dtb);
+            g.norm = ones(bk, dv);
+            g.state.conv_state = bk->alloc<float>((cfg.conv_k - 1) * conv_dim);
+            g.state.s = bk->alloc<float>(n_v * dk * dv);
+        }
+        l.attn_norm = ones(bk, h);
+        l.ffn_norm = ones(bk, h);
+        l.gu = make_proj(bk, seed, i, {{T_FFN_GATE, inter, h, wb}, {T_FFN_UP, inter, h, wb}});
+        l.down = make_proj(bk, seed, i, {{T_FFN_DOWN, h, inter, wb}});
+    }
+    const size_t mb = max_batch;
+    Work& w = m.w;   // model.rs:316-347
+    w.x = bk->alloc<float>(mb * h);
+    w.xq = bk->alloc<int8_t>(mb * h);
+    w.sx = bk->alloc<float>(mb);
+    w.mx = bk->alloc<uint16_t>(mb * h / 128);
+    w.qg = bk->alloc<float>(mb * n_h * 2 * hd);
+    w.k = bk->alloc<float>(mb * n_kv * hd);
+    w.v = bk->alloc<float>(mb * n_kv * hd);
+    w.o = bk->alloc<float>(mb * n_h * hd);
+    w.oq = bk->alloc<int8_t>(mb * n_h * hd);
+    w.so = bk->alloc<float>(mb);
+    w.mo = bk->alloc<uint16_t>(mb * n_h * hd / 128);
+    w.qkv = bk->alloc<float>(mb * conv_dim);
+    w.z = bk->alloc<float>(mb * n_v * dv);
+    w.a = bk->alloc<float>(mb * n_v);
+    w.b = bk->alloc<float>(mb * n_v);
+    w.on = bk->alloc<float>(mb * n_v * dv);
+    w.onq = bk->alloc<int8_t>(mb * n_v * dv);
+    w.son = bk->alloc<float>(mb);
+    w.mon = bk->alloc<uint16_t>(mb * n_v * dv / 128);
+    w.g = bk->alloc<float>(mb * inter);
+    w.u = bk->alloc<float>(mb * inter);
+    w.hq = bk->alloc<int8_t>(mb * inter);
+    w.sh = bk->alloc<float>(mb);
+    w.mh = bk->alloc<uint16_t>(mb * inter / 128);
+    w.logits = bk->alloc<float>(cfg.vocab);
+    return mp;
+}
+
+void Model::set_all_logits(bool all) {
+    backend->sync();
+    const size_t n = (all ? max_batch : 1) * cfg.vocab;
+    if (w.logits.len() != n) w.logits = backend->alloc<float>(n);
+    all_logits = all;
+}
+
+void Model::reset() {
+    backend->sync();
+    pos = 0;
+    for (Layer& l : layers)
+        if (!l.is_attn) {
+            backend->zero(l.gdn.state.conv_state);
+            backend->zero(l.gdn.state.s);
+        }
+}
+
+std::string Model::embed_rows(const int32_t* ids, size_t t) {
+    const size_t h = cfg.hidden;
+    std::vector<float> x(t * h);
+    const uint64_t tid = tensor_id(GLOBAL_LAYER, T_EMBED);
+    for (size_t i = 0; i < t; i++) {
+        if (ids[i] < 0 || (size_t)ids[i] >= cfg.vocab)
+            return "token id " + std::to_string(ids[i]) + " is outside the embedding table (" +
+                   std::to_string(cfg.vocab) + " rows)";
+        for (size_t j = 0; j < h; j++) x[i * h + j] = synth_weight(seed, tid, (uint64_t)ids[i] * h + j);
+    }
+    backend->write(w.x, 0, x.data(), x.size());
+    return "";
+}
+
+void Model::project(const Proj& p, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx, size_t t,
+                    const std::vector<const Buf<float>*>& dsts) {
+    size_t i = 0;
+    for (const auto& lin : p.lins) {
+        const size_t n = lin->widths.size();
+        if (n == 1) backend->gemm(*lin, xq, sx, mx, t, GemmOut::write(*dsts[i]));
+        else backend->gemm(*lin, xq, sx, mx, t, GemmOut::parts(std::vector<const Buf<float>*>(dsts.begin() + i, dsts.begin() + i + n)));
+        i += n;
+    }
+    if (i != dsts.size()) throw std::logic_error("project: part count mismatch");
+}
+
+// qwen35.rs:31-170
+void Model::network(size_t pos0, size_t t) {
+    const Config& c = cfg;
+    Backend* bk = backend;
+    const size_t h = c.hidden;
+    for (Layer& l : layers) {
+        bk->rmsnorm_quant(w.x, l.attn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
+        if (l.is_attn) {
+            Attn& a = l.attn;
+            project(a.qkv, w.xq, w.sx, w.mx, t, {&w.qg, &w.k, &w.v});
+            AttnLayer layer{&a.q_norm, &a.k_norm, &a.v_scale, &a.v_inv_scale, &rope_cos, &rope_sin};
+            Shape shape{t, pos0, c.n_heads, c.n_kv, c.head_dim, c.rot_dim, c.eps};
+            bk->attention(layer, a.kv, shape, w.qg, w.k, w.v, w.o);
+            bk->quant(w.o, t, c.n_heads * c.head_dim, w.oq, w.so, w.mo);
+            bk->gemm(*a.o.lins[0], w.oq, w.so, w.mo, t, GemmOut::accumulate(w.x));
+        } else {
+            Gdn& g = l.gdn;
+            project(g.qkvz, w.xq, w.sx, w.mx, t, {&w.qkv, &w.z});
+            project(g.ab, w.xq, w.sx, w.mx, t, {&w.a, &w.b});
+            GdnLayer layer{&g.conv, &g.a, &g.dt_bias, &g.norm};
+            GdnShape shape{t, c.gdn_k_heads, c.gdn_v_heads, c.gdn_dk, c.gdn_dv, c.eps};
+            bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.on, GdnExport{});
+            bk->quant(w.on, t, c.gdn_v_heads * c.gdn_dv, w.onq, w.son, w.mon);
+            bk->gemm(*g.out.lins[0], w.onq, w.son, w.mon, t, GemmOut::accumulate(w.x));
+        }
+        bk->rmsnorm_quant(w.x, l.ffn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
+        project(l.gu, w.xq, w.sx, w.mx, t, {&w.g, &w.u});
+        bk->silu_mul_quant(w.g, w.u, t, c.intermediate, w.hq, w.sh, w.mh);
+        bk->gemm(*l.down.lins[0], w.hq, w.sh, w.mh, t, GemmOut::accumulate(w.x));
+    }
+    if (all_logits) {
+        bk->rmsnorm_quant(w.x, final_norm, c.eps, t, h, w.xq, w.sx, w.mx);
+        bk->gemm(*lm_head.lins[0], w.xq, w.sx, w.mx, t, GemmOut::write(w.logits));
+    } else {
+        Buf<float> last = Buf<float>::view(w.x.ptr_at((t - 1) * h), h);
+        bk->rmsnorm_quant(last, final_norm, c.eps, 1, h, w.xq, w.sx, w.mx);
+        bk->gemm(*lm_head.lins[0], w.xq, w.sx, w.mx, 1, GemmOut::write(w.logits));
+    }
+}
+
+std::string Model::forward(const int32_t* ids, size_t t) {
+    if (t == 0 || t > max_batch)
+        return "batch of " + std::to_string(t) + " tokens (1 to " + std::to_string(max_batch) + " allowed)";
+    if (pos + t > max_ctx)
+        return std::to_string(t) + " tokens at position " + std::to_string(pos) + " exceed the context of " +
+               std::to_string(max_ctx);
+    std::string e = embed_rows(ids, t);
+    if (!e.empty()) return e;
+    network(pos, t);
+    pos += t;
+    return "";
+}
+
+std::vector<float> Model::logits() { return backend->download(w.logits); }
+
+std::string Model::pick(Sampling& s, int32_t& id) {
+    if (s.greedy) {
+        id = backend->argmax(w.logits, cfg.vocab);
+        return "";
+    }
+    if (!std::isfinite(s.inv_temp) || std::isnan(s.top_p))
+        return "sampling parameters inv_temp=" + std::to_string(s.inv_temp) + " top_p=" + std::to_string(s.top_p) +
+               " are not finite";
+    s.rng += 0x9E3779B97F4A7C15ull;   // splitmix64 (spec/prim.rs:207-215): the state advances once per draw
+    uint64_t z = s.rng;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    id = backend->sample(w.logits, cfg.vocab, s.inv_temp, s.top_k, s.top_p, z);
+    return "";
+}
+
+std::string Model::prefill(const int32_t* ids, size_t n) {
+    for (size_t i = 0; i < n; i += max_batch) {
+        std::string e = forward(ids + i, std::min(max_batch, n - i));
+        if (!e.empty()) return e;
+    }
+    return "";
+}
+
+std::string Model::generate(const int32_t* prompt, size_t n_prompt, size_t n_new, Sampling s,
+                            const std::vector<int32_t>& stop, std::vector<int32_t>& out,
+                            const std::function<void(int32_t)>& on_token) {
+    std::string e = prefill(prompt, n_prompt);
+    if (!e.empty()) return e;
+    out.clear();
+    for (size_t i = 0; i < n_new; i++) {
+        int32_t id = 0;
+        e = pick(s, id);
+        if (!e.empty()) return e;
+        out.push_back(id);
+        if (on_token) on_token(id);
+        if (std::find(stop.begin(), stop.end(), id) != stop.end() || i + 1 == n_new) break;
+        e = forward(&id, 1);
+        if (!e.empty()) return e;
+    }
+    return "";
+}
+
+}  // namespace det

@@ -1,0 +1,97 @@
+// The model, its activation buffers and the token loop — the C++ mirror of crates/det/src/model.rs (Proj, Attn, Gdn,
+// Layer, Work, Sampling, Model::{load, set_all_logits, reset, embed_rows, project, forward, logits, pick, prefill,
+// generate}) and of the network's op sequence crates/det/src/qwen35.rs:8-172.  It talks to a backend only through
+// the op set of backend.hpp, so the same driver runs the CUDA backend and, in tests, the CPU reference backend.
+#pragma once
+#include "backend.hpp"
+#include "synth.hpp"
+#include <functional>
+#include <memory>
+#include <string>
+#include <vector>
+
+namespace det {
+
+constexpr float DEFAULT_V_SCALE = 1.0f / 1024.0f;   // model.rs:47
+
+struct Proj {   // model.rs:51-53
+    std::vector<std::unique_ptr<Linear>> lins;
+};
+struct Attn {   // model.rs:55-63
+    Proj qkv, o;
+    Buf<float> q_norm, k_norm, v_scale, v_inv_scale;
+    KvCache kv;
+};
+struct Gdn {   // model.rs:65-74
+    Proj qkvz, ab, out;
+    Buf<float> conv, a, dt_bias, norm;
+    GdnState state;
+};
+struct Layer {   // model.rs:81-87
+    Buf<float> attn_norm, ffn_norm;
+    Proj gu, down;
+    bool is_attn = false;
+    Attn attn;
+    Gdn gdn;
+};
+struct Work {   // model.rs:89-118
+    Buf<float> x;
+    Buf<int8_t> xq;
+    Buf<float> sx;
+    Buf<uint16_t> mx;
+    Buf<float> qg, k, v, o;
+    Buf<int8_t> oq;
+    Buf<float> so;
+    Buf<uint16_t> mo;
+    Buf<float> qkv, z, a, b, on;
+    Buf<int8_t> onq;
+    Buf<float> son;
+    Buf<uint16_t> mon;
+    Buf<float> g, u;
+    Buf<int8_t> hq;
+    Buf<float> sh;
+    Buf<uint16_t> mh;
+    Buf<float> logits;
+};
+struct Sampling {   // model.rs:120-141
+    bool greedy = true;
+    float inv_temp = 1.0f;
+    size_t top_k = 0;
+    float top_p = 1.0f;
+    uint64_t rng = 0;
+};
+
+class Model {
+  public:
+    // A seeded random-init model of shape `cfg` (the stand-in for Model::load on a converted checkpoint).
+    static std::unique_ptr<Model> load_synthetic(const Config& cfg, uint64_t seed, Backend* backend, size_t max_ctx,
+                                                 size_t max_batch);
+
+    void set_all_logits(bool all);                                   // model.rs:367-375
+    void reset();                                                    // model.rs:377-387
+    std::string embed_rows(const int32_t* ids, size_t t);            // model.rs:389-413; "" on success
+    void project(const Proj& p, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx, size_t t,
+                 const std::vector<const Buf<float>*>& dsts);        // model.rs:415-437
+    std::string forward(const int32_t* ids, size_t t);               // model.rs:439-465
+    std::vector<float> logits();                                     // model.rs:467-470
+    std::string pick(Sampling& s, int32_t& id);                      // model.rs:472-496
+    std::string prefill(const int32_t* ids, size_t n);               // model.rs:498-508
+    std::string generate(const int32_t* prompt, size_t n_prompt, size_t n_new, Sampling s,
+                         const std::vector<int32_t>& stop, std::vector<int32_t>& out,
+                         const std::function<void(int32_t)>& on_token = nullptr);   // model.rs:510-547
+
+    Config cfg;
+    Backend* backend = nullptr;
+    uint64_t seed = 0;
+    Buf<float> final_norm, rope_cos, rope_sin;
+    Proj lm_head;
+    std::vector<Layer> layers;
+    Work w;
+    size_t max_ctx = 0, max_batch = 0, pos = 0;
+    bool all_logits = false;
+
+  private:
+    void network(size_t pos0, size_t t);   // qwen35.rs:8-172
+};
+
+}  // namespace det

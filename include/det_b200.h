@@ -1,0 +1,172 @@
+/* det_b200 — C ABI of the B200 (sm_100a) backend for det.
+ *
+ * Part 1 is the drop-in boundary: the same symbols, argument order, struct layouts and error behaviour that det's
+ * FFI crate binds (crates/det-sys/src/lib.rs:54-228, declared in C by kernels/cuda/det_cuda.h), so that
+ * crates/det/src/cuda.rs can drive this library unchanged.  Part 2 holds additive entry points that the reference does
+ * not have (weight repack for the streaming GEMV, graph replay of the decode step, device-side token feedback).
+ *
+ * Conventions (kernels/cuda/det_cuda.h:1-5): every data pointer is a DEVICE pointer obtained from det_malloc unless a
+ * parameter says "host"; tensors are row-major fp32 unless noted; work is issued in program order on one in-order
+ * queue.  A stream argument of 0 selects that queue (det_cuda_stream()).  Failures of the CUDA runtime and malformed
+ * shapes print to stderr and abort(), as the reference does (kernels/cuda/common.cuh:8-9); det_init and det_malloc
+ * report through their return values.
+ */
+#ifndef DET_B200_H
+#define DET_B200_H
+#include <stddef.h>
+#include <stdint.h>
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ================================================================================================================
+ * Part 1 — reference-compatible symbols
+ * ============================================================================================================== */
+
+/* ---- runtime (replaces kernels/cuda/runtime.cu:83-121; bound at crates/det-sys/src/lib.rs:56-69) */
+int det_init(void);                      /* 0 on success; selects the current device                               */
+const char* det_device_name(void);
+void* det_malloc(size_t bytes);          /* zero-filled device buffer, NULL when the allocation fails              */
+void det_free(void* p);                  /* waits for pending work before releasing                                */
+size_t det_allocated_bytes(void);
+void det_sync(void);                     /* waits for everything issued so far; aborts on a kernel error           */
+void det_flush(void);                    /* nothing to do: launches are submitted eagerly                          */
+void det_memset(void* p, int value, size_t bytes, cudaStream_t st);
+void det_memcpy(void* dst, const void* src, size_t bytes, cudaStream_t st);   /* any direction                     */
+void* det_cuda_stream(void);             /* the queue det's work runs on                                           */
+
+/* ---- a quantized linear y = W x, W[N][K] (kernels/cuda/det_cuda.h:26-32, docs/SPEC.md §2)
+ * bits in {4, 6, 8}: wq is the reference layout, row-major packed codes [N][K/32 * bytes_per_32].
+ * bits | DET_LAYOUT_STREAM: wq points at a buffer produced by det_linear_repack (Part 2).                          */
+typedef struct {
+    const uint8_t* wq;
+    const float* c;      /* [N]        */
+    const uint16_t* m;   /* [N][K/128] */
+    int N, K, bits;
+} det_qlinear;
+
+/* ---- glue (replaces kernels/cuda/norm.cu:126-227; det_cuda.h:34-43)
+ * Quantization is quant_act_i8g (spec/quant.rs:21-49): sx[M] and, when mx != NULL, mx[M][n/128]; mx == NULL selects
+ * the per-row form quant_act_i8 (spec/quant.rs:7-16).                                                               */
+void det_rmsnorm_quant(const float* x, const float* w, float eps, int M, int n, float* y /* may be NULL */,
+                       int8_t* xq /* may be NULL */, float* sx, uint16_t* mx, cudaStream_t st);
+void det_quant(const float* x, int M, int n, int8_t* xq, float* sx, uint16_t* mx, cudaStream_t st);
+void det_embed(const uint16_t* table_bf16, const int* ids, int M, int H, float* x, cudaStream_t st);
+void det_add(float* x, const float* y, long long n, cudaStream_t st);                       /* x += y             */
+void det_silu_mul_quant(const float* g, const float* u, int M, int n, float* h /* may be NULL */, int8_t* hq,
+                        float* sh, uint16_t* mh, cudaStream_t st);
+void det_argmax(const float* logits, int M, int V, int* out, cudaStream_t st);              /* lowest index wins  */
+
+/* ---- integer GEMM (replaces kernels/cuda/gemm.cu:1030-1061; det_cuda.h:45-57; docs/SPEC.md §3)
+ *   acc[t][n] = sum_g (m[n][g] * mx[t][g]) * sum_{k in g} wq[n][k] * xq[t][k]      exact, int64
+ *   y[t][n]   = ((float)acc * c[n]) * sx[t]
+ * accumulate != 0: y += result (one fp32 add).  nparts > 1: column range [offs[i], offs[i+1]) (the last one ends at N)
+ * goes to dsts[i], a [M][width_i] buffer; offs and dsts are HOST arrays read before the call returns.               */
+void det_gemm(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M, float* y,
+              cudaStream_t st);
+void det_gemm_ex(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M, float* y,
+                 int accumulate, int nparts, const int* offs, float* const* dsts, cudaStream_t st);
+/* Scratch protocol of the reference's large-M path (det_cuda.h:52-57).  Kept for callers that follow it; this backend's
+ * large-M path needs det_gemm_scratch_bytes(M, K) bytes of per-(token, group) activation sums and falls back to an
+ * internal buffer when none (or a too small one) was registered.                                                    */
+size_t det_gemm_scratch_bytes(int M, int K);
+void det_gemm_set_scratch(void* p, size_t bytes);
+
+/* ---- gated attention (replaces kernels/cuda/attn.cu:856-930; det_cuda.h:59-83; docs/SPEC.md §5.1)
+ * Cache: kq[pos][n_kv][hd] int8, sk[pos][n_kv] fp32, vq[pos][n_kv][hd] int16.                                       */
+typedef struct {
+    const float* q_norm;        /* [hd] */
+    const float* k_norm;        /* [hd] */
+    const float* v_scale;       /* [n_kv] */
+    const float* v_inv_scale;   /* [n_kv] */
+} det_attn_layer;
+typedef struct {
+    int8_t* kq;
+    float* sk;
+    int16_t* vq;
+    int capacity;
+    int8_t* vlo;   /* unused (Metal keeps V as two planes) */
+    int8_t* vhi;
+} det_kv_cache;
+/* M new tokens at positions pos0 .. pos0+M-1: qg[M][n_h*2*hd] (per head q | gate), k[M][n_kv*hd], v[M][n_kv*hd],
+ * rope tables [pos][rot/2].  Writes the cache rows, attends each token to positions <= its own, applies
+ * sigmoid(gate), writes o[M][n_h*hd].  scratch >= det_attn_scratch_bytes(M, n_h, hd).                              */
+void det_attention(const det_attn_layer* L, const det_kv_cache* kv, const float* qg, const float* k, const float* v,
+                   const float* rope_cos, const float* rope_sin, int rot, float eps, int M, int pos0, int n_h,
+                   int n_kv, int hd, float* o, void* scratch, cudaStream_t st);
+size_t det_attn_scratch_bytes(int M, int n_h, int hd);
+/* Same, with pos0 read from device memory at execution time so the launch can be replayed from a graph; sized for
+ * any pos0 <= max_pos (det_cuda.h:77-83).                                                                            */
+void det_attention_dev(const det_attn_layer* L, const det_kv_cache* kv, const float* qg, const float* k,
+                       const float* v, const float* rope_cos, const float* rope_sin, int rot, float eps, int M,
+                       const int* pos0_dev, int max_pos, int n_h, int n_kv, int hd, float* o, void* scratch,
+                       cudaStream_t st);
+
+/* ---- Gated DeltaNet (replaces kernels/cuda/gdn.cu:271-309; det_cuda.h:85-105; docs/SPEC.md §5.2) */
+typedef struct {
+    const float* conv;      /* [conv_dim][4], oldest tap first */
+    const float* A;         /* [n_v] */
+    const float* dt_bias;   /* [n_v] */
+    const float* norm;      /* [dv]  */
+} det_gdn_layer;
+typedef struct {
+    float* conv_state;      /* [3][conv_dim], oldest first */
+    float* S;               /* [n_v][dk][dv] */
+} det_gdn_state;
+/* qkv[M][conv_dim], conv_dim = 2*n_k*dk + n_v*dv; z[M][n_v*dv]; a[M][n_v]; b[M][n_v] -> on[M][n_v*dv].
+ * det_gdn_ex also exports gin[M][n_k][2*dk + rep*dv + 2*rep] (q | k | v[rep] | beta[rep] | decay[rep]) and
+ * gout[M][n_v][dv] (mixer output before the gated norm); either may be NULL.                                        */
+void det_gdn(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a,
+             const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
+             cudaStream_t st);
+size_t det_gdn_scratch_bytes(int M, int n_k, int n_v, int dk, int dv);
+void det_gdn_ex(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a,
+                const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
+                float* gin, float* gout, cudaStream_t st);
+
+/* ---- deterministic sampling (replaces kernels/cuda/sample.cu:237-287; det_cuda.h:107-112; docs/SPEC.md §5.5)
+ * z[M]: raw 64-bit draws (splitmix64, advanced by the host).                                                        */
+void det_sample(const float* logits, int M, int V, float inv_temp, const unsigned long long* z, int* out,
+                cudaStream_t st);
+void det_sample_topkp(const float* logits, int M, int V, float inv_temp, int top_k, float top_p,
+                      const unsigned long long* z, int* out, void* scratch, cudaStream_t st);
+size_t det_sample_scratch_bytes(int M, int V);
+
+/* ---- primitive test hook (replaces kernels/cuda/runtime.cu:40-77,123-127; det_cuda.h:114-118)
+ * op: 0 exp_f, 1 log_f, 2 softplus_f, 3 sigmoid_f, 4 silu_f, 5 int64 (bits of x[2i], x[2i+1]) -> fp32 into out[2i],
+ *     6 rint, 7 1/x, 8 sqrt, 9 x*y, 10 x+y (y = x reversed), 11 treesum of each of M rows of n (n <= 8192) -> out[M],
+ *     12 same as 5 through the plain cast, 13 rint to int32 (saturating) back to fp32, 14 x/y, 15 x-y, 16 max(x,y).  */
+void det_test_prim(int op, const float* x, int M, int n, float* out, cudaStream_t st);
+
+/* ================================================================================================================
+ * Part 2 — additions (no counterpart in the reference unless noted)
+ * ============================================================================================================== */
+
+/* Layout tag OR-ed into det_qlinear.bits once wq points at a det_linear_repack buffer. */
+#define DET_LAYOUT_STREAM 0x100
+
+/* Streaming layout for the decode GEMV.  The reference's Rust glue builds its device layout in Backend::linear
+ * (crates/det/src/cuda.rs:139-163: row-major codes, c and m split out); Metal and x86 repack there
+ * (metal.rs:95-122, x86/gemm.rs:59-134).  This is that hook for B200: `src` describes device arrays in the reference
+ * layout; `dst` receives det_linear_repack_bytes(N, K, bits) bytes in which every tile of 4 output rows is one
+ * contiguous 16-byte-aligned record [codes of 4 rows | c[4] | m[4][K/128] | pad]; any run of records is one bulk copy. */
+size_t det_linear_repack_bytes(int N, int K, int bits);
+void det_linear_repack(const det_qlinear* src, void* dst, cudaStream_t st);
+
+/* Seeded synthetic weights generated in device memory (the benchmarks' stand-in for a converted checkpoint; the host
+ * twin is det_b200/csrc/host/synth.cpp and follows crates/det/src/quantize.rs:33-85).  det_synth_linear fills rows
+ * [row0, row0 + n) of a reference-layout linear (wq, c, m as in det_qlinear) from tensor `tid` of model `seed`;
+ * `scratch` needs n * (K/128) doubles.  det_synth_bf16 writes `count` bf16 elements of tensor `tid`.                */
+void det_synth_linear(unsigned long long seed, unsigned long long tid, int n, int K, int bits, int row0, uint8_t* wq,
+                      float* c, uint16_t* m, double* scratch, cudaStream_t st);
+void det_synth_bf16(unsigned long long seed, unsigned long long tid, long long count, uint16_t* out, cudaStream_t st);
+
+/* Last error recorded by a bounded device-side wait or a size check that chose not to abort (0 = none). */
+int det_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DET_B200_H */

@@ -1,0 +1,76 @@
+"""End-to-end parity on the tiny seeded model (BASELINE configs[0]): every logit of a 64-token prompt and 64 greedy
+tokens, CUDA backend vs the CPU oracle running the same driver; plus invariance to the prefill chunking."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+SEED = 20261125
+
+
+def _model(h, backend, max_batch, cfg=b"tiny", layers=0, max_ctx=192):
+    m = h.dh_model_new_synth(backend, cfg, layers, SEED, max_ctx, max_batch)
+    assert m, h.dh_last_error()
+    return m
+
+
+def _prompt(h, n, vocab):
+    ids = np.zeros(n, np.int32)
+    h.dh_synth_prompt(1, n, vocab, ids.ctypes.data)
+    return ids
+
+
+def _all_logits(h, m, ids):
+    vocab = h.dh_model_vocab(m)
+    assert h.dh_model_set_all_logits(m, 1) == 0
+    assert h.dh_model_forward(m, ids.ctypes.data, len(ids)) == 0, h.dh_last_error()
+    out = np.zeros(len(ids) * vocab, np.float32)
+    h.dh_model_logits(m, out.ctypes.data, out.size)
+    return out.view(np.uint32)
+
+
+def _greedy(h, m, ids, n_new):
+    out = np.zeros(n_new, np.int32)
+    n = C.c_size_t(0)
+    assert h.dh_model_generate(m, ids.ctypes.data, len(ids), n_new, 1, 1.0, 0, 1.0, 0, out.ctypes.data, C.byref(n)) == 0
+    return out[: n.value]
+
+
+def test_tiny_every_logit_and_greedy_tokens(libs, ref_backend, cuda_backend):
+    h = libs.host()
+    ids = _prompt(h, 64, 32768)
+    ref, gpu = _model(h, ref_backend, 64), _model(h, cuda_backend, 64)
+    try:
+        a, b = _all_logits(h, ref, ids), _all_logits(h, gpu, ids)
+        assert np.array_equal(a, b), f"{(a != b).sum()} of {a.size} logits differ"
+        for m in (ref, gpu):
+            h.dh_model_set_all_logits(m, 0)
+            h.dh_model_reset(m)
+        ta, tb = _greedy(h, ref, ids, 64), _greedy(h, gpu, ids, 64)
+        assert np.array_equal(ta, tb), (ta, tb)
+        la, lb = np.zeros(32768, np.float32), np.zeros(32768, np.float32)
+        h.dh_model_logits(ref, la.ctypes.data, la.size)
+        h.dh_model_logits(gpu, lb.ctypes.data, lb.size)
+        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+    finally:
+        h.dh_model_free(ref)
+        h.dh_model_free(gpu)
+
+
+@pytest.mark.parametrize("chunk", [1, 16])
+def test_tiny_chunking_invariance(chunk, libs, cuda_backend):
+    h = libs.host()
+    ids = _prompt(h, 64, 32768)
+    whole, parts = _model(h, cuda_backend, 64), _model(h, cuda_backend, chunk)
+    try:
+        assert h.dh_model_prefill(whole, ids.ctypes.data, 64) == 0
+        assert h.dh_model_prefill(parts, ids.ctypes.data, 64) == 0
+        la, lb = np.zeros(32768, np.float32), np.zeros(32768, np.float32)
+        h.dh_model_logits(whole, la.ctypes.data, la.size)
+        h.dh_model_logits(parts, lb.ctypes.data, lb.size)
+        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+    finally:
+        h.dh_model_free(whole)
+        h.dh_model_free(parts)
