@@ -1,0 +1,395 @@
+#!/usr/bin/env python
+"""Headline benchmark: greedy decode of the seeded random-init 27B-shape W6 model at batch 1 (BASELINE configs[3]):
+prefill of 2048 seeded tokens in 512-token chunks, then decode steps.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 27b|4b|tiny]
+
+One "step" is one decoded token.  `value` is decode tok/s with the step replayed as a CUDA graph and the token fed back
+on the device (inputs resident in HBM); `e2e` is the same loop driven like the reference drives its backend
+(crates/det/src/model.rs:439-547): host embedding row -> H2D, forward, argmax, 4-byte D2H per token.  The roofline object
+covers the decode GEMV (k_gemv_stream) timed alone with CUDA events on the library's queue; `cpu_baseline` is the CPU
+reference port timed on a bounded slice of the same model.  Prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SEED = 20261125
+PROMPT_SEED = 1
+
+
+def _peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class Events:
+    """CUDA events on the library's own queue (torch.cuda.Event would only see torch's stream)."""
+
+    def __init__(self, stream):
+        self.rt = C.CDLL("libcudart.so.12")
+        self.stream = C.c_void_p(stream)
+
+    def record(self):
+        e = C.c_void_p()
+        assert self.rt.cudaEventCreate(C.byref(e)) == 0
+        assert self.rt.cudaEventRecord(e, self.stream) == 0
+        return e
+
+    def ms(self, a, b) -> float:
+        assert self.rt.cudaEventSynchronize(b) == 0
+        out = C.c_float()
+        assert self.rt.cudaEventElapsedTime(C.byref(out), a, b) == 0
+        return out.value
+
+
+class ClockSampler:
+    """Samples the SM clock, power and throttle reasons through NVML from a thread of this process while the timed
+    regions run (read-only queries; a polling nvidia-smi process disturbs a latency-bound decode loop measurably)."""
+
+    def __init__(self, index: int, period_s: float = 0.2):
+        self.rows, self.index, self.period, self._stop, self.thread = [], index, period_s, threading.Event(), None
+
+    def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.dev = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        except Exception:
+            self.nv = None
+            return
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(self.dev, nv.NVML_CLOCK_SM)
+                mx = nv.nvmlDeviceGetMaxClockInfo(self.dev, nv.NVML_CLOCK_SM)
+                reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.dev)
+                self.rows.append((time.time(), sm, mx, reasons))
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def stop(self):
+        self._stop.set()
+        if self.thread:
+            self.thread.join(timeout=2)
+
+    def summary(self, windows) -> dict:
+        if not getattr(self, "nv", None):
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "note": "NVML unavailable"}
+        nv = self.nv
+        flags = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                 "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                 "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        sm, mx, reasons = [], 0, set()
+        for ts, s_, m_, r in self.rows:
+            if not any(a <= ts <= b for a, b in windows):
+                continue
+            sm.append(s_)
+            mx = max(mx, m_)
+            for name, bit in flags.items():
+                if r & bit:
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+SHAPES = {   # layers, hidden, ffn, attention (q heads, kv heads, head dim), GDN (k heads, v heads), vocab
+    "tiny": dict(layers=8, hidden=1024, ffn=3072, n_h=8, n_kv=2, hd=256, n_k=8, n_v=16, vocab=32768),
+    "4b": dict(layers=32, hidden=2560, ffn=9216, n_h=16, n_kv=4, hd=256, n_k=16, n_v=32, vocab=248320),
+    "27b": dict(layers=64, hidden=5120, ffn=17408, n_h=24, n_kv=4, hd=256, n_k=16, n_v=48, vocab=248320),
+}
+
+
+def launches_per_token(cfg: str) -> int:
+    """Kernels of one device-resident decode step: 12 per layer (norm+quant, 2-3 GEMVs, 3-4 mixer kernels, quant, GEMV,
+    norm+quant, GEMV, SwiGLU+quant, GEMV) plus embed, final norm, head GEMV, argmax and token feedback."""
+    return SHAPES[cfg]["layers"] * 12 + 5
+
+
+def _prompt(h, n, vocab):
+    import numpy as np
+    ids = np.zeros(n, np.int32)
+    h.dh_synth_prompt(PROMPT_SEED, n, vocab, ids.ctypes.data)
+    return ids
+
+
+def _check(rc, h):
+    if rc != 0:
+        raise RuntimeError(h.dh_last_error().decode())
+
+
+def cpu_baseline(h, cfg: str, threads: int, tokens: int = 2):
+    """The CPU reference port (oracle: restated `--backend ref`, OpenMP over independent rows) on a bounded slice of the
+    same model: the first 4 and the first 8 layers plus the output head; the per-token time of the full depth is
+    extrapolated from the two (every 4-layer block has the same shapes)."""
+    import importlib.util
+    import numpy as np
+    spec = importlib.util.spec_from_file_location("oracle_build", ROOT / "oracle" / "build.py")
+    ob = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ob)
+    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+    o = C.CDLL(str(ob.build()))
+    o.orc_ref_backend_new.restype = C.c_void_p
+    o.orc_ref_backend_free.argtypes = [C.c_void_p]
+    rb = o.orc_ref_backend_new()
+    vocab = SHAPES[cfg]["vocab"]
+    ids = _prompt(h, 8, vocab)
+    times = {}
+    for layers in (4, 8):
+        if layers > SHAPES[cfg]["layers"]:
+            continue
+        m = h.dh_model_new_synth(rb, cfg.encode(), layers, SEED, 64, 8)
+        if not m:
+            raise RuntimeError(h.dh_last_error().decode())
+        _check(h.dh_model_prefill(m, ids.ctypes.data, len(ids)), h)
+        tok = C.c_int32(0)
+        rng = C.c_uint64(0)
+        _check(h.dh_model_pick(m, 1, 1.0, 0, 1.0, C.byref(rng), C.byref(tok)), h)
+        t0 = time.perf_counter()
+        for _ in range(tokens):
+            one = np.array([tok.value], np.int32)
+            _check(h.dh_model_forward(m, one.ctypes.data, 1), h)
+            _check(h.dh_model_pick(m, 1, 1.0, 0, 1.0, C.byref(rng), C.byref(tok)), h)
+        times[layers] = (time.perf_counter() - t0) / tokens
+        h.dh_model_free(m)
+    o.orc_ref_backend_free(rb)
+    full = SHAPES[cfg]["layers"]
+    if 8 in times:
+        block = times[8] - times[4]
+        per_token = times[4] + block * (full // 4 - 1)
+    else:
+        per_token = times[4]
+    return {"value": 1.0 / per_token, "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": f"{cfg} shape, first 4 and 8 layers + W8 head, {tokens} decode tokens each at position 8, "
+                      f"extrapolated linearly to {full} layers; restated --backend ref (scalar spec, OpenMP over rows)",
+            "ms_per_token_4_layers": times[4] * 1e3, "ms_per_token_8_layers": times.get(8, 0) * 1e3}
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import numpy as np
+    from det_b200 import capi
+    rt = C.CDLL("libcudart.so.12")
+    assert rt.cudaSetDevice(local_rank) == 0
+    h, d = capi.host(), capi.cuda()
+    cfg = args.config
+    shape = SHAPES[cfg]
+    K, W, P, chunk = args.steps, args.warmup, args.prefill, args.chunk
+    max_ctx = P + 2 * (K + W) + 16
+    bk = h.dh_cuda_backend_new(1, 1)
+    if not bk:
+        raise RuntimeError(h.dh_last_error().decode())
+    t_load = time.perf_counter()
+    model = h.dh_model_new_synth(bk, cfg.encode(), 0, SEED, max_ctx, chunk)
+    if not model:
+        raise RuntimeError(h.dh_last_error().decode())
+    d.det_sync()
+    t_load = time.perf_counter() - t_load
+    ev = Events(d.det_cuda_stream())
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    windows = []
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist_mod
+        torch.cuda.set_device(local_rank)
+        dist_mod.init_process_group("nccl")
+        dist = dist_mod
+
+    def barrier():
+        if dist:
+            dist.barrier()
+        d.det_sync()
+
+    def max_over_ranks(ms: float) -> float:
+        if not dist:
+            return ms
+        import torch
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- prefill (P tokens in `chunk`-token batches), timed for the secondary metric
+    ids = _prompt(h, P, shape["vocab"])
+    barrier()
+    w0 = time.time()
+    a = ev.record()
+    _check(h.dh_model_prefill(model, ids.ctypes.data, P), h)
+    b = ev.record()
+    prefill_ms = max_over_ranks(ev.ms(a, b))
+    windows.append((w0, time.time()))
+    tok = C.c_int32(0)
+    rng = C.c_uint64(0)
+    _check(h.dh_model_pick(model, 1, 1.0, 0, 1.0, C.byref(rng), C.byref(tok)), h)
+
+    # ---- decode, device-resident (value): W warm-up steps (the first one captures the graph), then exactly K
+    dec = h.dh_graph_decoder_new(model)
+    if not dec:
+        raise RuntimeError(h.dh_last_error().decode())
+    out = np.zeros(max(K, W), np.int32)
+    _check(h.dh_graph_decoder_enqueue(dec, tok.value, W, 1), h)
+    n = h.dh_graph_decoder_finish(dec, out.ctypes.data, out.size)
+    last = int(out[n - 1])
+    barrier()
+    w0 = time.time()
+    a = ev.record()
+    _check(h.dh_graph_decoder_enqueue(dec, last, K, 1), h)
+    b = ev.record()
+    decode_ms = max_over_ranks(ev.ms(a, b))
+    windows.append((w0, time.time()))
+    n = h.dh_graph_decoder_finish(dec, out.ctypes.data, out.size)
+    graph_tokens = out[:n].copy()
+    last = int(graph_tokens[-1])
+
+    # ---- decode end to end through the plugin calls (host embedding -> H2D, forward, argmax, D2H) as model.rs drives it
+    def eager_steps(count, tok_id):
+        one = np.zeros(1, np.int32)
+        t = C.c_int32(tok_id)
+        for _ in range(count):
+            one[0] = t.value
+            _check(h.dh_model_forward(model, one.ctypes.data, 1), h)
+            _check(h.dh_model_pick(model, 1, 1.0, 0, 1.0, C.byref(rng), C.byref(t)), h)
+        return t.value
+
+    last = eager_steps(W, last)
+    barrier()
+    w0 = time.time()
+    a = ev.record()
+    t_wall = time.perf_counter()
+    last = eager_steps(K, last)
+    b = ev.record()
+    e2e_ms = max_over_ranks(max(ev.ms(a, b), (time.perf_counter() - t_wall) * 1e3))
+    windows.append((w0, time.time()))
+
+    # ---- the decode GEMV alone: every linear of the model at M = 1 (one token's GEMVs), weights 20 GB >> L2
+    nbytes, nlaunch = C.c_size_t(0), C.c_size_t(0)
+    _check(h.dh_gemv_sweep(model, 1, C.byref(nbytes), C.byref(nlaunch)), h)
+    reps = 3
+    barrier()
+    w0 = time.time()
+    a = ev.record()
+    _check(h.dh_gemv_sweep(model, reps, C.byref(nbytes), C.byref(nlaunch)), h)
+    b = ev.record()
+    sweep_ms = ev.ms(a, b)
+    windows.append((w0, time.time()))
+    time.sleep(0.3)
+    sampler.stop()
+    err = d.det_last_error()
+    if err:
+        raise RuntimeError(f"device-side wait reported error {err}")
+
+    if rank != 0:
+        return
+    peak, peak_kind = _peaks()
+    achieved = nbytes.value / (sweep_ms * 1e-3) / 1e9
+    line = {
+        "metric": "27B W6 decode tok/s bs1" if cfg == "27b" else f"{cfg} W6 decode tok/s bs1",
+        "value": world * K / (decode_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 x W6 -> int64 (fp32 glue)", "data": "synthetic",
+        "config": {"workload": f"{cfg}-shape seeded random-init W6 model (W8 head and GDN a/b), batch 1: prefill {P} tokens in "
+                               f"{chunk}-token chunks, then greedy decode", "context_at_timing": P + W,
+                   "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas (tensor parallel not built)",
+                   "l2": "weights streamed per token (20 GB at 27B) exceed the 126 MB L2", "seed": SEED,
+                   "rot_dim": 64, "rope_theta": 1e7, "eps": 1e-6, "v_scale": 2 ** -10},
+        "e2e": {"value": world * K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": shape["hidden"] * 4,
+                "d2h_bytes_per_step": 4},
+        "gpu_launches": K * launches_per_token(cfg),
+        "prefill": {"value": world * P / (prefill_ms * 1e-3), "unit": "tok/s", "tokens": P, "chunk": chunk},
+        "roofline": {"bound": "hbm", "kernel": "k_gemv_stream", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "launches": nlaunch.value, "bytes": nbytes.value, "ms": sweep_ms,
+                     "how": "every linear of the model at M=1, 3 passes back to back, CUDA events on the launch queue"},
+        "clocks": sampler.summary(windows),
+        "load_s": t_load,
+        "tokens_head": [int(x) for x in graph_tokens[:8]],
+    }
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(h, cfg, os.cpu_count() or 1)
+    print(json.dumps(line), flush=True)
+
+
+def run_reference(args, rank: int, world: int):
+    """`--impl reference`: the reference's own CPU path for the same metric.  The reference is Rust and cannot be built
+    here (no cargo / rustc), so this arm times the CPU port of its `--backend ref` (oracle/) with every host thread on a
+    bounded slice of the same workload; rank 0 alone runs."""
+    if rank != 0:
+        return
+    from det_b200 import capi
+    h = capi.host()
+    try:
+        h.dh_use_cuda_synth_rows(1)   # build the CPU-side weights with the device generator when a GPU is present
+        capi.cuda().det_init()
+    except Exception:
+        pass
+    threads = os.cpu_count() or 1
+    K, W = args.steps, args.warmup
+    base = cpu_baseline(h, args.config, threads, tokens=max(1, min(K, 2)))
+    cfg = args.config
+    line = {
+        "impl": "reference",
+        "metric": "27B W6 decode tok/s bs1" if cfg == "27b" else f"{cfg} W6 decode tok/s bs1",
+        "value": base["value"], "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": 1e3 / base["value"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 x W6 -> int64 (fp32 glue)", "data": "synthetic",
+        "config": {"workload": f"{cfg}-shape seeded random-init W6 model, batch 1 greedy decode on host cores",
+                   "sample": base["sample"]},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="27b", choices=sorted(SHAPES))
+    ap.add_argument("--prefill", type=int, default=2048)
+    ap.add_argument("--chunk", type=int, default=512)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    from det_b200 import build
+    if rank == 0 and not (build.LIB / "libdet_host.so").exists():
+        build.build_all()
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        if world == 1:
+            from det_b200 import capi
+            capi.host().dh_use_cuda_synth_rows(1)
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

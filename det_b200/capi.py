@@ -83,6 +83,11 @@ CUDA_ABI = {
     "det_linear_repack": (None, [C.POINTER(QLinear), c_void_p, c_void_p]),
     "det_synth_linear": (None, [c_u64, c_u64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "det_synth_bf16": (None, [c_u64, c_u64, C.c_longlong, c_void_p, c_void_p]),
+    "det_graph_begin": (None, []),
+    "det_graph_end": (c_void_p, []),
+    "det_graph_launch": (None, [c_void_p]),
+    "det_graph_free": (None, [c_void_p]),
+    "det_token_feedback": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "det_last_error": (c_int, []),
 }
 
@@ -104,6 +109,12 @@ HOST_API = {
     "dh_model_pick": (c_int, [c_void_p, c_int, c_float, c_size_t, c_float, C.POINTER(c_u64), C.POINTER(c_i32)]),
     "dh_model_generate": (c_int, [c_void_p, c_void_p, c_size_t, c_size_t, c_int, c_float, c_size_t, c_float, c_u64,
                                   c_void_p, C.POINTER(c_size_t)]),
+    "dh_graph_decoder_new": (c_void_p, [c_void_p]),
+    "dh_graph_decoder_free": (None, [c_void_p]),
+    "dh_graph_decoder_enqueue": (c_int, [c_void_p, c_i32, c_size_t, c_int]),
+    "dh_graph_decoder_finish": (c_size_t, [c_void_p, c_void_p, c_size_t]),
+    "dh_gemv_sweep": (c_int, [c_void_p, c_int, C.POINTER(c_size_t), C.POINTER(c_size_t)]),
+    "dh_use_cuda_synth_rows": (None, [c_int]),
     "dh_synth_prompt": (None, [c_u64, c_size_t, c_size_t, c_void_p]),
     "dh_synth_det_rows": (None, [c_u64, c_u64, c_size_t, c_size_t, c_int, c_void_p]),
     "dh_det_row_bytes": (c_size_t, [c_int, c_size_t]),

@@ -484,14 +484,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
 
 // ------------------------------------------------------------------------------------------------------------------
 // Host side
-static int* g_error_flag = nullptr;    // device word the kernels report into
-static int* error_flag() {
-    if (!g_error_flag) {
-        DETB_CUDA_OK(cudaMalloc(&g_error_flag, sizeof(int)));
-        DETB_CUDA_OK(cudaMemset(g_error_flag, 0, sizeof(int)));
-    }
-    return g_error_flag;
-}
 
 struct GemvPlan {
     int rec_per_chunk, stages, stage_bytes;
@@ -555,7 +547,7 @@ static void gemv_stream_bits(const det_qlinear* L, const int8_t* xq, const float
         a.rec_per_chunk = p.rec_per_chunk;
         a.stages = p.stages;
         a.stage_bytes = p.stage_bytes;
-        a.error_flag = error_flag();
+        a.error_flag = error_word();
         a.out = out;
         switch (MT) {
             case 1: launch_gemv<BITS, 1>(a, p, q); break;

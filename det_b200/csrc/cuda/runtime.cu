@@ -20,7 +20,7 @@ struct Runtime {
     std::mutex mu;
     std::unordered_map<void*, size_t> live;
     size_t live_bytes = 0;
-    int last_error = 0;
+    int* error_word = nullptr;
 };
 Runtime* g_rt = nullptr;
 std::once_flag g_once;
@@ -46,6 +46,8 @@ void bring_up() {
     rt->sm_count = prop.multiProcessorCount;
     rt->smem_optin = prop.sharedMemPerBlockOptin;
     if (cudaStreamCreateWithFlags(&rt->queue, cudaStreamNonBlocking) != cudaSuccess) { delete rt; return; }
+    if (cudaMalloc(&rt->error_word, sizeof(int)) != cudaSuccess) { delete rt; return; }
+    if (cudaMemset(rt->error_word, 0, sizeof(int)) != cudaSuccess) { delete rt; return; }
     g_rt = rt;
 }
 }  // namespace
@@ -64,7 +66,7 @@ static Runtime& rt() {
 cudaStream_t queue_of(cudaStream_t st) { return st ? st : rt().queue; }
 int sm_count() { return rt().sm_count; }
 size_t smem_optin() { return rt().smem_optin; }
-void record_error(int code) { rt().last_error = code; }
+int* error_word() { return rt().error_word; }
 
 // ---- primitive test hook kernels
 __global__ void k_unary_binary(int op, const float* __restrict__ x, int n, float* __restrict__ out) {
@@ -136,7 +138,13 @@ extern "C" {
 int det_init(void) { return runtime_ready() ? 0 : 1; }
 const char* det_device_name(void) { return rt().name; }
 void* det_cuda_stream(void) { return (void*)rt().queue; }
-int det_last_error(void) { return runtime_ready() ? g_rt->last_error : 0; }
+int det_last_error(void) {
+    if (!runtime_ready()) return 0;
+    int code = 0;
+    DETB_CUDA_OK(cudaDeviceSynchronize());
+    DETB_CUDA_OK(cudaMemcpy(&code, g_rt->error_word, sizeof(int), cudaMemcpyDeviceToHost));
+    return code;
+}
 
 void* det_malloc(size_t bytes) {
     Runtime& r = rt();

@@ -8,7 +8,7 @@ bool runtime_ready();
 cudaStream_t queue_of(cudaStream_t st);   // maps the ABI's stream 0 onto the library's queue
 int sm_count();
 size_t smem_optin();
-void record_error(int code);
+int* error_word();   // device word that bounded waits report into
 
 // Error codes reported by det_last_error().
 enum : int { DETB_ERR_NONE = 0, DETB_ERR_WAIT_EXPIRED = 1, DETB_ERR_SIZE = 2 };

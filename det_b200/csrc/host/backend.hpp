@@ -73,6 +73,11 @@ struct SynthPart {
     size_t n;
 };
 
+// Optional source of synthetic det rows for Backend::linear_synth's default path (n rows of tensor tid).  When unset the
+// rows come from the host generator; a benchmark may plug in the device generator to build a CPU-side model quickly.
+using SynthRowsProvider = std::vector<uint8_t> (*)(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits);
+void set_synth_rows_provider(SynthRowsProvider p);
+
 // backend.rs:136-142
 struct GemmOut {
     enum Kind { Write, Accumulate, Parts } kind;

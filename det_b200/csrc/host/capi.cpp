@@ -1,6 +1,7 @@
 // C entry points of the host driver library for the Python package (ctypes): backend objects, the synthetic model,
 // the token loop.  Every function that can fail returns 0 on success and leaves a message for dh_last_error().
 #include "cuda_backend.hpp"
+#include "graph_decode.hpp"
 #include "model.hpp"
 #include <cstring>
 #include <string>
@@ -123,6 +124,39 @@ int dh_model_generate(void* m, const int32_t* prompt, size_t n_prompt, size_t n_
         return e;
     });
 }
+// ---- device-resident greedy decode (CUDA backend only)
+void* dh_graph_decoder_new(void* m) {
+    try {
+        return new det::GraphDecoder(*static_cast<det::Model*>(m));
+    } catch (const std::exception& ex) {
+        g_err = ex.what();
+        return nullptr;
+    }
+}
+void dh_graph_decoder_free(void* d) { delete static_cast<det::GraphDecoder*>(d); }
+// Queues n steps starting from token first_id (returns without waiting); use_graph replays the captured step.
+int dh_graph_decoder_enqueue(void* d, int32_t first_id, size_t n, int use_graph) {
+    return guarded([&] { return static_cast<det::GraphDecoder*>(d)->enqueue(first_id, n, use_graph != 0); });
+}
+// Waits for the queued steps and copies their tokens; returns the count.
+size_t dh_graph_decoder_finish(void* d, int32_t* out, size_t cap) {
+    std::vector<int32_t> ids = static_cast<det::GraphDecoder*>(d)->finish();
+    std::memcpy(out, ids.data(), (ids.size() < cap ? ids.size() : cap) * sizeof(int32_t));
+    return ids.size();
+}
+
+// One decoded token's GEMVs, `reps` times, without syncing in between (the caller times it with events on the queue).
+int dh_gemv_sweep(void* m, int reps, size_t* bytes, size_t* launches) {
+    return guarded([&] {
+        det::GemvSweep r = det::gemv_sweep(*static_cast<det::Model*>(m), reps);
+        *bytes = r.bytes;
+        *launches = r.launches;
+        return std::string();
+    });
+}
+// Routes the default (host-side) synthetic weight path through the device generator: identical rows, built in seconds.
+void dh_use_cuda_synth_rows(int on) { det::set_synth_rows_provider(on ? det::cuda_synth_det_rows : nullptr); }
+
 void dh_synth_prompt(uint64_t seed, size_t n, size_t vocab, int32_t* out) {
     std::vector<int32_t> ids = det::synth_prompt(seed, n, vocab);
     std::memcpy(out, ids.data(), n * sizeof(int32_t));

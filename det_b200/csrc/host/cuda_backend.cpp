@@ -4,6 +4,7 @@
 // picks back through a one-element device buffer.  The B200-specific part is linear(): besides the reference layout
 // (kept for large-M GEMMs) it builds the streaming layout the decode GEMV reads (det_linear_repack).
 #include "cuda_backend.hpp"
+#include "model.hpp"
 #include <cstdio>
 #include <cstdlib>
 #include <stdexcept>
@@ -169,8 +170,12 @@ void CudaBackend::attention(const AttnLayer& l, const KvCache& kv, const Shape& 
     det_attn_layer layer{l.q_norm->ptr(), l.k_norm->ptr(), l.v_scale->ptr(), l.v_inv_scale->ptr()};
     det_kv_cache cache{kv.kq.ptr(), kv.sk.ptr(), kv.vq.ptr(), (int)kv.capacity, nullptr, nullptr};
     void* sc = scratch(attn_scratch_, det_attn_scratch_bytes((int)s.m, (int)s.n_h, (int)s.hd));
-    det_attention(&layer, &cache, qg.ptr(), k.ptr(), v.ptr(), l.rope_cos->ptr(), l.rope_sin->ptr(), (int)s.rot, s.eps,
-                  (int)s.m, (int)s.pos0, (int)s.n_h, (int)s.n_kv, (int)s.hd, o.ptr(), sc, ST);
+    if (pos_dev)
+        det_attention_dev(&layer, &cache, qg.ptr(), k.ptr(), v.ptr(), l.rope_cos->ptr(), l.rope_sin->ptr(), (int)s.rot,
+                          s.eps, (int)s.m, pos_dev, max_pos, (int)s.n_h, (int)s.n_kv, (int)s.hd, o.ptr(), sc, ST);
+    else
+        det_attention(&layer, &cache, qg.ptr(), k.ptr(), v.ptr(), l.rope_cos->ptr(), l.rope_sin->ptr(), (int)s.rot,
+                      s.eps, (int)s.m, (int)s.pos0, (int)s.n_h, (int)s.n_kv, (int)s.hd, o.ptr(), sc, ST);
 }
 
 // cuda.rs:366-423
@@ -201,6 +206,64 @@ int32_t CudaBackend::sample(const Buf<float>& logits, size_t v, float inv_temp, 
         det_sample_topkp(logits.ptr(), 1, (int)v, inv_temp, (int)top_k, top_p, zp, pick_.ptr(), sc, ST);
     }
     return download(pick_)[0];
+}
+
+// det rows [codes | c | m] of a synthetic tensor, generated on the device and copied to the host
+std::vector<uint8_t> cuda_synth_det_rows(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits) {
+    const size_t nc = k / 32 * bytes_per_32(bits), g = k / 128, rb = nc + 4 + 2 * g;
+    void* wq = det_malloc(n * nc);
+    void* c = det_malloc(n * 4);
+    void* m = det_malloc(n * g * 2);
+    void* tmp = det_malloc(n * g * sizeof(double));
+    if (!wq || !c || !m || !tmp) throw std::runtime_error("cuda_synth_det_rows: out of device memory");
+    det_synth_linear(seed, tid, (int)n, (int)k, bits, 0, (uint8_t*)wq, (float*)c, (uint16_t*)m, (double*)tmp, ST);
+    std::vector<uint8_t> hw(n * nc), hm(n * g * 2), out(n * rb);
+    std::vector<float> hc(n);
+    det_memcpy(hw.data(), wq, hw.size(), ST);
+    det_memcpy(hc.data(), c, n * 4, ST);
+    det_memcpy(hm.data(), m, hm.size(), ST);
+    det_sync();
+    for (void* p : {wq, c, m, tmp}) det_free(p);
+    for (size_t r = 0; r < n; r++) {
+        std::memcpy(out.data() + r * rb, hw.data() + r * nc, nc);
+        std::memcpy(out.data() + r * rb + nc, &hc[r], 4);
+        std::memcpy(out.data() + r * rb + nc + 4, hm.data() + r * g * 2, g * 2);
+    }
+    return out;
+}
+
+// Every linear of the model once at M = 1 (the launches of one decoded token's GEMVs), `reps` times.
+GemvSweep gemv_sweep(Model& m, int reps) {
+    GemvSweep r{0, 0};
+    CudaBackend* bk = dynamic_cast<CudaBackend*>(m.backend);
+    if (!bk) throw std::runtime_error("gemv_sweep needs the CUDA backend");
+    size_t nmax = m.cfg.vocab;
+    Buf<float> y = bk->alloc<float>(nmax);
+    auto run = [&](const Proj& p, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx) {
+        for (const auto& lin : p.lins) {
+            bk->gemm(*lin, xq, sx, mx, 1, GemmOut::write(y));
+            const size_t n = lin->n(), k = lin->k;
+            r.bytes += n * (k / 32 * bytes_per_32(lin->bits) + 4 + k / 128 * 2) + (k + 4 + k / 128 * 2) + n * 4;
+            r.launches++;
+        }
+    };
+    for (int i = 0; i < reps; i++) {
+        for (Layer& l : m.layers) {
+            if (l.is_attn) {
+                run(l.attn.qkv, m.w.xq, m.w.sx, m.w.mx);
+                run(l.attn.o, m.w.oq, m.w.so, m.w.mo);
+            } else {
+                run(l.gdn.qkvz, m.w.xq, m.w.sx, m.w.mx);
+                run(l.gdn.ab, m.w.xq, m.w.sx, m.w.mx);
+                run(l.gdn.out, m.w.onq, m.w.son, m.w.mon);
+            }
+            run(l.gu, m.w.xq, m.w.sx, m.w.mx);
+            run(l.down, m.w.hq, m.w.sh, m.w.mh);
+        }
+        run(m.lm_head, m.w.xq, m.w.sx, m.w.mx);
+    }
+    bk->sync();
+    return r;
 }
 
 // cuda.rs:474-490

@@ -50,6 +50,11 @@ class CudaBackend : public Backend {
     bool keep_rowmajor = true;    // keep the reference layout too (needed by the large-M GEMM)
     int stream_max_m = 8;         // batches up to this many tokens go through the streaming GEMV
 
+    // Device-position mode (graph replay): when set, attention() reads pos0 from this device word
+    // (det_attention_dev) and sizes its launch for positions up to max_pos.
+    const int* pos_dev = nullptr;
+    int max_pos = 0;
+
   private:
     void* scratch(Buf<uint8_t>& slot, size_t bytes);
     void finish_linear(CudaLinear& l);
@@ -57,5 +62,16 @@ class CudaBackend : public Backend {
     Buf<int32_t> pick_;
     Buf<uint64_t> z_;
 };
+
+std::vector<uint8_t> cuda_synth_det_rows(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits);
+
+class Model;
+struct GemvSweep {
+    size_t bytes;      // algorithmic bytes moved: weights + scales + activations in + outputs
+    size_t launches;
+};
+// Issues the GEMV of every linear of the model at M = 1 (one decoded token's worth), `reps` times; no sync inside the
+// loop, one at the end.  The caller brackets it with events to get the GEMV-only rate.
+GemvSweep gemv_sweep(Model& m, int reps);
 
 }  // namespace det

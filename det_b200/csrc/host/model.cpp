@@ -6,12 +6,16 @@
 
 namespace det {
 
+static SynthRowsProvider g_rows_provider = nullptr;
+void set_synth_rows_provider(SynthRowsProvider p) { g_rows_provider = p; }
+
 // Default of Backend::linear_synth: det rows on the host, then the ordinary weight-ingestion path.
 std::unique_ptr<Linear> Backend::linear_synth(uint64_t seed, const std::vector<SynthPart>& parts, size_t k, int bits) {
     std::vector<std::vector<uint8_t>> rows;
     std::vector<LinearPart> lp;
     for (const SynthPart& p : parts) {
-        rows.push_back(synth_det_rows(seed, p.tensor_id, p.n, k, bits));
+        rows.push_back(g_rows_provider ? g_rows_provider(seed, p.tensor_id, p.n, k, bits)
+                                       : synth_det_rows(seed, p.tensor_id, p.n, k, bits));
         lp.push_back(LinearPart{rows.back().data(), p.n});
     }
     return linear(lp, k, bits);

@@ -90,7 +90,6 @@ class Model {
     size_t max_ctx = 0, max_batch = 0, pos = 0;
     bool all_logits = false;
 
-  private:
     void network(size_t pos0, size_t t);   // qwen35.rs:8-172
 };
 

@@ -163,7 +163,21 @@ void det_synth_linear(unsigned long long seed, unsigned long long tid, int n, in
                       float* c, uint16_t* m, double* scratch, cudaStream_t st);
 void det_synth_bf16(unsigned long long seed, unsigned long long tid, long long count, uint16_t* out, cudaStream_t st);
 
-/* Last error recorded by a bounded device-side wait or a size check that chose not to abort (0 = none). */
+/* Decode-step graph (the reference lists "CUDA graphs for decode" as future work, README.md:115; its C side only has the
+ * graph-capturable det_attention_dev).  det_graph_begin starts capturing everything issued on the library queue;
+ * det_graph_end returns an executable graph (NULL on failure); det_graph_launch replays it on the queue.  Ops captured
+ * this way must read their position from device memory (det_attention_dev) and their token from device memory
+ * (det_embed with a device id).  Scratch buffers must have reached their final size before the capture starts.      */
+void det_graph_begin(void);
+void* det_graph_end(void);
+void det_graph_launch(void* graph);
+void det_graph_free(void* graph);
+/* Token feedback of a replayed decode step: log[*pos - log_base] = *pick (when log != NULL and in range), then *pos += 1.
+ * All pointers are device pointers.                                                                                  */
+void det_token_feedback(const int* pick, int* pos, int* log, int log_base, int log_cap, cudaStream_t st);
+
+/* Last error recorded by a bounded device-side wait (0 = none; see the DETB_ERR_* codes in csrc/cuda/runtime.cuh).
+ * Waits for pending work.                                                                                            */
 int det_last_error(void);
 
 #ifdef __cplusplus
