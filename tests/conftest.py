@@ -42,6 +42,17 @@ def oracle(libs):
     lib.orc_sample.restype = C.c_int
     lib.orc_sample.argtypes = [C.c_void_p, C.c_size_t, C.c_float, C.c_size_t, C.c_float, C.c_uint64]
     lib.orc_splitmix64.restype = C.c_uint64
+    vp, sz = C.c_void_p, C.c_size_t
+    lib.orc_gemm.argtypes = [vp, sz, sz, C.c_int, vp, vp, vp, sz, vp, C.c_int]
+    lib.orc_quant.argtypes = [vp, sz, sz, vp, vp, vp]
+    lib.orc_rmsnorm_quant.argtypes = [vp, vp, C.c_float, sz, sz, vp, vp, vp]
+    lib.orc_silu_mul_quant.argtypes = [vp, vp, sz, sz, vp, vp, vp]
+    lib.orc_unpack_row.argtypes = [vp, C.c_int, sz, vp]
+    lib.orc_treesum.argtypes = [vp, sz]
+    lib.orc_argmax.argtypes = [vp, sz]
+    lib.orc_weights.argtypes = [vp, sz, C.c_float, vp]
+    lib.orc_prim.argtypes = [C.c_int, vp, sz, sz, sz, vp, sz]
+    lib.orc_splitmix64.argtypes = [C.POINTER(C.c_uint64)]
     return lib
 
 

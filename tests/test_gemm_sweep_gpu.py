@@ -1,0 +1,72 @@
+"""Single-linear integer GEMM at the benchmark shapes (BASELINE configs[1]: K=5120 x N=17408 and the transposed FFN
+shape), through det_gemm_ex on both weight layouts, bit for bit against the oracle's gemm_row."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+PER32 = {8: 32, 6: 24, 4: 16}
+
+
+def _det_rows(rng, n, k, bits):
+    """Random det rows: random code bytes (every code value occurs), c in [1e-8, 1e-6], m in [1, 65535]."""
+    nc = k // 32 * PER32[bits]
+    g = k // 128
+    rows = np.zeros((n, nc + 4 + 2 * g), np.uint8)
+    rows[:, :nc] = rng.integers(0, 256, (n, nc), dtype=np.uint8)
+    c = (rng.random(n, dtype=np.float32) * 1e-6 + 1e-8).astype(np.float32)
+    m = rng.integers(1, 65536, (n, g)).astype(np.uint16)
+    rows[:, nc:nc + 4] = c.view(np.uint8).reshape(n, 4)
+    rows[:, nc + 4:] = m.view(np.uint8).reshape(n, 2 * g)
+    return rows, c, m, nc
+
+
+@pytest.mark.parametrize("n,k,bits,ms", [
+    (17408, 5120, 6, [1, 4, 8, 16]),
+    (17408, 5120, 8, [1, 3]),
+    (17408, 5120, 4, [1, 5]),
+    (5120, 17408, 6, [1, 2]),
+    (5120, 6144, 6, [1]),
+])
+def test_gemm_matches_oracle(n, k, bits, ms, libs, oracle):
+    d = libs.cuda()
+    rng = np.random.default_rng(n + k + bits)
+    rows, c, m, nc = _det_rows(rng, n, k, bits)
+    g = k // 128
+    wq, cc, mm = d.det_malloc(n * nc), d.det_malloc(n * 4), d.det_malloc(n * g * 2)
+    codes = np.ascontiguousarray(rows[:, :nc])
+    d.det_memcpy(wq, codes.ctypes.data, codes.nbytes, None)
+    d.det_memcpy(cc, c.ctypes.data, c.nbytes, None)
+    d.det_memcpy(mm, m.ctypes.data, m.nbytes, None)
+    src = libs.QLinear(wq, cc, mm, n, k, bits)
+    sp = d.det_malloc(d.det_linear_repack_bytes(n, k, bits))
+    d.det_linear_repack(C.byref(src), sp, None)
+    stream = libs.QLinear(sp, cc, mm, n, k, bits | libs.DET_LAYOUT_STREAM)
+    try:
+        for mtok in ms:
+            xq = rng.integers(-127, 128, (mtok, k)).astype(np.int8)
+            sx = (1e-3 * (0.5 + rng.random(mtok))).astype(np.float32)
+            mx = rng.integers(1, 65536, (mtok, g)).astype(np.uint16)
+            want = np.zeros((mtok, n), np.float32)
+            oracle.orc_gemm(rows.ctypes.data, n, k, bits, xq.ctypes.data, sx.ctypes.data, mx.ctypes.data, mtok,
+                            want.ctypes.data, 0)
+            dx, ds, dm, dy = d.det_malloc(xq.nbytes), d.det_malloc(sx.nbytes), d.det_malloc(mx.nbytes), d.det_malloc(want.nbytes)
+            d.det_memcpy(dx, xq.ctypes.data, xq.nbytes, None)
+            d.det_memcpy(ds, sx.ctypes.data, sx.nbytes, None)
+            d.det_memcpy(dm, mx.ctypes.data, mx.nbytes, None)
+            for name, lin in (("stream", stream), ("rowmajor", src)):
+                got = np.zeros_like(want)
+                d.det_memset(dy, 0xFF, want.nbytes, None)
+                d.det_gemm(C.byref(lin), dx, ds, dm, mtok, dy, None)
+                d.det_memcpy(got.ctypes.data, dy, got.nbytes, None)
+                d.det_sync()
+                bad = int((got.view(np.uint32) != want.view(np.uint32)).sum())
+                assert bad == 0, f"{name} layout, M={mtok}: {bad} of {want.size} outputs differ"
+            for p in (dx, ds, dm, dy):
+                d.det_free(p)
+        assert d.det_last_error() == 0
+    finally:
+        for p in (wq, cc, mm, sp):
+            d.det_free(p)
