@@ -2,11 +2,13 @@
 // embedding lookup, residual add and greedy argmax.  Replaces kernels/cuda/norm.cu behind the same entry points
 // (det_rmsnorm_quant, det_quant, det_silu_mul_quant, det_embed, det_add, det_argmax).
 //
-// One CTA owns one row.  The sum of squares follows the spec tree (docs/SPEC.md §1.3): the row is padded with +0.0 to
-// P = next power of two, each thread folds an aligned run of P / blockDim values, lanes continue with ascending xor
-// offsets and warps in warp order.  Quantization then re-reads the row with one warp per 128-group (4 values per lane),
-// keeps the produced values in registers across the row-global max, and emits codes, multipliers and the row scale.
+// A row is spread over a thread-block cluster (up to 8 CTAs, one warp per 128-wide slice) so that a single decode row
+// of 5120 or 17408 values is not a one-SM job; the row-wide sum of squares (the spec tree, docs/SPEC.md §1.3) and the
+// row-wide maximum are combined through distributed shared memory.
 #include "runtime.cuh"
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 namespace detb {
 
@@ -23,16 +25,6 @@ struct RowArgs {
     uint16_t* mx;       // NULL: per-row int8 (quant_act_i8)
 };
 
-// Continues the spec tree over the warps of a block whose warp count is a power of two known at run time.
-__device__ __forceinline__ float fold_warps_rt(float warp_total, float* sh, int nw) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    __syncthreads();
-    if (lane == 0) sh[warp] = warp_total;
-    __syncthreads();
-    float v = (lane < nw) ? sh[lane] : 0.0f;
-    for (int off = 1; off < nw; off <<= 1) v = fadd(v, __shfl_xor_sync(FULL, v, off));
-    return __shfl_sync(FULL, v, 0);
-}
 __device__ __forceinline__ float max_block_rt(float v, float* sh, int nw) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     v = max_lanes(v);
@@ -42,99 +34,137 @@ __device__ __forceinline__ float max_block_rt(float v, float* sh, int nw) {
     return max_lanes((lane < nw) ? sh[lane] : sh[0]);
 }
 
-template <int MODE, int RUN, int MAXG>
-__global__ void __launch_bounds__(1024) k_row(RowArgs p) {
-    __shared__ float sh[32];
-    const int row = blockIdx.x;
+// One row is handled by a thread-block cluster of CS CTAs (1, 2, 4 or 8).  A warp owns one 128-wide slice of the row
+// (4 consecutive values per lane); CTA `rank` of the cluster owns the slices [rank * spc, (rank + 1) * spc).
+//   * sum of squares: a slice is an aligned subtree of the spec tree, so each warp folds its slice exactly; the slice
+//     sums are exchanged through distributed shared memory and every CTA finishes the same tree over the P / 128 slice
+//     sums (zero padded), so all CTAs hold the bit-identical row total;
+//   * the row-global maximum of the group scales is order-free: per-CTA maxima are exchanged the same way.
+// Values stay in registers between the two phases.
+constexpr int MAX_SLICES = 256;   // rows up to 32768 values
+
+__device__ __forceinline__ float* peer_smem(float* local, unsigned rank) {
+    return cg::this_cluster().map_shared_rank(local, rank);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(1024) k_row(RowArgs p, int spc /* slices per CTA */, int pslices /* P / 128 */) {
+    __shared__ float slice_sum[32];     // this CTA's slice sums (read by the peers)
+    __shared__ float cta_max;           // this CTA's largest group scale (read by the peers)
+    __shared__ float all_sums[MAX_SLICES];
+    __shared__ float shf[32];
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned rank = cluster.block_rank(), cs = cluster.num_blocks();
+    const int row = blockIdx.y;
     const int n = p.n;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const float* a = p.a + (size_t)row * n;
     const float* b = (MODE == ROW_SWIGLU) ? p.b + (size_t)row * n : p.b;
+    const int slices = (n + 127) >> 7;
+    const int g = (int)rank * spc + warp;           // this warp's slice
+    const bool have = warp < spc && g < slices;
+    const int base = g * 128 + lane * 4;
 
+    float raw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (have) {
+#pragma unroll
+        for (int e = 0; e < 4; e++)
+            if (base + e < n) raw[e] = a[base + e];
+    }
     float inv_rms = 0.0f;
     if (MODE == ROW_RMSNORM) {
-        float sq[RUN];
+        float sq[4];
 #pragma unroll
-        for (int i = 0; i < RUN; i++) {
-            const int idx = threadIdx.x * RUN + i;
-            const float v = idx < n ? a[idx] : 0.0f;
-            sq[i] = fmul(v, v);
+        for (int e = 0; e < 4; e++) sq[e] = fmul(raw[e], raw[e]);
+        const float ssum = fold_lanes<32>(fold_run<4>(sq));
+        if (lane == 0 && warp < spc) slice_sum[warp] = have ? ssum : 0.0f;
+        cluster.sync();
+        // gather the slice sums of the whole row in slice order, zero padded to the tree width
+        for (int i = threadIdx.x; i < pslices; i += blockDim.x) {
+            const int owner = i / spc, idx = i - owner * spc;
+            all_sums[i] = (owner < (int)cs && i < slices) ? peer_smem(slice_sum, owner)[idx] : 0.0f;
         }
-        float ss = fold_lanes<32>(fold_run<RUN>(sq));
-        ss = fold_warps_rt(ss, sh, nw);
-        const float mean = fdiv(ss, (float)n);
+        __syncthreads();
+        // finish the tree: lane owns pslices / 32 consecutive slice sums (or one each when there are fewer than 32)
+        float tot;
+        if (pslices >= 32) {
+            const int per = pslices >> 5;   // 1, 2, 4 or 8
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = i < per ? all_sums[lane * per + i] : 0.0f;
+            // fold the first `per` entries pairwise (per is a power of two; entries past it are never touched)
+#pragma unroll
+            for (int step = 1; step < 8; step <<= 1) {
+#pragma unroll
+                for (int i = 0; i < 8; i += 2 * step)
+                    if (step < per) v[i] = fadd(v[i], v[i + step]);
+            }
+            tot = fold_lanes<32>(v[0]);
+        } else {
+            float v = lane < pslices ? all_sums[lane] : 0.0f;
+            for (int off = 1; off < pslices; off <<= 1) v = fadd(v, __shfl_xor_sync(FULL, v, off));
+            tot = __shfl_sync(FULL, v, 0);
+        }
+        const float mean = fdiv(tot, (float)n);
         inv_rms = fdiv(1.0f, fsqrt(fadd(mean, p.eps)));
     }
 
-    // ---- one warp per 128-wide slice, 4 consecutive values per lane
-    const int slices = (n + 127) >> 7;
-    float val[MAXG][4];
-    float s_slice[MAXG];
-    float local_max = 0.0f;
+    // ---- produce the row values of this warp's slice, the slice scale and the CTA maximum
+    float val[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float s_slice = 0.0f;
+    if (have) {
+        float amax = 0.0f;
 #pragma unroll
-    for (int j = 0; j < MAXG; j++) {
-        const int g = warp + j * nw;
-        s_slice[j] = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 4; e++) val[j][e] = 0.0f;
-        if (g < slices) {
-            const int base = g * 128 + lane * 4;
-            float amax = 0.0f;
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int idx = base + e;
-                float v = 0.0f;
-                if (idx < n) {
-                    if (MODE == ROW_RMSNORM) v = fmul(fmul(a[idx], inv_rms), b[idx]);
-                    else if (MODE == ROW_PLAIN) v = a[idx];
-                    else v = fmul(silu_f(a[idx]), b[idx]);
-                    if (p.y) p.y[(size_t)row * n + idx] = v;
-                }
-                val[j][e] = v;
-                amax = fmaxf(amax, fabsf(v));
+        for (int e = 0; e < 4; e++) {
+            const int idx = base + e;
+            float v = 0.0f;
+            if (idx < n) {
+                if (MODE == ROW_RMSNORM) v = fmul(fmul(raw[e], inv_rms), b[idx]);
+                else if (MODE == ROW_PLAIN) v = raw[e];
+                else v = fmul(silu_f(raw[e]), b[idx]);
+                if (p.y) p.y[(size_t)row * n + idx] = v;
             }
-            amax = max_lanes(amax);
-            s_slice[j] = p.mx ? fdiv(amax, 127.0f) : amax;
-            local_max = fmaxf(local_max, s_slice[j]);
+            val[e] = v;
+            amax = fmaxf(amax, fabsf(v));
         }
+        amax = max_lanes(amax);
+        s_slice = p.mx ? fdiv(amax, 127.0f) : amax;
     }
-    if (!p.q) return;
-    const float top = max_block_rt(local_max, sh, nw);
+    if (!p.q) {
+        if (MODE == ROW_RMSNORM) cluster.sync();   // peers may still be reading slice_sum
+        return;
+    }
+    const float cmax = max_block_rt(s_slice, shf, nw);
+    if (threadIdx.x == 0) cta_max = cmax;
+    cluster.sync();
+    float top = 0.0f;
+    for (unsigned r = 0; r < cs; r++) top = fmaxf(top, *peer_smem(&cta_max, r));
+    cluster.sync();   // nobody exits (or rewrites shared memory) while a peer is still reading it
 
     if (p.mx) {
         // quant_act_i8g: sx = smax / 65535 (1 when smax == 0); per group mult, eff = sx * mult, inv = 1 / eff
         const float sx = (top == 0.0f) ? 1.0f : fdiv(top, 65535.0f);
-        if (threadIdx.x == 0) p.sx[row] = sx;
-#pragma unroll
-        for (int j = 0; j < MAXG; j++) {
-            const int g = warp + j * nw;
-            if (g < slices) {
-                const unsigned mult = group_mult(s_slice[j], sx);
-                const float inv = fdiv(1.0f, fmul(sx, (float)mult));
-                char4 c;
-                c.x = (signed char)quant_code(val[j][0], inv);
-                c.y = (signed char)quant_code(val[j][1], inv);
-                c.z = (signed char)quant_code(val[j][2], inv);
-                c.w = (signed char)quant_code(val[j][3], inv);
-                *reinterpret_cast<char4*>(p.q + (size_t)row * n + g * 128 + lane * 4) = c;
-                if (lane == 0) p.mx[(size_t)row * (n >> 7) + g] = (uint16_t)mult;
-            }
+        if (rank == 0 && threadIdx.x == 0) p.sx[row] = sx;
+        if (have) {
+            const unsigned mult = group_mult(s_slice, sx);
+            const float inv = fdiv(1.0f, fmul(sx, (float)mult));
+            char4 c;
+            c.x = (signed char)quant_code(val[0], inv);
+            c.y = (signed char)quant_code(val[1], inv);
+            c.z = (signed char)quant_code(val[2], inv);
+            c.w = (signed char)quant_code(val[3], inv);
+            *reinterpret_cast<char4*>(p.q + (size_t)row * n + base) = c;
+            if (lane == 0) p.mx[(size_t)row * (n >> 7) + g] = (uint16_t)mult;
         }
     } else {
         // quant_act_i8: s = amax / 127 (1 when amax == 0)
         const float s = (top == 0.0f) ? 1.0f : fdiv(top, 127.0f);
         const float inv = fdiv(1.0f, s);
-        if (threadIdx.x == 0) p.sx[row] = s;
+        if (rank == 0 && threadIdx.x == 0) p.sx[row] = s;
+        if (have) {
 #pragma unroll
-        for (int j = 0; j < MAXG; j++) {
-            const int g = warp + j * nw;
-            if (g < slices) {
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int idx = g * 128 + lane * 4 + e;
-                    if (idx < n) p.q[(size_t)row * n + idx] = (int8_t)quant_code(val[j][e], inv);
-                }
-            }
+            for (int e = 0; e < 4; e++)
+                if (base + e < n) p.q[(size_t)row * n + base + e] = (int8_t)quant_code(val[e], inv);
         }
     }
 }
@@ -144,31 +174,26 @@ static void launch_row(const RowArgs& p, int M, cudaStream_t q) {
     const int n = p.n;
     DETB_REQUIRE(n >= 1 && n <= 32768, "row length must be 1..32768");
     if (p.q && p.mx) DETB_REQUIRE(n % 128 == 0, "grouped quantization needs n % 128 == 0");
-    int P = 32;
+    DETB_REQUIRE(M <= 65535, "at most 65535 rows per call");
+    int P = 128;
     while (P < n) P <<= 1;
-    const int threads = P < 1024 ? P : 1024;
-    const int run = P / threads;                       // 1, 2, 4, ..., 32
-    const int nw = threads / 32;
-    const int maxg = (((n + 127) >> 7) + nw - 1) / nw;   // <= 8
-#define DETB_ROW(RUN_, MAXG_) k_row<MODE, RUN_, MAXG_><<<M, threads, 0, q>>>(p)
-    if (MODE != ROW_RMSNORM) {
-        // no tree: only the slice mapping matters
-        if (maxg <= 1) DETB_ROW(1, 1);
-        else if (maxg <= 2) DETB_ROW(1, 2);
-        else if (maxg <= 4) DETB_ROW(1, 4);
-        else DETB_ROW(1, 8);
-    } else {
-        switch (run) {
-            case 1: DETB_ROW(1, 1); break;
-            case 2: DETB_ROW(2, 1); break;
-            case 4: DETB_ROW(4, 1); break;
-            case 8: DETB_ROW(8, 2); break;
-            case 16: DETB_ROW(16, 4); break;
-            default: DETB_ROW(32, 8); break;
-        }
-    }
-#undef DETB_ROW
-    DETB_CUDA_OK(cudaGetLastError());
+    const int slices = (n + 127) >> 7;
+    int cs = 8;                                   // cluster size: by shape only
+    while (cs > 1 && slices / cs < 4) cs >>= 1;
+    const int spc = (slices + cs - 1) / cs;       // <= 32
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cs, M, 1);
+    cfg.blockDim = dim3(spc * 32, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = q;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DETB_CUDA_OK(cudaLaunchKernelEx(&cfg, k_row<MODE>, p, spc, P / 128));
 }
 
 // ---- embedding rows (bf16 table -> fp32, exact), residual add, argmax
