@@ -193,6 +193,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     rt = C.CDLL("libcudart.so.12")
     assert rt.cudaSetDevice(local_rank) == 0
     h, d = capi.host(), capi.cuda()
+    if args.no_pdl:
+        d.det_debug_set_pdl(0)
     cfg = args.config
     shape = SHAPES[cfg]
     K, W, P, chunk = args.steps, args.warmup, args.prefill, args.chunk
@@ -373,6 +375,7 @@ def main():
     ap.add_argument("--prefill", type=int, default=2048)
     ap.add_argument("--chunk", type=int, default=512)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-pdl", action="store_true", help="measurement switch: plain stream-ordered launches")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

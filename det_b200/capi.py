@@ -88,6 +88,7 @@ CUDA_ABI = {
     "det_graph_launch": (None, [c_void_p]),
     "det_graph_free": (None, [c_void_p]),
     "det_token_feedback": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "det_debug_set_pdl": (None, [c_int]),
     "det_last_error": (c_int, []),
 }
 

@@ -45,6 +45,8 @@ template <int HD>
 __global__ void __launch_bounds__(256) k_attn_prep(const AttnArgs a) {
     constexpr int PER = HD / 32;
     __shared__ float rowbuf[8][HD];
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const long long row = (long long)blockIdx.x * 8 + wib;
     const long long n_q = (long long)a.M * a.n_h, n_kvrows = (long long)a.M * a.n_kv;
@@ -66,6 +68,15 @@ __global__ void __launch_bounds__(256) k_attn_prep(const AttnArgs a) {
         return;
     }
     const bool is_q = row < n_q;
+    if (is_q) {
+        // this (token, head)'s reduction cells start from zero (0 is below every order-preserving score key)
+        if (lane == 0) {
+            a.mxkey[row] = 0u;
+            a.den[row] = 0;
+        }
+#pragma unroll
+        for (int i = 0; i < PER; i++) a.num[row * HD + lane * PER + i] = 0;
+    }
     int t, h;
     const float *src, *wn;
     if (is_q) {
@@ -167,6 +178,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_max(const AttnArgs a) {
     __shared__ float sks[KT];
     __shared__ float sqs[MAX_REP];
     __shared__ unsigned best[MAX_REP];
+    pdl_trigger();
+    pdl_wait();
     const int kvh = blockIdx.y, t = blockIdx.z;
     int k0, k1;
     key_range(a, t, k0, k1);
@@ -220,6 +233,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
     __shared__ float mxs[MAX_REP];
     __shared__ int pq[MAX_REP][KT];
     __shared__ long long den_sh[MAX_REP];
+    pdl_trigger();
+    pdl_wait();
     const int kvh = blockIdx.y, t = blockIdx.z;
     int k0, k1;
     key_range(a, t, k0, k1);
@@ -304,6 +319,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
 
 template <int HD>
 __global__ void k_attn_fin(const AttnArgs a) {
+    pdl_trigger();
+    pdl_wait();
     const size_t row = blockIdx.x;   // t * n_h + h
     const int d = threadIdx.x;
     const int t = (int)(row / a.n_h), h = (int)(row % a.n_h);
@@ -347,15 +364,12 @@ static void run_attention(AttnArgs a, void* scratch, int max_total_keys, cudaStr
     a.nsplit = nsplit;
     a.keys_per_split = tiles_per_split * KT;
 
-    DETB_CUDA_OK(cudaMemsetAsync(base + sm.mx, 0, sm.den - sm.mx, q));
-    if (nsplit > 1) DETB_CUDA_OK(cudaMemsetAsync(base + sm.den, 0, sm.total - sm.den, q));
     const long long rows = (long long)a.M * (a.n_h + 2 * a.n_kv);
-    k_attn_prep<HD><<<(unsigned)((rows + 7) / 8), 256, 0, q>>>(a);
+    launch_pdl(k_attn_prep<HD>, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, q, 1, a);
     const dim3 grid(nsplit, a.n_kv, a.M);
-    k_attn_max<HD><<<grid, ATT_THREADS, 0, q>>>(a);
-    k_attn_acc<HD><<<grid, ATT_THREADS, 0, q>>>(a);
-    if (nsplit > 1) k_attn_fin<HD><<<a.M * a.n_h, HD, 0, q>>>(a);
-    DETB_CUDA_OK(cudaGetLastError());
+    launch_pdl(k_attn_max<HD>, grid, dim3(ATT_THREADS), 0, q, 1, a);
+    launch_pdl(k_attn_acc<HD>, grid, dim3(ATT_THREADS), 0, q, 1, a);
+    if (nsplit > 1) launch_pdl(k_attn_fin<HD>, dim3(a.M * a.n_h), dim3(HD), 0, q, 1, a);
 }
 
 static void attention_entry(const det_attn_layer* L, const det_kv_cache* kv, const float* qg, const float* k,

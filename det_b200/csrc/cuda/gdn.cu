@@ -36,6 +36,8 @@ __device__ __forceinline__ float conv_in(const GdnArgs& g, int tau, int c) {
 }
 
 __global__ void __launch_bounds__(128) k_gdn_prep(const GdnArgs g) {
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const int t = blockIdx.y;
     const int heads = 2 * g.n_k + g.n_v;     // 128-channel slices of conv_dim
@@ -104,6 +106,8 @@ constexpr int RR = DK / RL;   // rows per lane (16)
 
 __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
     __shared__ float slab[DK][RC + 1];
+    pdl_trigger();
+    pdl_wait();
     const int h = blockIdx.x / (DV / RC);
     const int j0 = (blockIdx.x % (DV / RC)) * RC;
     const int kh = h / g.rep;
@@ -170,6 +174,8 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
 
 // on = rmsnorm(o, norm, eps) * silu_f(z): one warp per (token, v head).  Extra CTAs past the rows move the conv state.
 __global__ void __launch_bounds__(128) k_gdn_out(const GdnArgs g, int row_blocks) {
+    pdl_trigger();
+    pdl_wait();
     if ((int)blockIdx.x >= row_blocks) {
         // conv state <- the last three raw inputs (times M-3 .. M-1); each channel is read fully before it is written
         const int c = (blockIdx.x - row_blocks) * 128 + threadIdx.x;
@@ -249,11 +255,10 @@ void det_gdn_ex(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, cons
     g.gin = gin;
     cudaStream_t q = queue_of(st);
     const int heads = 2 * n_k + n_v;
-    k_gdn_prep<<<dim3((heads + 3) / 4, M), 128, 0, q>>>(g);
-    k_gdn_recur<<<n_v * (DV / RC), RC * RL, 0, q>>>(g);
+    launch_pdl(k_gdn_prep, dim3((heads + 3) / 4, M), dim3(128), 0, q, 1, g);
+    launch_pdl(k_gdn_recur, dim3(n_v * (DV / RC)), dim3(RC * RL), 0, q, 1, g);
     const int row_blocks = (int)(((long long)M * n_v + 3) / 4);
-    k_gdn_out<<<row_blocks + (g.conv_dim + 127) / 128, 128, 0, q>>>(g, row_blocks);
-    DETB_CUDA_OK(cudaGetLastError());
+    launch_pdl(k_gdn_out, dim3(row_blocks + (g.conv_dim + 127) / 128), dim3(128), 0, q, 1, g, row_blocks);
 }
 
 void det_gdn(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a,

@@ -170,6 +170,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
     unsigned long long* empty = full + MAX_SLOTS;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_trigger();
     if (tid == 0) {
         for (int s = 0; s < a.slots; s++) {
             mbar_init(&full[s], 1);
@@ -203,7 +204,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
         return;
     }
 
-    // ---------------- consumers: stage the activations once (piece-transposed like the weights), then drain records
+    // ---------------- consumers: stage the activations once (piece-transposed like the weights), then drain records.
+    // The activations (and the output rows) belong to earlier kernels: wait for them here, while the producer is
+    // already pulling weights.
+    pdl_wait();
     {
         const int pieces_per_tok = g.K >> 4;
         const int total = MT * pieces_per_tok;
@@ -328,8 +332,7 @@ static void launch_gemv(const GemvArgs& a, const GemvPlan& p, cudaStream_t q) {
                                           (int)(smem_optin())));
         configured = true;
     }
-    k_gemv_stream<BITS, MT><<<p.grid, GEMV_THREADS, p.smem, q>>>(a);
-    DETB_CUDA_OK(cudaGetLastError());
+    launch_pdl(k_gemv_stream<BITS, MT>, dim3(p.grid), dim3(GEMV_THREADS), p.smem, q, 1, a);
 }
 
 template <int BITS>

@@ -53,6 +53,8 @@ __global__ void __launch_bounds__(1024) k_row(RowArgs p, int spc /* slices per C
     __shared__ float cta_max;           // this CTA's largest group scale (read by the peers)
     __shared__ float all_sums[MAX_SLICES];
     __shared__ float shf[32];
+    pdl_trigger();
+    pdl_wait();
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned rank = cluster.block_rank(), cs = cluster.num_blocks();
     const int row = blockIdx.y;
@@ -181,24 +183,14 @@ static void launch_row(const RowArgs& p, int M, cudaStream_t q) {
     int cs = 8;                                   // cluster size: by shape only
     while (cs > 1 && slices / cs < 4) cs >>= 1;
     const int spc = (slices + cs - 1) / cs;       // <= 32
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(cs, M, 1);
-    cfg.blockDim = dim3(spc * 32, 1, 1);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = q;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cs;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    DETB_CUDA_OK(cudaLaunchKernelEx(&cfg, k_row<MODE>, p, spc, P / 128));
+    launch_pdl(k_row<MODE>, dim3(cs, M, 1), dim3(spc * 32, 1, 1), 0, q, cs, p, spc, P / 128);
 }
 
 // ---- embedding rows (bf16 table -> fp32, exact), residual add, argmax
 __global__ void k_embed_rows(const uint16_t* __restrict__ table, const int* __restrict__ ids, int H,
                              float* __restrict__ x) {
+    pdl_trigger();
+    pdl_wait();
     const uint16_t* src = table + (size_t)ids[blockIdx.x] * H;
     float* dst = x + (size_t)blockIdx.x * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = __uint_as_float((unsigned)src[i] << 16);
@@ -212,6 +204,8 @@ __global__ void k_residual_add(float* __restrict__ x, const float* __restrict__ 
 __global__ void __launch_bounds__(1024) k_argmax_rows(const float* __restrict__ logits, int V, int* __restrict__ out) {
     __shared__ float bv[32];
     __shared__ int bi[32];
+    pdl_trigger();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * V;
     float best = -INFINITY;
     int at = 0x7fffffff;
@@ -267,8 +261,7 @@ void det_silu_mul_quant(const float* g, const float* u, int M, int n, float* h, 
 }
 void det_embed(const uint16_t* table_bf16, const int* ids, int M, int H, float* x, cudaStream_t st) {
     if (M <= 0) return;
-    k_embed_rows<<<M, 256, 0, queue_of(st)>>>(table_bf16, ids, H, x);
-    DETB_CUDA_OK(cudaGetLastError());
+    launch_pdl(k_embed_rows, dim3(M), dim3(256), 0, queue_of(st), 1, table_bf16, ids, H, x);
 }
 void det_add(float* x, const float* y, long long n, cudaStream_t st) {
     if (n <= 0) return;
@@ -277,8 +270,7 @@ void det_add(float* x, const float* y, long long n, cudaStream_t st) {
 }
 void det_argmax(const float* logits, int M, int V, int* out, cudaStream_t st) {
     if (M <= 0) return;
-    k_argmax_rows<<<M, 1024, 0, queue_of(st)>>>(logits, V, out);
-    DETB_CUDA_OK(cudaGetLastError());
+    launch_pdl(k_argmax_rows, dim3(M), dim3(1024), 0, queue_of(st), 1, logits, V, out);
 }
 
 }  // extern "C"

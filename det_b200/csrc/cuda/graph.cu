@@ -6,6 +6,8 @@
 namespace detb {
 __global__ void k_token_feedback(const int* __restrict__ pick, int* __restrict__ pos, int* __restrict__ log,
                                  int log_base, int log_cap) {
+    pdl_trigger();
+    pdl_wait();
     const int p = *pos;
     const int slot = p - log_base;
     if (log && slot >= 0 && slot < log_cap) log[slot] = *pick;
@@ -44,8 +46,7 @@ void det_graph_free(void* graph) {
 }
 
 void det_token_feedback(const int* pick, int* pos, int* log, int log_base, int log_cap, cudaStream_t st) {
-    k_token_feedback<<<1, 1, 0, queue_of(st)>>>(pick, pos, log, log_base, log_cap);
-    DETB_CUDA_OK(cudaGetLastError());
+    launch_pdl(k_token_feedback, dim3(1), dim3(1), 0, queue_of(st), 1, pick, pos, log, log_base, log_cap);
 }
 
 }  // extern "C"

@@ -32,6 +32,14 @@ namespace detb {
 
 constexpr unsigned FULL = 0xffffffffu;
 
+// Programmatic dependent launch (PTX griddepcontrol).  A kernel launched with the programmatic-serialization attribute
+// may start while its predecessor in the stream still runs: pdl_trigger() lets the successor's CTAs be scheduled,
+// pdl_wait() blocks until the predecessor has completed and its writes are visible.  Every kernel here triggers first
+// thing and waits before it touches anything an earlier kernel may write; only read-only weights are fetched before
+// the wait.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- the five rounded operations and the conversions (docs/SPEC.md §1.2, §8 CUDA bullet)
 __device__ __forceinline__ float fmul(float a, float b) { return __fmul_rn(a, b); }
 __device__ __forceinline__ float fadd(float a, float b) { return __fadd_rn(a, b); }

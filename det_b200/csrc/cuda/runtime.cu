@@ -67,6 +67,8 @@ cudaStream_t queue_of(cudaStream_t st) { return st ? st : rt().queue; }
 int sm_count() { return rt().sm_count; }
 size_t smem_optin() { return rt().smem_optin; }
 int* error_word() { return rt().error_word; }
+static bool g_pdl = true;
+bool pdl_enabled() { return g_pdl; }
 
 // ---- primitive test hook kernels
 __global__ void k_unary_binary(int op, const float* __restrict__ x, int n, float* __restrict__ out) {
@@ -190,6 +192,8 @@ void det_sync(void) {
     }
 }
 void det_flush(void) {}
+// Debug switch for A/B measurements: programmatic dependent launch on (default) or off.
+void det_debug_set_pdl(int on) { g_pdl = on != 0; }
 
 void det_memset(void* p, int value, size_t bytes, cudaStream_t st) {
     DETB_CUDA_OK(cudaMemsetAsync(p, value, bytes, queue_of(st)));

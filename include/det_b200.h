@@ -176,6 +176,10 @@ void det_graph_free(void* graph);
  * All pointers are device pointers.                                                                                  */
 void det_token_feedback(const int* pick, int* pos, int* log, int log_base, int log_cap, cudaStream_t st);
 
+/* Measurement switch: programmatic dependent launch between the library's kernels on (default, non-zero) or off.
+ * Results are identical either way; only the overlap of one kernel's prologue with its predecessor's tail changes.  */
+void det_debug_set_pdl(int on);
+
 /* Last error recorded by a bounded device-side wait (0 = none; see the DETB_ERR_* codes in csrc/cuda/runtime.cuh).
  * Waits for pending work.                                                                                            */
 int det_last_error(void);

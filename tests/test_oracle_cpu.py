@@ -1,0 +1,103 @@
+"""Pins the CPU oracle (oracle/spec.hpp) against the committed known-answer vectors of tests/golden (an independent
+numpy restatement of the spec's primitives) and against the spec's literal constants."""
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+G = np.load(Path(__file__).resolve().parent / "golden" / "spec_vectors.npz")
+
+
+def _prim(oracle, op, x, m=1, n=None):
+    x = np.ascontiguousarray(x, np.float32)
+    n = len(x) if n is None else n
+    out = np.zeros(max(len(x), m), np.float32)
+    oracle.orc_prim(op, x.ctypes.data, len(x), m, n, out.ctypes.data, len(out))
+    return out
+
+
+def _same(a, b):
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    return np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_elementwise_primitives(oracle):
+    x = G["x"]
+    for op, key in ((0, "exp"), (3, "sigmoid"), (4, "silu"), (2, "softplus")):
+        got = _prim(oracle, op, x)[: len(x)]
+        bad = np.flatnonzero(got.view(np.uint32) != G[key].view(np.uint32))
+        bad = [i for i in bad if not (np.isnan(got[i]) and np.isnan(G[key][i]))]
+        assert not bad, f"{key}: {len(bad)} differ, first x={x[bad[0]]!r} oracle={got[bad[0]]!r} numpy={G[key][bad[0]]!r}"
+    assert _same(_prim(oracle, 1, G["pos"])[: len(G["pos"])], G["log"])
+
+
+def test_treesum(oracle):
+    rows = G["tree_rows"]
+    for i, n in enumerate(G["tree_len"]):
+        row = np.ascontiguousarray(rows[i, :n])
+        assert _same([oracle.orc_treesum(row.ctypes.data, int(n))], [G["tree_out"][i]]), f"row {i} of length {n}"
+
+
+def test_quant_act_i8g(oracle):
+    qx = np.ascontiguousarray(G["qx"])
+    m, n = qx.shape
+    q, sx, mx = np.zeros((m, n), np.int8), np.zeros(m, np.float32), np.zeros((m, n // 128), np.uint16)
+    oracle.orc_quant(qx.ctypes.data, m, n, q.ctypes.data, sx.ctypes.data, mx.ctypes.data)
+    assert np.array_equal(q, G["q_codes"])
+    assert np.array_equal(mx, G["q_mx"])
+    assert _same(sx, G["q_sx"])
+
+
+def test_unpack_and_gemm_row(oracle):
+    k = 512
+    rows = {}
+    for bits in (4, 6, 8):
+        packed = np.ascontiguousarray(G[f"packed{bits}"])
+        codes = np.zeros(k, np.int8)
+        oracle.orc_unpack_row(packed.ctypes.data, bits, k, codes.ctypes.data)
+        assert np.array_equal(codes, G[f"codes{bits}"]), f"W{bits}"
+        c = np.array([3.1e-7], np.float32)
+        rows[bits] = np.concatenate([packed, c.view(np.uint8), G["gemm_m"].view(np.uint8)])
+    xq, mx = np.ascontiguousarray(G["gemm_xq"]), np.ascontiguousarray(G["gemm_mx"])
+    sx = np.array([1.7e-3], np.float32)
+    for i, bits in enumerate((4, 6, 8)):
+        y = np.zeros(1, np.float32)
+        row = np.ascontiguousarray(rows[bits])
+        oracle.orc_gemm(row.ctypes.data, 1, k, bits, xq.ctypes.data, sx.ctypes.data, mx.ctypes.data, 1, y.ctypes.data, 0)
+        assert _same(y, G["gemm_out"][i:i + 1]), f"W{bits}"
+
+
+def test_splitmix64_and_sampling_weights(oracle):
+    state = C.c_uint64(0)
+    for want_state, want_out in zip(G["sm_states"], G["sm_outs"]):
+        assert oracle.orc_splitmix64(C.byref(state)) == int(want_out)
+        assert state.value == int(want_state)
+    logits = np.ascontiguousarray(G["logits"])
+    for key, inv_temp in (("weights_1", np.float32(1.0)), ("weights_07", np.float32(1.0) / np.float32(0.7))):
+        w = np.zeros(len(logits), np.uint64)
+        oracle.orc_weights(logits.ctypes.data, len(logits), float(inv_temp), w.ctypes.data)
+        assert np.array_equal(w, G[key]), key
+
+
+def test_literal_constants(oracle):
+    """The constants the reference pins literally (spec/layers.rs:16,147; model.rs:47; spec/prim.rs:204-211)."""
+    assert _prim(oracle, 0, [0.0])[0] == 1.0
+    one = np.array([1.0], np.float32)
+    w = np.zeros(1, np.uint64)
+    oracle.orc_weights(one.ctypes.data, 1, 1.0, w.ctypes.data)
+    assert int(w[0]) == 1 << 32                      # the largest weight is exactly 2^32 (33 bits)
+    assert np.float32(1.0 / 1024.0) == np.float32(2.0 ** -10)
+    assert np.array([0x3DB504F3], np.uint32).view(np.float32)[0] == np.float32(1.0 / np.sqrt(np.float32(128.0)))
+
+
+def test_sampler_properties(oracle):
+    """top_p <= 0 keeps the first candidate only; top_k = 1 is argmax; a huge top_k is the plain sampler."""
+    rng = np.random.default_rng(5)
+    logits = np.ascontiguousarray((rng.random(5000) * 10).astype(np.float32))
+    best = oracle.orc_argmax(logits.ctypes.data, len(logits))
+    for z in (0, 1, 2 ** 63, 2 ** 64 - 1):
+        assert oracle.orc_sample(logits.ctypes.data, len(logits), 1.0, 0, 0.0, z) == best
+        assert oracle.orc_sample(logits.ctypes.data, len(logits), 1.0, 1, 1.0, z) == best
+        a = oracle.orc_sample(logits.ctypes.data, len(logits), 0.5, 0, 1.0, z)
+        b = oracle.orc_sample(logits.ctypes.data, len(logits), 0.5, len(logits) + 5, 1.0, z)
+        assert a == b
