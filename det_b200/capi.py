@@ -39,7 +39,14 @@ class GdnState(C.Structure):
     _fields_ = [("conv_state", c_void_p), ("S", c_void_p)]
 
 
+class ActSource(C.Structure):
+    """det_act_source (include/det_b200.h): fp32 inputs of a GEMM whose activation quantization is fused in."""
+    _fields_ = [("kind", c_int), ("a", c_void_p), ("b", c_void_p), ("eps", c_float), ("xq", c_void_p), ("sx", c_void_p),
+                ("mx", c_void_p)]
+
+
 DET_LAYOUT_STREAM = 0x100
+DET_ACT_RMSNORM, DET_ACT_PLAIN, DET_ACT_SWIGLU = 1, 2, 3
 
 # every symbol include/det_b200.h declares: name -> (restype, argtypes)
 CUDA_ABI = {
@@ -62,6 +69,8 @@ CUDA_ABI = {
     "det_gemm": (None, [C.POINTER(QLinear), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "det_gemm_ex": (None, [C.POINTER(QLinear), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                            C.POINTER(c_int), C.POINTER(c_void_p), c_void_p]),
+    "det_gemm_fused": (None, [C.POINTER(QLinear), C.POINTER(ActSource), c_int, c_void_p, c_int, c_int, C.POINTER(c_int),
+                              C.POINTER(c_void_p), c_void_p]),
     "det_gemm_scratch_bytes": (c_size_t, [c_int, c_int]),
     "det_gemm_set_scratch": (None, [c_void_p, c_size_t]),
     "det_attention": (None, [C.POINTER(AttnLayer), C.POINTER(KvCache), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -97,6 +106,7 @@ HOST_API = {
     "dh_cuda_backend_new": (c_void_p, [c_int, c_int]),
     "dh_backend_free": (None, [c_void_p]),
     "dh_backend_name": (c_int, [c_void_p, c_char_p, c_size_t]),
+    "dh_cuda_debug": (None, [c_void_p, C.c_uint, c_int]),
     "dh_cuda_test_prim": (None, [c_int, c_void_p, c_size_t, c_size_t, c_size_t, c_void_p, c_size_t]),
     "dh_model_new_synth": (c_void_p, [c_void_p, c_char_p, c_size_t, c_u64, c_size_t, c_size_t]),
     "dh_model_free": (None, [c_void_p]),

@@ -115,8 +115,9 @@ extern "C" {
 size_t det_gemm_scratch_bytes(int M, int K) { return (size_t)(M > 0 ? M : 1) * (size_t)(K / 128) * sizeof(int); }
 void det_gemm_set_scratch(void* p, size_t bytes) { (void)p; (void)bytes; }
 
-void det_gemm_ex(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M, float* y,
-                 int accumulate, int nparts, const int* offs, float* const* dsts, cudaStream_t st) {
+static void gemm_entry(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx,
+                       const det_act_source* src, int M, float* y, int accumulate, int nparts, const int* offs,
+                       float* const* dsts, cudaStream_t st) {
     if (M <= 0) return;
     const int bits = L->bits & 0xff;
     const bool stream = (L->bits & DET_LAYOUT_STREAM) != 0;
@@ -140,13 +141,27 @@ void det_gemm_ex(const det_qlinear* L, const int8_t* xq, const float* sx, const 
         out.y = dsts[0];
     }
     cudaStream_t q = queue_of(st);
-    if (stream) {
+    if (src) {
+        DETB_REQUIRE(stream, "det_gemm_fused needs the streaming weight layout");
+        gemv_stream_launch(L, bits, nullptr, nullptr, nullptr, M, out, q, src);
+    } else if (stream) {
         gemv_stream_launch(L, bits, xq, sx, mx, M, out, q);
     } else {
         if (bits == 8) gemm_rowmajor_bits<8>(L, xq, sx, mx, M, out, q);
         else if (bits == 6) gemm_rowmajor_bits<6>(L, xq, sx, mx, M, out, q);
         else gemm_rowmajor_bits<4>(L, xq, sx, mx, M, out, q);
     }
+}
+
+void det_gemm_ex(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M, float* y,
+                 int accumulate, int nparts, const int* offs, float* const* dsts, cudaStream_t st) {
+    gemm_entry(L, xq, sx, mx, nullptr, M, y, accumulate, nparts, offs, dsts, st);
+}
+
+void det_gemm_fused(const det_qlinear* L, const det_act_source* src, int M, float* y, int accumulate, int nparts,
+                    const int* offs, float* const* dsts, cudaStream_t st) {
+    DETB_REQUIRE(src != nullptr, "det_gemm_fused needs an activation source");
+    gemm_entry(L, nullptr, nullptr, nullptr, src, M, y, accumulate, nparts, offs, dsts, st);
 }
 
 void det_gemm(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M, float* y,

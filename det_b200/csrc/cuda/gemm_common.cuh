@@ -96,6 +96,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
 
 // Entry of the streaming GEMV (gemv_stream.cu): M tokens against a det_linear_repack layout.
 void gemv_stream_launch(const det_qlinear* L, int bits, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
-                        const OutSpec& out, cudaStream_t q);
+                        const OutSpec& out, cudaStream_t q, const det_act_source* src = nullptr);
 
 }  // namespace detb

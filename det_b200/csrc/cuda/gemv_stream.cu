@@ -122,7 +122,20 @@ struct GemvArgs {
     int workers;              // consumer warps that take records (<= NCW); warp w owns slots w, w + workers, ...
     int* error_flag;
     OutSpec out;
+    // Fused activation prologue (k_gemv_stream<.., FUSED = true>): the rows are produced from fp32 inputs inside the
+    // kernel — the op sequences of RMSNorm + quant_act_i8g, plain quant_act_i8g or SwiGLU + quant_act_i8g — instead of
+    // being read as codes.  CTA 0 also stores the codes / scale / multipliers for later consumers when asked to.
+    int pro;                  // PRO_RMS, PRO_PLAIN, PRO_SWIGLU
+    const float* pa;          // x, or the gate rows
+    const float* pb;          // norm weight, or the up rows
+    float eps;
+    int pslices;              // next power of two >= K, over 128
+    int8_t* xq_out;
+    float* sx_out;
+    uint16_t* mx_out;
 };
+enum : int { PRO_RMS = 1, PRO_PLAIN = 2, PRO_SWIGLU = 3 };
+constexpr int FUSED_MAX_ROUNDS = 9;   // slices per consumer warp: K <= 9 * 16 * 128 = 18432
 
 // Sixteen words of four consecutive-k codes from one unit; `pu` is the byte distance between pieces (U * 16).
 template <int BITS>
@@ -156,9 +169,126 @@ __device__ __forceinline__ void unpack_unit(const uint8_t* wp, int pu, unsigned 
     }
 }
 
+
+// Produces the int8 rows of this pass from fp32 inputs, straight into the staged (piece-transposed) layout.
+// One warp owns one 128-wide slice at a time, 4 consecutive values per lane, values held in registers between phases;
+// the row-wide sum of squares is the spec tree (slice sums are aligned subtrees; every warp finishes the same tree over
+// them), the row-wide maximum is order-free.  Same fp32 operation sequence as k_row in glue.cu.
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory"); }
+
+__device__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2* xmeta, float* slice_sum, float* wmax, float* sxs) {
+    const StreamGeom& g = a.g;
+    const int K = g.K, U = g.U, G = g.G;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool keep = blockIdx.x == 0 && a.xq_out != nullptr;
+    for (int t = 0; t < a.mt; t++) {
+        const float* pa = a.pa + (size_t)t * K;
+        const float* pb = a.pro == PRO_SWIGLU ? a.pb + (size_t)t * K : a.pb;
+        float v[FUSED_MAX_ROUNDS][4];
+#pragma unroll
+        for (int r = 0; r < FUSED_MAX_ROUNDS; r++) {
+            const int s = warp + r * NCW;
+            float4 x4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (s < G) x4 = *reinterpret_cast<const float4*>(pa + s * 128 + lane * 4);
+            v[r][0] = x4.x; v[r][1] = x4.y; v[r][2] = x4.z; v[r][3] = x4.w;
+        }
+        float inv_rms = 0.0f;
+        if (a.pro == PRO_RMS) {
+#pragma unroll
+            for (int r = 0; r < FUSED_MAX_ROUNDS; r++) {
+                const int s = warp + r * NCW;
+                float sq[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) sq[e] = fmul(v[r][e], v[r][e]);
+                const float ssum = fold_lanes<32>(fold_run<4>(sq));
+                if (lane == 0 && s < G) slice_sum[s] = ssum;
+            }
+            for (int i = G + tid; i < a.pslices; i += NCW * 32) slice_sum[i] = 0.0f;
+            consumer_barrier();
+            float tot;
+            if (a.pslices >= 32) {
+                const int per = a.pslices >> 5;   // 1, 2, 4 or 8
+                float w8[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) w8[i] = i < per ? slice_sum[lane * per + i] : 0.0f;
+#pragma unroll
+                for (int step = 1; step < 8; step <<= 1) {
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2 * step)
+                        if (step < per) w8[i] = fadd(w8[i], w8[i + step]);
+                }
+                tot = fold_lanes<32>(w8[0]);
+            } else {
+                float w1 = lane < a.pslices ? slice_sum[lane] : 0.0f;
+                for (int off = 1; off < a.pslices; off <<= 1) w1 = fadd(w1, __shfl_xor_sync(FULL, w1, off));
+                tot = __shfl_sync(FULL, w1, 0);
+            }
+            inv_rms = fdiv(1.0f, fsqrt(fadd(fdiv(tot, (float)K), a.eps)));
+        }
+        float s_slice[FUSED_MAX_ROUNDS];
+        float local_max = 0.0f;
+#pragma unroll
+        for (int r = 0; r < FUSED_MAX_ROUNDS; r++) {
+            const int s = warp + r * NCW;
+            s_slice[r] = 0.0f;
+            if (s < G) {
+                float amax = 0.0f;
+                float4 b4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (a.pro != PRO_PLAIN) b4 = *reinterpret_cast<const float4*>(pb + s * 128 + lane * 4);
+                const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    float val = v[r][e];
+                    if (a.pro == PRO_RMS) val = fmul(fmul(val, inv_rms), bb[e]);
+                    else if (a.pro == PRO_SWIGLU) val = fmul(silu_f(val), bb[e]);
+                    v[r][e] = val;
+                    amax = fmaxf(amax, fabsf(val));
+                }
+                amax = max_lanes(amax);
+                s_slice[r] = fdiv(amax, 127.0f);
+                local_max = fmaxf(local_max, s_slice[r]);
+            }
+        }
+        if (lane == 0) wmax[warp] = local_max;
+        consumer_barrier();
+        float top = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NCW; w++) top = fmaxf(top, wmax[w]);
+        const float sx = (top == 0.0f) ? 1.0f : fdiv(top, 65535.0f);
+        if (tid == 0) {
+            sxs[t] = sx;
+            if (keep) a.sx_out[t] = sx;
+        }
+#pragma unroll
+        for (int r = 0; r < FUSED_MAX_ROUNDS; r++) {
+            const int s = warp + r * NCW;
+            if (s < G) {
+                const unsigned mult = group_mult(s_slice[r], sx);
+                const float inv = fdiv(1.0f, fmul(sx, (float)mult));
+                unsigned word = (unsigned)(quant_code(v[r][0], inv) & 0xff);
+                word |= (unsigned)(quant_code(v[r][1], inv) & 0xff) << 8;
+                word |= (unsigned)(quant_code(v[r][2], inv) & 0xff) << 16;
+                word |= (unsigned)(quant_code(v[r][3], inv) & 0xff) << 24;
+                // value index e = s * 128 + lane * 4: unit 2s + lane / 16, piece (lane % 16) / 4, word lane % 4
+                const int u = 2 * s + (lane >> 4), pc = (lane & 15) >> 2;
+                *reinterpret_cast<unsigned*>(xs + ((size_t)(t * 4 + pc) * U + u) * 16 + (lane & 3) * 4) = word;
+                int sum = __dp4a((int)word, 0x01010101, 0);
+#pragma unroll
+                for (int off = 1; off < 16; off <<= 1) sum += __shfl_xor_sync(FULL, sum, off);
+                if ((lane & 15) == 0) xmeta[t * U + u] = make_int2(sum, (int)mult);
+                if (keep) {
+                    *reinterpret_cast<unsigned*>(a.xq_out + (size_t)t * K + s * 128 + lane * 4) = word;
+                    if (lane == 0) a.mx_out[(size_t)t * G + s] = (uint16_t)mult;
+                }
+            }
+        }
+        consumer_barrier();
+    }
+}
+
 // Shared memory: [slots x rec_bytes] [x pieces: MT*K] [xmeta: MT*U int2 = (sum of x over the unit, mx of its group)]
-//                [full[MAX_SLOTS]] [empty[MAX_SLOTS]]
-template <int BITS, int MT>
+//                [full[MAX_SLOTS]] [empty[MAX_SLOTS]] [slice sums: 256 f32] [warp maxima: NCW f32] [row scales: 8 f32]
+template <int BITS, int MT, bool FUSED>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     const StreamGeom& g = a.g;
@@ -168,6 +298,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
     int2* xmeta = reinterpret_cast<int2*>(xs + (size_t)MT * g.K);
     unsigned long long* full = reinterpret_cast<unsigned long long*>(xmeta + MT * U);
     unsigned long long* empty = full + MAX_SLOTS;
+    float* slice_sum = reinterpret_cast<float*>(empty + MAX_SLOTS);
+    float* wmax = slice_sum + 256;
+    float* sxs = wmax + NCW;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_trigger();
@@ -208,7 +341,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
     // The activations (and the output rows) belong to earlier kernels: wait for them here, while the producer is
     // already pulling weights.
     pdl_wait();
-    {
+    if (FUSED) {
+        fused_stage(a, xs, xmeta, slice_sum, wmax, sxs);
+    } else {
         const int pieces_per_tok = g.K >> 4;
         const int total = MT * pieces_per_tok;
         for (int base = 0; base < total; base += NCW * 32) {
@@ -296,7 +431,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
         if (j == 0 && n < g.N) {
 #pragma unroll
             for (int t = 0; t < MT; t++)
-                if (t < a.mt) emit(a.out, a.t0 + t, n, fmul(fmul(i64_to_f32(acc[t]), cn), a.sx[t]));
+                if (t < a.mt) emit(a.out, a.t0 + t, n, fmul(fmul(i64_to_f32(acc[t]), cn), FUSED ? sxs[t] : a.sx[t]));
         }
     }
     if (!ok && lane == 0) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
@@ -311,7 +446,7 @@ struct GemvPlan {
 // A plan by shape only: the ring takes whatever shared memory the staged activations leave, up to MAX_SLOTS records.
 static bool plan_gemv(const StreamGeom& g, int MT, GemvPlan& p) {
     const size_t budget = smem_optin() - 1024;
-    const size_t fixed = (size_t)MT * g.K + (size_t)MT * g.U * 8 + 2 * MAX_SLOTS * 8;
+    const size_t fixed = (size_t)MT * g.K + (size_t)MT * g.U * 8 + 2 * MAX_SLOTS * 8 + (256 + NCW + 8) * 4;
     if (fixed + 2 * (size_t)g.rec_bytes > budget) return false;
     int slots = (int)((budget - fixed) / g.rec_bytes);
     if (slots > MAX_SLOTS) slots = MAX_SLOTS;
@@ -324,20 +459,25 @@ static bool plan_gemv(const StreamGeom& g, int MT, GemvPlan& p) {
     return true;
 }
 
-template <int BITS, int MT>
-static void launch_gemv(const GemvArgs& a, const GemvPlan& p, cudaStream_t q) {
+template <int BITS, int MT, bool FUSED>
+static void launch_gemv_one(const GemvArgs& a, const GemvPlan& p, cudaStream_t q) {
     static bool configured = false;
     if (!configured) {
-        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemv_stream<BITS, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemv_stream<BITS, MT, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)(smem_optin())));
         configured = true;
     }
-    launch_pdl(k_gemv_stream<BITS, MT>, dim3(p.grid), dim3(GEMV_THREADS), p.smem, q, 1, a);
+    launch_pdl(k_gemv_stream<BITS, MT, FUSED>, dim3(p.grid), dim3(GEMV_THREADS), p.smem, q, 1, a);
+}
+template <int BITS, int MT>
+static void launch_gemv(const GemvArgs& a, const GemvPlan& p, cudaStream_t q) {
+    if (a.pro) launch_gemv_one<BITS, MT, true>(a, p, q);
+    else launch_gemv_one<BITS, MT, false>(a, p, q);
 }
 
 template <int BITS>
 static void gemv_stream_bits(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
-                             const OutSpec& out, cudaStream_t q) {
+                             const OutSpec& out, cudaStream_t q, const det_act_source* src) {
     const StreamGeom g = stream_geom(L->N, L->K, BITS);
     int t0 = 0;
     while (t0 < M) {
@@ -360,6 +500,20 @@ static void gemv_stream_bits(const det_qlinear* L, const int8_t* xq, const float
         a.workers = p.workers;
         a.error_flag = error_word();
         a.out = out;
+        a.pro = 0;
+        if (src) {
+            DETB_REQUIRE(g.G <= FUSED_MAX_ROUNDS * NCW, "K is too large for the fused activation prologue");
+            a.pro = src->kind;
+            a.pa = src->a + (size_t)t0 * g.K;
+            a.pb = src->kind == PRO_SWIGLU ? src->b + (size_t)t0 * g.K : src->b;
+            a.eps = src->eps;
+            int P = 128;
+            while (P < g.K) P <<= 1;
+            a.pslices = P / 128;
+            a.xq_out = src->xq ? src->xq + (size_t)t0 * g.K : nullptr;
+            a.sx_out = src->sx ? src->sx + t0 : nullptr;
+            a.mx_out = src->mx ? src->mx + (size_t)t0 * g.G : nullptr;
+        }
         switch (MT) {
             case 1: launch_gemv<BITS, 1>(a, p, q); break;
             case 2: launch_gemv<BITS, 2>(a, p, q); break;
@@ -371,10 +525,15 @@ static void gemv_stream_bits(const det_qlinear* L, const int8_t* xq, const float
 }
 
 void gemv_stream_launch(const det_qlinear* L, int bits, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
-                        const OutSpec& out, cudaStream_t q) {
-    if (bits == 8) gemv_stream_bits<8>(L, xq, sx, mx, M, out, q);
-    else if (bits == 6) gemv_stream_bits<6>(L, xq, sx, mx, M, out, q);
-    else gemv_stream_bits<4>(L, xq, sx, mx, M, out, q);
+                        const OutSpec& out, cudaStream_t q, const det_act_source* src) {
+    if (src) {
+        DETB_REQUIRE(src->kind >= PRO_RMS && src->kind <= PRO_SWIGLU && src->a, "bad activation source");
+        DETB_REQUIRE((src->xq != nullptr) == (src->sx != nullptr) && (src->xq != nullptr) == (src->mx != nullptr),
+                     "the quantized-row outputs come all together or not at all");
+    }
+    if (bits == 8) gemv_stream_bits<8>(L, xq, sx, mx, M, out, q, src);
+    else if (bits == 6) gemv_stream_bits<6>(L, xq, sx, mx, M, out, q, src);
+    else gemv_stream_bits<4>(L, xq, sx, mx, M, out, q, src);
 }
 
 }  // namespace detb

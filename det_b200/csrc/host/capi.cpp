@@ -47,6 +47,14 @@ int dh_backend_name(void* b, char* out, size_t cap) {
         return std::string();
     });
 }
+// Profiling / measurement switches of a CUDA backend handle (see CudaBackend::skip_mask, fuse_activations).
+void dh_cuda_debug(void* b, unsigned skip_mask, int fuse_activations) {
+    auto* cb = dynamic_cast<det::CudaBackend*>(static_cast<det::Backend*>(b));
+    if (!cb) return;
+    cb->skip_mask = skip_mask;
+    cb->fuse_activations = fuse_activations != 0;
+    if (fuse_activations > 1) cb->fuse_kinds = (unsigned)fuse_activations;   // a mask of DET_ACT_* bits
+}
 // The primitive test hook of the CUDA backend (cuda.rs:474-490).
 void dh_cuda_test_prim(int op, const float* x, size_t len, size_t m, size_t n, float* out, size_t out_len) {
     static det::CudaBackend* hook = new det::CudaBackend();

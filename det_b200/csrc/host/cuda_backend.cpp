@@ -33,14 +33,50 @@ void* CudaBackend::alloc_bytes(size_t bytes) {
     }
     return p;
 }
-void CudaBackend::free_bytes(void* p) { det_free(p); }
-void CudaBackend::write_bytes(void* dst, const void* src, size_t bytes) { det_memcpy(dst, src, bytes, ST); }
+void CudaBackend::free_bytes(void* p) {
+    flush_pending();
+    det_free(p);
+}
+void CudaBackend::write_bytes(void* dst, const void* src, size_t bytes) {
+    flush_pending();
+    det_memcpy(dst, src, bytes, ST);
+}
 void CudaBackend::read_bytes(const void* src, void* dst, size_t bytes) {
+    flush_pending();
     det_memcpy(dst, src, bytes, ST);
     det_sync();
 }
-void CudaBackend::zero_bytes(void* p, size_t bytes) { det_memset(p, 0, bytes, ST); }
-void CudaBackend::sync() { det_sync(); }
+void CudaBackend::zero_bytes(void* p, size_t bytes) {
+    flush_pending();
+    det_memset(p, 0, bytes, ST);
+}
+void CudaBackend::sync() {
+    flush_pending();
+    det_sync();
+}
+
+// Holds an activation quantization back so that the next gemm() can absorb it.  Returns false when it does not qualify.
+bool CudaBackend::hold(int kind, const float* a, const float* b, float eps, size_t m, size_t n, int8_t* xq, float* sx,
+                       uint16_t* mx) {
+    flush_pending();
+    if (!fuse_activations || !(fuse_kinds & (1u << kind)) || !stream_layout || m > (size_t)stream_max_m || n % 128 != 0 || n > 18432 || !mx) return false;
+    pending_.kind = kind;
+    pending_.a = a; pending_.b = b; pending_.eps = eps;
+    pending_.m = m; pending_.n = n;
+    pending_.xq = xq; pending_.sx = sx; pending_.mx = mx;
+    return true;
+}
+void CudaBackend::flush_pending() {
+    if (!pending_.kind) return;
+    const PendingAct p = pending_;
+    pending_.kind = 0;
+    if (p.kind == DET_ACT_RMSNORM)
+        det_rmsnorm_quant(p.a, p.b, p.eps, (int)p.m, (int)p.n, nullptr, p.xq, p.sx, p.mx, ST);
+    else if (p.kind == DET_ACT_PLAIN)
+        det_quant(p.a, (int)p.m, (int)p.n, p.xq, p.sx, p.mx, ST);
+    else
+        det_silu_mul_quant(p.a, p.b, (int)p.m, (int)p.n, nullptr, p.xq, p.sx, p.mx, ST);
+}
 
 void* CudaBackend::scratch(Buf<uint8_t>& slot, size_t bytes) {   // cuda.rs:81-87
     if (slot.len() < bytes) slot = alloc<uint8_t>(bytes < 256 ? 256 : bytes);
@@ -116,10 +152,14 @@ std::unique_ptr<Linear> CudaBackend::linear_synth(uint64_t seed, const std::vect
 
 void CudaBackend::rmsnorm_quant(const Buf<float>& x, const Buf<float>& w, float eps, size_t m, size_t n,
                                 const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx) {
+    if (skip_mask & 1) return;
+    if (hold(DET_ACT_RMSNORM, x.ptr(), w.ptr(), eps, m, n, xq.ptr(), sx.ptr(), mx.ptr())) return;
     det_rmsnorm_quant(x.ptr(), w.ptr(), eps, (int)m, (int)n, nullptr, xq.ptr(), sx.ptr(), mx.ptr(), ST);
 }
 void CudaBackend::quant(const Buf<float>& x, size_t m, size_t n, const Buf<int8_t>& xq, const Buf<float>& sx,
                         const Buf<uint16_t>& mx) {
+    if (skip_mask & 2) return;
+    if (hold(DET_ACT_PLAIN, x.ptr(), nullptr, 0.0f, m, n, xq.ptr(), sx.ptr(), mx.ptr())) return;
     det_quant(x.ptr(), (int)m, (int)n, xq.ptr(), sx.ptr(), mx.ptr(), ST);
 }
 
@@ -127,6 +167,10 @@ void CudaBackend::quant(const Buf<float>& x, size_t m, size_t n, const Buf<int8_
 void CudaBackend::gemm(const Linear& lin_, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx,
                        size_t m, const GemmOut& out) {
     const CudaLinear& lin = static_cast<const CudaLinear&>(lin_);
+    if (skip_mask & 8) {
+        pending_.kind = 0;
+        return;
+    }
     det_qlinear q;
     const bool use_stream = lin.stream.ptr() && (m <= (size_t)stream_max_m || !lin.wq.ptr());
     q.wq = use_stream ? lin.stream.ptr() : lin.wq.ptr();
@@ -135,12 +179,34 @@ void CudaBackend::gemm(const Linear& lin_, const Buf<int8_t>& xq, const Buf<floa
     q.N = (int)lin.n();
     q.K = (int)lin.k;
     q.bits = use_stream ? (lin.bits | DET_LAYOUT_STREAM) : lin.bits;
+    // absorb a held activation quantization when this GEMM is its consumer and nothing it writes feeds the producer
+    det_act_source src{};
+    const det_act_source* fused = nullptr;
+    if (pending_.kind) {
+        bool ok = use_stream && pending_.xq == xq.ptr() && pending_.sx == sx.ptr() && pending_.mx == mx.ptr() &&
+                  pending_.m == m && pending_.n == lin.k;
+        for (const Buf<float>* d : out.dst)
+            if (d->ptr() == pending_.a || d->ptr() == pending_.b) ok = false;
+        if (ok) {
+            src.kind = pending_.kind;
+            src.a = pending_.a; src.b = pending_.b; src.eps = pending_.eps;
+            src.xq = pending_.xq; src.sx = pending_.sx; src.mx = pending_.mx;
+            fused = &src;
+            pending_.kind = 0;
+        } else {
+            flush_pending();
+        }
+    }
+    auto run = [&](float* y, int accumulate, int nparts, const int* offs, float* const* dsts) {
+        if (fused) det_gemm_fused(&q, fused, (int)m, y, accumulate, nparts, offs, dsts, ST);
+        else det_gemm_ex(&q, xq.ptr(), sx.ptr(), mx.ptr(), (int)m, y, accumulate, nparts, offs, dsts, ST);
+    };
     switch (out.kind) {
         case GemmOut::Write:
-            det_gemm_ex(&q, xq.ptr(), sx.ptr(), mx.ptr(), (int)m, out.dst[0]->ptr(), 0, 0, nullptr, nullptr, ST);
+            run(out.dst[0]->ptr(), 0, 0, nullptr, nullptr);
             break;
         case GemmOut::Accumulate:
-            det_gemm_ex(&q, xq.ptr(), sx.ptr(), mx.ptr(), (int)m, out.dst[0]->ptr(), 1, 0, nullptr, nullptr, ST);
+            run(out.dst[0]->ptr(), 1, 0, nullptr, nullptr);
             break;
         case GemmOut::Parts: {
             if (out.dst.size() != lin.widths.size()) throw std::logic_error("gemm: part count mismatch");
@@ -152,8 +218,7 @@ void CudaBackend::gemm(const Linear& lin_, const Buf<int8_t>& xq, const Buf<floa
                 acc += (int)lin.widths[i];
                 ptrs.push_back(out.dst[i]->ptr());
             }
-            det_gemm_ex(&q, xq.ptr(), sx.ptr(), mx.ptr(), (int)m, nullptr, 0, (int)offs.size(), offs.data(),
-                        ptrs.data(), ST);
+            run(nullptr, 0, (int)offs.size(), offs.data(), ptrs.data());
             break;
         }
     }
@@ -161,12 +226,16 @@ void CudaBackend::gemm(const Linear& lin_, const Buf<int8_t>& xq, const Buf<floa
 
 void CudaBackend::silu_mul_quant(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<int8_t>& hq,
                                  const Buf<float>& sh, const Buf<uint16_t>& mh) {
+    if (skip_mask & 4) return;
+    if (hold(DET_ACT_SWIGLU, g.ptr(), u.ptr(), 0.0f, m, n, hq.ptr(), sh.ptr(), mh.ptr())) return;
     det_silu_mul_quant(g.ptr(), u.ptr(), (int)m, (int)n, nullptr, hq.ptr(), sh.ptr(), mh.ptr(), ST);
 }
 
 // cuda.rs:316-364
 void CudaBackend::attention(const AttnLayer& l, const KvCache& kv, const Shape& s, const Buf<float>& qg,
                             const Buf<float>& k, const Buf<float>& v, const Buf<float>& o) {
+    if (skip_mask & 16) return;
+    flush_pending();
     det_attn_layer layer{l.q_norm->ptr(), l.k_norm->ptr(), l.v_scale->ptr(), l.v_inv_scale->ptr()};
     det_kv_cache cache{kv.kq.ptr(), kv.sk.ptr(), kv.vq.ptr(), (int)kv.capacity, nullptr, nullptr};
     void* sc = scratch(attn_scratch_, det_attn_scratch_bytes((int)s.m, (int)s.n_h, (int)s.hd));
@@ -182,6 +251,8 @@ void CudaBackend::attention(const AttnLayer& l, const KvCache& kv, const Shape& 
 void CudaBackend::gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, const Buf<float>& qkv,
                       const Buf<float>& z, const Buf<float>& a, const Buf<float>& b, const Buf<float>& on,
                       const GdnExport& ex) {
+    if (skip_mask & 32) return;
+    flush_pending();
     det_gdn_layer layer{l.conv->ptr(), l.a->ptr(), l.dt_bias->ptr(), l.norm->ptr()};
     det_gdn_state state{st.conv_state.ptr(), st.s.ptr()};
     void* sc = scratch(gdn_scratch_, det_gdn_scratch_bytes((int)s.m, (int)s.n_k, (int)s.n_v, (int)s.dk, (int)s.dv));
@@ -192,11 +263,13 @@ void CudaBackend::gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, 
 
 // cuda.rs:425-471
 int32_t CudaBackend::argmax(const Buf<float>& logits, size_t v) {
+    flush_pending();
     det_argmax(logits.ptr(), 1, (int)v, pick_.ptr(), ST);
     return download(pick_)[0];
 }
 int32_t CudaBackend::sample(const Buf<float>& logits, size_t v, float inv_temp, size_t top_k, float top_p,
                             uint64_t z) {
+    flush_pending();
     write(z_, 0, &z, 1);
     const unsigned long long* zp = reinterpret_cast<const unsigned long long*>(z_.ptr());
     if (top_k == 0 && top_p >= 1.0f) {

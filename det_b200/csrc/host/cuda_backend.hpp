@@ -50,12 +50,38 @@ class CudaBackend : public Backend {
     bool keep_rowmajor = true;    // keep the reference layout too (needed by the large-M GEMM)
     int stream_max_m = 8;         // batches up to this many tokens go through the streaming GEMV
 
+    // Fuse the activation quantization (rmsnorm_quant / quant / silu_mul_quant) into the prologue of the GEMM that
+    // consumes it when that GEMM is a decode-sized streaming GEMV (det_gemm_fused).  The quantization call is held
+    // back until the next op: a matching gemm() absorbs it, anything else runs it on its own first.  Results are
+    // bit-identical either way.  Off by default: measured on the 27B decode step the redundant per-CTA prologue costs
+    // more than the separate cluster kernels it removes (+0.3 to +0.9 ms per token depending on the kind).
+    bool fuse_activations = false;
+    unsigned fuse_kinds = 0xE;   // bit DET_ACT_* set: that kind may be fused
+
+    // Profiling aid: op families in this mask are not launched at all (results are then meaningless); the time a
+    // decode step loses without a family is that family's cost.  1 rmsnorm_quant, 2 quant, 4 silu_mul_quant, 8 gemm,
+    // 16 attention, 32 gdn.
+    unsigned skip_mask = 0;
+
     // Device-position mode (graph replay): when set, attention() reads pos0 from this device word
     // (det_attention_dev) and sizes its launch for positions up to max_pos.
     const int* pos_dev = nullptr;
     int max_pos = 0;
 
   private:
+    struct PendingAct {
+        int kind = 0;   // 0 none, else DET_ACT_*
+        const float* a = nullptr;
+        const float* b = nullptr;
+        float eps = 0.0f;
+        size_t m = 0, n = 0;
+        int8_t* xq = nullptr;
+        float* sx = nullptr;
+        uint16_t* mx = nullptr;
+    } pending_;
+    bool hold(int kind, const float* a, const float* b, float eps, size_t m, size_t n, int8_t* xq, float* sx,
+              uint16_t* mx);
+    void flush_pending();
     void* scratch(Buf<uint8_t>& slot, size_t bytes);
     void finish_linear(CudaLinear& l);
     Buf<uint8_t> attn_scratch_, gdn_scratch_, sample_scratch_, synth_scratch_;

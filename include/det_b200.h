@@ -155,6 +155,28 @@ void det_test_prim(int op, const float* x, int M, int n, float* out, cudaStream_
 size_t det_linear_repack_bytes(int N, int K, int bits);
 void det_linear_repack(const det_qlinear* src, void* dst, cudaStream_t st);
 
+/* GEMM with the activation quantization fused into its prologue (decode: M <= 8 per pass, streaming layout,
+ * K <= 18432).  The reference runs these as separate kernels (det_rmsnorm_quant / det_quant / det_silu_mul_quant, then
+ * det_gemm_ex; crates/det/src/qwen35.rs:33-36,121-129,133-143); here every CTA of the GEMV rebuilds the quantized row
+ * from the fp32 inputs while its weight ring fills — the same fp32 operation sequence, so y and the optional xq / sx / mx
+ * outputs (stored by one CTA, for other consumers of the same row) equal the unfused results bit for bit.
+ *   kind DET_ACT_RMSNORM: a = x[M][K], b = norm weight [K], eps;   DET_ACT_PLAIN: a = x[M][K];
+ *   kind DET_ACT_SWIGLU:  a = gate[M][K], b = up[M][K]   (row = silu_f(gate) * up)                                    */
+#define DET_ACT_RMSNORM 1
+#define DET_ACT_PLAIN 2
+#define DET_ACT_SWIGLU 3
+typedef struct {
+    int kind;
+    const float* a;
+    const float* b;
+    float eps;
+    int8_t* xq;       /* optional outputs: all three or none */
+    float* sx;
+    uint16_t* mx;
+} det_act_source;
+void det_gemm_fused(const det_qlinear* L, const det_act_source* src, int M, float* y, int accumulate, int nparts,
+                    const int* offs, float* const* dsts, cudaStream_t st);
+
 /* Seeded synthetic weights generated in device memory (the benchmarks' stand-in for a converted checkpoint; the host
  * twin is det_b200/csrc/host/synth.cpp and follows crates/det/src/quantize.rs:33-85).  det_synth_linear fills rows
  * [row0, row0 + n) of a reference-layout linear (wq, c, m as in det_qlinear) from tensor `tid` of model `seed`;
