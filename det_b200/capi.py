@@ -46,6 +46,7 @@ class ActSource(C.Structure):
 
 
 DET_LAYOUT_STREAM = 0x100
+DET_LAYOUT_INT8 = 0x200
 DET_ACT_RMSNORM, DET_ACT_PLAIN, DET_ACT_SWIGLU = 1, 2, 3
 
 # every symbol include/det_b200.h declares: name -> (restype, argtypes)
@@ -90,6 +91,8 @@ CUDA_ABI = {
     "det_test_prim": (None, [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "det_linear_repack_bytes": (c_size_t, [c_int, c_int, c_int]),
     "det_linear_repack": (None, [C.POINTER(QLinear), c_void_p, c_void_p]),
+    "det_linear_expand_bytes": (c_size_t, [c_int, c_int]),
+    "det_linear_expand": (None, [C.POINTER(QLinear), c_void_p, c_void_p]),
     "det_synth_linear": (None, [c_u64, c_u64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "det_synth_bf16": (None, [c_u64, c_u64, C.c_longlong, c_void_p, c_void_p]),
     "det_graph_begin": (None, []),

@@ -144,6 +144,8 @@ static void gemm_entry(const det_qlinear* L, const int8_t* xq, const float* sx, 
     if (src) {
         DETB_REQUIRE(stream, "det_gemm_fused needs the streaming weight layout");
         gemv_stream_launch(L, bits, nullptr, nullptr, nullptr, M, out, q, src);
+    } else if (L->bits & DET_LAYOUT_INT8) {
+        gemm_tc_launch(L, xq, sx, mx, M, out, q);
     } else if (stream) {
         gemv_stream_launch(L, bits, xq, sx, mx, M, out, q);
     } else {

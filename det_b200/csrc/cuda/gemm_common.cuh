@@ -98,4 +98,8 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
 void gemv_stream_launch(const det_qlinear* L, int bits, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
                         const OutSpec& out, cudaStream_t q, const det_act_source* src = nullptr);
 
+// Entry of the tensor-core GEMM (gemm_tc.cu): L->wq is the int8-expanded layout.
+void gemm_tc_launch(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
+                    const OutSpec& out, cudaStream_t q);
+
 }  // namespace detb

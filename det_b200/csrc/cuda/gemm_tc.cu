@@ -1,0 +1,306 @@
+// Prefill integer GEMM on the 5th-generation tensor cores: tcgen05.mma kind::i8 (s8 x s8 -> s32) with TMA-fed operands
+// and TMEM accumulators.  Replaces the reference's mma.sync kernels (kernels/cuda/gemm.cu:496-895) for M > 8.
+//
+//   acc[t][n] = sum_g (m[n][g] * mx[t][g]) * sum_{k in g} wq[n][k] * xq[t][k]        (docs/SPEC.md §3)
+//
+// The inner sum of one 128-wide group is four UMMA steps (K = 32 bytes each) into a TMEM tile; the group multiplier
+// m * mx is a 32-bit integer that differs per (row, token, group), so every group's s32 tile is drained from TMEM and
+// folded into int64 registers by the epilogue warps while the tensor core already works on the next group in the
+// second TMEM buffer.  CTA tile: 128 weight rows (UMMA M, one TMEM lane per row) x 64 tokens (UMMA N).
+//
+// Warp roles (192 threads): warp 0 = TMA producer (one thread), warp 1 = TMEM allocation + MMA issue (one thread),
+// warps 2-5 = epilogue (warp w owns TMEM lanes 32*(w%4) .. +31).  Operands come from an int8-expanded row-major copy
+// of the weights (det_linear_expand) and from the int8 activations, both through 128-byte-swizzled TMA boxes, which is
+// the canonical K-major SWIZZLE_128B layout the UMMA shared-memory descriptor names.  No multicast anywhere.
+#include "gemm_common.cuh"
+#include <cuda.h>
+
+namespace detb {
+
+constexpr int TC_ROWS = 128;      // weight rows per CTA (UMMA M)
+constexpr int TC_TOK = 64;        // tokens per CTA (UMMA N)
+constexpr int TC_KB = 128;        // bytes of K per stage = one quantization group
+constexpr int TC_STAGES = 6;
+constexpr int TC_A_BYTES = TC_ROWS * TC_KB;   // 16 KB
+constexpr int TC_B_BYTES = TC_TOK * TC_KB;    // 8 KB
+constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+constexpr int TC_THREADS = 192;
+constexpr int TC_TMEM_COLS = 128;             // two accumulator buffers of 64 columns
+
+// UMMA instruction descriptor (kind::i8): D = s32, A = B = signed 8-bit, both K-major, N = 64, M = 128.
+constexpr unsigned TC_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((TC_TOK >> 3) << 17) | ((TC_ROWS >> 4) << 24);
+
+// Shared-memory matrix descriptor, K-major, SWIZZLE_128B: 8-row groups 1024 bytes apart, descriptor version 1.
+__device__ __forceinline__ unsigned long long umma_desc(const void* smem) {
+    const unsigned addr = smem_addr(smem);
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);          // start address
+    d |= (unsigned long long)1 << 16;                           // leading byte offset (unused with swizzle)
+    d |= (unsigned long long)(1024 >> 4) << 32;                 // stride byte offset
+    d |= (unsigned long long)1 << 46;                           // version
+    d |= (unsigned long long)2 << 61;                           // SWIZZLE_128B
+    return d;
+}
+__device__ __forceinline__ void umma_i8(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(TC_IDESC), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld64(unsigned taddr, int (&r)[64]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+        "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+        "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]),
+          "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]),
+          "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
+          "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]),
+          "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr)
+        : "memory");
+}
+
+struct TcArgs {
+    int N, K, G, M;
+    const float* c;
+    const uint16_t* m;
+    const float* sx;
+    const uint16_t* mx;   // may be NULL
+    int* error_flag;
+    OutSpec out;
+};
+
+// Shared memory: [stages x (A 16 KB | B 8 KB)] (1024-byte aligned) [mx table: G x 64 u16] [barriers] [tmem address]
+__global__ void __launch_bounds__(TC_THREADS, 1)
+k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* stages = smem;
+    uint16_t* mxs = reinterpret_cast<uint16_t*>(stages + TC_STAGES * TC_STAGE_BYTES);
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(
+        (reinterpret_cast<uintptr_t>(mxs + (size_t)a.G * TC_TOK) + 15) & ~(uintptr_t)15);
+    unsigned long long* full = bars;                       // [TC_STAGES]  TMA bytes landed
+    unsigned long long* empty = bars + TC_STAGES;          // [TC_STAGES]  MMAs that read the stage are done
+    unsigned long long* tfull = bars + 2 * TC_STAGES;      // [2]          group result complete in TMEM buffer
+    unsigned long long* tempty = tfull + 2;                // [2]          epilogue drained the buffer
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(tempty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * TC_TOK, n0 = blockIdx.y * TC_ROWS;
+    const int G = a.G;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tfull[b], 1);
+            mbar_init(&tempty[b], 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)),
+                     "r"(TC_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---------------- TMA producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int g = 0; g < G; g++, issued++) {
+                const int s = g % TC_STAGES;
+                ok = mbar_wait(&empty[s], ((unsigned)(g / TC_STAGES) & 1u) ^ 1u);
+                if (!ok) break;
+                uint8_t* st = stages + (size_t)s * TC_STAGE_BYTES;
+                mbar_expect_tx(&full[s], TC_STAGE_BYTES);
+                tma_load_2d(st, &map_w, g * TC_KB, n0, &full[s]);
+                tma_load_2d(st + TC_A_BYTES, &map_x, g * TC_KB, t0, &full[s]);
+            }
+            if (!ok) {
+                atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
+                for (int k = 0; k < TC_STAGES && k < issued; k++) {
+                    const int i = issued - 1 - k;
+                    (void)mbar_wait(&full[i % TC_STAGES], (unsigned)(i / TC_STAGES) & 1u);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue: four K = 32 steps per group into TMEM buffer g & 1
+        if (lane == 0) {
+            for (int g = 0; g < G; g++) {
+                const int s = g % TC_STAGES, b = g & 1;
+                ok = mbar_wait(&full[s], (unsigned)(g / TC_STAGES) & 1u) &&
+                     mbar_wait(&tempty[b], ((unsigned)(g >> 1) & 1u) ^ 1u);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint8_t* st = stages + (size_t)s * TC_STAGE_BYTES;
+                const unsigned long long da = umma_desc(st), db = umma_desc(st + TC_A_BYTES);
+#pragma unroll
+                for (int k = 0; k < 4; k++) umma_i8(tmem_base + b * TC_TOK, da + 2 * k, db + 2 * k, k > 0 ? 1u : 0u);
+                umma_commit(&empty[s]);
+                umma_commit(&tfull[b]);
+            }
+            if (!ok) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
+        }
+    } else {
+        // ---------------- epilogue: thread = one weight row, 64 tokens in registers as int64
+        const int q = warp & 3;                        // TMEM lane quarter this warp may read
+        const int n = n0 + q * 32 + lane;
+        const int et = threadIdx.x - 64;               // 0..127
+        for (int i = et; i < G * TC_TOK; i += 128) {
+            const int g = i / TC_TOK, t = i - g * TC_TOK;
+            mxs[i] = (a.mx && t0 + t < a.M) ? a.mx[(size_t)(t0 + t) * G + g] : (uint16_t)1;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        long long acc[TC_TOK];
+#pragma unroll
+        for (int t = 0; t < TC_TOK; t++) acc[t] = 0;
+        const uint16_t* mrow = a.m + (size_t)(n < a.N ? n : 0) * G;
+        for (int g = 0; g < G; g++) {
+            const int b = g & 1;
+            ok = mbar_wait(&tfull[b], (unsigned)(g >> 1) & 1u);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            int r[TC_TOK];
+            tmem_ld64(tmem_base + ((unsigned)(q * 32) << 16) + b * TC_TOK, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[b]);
+            const unsigned mw = mrow[g];
+            const uint16_t* mxg = mxs + g * TC_TOK;
+#pragma unroll
+            for (int t = 0; t < TC_TOK; t++) acc[t] += (long long)r[t] * (long long)(mw * (unsigned)mxg[t]);
+        }
+        if (!ok && lane == 0) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
+        if (ok && n < a.N) {
+            const float cn = a.c[n];
+#pragma unroll
+            for (int t = 0; t < TC_TOK; t++)
+                if (t0 + t < a.M) emit(a.out, t0 + t, n, fmul(fmul(i64_to_f32(acc[t]), cn), a.sx[t0 + t]));
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS)
+                     : "memory");
+}
+
+// One thread per 32-code block: reference layout -> signed int8 codes, row-major [N][K].
+__global__ void k_expand_int8(const uint8_t* __restrict__ wq, int bits, long long nblocks, int8_t* __restrict__ dst) {
+    const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= nblocks) return;
+    const uint8_t* blk = wq + (size_t)id * bytes_per_32(bits);
+    __align__(16) int8_t out[32];
+    for (int i = 0; i < 32; i++) {
+        int v;
+        if (bits == 8) v = (int8_t)blk[i];
+        else {
+            v = (i < 16) ? (blk[i] & 0xF) : (blk[i - 16] >> 4);
+            if (bits == 6) v |= ((blk[16 + (i & 7)] >> (2 * (i >> 3))) & 3) << 4;
+            v -= code_offset(bits);
+        }
+        out[i] = (int8_t)v;
+    }
+    uint4* d4 = reinterpret_cast<uint4*>(dst + (size_t)id * 32);
+    d4[0] = reinterpret_cast<const uint4*>(out)[0];
+    d4[1] = reinterpret_cast<const uint4*>(out)[1];
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        DETB_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr));
+        DETB_REQUIRE(p != nullptr && qr == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available");
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+// A [rows][K] int8 matrix as a 2-D tensor map with a (128 bytes x box_rows) box, 128-byte swizzle, zero fill.
+static CUtensorMap make_map(const void* base, int rows, int K, int box_rows) {
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_KB, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    DETB_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed");
+    return map;
+}
+
+void gemm_tc_launch(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
+                    const OutSpec& out, cudaStream_t q) {
+    const int N = L->N, K = L->K, G = K / 128;
+    DETB_REQUIRE((reinterpret_cast<uintptr_t>(L->wq) & 15) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15) == 0,
+                 "tensor-core GEMM operands must be 16-byte aligned");
+    const CUtensorMap map_w = make_map(L->wq, N, K, TC_ROWS);
+    const CUtensorMap map_x = make_map(xq, M, K, TC_TOK);
+    TcArgs a;
+    a.N = N; a.K = K; a.G = G; a.M = M;
+    a.c = L->c; a.m = L->m; a.sx = sx; a.mx = mx;
+    a.error_flag = error_word();
+    a.out = out;
+    const size_t smem = 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES + (size_t)G * TC_TOK * 2 + 16 + (2 * TC_STAGES + 4) * 8 + 16;
+    static bool configured = false;
+    if (!configured) {
+        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin()));
+        configured = true;
+    }
+    DETB_REQUIRE(smem <= smem_optin(), "K is too large for the tensor-core GEMM's multiplier table");
+    const dim3 grid((M + TC_TOK - 1) / TC_TOK, (N + TC_ROWS - 1) / TC_ROWS);
+    k_gemm_tc<<<grid, TC_THREADS, smem, q>>>(map_w, map_x, a);
+    DETB_CUDA_OK(cudaGetLastError());
+}
+
+}  // namespace detb
+
+using namespace detb;
+
+extern "C" {
+
+size_t det_linear_expand_bytes(int N, int K) { return (size_t)N * (size_t)K; }
+
+void det_linear_expand(const det_qlinear* src, void* dst, cudaStream_t st) {
+    DETB_REQUIRE((src->bits == 4 || src->bits == 6 || src->bits == 8) && src->K % 128 == 0, "bad linear shape");
+    const long long nblocks = (long long)src->N * (src->K / 32);
+    k_expand_int8<<<(unsigned)((nblocks + 255) / 256), 256, 0, queue_of(st)>>>(src->wq, src->bits, nblocks,
+                                                                              static_cast<int8_t*>(dst));
+    DETB_CUDA_OK(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -84,8 +84,12 @@ void* CudaBackend::scratch(Buf<uint8_t>& slot, size_t bytes) {   // cuda.rs:81-8
 }
 
 void CudaBackend::finish_linear(CudaLinear& l) {
-    if (!stream_layout) return;
     det_qlinear src{l.wq.ptr(), l.c.ptr(), l.m.ptr(), (int)l.n(), (int)l.k, l.bits};
+    if (int8_layout) {
+        l.wq8 = alloc<uint8_t>(det_linear_expand_bytes((int)l.n(), (int)l.k));
+        det_linear_expand(&src, l.wq8.ptr(), ST);
+    }
+    if (!stream_layout) return;
     l.stream = alloc<uint8_t>(det_linear_repack_bytes((int)l.n(), (int)l.k, l.bits));
     det_linear_repack(&src, l.stream.ptr(), ST);
     if (!keep_rowmajor) {
@@ -179,6 +183,10 @@ void CudaBackend::gemm(const Linear& lin_, const Buf<int8_t>& xq, const Buf<floa
     q.N = (int)lin.n();
     q.K = (int)lin.k;
     q.bits = use_stream ? (lin.bits | DET_LAYOUT_STREAM) : lin.bits;
+    if (!use_stream && lin.wq8.ptr()) {
+        q.wq = lin.wq8.ptr();
+        q.bits = lin.bits | DET_LAYOUT_INT8;
+    }
     // absorb a held activation quantization when this GEMM is its consumer and nothing it writes feeds the producer
     det_act_source src{};
     const det_act_source* fused = nullptr;

@@ -11,6 +11,7 @@ struct CudaLinear : Linear {
     Buf<float> c;          // [N]
     Buf<uint16_t> m;       // [N][K/128]
     Buf<uint8_t> stream;   // det_linear_repack layout
+    Buf<uint8_t> wq8;      // det_linear_expand layout (signed int8 codes) for the tensor-core GEMM
 };
 
 class CudaBackend : public Backend {
@@ -49,6 +50,7 @@ class CudaBackend : public Backend {
     bool stream_layout = true;    // build the streaming copy for the decode GEMV
     bool keep_rowmajor = true;    // keep the reference layout too (needed by the large-M GEMM)
     int stream_max_m = 8;         // batches up to this many tokens go through the streaming GEMV
+    bool int8_layout = true;      // build the int8-expanded copy; larger batches then run on the tensor cores
 
     // Fuse the activation quantization (rmsnorm_quant / quant / silu_mul_quant) into the prologue of the GEMM that
     // consumes it when that GEMM is a decode-sized streaming GEMV (det_gemm_fused).  The quantization call is held

@@ -155,6 +155,13 @@ void det_test_prim(int op, const float* x, int M, int n, float* out, cudaStream_
 size_t det_linear_repack_bytes(int N, int K, int bits);
 void det_linear_repack(const det_qlinear* src, void* dst, cudaStream_t st);
 
+/* Tensor-core layout for prefill (M > 8): signed int8 codes, row-major [N][K] (det_linear_expand_bytes(N, K) bytes),
+ * tagged bits | DET_LAYOUT_INT8 in det_qlinear.  det_gemm_ex then runs the tcgen05 kind::i8 kernel.  Like the repack
+ * above this belongs in Backend::linear (crates/det/src/cuda.rs:139-163).                                            */
+#define DET_LAYOUT_INT8 0x200
+size_t det_linear_expand_bytes(int N, int K);
+void det_linear_expand(const det_qlinear* src, void* dst, cudaStream_t st);
+
 /* GEMM with the activation quantization fused into its prologue (decode: M <= 8 per pass, streaming layout,
  * K <= 18432).  The reference runs these as separate kernels (det_rmsnorm_quant / det_quant / det_silu_mul_quant, then
  * det_gemm_ex; crates/det/src/qwen35.rs:33-36,121-129,133-143); here every CTA of the GEMV rebuilds the quantized row
