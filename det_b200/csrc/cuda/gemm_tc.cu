@@ -8,8 +8,8 @@
 // folded into int64 registers by the epilogue warps while the tensor core already works on the next group in the
 // second TMEM buffer.  CTA tile: 128 weight rows (UMMA M, one TMEM lane per row) x 64 tokens (UMMA N).
 //
-// Warp roles (192 threads): warp 0 = TMA producer (one thread), warp 1 = TMEM allocation + MMA issue (one thread),
-// warps 2-5 = epilogue (warp w owns TMEM lanes 32*(w%4) .. +31).  Operands come from an int8-expanded row-major copy
+// Warp roles (320 threads): warp 0 = TMA producer (one thread), warp 1 = TMEM allocation + MMA issue (one thread),
+// warps 2-9 = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31, half of the 64 token columns each).  Operands come from an int8-expanded row-major copy
 // of the weights (det_linear_expand) and from the int8 activations, both through 128-byte-swizzled TMA boxes, which is
 // the canonical K-major SWIZZLE_128B layout the UMMA shared-memory descriptor names.  No multicast anywhere.
 #include "gemm_common.cuh"
@@ -18,17 +18,21 @@
 namespace detb {
 
 constexpr int TC_ROWS = 128;      // weight rows per CTA (UMMA M)
-constexpr int TC_TOK = 64;        // tokens per CTA (UMMA N)
 constexpr int TC_KB = 128;        // bytes of K per stage = one quantization group
-constexpr int TC_STAGES = 6;
 constexpr int TC_A_BYTES = TC_ROWS * TC_KB;   // 16 KB
-constexpr int TC_B_BYTES = TC_TOK * TC_KB;    // 8 KB
-constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
-constexpr int TC_THREADS = 192;
-constexpr int TC_TMEM_COLS = 128;             // two accumulator buffers of 64 columns
-
-// UMMA instruction descriptor (kind::i8): D = s32, A = B = signed 8-bit, both K-major, N = 64, M = 128.
-constexpr unsigned TC_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((TC_TOK >> 3) << 17) | ((TC_ROWS >> 4) << 24);
+// Per token-tile width TOK (UMMA N, 64 or 128): TOK / 32 epilogue warps per TMEM lane quarter, 32 token columns each;
+// two TMEM accumulator buffers of TOK columns; as many stages as fit next to the multiplier table.
+template <int TOK>
+struct TcCfg {
+    static constexpr int B_BYTES = TOK * TC_KB;
+    static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
+    static constexpr int STAGES = TOK == 64 ? 6 : 5;
+    static constexpr int EPI_WARPS = 4 * (TOK / 32);
+    static constexpr int THREADS = (2 + EPI_WARPS) * 32;
+    static constexpr int TMEM_COLS = 2 * TOK;
+    // UMMA instruction descriptor (kind::i8): D = s32, A = B = signed 8-bit, both K-major, N = TOK, M = 128.
+    static constexpr unsigned IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TOK >> 3) << 17) | ((TC_ROWS >> 4) << 24);
+};
 
 // Shared-memory matrix descriptor, K-major, SWIZZLE_128B: 8-row groups 1024 bytes apart, descriptor version 1.
 __device__ __forceinline__ unsigned long long umma_desc(const void* smem) {
@@ -41,12 +45,13 @@ __device__ __forceinline__ unsigned long long umma_desc(const void* smem) {
     d |= (unsigned long long)2 << 61;                           // SWIZZLE_128B
     return d;
 }
-__device__ __forceinline__ void umma_i8(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned accumulate) {
+__device__ __forceinline__ void umma_i8(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc,
+                                        unsigned accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(TC_IDESC), "r"(accumulate)
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
@@ -59,23 +64,30 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld64(unsigned taddr, int (&r)[64]) {
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, int (&r)[32]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
-        "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
-        "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]),
-          "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]),
-          "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
-          "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]),
-          "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+// acc += (s32) p * (u32) mult, exactly, in three integer instructions: an unsigned 32x32+64 multiply-add, then the
+// high word loses `mult` when p is negative (p as unsigned is p + 2^32).
+__device__ __forceinline__ void mad_s32_u32(long long& acc, int p, unsigned mult) {
+    asm("{\n\t.reg .u32 lo, hi, corr;\n\t.reg .s32 sg;\n\t"
+        "mad.wide.u32 %0, %1, %2, %0;\n\t"
+        "shr.s32 sg, %1, 31;\n\t"
+        "and.b32 corr, sg, %2;\n\t"
+        "mov.b64 {lo, hi}, %0;\n\t"
+        "sub.u32 hi, hi, corr;\n\t"
+        "mov.b64 %0, {lo, hi};\n\t}"
+        : "+l"(acc)
+        : "r"(p), "r"(mult));
 }
 
 struct TcArgs {
@@ -88,9 +100,12 @@ struct TcArgs {
     OutSpec out;
 };
 
-// Shared memory: [stages x (A 16 KB | B 8 KB)] (1024-byte aligned) [mx table: G x 64 u16] [barriers] [tmem address]
-__global__ void __launch_bounds__(TC_THREADS, 1)
+// Shared memory: [stages x (A 16 KB | B)] (1024-byte aligned) [mx table: G x TOK u16] [barriers] [tmem address]
+template <int TOK>
+__global__ void __launch_bounds__(TcCfg<TOK>::THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
+    constexpr int TC_TOK = TOK, TC_STAGES = TcCfg<TOK>::STAGES, TC_STAGE_BYTES = TcCfg<TOK>::STAGE_BYTES;
+    constexpr int TC_EPI_WARPS = TcCfg<TOK>::EPI_WARPS, TC_TMEM_COLS = TcCfg<TOK>::TMEM_COLS;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* stages = smem;
@@ -114,7 +129,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&tfull[b], 1);
-            mbar_init(&tempty[b], 4);
+            mbar_init(&tempty[b], TC_EPI_WARPS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -163,48 +178,57 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 const uint8_t* st = stages + (size_t)s * TC_STAGE_BYTES;
                 const unsigned long long da = umma_desc(st), db = umma_desc(st + TC_A_BYTES);
 #pragma unroll
-                for (int k = 0; k < 4; k++) umma_i8(tmem_base + b * TC_TOK, da + 2 * k, db + 2 * k, k > 0 ? 1u : 0u);
+                for (int k = 0; k < 4; k++)
+                    umma_i8(tmem_base + b * TC_TOK, da + 2 * k, db + 2 * k, TcCfg<TOK>::IDESC, k > 0 ? 1u : 0u);
                 umma_commit(&empty[s]);
                 umma_commit(&tfull[b]);
             }
             if (!ok) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
         }
     } else {
-        // ---------------- epilogue: thread = one weight row, 64 tokens in registers as int64
+        // ---------------- epilogue: thread = one weight row x 32 tokens, int64 accumulators in registers
+        constexpr int EC = 32;                         // token columns per epilogue warp
         const int q = warp & 3;                        // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;              // which block of 32 token columns
         const int n = n0 + q * 32 + lane;
-        const int et = threadIdx.x - 64;               // 0..127
-        for (int i = et; i < G * TC_TOK; i += 128) {
+        const int et = threadIdx.x - 64;
+        for (int i = et; i < G * TC_TOK; i += TC_EPI_WARPS * 32) {
             const int g = i / TC_TOK, t = i - g * TC_TOK;
             mxs[i] = (a.mx && t0 + t < a.M) ? a.mx[(size_t)(t0 + t) * G + g] : (uint16_t)1;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        long long acc[TC_TOK];
+        asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
+        long long acc[EC];
 #pragma unroll
-        for (int t = 0; t < TC_TOK; t++) acc[t] = 0;
+        for (int t = 0; t < EC; t++) acc[t] = 0;
         const uint16_t* mrow = a.m + (size_t)(n < a.N ? n : 0) * G;
         for (int g = 0; g < G; g++) {
             const int b = g & 1;
             ok = mbar_wait(&tfull[b], (unsigned)(g >> 1) & 1u);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            int r[TC_TOK];
-            tmem_ld64(tmem_base + ((unsigned)(q * 32) << 16) + b * TC_TOK, r);
+            int r[EC];
+            tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + b * TC_TOK + half * EC, r);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&tempty[b]);
             const unsigned mw = mrow[g];
-            const uint16_t* mxg = mxs + g * TC_TOK;
+            const unsigned* mxg = reinterpret_cast<const unsigned*>(mxs + g * TC_TOK + half * EC);
 #pragma unroll
-            for (int t = 0; t < TC_TOK; t++) acc[t] += (long long)r[t] * (long long)(mw * (unsigned)mxg[t]);
+            for (int t = 0; t < EC; t += 2) {
+                const unsigned pair = mxg[t >> 1];     // two u16 multipliers
+                mad_s32_u32(acc[t], r[t], mw * (pair & 0xffffu));
+                mad_s32_u32(acc[t + 1], r[t + 1], mw * (pair >> 16));
+            }
         }
         if (!ok && lane == 0) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
         if (ok && n < a.N) {
             const float cn = a.c[n];
 #pragma unroll
-            for (int t = 0; t < TC_TOK; t++)
-                if (t0 + t < a.M) emit(a.out, t0 + t, n, fmul(fmul(i64_to_f32(acc[t]), cn), a.sx[t0 + t]));
+            for (int t = 0; t < EC; t++) {
+                const int tt = t0 + half * EC + t;
+                if (tt < a.M) emit(a.out, tt, n, fmul(fmul(i64_to_f32(acc[t]), cn), a.sx[tt]));
+            }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -263,8 +287,10 @@ static CUtensorMap make_map(const void* base, int rows, int K, int box_rows) {
     return map;
 }
 
-void gemm_tc_launch(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
-                    const OutSpec& out, cudaStream_t q) {
+template <int TOK>
+static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
+                               const OutSpec& out, cudaStream_t q) {
+    constexpr int TC_TOK = TOK, TC_STAGES = TcCfg<TOK>::STAGES, TC_STAGE_BYTES = TcCfg<TOK>::STAGE_BYTES;
     const int N = L->N, K = L->K, G = K / 128;
     DETB_REQUIRE((reinterpret_cast<uintptr_t>(L->wq) & 15) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15) == 0,
                  "tensor-core GEMM operands must be 16-byte aligned");
@@ -278,13 +304,24 @@ void gemm_tc_launch(const det_qlinear* L, const int8_t* xq, const float* sx, con
     const size_t smem = 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES + (size_t)G * TC_TOK * 2 + 16 + (2 * TC_STAGES + 4) * 8 + 16;
     static bool configured = false;
     if (!configured) {
-        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin()));
+        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemm_tc<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin()));
         configured = true;
     }
     DETB_REQUIRE(smem <= smem_optin(), "K is too large for the tensor-core GEMM's multiplier table");
     const dim3 grid((M + TC_TOK - 1) / TC_TOK, (N + TC_ROWS - 1) / TC_ROWS);
-    k_gemm_tc<<<grid, TC_THREADS, smem, q>>>(map_w, map_x, a);
+    k_gemm_tc<TOK><<<grid, TcCfg<TOK>::THREADS, smem, q>>>(map_w, map_x, a);
     DETB_CUDA_OK(cudaGetLastError());
+}
+
+// Token-tile width.  Measured on B200 (K=5120 x N=17408, M=512): the 64-token tile reaches 385 TOPS, the 128-token
+// tile 315 TOPS (with the epilogue arithmetic removed: 520 vs 860 TOPS, i.e. the 128-wide tile is better fed from L2
+// but its sixteen epilogue warps are bound by the per-group 64-bit multiply-adds).  The 64-token tile is used for every M
+// until the epilogue is cheaper; the wider instantiation stays compiled for that work.
+void gemm_tc_launch(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
+                    const OutSpec& out, cudaStream_t q) {
+    constexpr bool wide_tiles = false;
+    if (M <= 64 || !wide_tiles) gemm_tc_launch_tok<64>(L, xq, sx, mx, M, out, q);
+    else gemm_tc_launch_tok<128>(L, xq, sx, mx, M, out, q);
 }
 
 }  // namespace detb

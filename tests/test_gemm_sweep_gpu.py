@@ -24,7 +24,7 @@ def _det_rows(rng, n, k, bits):
 
 
 @pytest.mark.parametrize("n,k,bits,ms", [
-    (17408, 5120, 6, [1, 4, 8, 16]),
+    (17408, 5120, 6, [1, 4, 8, 16, 70]),
     (17408, 5120, 8, [1, 3]),
     (17408, 5120, 4, [1, 5]),
     (5120, 17408, 6, [1, 2]),
@@ -44,6 +44,9 @@ def test_gemm_matches_oracle(n, k, bits, ms, libs, oracle):
     sp = d.det_malloc(d.det_linear_repack_bytes(n, k, bits))
     d.det_linear_repack(C.byref(src), sp, None)
     stream = libs.QLinear(sp, cc, mm, n, k, bits | libs.DET_LAYOUT_STREAM)
+    w8 = d.det_malloc(d.det_linear_expand_bytes(n, k))
+    d.det_linear_expand(C.byref(src), w8, None)
+    tensor = libs.QLinear(w8, cc, mm, n, k, bits | libs.DET_LAYOUT_INT8)
     try:
         for mtok in ms:
             xq = rng.integers(-127, 128, (mtok, k)).astype(np.int8)
@@ -56,7 +59,7 @@ def test_gemm_matches_oracle(n, k, bits, ms, libs, oracle):
             d.det_memcpy(dx, xq.ctypes.data, xq.nbytes, None)
             d.det_memcpy(ds, sx.ctypes.data, sx.nbytes, None)
             d.det_memcpy(dm, mx.ctypes.data, mx.nbytes, None)
-            for name, lin in (("stream", stream), ("rowmajor", src)):
+            for name, lin in (("stream", stream), ("rowmajor", src), ("int8 tensor-core", tensor)):
                 got = np.zeros_like(want)
                 d.det_memset(dy, 0xFF, want.nbytes, None)
                 d.det_gemm(C.byref(lin), dx, ds, dm, mtok, dy, None)
@@ -68,5 +71,5 @@ def test_gemm_matches_oracle(n, k, bits, ms, libs, oracle):
                 d.det_free(p)
         assert d.det_last_error() == 0
     finally:
-        for p in (wq, cc, mm, sp):
+        for p in (wq, cc, mm, sp, w8):
             d.det_free(p)
