@@ -96,7 +96,7 @@ def build_host(force: bool = False) -> Path | None:
     out = LIB / "libdet_host.so"
     if force or jobs or _newer(out, objs):
         _run(["g++", "-shared", "-o", str(out)] + [str(o) for o in objs] +
-             ["-L", str(LIB), "-ldet_b200", "-Wl,-rpath,$ORIGIN", "-pthread"])
+             ["-L", str(LIB), "-ldet_b200", "-Wl,-rpath,$ORIGIN", "-pthread", "-ldl"])
     return out
 
 

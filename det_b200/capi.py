@@ -93,7 +93,9 @@ CUDA_ABI = {
     "det_linear_repack": (None, [C.POINTER(QLinear), c_void_p, c_void_p]),
     "det_linear_expand_bytes": (c_size_t, [c_int, c_int]),
     "det_linear_expand": (None, [C.POINTER(QLinear), c_void_p, c_void_p]),
-    "det_synth_linear": (None, [c_u64, c_u64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "det_synth_linear": (None, [c_u64, c_u64, C.c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p]),
+    "det_unshard": (None, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "det_synth_bf16": (None, [c_u64, c_u64, C.c_longlong, c_void_p, c_void_p]),
     "det_graph_begin": (None, []),
     "det_graph_end": (c_void_p, []),
@@ -112,6 +114,11 @@ HOST_API = {
     "dh_cuda_debug": (None, [c_void_p, C.c_uint, c_int]),
     "dh_cuda_test_prim": (None, [c_int, c_void_p, c_size_t, c_size_t, c_size_t, c_void_p, c_size_t]),
     "dh_model_new_synth": (c_void_p, [c_void_p, c_char_p, c_size_t, c_u64, c_size_t, c_size_t]),
+    "dh_nccl_unique_id": (None, [c_void_p]),
+    "dh_nccl_comm_new": (c_void_p, [c_void_p, c_int, c_int]),
+    "dh_callback_comm_new": (c_void_p, [c_int, c_int, c_void_p]),
+    "dh_comm_free": (None, [c_void_p]),
+    "dh_model_new_synth_tp": (c_void_p, [c_void_p, c_char_p, c_size_t, c_u64, c_size_t, c_size_t, c_void_p]),
     "dh_model_free": (None, [c_void_p]),
     "dh_model_vocab": (c_size_t, [c_void_p]),
     "dh_model_pos": (c_size_t, [c_void_p]),

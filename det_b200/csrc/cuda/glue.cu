@@ -196,6 +196,8 @@ __global__ void k_embed_rows(const uint16_t* __restrict__ table, const int* __re
     for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = __uint_as_float((unsigned)src[i] << 16);
 }
 __global__ void k_residual_add(float* __restrict__ x, const float* __restrict__ y, long long n) {
+    pdl_trigger();
+    pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] = fadd(x[i], y[i]);
 }
@@ -236,6 +238,19 @@ __global__ void __launch_bounds__(1024) k_argmax_rows(const float* __restrict__ 
     }
 }
 
+// tmp[P][M][slice] -> full[M][P][slice]
+__global__ void k_unshard(const float* __restrict__ tmp, float* __restrict__ full, int P, int M, int slice) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = (long long)P * M * slice;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int e = (int)(i % slice);
+        const long long rm = i / slice;
+        const int t = (int)(rm % M), r = (int)(rm / M);
+        full[((size_t)t * P + r) * slice + e] = tmp[i];
+    }
+}
+
 }  // namespace detb
 
 using namespace detb;
@@ -265,8 +280,13 @@ void det_embed(const uint16_t* table_bf16, const int* ids, int M, int H, float* 
 }
 void det_add(float* x, const float* y, long long n, cudaStream_t st) {
     if (n <= 0) return;
-    k_residual_add<<<(unsigned)((n + 255) / 256), 256, 0, queue_of(st)>>>(x, y, n);
-    DETB_CUDA_OK(cudaGetLastError());
+    launch_pdl(k_residual_add, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, queue_of(st), 1, x, y, n);
+}
+void det_unshard(const float* tmp, float* full, int P, int M, int slice, cudaStream_t st) {
+    const long long total = (long long)P * M * slice;
+    if (total <= 0) return;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < 1184 ? (total + 255) / 256 : 1184);
+    launch_pdl(k_unshard, dim3(blocks), dim3(256), 0, queue_of(st), 1, tmp, full, P, M, slice);
 }
 void det_argmax(const float* logits, int M, int V, int* out, cudaStream_t st) {
     if (M <= 0) return;

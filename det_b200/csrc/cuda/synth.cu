@@ -32,14 +32,14 @@ __device__ __forceinline__ double weight_f64(unsigned long long seed, unsigned l
 __device__ __forceinline__ double clampd(double q, double lim) { return q < -lim ? -lim : (q > lim ? lim : q); }
 
 // quantize.rs:33-56 for one (row, 128-group)
-__global__ void k_synth_scales(unsigned long long seed, unsigned long long tid, int n, int K, double qmax,
+__global__ void k_synth_scales(unsigned long long seed, unsigned long long tid, long long src0, int n, int K, double qmax,
                                double* __restrict__ scales) {
     const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int G = K >> 7;
     if (id >= (long long)n * G) return;
     const long long r = id / G;
     const int g = (int)(id % G);
-    const unsigned long long e0 = (unsigned long long)r * K + (unsigned long long)g * 128;
+    const unsigned long long e0 = (unsigned long long)(src0 + r) * K + (unsigned long long)g * 128;
     double amax = 0.0;
     for (int i = 0; i < 128; i++) {
         const double a = fabs(weight_f64(seed, tid, e0 + i));
@@ -66,7 +66,7 @@ __global__ void k_synth_scales(unsigned long long seed, unsigned long long tid, 
 }
 
 // quantize.rs:58-85 for one (row, 128-group): c, m, codes, packing (quantize.rs:8-31) into the reference layout
-__global__ void k_synth_rows(unsigned long long seed, unsigned long long tid, int n, int K, int bits, double qmax,
+__global__ void k_synth_rows(unsigned long long seed, unsigned long long tid, long long src0, int n, int K, int bits, double qmax,
                              const double* __restrict__ scales, int row0, uint8_t* __restrict__ wq,
                              float* __restrict__ c, uint16_t* __restrict__ m) {
     const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -87,7 +87,7 @@ __global__ void k_synth_rows(unsigned long long seed, unsigned long long tid, in
     const long long orow = row0 + r;
     if (g == 0) c[orow] = cf;
     m[orow * G + g] = (uint16_t)mg;
-    const unsigned long long e0 = (unsigned long long)r * K + (unsigned long long)g * 128;
+    const unsigned long long e0 = (unsigned long long)(src0 + r) * K + (unsigned long long)g * 128;
     const int bp32 = bits == 8 ? 32 : (bits == 6 ? 24 : 16);
     uint8_t* dst = wq + ((size_t)orow * (K >> 5) + (size_t)g * 4) * bp32;
     const int off = bits == 6 ? 32 : (bits == 4 ? 8 : 0);
@@ -121,16 +121,17 @@ using namespace detb;
 
 extern "C" {
 
-// Rows [row0, row0 + n) of a reference-layout linear from synthetic tensor `tid`.  `scratch` holds n * K/128 doubles.
-void det_synth_linear(unsigned long long seed, unsigned long long tid, int n, int K, int bits, int row0, uint8_t* wq,
-                      float* c, uint16_t* m, double* scratch, cudaStream_t st) {
+// Rows [src_row0, src_row0 + n) of synthetic tensor `tid` into rows [row0, row0 + n) of a reference-layout linear.
+// `scratch` holds n * K/128 doubles.
+void det_synth_linear(unsigned long long seed, unsigned long long tid, long long src_row0, int n, int K, int bits,
+                      int row0, uint8_t* wq, float* c, uint16_t* m, double* scratch, cudaStream_t st) {
     DETB_REQUIRE((bits == 4 || bits == 6 || bits == 8) && K % 128 == 0 && n > 0, "bad synthetic linear shape");
     const double qmax = (double)((1 << (bits - 1)) - 1);
     const long long work = (long long)n * (K >> 7);
     const unsigned grid = (unsigned)((work + 127) / 128);
     cudaStream_t q = queue_of(st);
-    k_synth_scales<<<grid, 128, 0, q>>>(seed, tid, n, K, qmax, scratch);
-    k_synth_rows<<<grid, 128, 0, q>>>(seed, tid, n, K, bits, qmax, scratch, row0, wq, c, m);
+    k_synth_scales<<<grid, 128, 0, q>>>(seed, tid, src_row0, n, K, qmax, scratch);
+    k_synth_rows<<<grid, 128, 0, q>>>(seed, tid, src_row0, n, K, bits, qmax, scratch, row0, wq, c, m);
     DETB_CUDA_OK(cudaGetLastError());
 }
 

@@ -71,11 +71,12 @@ struct LinearPart {
 struct SynthPart {
     uint64_t tensor_id;
     size_t n;
+    size_t row0 = 0;   // first row of the tensor this part takes (a tensor-parallel rank takes a slice of the rows)
 };
 
 // Optional source of synthetic det rows for Backend::linear_synth's default path (n rows of tensor tid).  When unset the
 // rows come from the host generator; a benchmark may plug in the device generator to build a CPU-side model quickly.
-using SynthRowsProvider = std::vector<uint8_t> (*)(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits);
+using SynthRowsProvider = std::vector<uint8_t> (*)(uint64_t seed, uint64_t tid, size_t row0, size_t n, size_t k, int bits);
 void set_synth_rows_provider(SynthRowsProvider p);
 
 // backend.rs:136-142
@@ -136,6 +137,7 @@ class Backend {
     virtual void read_bytes(const void* src, void* host_dst, size_t bytes) = 0;   // waits for the producers
     virtual void zero_bytes(void* p, size_t bytes) = 0;
     virtual void sync() = 0;
+    virtual void flush() {}   // issues anything a backend holds back (nothing by default); does not wait
 
     virtual std::unique_ptr<Linear> linear(const std::vector<LinearPart>& parts, size_t k, int bits) = 0;
     // A linear of the seeded synthetic model.  The default builds the det rows on the host and calls linear();
@@ -155,6 +157,11 @@ class Backend {
     virtual void gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, const Buf<float>& qkv,
                      const Buf<float>& z, const Buf<float>& a, const Buf<float>& b, const Buf<float>& on,
                      const GdnExport& ex) = 0;
+    // Not in the reference trait (its token loop is single-device): the two elementwise steps a tensor-parallel step
+    // needs on their own — the residual add that GemmOut::Accumulate otherwise fuses (x[i] = x[i] + y[i]), and the
+    // SwiGLU product without quantization (h[i] = silu_f(g[i]) * u[i]) — each exactly one spec operation per element.
+    virtual void add(const Buf<float>& x, const Buf<float>& y, size_t n) = 0;
+    virtual void silu_mul(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<float>& h) = 0;
     virtual int32_t argmax(const Buf<float>& logits, size_t v) = 0;
     virtual int32_t sample(const Buf<float>& logits, size_t v, float inv_temp, size_t top_k, float top_p,
                            uint64_t z) = 0;

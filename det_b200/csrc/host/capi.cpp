@@ -73,6 +73,32 @@ void* dh_model_new_synth(void* backend, const char* config, size_t layers, uint6
         return nullptr;
     }
 }
+// ---- tensor parallel: a communicator handle is a det::Comm*
+void dh_nccl_unique_id(uint8_t* out128) { det::NcclComm::unique_id(out128); }
+void* dh_nccl_comm_new(const uint8_t* id128, int rank, int size) {
+    try {
+        return static_cast<det::Comm*>(new det::NcclComm(id128, rank, size));
+    } catch (const std::exception& ex) {
+        g_err = ex.what();
+        return nullptr;
+    }
+}
+// gather(local, gathered, bytes): fills gathered[size][bytes] with every rank's block (host memory).
+void* dh_callback_comm_new(int rank, int size, void (*gather)(const void*, void*, size_t)) {
+    return static_cast<det::Comm*>(new det::CallbackComm(rank, size, gather));
+}
+void dh_comm_free(void* c) { delete static_cast<det::Comm*>(c); }
+void* dh_model_new_synth_tp(void* backend, const char* config, size_t layers, uint64_t seed, size_t max_ctx,
+                            size_t max_batch, void* comm) {
+    try {
+        det::Config cfg = det::config_by_name(config, layers);
+        return det::Model::load_synthetic(cfg, seed, static_cast<det::Backend*>(backend), max_ctx, max_batch,
+                                          static_cast<det::Comm*>(comm)).release();
+    } catch (const std::exception& ex) {
+        g_err = ex.what();
+        return nullptr;
+    }
+}
 void dh_model_free(void* m) { delete static_cast<det::Model*>(m); }
 size_t dh_model_vocab(void* m) { return static_cast<det::Model*>(m)->cfg.vocab; }
 size_t dh_model_pos(void* m) { return static_cast<det::Model*>(m)->pos; }
@@ -171,7 +197,7 @@ void dh_synth_prompt(uint64_t seed, size_t n, size_t vocab, int32_t* out) {
 }
 // Host twin of the synthetic generator: `n` det rows of tensor `tid` (for checking the device twin).
 void dh_synth_det_rows(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits, uint8_t* out) {
-    std::vector<uint8_t> rows = det::synth_det_rows(seed, tid, n, k, bits);
+    std::vector<uint8_t> rows = det::synth_det_rows(seed, tid, n, k, bits, 0);
     std::memcpy(out, rows.data(), rows.size());
 }
 size_t dh_det_row_bytes(int bits, size_t k) { return det::det_row_bytes(bits, k); }

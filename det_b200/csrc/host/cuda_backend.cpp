@@ -146,7 +146,7 @@ std::unique_ptr<Linear> CudaBackend::linear_synth(uint64_t seed, const std::vect
     double* tmp = static_cast<double*>(scratch(synth_scratch_, nmax * g * sizeof(double)));
     size_t row0 = 0;
     for (const SynthPart& p : parts) {
-        det_synth_linear(seed, p.tensor_id, (int)p.n, (int)k, bits, (int)row0, lin->wq.ptr(), lin->c.ptr(),
+        det_synth_linear(seed, p.tensor_id, (long long)p.row0, (int)p.n, (int)k, bits, (int)row0, lin->wq.ptr(), lin->c.ptr(),
                          lin->m.ptr(), tmp, ST);
         row0 += p.n;
     }
@@ -269,6 +269,15 @@ void CudaBackend::gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, 
                ST);
 }
 
+void CudaBackend::add(const Buf<float>& x, const Buf<float>& y, size_t n) {
+    flush_pending();
+    det_add(x.ptr(), y.ptr(), (long long)n, ST);
+}
+void CudaBackend::silu_mul(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<float>& h) {
+    flush_pending();
+    det_silu_mul_quant(g.ptr(), u.ptr(), (int)m, (int)n, h.ptr(), nullptr, nullptr, nullptr, ST);
+}
+
 // cuda.rs:425-471
 int32_t CudaBackend::argmax(const Buf<float>& logits, size_t v) {
     flush_pending();
@@ -290,14 +299,14 @@ int32_t CudaBackend::sample(const Buf<float>& logits, size_t v, float inv_temp, 
 }
 
 // det rows [codes | c | m] of a synthetic tensor, generated on the device and copied to the host
-std::vector<uint8_t> cuda_synth_det_rows(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits) {
+std::vector<uint8_t> cuda_synth_det_rows(uint64_t seed, uint64_t tid, size_t src0, size_t n, size_t k, int bits) {
     const size_t nc = k / 32 * bytes_per_32(bits), g = k / 128, rb = nc + 4 + 2 * g;
     void* wq = det_malloc(n * nc);
     void* c = det_malloc(n * 4);
     void* m = det_malloc(n * g * 2);
     void* tmp = det_malloc(n * g * sizeof(double));
     if (!wq || !c || !m || !tmp) throw std::runtime_error("cuda_synth_det_rows: out of device memory");
-    det_synth_linear(seed, tid, (int)n, (int)k, bits, 0, (uint8_t*)wq, (float*)c, (uint16_t*)m, (double*)tmp, ST);
+    det_synth_linear(seed, tid, (long long)src0, (int)n, (int)k, bits, 0, (uint8_t*)wq, (float*)c, (uint16_t*)m, (double*)tmp, ST);
     std::vector<uint8_t> hw(n * nc), hm(n * g * 2), out(n * rb);
     std::vector<float> hc(n);
     det_memcpy(hw.data(), wq, hw.size(), ST);

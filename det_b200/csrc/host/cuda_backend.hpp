@@ -25,6 +25,7 @@ class CudaBackend : public Backend {
     void read_bytes(const void* src, void* host_dst, size_t bytes) override;
     void zero_bytes(void* p, size_t bytes) override;
     void sync() override;
+    void flush() override { flush_pending(); }
     std::unique_ptr<Linear> linear(const std::vector<LinearPart>& parts, size_t k, int bits) override;
     std::unique_ptr<Linear> linear_synth(uint64_t seed, const std::vector<SynthPart>& parts, size_t k,
                                          int bits) override;
@@ -40,6 +41,8 @@ class CudaBackend : public Backend {
                    const Buf<float>& v, const Buf<float>& o) override;
     void gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, const Buf<float>& qkv, const Buf<float>& z,
              const Buf<float>& a, const Buf<float>& b, const Buf<float>& on, const GdnExport& ex) override;
+    void add(const Buf<float>& x, const Buf<float>& y, size_t n) override;
+    void silu_mul(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<float>& h) override;
     int32_t argmax(const Buf<float>& logits, size_t v) override;
     int32_t sample(const Buf<float>& logits, size_t v, float inv_temp, size_t top_k, float top_p, uint64_t z) override;
 
@@ -91,7 +94,7 @@ class CudaBackend : public Backend {
     Buf<uint64_t> z_;
 };
 
-std::vector<uint8_t> cuda_synth_det_rows(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits);
+std::vector<uint8_t> cuda_synth_det_rows(uint64_t seed, uint64_t tid, size_t src0, size_t n, size_t k, int bits);
 
 class Model;
 struct GemvSweep {

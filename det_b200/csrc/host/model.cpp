@@ -14,8 +14,8 @@ std::unique_ptr<Linear> Backend::linear_synth(uint64_t seed, const std::vector<S
     std::vector<std::vector<uint8_t>> rows;
     std::vector<LinearPart> lp;
     for (const SynthPart& p : parts) {
-        rows.push_back(g_rows_provider ? g_rows_provider(seed, p.tensor_id, p.n, k, bits)
-                                       : synth_det_rows(seed, p.tensor_id, p.n, k, bits));
+        rows.push_back(g_rows_provider ? g_rows_provider(seed, p.tensor_id, p.row0, p.n, k, bits)
+                                       : synth_det_rows(seed, p.tensor_id, p.n, k, bits, p.row0));
         lp.push_back(LinearPart{rows.back().data(), p.n});
     }
     return linear(lp, k, bits);
@@ -26,6 +26,7 @@ struct SynthTensor {
     TensorKind kind;
     size_t n, k;
     int bits;
+    size_t row0 = 0;
 };
 // model.rs:180-197 — consecutive tensors of equal type and K become one fused linear.
 Proj make_proj(Backend* bk, uint64_t seed, size_t layer, const std::vector<SynthTensor>& ts) {
@@ -35,7 +36,7 @@ Proj make_proj(Backend* bk, uint64_t seed, size_t layer, const std::vector<Synth
         size_t j = i + 1;
         while (j < ts.size() && ts[j].bits == ts[i].bits && ts[j].k == ts[i].k) j++;
         std::vector<SynthPart> parts;
-        for (size_t q = i; q < j; q++) parts.push_back(SynthPart{tensor_id(layer, ts[q].kind), ts[q].n});
+        for (size_t q = i; q < j; q++) parts.push_back(SynthPart{tensor_id(layer, ts[q].kind), ts[q].n, ts[q].row0});
         p.lins.push_back(bk->linear_synth(seed, parts, ts[i].k, ts[i].bits));
         i = j;
     }
@@ -44,10 +45,17 @@ Proj make_proj(Backend* bk, uint64_t seed, size_t layer, const std::vector<Synth
 Buf<float> ones(Backend* bk, size_t n) { return bk->upload(std::vector<float>(n, 1.0f)); }
 }  // namespace
 
+static void load_shard(Model& m, const Config& cfg, uint64_t seed, Backend* bk, size_t max_ctx, size_t max_batch);
+
 std::unique_ptr<Model> Model::load_synthetic(const Config& cfg, uint64_t seed, Backend* bk, size_t max_ctx,
-                                             size_t max_batch) {
+                                             size_t max_batch, Comm* comm) {
     auto mp = std::make_unique<Model>();
     Model& m = *mp;
+    if (comm && comm->size > 1) {
+        m.comm = comm;
+        load_shard(m, cfg, seed, bk, max_ctx, max_batch);
+        return mp;
+    }
     m.cfg = cfg;
     m.backend = bk;
     m.seed = seed;
@@ -183,6 +191,10 @@ void Model::project(const Proj& p, const Buf<int8_t>& xq, const Buf<float>& sx, 
 
 // qwen35.rs:31-170
 void Model::network(size_t pos0, size_t t) {
+    if (comm) {
+        network_tp(pos0, t);
+        return;
+    }
     const Config& c = cfg;
     Backend* bk = backend;
     const size_t h = c.hidden;
@@ -219,6 +231,200 @@ void Model::network(size_t pos0, size_t t) {
         bk->rmsnorm_quant(last, final_norm, c.eps, 1, h, w.xq, w.sx, w.mx);
         bk->gemm(*lm_head.lins[0], w.xq, w.sx, w.mx, 1, GemmOut::write(w.logits));
     }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Tensor parallel shard.  Rank r of P owns, per layer:
+//   attention  q heads [r*n_h/P, ...) with the kv head(s) they read (a kv head shared by several ranks is recomputed on
+//              each of them, identically); rows [r*H/P, ...) of the output projection
+//   GDN        k heads [r*n_k/P, ...) with their v heads (conv channels, a/b rows, state); rows of ssm_out as above
+//   FFN        columns [r*F/P, ...) of gate and up (whole 128-groups); rows [r*H/P, ...) of down
+//   head       vocabulary rows [r*V/P, ...)
+// Every fp32 value is produced by exactly one rank (or identically on several) with the single-device op sequence; the
+// exchanges copy finished values (mixer output, SwiGLU product, projection rows, logits), so logits cannot change.
+static void load_shard(Model& m, const Config& cfg, uint64_t seed, Backend* bk, size_t max_ctx, size_t max_batch) {
+    const size_t P = (size_t)m.comm->size, r = (size_t)m.comm->rank;
+    m.cfg = cfg;
+    m.backend = bk;
+    m.seed = seed;
+    m.max_ctx = max_ctx;
+    m.max_batch = max_batch;
+    const size_t h = cfg.hidden, inter = cfg.intermediate;
+    const size_t n_h = cfg.n_heads, n_kv = cfg.n_kv, hd = cfg.head_dim, rep = n_h / n_kv;
+    const size_t n_k = cfg.gdn_k_heads, n_v = cfg.gdn_v_heads, dk = cfg.gdn_dk, dv = cfg.gdn_dv, grep = n_v / n_k;
+    const int wb = cfg.bits_default;
+    auto need = [](bool ok, const char* what) {
+        if (!ok) throw std::runtime_error(std::string("tensor parallel size does not divide ") + what);
+    };
+    need(n_h % P == 0, "the attention heads");
+    need(n_k % P == 0, "the GDN key heads");
+    need(h % (P * 128) == 0 || h % P == 0, "the hidden size");
+    need(inter % (P * 128) == 0, "the FFN groups");
+    need(cfg.vocab % P == 0, "the vocabulary");
+    need(n_h * hd == n_v * dv, "mixer widths (attention and GDN outputs share one gather buffer)");
+    Model::Tp& tp = m.tp;
+    tp.heads = n_h / P;
+    const size_t h0 = r * tp.heads;
+    tp.kv = n_kv >= P ? n_kv / P : 1;
+    const size_t kv0 = h0 / rep;
+    need(n_kv >= P ? n_kv % P == 0 : rep % tp.heads == 0, "the kv heads");
+    tp.k_heads = n_k / P;
+    tp.v_heads = tp.k_heads * grep;
+    const size_t k0 = r * tp.k_heads, v0 = k0 * grep;
+    tp.ffn = inter / P;
+    tp.hid = h / P;
+    tp.voc = cfg.vocab / P;
+    const size_t f0 = r * tp.ffn, hr0 = r * tp.hid;
+
+    m.final_norm = ones(bk, h);
+    std::vector<float> rc, rs;
+    rope_tables(cfg, max_ctx, rc, rs);
+    m.rope_cos = bk->upload(rc);
+    m.rope_sin = bk->upload(rs);
+    m.lm_head = make_proj(bk, seed, GLOBAL_LAYER, {{T_EMBED, tp.voc, h, 8, r * tp.voc}});
+    const size_t conv_l = 2 * tp.k_heads * dk + tp.v_heads * dv;
+    m.layers.resize(cfg.n_layers);
+    for (size_t i = 0; i < cfg.n_layers; i++) {
+        Layer& l = m.layers[i];
+        l.is_attn = cfg.is_attention(i);
+        if (l.is_attn) {
+            Attn& a = l.attn;
+            a.qkv = make_proj(bk, seed, i, {{T_ATTN_Q, tp.heads * 2 * hd, h, wb, h0 * 2 * hd},
+                                            {T_ATTN_K, tp.kv * hd, h, wb, kv0 * hd},
+                                            {T_ATTN_V, tp.kv * hd, h, wb, kv0 * hd}});
+            a.o = make_proj(bk, seed, i, {{T_ATTN_OUT, tp.hid, n_h * hd, wb, hr0}});
+            a.q_norm = ones(bk, hd);
+            a.k_norm = ones(bk, hd);
+            std::vector<float> vs(tp.kv, DEFAULT_V_SCALE), vis(tp.kv);
+            for (size_t q = 0; q < tp.kv; q++) vis[q] = 1.0f / vs[q];
+            a.v_scale = bk->upload(vs);
+            a.v_inv_scale = bk->upload(vis);
+            a.kv.kq = bk->alloc<int8_t>(max_ctx * tp.kv * hd);
+            a.kv.sk = bk->alloc<float>(max_ctx * tp.kv);
+            a.kv.vq = bk->alloc<int16_t>(max_ctx * tp.kv * hd);
+            a.kv.capacity = max_ctx;
+        } else {
+            Gdn& g = l.gdn;
+            // attn_qkv rows are [q: n_k*dk | k: n_k*dk | v: n_v*dv]; the local linear keeps that order for its heads
+            g.qkvz = make_proj(bk, seed, i, {{T_GDN_QKV, tp.k_heads * dk, h, wb, k0 * dk},
+                                             {T_GDN_QKV, tp.k_heads * dk, h, wb, n_k * dk + k0 * dk},
+                                             {T_GDN_QKV, tp.v_heads * dv, h, wb, 2 * n_k * dk + v0 * dv},
+                                             {T_GDN_GATE, tp.v_heads * dv, h, wb, v0 * dv}});
+            // the q, k and v row ranges are one output ([q | k | v] per token, what the mixer reads); z is the other
+            g.qkvz.lins[0]->widths = {conv_l, tp.v_heads * dv};
+            g.ab = make_proj(bk, seed, i, {{T_GDN_ALPHA, tp.v_heads, h, 8, v0}, {T_GDN_BETA, tp.v_heads, h, 8, v0}});
+            g.out = make_proj(bk, seed, i, {{T_GDN_OUT, tp.hid, n_v * dv, wb, hr0}});
+            std::vector<float> conv(conv_l * cfg.conv_k), dtb(tp.v_heads), av(tp.v_heads);
+            auto global_channel = [&](size_t c) {   // local conv channel -> channel of the full model
+                if (c < tp.k_heads * dk) return k0 * dk + c;
+                c -= tp.k_heads * dk;
+                if (c < tp.k_heads * dk) return n_k * dk + k0 * dk + c;
+                c -= tp.k_heads * dk;
+                return 2 * n_k * dk + v0 * dv + c;
+            };
+            for (size_t c = 0; c < conv_l; c++)
+                for (size_t tap = 0; tap < cfg.conv_k; tap++)
+                    conv[c * cfg.conv_k + tap] =
+                        draw_normal(seed, tensor_id(i, T_CONV), global_channel(c) * cfg.conv_k + tap, WEIGHT_STD);
+            for (size_t q = 0; q < tp.v_heads; q++) {
+                dtb[q] = draw_normal(seed, tensor_id(i, T_DT_BIAS), v0 + q, WEIGHT_STD);
+                av[q] = 1.0f + 15.0f * draw_unit(seed, tensor_id(i, T_SSM_A), v0 + q);
+            }
+            g.conv = bk->upload(conv);
+            g.a = bk->upload(av);
+            g.dt_bias = bk->upload(dtb);
+            g.norm = ones(bk, dv);
+            g.state.conv_state = bk->alloc<float>((cfg.conv_k - 1) * conv_l);
+            g.state.s = bk->alloc<float>(tp.v_heads * dk * dv);
+        }
+        l.attn_norm = ones(bk, h);
+        l.ffn_norm = ones(bk, h);
+        l.gu = make_proj(bk, seed, i, {{T_FFN_GATE, tp.ffn, h, wb, f0}, {T_FFN_UP, tp.ffn, h, wb, f0}});
+        l.down = make_proj(bk, seed, i, {{T_FFN_DOWN, tp.hid, inter, wb, hr0}});
+    }
+    const size_t mb = max_batch;
+    Work& w = m.w;
+    const size_t mix = n_h * hd;
+    w.x = bk->alloc<float>(mb * h);
+    w.xq = bk->alloc<int8_t>(mb * h);
+    w.sx = bk->alloc<float>(mb);
+    w.mx = bk->alloc<uint16_t>(mb * h / 128);
+    w.qg = bk->alloc<float>(mb * tp.heads * 2 * hd);
+    w.k = bk->alloc<float>(mb * tp.kv * hd);
+    w.v = bk->alloc<float>(mb * tp.kv * hd);
+    w.o = bk->alloc<float>(mb * std::max(tp.heads * hd, tp.v_heads * dv));   // local mixer output (either kind)
+    w.oq = bk->alloc<int8_t>(mb * mix);
+    w.so = bk->alloc<float>(mb);
+    w.mo = bk->alloc<uint16_t>(mb * mix / 128);
+    w.qkv = bk->alloc<float>(mb * conv_l);
+    w.z = bk->alloc<float>(mb * tp.v_heads * dv);
+    w.a = bk->alloc<float>(mb * tp.v_heads);
+    w.b = bk->alloc<float>(mb * tp.v_heads);
+    w.g = bk->alloc<float>(mb * tp.ffn);
+    w.u = bk->alloc<float>(mb * tp.ffn);
+    w.hq = bk->alloc<int8_t>(mb * inter);
+    w.sh = bk->alloc<float>(mb);
+    w.mh = bk->alloc<uint16_t>(mb * inter / 128);
+    w.logits = bk->alloc<float>(cfg.vocab);
+    tp.mix_full = bk->alloc<float>(mb * mix);
+    tp.h_l = bk->alloc<float>(mb * tp.ffn);
+    tp.h_full = bk->alloc<float>(mb * inter);
+    tp.y_l = bk->alloc<float>(mb * tp.hid);
+    tp.y_full = bk->alloc<float>(mb * h);
+    tp.logits_l = bk->alloc<float>(mb * tp.voc);
+    tp.tmp = bk->alloc<float>(std::max(mb * std::max(inter, mix), cfg.vocab));
+}
+
+void Model::network_tp(size_t pos0, size_t t) {
+    const Config& c = cfg;
+    Backend* bk = backend;
+    const size_t h = c.hidden, P = (size_t)comm->size;
+    const size_t mix = c.n_heads * c.head_dim;
+    // y_l holds this rank's rows of a projection back to the hidden size: gather the rows, then x += y on every rank
+    auto reduce_into_x = [&](const Linear& lin, const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
+        bk->gemm(lin, q, s, mm, t, GemmOut::write(tp.y_l));
+        comm->all_gather(*bk, tp.y_l, tp.tmp, tp.y_full, t, tp.hid);
+        bk->add(w.x, tp.y_full, t * h);
+    };
+    for (Layer& l : layers) {
+        bk->rmsnorm_quant(w.x, l.attn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
+        if (l.is_attn) {
+            Attn& a = l.attn;
+            project(a.qkv, w.xq, w.sx, w.mx, t, {&w.qg, &w.k, &w.v});
+            AttnLayer layer{&a.q_norm, &a.k_norm, &a.v_scale, &a.v_inv_scale, &rope_cos, &rope_sin};
+            Shape shape{t, pos0, tp.heads, tp.kv, c.head_dim, c.rot_dim, c.eps};
+            bk->attention(layer, a.kv, shape, w.qg, w.k, w.v, w.o);
+            comm->all_gather(*bk, w.o, tp.tmp, tp.mix_full, t, tp.heads * c.head_dim);
+            bk->quant(tp.mix_full, t, mix, w.oq, w.so, w.mo);
+            reduce_into_x(*a.o.lins[0], w.oq, w.so, w.mo);
+        } else {
+            Gdn& g = l.gdn;
+            project(g.qkvz, w.xq, w.sx, w.mx, t, {&w.qkv, &w.z});
+            project(g.ab, w.xq, w.sx, w.mx, t, {&w.a, &w.b});
+            GdnLayer layer{&g.conv, &g.a, &g.dt_bias, &g.norm};
+            GdnShape shape{t, tp.k_heads, tp.v_heads, c.gdn_dk, c.gdn_dv, c.eps};
+            bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.o, GdnExport{});
+            comm->all_gather(*bk, w.o, tp.tmp, tp.mix_full, t, tp.v_heads * c.gdn_dv);
+            bk->quant(tp.mix_full, t, mix, w.oq, w.so, w.mo);
+            reduce_into_x(*g.out.lins[0], w.oq, w.so, w.mo);
+        }
+        bk->rmsnorm_quant(w.x, l.ffn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
+        project(l.gu, w.xq, w.sx, w.mx, t, {&w.g, &w.u});
+        bk->silu_mul(w.g, w.u, t, tp.ffn, tp.h_l);
+        comm->all_gather(*bk, tp.h_l, tp.tmp, tp.h_full, t, tp.ffn);
+        bk->quant(tp.h_full, t, c.intermediate, w.hq, w.sh, w.mh);
+        reduce_into_x(*l.down.lins[0], w.hq, w.sh, w.mh);
+    }
+    const size_t rows = all_logits ? t : 1;
+    if (all_logits) {
+        bk->rmsnorm_quant(w.x, final_norm, c.eps, t, h, w.xq, w.sx, w.mx);
+    } else {
+        Buf<float> last = Buf<float>::view(w.x.ptr_at((t - 1) * h), h);
+        bk->rmsnorm_quant(last, final_norm, c.eps, 1, h, w.xq, w.sx, w.mx);
+    }
+    bk->gemm(*lm_head.lins[0], w.xq, w.sx, w.mx, rows, GemmOut::write(tp.logits_l));
+    comm->all_gather(*bk, tp.logits_l, tp.tmp, w.logits, rows, tp.voc);
+    (void)P;
 }
 
 std::string Model::forward(const int32_t* ids, size_t t) {

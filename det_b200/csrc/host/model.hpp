@@ -4,6 +4,7 @@
 // the op set of backend.hpp, so the same driver runs the CUDA backend and, in tests, the CPU reference backend.
 #pragma once
 #include "backend.hpp"
+#include "comm.hpp"
 #include "synth.hpp"
 #include <functional>
 #include <memory>
@@ -64,8 +65,11 @@ struct Sampling {   // model.rs:120-141
 class Model {
   public:
     // A seeded random-init model of shape `cfg` (the stand-in for Model::load on a converted checkpoint).
+    // `comm` (optional) makes this the shard of rank comm->rank in a tensor-parallel group of comm->size: linears are
+    // cut by output rows, attention by q heads, Gated DeltaNet by k heads, the FFN by 128-column groups, the head by
+    // vocabulary rows; the residual stream and the norms stay replicated (see network_tp in model.cpp).
     static std::unique_ptr<Model> load_synthetic(const Config& cfg, uint64_t seed, Backend* backend, size_t max_ctx,
-                                                 size_t max_batch);
+                                                 size_t max_batch, Comm* comm = nullptr);
 
     void set_all_logits(bool all);                                   // model.rs:367-375
     void reset();                                                    // model.rs:377-387
@@ -91,6 +95,22 @@ class Model {
     bool all_logits = false;
 
     void network(size_t pos0, size_t t);   // qwen35.rs:8-172
+
+    // ---- tensor parallel state (comm == nullptr: none of it is used)
+    Comm* comm = nullptr;
+    struct Tp {
+        size_t heads = 0, kv = 0;        // local q heads / kv heads of an attention layer
+        size_t k_heads = 0, v_heads = 0; // local GDN heads
+        size_t ffn = 0, hid = 0, voc = 0;   // local FFN columns, hidden rows, vocabulary rows
+        Buf<float> mix_full;   // [mb][n_h*hd] gathered mixer output
+        Buf<float> h_l, h_full;      // SwiGLU product, local and gathered
+        Buf<float> y_l, y_full;      // projection back to hidden, local rows and gathered
+        Buf<float> logits_l;
+        Buf<float> tmp;              // all-gather scratch
+    } tp;
+
+  private:
+    void network_tp(size_t pos0, size_t t);
 };
 
 }  // namespace det

@@ -127,7 +127,7 @@ void quantize_row(const float* w, size_t k, int bits, uint8_t* out_row) {
     std::memcpy(tail + 4, m.data(), g * 2);
 }
 
-std::vector<uint8_t> synth_det_rows(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits) {
+std::vector<uint8_t> synth_det_rows(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits, size_t row0) {
     const size_t rb = det_row_bytes(bits, k);
     std::vector<uint8_t> out(n * rb);
     unsigned nt = std::max(1u, std::min(std::thread::hardware_concurrency(), 32u));
@@ -137,7 +137,7 @@ std::vector<uint8_t> synth_det_rows(uint64_t seed, uint64_t tid, size_t n, size_
         pool.emplace_back([&, w]() {
             std::vector<float> row(k);
             for (size_t r = w; r < n; r += nt) {
-                for (size_t i = 0; i < k; i++) row[i] = synth_weight(seed, tid, r * k + i);
+                for (size_t i = 0; i < k; i++) row[i] = synth_weight(seed, tid, (row0 + r) * k + i);
                 quantize_row(row.data(), k, bits, out.data() + r * rb);
             }
         });

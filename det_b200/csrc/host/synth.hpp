@@ -84,7 +84,7 @@ size_t det_row_bytes(int bits, size_t k);                                     //
 void pack_codes(const int8_t* codes, size_t n, int bits, uint8_t* out);       // quantize.rs:8-31
 void quantize_row(const float* w, size_t k, int bits, uint8_t* out_row);      // quantize.rs:58-85
 // `n` det rows of a synthetic tensor (rows generated on the fly, threads over rows).
-std::vector<uint8_t> synth_det_rows(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits);
+std::vector<uint8_t> synth_det_rows(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits, size_t row0 = 0);
 
 // ---- rope tables [pos][rot/2], computed in binary64 and rounded once (convert.rs:370-385)
 void rope_tables(const Config& c, size_t n_pos, std::vector<float>& cos, std::vector<float>& sin);

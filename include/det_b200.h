@@ -185,11 +185,13 @@ void det_gemm_fused(const det_qlinear* L, const det_act_source* src, int M, floa
                     const int* offs, float* const* dsts, cudaStream_t st);
 
 /* Seeded synthetic weights generated in device memory (the benchmarks' stand-in for a converted checkpoint; the host
- * twin is det_b200/csrc/host/synth.cpp and follows crates/det/src/quantize.rs:33-85).  det_synth_linear fills rows
- * [row0, row0 + n) of a reference-layout linear (wq, c, m as in det_qlinear) from tensor `tid` of model `seed`;
- * `scratch` needs n * (K/128) doubles.  det_synth_bf16 writes `count` bf16 elements of tensor `tid`.                */
-void det_synth_linear(unsigned long long seed, unsigned long long tid, int n, int K, int bits, int row0, uint8_t* wq,
-                      float* c, uint16_t* m, double* scratch, cudaStream_t st);
+ * twin is det_b200/csrc/host/synth.cpp and follows crates/det/src/quantize.rs:33-85).  det_synth_linear writes rows
+ * [src_row0, src_row0 + n) of tensor `tid` of model `seed` into rows [row0, row0 + n) of a reference-layout linear
+ * (wq, c, m as in det_qlinear); `scratch` needs n * (K/128) doubles.  det_synth_bf16 writes `count` bf16 elements.    */
+void det_synth_linear(unsigned long long seed, unsigned long long tid, long long src_row0, int n, int K, int bits,
+                      int row0, uint8_t* wq, float* c, uint16_t* m, double* scratch, cudaStream_t st);
+/* Tensor-parallel helper: tmp[P][M][slice] (what an all-gather of per-rank [M][slice] blocks yields) -> full[M][P*slice]. */
+void det_unshard(const float* tmp, float* full, int P, int M, int slice, cudaStream_t st);
 void det_synth_bf16(unsigned long long seed, unsigned long long tid, long long count, uint16_t* out, cudaStream_t st);
 
 /* Decode-step graph (the reference lists "CUDA graphs for decode" as future work, README.md:115; its C side only has the

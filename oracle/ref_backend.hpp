@@ -54,7 +54,7 @@ class RefBackend : public det::Backend {
         const refops::Out mode = out.kind == det::GemmOut::Write ? refops::Out::Write
                                  : out.kind == det::GemmOut::Accumulate ? refops::Out::Accumulate
                                                                         : refops::Out::Parts;
-        refops::gemm(l.view, xq.ptr(), sx.ptr(), mx.ptr(), m, mode, dsts.data());
+        refops::gemm(l.view, xq.ptr(), sx.ptr(), mx.ptr(), m, mode, dsts.data(), &l.widths);
     }
     void silu_mul_quant(const det::Buf<float>& g, const det::Buf<float>& u, size_t m, size_t n,
                         const det::Buf<int8_t>& hq, const det::Buf<float>& sh, const det::Buf<uint16_t>& mh) override {
@@ -76,6 +76,12 @@ class RefBackend : public det::Backend {
         refops::GdnShape rs{s.m, s.n_k, s.n_v, s.dk, s.dv, s.eps};
         refops::gdn(rl, rst, rs, qkv.ptr(), z.ptr(), a.ptr(), b.ptr(), on.ptr(), ex.gin ? ex.gin->ptr() : nullptr,
                     ex.gout ? ex.gout->ptr() : nullptr);
+    }
+    void add(const det::Buf<float>& x, const det::Buf<float>& y, size_t n) override {
+        for (size_t i = 0; i < n; i++) x.ptr()[i] = x.ptr()[i] + y.ptr()[i];   // the add of GemmOut::Accumulate (cpu.rs:172-175)
+    }
+    void silu_mul(const det::Buf<float>& g, const det::Buf<float>& u, size_t m, size_t n, const det::Buf<float>& h) override {
+        for (size_t i = 0; i < m * n; i++) h.ptr()[i] = spec::silu_f(g.ptr()[i]) * u.ptr()[i];   // cpu.rs:207
     }
     int32_t argmax(const det::Buf<float>& logits, size_t v) override { return (int32_t)spec::argmax(logits.ptr(), v); }
     int32_t sample(const det::Buf<float>& logits, size_t v, float inv_temp, size_t top_k, float top_p,

@@ -47,8 +47,9 @@ inline void quant(const float* x, size_t m, size_t n, int8_t* xq, float* sx, uin
 
 enum class Out { Write, Accumulate, Parts };
 // cpu.rs:142-186.  The per-token unpack of cpu.rs:159-167 is hoisted out of the token loop (integers; legal).
+// `out_widths` (Parts only) are the widths of the destination buffers; they default to the widths of the source parts.
 inline void gemm(const Linear& lin, const int8_t* xq, const float* sx, const uint16_t* mx, size_t m, Out mode,
-                 float* const* dsts /* Write/Accumulate: dsts[0] */) {
+                 float* const* dsts /* Write/Accumulate: dsts[0] */, const std::vector<size_t>* out_widths = nullptr) {
     const size_t k = lin.k, n = lin.n(), g = k / spec::GROUP;
     std::vector<float> y(m * n);
 #pragma omp parallel for schedule(static)
@@ -74,8 +75,9 @@ inline void gemm(const Linear& lin, const int8_t* xq, const float* sx, const uin
             }
             case Out::Parts: {
                 size_t off = 0;
-                for (size_t i = 0; i < lin.widths.size(); i++) {
-                    size_t w = lin.widths[i];
+                const std::vector<size_t>& ws = out_widths ? *out_widths : lin.widths;
+                for (size_t i = 0; i < ws.size(); i++) {
+                    size_t w = ws[i];
                     std::memcpy(dsts[i] + t * w, yt + off, w * sizeof(float));
                     off += w;
                 }
