@@ -202,8 +202,26 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     bk = h.dh_cuda_backend_new(1, 1)
     if not bk:
         raise RuntimeError(h.dh_last_error().decode())
+    # N > 1: tensor parallel over NVLink.  torch.distributed (gloo, CPU) only carries the NCCL id, the barriers and the
+    # max-over-ranks of the timings; the data path uses the library's own NCCL communicator on its queue.
+    dist, comm = None, None
+    if world > 1:
+        import torch
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("gloo")
+        dist = dist_mod
+        nid = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = np.zeros(128, np.uint8)
+            h.dh_nccl_unique_id(buf.ctypes.data)
+            nid = torch.from_numpy(buf)
+        dist.broadcast(nid, 0)
+        nid_np = nid.numpy().copy()
+        comm = h.dh_nccl_comm_new(nid_np.ctypes.data, rank, world)
+        if not comm:
+            raise RuntimeError(h.dh_last_error().decode())
     t_load = time.perf_counter()
-    model = h.dh_model_new_synth(bk, cfg.encode(), 0, SEED, max_ctx, chunk)
+    model = h.dh_model_new_synth_tp(bk, cfg.encode(), 0, SEED, max_ctx, chunk, comm)
     if not model:
         raise RuntimeError(h.dh_last_error().decode())
     d.det_sync()
@@ -213,24 +231,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     sampler.start()
     windows = []
 
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist_mod
-        torch.cuda.set_device(local_rank)
-        dist_mod.init_process_group("nccl")
-        dist = dist_mod
-
     def barrier():
+        d.det_sync()
         if dist:
             dist.barrier()
-        d.det_sync()
 
     def max_over_ranks(ms: float) -> float:
         if not dist:
             return ms
         import torch
-        t = torch.tensor([ms], device="cuda")
+        t = torch.tensor([ms], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
@@ -287,16 +297,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     windows.append((w0, time.time()))
 
     # ---- the decode GEMV alone: every linear of the model at M = 1 (one token's GEMVs), weights 20 GB >> L2
-    nbytes, nlaunch = C.c_size_t(0), C.c_size_t(0)
-    _check(h.dh_gemv_sweep(model, 1, C.byref(nbytes), C.byref(nlaunch)), h)
-    reps = 3
-    barrier()
-    w0 = time.time()
-    a = ev.record()
-    _check(h.dh_gemv_sweep(model, reps, C.byref(nbytes), C.byref(nlaunch)), h)
-    b = ev.record()
-    sweep_ms = ev.ms(a, b)
-    windows.append((w0, time.time()))
+    nbytes, nlaunch, sweep_ms = C.c_size_t(0), C.c_size_t(0), None
+    if world == 1:
+        _check(h.dh_gemv_sweep(model, 1, C.byref(nbytes), C.byref(nlaunch)), h)
+        reps = 3
+        barrier()
+        w0 = time.time()
+        a = ev.record()
+        _check(h.dh_gemv_sweep(model, reps, C.byref(nbytes), C.byref(nlaunch)), h)
+        b = ev.record()
+        sweep_ms = ev.ms(a, b)
+        windows.append((w0, time.time()))
     time.sleep(0.3)
     sampler.stop()
     err = d.det_last_error()
@@ -306,23 +317,30 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if rank != 0:
         return
     peak, peak_kind = _peaks()
-    achieved = nbytes.value / (sweep_ms * 1e-3) / 1e9
+    achieved = nbytes.value / (sweep_ms * 1e-3) / 1e9 if sweep_ms else None
     line = {
         "metric": "27B W6 decode tok/s bs1" if cfg == "27b" else f"{cfg} W6 decode tok/s bs1",
-        "value": world * K / (decode_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "value": K / (decode_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+        "vs_baseline": None,
         "dtype": "int8 x W6 -> int64 (fp32 glue)", "data": "synthetic",
         "config": {"workload": f"{cfg}-shape seeded random-init W6 model (W8 head and GDN a/b), batch 1: prefill {P} tokens in "
                                f"{chunk}-token chunks, then greedy decode", "context_at_timing": P + W,
-                   "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas (tensor parallel not built)",
+                   "parallelism": "1 GPU" if world == 1 else
+                   f"tp{world}: output-row / head tensor parallel, fp32 slices all-gathered over NCCL (one batch-1 sequence)",
                    "l2": "weights streamed per token (20 GB at 27B) exceed the 126 MB L2", "seed": SEED,
                    "rot_dim": 64, "rope_theta": 1e7, "eps": 1e-6, "v_scale": 2 ** -10},
-        "e2e": {"value": world * K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": shape["hidden"] * 4,
+        "e2e": {"value": K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": shape["hidden"] * 4,
                 "d2h_bytes_per_step": 4},
-        "gpu_launches": K * launches_per_token(cfg),
-        "prefill": {"value": world * P / (prefill_ms * 1e-3), "unit": "tok/s", "tokens": P, "chunk": chunk},
-        "roofline": {"bound": "hbm", "kernel": "k_gemv_stream", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+        # tensor parallel adds per layer: 2 residual adds, 1 extra quant, 4 NCCL all-gather kernels
+        "gpu_launches": K * (launches_per_token(cfg) + (0 if world == 1 else SHAPES[cfg]["layers"] * 7 + 1)),
+        "prefill": {"value": P / (prefill_ms * 1e-3), "unit": "tok/s", "tokens": P, "chunk": chunk},
+        "roofline": None if achieved is None else
+                    {"bound": "hbm", "kernel": "k_gemv_stream", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                     # DRAM bytes per launch: ncu on the K=5120 x N=17408 W6 launch read+wrote 1.0073x its algorithmic
+                     # bytes (profiles/k_gemv_stream_w6_k5120_n17408.md); scaled to the average launch of the sweep
+                     "traffic": nbytes.value / nlaunch.value * 1.0073,
                      "launches": nlaunch.value, "bytes": nbytes.value, "ms": sweep_ms,
                      "how": "every linear of the model at M=1, 3 passes back to back, CUDA events on the launch queue"},
         "clocks": sampler.summary(windows),
