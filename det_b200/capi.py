@@ -88,6 +88,7 @@ CUDA_ABI = {
     "det_sample": (None, [c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "det_sample_topkp": (None, [c_void_p, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
     "det_sample_scratch_bytes": (c_size_t, [c_int, c_int]),
+    "det_sample_topkp_static": (c_int, [c_void_p, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "det_test_prim": (None, [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "det_linear_repack_bytes": (c_size_t, [c_int, c_int, c_int]),
     "det_linear_repack": (None, [C.POINTER(QLinear), c_void_p, c_void_p]),

@@ -56,6 +56,7 @@ bool runtime_ready() {
     std::call_once(g_once, bring_up);
     return g_rt != nullptr;
 }
+bool runtime_is_up() { return g_rt != nullptr; }
 static Runtime& rt() {
     if (!runtime_ready()) {
         fprintf(stderr, "det_b200: the CUDA runtime could not be initialised\n");

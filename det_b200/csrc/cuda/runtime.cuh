@@ -5,6 +5,7 @@
 
 namespace detb {
 bool runtime_ready();
+bool runtime_is_up();   // true once det_init (or any earlier call) has brought the runtime up; never initialises
 cudaStream_t queue_of(cudaStream_t st);   // maps the ABI's stream 0 onto the library's queue
 int sm_count();
 size_t smem_optin();

@@ -238,6 +238,10 @@ __global__ void __launch_bounds__(ST) k_sample_topkp(const float* __restrict__ l
     if (threadIdx.x == 0) out[blockIdx.x] = r;
 }
 
+// ---- scratch that lives in the library image, for det_sample_topkp_static
+constexpr long long STATIC_SAMPLE_MAX = 1ll << 19;   // M * V weights of 8 bytes: 4 MiB per GPU that loads the library
+static __device__ __align__(256) unsigned long long g_static_weights[STATIC_SAMPLE_MAX];
+
 }  // namespace detb
 
 using namespace detb;
@@ -268,6 +272,67 @@ void det_sample_topkp(const float* logits, int M, int V, float inv_temp, int top
     k_sample_topkp<<<M, ST, 0, queue_of(st)>>>(logits, V, inv_temp, use_k, (u64)(top_k > 0 ? top_k : 0), use_p, p24, z,
                                                 out, static_cast<u64*>(scratch));
     DETB_CUDA_OK(cudaGetLastError());
+}
+
+// Top-k / top-p sampling for callers that must not allocate.  Same result as det_sample_topkp, but the weight buffer is
+// a fixed array inside the library image instead of a caller-provided scratch, and the call itself never reaches an
+// allocator: no cudaMalloc, no cudaFree, nothing that allocates behind the scenes.  That is for hosts that fix their
+// device-memory budget at start-up and ban allocation afterwards (an allocation can stall on the driver lock or fail
+// once the KV cache owns the rest of HBM), and for plug-ins that only ever receive pointers and own no allocator.
+//
+// Limits and rules:
+//   * M * V <= 524288 weights (4 MiB; one row of a 248320-token vocabulary fits twice over).  Larger requests are
+//     refused: the function prints the reason, launches nothing and returns 1.  0 means the work was queued.
+//   * det_init() must have succeeded earlier (this call does not bring the runtime up, since that allocates).
+//   * The first call on a device looks the array's device address up (cudaGetSymbolAddress, with that device current)
+//     and keeps it; make that first call outside any stream capture.
+//   * Every call uses the same array and finds the previous call's weights in it.  Nothing has to be cleared: the kernel
+//     writes every weight of its rows before it reads any.  Two calls that overlap on the GPU (different streams) race
+//     on the array; keep them on one stream or order them yourself.
+int det_sample_topkp_static(const float* logits, int M, int V, float inv_temp, int top_k, float top_p,
+                            const unsigned long long* z, int* out, cudaStream_t st) {
+    if (M <= 0) return 0;
+    if (V <= 0 || (long long)M * V > STATIC_SAMPLE_MAX) {
+        fprintf(stderr, "det_b200: det_sample_topkp_static: M * V = %lld exceeds the built-in scratch of %lld weights\n",
+                (long long)M * V, STATIC_SAMPLE_MAX);
+        return 1;
+    }
+    if (!runtime_is_up()) {
+        fprintf(stderr, "det_b200: det_sample_topkp_static: call det_init() first\n");
+        return 1;
+    }
+    // one address per device: in host code the array's name is only a handle, never a device pointer
+    static unsigned long long* addr[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        fprintf(stderr, "det_b200: det_sample_topkp_static: no current device\n");
+        return 1;
+    }
+    if (!addr[dev]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_weights);
+        if (e != cudaSuccess || !p) {
+            fprintf(stderr, "det_b200: det_sample_topkp_static: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+            return 1;
+        }
+        addr[dev] = static_cast<unsigned long long*>(p);
+    }
+    const int use_k = top_k > 0 && top_k < V;
+    const int use_p = top_p < 1.0f;
+    if (!use_k && !use_p) {
+        k_sample_plain<<<M, ST, 0, queue_of(st)>>>(logits, V, inv_temp, z, out);
+    } else {
+        double pr = __builtin_nearbyint((double)top_p * 16777216.0);
+        const u64 p24 = (pr != pr || pr <= 0.0) ? 0 : (u64)pr;
+        k_sample_topkp<<<M, ST, 0, queue_of(st)>>>(logits, V, inv_temp, use_k, (u64)(top_k > 0 ? top_k : 0), use_p, p24, z,
+                                                    out, addr[dev]);
+    }
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        fprintf(stderr, "det_b200: det_sample_topkp_static: launch failed: %s\n", cudaGetErrorString(e));
+        return 1;
+    }
+    return 0;
 }
 
 }  // extern "C"

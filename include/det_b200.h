@@ -207,6 +207,14 @@ void det_graph_free(void* graph);
  * All pointers are device pointers.                                                                                  */
 void det_token_feedback(const int* pick, int* pos, int* log, int log_base, int log_cap, cudaStream_t st);
 
+/* No counterpart in the reference.  det_sample_topkp for callers that may not allocate device memory: the weight
+ * scratch is a fixed 4 MiB array inside the library (M * V <= 524288), so no scratch argument and no allocation of any
+ * kind inside the call.  Returns 0 when the work was queued, 1 when the request was refused (too large, or det_init was
+ * never called); a refusal prints its reason and launches nothing.  The first call on a device resolves the array's
+ * address and should be made outside stream capture; calls share the array, so calls that overlap on the GPU race.     */
+int det_sample_topkp_static(const float* logits, int M, int V, float inv_temp, int top_k, float top_p,
+                            const unsigned long long* z, int* out, cudaStream_t st);
+
 /* Measurement switch: programmatic dependent launch between the library's kernels on (default, non-zero) or off.
  * Results are identical either way; only the overlap of one kernel's prologue with its predecessor's tail changes.  */
 void det_debug_set_pdl(int on);
