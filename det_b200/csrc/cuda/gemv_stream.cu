@@ -375,6 +375,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
     // Record i of this CTA lands in slot i % slots and belongs to warp i % workers.  slots is a multiple of workers, so
     // a warp meets the phases of each of its slots strictly in order (a parity wait can tell only two phases apart).
     if (warp >= a.workers) return;
+    float sxr[MT];                               // row scales, fetched once (not once per record)
+#pragma unroll
+    for (int t = 0; t < MT; t++) sxr[t] = FUSED ? sxs[t] : (t < a.mt ? a.sx[t] : 0.0f);
     const int lpr = 32 / g.TR;                   // lanes per row
     const int r = lane / lpr, j = lane - r * lpr;
     const int pu = U * 16;
@@ -431,7 +434,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
         if (j == 0 && n < g.N) {
 #pragma unroll
             for (int t = 0; t < MT; t++)
-                if (t < a.mt) emit(a.out, a.t0 + t, n, fmul(fmul(i64_to_f32(acc[t]), cn), FUSED ? sxs[t] : a.sx[t]));
+                if (t < a.mt) emit(a.out, a.t0 + t, n, fmul(fmul(i64_to_f32(acc[t]), cn), sxr[t]));
         }
     }
     if (!ok && lane == 0) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
