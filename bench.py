@@ -217,9 +217,25 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             nid = torch.from_numpy(buf)
         dist.broadcast(nid, 0)
         nid_np = nid.numpy().copy()
-        comm = h.dh_nccl_comm_new(nid_np.ctypes.data, rank, world)
-        if not comm:
-            raise RuntimeError(h.dh_last_error().decode())
+        if args.exchange == "nccl":
+            comm = h.dh_nccl_comm_new(nid_np.ctypes.data, rank, world)
+            if not comm:
+                raise RuntimeError(h.dh_last_error().decode())
+        else:
+            # decode-sized exchanges: one kernel per rank storing into every peer's gathered buffer (CUDA IPC mapped);
+            # prefill chunks (megabytes) stay on NCCL.  The region holds the four gathered buffers of the token loop.
+            mixw = shape["n_h"] * shape["hd"]
+            region = 4 * (chunk * (mixw + shape["ffn"] + shape["hidden"]) + shape["vocab"]) + (1 << 16)
+            comm = h.dh_peer_comm_new(nid_np.ctypes.data, rank, world, region)
+            if not comm:
+                raise RuntimeError(h.dh_last_error().decode())
+            mine = np.zeros(64, np.uint8)
+            h.dh_peer_comm_handle(comm, mine.ctypes.data)
+            every = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
+            dist.all_gather(every, torch.from_numpy(mine))
+            handles = np.concatenate([e.numpy() for e in every]).copy()
+            h.dh_peer_comm_open(comm, handles.ctypes.data)
+            dist.barrier()
     t_load = time.perf_counter()
     model = h.dh_model_new_synth_tp(bk, cfg.encode(), 0, SEED, max_ctx, chunk, comm)
     if not model:
@@ -327,12 +343,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "config": {"workload": f"{cfg}-shape seeded random-init W6 model (W8 head and GDN a/b), batch 1: prefill {P} tokens in "
                                f"{chunk}-token chunks, then greedy decode", "context_at_timing": P + W,
                    "parallelism": "1 GPU" if world == 1 else
-                   f"tp{world}: output-row / head tensor parallel, fp32 slices all-gathered over NCCL (one batch-1 sequence)",
+                   f"tp{world}: output-row / head tensor parallel, one batch-1 sequence; fp32 slices all-gathered " +
+                   ("by NCCL" if args.exchange == "nccl" else
+                    "by one peer-store kernel per rank over NVLink in decode, by NCCL in prefill"),
                    "l2": "weights streamed per token (20 GB at 27B) exceed the 126 MB L2", "seed": SEED,
                    "rot_dim": 64, "rope_theta": 1e7, "eps": 1e-6, "v_scale": 2 ** -10},
         "e2e": {"value": K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": shape["hidden"] * 4,
                 "d2h_bytes_per_step": 4},
-        # tensor parallel adds per layer: 2 residual adds, 1 extra quant, 4 NCCL all-gather kernels
+        # tensor parallel adds per layer: 2 residual adds, 1 extra quant, 4 exchange kernels
         "gpu_launches": K * (launches_per_token(cfg) + (0 if world == 1 else SHAPES[cfg]["layers"] * 7 + 1)),
         "prefill": {"value": P / (prefill_ms * 1e-3), "unit": "tok/s", "tokens": P, "chunk": chunk},
         "roofline": None if achieved is None else
@@ -392,6 +410,8 @@ def main():
     ap.add_argument("--config", default="27b", choices=sorted(SHAPES))
     ap.add_argument("--prefill", type=int, default=2048)
     ap.add_argument("--chunk", type=int, default=512)
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: decode exchanges as one peer-memory kernel per rank (default) or as NCCL all-gathers")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-pdl", action="store_true", help="measurement switch: plain stream-ordered launches")
     args = ap.parse_args()

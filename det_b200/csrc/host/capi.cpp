@@ -83,6 +83,20 @@ void* dh_nccl_comm_new(const uint8_t* id128, int rank, int size) {
         return nullptr;
     }
 }
+// One-kernel exchanges over NVLink peer memory for up to 8 rows, NCCL (id128, may be null: none) above that.
+// Collective set-up: new on every rank, exchange the 64-byte handles, open with all of them in rank order.
+void* dh_peer_comm_new(const uint8_t* id128, int rank, int size, size_t region_bytes) {
+    try {
+        std::unique_ptr<det::Comm> bulk;
+        if (id128) bulk = std::make_unique<det::NcclComm>(id128, rank, size);
+        return static_cast<det::Comm*>(new det::PeerComm(rank, size, region_bytes, std::move(bulk)));
+    } catch (const std::exception& ex) {
+        g_err = ex.what();
+        return nullptr;
+    }
+}
+void dh_peer_comm_handle(void* c, uint8_t* out64) { static_cast<det::PeerComm*>(static_cast<det::Comm*>(c))->handle(out64); }
+void dh_peer_comm_open(void* c, const uint8_t* handles) { static_cast<det::PeerComm*>(static_cast<det::Comm*>(c))->open(handles); }
 // gather(local, gathered, bytes): fills gathered[size][bytes] with every rank's block (host memory).
 void* dh_callback_comm_new(int rank, int size, void (*gather)(const void*, void*, size_t)) {
     return static_cast<det::Comm*>(new det::CallbackComm(rank, size, gather));

@@ -4,6 +4,7 @@
 // and needs the whole row.  One primitive covers all of it.
 #pragma once
 #include "backend.hpp"
+#include <memory>
 
 namespace det {
 
@@ -15,6 +16,9 @@ class Comm {
     // `tmp` holds size * m * slice floats of scratch.
     virtual void all_gather(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full,
                             size_t m, size_t slice) = 0;
+    // Storage for a gathered buffer (`full` above).  An exchange that writes straight into its peers' gathered buffers
+    // hands out pieces of its own shared region here; the default is ordinary backend memory.
+    virtual Buf<float> alloc_gathered(Backend& bk, size_t n) { return bk.alloc<float>(n); }
 };
 
 // Host-memory exchange through a caller-supplied function (tests run it over torch.distributed / gloo):
@@ -51,6 +55,30 @@ class NcclComm : public Comm {
 
   private:
     void* comm_ = nullptr;
+};
+
+// Decode-sized exchanges as ONE kernel per rank over NVLink peer memory (det_xchg_* of the C ABI): the local slice is
+// stored directly into every rank's gathered buffer, then a flag handshake.  Exchanges of more than `small_rows` rows
+// (prefill chunks: megabytes, bandwidth-bound) go through the NCCL communicator given at construction.
+// Set-up is collective: construct on every rank, pass every rank's handle() to open() in rank order.
+class PeerComm : public Comm {
+  public:
+    PeerComm(int rank_, int size_, size_t region_bytes, std::unique_ptr<Comm> bulk);
+    ~PeerComm() override;
+    void handle(uint8_t out[64]) const;
+    void open(const uint8_t* handles);
+    void all_gather(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full, size_t m,
+                    size_t slice) override;
+    Buf<float> alloc_gathered(Backend& bk, size_t n) override;
+    size_t small_rows = 8;
+
+  private:
+    void* x_ = nullptr;
+    uint8_t* base_ = nullptr;
+    size_t bytes_ = 0, used_ = 0;
+    const float* last_full_ = nullptr;
+    std::unique_ptr<Comm> bulk_;
+    bool opened_ = false;
 };
 
 }  // namespace det

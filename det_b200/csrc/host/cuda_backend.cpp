@@ -327,8 +327,7 @@ GemvSweep gemv_sweep(Model& m, int reps) {
     GemvSweep r{0, 0};
     CudaBackend* bk = dynamic_cast<CudaBackend*>(m.backend);
     if (!bk) throw std::runtime_error("gemv_sweep needs the CUDA backend");
-    size_t nmax = m.cfg.vocab;
-    Buf<float> y = bk->alloc<float>(nmax);
+    const Buf<float>& y = m.w.logits;   // widest output of any linear; nothing is allocated or freed in here
     auto run = [&](const Proj& p, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx) {
         for (const auto& lin : p.lins) {
             bk->gemm(*lin, xq, sx, mx, 1, GemmOut::write(y));
@@ -352,7 +351,7 @@ GemvSweep gemv_sweep(Model& m, int reps) {
         }
         run(m.lm_head, m.w.xq, m.w.sx, m.w.mx);
     }
-    bk->sync();
+    bk->flush();
     return r;
 }
 

@@ -101,8 +101,8 @@ struct GemvSweep {
     size_t bytes;      // algorithmic bytes moved: weights + scales + activations in + outputs
     size_t launches;
 };
-// Issues the GEMV of every linear of the model at M = 1 (one decoded token's worth), `reps` times; no sync inside the
-// loop, one at the end.  The caller brackets it with events to get the GEMV-only rate.
+// Issues the GEMV of every linear of the model at M = 1 (one decoded token's worth), `reps` times, into the model's
+// logits buffer; no allocation and no sync inside.  The caller brackets it with events to get the GEMV-only rate.
 GemvSweep gemv_sweep(Model& m, int reps);
 
 }  // namespace det

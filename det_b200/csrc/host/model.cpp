@@ -365,12 +365,12 @@ static void load_shard(Model& m, const Config& cfg, uint64_t seed, Backend* bk, 
     w.hq = bk->alloc<int8_t>(mb * inter);
     w.sh = bk->alloc<float>(mb);
     w.mh = bk->alloc<uint16_t>(mb * inter / 128);
-    w.logits = bk->alloc<float>(cfg.vocab);
-    tp.mix_full = bk->alloc<float>(mb * mix);
+    w.logits = m.comm->alloc_gathered(*bk, cfg.vocab);
+    tp.mix_full = m.comm->alloc_gathered(*bk, mb * mix);
     tp.h_l = bk->alloc<float>(mb * tp.ffn);
-    tp.h_full = bk->alloc<float>(mb * inter);
+    tp.h_full = m.comm->alloc_gathered(*bk, mb * inter);
     tp.y_l = bk->alloc<float>(mb * tp.hid);
-    tp.y_full = bk->alloc<float>(mb * h);
+    tp.y_full = m.comm->alloc_gathered(*bk, mb * h);
     tp.logits_l = bk->alloc<float>(mb * tp.voc);
     tp.tmp = bk->alloc<float>(std::max(mb * std::max(inter, mix), cfg.vocab));
 }

@@ -69,4 +69,46 @@ void NcclComm::all_gather(Backend& bk, const Buf<float>& local, const Buf<float>
     if (m > 1) det_unshard(tmp.ptr(), full.ptr(), size, (int)m, (int)slice, nullptr);
 }
 
+// ---- PeerComm
+
+PeerComm::PeerComm(int rank_, int size_, size_t region_bytes, std::unique_ptr<Comm> bulk) : bulk_(std::move(bulk)) {
+    rank = rank_;
+    size = size_;
+    x_ = det_xchg_create(region_bytes, rank_, size_);
+    base_ = static_cast<uint8_t*>(det_xchg_base(x_));
+    bytes_ = det_xchg_bytes(x_);
+}
+PeerComm::~PeerComm() {
+    if (x_) det_xchg_destroy(x_);
+}
+void PeerComm::handle(uint8_t out[64]) const { det_xchg_ipc_handle(x_, out); }
+void PeerComm::open(const uint8_t* handles) {
+    det_xchg_open(x_, handles);
+    opened_ = true;
+}
+Buf<float> PeerComm::alloc_gathered(Backend&, size_t n) {
+    const size_t need = (n * sizeof(float) + 255) & ~(size_t)255;
+    if (used_ + need > bytes_) throw std::runtime_error("exchange region too small for the gathered buffers");
+    float* p = reinterpret_cast<float*>(base_ + used_);
+    used_ += need;
+    return Buf<float>::view(p, n);
+}
+void PeerComm::all_gather(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full, size_t m,
+                          size_t slice) {
+    const uint8_t* f = reinterpret_cast<const uint8_t*>(full.ptr());
+    const bool inside = f >= base_ && f + m * size * slice * sizeof(float) <= base_ + bytes_;
+    if (m > small_rows || !inside || slice % 4 != 0) {
+        if (!bulk_) throw std::runtime_error("exchange too large for the peer path and no bulk communicator given");
+        last_full_ = nullptr;
+        bulk_->all_gather(bk, local, tmp, full, m, slice);
+        return;
+    }
+    if (!opened_) throw std::runtime_error("PeerComm::open has not run");
+    // a rank may still be reading the result of the previous exchange when this one starts: never the same buffer twice in a row
+    if (last_full_ == full.ptr()) throw std::runtime_error("two consecutive exchanges into the same gathered buffer");
+    last_full_ = full.ptr();
+    bk.flush();
+    det_xchg_all_gather(x_, local.ptr(), (size_t)(f - base_), (int)m, (int)slice, nullptr);
+}
+
 }  // namespace det

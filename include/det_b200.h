@@ -207,6 +207,20 @@ void det_graph_free(void* graph);
  * All pointers are device pointers.                                                                                  */
 void det_token_feedback(const int* pick, int* pos, int* log, int log_base, int log_cap, cudaStream_t st);
 
+/* Tensor-parallel exchange over NVLink peer memory (no reference counterpart: the reference is single-device).  Every
+ * rank creates a region of the same size, publishes its CUDA IPC handle (64 bytes), opens the others', and places its
+ * gathered buffers at the same offsets inside the region.  det_xchg_all_gather stores local[M][slice] into column block
+ * `rank` of the gathered [M][size*slice] buffer on EVERY rank with peer stores, then waits (bounded) until all ranks have
+ * done the same.  Consecutive exchanges must target different gathered buffers.  One launch, no host involvement; it can
+ * be captured into the decode graph.                                                                                 */
+void* det_xchg_create(size_t bytes, int rank, int size);
+void det_xchg_ipc_handle(void* h, uint8_t out[64]);
+void det_xchg_open(void* h, const uint8_t* handles /* size x 64 bytes */);
+void* det_xchg_base(void* h);
+size_t det_xchg_bytes(void* h);
+void det_xchg_all_gather(void* h, const float* local, size_t full_off, int M, int slice, cudaStream_t st);
+void det_xchg_destroy(void* h);
+
 /* No counterpart in the reference.  det_sample_topkp for callers that may not allocate device memory: the weight
  * scratch is a fixed 4 MiB array inside the library (M * V <= 524288), so no scratch argument and no allocation of any
  * kind inside the call.  Returns 0 when the work was queued, 1 when the request was refused (too large, or det_init was
