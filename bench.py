@@ -222,11 +222,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             if not comm:
                 raise RuntimeError(h.dh_last_error().decode())
         else:
-            # decode-sized exchanges: one kernel per rank storing into every peer's gathered buffer (CUDA IPC mapped);
-            # prefill chunks (megabytes) stay on NCCL.  The region holds the four gathered buffers of the token loop.
+            # decode-sized exchanges: one kernel per rank storing packets into every peer's staging (CUDA IPC mapped);
+            # prefill chunks (megabytes) stay on NCCL.  16 staging bytes per gathered value of the largest exchange.
             mixw = shape["n_h"] * shape["hd"]
-            region = 4 * (chunk * (mixw + shape["ffn"] + shape["hidden"]) + shape["vocab"]) + (1 << 16)
-            comm = h.dh_peer_comm_new(nid_np.ctypes.data, rank, world, region)
+            staging = 16 * max(8 * max(mixw, shape["ffn"], shape["hidden"]), shape["vocab"]) + 4096
+            comm = h.dh_peer_comm_new(nid_np.ctypes.data, rank, world, staging)
             if not comm:
                 raise RuntimeError(h.dh_last_error().decode())
             mine = np.zeros(64, np.uint8)
@@ -235,7 +235,18 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             dist.all_gather(every, torch.from_numpy(mine))
             handles = np.concatenate([e.numpy() for e in every]).copy()
             h.dh_peer_comm_open(comm, handles.ctypes.data)
+            if args.exchange == "peer-unfused":
+                h.dh_peer_comm_set_fuse(comm, 0)
             dist.barrier()
+    if world == 1 and args.emulate_tp > 1:
+        # timing aid: this process runs the launch sequence of rank 0 of an N-way shard with every exchange looped back
+        # to its own memory (no peer latency, meaningless values): what one rank costs without waiting for the others
+        mixw = shape["n_h"] * shape["hd"]
+        staging = 16 * max(chunk * max(mixw, shape["ffn"], shape["hidden"]), shape["vocab"]) + 4096
+        comm = h.dh_peer_comm_new(None, 0, args.emulate_tp, staging)
+        if not comm:
+            raise RuntimeError(h.dh_last_error().decode())
+        h.dh_peer_comm_open_loopback(comm)
     t_load = time.perf_counter()
     model = h.dh_model_new_synth_tp(bk, cfg.encode(), 0, SEED, max_ctx, chunk, comm)
     if not model:
@@ -262,6 +273,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # ---- prefill (P tokens in `chunk`-token batches), timed for the secondary metric
     ids = _prompt(h, P, shape["vocab"])
+    # warm-up: one chunk through every prefill kernel and exchange (first-use set-up of descriptors and of the NCCL
+    # channels is not part of the rate), then back to an empty context
+    _check(h.dh_model_prefill(model, ids.ctypes.data, min(P, chunk)), h)
+    _check(h.dh_model_reset(model), h)
     barrier()
     w0 = time.time()
     a = ev.record()
@@ -314,7 +329,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # ---- the decode GEMV alone: every linear of the model at M = 1 (one token's GEMVs), weights 20 GB >> L2
     nbytes, nlaunch, sweep_ms = C.c_size_t(0), C.c_size_t(0), None
-    if world == 1:
+    if world == 1 and args.emulate_tp <= 1:
         _check(h.dh_gemv_sweep(model, 1, C.byref(nbytes), C.byref(nlaunch)), h)
         reps = 3
         barrier()
@@ -342,7 +357,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "dtype": "int8 x W6 -> int64 (fp32 glue)", "data": "synthetic",
         "config": {"workload": f"{cfg}-shape seeded random-init W6 model (W8 head and GDN a/b), batch 1: prefill {P} tokens in "
                                f"{chunk}-token chunks, then greedy decode", "context_at_timing": P + W,
-                   "parallelism": "1 GPU" if world == 1 else
+                   "parallelism": (f"EMULATED rank 0 of tp{args.emulate_tp}, exchanges looped back: not a result"
+                                   if args.emulate_tp > 1 else "1 GPU") if world == 1 else
                    f"tp{world}: output-row / head tensor parallel, one batch-1 sequence; fp32 slices all-gathered " +
                    ("by NCCL" if args.exchange == "nccl" else
                     "by one peer-store kernel per rank over NVLink in decode, by NCCL in prefill"),
@@ -410,8 +426,10 @@ def main():
     ap.add_argument("--config", default="27b", choices=sorted(SHAPES))
     ap.add_argument("--prefill", type=int, default=2048)
     ap.add_argument("--chunk", type=int, default=512)
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+    ap.add_argument("--exchange", default="peer", choices=["peer", "peer-unfused", "nccl"],
                     help="N > 1: decode exchanges as one peer-memory kernel per rank (default) or as NCCL all-gathers")
+    ap.add_argument("--emulate-tp", type=int, default=0,
+                    help="timing aid at N = 1: run rank 0 of a P-way shard with exchanges looped back (values meaningless)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-pdl", action="store_true", help="measurement switch: plain stream-ordered launches")
     args = ap.parse_args()

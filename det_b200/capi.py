@@ -106,10 +106,13 @@ CUDA_ABI = {
     "det_xchg_create": (c_void_p, [c_size_t, c_int, c_int]),
     "det_xchg_ipc_handle": (None, [c_void_p, c_void_p]),
     "det_xchg_open": (None, [c_void_p, c_void_p]),
-    "det_xchg_base": (c_void_p, [c_void_p]),
-    "det_xchg_bytes": (c_size_t, [c_void_p]),
-    "det_xchg_all_gather": (None, [c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p]),
+    "det_xchg_open_loopback": (None, [c_void_p]),
+    "det_xchg_capacity": (c_size_t, [c_void_p]),
+    "det_xchg_all_gather": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "det_xchg_destroy": (None, [c_void_p]),
+    "det_xchg_add_rmsnorm_quant": (None, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int,
+                                          c_void_p, c_void_p, c_void_p, c_void_p]),
+    "det_xchg_quant": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "det_debug_set_pdl": (None, [c_int]),
     "det_last_error": (c_int, []),
 }
@@ -128,6 +131,8 @@ HOST_API = {
     "dh_peer_comm_new": (c_void_p, [c_void_p, c_int, c_int, c_size_t]),
     "dh_peer_comm_handle": (None, [c_void_p, c_void_p]),
     "dh_peer_comm_open": (None, [c_void_p, c_void_p]),
+    "dh_peer_comm_set_fuse": (None, [c_void_p, c_int]),
+    "dh_peer_comm_open_loopback": (None, [c_void_p]),
     "dh_comm_free": (None, [c_void_p]),
     "dh_model_new_synth_tp": (c_void_p, [c_void_p, c_char_p, c_size_t, c_u64, c_size_t, c_size_t, c_void_p]),
     "dh_model_free": (None, [c_void_p]),

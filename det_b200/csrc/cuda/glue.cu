@@ -5,7 +5,7 @@
 // A row is spread over a thread-block cluster (up to 8 CTAs, one warp per 128-wide slice) so that a single decode row
 // of 5120 or 17408 values is not a one-SM job; the row-wide sum of squares (the spec tree, docs/SPEC.md §1.3) and the
 // row-wide maximum are combined through distributed shared memory.
-#include "runtime.cuh"
+#include "exchange.cuh"
 #include <cooperative_groups.h>
 
 namespace cg = cooperative_groups;
@@ -23,6 +23,7 @@ struct RowArgs {
     int8_t* q;          // optional codes
     float* sx;
     uint16_t* mx;       // NULL: per-row int8 (quant_act_i8)
+    float* acc;         // optional (rmsnorm, plain): the row is acc + a, and acc is updated to it (residual add)
 };
 
 __device__ __forceinline__ float max_block_rt(float v, float* sh, int nw) {
@@ -47,14 +48,23 @@ __device__ __forceinline__ float* peer_smem(float* local, unsigned rank) {
     return cg::this_cluster().map_shared_rank(local, rank);
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(1024) k_row(RowArgs p, int spc /* slices per CTA */, int pslices /* P / 128 */) {
+// XCHG: the rows come out of the tensor-parallel exchange, which is this kernel's prologue: every CTA of the grid sends its
+// share of the local slice to all ranks, then each lane polls the staging packets that hold its four values (the grid is
+// at most 8 CTAs per row and 8 rows, all resident).  p.a is unused.
+template <int MODE, bool XCHG>
+__global__ void __launch_bounds__(1024) k_row(RowArgs p, int spc /* slices per CTA */, int pslices /* P / 128 */,
+                                              const XchgArgs xa) {
     __shared__ float slice_sum[32];     // this CTA's slice sums (read by the peers)
     __shared__ float cta_max;           // this CTA's largest group scale (read by the peers)
     __shared__ float all_sums[MAX_SLICES];
     __shared__ float shf[32];
     pdl_trigger();
     pdl_wait();
+    unsigned seq = 0;
+    if (XCHG) {
+        seq = xchg_seq(xa);
+        xchg_push(xa, seq);
+    }
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned rank = cluster.block_rank(), cs = cluster.num_blocks();
     const int row = blockIdx.y;
@@ -69,9 +79,21 @@ __global__ void __launch_bounds__(1024) k_row(RowArgs p, int spc /* slices per C
 
     float raw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (have) {
+        if (XCHG) {   // n is a multiple of 128 here
+            const size_t pk = ((size_t)row * n + base) >> 1;
+            const float2 lo = xchg_read(xa, seq, pk), hi = xchg_read(xa, seq, pk + 1);
+            raw[0] = lo.x; raw[1] = lo.y; raw[2] = hi.x; raw[3] = hi.y;
+        } else {
 #pragma unroll
-        for (int e = 0; e < 4; e++)
-            if (base + e < n) raw[e] = a[base + e];
+            for (int e = 0; e < 4; e++)
+                if (base + e < n) raw[e] = a[base + e];
+        }
+        if (MODE != ROW_SWIGLU && p.acc) {
+            float* acc = p.acc + (size_t)row * n;
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                if (base + e < n) acc[base + e] = raw[e] = fadd(acc[base + e], raw[e]);
+        }
     }
     float inv_rms = 0.0f;
     if (MODE == ROW_RMSNORM) {
@@ -171,8 +193,8 @@ __global__ void __launch_bounds__(1024) k_row(RowArgs p, int spc /* slices per C
     }
 }
 
-template <int MODE>
-static void launch_row(const RowArgs& p, int M, cudaStream_t q) {
+template <int MODE, bool XCHG = false>
+static void launch_row(const RowArgs& p, int M, cudaStream_t q, const XchgArgs* xa = nullptr) {
     const int n = p.n;
     DETB_REQUIRE(n >= 1 && n <= 32768, "row length must be 1..32768");
     if (p.q && p.mx) DETB_REQUIRE(n % 128 == 0, "grouped quantization needs n % 128 == 0");
@@ -183,7 +205,9 @@ static void launch_row(const RowArgs& p, int M, cudaStream_t q) {
     int cs = 8;                                   // cluster size: by shape only
     while (cs > 1 && slices / cs < 4) cs >>= 1;
     const int spc = (slices + cs - 1) / cs;       // <= 32
-    launch_pdl(k_row<MODE>, dim3(cs, M, 1), dim3(spc * 32, 1, 1), 0, q, cs, p, spc, P / 128);
+    if (XCHG) DETB_REQUIRE(cs * M <= 64 && spc * 32 >= XCHG_MAX_RANKS, "fused exchange: at most 8 rows");
+    launch_pdl(k_row<MODE, XCHG>, dim3(cs, M, 1), dim3(spc * 32, 1, 1), 0, q, cs, p, spc, P / 128,
+               xa ? *xa : XchgArgs{});
 }
 
 // ---- embedding rows (bf16 table -> fp32, exact), residual add, argmax
@@ -260,19 +284,44 @@ extern "C" {
 void det_rmsnorm_quant(const float* x, const float* w, float eps, int M, int n, float* y, int8_t* xq, float* sx,
                        uint16_t* mx, cudaStream_t st) {
     if (M <= 0) return;
-    RowArgs p{x, w, eps, n, y, xq, sx, mx};
+    RowArgs p{x, w, eps, n, y, xq, sx, mx, nullptr};
     launch_row<ROW_RMSNORM>(p, M, queue_of(st));
 }
 void det_quant(const float* x, int M, int n, int8_t* xq, float* sx, uint16_t* mx, cudaStream_t st) {
     if (M <= 0) return;
-    RowArgs p{x, nullptr, 0.0f, n, nullptr, xq, sx, mx};
+    RowArgs p{x, nullptr, 0.0f, n, nullptr, xq, sx, mx, nullptr};
     launch_row<ROW_PLAIN>(p, M, queue_of(st));
 }
 void det_silu_mul_quant(const float* g, const float* u, int M, int n, float* h, int8_t* hq, float* sh, uint16_t* mh,
                         cudaStream_t st) {
     if (M <= 0) return;
-    RowArgs p{g, u, 0.0f, n, h, hq, sh, mh};
+    RowArgs p{g, u, 0.0f, n, h, hq, sh, mh, nullptr};
     launch_row<ROW_SWIGLU>(p, M, queue_of(st));
+}
+// ---- tensor-parallel decode: the exchange that produces a gathered row, and the row operation that consumes it, as
+// one launch; n = size * slice.   x[M][n] += gathered; then det_rmsnorm_quant of x.
+static void check_fused(const Xchg* xc, int M, int slice) {
+    DETB_REQUIRE(M >= 1 && M <= 8 && slice % 2 == 0 && (slice * xc->size) % 128 == 0,
+                 "fused exchange: 1..8 rows of whole 128-value groups");
+    DETB_REQUIRE((size_t)M * xc->size * slice * 8 <= xc->slot_bytes, "exchange larger than the staging slot");
+}
+void det_xchg_add_rmsnorm_quant(void* h, const float* local, int slice, float* x, const float* w, float eps, int M,
+                                int8_t* xq, float* sx, uint16_t* mx, cudaStream_t st) {
+    const Xchg* xc = static_cast<const Xchg*>(h);
+    check_fused(xc, M, slice);
+    const XchgArgs xa = xchg_args(xc, local, nullptr, M, slice);
+    RowArgs p{nullptr, w, eps, slice * xc->size, nullptr, xq, sx, mx, x};
+    launch_row<ROW_RMSNORM, true>(p, M, queue_of(st), &xa);
+}
+// det_quant of the gathered rows; with local_b the sent values are silu(local) * local_b (det_silu_mul_quant's product
+// over this rank's columns), so SwiGLU + exchange + quantization are one launch.
+void det_xchg_quant(void* h, const float* local, const float* local_b, int slice, int M, int8_t* xq, float* sx,
+                    uint16_t* mx, cudaStream_t st) {
+    const Xchg* xc = static_cast<const Xchg*>(h);
+    check_fused(xc, M, slice);
+    const XchgArgs xa = xchg_args(xc, local, local_b, M, slice);
+    RowArgs p{nullptr, nullptr, 0.0f, slice * xc->size, nullptr, xq, sx, mx, nullptr};
+    launch_row<ROW_PLAIN, true>(p, M, queue_of(st), &xa);
 }
 void det_embed(const uint16_t* table_bf16, const int* ids, int M, int H, float* x, cudaStream_t st) {
     if (M <= 0) return;

@@ -16,9 +16,30 @@ class Comm {
     // `tmp` holds size * m * slice floats of scratch.
     virtual void all_gather(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full,
                             size_t m, size_t slice) = 0;
-    // Storage for a gathered buffer (`full` above).  An exchange that writes straight into its peers' gathered buffers
-    // hands out pieces of its own shared region here; the default is ordinary backend memory.
-    virtual Buf<float> alloc_gathered(Backend& bk, size_t n) { return bk.alloc<float>(n); }
+
+    // The three exchange-plus-consumer steps of the sharded token loop.  The defaults spell them out op by op; an
+    // exchange that can run them as one launch overrides them (same values either way).
+    // x[t][size*slice] += gather(y_l); rmsnorm_quant(x, w) -> q, s, mm
+    virtual void gather_add_norm_quant(Backend& bk, const Buf<float>& y_l, const Buf<float>& tmp, const Buf<float>& y_full,
+                                       size_t t, size_t slice, const Buf<float>& x, const Buf<float>& w, float eps,
+                                       const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
+        all_gather(bk, y_l, tmp, y_full, t, slice);
+        bk.add(x, y_full, t * slice * size);
+        bk.rmsnorm_quant(x, w, eps, t, slice * size, q, s, mm);
+    }
+    // quant(gather(local)) -> q, s, mm
+    virtual void gather_quant(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full, size_t t,
+                              size_t slice, const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
+        all_gather(bk, local, tmp, full, t, slice);
+        bk.quant(full, t, slice * size, q, s, mm);
+    }
+    // h_l = silu(g) * u over the local columns; quant(gather(h_l)) -> q, s, mm
+    virtual void silu_gather_quant(Backend& bk, const Buf<float>& g, const Buf<float>& u, const Buf<float>& h_l,
+                                   const Buf<float>& tmp, const Buf<float>& h_full, size_t t, size_t slice,
+                                   const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
+        bk.silu_mul(g, u, t, slice, h_l);
+        gather_quant(bk, h_l, tmp, h_full, t, slice, q, s, mm);
+    }
 };
 
 // Host-memory exchange through a caller-supplied function (tests run it over torch.distributed / gloo):
@@ -58,25 +79,33 @@ class NcclComm : public Comm {
 };
 
 // Decode-sized exchanges as ONE kernel per rank over NVLink peer memory (det_xchg_* of the C ABI): the local slice is
-// stored directly into every rank's gathered buffer, then a flag handshake.  Exchanges of more than `small_rows` rows
+// stored into every rank's staging area as self-validating packets.  Exchanges of more than `small_rows` rows
 // (prefill chunks: megabytes, bandwidth-bound) go through the NCCL communicator given at construction.
 // Set-up is collective: construct on every rank, pass every rank's handle() to open() in rank order.
 class PeerComm : public Comm {
   public:
-    PeerComm(int rank_, int size_, size_t region_bytes, std::unique_ptr<Comm> bulk);
+    PeerComm(int rank_, int size_, size_t staging_bytes, std::unique_ptr<Comm> bulk);
     ~PeerComm() override;
     void handle(uint8_t out[64]) const;
     void open(const uint8_t* handles);
+    void open_loopback();   // timing aid: one process runs the launch sequence of one rank (values meaningless)
     void all_gather(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full, size_t m,
                     size_t slice) override;
-    Buf<float> alloc_gathered(Backend& bk, size_t n) override;
+    void gather_add_norm_quant(Backend& bk, const Buf<float>& y_l, const Buf<float>& tmp, const Buf<float>& y_full, size_t t,
+                               size_t slice, const Buf<float>& x, const Buf<float>& w, float eps, const Buf<int8_t>& q,
+                               const Buf<float>& s, const Buf<uint16_t>& mm) override;
+    void gather_quant(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full, size_t t,
+                      size_t slice, const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) override;
+    void silu_gather_quant(Backend& bk, const Buf<float>& g, const Buf<float>& u, const Buf<float>& h_l,
+                           const Buf<float>& tmp, const Buf<float>& h_full, size_t t, size_t slice, const Buf<int8_t>& q,
+                           const Buf<float>& s, const Buf<uint16_t>& mm) override;
     size_t small_rows = 8;
+    bool fuse = true;   // run exchange + consumer as one launch (measurement switch; results are the same)
 
   private:
+    bool small(size_t t, size_t slice) const;   // the exchange fits the staging and is decode-sized
     void* x_ = nullptr;
-    uint8_t* base_ = nullptr;
-    size_t bytes_ = 0, used_ = 0;
-    const float* last_full_ = nullptr;
+    size_t capacity_ = 0;
     std::unique_ptr<Comm> bulk_;
     bool opened_ = false;
 };

@@ -63,7 +63,7 @@ std::unique_ptr<Model> Model::load_synthetic(const Config& cfg, uint64_t seed, B
     m.max_batch = max_batch;
     const size_t h = cfg.hidden, inter = cfg.intermediate;
     const size_t n_h = cfg.n_heads, n_kv = cfg.n_kv, hd = cfg.head_dim;
-    const size_t n_k = cfg.gdn_k_heads, n_v = cfg.gdn_v_heads, dk = cfg.gdn_dk, dv = cfg.gdn_dv;
+    const size_t n_v = cfg.gdn_v_heads, dk = cfg.gdn_dk, dv = cfg.gdn_dv;
     const size_t conv_dim = cfg.conv_dim();
     const int wb = cfg.bits_default;
 
@@ -365,12 +365,12 @@ static void load_shard(Model& m, const Config& cfg, uint64_t seed, Backend* bk, 
     w.hq = bk->alloc<int8_t>(mb * inter);
     w.sh = bk->alloc<float>(mb);
     w.mh = bk->alloc<uint16_t>(mb * inter / 128);
-    w.logits = m.comm->alloc_gathered(*bk, cfg.vocab);
-    tp.mix_full = m.comm->alloc_gathered(*bk, mb * mix);
+    w.logits = bk->alloc<float>(cfg.vocab);
+    tp.mix_full = bk->alloc<float>(mb * mix);
     tp.h_l = bk->alloc<float>(mb * tp.ffn);
-    tp.h_full = m.comm->alloc_gathered(*bk, mb * inter);
+    tp.h_full = bk->alloc<float>(mb * inter);
     tp.y_l = bk->alloc<float>(mb * tp.hid);
-    tp.y_full = m.comm->alloc_gathered(*bk, mb * h);
+    tp.y_full = bk->alloc<float>(mb * h);
     tp.logits_l = bk->alloc<float>(mb * tp.voc);
     tp.tmp = bk->alloc<float>(std::max(mb * std::max(inter, mix), cfg.vocab));
 }
@@ -379,24 +379,26 @@ void Model::network_tp(size_t pos0, size_t t) {
     const Config& c = cfg;
     Backend* bk = backend;
     const size_t h = c.hidden, P = (size_t)comm->size;
-    const size_t mix = c.n_heads * c.head_dim;
-    // y_l holds this rank's rows of a projection back to the hidden size: gather the rows, then x += y on every rank
-    auto reduce_into_x = [&](const Linear& lin, const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
+    // A projection back to the hidden size leaves this rank's rows in y_l; the exchange, the residual add and the
+    // RMSNorm + quantization that follows are one step of the communicator (one launch on the peer-memory exchange).
+    auto project_back = [&](const Linear& lin, const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
         bk->gemm(lin, q, s, mm, t, GemmOut::write(tp.y_l));
-        comm->all_gather(*bk, tp.y_l, tp.tmp, tp.y_full, t, tp.hid);
-        bk->add(w.x, tp.y_full, t * h);
     };
+    auto add_norm_quant = [&](const Buf<float>& norm_w) {
+        comm->gather_add_norm_quant(*bk, tp.y_l, tp.tmp, tp.y_full, t, tp.hid, w.x, norm_w, c.eps, w.xq, w.sx, w.mx);
+    };
+    bool pending = false;   // y_l of the previous layer's down projection has not been added to x yet
     for (Layer& l : layers) {
-        bk->rmsnorm_quant(w.x, l.attn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
+        if (pending) add_norm_quant(l.attn_norm);
+        else bk->rmsnorm_quant(w.x, l.attn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
         if (l.is_attn) {
             Attn& a = l.attn;
             project(a.qkv, w.xq, w.sx, w.mx, t, {&w.qg, &w.k, &w.v});
             AttnLayer layer{&a.q_norm, &a.k_norm, &a.v_scale, &a.v_inv_scale, &rope_cos, &rope_sin};
             Shape shape{t, pos0, tp.heads, tp.kv, c.head_dim, c.rot_dim, c.eps};
             bk->attention(layer, a.kv, shape, w.qg, w.k, w.v, w.o);
-            comm->all_gather(*bk, w.o, tp.tmp, tp.mix_full, t, tp.heads * c.head_dim);
-            bk->quant(tp.mix_full, t, mix, w.oq, w.so, w.mo);
-            reduce_into_x(*a.o.lins[0], w.oq, w.so, w.mo);
+            comm->gather_quant(*bk, w.o, tp.tmp, tp.mix_full, t, tp.heads * c.head_dim, w.oq, w.so, w.mo);
+            project_back(*a.o.lins[0], w.oq, w.so, w.mo);
         } else {
             Gdn& g = l.gdn;
             project(g.qkvz, w.xq, w.sx, w.mx, t, {&w.qkv, &w.z});
@@ -404,21 +406,24 @@ void Model::network_tp(size_t pos0, size_t t) {
             GdnLayer layer{&g.conv, &g.a, &g.dt_bias, &g.norm};
             GdnShape shape{t, tp.k_heads, tp.v_heads, c.gdn_dk, c.gdn_dv, c.eps};
             bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.o, GdnExport{});
-            comm->all_gather(*bk, w.o, tp.tmp, tp.mix_full, t, tp.v_heads * c.gdn_dv);
-            bk->quant(tp.mix_full, t, mix, w.oq, w.so, w.mo);
-            reduce_into_x(*g.out.lins[0], w.oq, w.so, w.mo);
+            comm->gather_quant(*bk, w.o, tp.tmp, tp.mix_full, t, tp.v_heads * c.gdn_dv, w.oq, w.so, w.mo);
+            project_back(*g.out.lins[0], w.oq, w.so, w.mo);
         }
-        bk->rmsnorm_quant(w.x, l.ffn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
+        add_norm_quant(l.ffn_norm);
         project(l.gu, w.xq, w.sx, w.mx, t, {&w.g, &w.u});
-        bk->silu_mul(w.g, w.u, t, tp.ffn, tp.h_l);
-        comm->all_gather(*bk, tp.h_l, tp.tmp, tp.h_full, t, tp.ffn);
-        bk->quant(tp.h_full, t, c.intermediate, w.hq, w.sh, w.mh);
-        reduce_into_x(*l.down.lins[0], w.hq, w.sh, w.mh);
+        comm->silu_gather_quant(*bk, w.g, w.u, tp.h_l, tp.tmp, tp.h_full, t, tp.ffn, w.hq, w.sh, w.mh);
+        project_back(*l.down.lins[0], w.hq, w.sh, w.mh);
+        pending = true;
     }
     const size_t rows = all_logits ? t : 1;
-    if (all_logits) {
-        bk->rmsnorm_quant(w.x, final_norm, c.eps, t, h, w.xq, w.sx, w.mx);
+    if (all_logits || t == 1) {
+        if (pending) add_norm_quant(final_norm);
+        else bk->rmsnorm_quant(w.x, final_norm, c.eps, t, h, w.xq, w.sx, w.mx);
     } else {
+        if (pending) {
+            comm->all_gather(*bk, tp.y_l, tp.tmp, tp.y_full, t, tp.hid);
+            bk->add(w.x, tp.y_full, t * h);
+        }
         Buf<float> last = Buf<float>::view(w.x.ptr_at((t - 1) * h), h);
         bk->rmsnorm_quant(last, final_norm, c.eps, 1, h, w.xq, w.sx, w.mx);
     }

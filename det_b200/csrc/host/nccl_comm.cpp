@@ -4,6 +4,7 @@
 #include "cuda_backend.hpp"
 #include <dlfcn.h>
 #include <nccl.h>
+#include <algorithm>
 #include <stdexcept>
 #include <string>
 
@@ -71,12 +72,11 @@ void NcclComm::all_gather(Backend& bk, const Buf<float>& local, const Buf<float>
 
 // ---- PeerComm
 
-PeerComm::PeerComm(int rank_, int size_, size_t region_bytes, std::unique_ptr<Comm> bulk) : bulk_(std::move(bulk)) {
+PeerComm::PeerComm(int rank_, int size_, size_t staging_bytes, std::unique_ptr<Comm> bulk) : bulk_(std::move(bulk)) {
     rank = rank_;
     size = size_;
-    x_ = det_xchg_create(region_bytes, rank_, size_);
-    base_ = static_cast<uint8_t*>(det_xchg_base(x_));
-    bytes_ = det_xchg_bytes(x_);
+    x_ = det_xchg_create(staging_bytes, rank_, size_);
+    capacity_ = det_xchg_capacity(x_);
 }
 PeerComm::~PeerComm() {
     if (x_) det_xchg_destroy(x_);
@@ -86,29 +86,48 @@ void PeerComm::open(const uint8_t* handles) {
     det_xchg_open(x_, handles);
     opened_ = true;
 }
-Buf<float> PeerComm::alloc_gathered(Backend&, size_t n) {
-    const size_t need = (n * sizeof(float) + 255) & ~(size_t)255;
-    if (used_ + need > bytes_) throw std::runtime_error("exchange region too small for the gathered buffers");
-    float* p = reinterpret_cast<float*>(base_ + used_);
-    used_ += need;
-    return Buf<float>::view(p, n);
+void PeerComm::open_loopback() {
+    det_xchg_open_loopback(x_);
+    opened_ = true;
+    small_rows = 1 << 30;   // no bulk communicator in this mode: everything that fits goes through the staging
+}
+bool PeerComm::small(size_t t, size_t slice) const {
+    if (t > small_rows || slice % 2 != 0 || t * size * slice > capacity_) return false;
+    if (!opened_) throw std::runtime_error("PeerComm::open has not run");
+    return true;
 }
 void PeerComm::all_gather(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full, size_t m,
                           size_t slice) {
-    const uint8_t* f = reinterpret_cast<const uint8_t*>(full.ptr());
-    const bool inside = f >= base_ && f + m * size * slice * sizeof(float) <= base_ + bytes_;
-    if (m > small_rows || !inside || slice % 4 != 0) {
+    if (!small(m, slice)) {
         if (!bulk_) throw std::runtime_error("exchange too large for the peer path and no bulk communicator given");
-        last_full_ = nullptr;
         bulk_->all_gather(bk, local, tmp, full, m, slice);
         return;
     }
-    if (!opened_) throw std::runtime_error("PeerComm::open has not run");
-    // a rank may still be reading the result of the previous exchange when this one starts: never the same buffer twice in a row
-    if (last_full_ == full.ptr()) throw std::runtime_error("two consecutive exchanges into the same gathered buffer");
-    last_full_ = full.ptr();
     bk.flush();
-    det_xchg_all_gather(x_, local.ptr(), (size_t)(f - base_), (int)m, (int)slice, nullptr);
+    det_xchg_all_gather(x_, local.ptr(), full.ptr(), (int)m, (int)slice, nullptr);
+}
+void PeerComm::gather_add_norm_quant(Backend& bk, const Buf<float>& y_l, const Buf<float>& tmp, const Buf<float>& y_full,
+                                     size_t t, size_t slice, const Buf<float>& x, const Buf<float>& w, float eps,
+                                     const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
+    if (!(fuse && t <= 8 && (slice * size) % 128 == 0 && small(t, slice)))
+        return Comm::gather_add_norm_quant(bk, y_l, tmp, y_full, t, slice, x, w, eps, q, s, mm);
+    bk.flush();
+    det_xchg_add_rmsnorm_quant(x_, y_l.ptr(), (int)slice, x.ptr(), w.ptr(), eps, (int)t, q.ptr(), s.ptr(), mm.ptr(), nullptr);
+}
+void PeerComm::gather_quant(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full, size_t t,
+                            size_t slice, const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
+    if (!(fuse && t <= 8 && (slice * size) % 128 == 0 && small(t, slice)))
+        return Comm::gather_quant(bk, local, tmp, full, t, slice, q, s, mm);
+    bk.flush();
+    det_xchg_quant(x_, local.ptr(), nullptr, (int)slice, (int)t, q.ptr(), s.ptr(), mm.ptr(), nullptr);
+}
+void PeerComm::silu_gather_quant(Backend& bk, const Buf<float>& g, const Buf<float>& u, const Buf<float>& h_l,
+                                 const Buf<float>& tmp, const Buf<float>& h_full, size_t t, size_t slice,
+                                 const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
+    if (!(fuse && t <= 8 && (slice * size) % 128 == 0 && small(t, slice)))
+        return Comm::silu_gather_quant(bk, g, u, h_l, tmp, h_full, t, slice, q, s, mm);
+    bk.flush();
+    det_xchg_quant(x_, g.ptr(), u.ptr(), (int)slice, (int)t, q.ptr(), s.ptr(), mm.ptr(), nullptr);
 }
 
 }  // namespace det

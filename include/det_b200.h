@@ -208,18 +208,27 @@ void det_graph_free(void* graph);
 void det_token_feedback(const int* pick, int* pos, int* log, int log_base, int log_cap, cudaStream_t st);
 
 /* Tensor-parallel exchange over NVLink peer memory (no reference counterpart: the reference is single-device).  Every
- * rank creates a region of the same size, publishes its CUDA IPC handle (64 bytes), opens the others', and places its
- * gathered buffers at the same offsets inside the region.  det_xchg_all_gather stores local[M][slice] into column block
- * `rank` of the gathered [M][size*slice] buffer on EVERY rank with peer stores, then waits (bounded) until all ranks have
- * done the same.  Consecutive exchanges must target different gathered buffers.  One launch, no host involvement; it can
- * be captured into the decode graph.                                                                                 */
+ * rank creates a staging area of the same size, publishes its CUDA IPC handle (64 bytes) and opens the others'.
+ * det_xchg_all_gather sends local[M][slice] to every rank as self-validating 16-byte packets (plain peer stores) and
+ * fills full[M][size*slice] — ordinary local memory, column block r = rank r's slice — as the packets of all ranks
+ * arrive (bounded polling; a timeout sets the error word read by det_last_error).  One launch per rank, no host
+ * involvement, capturable into the decode graph.  Every rank must issue the same sequence of exchanges.
+ * `bytes` of staging take exchanges of up to det_xchg_capacity() gathered values (bytes / 16).                       */
 void* det_xchg_create(size_t bytes, int rank, int size);
 void det_xchg_ipc_handle(void* h, uint8_t out[64]);
 void det_xchg_open(void* h, const uint8_t* handles /* size x 64 bytes */);
-void* det_xchg_base(void* h);
-size_t det_xchg_bytes(void* h);
-void det_xchg_all_gather(void* h, const float* local, size_t full_off, int M, int slice, cudaStream_t st);
+void det_xchg_open_loopback(void* h);   /* timing aid: all rank slots map to this rank's staging (values meaningless) */
+size_t det_xchg_capacity(void* h);
+void det_xchg_all_gather(void* h, const float* local, float* full, int M, int slice, cudaStream_t st);
 void det_xchg_destroy(void* h);
+/* The exchange fused with the row operation that consumes the gathered rows (decode: M <= 8), n = size * slice:
+ *   det_xchg_add_rmsnorm_quant   gather local[M][slice]; x[M][n] += gathered; det_rmsnorm_quant(x, w) -> xq, sx, mx
+ *   det_xchg_quant               gather local (or silu(local) * local_b when local_b != NULL); det_quant -> xq, sx, mx
+ * Results equal det_xchg_all_gather followed by det_add / det_rmsnorm_quant / det_silu_mul_quant / det_quant.       */
+void det_xchg_add_rmsnorm_quant(void* h, const float* local, int slice, float* x, const float* w, float eps, int M,
+                                int8_t* xq, float* sx, uint16_t* mx, cudaStream_t st);
+void det_xchg_quant(void* h, const float* local, const float* local_b, int slice, int M, int8_t* xq, float* sx,
+                    uint16_t* mx, cudaStream_t st);
 
 /* No counterpart in the reference.  det_sample_topkp for callers that may not allocate device memory: the weight
  * scratch is a fixed 4 MiB array inside the library (M * V <= 524288), so no scratch argument and no allocation of any

@@ -1,5 +1,6 @@
 """Tensor-parallel token loop on real GPUs (one process per GPU): the shard of every rank runs on the CUDA backend, decode
-exchanges go through the peer-memory kernel (det_xchg_all_gather), the 16-token batch through NCCL.  Logits and greedy
+exchanges go through the peer-memory kernels (fused with their consumer, det_xchg_add_rmsnorm_quant / det_xchg_quant, or
+stand-alone, det_xchg_all_gather), the 16-token batch through NCCL.  Logits and greedy
 tokens must equal the single-GPU model bit for bit, eagerly and through the captured decode graph.  Skipped on a box
 with fewer GPUs than ranks."""
 import ctypes as C
@@ -44,7 +45,7 @@ def _run_rank(rank, world, port, out_dir, exchange):
         comm = h.dh_nccl_comm_new(nid_np.ctypes.data, rank, world)
         assert comm, h.dh_last_error()
     else:
-        comm = h.dh_peer_comm_new(nid_np.ctypes.data, rank, world, 4 * (16 * (2048 + 3072 + 1024) + VOCAB) + 4096)
+        comm = h.dh_peer_comm_new(nid_np.ctypes.data, rank, world, 16 * max(8 * 3072, VOCAB) + 4096)
         assert comm, h.dh_last_error()
         mine = np.zeros(64, np.uint8)
         h.dh_peer_comm_handle(comm, mine.ctypes.data)
@@ -52,6 +53,8 @@ def _run_rank(rank, world, port, out_dir, exchange):
         dist.all_gather(every, torch.from_numpy(mine))
         handles = np.concatenate([e.numpy() for e in every]).copy()
         h.dh_peer_comm_open(comm, handles.ctypes.data)
+        if exchange == "peer_unfused":
+            h.dh_peer_comm_set_fuse(comm, 0)
         dist.barrier()
     ids = np.zeros(22, np.int32)
     h.dh_synth_prompt(1, ids.size, VOCAB, ids.ctypes.data)
@@ -92,7 +95,7 @@ def _gpu_count():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("world,exchange", [(2, "peer"), (2, "nccl"), (4, "peer")])
+@pytest.mark.parametrize("world,exchange", [(2, "peer"), (2, "peer_unfused"), (2, "nccl"), (4, "peer")])
 def test_sharded_model_equals_single_gpu(world, exchange, libs, tmp_path):
     if _gpu_count() < world:
         pytest.skip(f"needs {world} GPUs")
