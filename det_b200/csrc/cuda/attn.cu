@@ -37,6 +37,9 @@ struct AttnArgs {
     unsigned* mxkey;         // [M][n_h]
     long long* den;          // [M][n_h]
     long long* num;          // [M][n_h][HD]
+    unsigned* bar;           // [M][n_kv] CTAs of a (token, kv head) that have published their maxima (fused decode kernel)
+    unsigned* done;          // [M][n_kv] CTAs that have added their partial sums
+    int* error_flag;
     int nsplit, keys_per_split;
 };
 __device__ __forceinline__ int base_pos(const AttnArgs& a) { return a.pos0_dev ? *a.pos0_dev : a.pos0; }
@@ -73,6 +76,8 @@ __global__ void __launch_bounds__(256) k_attn_prep(const AttnArgs a) {
         if (lane == 0) {
             a.mxkey[row] = 0u;
             a.den[row] = 0;
+            a.bar[row] = 0u;     // indexed by (token, kv head) <= (token, q head)
+            a.done[row] = 0u;
         }
 #pragma unroll
         for (int i = 0; i < PER; i++) a.num[row * HD + lane * PER + i] = 0;
@@ -330,9 +335,215 @@ __global__ void k_attn_fin(const AttnArgs a) {
     a.o[row * HD + d] = fmul(val, sigmoid_f(gate));
 }
 
+// ---- decode-sized attention as one launch after prep: max, acc and fin of the same key range in one CTA.  The scores of
+// the CTA's keys stay in shared memory between the two passes (K is read and multiplied once); the CTAs of one
+// (token, kv head) meet at a counter after publishing their maxima (all CTAs of the grid are resident: the launcher asks
+// for at most one per SM; the wait is bounded), V tiles are staged in shared memory (the first one is fetched
+// asynchronously while the scores are computed), and the CTA that adds its partial sums last finishes the heads.
+constexpr int DEC_MAX_KEYS = 512;   // keys per CTA whose scores fit the shared buffer
+
+template <int HD>
+struct DecSmem {
+    static constexpr int KTILE = KT * KTile<HD>::STRIDE;
+    static constexpr int VTILE = KT * HD * 2;
+    static constexpr int SBUF = MAX_REP * DEC_MAX_KEYS * 4;
+    static constexpr int QS = MAX_REP * HD;
+    static constexpr int PQ = MAX_REP * KT * 4;
+    static constexpr int TOTAL = KTILE + VTILE + SBUF + QS + PQ;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS) k_attn_dec(const AttnArgs a) {
+    static_assert(HD <= ATT_THREADS, "one thread per value dimension");
+    extern __shared__ __align__(16) uint8_t dsm[];
+    int8_t* ktile = reinterpret_cast<int8_t*>(dsm);
+    int16_t* vtile = reinterpret_cast<int16_t*>(dsm + DecSmem<HD>::KTILE);
+    float* sbuf = reinterpret_cast<float*>(dsm + DecSmem<HD>::KTILE + DecSmem<HD>::VTILE);
+    int8_t* qs = reinterpret_cast<int8_t*>(dsm + DecSmem<HD>::KTILE + DecSmem<HD>::VTILE + DecSmem<HD>::SBUF);
+    int (*pq)[KT] = reinterpret_cast<int (*)[KT]>(dsm + DecSmem<HD>::KTILE + DecSmem<HD>::VTILE + DecSmem<HD>::SBUF + DecSmem<HD>::QS);
+    __shared__ float sks[KT];
+    __shared__ float sqs[MAX_REP];
+    __shared__ float mxs[MAX_REP];
+    __shared__ unsigned best[MAX_REP];
+    __shared__ long long den_sh[MAX_REP];
+    __shared__ bool last;
+    pdl_trigger();
+    pdl_wait();
+    const int kvh = blockIdx.y, t = blockIdx.z;
+    const int total = base_pos(a) + t + 1;
+    const int k0 = blockIdx.x * a.keys_per_split;
+    const int k1 = min(total, k0 + a.keys_per_split);
+    if (k0 >= k1) return;
+    const unsigned active = (unsigned)((total + a.keys_per_split - 1) / a.keys_per_split);
+    const int rep = a.rep;
+    const size_t vstride = (size_t)a.n_kv * HD;            // int16 elements between consecutive keys
+
+    // first V tile: asynchronous 16-byte copies, consumed in pass 2
+    auto fetch_v_async = [&](int key0, int nkeys) {
+        constexpr int VEC = HD / 8;                          // 16-byte pieces per row
+        for (int i = threadIdx.x; i < nkeys * VEC; i += ATT_THREADS) {
+            const int q = i / VEC, v = i % VEC;
+            const int16_t* src = a.vq + ((size_t)(key0 + q) * a.n_kv + kvh) * HD + v * 8;
+            const unsigned dst = (unsigned)__cvta_generic_to_shared(vtile + q * HD + v * 8);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch_v_async(k0, min(KT, k1 - k0));
+
+    for (int i = threadIdx.x; i < rep * HD / 16; i += ATT_THREADS)
+        reinterpret_cast<uint4*>(qs)[i] =
+            reinterpret_cast<const uint4*>(a.qq + ((size_t)t * a.n_h + (size_t)kvh * rep) * HD)[i];
+    if (threadIdx.x < rep) {
+        sqs[threadIdx.x] = a.sq[(size_t)t * a.n_h + kvh * rep + threadIdx.x];
+        best[threadIdx.x] = 0u;
+        den_sh[threadIdx.x] = 0;
+    }
+    const int j = threadIdx.x % KT, part = threadIdx.x / KT;   // 4 parts share the heads
+    const int d = threadIdx.x;                                  // value dimension owned in the P.V phase
+
+    // ---- pass 1: scores of this CTA's keys into sbuf, their maxima into best[]
+    unsigned mine[MAX_REP / 4 + 1];
+#pragma unroll
+    for (int i = 0; i < MAX_REP / 4 + 1; i++) mine[i] = 0u;
+    for (int key0 = k0; key0 < k1; key0 += KT) {
+        const int nkeys = min(KT, k1 - key0);
+        __syncthreads();
+        KTile<HD>::load(ktile, sks, a, kvh, key0, nkeys);
+        __syncthreads();
+        if (j < nkeys) {
+#pragma unroll
+            for (int i = 0; i < MAX_REP / 4 + 1; i++) {
+                const int r = part + 4 * i;
+                if (r < rep) {
+                    const int dt = KTile<HD>::dot(ktile, j, qs + r * HD);
+                    const float sc = fmul(fmul((float)dt, sqs[r]), sks[j]);
+                    sbuf[r * DEC_MAX_KEYS + (key0 - k0) + j] = sc;
+                    mine[i] = max(mine[i], f32_key(sc));
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_REP / 4 + 1; i++) {
+        const int r = part + 4 * i;
+        if (r < rep && mine[i]) atomicMax(&best[r], mine[i]);
+    }
+    __syncthreads();
+    const unsigned cell = (unsigned)t * a.n_kv + kvh;
+    if (active > 1) {
+        if (threadIdx.x < rep && best[threadIdx.x])
+            atomicMax(a.mxkey + (size_t)t * a.n_h + kvh * rep + threadIdx.x, best[threadIdx.x]);
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            atomicAdd(a.bar + cell, 1u);
+            const long long start = clock64();
+            bool ok = *reinterpret_cast<volatile int*>(a.error_flag) != 0;
+            while (!ok) {
+                if (*reinterpret_cast<volatile unsigned*>(a.bar + cell) >= active) { ok = true; break; }
+                if (clock64() - start > 4000000000ll) break;      // about two seconds: report and carry on
+            }
+            if (!ok) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
+            __threadfence();
+        }
+        __syncthreads();
+        if (threadIdx.x < rep)
+            mxs[threadIdx.x] = key_f32(*reinterpret_cast<volatile unsigned*>(a.mxkey + (size_t)t * a.n_h + kvh * rep + threadIdx.x));
+    } else if (threadIdx.x < rep) {
+        mxs[threadIdx.x] = key_f32(best[threadIdx.x]);
+    }
+
+    // ---- pass 2: pq from the stored scores, den and num in int64
+    long long num[MAX_REP];
+#pragma unroll
+    for (int r = 0; r < MAX_REP; r++) num[r] = 0;
+    for (int key0 = k0; key0 < k1; key0 += KT) {
+        const int nkeys = min(KT, k1 - key0);
+        __syncthreads();            // mxs visible; the previous tile's pq and vtile are no longer read
+        if (key0 == k0) {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        } else {
+            constexpr int VEC = HD / 8;
+            for (int i = threadIdx.x; i < nkeys * VEC; i += ATT_THREADS) {
+                const int q = i / VEC, v = i % VEC;
+                *reinterpret_cast<uint4*>(vtile + q * HD + v * 8) =
+                    *reinterpret_cast<const uint4*>(a.vq + ((size_t)(key0 + q) * a.n_kv + kvh) * HD + v * 8);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_REP / 4 + 1; i++) {
+            const int r = part + 4 * i;
+            if (r < rep) {
+                int p = 0;
+                if (j < nkeys)
+                    p = f2i_sat(fmul(exp_f(fsub(sbuf[r * DEC_MAX_KEYS + (key0 - k0) + j], mxs[r])), 16777216.0f));
+                pq[r][j] = p;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < rep) {
+            long long sum = 0;
+            for (int q = 0; q < nkeys; q++) sum += pq[threadIdx.x][q];
+            den_sh[threadIdx.x] += sum;
+        }
+        if (d < HD) {
+            for (int q = 0; q < nkeys; q++) {
+                const int vv = vtile[q * HD + d];
+#pragma unroll
+                for (int r = 0; r < MAX_REP; r++)
+                    if (r < rep) num[r] += (long long)pq[r][q] * (long long)vv;
+            }
+        }
+    }
+    __syncthreads();
+    (void)vstride;
+    // ---- finish: alone, or through the global cells with the last CTA converting
+    if (active == 1) {
+        if (d < HD) {
+            const float vs = a.v_scale[kvh];
+#pragma unroll
+            for (int r = 0; r < MAX_REP; r++) {
+                if (r < rep) {
+                    const int h = kvh * rep + r;
+                    const float gate = a.qg[((size_t)t * a.n_h + h) * 2 * HD + HD + d];
+                    const float val = fmul(fdiv(i64_to_f32(num[r]), i64_to_f32(den_sh[r])), vs);
+                    a.o[((size_t)t * a.n_h + h) * HD + d] = fmul(val, sigmoid_f(gate));
+                }
+            }
+        }
+        return;
+    }
+    if (d < HD) {
+#pragma unroll
+        for (int r = 0; r < MAX_REP; r++)
+            if (r < rep)
+                atomicAdd(reinterpret_cast<unsigned long long*>(a.num + ((size_t)t * a.n_h + kvh * rep + r) * HD + d),
+                          (unsigned long long)num[r]);
+    }
+    if (threadIdx.x < rep)
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.den + (size_t)t * a.n_h + kvh * rep + threadIdx.x),
+                  (unsigned long long)den_sh[threadIdx.x]);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(a.done + cell, 1u) == active - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    if (d < HD) {
+        const float vs = a.v_scale[kvh];
+        for (int r = 0; r < rep; r++) {
+            const size_t row = (size_t)t * a.n_h + kvh * rep + r;
+            const float gate = a.qg[row * 2 * HD + HD + d];
+            const float val = fmul(fdiv(i64_to_f32(__ldcg(a.num + row * HD + d)), i64_to_f32(__ldcg(a.den + row))), vs);
+            a.o[row * HD + d] = fmul(val, sigmoid_f(gate));
+        }
+    }
+}
+
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 struct ScratchMap {
-    size_t qq, sq, mx, den, num, total;
+    size_t qq, sq, mx, den, num, bar, done, total;
 };
 static ScratchMap scratch_map(int M, int n_h, int hd) {
     ScratchMap s;
@@ -342,7 +553,9 @@ static ScratchMap scratch_map(int M, int n_h, int hd) {
     s.mx = s.sq + align256(rows * 4);
     s.den = s.mx + align256(rows * 4);
     s.num = s.den + align256(rows * 8);
-    s.total = s.num + align256(rows * hd * 8);
+    s.bar = s.num + align256(rows * hd * 8);
+    s.done = s.bar + align256(rows * 4);
+    s.total = s.done + align256(rows * 4);
     return s;
 }
 
@@ -355,6 +568,9 @@ static void run_attention(AttnArgs a, void* scratch, int max_total_keys, cudaStr
     a.mxkey = reinterpret_cast<unsigned*>(base + sm.mx);
     a.den = reinterpret_cast<long long*>(base + sm.den);
     a.num = reinterpret_cast<long long*>(base + sm.num);
+    a.bar = reinterpret_cast<unsigned*>(base + sm.bar);
+    a.done = reinterpret_cast<unsigned*>(base + sm.done);
+    a.error_flag = error_word();
     // key split: aim at ~4 CTAs per SM in total, whole tiles per split (a choice by shape only)
     const int tiles = (max_total_keys + KT - 1) / KT;
     int want = (4 * sm_count()) / (a.n_kv * a.M);
@@ -366,6 +582,22 @@ static void run_attention(AttnArgs a, void* scratch, int max_total_keys, cudaStr
 
     const long long rows = (long long)a.M * (a.n_h + 2 * a.n_kv);
     launch_pdl(k_attn_prep<HD>, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, q, 1, a);
+    // decode-sized calls: one fused launch, at most one CTA per SM so that all of them are resident at the counter
+    const int fit = sm_count() / (a.n_kv * a.M);
+    if (fit >= 1) {
+        const int tps = (tiles + fit - 1) / fit;
+        if (tps * KT <= DEC_MAX_KEYS) {
+            a.nsplit = (tiles + tps - 1) / tps;
+            a.keys_per_split = tps * KT;
+            static bool attr_set = false;
+            if (!attr_set) {
+                DETB_CUDA_OK(cudaFuncSetAttribute(k_attn_dec<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecSmem<HD>::TOTAL));
+                attr_set = true;
+            }
+            launch_pdl(k_attn_dec<HD>, dim3(a.nsplit, a.n_kv, a.M), dim3(ATT_THREADS), DecSmem<HD>::TOTAL, q, 1, a);
+            return;
+        }
+    }
     const dim3 grid(nsplit, a.n_kv, a.M);
     launch_pdl(k_attn_max<HD>, grid, dim3(ATT_THREADS), 0, q, 1, a);
     launch_pdl(k_attn_acc<HD>, grid, dim3(ATT_THREADS), 0, q, 1, a);

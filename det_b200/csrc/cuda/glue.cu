@@ -262,6 +262,64 @@ __global__ void __launch_bounds__(1024) k_argmax_rows(const float* __restrict__ 
     }
 }
 
+// The same result for few rows of a large vocabulary (decode): ARGMAX_SPLIT CTAs per row each reduce one contiguous
+// chunk, the CTA that finishes last merges the chunk results.  (value, index) pairs merge exactly: greater value wins,
+// equal values keep the lower index.
+constexpr int ARGMAX_SPLIT = 32, ARGMAX_SPLIT_ROWS = 8;
+static __device__ float g_argmax_val[ARGMAX_SPLIT_ROWS * ARGMAX_SPLIT];
+static __device__ int g_argmax_idx[ARGMAX_SPLIT_ROWS * ARGMAX_SPLIT];
+static __device__ unsigned g_argmax_done[ARGMAX_SPLIT_ROWS];
+
+__global__ void __launch_bounds__(256) k_argmax_split(const float* __restrict__ logits, int V, int* __restrict__ out) {
+    __shared__ float bv[8];
+    __shared__ int bi[8];
+    __shared__ bool last;
+    pdl_trigger();
+    pdl_wait();
+    const int rowi = blockIdx.y;
+    const float* row = logits + (size_t)rowi * V;
+    const int chunk = (V + ARGMAX_SPLIT - 1) / ARGMAX_SPLIT;
+    const int lo = blockIdx.x * chunk, hi = min(V, lo + chunk);
+    auto better = [](float v, int i, float w, int j) { return v > w || (v == w && i < j); };
+    auto merge = [&](float& best, int& at, float ov, int oi) {
+        if (oi != 0x7fffffff && (at == 0x7fffffff || better(ov, oi, best, at))) { best = ov; at = oi; }
+    };
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || at == 0x7fffffff) { best = v; at = i; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) merge(best, at, __shfl_xor_sync(FULL, best, off), __shfl_xor_sync(FULL, at, off));
+    if (lane == 0) { bv[warp] = best; bi[warp] = at; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < 8 ? bv[lane] : -INFINITY;
+        at = lane < 8 ? bi[lane] : 0x7fffffff;
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) merge(best, at, __shfl_xor_sync(FULL, best, off), __shfl_xor_sync(FULL, at, off));
+        if (lane == 0) {
+            g_argmax_val[rowi * ARGMAX_SPLIT + blockIdx.x] = best;
+            g_argmax_idx[rowi * ARGMAX_SPLIT + blockIdx.x] = at;
+            __threadfence();
+            last = atomicAdd(&g_argmax_done[rowi], 1u) == ARGMAX_SPLIT - 1;
+        }
+    }
+    __syncthreads();
+    if (!last || warp != 0) return;
+    __threadfence();
+    best = __ldcg(&g_argmax_val[rowi * ARGMAX_SPLIT + lane]);
+    at = __ldcg(&g_argmax_idx[rowi * ARGMAX_SPLIT + lane]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) merge(best, at, __shfl_xor_sync(FULL, best, off), __shfl_xor_sync(FULL, at, off));
+    if (lane == 0) {
+        out[rowi] = at == 0x7fffffff ? 0 : at;
+        g_argmax_done[rowi] = 0;
+    }
+}
+
 // tmp[P][M][slice] -> full[M][P][slice]
 __global__ void k_unshard(const float* __restrict__ tmp, float* __restrict__ full, int P, int M, int slice) {
     pdl_trigger();
@@ -339,7 +397,10 @@ void det_unshard(const float* tmp, float* full, int P, int M, int slice, cudaStr
 }
 void det_argmax(const float* logits, int M, int V, int* out, cudaStream_t st) {
     if (M <= 0) return;
-    launch_pdl(k_argmax_rows, dim3(M), dim3(1024), 0, queue_of(st), 1, logits, V, out);
+    if (M <= ARGMAX_SPLIT_ROWS && V >= 16384)
+        launch_pdl(k_argmax_split, dim3(ARGMAX_SPLIT, M), dim3(256), 0, queue_of(st), 1, logits, V, out);
+    else
+        launch_pdl(k_argmax_rows, dim3(M), dim3(1024), 0, queue_of(st), 1, logits, V, out);
 }
 
 }  // extern "C"

@@ -1,0 +1,117 @@
+"""One linear of a chosen shape through the C ABI, timed with CUDA events: the small stand-alone case of the two GEMM
+kernels that a profiler capture needs (a few hundred MB on the device, a handful of launches).
+
+    python -m det_b200.kernel_case gemv    [N K bits M]    # k_gemv_stream, default 17408 5120 6 1
+    python -m det_b200.kernel_case gemm_tc [N K bits M]    # k_gemm_tc,     default 17408 5120 6 512
+
+gemv: six copies of the weights (seeded, generated on the device, repacked into the streaming layout) are cycled through
+so that no launch finds its weights in the 126 MB L2; 6 warm-up launches, then 12 timed ones.
+gemm_tc: one int8-expanded copy; 3 warm-up launches, then 10 timed ones.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import sys
+
+import numpy as np
+
+from det_b200 import capi
+
+PER32 = {8: 32, 6: 24, 4: 16}
+
+
+class _Events:
+    def __init__(self, stream):
+        self.rt = C.CDLL("libcudart.so.12")
+        self.stream = C.c_void_p(stream)
+
+    def record(self):
+        e = C.c_void_p()
+        assert self.rt.cudaEventCreate(C.byref(e)) == 0
+        assert self.rt.cudaEventRecord(e, self.stream) == 0
+        return e
+
+    def ms(self, a, b):
+        assert self.rt.cudaEventSynchronize(b) == 0
+        out = C.c_float()
+        assert self.rt.cudaEventElapsedTime(C.byref(out), a, b) == 0
+        return out.value
+
+
+def _linear(d, n, k, bits, tensor_id):
+    g = k // 128
+    wq = d.det_malloc(n * (k // 32) * PER32[bits])
+    c = d.det_malloc(n * 4)
+    m = d.det_malloc(n * g * 2)
+    scratch = d.det_malloc(n * g * 8)
+    d.det_synth_linear(20261125, tensor_id, 0, n, k, bits, 0, wq, c, m, scratch, None)
+    d.det_sync()
+    d.det_free(scratch)
+    return capi.QLinear(wq, c, m, n, k, bits)
+
+
+def _activations(d, m, k, n):
+    rng = np.random.default_rng(1)
+    g = k // 128
+    xq, sx, mx, y = d.det_malloc(m * k), d.det_malloc(m * 4), d.det_malloc(m * g * 2), d.det_malloc(m * n * 4)
+    hx = rng.integers(-127, 128, m * k).astype(np.int8)
+    hs = (rng.random(m, dtype=np.float32) * 1e-3 + 1e-4).astype(np.float32)
+    hm = rng.integers(1, 65536, m * g).astype(np.uint16)
+    d.det_memcpy(xq, hx.ctypes.data, hx.nbytes, None)
+    d.det_memcpy(sx, hs.ctypes.data, hs.nbytes, None)
+    d.det_memcpy(mx, hm.ctypes.data, hm.nbytes, None)
+    d.det_sync()
+    return xq, sx, mx, y
+
+
+def main(argv):
+    kind = argv[0] if argv else "gemv"
+    if kind not in ("gemv", "gemm_tc"):
+        raise SystemExit(__doc__)
+    n, k, bits, m = (17408, 5120, 6, 1 if kind == "gemv" else 512)
+    if len(argv) >= 5:
+        n, k, bits, m = map(int, argv[1:5])
+    d = capi.cuda()
+    assert d.det_init() == 0
+    ev = _Events(d.det_cuda_stream())
+    xq, sx, mx, y = _activations(d, m, k, n)
+    g = k // 128
+    if kind == "gemv":
+        lins = []
+        for copy in range(6):
+            src = _linear(d, n, k, bits, 100 + copy)
+            sp = d.det_malloc(d.det_linear_repack_bytes(n, k, bits))
+            d.det_linear_repack(C.byref(src), sp, None)
+            d.det_sync()
+            d.det_free(src.wq)
+            lins.append(capi.QLinear(sp, src.c, src.m, n, k, bits | capi.DET_LAYOUT_STREAM))
+        for it in range(6):
+            d.det_gemm(C.byref(lins[it % 6]), xq, sx, mx, m, y, None)
+        a = ev.record()
+        for it in range(12):
+            d.det_gemm(C.byref(lins[it % 6]), xq, sx, mx, m, y, None)
+        b = ev.record()
+        us = ev.ms(a, b) / 12 * 1e3
+        nbytes = n * (k // 32 * PER32[bits] + 4 + g * 2) + m * (k + 4 + g * 2) + m * n * 4
+        print(f"k_gemv_stream N={n} K={k} W{bits} M={m}: {us:.2f} us/launch, {nbytes / 1e6:.2f} MB algorithmic, "
+              f"{nbytes / us / 1e3:.0f} GB/s; device error word {d.det_last_error()}")
+    else:
+        src = _linear(d, n, k, bits, 100)
+        w8 = d.det_malloc(d.det_linear_expand_bytes(n, k))
+        d.det_linear_expand(C.byref(src), w8, None)
+        d.det_sync()
+        tc = capi.QLinear(w8, src.c, src.m, n, k, bits | capi.DET_LAYOUT_INT8)
+        for _ in range(3):
+            d.det_gemm(C.byref(tc), xq, sx, mx, m, y, None)
+        a = ev.record()
+        for _ in range(10):
+            d.det_gemm(C.byref(tc), xq, sx, mx, m, y, None)
+        b = ev.record()
+        us = ev.ms(a, b) / 10 * 1e3
+        print(f"k_gemm_tc N={n} K={k} W{bits} M={m}: {us:.1f} us/launch, {2 * m * n * k / us / 1e6:.0f} TOPS; "
+              f"device error word {d.det_last_error()}")
+    d.det_sync()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

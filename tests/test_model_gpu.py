@@ -74,3 +74,27 @@ def test_tiny_chunking_invariance(chunk, libs, cuda_backend):
     finally:
         h.dh_model_free(whole)
         h.dh_model_free(parts)
+
+
+def test_long_context_decode_equals_chunked_prefill(libs, cuda_backend):
+    """Context of 5200 keys on a 4-layer tiny model (one attention layer): the last 400 tokens are fed one at a time (the fused decode attention
+    kernel, two key tiles per CTA, key ranges merged through the global cells) on one model and in 64-token
+    batches (the separate max / acc / fin kernels) on the other; the final logits must be the same bits."""
+    h = libs.host()
+    n = 5200
+    ids = _prompt(h, n, 32768)
+    a = _model(h, cuda_backend, 64, layers=4, max_ctx=n + 8)
+    b = _model(h, cuda_backend, 64, layers=4, max_ctx=n + 8)
+    try:
+        assert h.dh_model_prefill(a, ids.ctypes.data, n) == 0, h.dh_last_error()
+        assert h.dh_model_prefill(b, ids.ctypes.data, n - 400) == 0, h.dh_last_error()
+        for i in range(n - 400, n):
+            assert h.dh_model_forward(b, ids[i:].ctypes.data, 1) == 0, h.dh_last_error()
+        la, lb = np.zeros(32768, np.float32), np.zeros(32768, np.float32)
+        h.dh_model_logits(a, la.ctypes.data, la.size)
+        h.dh_model_logits(b, lb.ctypes.data, lb.size)
+        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32)), f"{(la.view(np.uint32) != lb.view(np.uint32)).sum()} logits differ"
+        assert libs.cuda().det_last_error() == 0
+    finally:
+        h.dh_model_free(a)
+        h.dh_model_free(b)
