@@ -248,7 +248,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             raise RuntimeError(h.dh_last_error().decode())
         h.dh_peer_comm_open_loopback(comm)
     t_load = time.perf_counter()
-    model = h.dh_model_new_synth_tp(bk, cfg.encode(), 0, SEED, max_ctx, chunk, comm)
+    model = h.dh_model_new_synth_tp(bk, cfg.encode(), args.layers, SEED, max_ctx, chunk, comm)
     if not model:
         raise RuntimeError(h.dh_last_error().decode())
     d.det_sync()
@@ -297,6 +297,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     n = h.dh_graph_decoder_finish(dec, out.ctypes.data, out.size)
     last = int(out[n - 1])
     barrier()
+    rt.cudaProfilerStart()      # a profiler started with "--profile-from-start off" sees the timed decode steps only
     w0 = time.time()
     a = ev.record()
     _check(h.dh_graph_decoder_enqueue(dec, last, K, 1), h)
@@ -304,6 +305,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     decode_ms = max_over_ranks(ev.ms(a, b))
     windows.append((w0, time.time()))
     n = h.dh_graph_decoder_finish(dec, out.ctypes.data, out.size)
+    rt.cudaProfilerStop()
     graph_tokens = out[:n].copy()
     last = int(graph_tokens[-1])
 
@@ -357,6 +359,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "dtype": "int8 x W6 -> int64 (fp32 glue)", "data": "synthetic",
         "config": {"workload": f"{cfg}-shape seeded random-init W6 model (W8 head and GDN a/b), batch 1: prefill {P} tokens in "
                                f"{chunk}-token chunks, then greedy decode", "context_at_timing": P + W,
+                   **({"layers_built": args.layers, "note": "reduced depth: not a result"} if args.layers else {}),
                    "parallelism": (f"EMULATED rank 0 of tp{args.emulate_tp}, exchanges looped back: not a result"
                                    if args.emulate_tp > 1 else "1 GPU") if world == 1 else
                    f"tp{world}: output-row / head tensor parallel, one batch-1 sequence; fp32 slices all-gathered " +
@@ -417,6 +420,78 @@ def run_reference(args, rank: int, world: int):
     print(json.dumps(line), flush=True)
 
 
+def run_serving(args, local_rank: int):
+    """BASELINE configs[4]: `--seqs` independent sequences (contexts uniform in [ctx-min, ctx-max], seeded) decode
+    `--new` tokens each at temp 0.7 / top-p 0.95 / top-k 40 with per-sequence seeds, one batched step per token.  Not the
+    headline line: a second workload, printed in the same format (one step = one token for every sequence)."""
+    import numpy as np
+    from det_b200 import capi
+    rt = C.CDLL("libcudart.so.12")
+    assert rt.cudaSetDevice(local_rank) == 0
+    h, d = capi.host(), capi.cuda()
+    cfg, shape = args.config, SHAPES[args.config]
+    B, new = args.seqs, args.new
+    rng = np.random.default_rng(SEED)
+    ctxs = [int(x) for x in rng.integers(args.ctx_min, args.ctx_max + 1, B)]
+    bk = h.dh_cuda_backend_new(1, 1)
+    if not bk:
+        raise RuntimeError(h.dh_last_error().decode())
+    if args.compose_rows:
+        h.dh_cuda_set_fuse_rows(bk, 0)
+    model = h.dh_model_new_synth(bk, cfg.encode(), args.layers, SEED, 16, max(args.chunk, B))
+    if not model:
+        raise RuntimeError(h.dh_last_error().decode())
+    batch = h.dh_batch_new(model, B, max(ctxs) + new + 1)
+    if not batch:
+        raise RuntimeError(h.dh_last_error().decode())
+    ev = Events(d.det_cuda_stream())
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t0 = time.perf_counter()
+    for i, n in enumerate(ctxs):
+        ids = np.zeros(n, np.int32)
+        h.dh_synth_prompt(PROMPT_SEED + i, n, shape["vocab"], ids.ctypes.data)
+        _check(h.dh_batch_prefill(batch, i, ids.ctypes.data, n, 0, 1.0 / 0.7, 40, 0.95, 1000 + i), h)
+    d.det_sync()
+    prefill_s = time.perf_counter() - t0
+    W = args.warmup
+    _check(h.dh_batch_step(batch, W), h)
+    d.det_sync()
+    rt.cudaProfilerStart()      # a profiler started with "--profile-from-start off" sees the timed steps only
+    w0 = time.time()
+    marks = [ev.record()]
+    for _ in range(new - 1 - W):
+        _check(h.dh_batch_step(batch, 1), h)
+        marks.append(ev.record())
+    steps_ms = [ev.ms(a, b) for a, b in zip(marks[:-1], marks[1:])]
+    rt.cudaProfilerStop()
+    window = (w0, time.time())
+    time.sleep(0.3)
+    sampler.stop()
+    if d.det_last_error():
+        raise RuntimeError("device-side wait reported an error")
+    total_ms = sum(steps_ms)
+    K = len(steps_ms)
+    head = np.zeros(4, np.int32)
+    h.dh_batch_tokens(batch, 0, head.ctypes.data, 4)
+    print(json.dumps({
+        "metric": f"{cfg} W6 serving decode tok/s, {B} sequences", "value": B * K / (total_ms * 1e-3), "unit": "tok/s",
+        "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 x W6 -> int64 (fp32 glue)", "data": "synthetic",
+        "config": {"workload": f"{cfg}-shape seeded random-init W6 model, {B} sequences with contexts uniform in "
+                               f"[{args.ctx_min}, {args.ctx_max}], {new} tokens each at temp 0.7 / top-k 40 / top-p 0.95, "
+                               f"per-sequence seeds; one batched step per token",
+                   "contexts": ctxs, **({"layers_built": args.layers, "note": "reduced depth: not a result"} if args.layers else {}),
+                   "rows_path": "composed per-sequence calls" if args.compose_rows else
+                   "det_attention_rows / det_gdn_rows", "l2": "weights streamed per step exceed the 126 MB L2"},
+        "per_token_ms": {"p50": float(np.percentile(steps_ms, 50)), "p99": float(np.percentile(steps_ms, 99))},
+        "prefill": {"tokens": int(sum(ctxs)), "value": sum(ctxs) / prefill_s, "unit": "tok/s (host wall clock, sequence by sequence)"},
+        "clocks": sampler.summary([window]),
+        "tokens_head": [int(x) for x in head],
+    }))
+    h.dh_batch_free(batch)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -430,6 +505,17 @@ def main():
                     help="N > 1: decode exchanges as one peer-memory kernel per rank (default) or as NCCL all-gathers")
     ap.add_argument("--emulate-tp", type=int, default=0,
                     help="timing aid at N = 1: run rank 0 of a P-way shard with exchanges looped back (values meaningless)")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="build only the first L layers of the configuration (a small case for profiler captures; the "
+                         "line says so and is not a result)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+                    help="decode: the headline batch-1 token loop; serving: many sequences, one batched step per token")
+    ap.add_argument("--seqs", type=int, default=32)
+    ap.add_argument("--ctx-min", type=int, default=512)
+    ap.add_argument("--ctx-max", type=int, default=8192)
+    ap.add_argument("--new", type=int, default=256)
+    ap.add_argument("--compose-rows", action="store_true",
+                    help="serving: per-sequence attention / GDN calls instead of the batched kernels (same tokens)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-pdl", action="store_true", help="measurement switch: plain stream-ordered launches")
     args = ap.parse_args()
@@ -447,7 +533,12 @@ def main():
         if world == 1:
             from det_b200 import capi
             capi.host().dh_use_cuda_synth_rows(1)
-        run_ours(args, rank, world, local_rank)
+        if args.workload == "serving":
+            if world != 1:
+                raise SystemExit("the serving workload runs on one GPU")
+            run_serving(args, local_rank)
+        else:
+            run_ours(args, rank, world, local_rank)
 
 
 if __name__ == "__main__":

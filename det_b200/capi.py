@@ -103,6 +103,10 @@ CUDA_ABI = {
     "det_graph_launch": (None, [c_void_p]),
     "det_graph_free": (None, [c_void_p]),
     "det_token_feedback": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "det_attention_rows": (None, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "det_gdn_rows": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int,
+                            c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "det_xchg_create": (c_void_p, [c_size_t, c_int, c_int]),
     "det_xchg_ipc_handle": (None, [c_void_p, c_void_p]),
     "det_xchg_open": (None, [c_void_p, c_void_p]),
@@ -146,6 +150,12 @@ HOST_API = {
     "dh_model_pick": (c_int, [c_void_p, c_int, c_float, c_size_t, c_float, C.POINTER(c_u64), C.POINTER(c_i32)]),
     "dh_model_generate": (c_int, [c_void_p, c_void_p, c_size_t, c_size_t, c_int, c_float, c_size_t, c_float, c_u64,
                                   c_void_p, C.POINTER(c_size_t)]),
+    "dh_cuda_set_fuse_rows": (None, [c_void_p, c_int]),
+    "dh_batch_new": (c_void_p, [c_void_p, c_size_t, c_size_t]),
+    "dh_batch_free": (None, [c_void_p]),
+    "dh_batch_prefill": (c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_int, c_float, c_size_t, c_float, c_u64]),
+    "dh_batch_step": (c_int, [c_void_p, c_size_t]),
+    "dh_batch_tokens": (c_size_t, [c_void_p, c_size_t, c_void_p, c_size_t]),
     "dh_graph_decoder_new": (c_void_p, [c_void_p]),
     "dh_graph_decoder_free": (None, [c_void_p]),
     "dh_graph_decoder_enqueue": (c_int, [c_void_p, c_i32, c_size_t, c_int]),

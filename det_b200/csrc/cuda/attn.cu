@@ -30,6 +30,9 @@ struct AttnArgs {
     int M, n_h, n_kv, rep;
     int pos0;                // used when pos0_dev == NULL
     const int* pos0_dev;
+    // batched decode: token row t belongs to its own sequence with cache rows[t] at position pos_rows[t]
+    const det_kv_cache* rows;
+    const int* pos_rows;
     float* o;
     // scratch
     int8_t* qq;              // [M][n_h][HD]
@@ -42,7 +45,20 @@ struct AttnArgs {
     int* error_flag;
     int nsplit, keys_per_split;
 };
-__device__ __forceinline__ int base_pos(const AttnArgs& a) { return a.pos0_dev ? *a.pos0_dev : a.pos0; }
+// cache and position of token row t
+struct RowCache {
+    int8_t* kq;
+    float* sk;
+    int16_t* vq;
+    int pos;
+};
+__device__ __forceinline__ RowCache row_cache(const AttnArgs& a, int t) {
+    if (a.rows) {
+        const det_kv_cache c = a.rows[t];
+        return RowCache{c.kq, c.sk, c.vq, a.pos_rows[t]};
+    }
+    return RowCache{a.kq, a.sk, a.vq, (a.pos0_dev ? *a.pos0_dev : a.pos0) + t};
+}
 
 template <int HD>
 __global__ void __launch_bounds__(256) k_attn_prep(const AttnArgs a) {
@@ -54,14 +70,14 @@ __global__ void __launch_bounds__(256) k_attn_prep(const AttnArgs a) {
     const long long row = (long long)blockIdx.x * 8 + wib;
     const long long n_q = (long long)a.M * a.n_h, n_kvrows = (long long)a.M * a.n_kv;
     if (row >= n_q + 2 * n_kvrows) return;
-    const int pos0 = base_pos(a);
     if (row >= n_q + n_kvrows) {
         // ---- v row -> int16 cache (spec/layers.rs:76-87)
         const long long r = row - n_q - n_kvrows;
         const int t = (int)(r / a.n_kv), h = (int)(r % a.n_kv);
+        const RowCache rc = row_cache(a, t);
         const float inv = a.v_inv[h];
         const float* src = a.v + ((size_t)t * a.n_kv + h) * HD;
-        int16_t* dst = a.vq + ((size_t)(pos0 + t) * a.n_kv + h) * HD;
+        int16_t* dst = rc.vq + ((size_t)rc.pos * a.n_kv + h) * HD;
 #pragma unroll
         for (int i = 0; i < PER; i++) {
             const int idx = lane * PER + i;
@@ -109,8 +125,9 @@ __global__ void __launch_bounds__(256) k_attn_prep(const AttnArgs a) {
     __syncwarp();
     // rope on the first `rot` dims, neox pairing (spec/layers.rs:5-13)
     const int half = a.rot >> 1;
-    const float* rc = a.rope_cos + (size_t)(pos0 + t) * half;
-    const float* rs = a.rope_sin + (size_t)(pos0 + t) * half;
+    const RowCache cache = row_cache(a, t);
+    const float* rc = a.rope_cos + (size_t)cache.pos * half;
+    const float* rs = a.rope_sin + (size_t)cache.pos * half;
     for (int p = lane; p < half; p += 32) {
         const float u = buf[p], w = buf[p + half];
         const float c = rc[p], s = rs[p];
@@ -129,12 +146,12 @@ __global__ void __launch_bounds__(256) k_attn_prep(const AttnArgs a) {
     amax = max_lanes(amax);
     const float s = (amax == 0.0f) ? 1.0f : fdiv(amax, 127.0f);   // spec/quant.rs:7-16
     const float inv = fdiv(1.0f, s);
-    int8_t* dst = is_q ? a.qq + ((size_t)t * a.n_h + h) * HD : a.kq + ((size_t)(pos0 + t) * a.n_kv + h) * HD;
+    int8_t* dst = is_q ? a.qq + ((size_t)t * a.n_h + h) * HD : cache.kq + ((size_t)cache.pos * a.n_kv + h) * HD;
 #pragma unroll
     for (int i = 0; i < PER; i++) dst[lane * PER + i] = (int8_t)quant_code(x[i], inv);
     if (lane == 0) {
         if (is_q) a.sq[(size_t)t * a.n_h + h] = s;
-        else a.sk[(size_t)(pos0 + t) * a.n_kv + h] = s;
+        else cache.sk[(size_t)cache.pos * a.n_kv + h] = s;
     }
 }
 
@@ -143,16 +160,16 @@ __global__ void __launch_bounds__(256) k_attn_prep(const AttnArgs a) {
 template <int HD>
 struct KTile {
     static constexpr int STRIDE = HD + 16;
-    __device__ static void load(int8_t* tile, float* sks, const AttnArgs& a, int kvh, int key0, int nkeys) {
+    __device__ static void load(int8_t* tile, float* sks, const AttnArgs& a, const RowCache& c, int kvh, int key0, int nkeys) {
         constexpr int VEC = HD / 16;
         for (int i = threadIdx.x; i < KT * VEC; i += ATT_THREADS) {
             const int j = i / VEC, v = i % VEC;
             uint4 val = make_uint4(0, 0, 0, 0);
             if (j < nkeys)
-                val = *reinterpret_cast<const uint4*>(a.kq + ((size_t)(key0 + j) * a.n_kv + kvh) * HD + v * 16);
+                val = *reinterpret_cast<const uint4*>(c.kq + ((size_t)(key0 + j) * a.n_kv + kvh) * HD + v * 16);
             *reinterpret_cast<uint4*>(tile + j * STRIDE + v * 16) = val;
         }
-        for (int j = threadIdx.x; j < KT; j += ATT_THREADS) sks[j] = j < nkeys ? a.sk[(size_t)(key0 + j) * a.n_kv + kvh] : 0.0f;
+        for (int j = threadIdx.x; j < KT; j += ATT_THREADS) sks[j] = j < nkeys ? c.sk[(size_t)(key0 + j) * a.n_kv + kvh] : 0.0f;
     }
     __device__ __forceinline__ static int dot(const int8_t* tile, int j, const int8_t* q) {
         int acc = 0;
@@ -169,9 +186,9 @@ struct KTile {
     }
 };
 
-// key range of this CTA for token t: [k0, k1) within [0, pos0 + t]
-__device__ __forceinline__ void key_range(const AttnArgs& a, int t, int& k0, int& k1) {
-    const int total = base_pos(a) + t + 1;
+// key range of this CTA for a token at position pos: [k0, k1) within [0, pos]
+__device__ __forceinline__ void key_range(const AttnArgs& a, int pos, int& k0, int& k1) {
+    const int total = pos + 1;
     k0 = blockIdx.x * a.keys_per_split;
     k1 = min(total, k0 + a.keys_per_split);
 }
@@ -186,8 +203,9 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_max(const AttnArgs a) {
     pdl_trigger();
     pdl_wait();
     const int kvh = blockIdx.y, t = blockIdx.z;
+    const RowCache cache = row_cache(a, t);
     int k0, k1;
-    key_range(a, t, k0, k1);
+    key_range(a, cache.pos, k0, k1);
     if (k0 >= k1) return;
     const int rep = a.rep;
     for (int i = threadIdx.x; i < rep * HD / 16; i += ATT_THREADS)
@@ -204,7 +222,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_max(const AttnArgs a) {
     for (int key0 = k0; key0 < k1; key0 += KT) {
         const int nkeys = min(KT, k1 - key0);
         __syncthreads();
-        KTile<HD>::load(ktile, sks, a, kvh, key0, nkeys);
+        KTile<HD>::load(ktile, sks, a, cache, kvh, key0, nkeys);
         __syncthreads();
         if (j < nkeys) {
 #pragma unroll
@@ -241,8 +259,9 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
     pdl_trigger();
     pdl_wait();
     const int kvh = blockIdx.y, t = blockIdx.z;
+    const RowCache cache = row_cache(a, t);
     int k0, k1;
-    key_range(a, t, k0, k1);
+    key_range(a, cache.pos, k0, k1);
     if (k0 >= k1) return;
     const int rep = a.rep;
     for (int i = threadIdx.x; i < rep * HD / 16; i += ATT_THREADS)
@@ -262,7 +281,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
     for (int key0 = k0; key0 < k1; key0 += KT) {
         const int nkeys = min(KT, k1 - key0);
         __syncthreads();
-        KTile<HD>::load(ktile, sks, a, kvh, key0, nkeys);
+        KTile<HD>::load(ktile, sks, a, cache, kvh, key0, nkeys);
         __syncthreads();
 #pragma unroll
         for (int i = 0; i < MAX_REP / 4 + 1; i++) {
@@ -284,7 +303,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
             den_sh[threadIdx.x] += s;
         }
         if (d < HD) {
-            const int16_t* vcol = a.vq + ((size_t)key0 * a.n_kv + kvh) * HD + d;
+            const int16_t* vcol = cache.vq + ((size_t)key0 * a.n_kv + kvh) * HD + d;
             const size_t vstride = (size_t)a.n_kv * HD;
             for (int q = 0; q < nkeys; q++) {
                 const int vv = vcol[q * vstride];
@@ -370,7 +389,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_dec(const AttnArgs a) {
     pdl_trigger();
     pdl_wait();
     const int kvh = blockIdx.y, t = blockIdx.z;
-    const int total = base_pos(a) + t + 1;
+    const RowCache cache = row_cache(a, t);
+    const int total = cache.pos + 1;
     const int k0 = blockIdx.x * a.keys_per_split;
     const int k1 = min(total, k0 + a.keys_per_split);
     if (k0 >= k1) return;
@@ -383,7 +403,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_dec(const AttnArgs a) {
         constexpr int VEC = HD / 8;                          // 16-byte pieces per row
         for (int i = threadIdx.x; i < nkeys * VEC; i += ATT_THREADS) {
             const int q = i / VEC, v = i % VEC;
-            const int16_t* src = a.vq + ((size_t)(key0 + q) * a.n_kv + kvh) * HD + v * 8;
+            const int16_t* src = cache.vq + ((size_t)(key0 + q) * a.n_kv + kvh) * HD + v * 8;
             const unsigned dst = (unsigned)__cvta_generic_to_shared(vtile + q * HD + v * 8);
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
         }
@@ -409,7 +429,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_dec(const AttnArgs a) {
     for (int key0 = k0; key0 < k1; key0 += KT) {
         const int nkeys = min(KT, k1 - key0);
         __syncthreads();
-        KTile<HD>::load(ktile, sks, a, kvh, key0, nkeys);
+        KTile<HD>::load(ktile, sks, a, cache, kvh, key0, nkeys);
         __syncthreads();
         if (j < nkeys) {
 #pragma unroll
@@ -468,7 +488,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_dec(const AttnArgs a) {
             for (int i = threadIdx.x; i < nkeys * VEC; i += ATT_THREADS) {
                 const int q = i / VEC, v = i % VEC;
                 *reinterpret_cast<uint4*>(vtile + q * HD + v * 8) =
-                    *reinterpret_cast<const uint4*>(a.vq + ((size_t)(key0 + q) * a.n_kv + kvh) * HD + v * 8);
+                    *reinterpret_cast<const uint4*>(cache.vq + ((size_t)(key0 + q) * a.n_kv + kvh) * HD + v * 8);
             }
         }
 #pragma unroll
@@ -607,23 +627,27 @@ static void run_attention(AttnArgs a, void* scratch, int max_total_keys, cudaStr
 static void attention_entry(const det_attn_layer* L, const det_kv_cache* kv, const float* qg, const float* k,
                             const float* v, const float* rope_cos, const float* rope_sin, int rot, float eps, int M,
                             int pos0, const int* pos0_dev, int max_pos, int n_h, int n_kv, int hd, float* o,
-                            void* scratch, cudaStream_t st) {
+                            void* scratch, cudaStream_t st, const det_kv_cache* rows = nullptr,
+                            const int* pos_rows = nullptr) {
     if (M <= 0) return;
     DETB_REQUIRE(n_kv > 0 && n_h % n_kv == 0 && n_h / n_kv <= MAX_REP, "n_h / n_kv must be an integer <= 8");
     DETB_REQUIRE(hd == 64 || hd == 256, "head_dim must be 64 or 256 (1/sqrt(hd) has to be a power of two, cpu.rs:225-230)");
     DETB_REQUIRE(rot >= 0 && rot <= hd && rot % 2 == 0, "bad rotary dimension");
-    DETB_REQUIRE(max_pos + M <= kv->capacity, "positions exceed the cache capacity");
+    if (!rows) DETB_REQUIRE(max_pos + M <= kv->capacity, "positions exceed the cache capacity");
     AttnArgs a;
+    a.rows = rows; a.pos_rows = pos_rows;
     a.q_norm = L->q_norm; a.k_norm = L->k_norm; a.v_scale = L->v_scale; a.v_inv = L->v_inv_scale;
-    a.kq = kv->kq; a.sk = kv->sk; a.vq = kv->vq;
+    if (kv) { a.kq = kv->kq; a.sk = kv->sk; a.vq = kv->vq; }
+    else { a.kq = nullptr; a.sk = nullptr; a.vq = nullptr; }
     a.qg = qg; a.k = k; a.v = v; a.rope_cos = rope_cos; a.rope_sin = rope_sin;
     a.rot = rot; a.eps = eps;
     a.qscale = hd == 256 ? 0.0625f : 0.125f;   // fp32(1/sqrt(hd)), exact
     a.M = M; a.n_h = n_h; a.n_kv = n_kv; a.rep = n_h / n_kv;
     a.pos0 = pos0; a.pos0_dev = pos0_dev; a.o = o;
     cudaStream_t q = queue_of(st);
-    if (hd == 256) run_attention<256>(a, scratch, max_pos + M, q);
-    else run_attention<64>(a, scratch, max_pos + M, q);
+    const int keys = rows ? max_pos + 1 : max_pos + M;
+    if (hd == 256) run_attention<256>(a, scratch, keys, q);
+    else run_attention<64>(a, scratch, keys, q);
 }
 
 }  // namespace detb
@@ -645,6 +669,17 @@ void det_attention_dev(const det_attn_layer* L, const det_kv_cache* kv, const fl
                        const int* pos0_dev, int max_pos, int n_h, int n_kv, int hd, float* o, void* scratch,
                        cudaStream_t st) {
     attention_entry(L, kv, qg, k, v, rope_cos, rope_sin, rot, eps, M, 0, pos0_dev, max_pos, n_h, n_kv, hd, o, scratch, st);
+}
+
+
+// Batched decode (no reference counterpart): M sequences advance one token each.  Row t of qg / k / v / o belongs to the
+// sequence whose cache is rows[t] (a DEVICE array of M det_kv_cache) at position pos[t] (device array); max_pos is a host
+// bound on the positions.  Each row equals det_attention(M = 1, pos0 = pos[t]) on that cache.
+void det_attention_rows(const det_attn_layer* L, const det_kv_cache* rows, const int* pos, int max_pos, const float* qg,
+                        const float* k, const float* v, const float* rope_cos, const float* rope_sin, int rot, float eps,
+                        int M, int n_h, int n_kv, int hd, float* o, void* scratch, cudaStream_t st) {
+    attention_entry(L, nullptr, qg, k, v, rope_cos, rope_sin, rot, eps, M, 0, nullptr, max_pos, n_h, n_kv, hd, o, scratch, st,
+                    rows, pos);
 }
 
 }  // extern "C"

@@ -28,10 +28,15 @@ struct GdnArgs {
     float* decay;    // [M][n_v]
     float* o;        // [M][n_v][DV] mixer output (gout when exported)
     float* gin;      // optional
+    const det_gdn_state* rows;   // batched decode: token row t is the next token of the sequence with state rows[t]
 };
 
-// input of channel c at time tau (tau < 0 reaches into the conv state, which holds times -3, -2, -1)
-__device__ __forceinline__ float conv_in(const GdnArgs& g, int tau, int c) {
+// input of channel c `back` steps before token row t (times before the call reach into the conv state, which holds the
+// three inputs before the call's first token; in a batched step every row is the first token of its own sequence)
+__device__ __forceinline__ float conv_in(const GdnArgs& g, int t, int back, int c) {
+    if (g.rows)
+        return back == 0 ? g.qkv[(size_t)t * g.conv_dim + c] : g.rows[t].conv_state[(size_t)(3 - back) * g.conv_dim + c];
+    const int tau = t - back;
     return tau < 0 ? g.conv_state[(size_t)(3 + tau) * g.conv_dim + c] : g.qkv[(size_t)tau * g.conv_dim + c];
 }
 
@@ -50,9 +55,9 @@ __global__ void __launch_bounds__(128) k_gdn_prep(const GdnArgs g) {
             const int c = c0 + e;
             const float4 w = *reinterpret_cast<const float4*>(g.conv + (size_t)c * 4);
             // ((w0*x[t-3] + w1*x[t-2]) + w2*x[t-1]) + w3*x[t]   (spec/layers.rs:135-140)
-            float acc = fadd(fmul(w.x, conv_in(g, t - 3, c)), fmul(w.y, conv_in(g, t - 2, c)));
-            acc = fadd(acc, fmul(w.z, conv_in(g, t - 1, c)));
-            acc = fadd(acc, fmul(w.w, conv_in(g, t, c)));
+            float acc = fadd(fmul(w.x, conv_in(g, t, 3, c)), fmul(w.y, conv_in(g, t, 2, c)));
+            acc = fadd(acc, fmul(w.z, conv_in(g, t, 1, c)));
+            acc = fadd(acc, fmul(w.w, conv_in(g, t, 0, c)));
             v[e] = silu_f(acc);
             sq[e] = fmul(v[e], v[e]);
         }
@@ -112,7 +117,9 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
     const int j0 = (blockIdx.x % (DV / RC)) * RC;
     const int kh = h / g.rep;
     const int p = threadIdx.x % RL, jj = threadIdx.x / RL;
-    float* Sh = g.S + (size_t)h * DK * DV;
+    // one sequence: this CTA walks all M tokens; batched step: blockIdx.y is the row, one token of its own sequence
+    float* Sh = (g.rows ? g.rows[blockIdx.y].S : g.S) + (size_t)h * DK * DV;
+    const int t_begin = g.rows ? blockIdx.y : 0, t_end = g.rows ? blockIdx.y + 1 : g.M;
 
     for (int i = threadIdx.x; i < DK * RC; i += RC * RL) slab[i / RC][i % RC] = Sh[(size_t)(i / RC) * DV + j0 + (i % RC)];
     __syncthreads();
@@ -139,14 +146,14 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
         be[b] = g.beta[(size_t)t * g.n_v + h];
         de[b] = g.decay[(size_t)t * g.n_v + h];
     };
-    fetch(0, 0);
+    fetch(t_begin, 0);
 #pragma unroll 1
-    for (int t = 0; t < g.M; t += 2) {
+    for (int t = t_begin; t < t_end; t += 2) {
 #pragma unroll
         for (int b = 0; b < 2; b++) {
             const int tt = t + b;
-            if (tt < g.M) {
-                if (tt + 1 < g.M) fetch(tt + 1, b ^ 1);
+            if (tt < t_end) {
+                if (tt + 1 < t_end) fetch(tt + 1, b ^ 1);
                 float prod[RR];
 #pragma unroll
                 for (int i = 0; i < RR; i++) {
@@ -178,13 +185,18 @@ __global__ void __launch_bounds__(128) k_gdn_out(const GdnArgs g, int row_blocks
     pdl_wait();
     if ((int)blockIdx.x >= row_blocks) {
         // conv state <- the last three raw inputs (times M-3 .. M-1); each channel is read fully before it is written
-        const int c = (blockIdx.x - row_blocks) * 128 + threadIdx.x;
+        const int cblocks = (g.conv_dim + 127) / 128;
+        const int idx = blockIdx.x - row_blocks;
+        const int seq = idx / cblocks;                       // 0 unless this is a batched step
+        const int c = (idx % cblocks) * 128 + threadIdx.x;
         if (c < g.conv_dim) {
+            const int t_last = g.rows ? seq : g.M - 1;       // the newest input of the sequence
+            float* state = g.rows ? g.rows[seq].conv_state : g.conv_state;
             float keep[3];
 #pragma unroll
-            for (int r = 0; r < 3; r++) keep[r] = conv_in(g, g.M - 3 + r, c);
+            for (int r = 0; r < 3; r++) keep[r] = conv_in(g, t_last, 2 - r, c);
 #pragma unroll
-            for (int r = 0; r < 3; r++) g.conv_state[(size_t)r * g.conv_dim + c] = keep[r];
+            for (int r = 0; r < 3; r++) state[(size_t)r * g.conv_dim + c] = keep[r];
         }
         return;
     }
@@ -233,9 +245,9 @@ size_t det_gdn_scratch_bytes(int M, int n_k, int n_v, int dk, int dv) {
     return gdn_scratch(M > 0 ? M : 1, n_k, n_v).total;
 }
 
-void det_gdn_ex(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a,
-                const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
-                float* gin, float* gout, cudaStream_t st) {
+static void gdn_entry(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_state* rows, const float* qkv, const float* z,
+                      const float* a, const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on,
+                      void* scratch, float* gin, float* gout, cudaStream_t st) {
     if (M <= 0) return;
     DETB_REQUIRE(dk == DK && dv == DV, "Gated DeltaNet kernels are built for dk = dv = 128");
     DETB_REQUIRE(n_k > 0 && n_v % n_k == 0, "n_v must be a multiple of n_k");
@@ -243,7 +255,9 @@ void det_gdn_ex(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, cons
     uint8_t* base = static_cast<uint8_t*>(scratch);
     GdnArgs g;
     g.conv = L->conv; g.A = L->A; g.dt_bias = L->dt_bias; g.norm = L->norm;
-    g.conv_state = S->conv_state; g.S = S->S;
+    g.rows = rows;
+    g.conv_state = S ? S->conv_state : nullptr;
+    g.S = S ? S->S : nullptr;
     g.qkv = qkv; g.z = z; g.a = a; g.b = b;
     g.eps = eps; g.M = M; g.n_k = n_k; g.n_v = n_v; g.rep = n_v / n_k;
     g.conv_dim = 2 * n_k * DK + n_v * DV;
@@ -256,9 +270,23 @@ void det_gdn_ex(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, cons
     cudaStream_t q = queue_of(st);
     const int heads = 2 * n_k + n_v;
     launch_pdl(k_gdn_prep, dim3((heads + 3) / 4, M), dim3(128), 0, q, 1, g);
-    launch_pdl(k_gdn_recur, dim3(n_v * (DV / RC)), dim3(RC * RL), 0, q, 1, g);
+    launch_pdl(k_gdn_recur, dim3(n_v * (DV / RC), rows ? M : 1), dim3(RC * RL), 0, q, 1, g);
     const int row_blocks = (int)(((long long)M * n_v + 3) / 4);
-    launch_pdl(k_gdn_out, dim3(row_blocks + (g.conv_dim + 127) / 128), dim3(128), 0, q, 1, g, row_blocks);
+    const int state_blocks = ((g.conv_dim + 127) / 128) * (rows ? M : 1);
+    launch_pdl(k_gdn_out, dim3(row_blocks + state_blocks), dim3(128), 0, q, 1, g, row_blocks);
+}
+
+void det_gdn_ex(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a,
+                const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
+                float* gin, float* gout, cudaStream_t st) {
+    gdn_entry(L, S, nullptr, qkv, z, a, b, eps, M, n_k, n_v, dk, dv, on, scratch, gin, gout, st);
+}
+// Batched decode (no reference counterpart): M sequences advance one token each; row t of the inputs belongs to the
+// sequence with state rows[t] (a DEVICE array of M det_gdn_state).  Each row equals det_gdn(M = 1) on that state.
+void det_gdn_rows(const det_gdn_layer* L, const det_gdn_state* rows, const float* qkv, const float* z, const float* a,
+                  const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
+                  cudaStream_t st) {
+    gdn_entry(L, nullptr, rows, qkv, z, a, b, eps, M, n_k, n_v, dk, dv, on, scratch, nullptr, nullptr, st);
 }
 
 void det_gdn(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a,

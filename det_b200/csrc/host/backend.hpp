@@ -124,6 +124,14 @@ struct GdnShape {
     float eps;
 };
 
+// The per-sequence caches (attention layer) or states (GDN layer) behind the rows of a batched decode step: row b of
+// the step's activations is the current token of sequence b.  A backend may attach its own lookup tables.
+struct RowSet {
+    virtual ~RowSet() = default;
+    std::vector<const KvCache*> kv;
+    std::vector<const GdnState*> st;
+};
+
 // backend.rs:203-302
 class Backend {
   public:
@@ -162,6 +170,34 @@ class Backend {
     // SwiGLU product without quantization (h[i] = silu_f(g[i]) * u[i]) — each exactly one spec operation per element.
     virtual void add(const Buf<float>& x, const Buf<float>& y, size_t n) = 0;
     virtual void silu_mul(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<float>& h) = 0;
+    // Batched serving decode (not in the reference trait, whose Model holds one sequence): `rows` sequences advance one
+    // token each.  Row b of qg/k/v/o (or qkv/z/a/b/on) belongs to sequence b, with its own cache or state and its own
+    // position pos[b] (a backend buffer of rows int32).  The defaults compose the step from the unchanged single-
+    // sequence ops on row views — each row is exactly attention(m=1, pos0=pos[b]) / gdn(m=1) of its sequence; a backend
+    // may override them with one launch over all rows (same values).
+    virtual std::unique_ptr<RowSet> make_rowset(std::vector<const KvCache*> kv, std::vector<const GdnState*> st) {
+        auto r = std::make_unique<RowSet>();
+        r->kv = std::move(kv);
+        r->st = std::move(st);
+        return r;
+    }
+    virtual void attention_rows(const AttnLayer& l, const RowSet& rows, const Buf<int32_t>& pos, size_t max_pos,
+                                const Shape& s /* m = rows; pos0 unused */, const Buf<float>& qg, const Buf<float>& k,
+                                const Buf<float>& v, const Buf<float>& o);
+    virtual void gdn_rows(const GdnLayer& l, const RowSet& rows, const GdnShape& s /* m = rows */, const Buf<float>& qkv,
+                          const Buf<float>& z, const Buf<float>& a, const Buf<float>& b, const Buf<float>& on);
+    // argmax / sample of `rows` logits rows at once (row r uses draw z[r]); the defaults loop over the single-row ops.
+    virtual std::vector<int32_t> argmax_rows(const Buf<float>& logits, size_t rows, size_t v) {
+        std::vector<int32_t> out(rows);
+        for (size_t r = 0; r < rows; r++) out[r] = argmax(Buf<float>::view(logits.ptr_at(r * v), v), v);
+        return out;
+    }
+    virtual std::vector<int32_t> sample_rows(const Buf<float>& logits, size_t rows, size_t v, float inv_temp, size_t top_k,
+                                             float top_p, const std::vector<uint64_t>& z) {
+        std::vector<int32_t> out(rows);
+        for (size_t r = 0; r < rows; r++) out[r] = sample(Buf<float>::view(logits.ptr_at(r * v), v), v, inv_temp, top_k, top_p, z[r]);
+        return out;
+    }
     virtual int32_t argmax(const Buf<float>& logits, size_t v) = 0;
     virtual int32_t sample(const Buf<float>& logits, size_t v, float inv_temp, size_t top_k, float top_p,
                            uint64_t z) = 0;
@@ -196,6 +232,30 @@ class Backend {
     template <class T>
     void zero(const Buf<T>& b) { zero_bytes(b.ptr(), b.bytes()); }
 };
+
+inline void Backend::attention_rows(const AttnLayer& l, const RowSet& rows, const Buf<int32_t>& pos, size_t,
+                                    const Shape& s, const Buf<float>& qg, const Buf<float>& k, const Buf<float>& v,
+                                    const Buf<float>& o) {
+    std::vector<int32_t> p(s.m);
+    read(pos, 0, p.data(), s.m);
+    for (size_t b = 0; b < s.m; b++) {
+        Shape one{1, (size_t)p[b], s.n_h, s.n_kv, s.hd, s.rot, s.eps};
+        attention(l, *rows.kv[b], one, Buf<float>::view(qg.ptr_at(b * s.n_h * 2 * s.hd), s.n_h * 2 * s.hd),
+                  Buf<float>::view(k.ptr_at(b * s.n_kv * s.hd), s.n_kv * s.hd),
+                  Buf<float>::view(v.ptr_at(b * s.n_kv * s.hd), s.n_kv * s.hd),
+                  Buf<float>::view(o.ptr_at(b * s.n_h * s.hd), s.n_h * s.hd));
+    }
+}
+inline void Backend::gdn_rows(const GdnLayer& l, const RowSet& rows, const GdnShape& s, const Buf<float>& qkv,
+                              const Buf<float>& z, const Buf<float>& a, const Buf<float>& b, const Buf<float>& on) {
+    const size_t conv_dim = 2 * s.n_k * s.dk + s.n_v * s.dv, vd = s.n_v * s.dv;
+    for (size_t r = 0; r < s.m; r++) {
+        GdnShape one{1, s.n_k, s.n_v, s.dk, s.dv, s.eps};
+        gdn(l, *rows.st[r], one, Buf<float>::view(qkv.ptr_at(r * conv_dim), conv_dim), Buf<float>::view(z.ptr_at(r * vd), vd),
+            Buf<float>::view(a.ptr_at(r * s.n_v), s.n_v), Buf<float>::view(b.ptr_at(r * s.n_v), s.n_v),
+            Buf<float>::view(on.ptr_at(r * vd), vd), GdnExport{});
+    }
+}
 
 template <class T>
 void Buf<T>::release() {

@@ -3,6 +3,7 @@
 #include "cuda_backend.hpp"
 #include "graph_decode.hpp"
 #include "model.hpp"
+#include "serve.hpp"
 #include <cstring>
 #include <string>
 
@@ -194,6 +195,49 @@ size_t dh_graph_decoder_finish(void* d, int32_t* out, size_t cap) {
     std::vector<int32_t> ids = static_cast<det::GraphDecoder*>(d)->finish();
     std::memcpy(out, ids.data(), (ids.size() < cap ? ids.size() : cap) * sizeof(int32_t));
     return ids.size();
+}
+
+// Measurement switch of the CUDA backend: 0 composes a batched step from per-sequence attention / GDN calls.
+void dh_cuda_set_fuse_rows(void* backend, int on) {
+    if (auto* c = dynamic_cast<det::CudaBackend*>(static_cast<det::Backend*>(backend))) c->fuse_rows = on != 0;
+}
+// ---- batched serving decode (serve.hpp)
+void* dh_batch_new(void* model, size_t n_seq, size_t ctx) {
+    try {
+        return new det::BatchDecoder(*static_cast<det::Model*>(model), n_seq, ctx);
+    } catch (const std::exception& ex) {
+        g_err = ex.what();
+        return nullptr;
+    }
+}
+void dh_batch_free(void* b) { delete static_cast<det::BatchDecoder*>(b); }
+int dh_batch_prefill(void* b, size_t i, const int32_t* ids, size_t n, int greedy, float inv_temp, size_t top_k, float top_p,
+                     uint64_t seed) {
+    return guarded([&] {
+        det::Sampling s;
+        s.greedy = greedy != 0;
+        s.inv_temp = inv_temp;
+        s.top_k = top_k;
+        s.top_p = top_p;
+        s.rng = seed;
+        return static_cast<det::BatchDecoder*>(b)->prefill(i, ids, n, s);
+    });
+}
+int dh_batch_step(void* b, size_t steps) {
+    return guarded([&] {
+        for (size_t i = 0; i < steps; i++) {
+            std::string e = static_cast<det::BatchDecoder*>(b)->step();
+            if (!e.empty()) return e;
+        }
+        return std::string();
+    });
+}
+// Tokens produced so far by sequence i (the first one comes from the prefill); returns their number.
+size_t dh_batch_tokens(void* b, size_t i, int32_t* out, size_t cap) {
+    const std::vector<int32_t>& t = static_cast<det::BatchDecoder*>(b)->seqs[i].out;
+    const size_t n = std::min(cap, t.size());
+    std::memcpy(out, t.data(), n * sizeof(int32_t));
+    return t.size();
 }
 
 // One decoded token's GEMVs, `reps` times, without syncing in between (the caller times it with events on the queue).

@@ -269,6 +269,85 @@ void CudaBackend::gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, 
                ST);
 }
 
+std::vector<int32_t> CudaBackend::argmax_rows(const Buf<float>& logits, size_t rows, size_t v) {
+    if (!fuse_rows) return Backend::argmax_rows(logits, rows, v);
+    flush_pending();
+    if (picks_.len() < rows) picks_ = alloc<int32_t>(rows);
+    det_argmax(logits.ptr(), (int)rows, (int)v, picks_.ptr(), ST);
+    std::vector<int32_t> out(rows);
+    read(picks_, 0, out.data(), rows);
+    return out;
+}
+std::vector<int32_t> CudaBackend::sample_rows(const Buf<float>& logits, size_t rows, size_t v, float inv_temp, size_t top_k,
+                                              float top_p, const std::vector<uint64_t>& z) {
+    if (!fuse_rows) return Backend::sample_rows(logits, rows, v, inv_temp, top_k, top_p, z);
+    flush_pending();
+    if (picks_.len() < rows) picks_ = alloc<int32_t>(rows);
+    if (zs_.len() < rows) zs_ = alloc<uint64_t>(rows);
+    write(zs_, 0, z.data(), rows);
+    const unsigned long long* zp = reinterpret_cast<const unsigned long long*>(zs_.ptr());
+    if (top_k == 0 && top_p >= 1.0f) {
+        det_sample(logits.ptr(), (int)rows, (int)v, inv_temp, zp, picks_.ptr(), ST);
+    } else {
+        void* sc = scratch(sample_scratch_, det_sample_scratch_bytes((int)rows, (int)v));
+        det_sample_topkp(logits.ptr(), (int)rows, (int)v, inv_temp, (int)top_k, top_p, zp, picks_.ptr(), sc, ST);
+    }
+    std::vector<int32_t> out(rows);
+    read(picks_, 0, out.data(), rows);
+    return out;
+}
+
+// ---- batched decode: device tables of the per-sequence caches / states of one layer
+namespace {
+struct CudaRowSet : RowSet {
+    Buf<uint8_t> table;   // det_kv_cache[rows] or det_gdn_state[rows] in device memory
+};
+}  // namespace
+
+std::unique_ptr<RowSet> CudaBackend::make_rowset(std::vector<const KvCache*> kv, std::vector<const GdnState*> st) {
+    auto r = std::make_unique<CudaRowSet>();
+    if (!kv.empty()) {
+        std::vector<det_kv_cache> t;
+        for (const KvCache* c : kv) t.push_back(det_kv_cache{c->kq.ptr(), c->sk.ptr(), c->vq.ptr(), (int)c->capacity, nullptr, nullptr});
+        r->table = upload(reinterpret_cast<const uint8_t*>(t.data()), t.size() * sizeof(det_kv_cache));
+    } else {
+        std::vector<det_gdn_state> t;
+        for (const GdnState* g : st) t.push_back(det_gdn_state{g->conv_state.ptr(), g->s.ptr()});
+        r->table = upload(reinterpret_cast<const uint8_t*>(t.data()), t.size() * sizeof(det_gdn_state));
+    }
+    r->kv = std::move(kv);
+    r->st = std::move(st);
+    return r;
+}
+
+void CudaBackend::attention_rows(const AttnLayer& l, const RowSet& rows, const Buf<int32_t>& pos, size_t max_pos,
+                                 const Shape& s, const Buf<float>& qg, const Buf<float>& k, const Buf<float>& v,
+                                 const Buf<float>& o) {
+    const CudaRowSet* rs = dynamic_cast<const CudaRowSet*>(&rows);
+    if (!fuse_rows || !rs) return Backend::attention_rows(l, rows, pos, max_pos, s, qg, k, v, o);
+    if (skip_mask & 16) return;
+    flush_pending();
+    for (const KvCache* c : rows.kv)
+        if (max_pos + 1 > c->capacity) throw std::runtime_error("a sequence's position exceeds its cache");
+    det_attn_layer layer{l.q_norm->ptr(), l.k_norm->ptr(), l.v_scale->ptr(), l.v_inv_scale->ptr()};
+    void* sc = scratch(attn_scratch_, det_attn_scratch_bytes((int)s.m, (int)s.n_h, (int)s.hd));
+    det_attention_rows(&layer, reinterpret_cast<const det_kv_cache*>(rs->table.ptr()), pos.ptr(), (int)max_pos, qg.ptr(),
+                       k.ptr(), v.ptr(), l.rope_cos->ptr(), l.rope_sin->ptr(), (int)s.rot, s.eps, (int)s.m, (int)s.n_h,
+                       (int)s.n_kv, (int)s.hd, o.ptr(), sc, ST);
+}
+
+void CudaBackend::gdn_rows(const GdnLayer& l, const RowSet& rows, const GdnShape& s, const Buf<float>& qkv,
+                           const Buf<float>& z, const Buf<float>& a, const Buf<float>& b, const Buf<float>& on) {
+    const CudaRowSet* rs = dynamic_cast<const CudaRowSet*>(&rows);
+    if (!fuse_rows || !rs) return Backend::gdn_rows(l, rows, s, qkv, z, a, b, on);
+    if (skip_mask & 32) return;
+    flush_pending();
+    det_gdn_layer layer{l.conv->ptr(), l.a->ptr(), l.dt_bias->ptr(), l.norm->ptr()};
+    void* sc = scratch(gdn_scratch_, det_gdn_scratch_bytes((int)s.m, (int)s.n_k, (int)s.n_v, (int)s.dk, (int)s.dv));
+    det_gdn_rows(&layer, reinterpret_cast<const det_gdn_state*>(rs->table.ptr()), qkv.ptr(), z.ptr(), a.ptr(), b.ptr(), s.eps,
+                 (int)s.m, (int)s.n_k, (int)s.n_v, (int)s.dk, (int)s.dv, on.ptr(), sc, ST);
+}
+
 void CudaBackend::add(const Buf<float>& x, const Buf<float>& y, size_t n) {
     flush_pending();
     det_add(x.ptr(), y.ptr(), (long long)n, ST);

@@ -41,6 +41,17 @@ class CudaBackend : public Backend {
                    const Buf<float>& v, const Buf<float>& o) override;
     void gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, const Buf<float>& qkv, const Buf<float>& z,
              const Buf<float>& a, const Buf<float>& b, const Buf<float>& on, const GdnExport& ex) override;
+    // batched decode: one launch sequence over all rows (det_attention_rows / det_gdn_rows); `fuse_rows = false` falls back
+    // to the composed per-row calls of the base class (measurement switch; same values)
+    std::unique_ptr<RowSet> make_rowset(std::vector<const KvCache*> kv, std::vector<const GdnState*> st) override;
+    void attention_rows(const AttnLayer& l, const RowSet& rows, const Buf<int32_t>& pos, size_t max_pos, const Shape& s,
+                        const Buf<float>& qg, const Buf<float>& k, const Buf<float>& v, const Buf<float>& o) override;
+    void gdn_rows(const GdnLayer& l, const RowSet& rows, const GdnShape& s, const Buf<float>& qkv, const Buf<float>& z,
+                  const Buf<float>& a, const Buf<float>& b, const Buf<float>& on) override;
+    std::vector<int32_t> argmax_rows(const Buf<float>& logits, size_t rows, size_t v) override;
+    std::vector<int32_t> sample_rows(const Buf<float>& logits, size_t rows, size_t v, float inv_temp, size_t top_k,
+                                     float top_p, const std::vector<uint64_t>& z) override;
+    bool fuse_rows = true;
     void add(const Buf<float>& x, const Buf<float>& y, size_t n) override;
     void silu_mul(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<float>& h) override;
     int32_t argmax(const Buf<float>& logits, size_t v) override;
@@ -90,8 +101,8 @@ class CudaBackend : public Backend {
     void* scratch(Buf<uint8_t>& slot, size_t bytes);
     void finish_linear(CudaLinear& l);
     Buf<uint8_t> attn_scratch_, gdn_scratch_, sample_scratch_, synth_scratch_;
-    Buf<int32_t> pick_;
-    Buf<uint64_t> z_;
+    Buf<int32_t> pick_, picks_;
+    Buf<uint64_t> z_, zs_;
 };
 
 std::vector<uint8_t> cuda_synth_det_rows(uint64_t seed, uint64_t tid, size_t src0, size_t n, size_t k, int bits);

@@ -447,21 +447,26 @@ std::string Model::forward(const int32_t* ids, size_t t) {
 
 std::vector<float> Model::logits() { return backend->download(w.logits); }
 
-std::string Model::pick(Sampling& s, int32_t& id) {
+std::string Model::pick(Sampling& s, int32_t& id) { return pick_row(w.logits, s, id); }
+
+std::string Model::pick_row(const Buf<float>& row, Sampling& s, int32_t& id) {
     if (s.greedy) {
-        id = backend->argmax(w.logits, cfg.vocab);
+        id = backend->argmax(row, cfg.vocab);
         return "";
     }
     if (!std::isfinite(s.inv_temp) || std::isnan(s.top_p))
         return "sampling parameters inv_temp=" + std::to_string(s.inv_temp) + " top_p=" + std::to_string(s.top_p) +
                " are not finite";
+    id = backend->sample(row, cfg.vocab, s.inv_temp, s.top_k, s.top_p, next_draw(s));
+    return "";
+}
+
+uint64_t Model::next_draw(Sampling& s) {
     s.rng += 0x9E3779B97F4A7C15ull;   // splitmix64 (spec/prim.rs:207-215): the state advances once per draw
     uint64_t z = s.rng;
     z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
     z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-    z ^= z >> 31;
-    id = backend->sample(w.logits, cfg.vocab, s.inv_temp, s.top_k, s.top_p, z);
-    return "";
+    return z ^ (z >> 31);
 }
 
 std::string Model::prefill(const int32_t* ids, size_t n) {

@@ -79,6 +79,8 @@ class Model {
     std::string forward(const int32_t* ids, size_t t);               // model.rs:439-465
     std::vector<float> logits();                                     // model.rs:467-470
     std::string pick(Sampling& s, int32_t& id);                      // model.rs:472-496
+    std::string pick_row(const Buf<float>& logits_row, Sampling& s, int32_t& id);   // the same draw on a given logits row
+    static uint64_t next_draw(Sampling& s);   // advances the generator once, returns z (model.rs:484-485)
     std::string prefill(const int32_t* ids, size_t n);               // model.rs:498-508
     std::string generate(const int32_t* prompt, size_t n_prompt, size_t n_new, Sampling s,
                          const std::vector<int32_t>& stop, std::vector<int32_t>& out,

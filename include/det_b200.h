@@ -207,6 +207,17 @@ void det_graph_free(void* graph);
  * All pointers are device pointers.                                                                                  */
 void det_token_feedback(const int* pick, int* pos, int* log, int log_base, int log_cap, cudaStream_t st);
 
+/* Batched serving decode (no reference counterpart: its Model holds one sequence).  M sequences advance one token each;
+ * row t of the activations belongs to the sequence whose cache / state is rows[t] — a DEVICE array of M structs — and,
+ * for attention, whose position is pos[t] (device array; max_pos is a host bound on them).  Row t equals
+ * det_attention(M = 1, pos0 = pos[t]) / det_gdn(M = 1) on that sequence.  Scratch as for the single-sequence calls.  */
+void det_attention_rows(const det_attn_layer* L, const det_kv_cache* rows, const int* pos, int max_pos, const float* qg,
+                        const float* k, const float* v, const float* rope_cos, const float* rope_sin, int rot, float eps,
+                        int M, int n_h, int n_kv, int hd, float* o, void* scratch, cudaStream_t st);
+void det_gdn_rows(const det_gdn_layer* L, const det_gdn_state* rows, const float* qkv, const float* z, const float* a,
+                  const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
+                  cudaStream_t st);
+
 /* Tensor-parallel exchange over NVLink peer memory (no reference counterpart: the reference is single-device).  Every
  * rank creates a staging area of the same size, publishes its CUDA IPC handle (64 bytes) and opens the others'.
  * det_xchg_all_gather sends local[M][slice] to every rank as self-validating 16-byte packets (plain peer stores) and

@@ -98,3 +98,28 @@ def test_long_context_decode_equals_chunked_prefill(libs, cuda_backend):
     finally:
         h.dh_model_free(a)
         h.dh_model_free(b)
+
+
+def test_4b_chunking_1_64_512(libs, cuda_backend):
+    """BASELINE configs[2] shape (4B: 32 layers, hidden 2560, vocabulary 248320): a 512-token prompt prefilled in
+    chunks of 512 (tensor-core GEMM), 64 and 1 (streaming GEMV), then 32 greedy tokens; last-position logits and all
+    tokens must be the same bits for the three chunkings."""
+    h = libs.host()
+    vocab = 248320
+    ids = _prompt(h, 512, vocab)
+    results = []
+    for chunk in (512, 64, 1):
+        m = _model(h, cuda_backend, chunk, cfg=b"4b", max_ctx=512 + 40)
+        try:
+            assert h.dh_model_prefill(m, ids.ctypes.data, 512) == 0, h.dh_last_error()
+            logits = np.zeros(vocab, np.float32)
+            h.dh_model_logits(m, logits.ctypes.data, logits.size)
+            h.dh_model_reset(m)
+            toks = _greedy(h, m, ids, 32)
+            results.append((logits.view(np.uint32).copy(), toks.copy()))
+        finally:
+            h.dh_model_free(m)
+    for lg, tk in results[1:]:
+        assert np.array_equal(lg, results[0][0]), f"{(lg != results[0][0]).sum()} logits differ"
+        assert np.array_equal(tk, results[0][1]), (tk, results[0][1])
+    assert libs.cuda().det_last_error() == 0

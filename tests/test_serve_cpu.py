@@ -1,0 +1,54 @@
+"""Batched serving decode on the CPU reference backend: four sequences of different prompt lengths advance together
+(rows stacked for the linears, attention / Gated DeltaNet per row against each sequence's own cache and state, one
+sampler state per sequence).  Every stream must equal the stream that sequence produces alone."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+SEED = 20261125
+VOCAB = 32768
+PROMPTS = [5, 17, 33, 9]
+SAMPLING = dict(greedy=0, inv_temp=1.0 / 0.7, top_k=40, top_p=0.95)
+
+
+def _prompt(h, seed, n):
+    ids = np.zeros(n, np.int32)
+    h.dh_synth_prompt(seed, n, VOCAB, ids.ctypes.data)
+    return ids
+
+
+def run_streams(h, backend, n_new, layers=4, ctx=64):
+    """(batched streams, solo streams) for the prompts above."""
+    model = h.dh_model_new_synth(backend, b"tiny", layers, SEED, ctx, 16)
+    assert model, h.dh_last_error()
+    solo = []
+    for i, n in enumerate(PROMPTS):
+        ids = _prompt(h, 100 + i, n)
+        out = np.zeros(n_new, np.int32)
+        cnt = C.c_size_t(0)
+        assert h.dh_model_reset(model) == 0
+        assert h.dh_model_generate(model, ids.ctypes.data, n, n_new, SAMPLING["greedy"], SAMPLING["inv_temp"],
+                                   SAMPLING["top_k"], SAMPLING["top_p"], 7000 + i, out.ctypes.data, C.byref(cnt)) == 0, h.dh_last_error()
+        solo.append(out[: cnt.value].copy())
+    batch = h.dh_batch_new(model, len(PROMPTS), ctx)
+    assert batch, h.dh_last_error()
+    for i, n in enumerate(PROMPTS):
+        ids = _prompt(h, 100 + i, n)
+        assert h.dh_batch_prefill(batch, i, ids.ctypes.data, n, SAMPLING["greedy"], SAMPLING["inv_temp"],
+                                  SAMPLING["top_k"], SAMPLING["top_p"], 7000 + i) == 0, h.dh_last_error()
+    assert h.dh_batch_step(batch, n_new - 1) == 0, h.dh_last_error()
+    together = []
+    for i in range(len(PROMPTS)):
+        out = np.zeros(n_new, np.int32)
+        assert h.dh_batch_tokens(batch, i, out.ctypes.data, n_new) == n_new
+        together.append(out)
+    h.dh_batch_free(batch)
+    h.dh_model_free(model)
+    return together, solo
+
+
+def test_batched_streams_equal_solo_streams_on_the_reference_backend(libs, ref_backend):
+    together, solo = run_streams(libs.host(), ref_backend, n_new=6)
+    for i, (a, b) in enumerate(zip(together, solo)):
+        assert np.array_equal(a, b), (i, a, b)
