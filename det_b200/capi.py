@@ -118,6 +118,7 @@ CUDA_ABI = {
                                           c_void_p, c_void_p, c_void_p, c_void_p]),
     "det_xchg_quant": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "det_debug_set_pdl": (None, [c_int]),
+    "det_debug_set_tc_variant": (None, [c_int]),
     "det_last_error": (c_int, []),
 }
 

@@ -247,9 +247,31 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_max(const AttnArgs a) {
 }
 
 template <int HD>
+struct AccSmem {
+    static constexpr int KTILE = KT * KTile<HD>::STRIDE;
+    static constexpr int VTILE = KT * HD * 2;
+    static constexpr int TOTAL = KTILE + VTILE;
+};
+
+// V tile (KT keys x HD int16) into shared memory with asynchronous 16-byte copies; rows past nkeys are not touched.
+template <int HD>
+__device__ __forceinline__ void fetch_v_async(int16_t* vtile, const AttnArgs& a, const RowCache& c, int kvh, int key0, int nkeys) {
+    constexpr int VEC = HD / 8;                          // 16-byte pieces per row
+    for (int i = threadIdx.x; i < nkeys * VEC; i += ATT_THREADS) {
+        const int q = i / VEC, v = i % VEC;
+        const int16_t* src = c.vq + ((size_t)(key0 + q) * a.n_kv + kvh) * HD + v * 8;
+        const unsigned dst = (unsigned)__cvta_generic_to_shared(vtile + q * HD + v * 8);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
     static_assert(HD <= ATT_THREADS, "one thread per value dimension");
-    __shared__ __align__(16) int8_t ktile[KT * KTile<HD>::STRIDE];
+    extern __shared__ __align__(16) uint8_t asm_[];
+    int8_t* ktile = reinterpret_cast<int8_t*>(asm_);
+    int16_t* vtile = reinterpret_cast<int16_t*>(asm_ + AccSmem<HD>::KTILE);
     __shared__ __align__(16) int8_t qs[MAX_REP * HD];
     __shared__ float sks[KT];
     __shared__ float sqs[MAX_REP];
@@ -280,7 +302,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
     for (int r = 0; r < MAX_REP; r++) num[r] = 0;
     for (int key0 = k0; key0 < k1; key0 += KT) {
         const int nkeys = min(KT, k1 - key0);
-        __syncthreads();
+        __syncthreads();                                   // the previous tile's K, V and pq are no longer read
+        fetch_v_async<HD>(vtile, a, cache, kvh, key0, nkeys);   // in flight while the scores are computed
         KTile<HD>::load(ktile, sks, a, cache, kvh, key0, nkeys);
         __syncthreads();
 #pragma unroll
@@ -296,6 +319,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
                 pq[r][j] = p;
             }
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         if (threadIdx.x < rep) {
             long long s = 0;
@@ -303,10 +327,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
             den_sh[threadIdx.x] += s;
         }
         if (d < HD) {
-            const int16_t* vcol = cache.vq + ((size_t)key0 * a.n_kv + kvh) * HD + d;
-            const size_t vstride = (size_t)a.n_kv * HD;
             for (int q = 0; q < nkeys; q++) {
-                const int vv = vcol[q * vstride];
+                const int vv = vtile[q * HD + d];
 #pragma unroll
                 for (int r = 0; r < MAX_REP; r++)
                     if (r < rep) num[r] += (long long)pq[r][q] * (long long)vv;
@@ -398,18 +420,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_dec(const AttnArgs a) {
     const int rep = a.rep;
     const size_t vstride = (size_t)a.n_kv * HD;            // int16 elements between consecutive keys
 
-    // first V tile: asynchronous 16-byte copies, consumed in pass 2
-    auto fetch_v_async = [&](int key0, int nkeys) {
-        constexpr int VEC = HD / 8;                          // 16-byte pieces per row
-        for (int i = threadIdx.x; i < nkeys * VEC; i += ATT_THREADS) {
-            const int q = i / VEC, v = i % VEC;
-            const int16_t* src = cache.vq + ((size_t)(key0 + q) * a.n_kv + kvh) * HD + v * 8;
-            const unsigned dst = (unsigned)__cvta_generic_to_shared(vtile + q * HD + v * 8);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    fetch_v_async(k0, min(KT, k1 - k0));
+    // first V tile: asynchronous copies, consumed in pass 2
+    fetch_v_async<HD>(vtile, a, cache, kvh, k0, min(KT, k1 - k0));
 
     for (int i = threadIdx.x; i < rep * HD / 16; i += ATT_THREADS)
         reinterpret_cast<uint4*>(qs)[i] =
@@ -618,9 +630,22 @@ static void run_attention(AttnArgs a, void* scratch, int max_total_keys, cudaStr
             return;
         }
     }
+    if (a.rows) {
+        // batched step: the sequences' lengths differ (only their maximum is known here), so cut fixed 512-key ranges
+        // and let the CTAs past a sequence's end return at once
+        const int tps = 8;
+        nsplit = (tiles + tps - 1) / tps;
+        a.nsplit = nsplit;
+        a.keys_per_split = tps * KT;
+    }
     const dim3 grid(nsplit, a.n_kv, a.M);
+    static bool acc_attr = false;
+    if (!acc_attr) {
+        DETB_CUDA_OK(cudaFuncSetAttribute(k_attn_acc<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, AccSmem<HD>::TOTAL));
+        acc_attr = true;
+    }
     launch_pdl(k_attn_max<HD>, grid, dim3(ATT_THREADS), 0, q, 1, a);
-    launch_pdl(k_attn_acc<HD>, grid, dim3(ATT_THREADS), 0, q, 1, a);
+    launch_pdl(k_attn_acc<HD>, grid, dim3(ATT_THREADS), AccSmem<HD>::TOTAL, q, 1, a);
     if (nsplit > 1) launch_pdl(k_attn_fin<HD>, dim3(a.M * a.n_h), dim3(HD), 0, q, 1, a);
 }
 

@@ -109,8 +109,10 @@ constexpr int RC = 16;    // columns per CTA
 constexpr int RL = 8;     // lanes per column
 constexpr int RR = DK / RL;   // rows per lane (16)
 
+constexpr int SLAB_STRIDE = RC + 4;   // floats per slab row: rows stay 16-byte aligned for the asynchronous copies
+
 __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
-    __shared__ float slab[DK][RC + 1];
+    __shared__ __align__(16) float slab[DK][SLAB_STRIDE];
     pdl_trigger();
     pdl_wait();
     const int h = blockIdx.x / (DV / RC);
@@ -121,11 +123,14 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
     float* Sh = (g.rows ? g.rows[blockIdx.y].S : g.S) + (size_t)h * DK * DV;
     const int t_begin = g.rows ? blockIdx.y : 0, t_end = g.rows ? blockIdx.y + 1 : g.M;
 
-    for (int i = threadIdx.x; i < DK * RC; i += RC * RL) slab[i / RC][i % RC] = Sh[(size_t)(i / RC) * DV + j0 + (i % RC)];
-    __syncthreads();
-    float s[RR];
-#pragma unroll
-    for (int i = 0; i < RR; i++) s[i] = slab[p * RR + i][jj];
+    // the CTA's 128 x 16 slab of the state: 16-byte asynchronous copies (4 per thread), in flight while the first
+    // token's operands are fetched
+    for (int i = threadIdx.x; i < DK * (RC / 4); i += RC * RL) {
+        const int row = i / (RC / 4), v = i % (RC / 4);
+        const unsigned dst = (unsigned)__cvta_generic_to_shared(&slab[row][v * 4]);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(Sh + (size_t)row * DV + j0 + v * 4) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
 
     const size_t ystride = g.conv_dim;
     const float* qrow = g.y + (size_t)kh * DK + p * RR;
@@ -147,6 +152,11 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
         de[b] = g.decay[(size_t)t * g.n_v + h];
     };
     fetch(t_begin, 0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    float s[RR];
+#pragma unroll
+    for (int i = 0; i < RR; i++) s[i] = slab[p * RR + i][jj];
 #pragma unroll 1
     for (int t = t_begin; t < t_end; t += 2) {
 #pragma unroll
@@ -176,7 +186,10 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
 #pragma unroll
     for (int i = 0; i < RR; i++) slab[p * RR + i][jj] = s[i];
     __syncthreads();
-    for (int i = threadIdx.x; i < DK * RC; i += RC * RL) Sh[(size_t)(i / RC) * DV + j0 + (i % RC)] = slab[i / RC][i % RC];
+    for (int i = threadIdx.x; i < DK * (RC / 4); i += RC * RL) {
+        const int row = i / (RC / 4), v = i % (RC / 4);
+        *reinterpret_cast<float4*>(Sh + (size_t)row * DV + j0 + v * 4) = *reinterpret_cast<const float4*>(&slab[row][v * 4]);
+    }
 }
 
 // on = rmsnorm(o, norm, eps) * silu_f(z): one warp per (token, v head).  Extra CTAs past the rows move the conv state.

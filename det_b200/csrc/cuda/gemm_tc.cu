@@ -5,12 +5,13 @@
 //
 // The inner sum of one 128-wide group is four UMMA steps (K = 32 bytes each) into a TMEM tile; the group multiplier
 // m * mx is a 32-bit integer that differs per (row, token, group), so every group's s32 tile is drained from TMEM and
-// folded into int64 registers by the epilogue warps while the tensor core already works on the next group in the
-// second TMEM buffer.  CTA tile: 128 weight rows (UMMA M, one TMEM lane per row) x 64 tokens (UMMA N).
+// folded into int64 registers by the epilogue warps while the tensor core already works on the following groups in the
+// other TMEM buffers (4 or 8 of them).  CTA tile: 128 weight rows (UMMA M, one TMEM lane per row) x 64 tokens (UMMA N).
 //
 // Warp roles (320 threads): warp 0 = TMA producer (one thread), warp 1 = TMEM allocation + MMA issue (one thread),
-// warps 2-9 = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31, half of the 64 token columns each).  Operands come from an int8-expanded row-major copy
-// of the weights (det_linear_expand) and from the int8 activations, both through 128-byte-swizzled TMA boxes, which is
+// warps 2.. = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31 and a block of the token columns).  Operands come from an
+// int8-expanded tile-major copy of the weights (det_linear_expand) and from the int8 activations, both through
+// 128-byte-swizzled TMA boxes, which is
 // the canonical K-major SWIZZLE_128B layout the UMMA shared-memory descriptor names.  No multicast anywhere.
 #include "gemm_common.cuh"
 #include <cuda.h>
@@ -22,14 +23,19 @@ constexpr int TC_KB = 128;        // bytes of K per stage = one quantization gro
 constexpr int TC_A_BYTES = TC_ROWS * TC_KB;   // 16 KB
 // Per token-tile width TOK (UMMA N, 64 or 128): TOK / 32 epilogue warps per TMEM lane quarter, 32 token columns each;
 // two TMEM accumulator buffers of TOK columns; as many stages as fit next to the multiplier table.
-template <int TOK>
+// EC = token columns per epilogue warp (8, 16 or 32): 4 * TOK / EC epilogue warps share a group's tile, so a narrower EC
+// shortens the per-group drain (what bounds a CTA's K loop) at the price of more threads.
+template <int TOK, int EC>
 struct TcCfg {
     static constexpr int B_BYTES = TOK * TC_KB;
     static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
-    static constexpr int STAGES = TOK == 64 ? 6 : 5;
-    static constexpr int EPI_WARPS = 4 * (TOK / 32);
+    static constexpr int STAGES = TOK <= 64 ? 6 : 5;
+    static constexpr int EPI_WARPS = 4 * (TOK / EC);
     static constexpr int THREADS = (2 + EPI_WARPS) * 32;
-    static constexpr int TMEM_COLS = 2 * TOK;
+    // TMEM accumulator buffers: the MMA warp runs up to NBUF groups ahead of the epilogue, which hides the
+    // commit -> mbarrier -> tcgen05.ld -> release round trip between the two
+    static constexpr int NBUF = TOK == 32 ? 8 : 4;
+    static constexpr int TMEM_COLS = NBUF * TOK;       // 256 or 512: a power of two
     // UMMA instruction descriptor (kind::i8): D = s32, A = B = signed 8-bit, both K-major, N = TOK, M = 128.
     static constexpr unsigned IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TOK >> 3) << 17) | ((TC_ROWS >> 4) << 24);
 };
@@ -64,7 +70,22 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, int (&r)[32]) {
+__device__ __forceinline__ void tmem_ld(unsigned taddr, int (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld(unsigned taddr, int (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld(unsigned taddr, int (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -101,33 +122,35 @@ struct TcArgs {
 };
 
 // Shared memory: [stages x (A 16 KB | B)] (1024-byte aligned) [mx table: G x TOK u16] [barriers] [tmem address]
-template <int TOK>
-__global__ void __launch_bounds__(TcCfg<TOK>::THREADS, 1)
+template <int TOK, int ECW>
+__global__ void __launch_bounds__(TcCfg<TOK, ECW>::THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
-    constexpr int TC_TOK = TOK, TC_STAGES = TcCfg<TOK>::STAGES, TC_STAGE_BYTES = TcCfg<TOK>::STAGE_BYTES;
-    constexpr int TC_EPI_WARPS = TcCfg<TOK>::EPI_WARPS, TC_TMEM_COLS = TcCfg<TOK>::TMEM_COLS;
+    using Cfg = TcCfg<TOK, ECW>;
+    constexpr int TC_TOK = TOK, TC_STAGES = Cfg::STAGES, TC_STAGE_BYTES = Cfg::STAGE_BYTES;
+    constexpr int TC_EPI_WARPS = Cfg::EPI_WARPS, TC_TMEM_COLS = Cfg::TMEM_COLS, NBUF = Cfg::NBUF;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* stages = smem;
-    uint16_t* mxs = reinterpret_cast<uint16_t*>(stages + TC_STAGES * TC_STAGE_BYTES);
+    uint16_t* mxs = reinterpret_cast<uint16_t*>(stages + TC_STAGES * TC_STAGE_BYTES);   // [G][TOK] token multipliers
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(
         (reinterpret_cast<uintptr_t>(mxs + (size_t)a.G * TC_TOK) + 15) & ~(uintptr_t)15);
     unsigned long long* full = bars;                       // [TC_STAGES]  TMA bytes landed
     unsigned long long* empty = bars + TC_STAGES;          // [TC_STAGES]  MMAs that read the stage are done
-    unsigned long long* tfull = bars + 2 * TC_STAGES;      // [2]          group result complete in TMEM buffer
-    unsigned long long* tempty = tfull + 2;                // [2]          epilogue drained the buffer
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(tempty + 2);
+    unsigned long long* tfull = bars + 2 * TC_STAGES;      // [NBUF]       group result complete in TMEM buffer
+    unsigned long long* tempty = tfull + NBUF;             // [NBUF]       epilogue drained the buffer
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(tempty + NBUF);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.x * TC_TOK, n0 = blockIdx.y * TC_ROWS;
     const int G = a.G;
+    pdl_trigger();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        for (int b = 0; b < 2; b++) {
+        for (int b = 0; b < NBUF; b++) {
             mbar_init(&tfull[b], 1);
             mbar_init(&tempty[b], TC_EPI_WARPS);
         }
@@ -146,16 +169,26 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     bool ok = true;
 
     if (warp == 0) {
-        // ---------------- TMA producer
+        // ---------------- TMA producer.  Weights do not depend on the previous kernel: the first stages' weight boxes are
+        // requested before griddepcontrol.wait, the activation boxes after it.
         if (lane == 0) {
-            int issued = 0;
-            for (int g = 0; g < G; g++, issued++) {
+            const int lead = G < TC_STAGES ? G : TC_STAGES;
+            for (int g = 0; g < lead; g++) {
+                uint8_t* st = stages + (size_t)g * TC_STAGE_BYTES;
+                mbar_expect_tx(&full[g], TC_STAGE_BYTES);
+                tma_load_2d(st, &map_w, 0, (blockIdx.y * G + g) * TC_ROWS, &full[g]);
+            }
+            pdl_wait();
+            for (int g = 0; g < lead; g++)
+                tma_load_2d(stages + (size_t)g * TC_STAGE_BYTES + TC_A_BYTES, &map_x, g * TC_KB, t0, &full[g]);
+            int issued = lead;
+            for (int g = lead; g < G; g++, issued++) {
                 const int s = g % TC_STAGES;
                 ok = mbar_wait(&empty[s], ((unsigned)(g / TC_STAGES) & 1u) ^ 1u);
                 if (!ok) break;
                 uint8_t* st = stages + (size_t)s * TC_STAGE_BYTES;
                 mbar_expect_tx(&full[s], TC_STAGE_BYTES);
-                tma_load_2d(st, &map_w, g * TC_KB, n0, &full[s]);
+                tma_load_2d(st, &map_w, 0, (blockIdx.y * G + g) * TC_ROWS, &full[s]);
                 tma_load_2d(st + TC_A_BYTES, &map_x, g * TC_KB, t0, &full[s]);
             }
             if (!ok) {
@@ -170,44 +203,48 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         // ---------------- MMA issue: four K = 32 steps per group into TMEM buffer g & 1
         if (lane == 0) {
             for (int g = 0; g < G; g++) {
-                const int s = g % TC_STAGES, b = g & 1;
+                const int s = g % TC_STAGES, b = g % NBUF;
                 ok = mbar_wait(&full[s], (unsigned)(g / TC_STAGES) & 1u) &&
-                     mbar_wait(&tempty[b], ((unsigned)(g >> 1) & 1u) ^ 1u);
+                     mbar_wait(&tempty[b], ((unsigned)(g / NBUF) & 1u) ^ 1u);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint8_t* st = stages + (size_t)s * TC_STAGE_BYTES;
                 const unsigned long long da = umma_desc(st), db = umma_desc(st + TC_A_BYTES);
 #pragma unroll
                 for (int k = 0; k < 4; k++)
-                    umma_i8(tmem_base + b * TC_TOK, da + 2 * k, db + 2 * k, TcCfg<TOK>::IDESC, k > 0 ? 1u : 0u);
+                    umma_i8(tmem_base + b * TC_TOK, da + 2 * k, db + 2 * k, Cfg::IDESC, k > 0 ? 1u : 0u);
                 umma_commit(&empty[s]);
                 umma_commit(&tfull[b]);
             }
             if (!ok) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
         }
     } else {
-        // ---------------- epilogue: thread = one weight row x 32 tokens, int64 accumulators in registers
-        constexpr int EC = 32;                         // token columns per epilogue warp
+        // ---------------- epilogue: thread = one weight row x EC tokens, int64 accumulators in registers
+        constexpr int EC = ECW;                        // token columns per epilogue warp
         const int q = warp & 3;                        // TMEM lane quarter this warp may read
         const int half = (warp - 2) >> 2;              // which block of 32 token columns
         const int n = n0 + q * 32 + lane;
         const int et = threadIdx.x - 64;
+        pdl_wait();   // activations, their multipliers and the output rows belong to the previous kernels
         for (int i = et; i < G * TC_TOK; i += TC_EPI_WARPS * 32) {
             const int g = i / TC_TOK, t = i - g * TC_TOK;
             mxs[i] = (a.mx && t0 + t < a.M) ? a.mx[(size_t)(t0 + t) * G + g] : (uint16_t)1;
         }
         asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
+        // Measured alternatives for the per-(row, token, group) step that did not pay: shifting the group sum to a
+        // non-negative value so that one unsigned multiply-add needs no sign fix (the sum of multipliers it needs costs
+        // as much as it saves), and more, narrower epilogue warps (same time per group).
         long long acc[EC];
 #pragma unroll
         for (int t = 0; t < EC; t++) acc[t] = 0;
         const uint16_t* mrow = a.m + (size_t)(n < a.N ? n : 0) * G;
         for (int g = 0; g < G; g++) {
-            const int b = g & 1;
-            ok = mbar_wait(&tfull[b], (unsigned)(g >> 1) & 1u);
+            const int b = g % NBUF;
+            ok = mbar_wait(&tfull[b], (unsigned)(g / NBUF) & 1u);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             int r[EC];
-            tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + b * TC_TOK + half * EC, r);
+            tmem_ld(tmem_base + ((unsigned)(q * 32) << 16) + b * TC_TOK + half * EC, r);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -238,23 +275,35 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                      : "memory");
 }
 
-// One thread per 32-code block: reference layout -> signed int8 codes, row-major [N][K].
-__global__ void k_expand_int8(const uint8_t* __restrict__ wq, int bits, long long nblocks, int8_t* __restrict__ dst) {
+// One thread per 32-code block: reference layout -> signed int8 codes in tile-major order
+// [N / 128 row tiles][K / 128 groups][128 rows][128 codes], so that the (row tile, group) box one TMA load fetches is 16 KB
+// of consecutive memory (whole DRAM pages, whole L2 lines) and a CTA's K loop streams forward.  The last row tile is
+// padded with zero rows.
+__global__ void k_expand_int8(const uint8_t* __restrict__ wq, int bits, int N, int K, int8_t* __restrict__ dst) {
     const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (id >= nblocks) return;
-    const uint8_t* blk = wq + (size_t)id * bytes_per_32(bits);
+    const int bpr = K / 32;                                  // 32-code blocks per row
+    const long long rows_padded = (long long)((N + TC_ROWS - 1) / TC_ROWS) * TC_ROWS;
+    if (id >= rows_padded * bpr) return;
+    const int n = (int)(id / bpr), kb = (int)(id % bpr);
     __align__(16) int8_t out[32];
-    for (int i = 0; i < 32; i++) {
-        int v;
-        if (bits == 8) v = (int8_t)blk[i];
-        else {
-            v = (i < 16) ? (blk[i] & 0xF) : (blk[i - 16] >> 4);
-            if (bits == 6) v |= ((blk[16 + (i & 7)] >> (2 * (i >> 3))) & 3) << 4;
-            v -= code_offset(bits);
+    if (n < N) {
+        const uint8_t* blk = wq + ((size_t)n * bpr + kb) * bytes_per_32(bits);
+        for (int i = 0; i < 32; i++) {
+            int v;
+            if (bits == 8) v = (int8_t)blk[i];
+            else {
+                v = (i < 16) ? (blk[i] & 0xF) : (blk[i - 16] >> 4);
+                if (bits == 6) v |= ((blk[16 + (i & 7)] >> (2 * (i >> 3))) & 3) << 4;
+                v -= code_offset(bits);
+            }
+            out[i] = (int8_t)v;
         }
-        out[i] = (int8_t)v;
+    } else {
+        for (int i = 0; i < 32; i++) out[i] = 0;
     }
-    uint4* d4 = reinterpret_cast<uint4*>(dst + (size_t)id * 32);
+    const int G = K / 128, g = kb >> 2, part = kb & 3;
+    const size_t off = ((((size_t)(n / TC_ROWS) * G + g) * TC_ROWS) + (n % TC_ROWS)) * TC_KB + part * 32;
+    uint4* d4 = reinterpret_cast<uint4*>(dst + off);
     d4[0] = reinterpret_cast<const uint4*>(out)[0];
     d4[1] = reinterpret_cast<const uint4*>(out)[1];
 }
@@ -287,41 +336,47 @@ static CUtensorMap make_map(const void* base, int rows, int K, int box_rows) {
     return map;
 }
 
-template <int TOK>
+template <int TOK, int EC>
 static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
                                const OutSpec& out, cudaStream_t q) {
-    constexpr int TC_TOK = TOK, TC_STAGES = TcCfg<TOK>::STAGES, TC_STAGE_BYTES = TcCfg<TOK>::STAGE_BYTES;
+    using Cfg = TcCfg<TOK, EC>;
+    constexpr int TC_TOK = TOK, TC_STAGES = Cfg::STAGES, TC_STAGE_BYTES = Cfg::STAGE_BYTES;
     const int N = L->N, K = L->K, G = K / 128;
     DETB_REQUIRE((reinterpret_cast<uintptr_t>(L->wq) & 15) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15) == 0,
                  "tensor-core GEMM operands must be 16-byte aligned");
-    const CUtensorMap map_w = make_map(L->wq, N, K, TC_ROWS);
+    const int row_tiles = (N + TC_ROWS - 1) / TC_ROWS;
+    const CUtensorMap map_w = make_map(L->wq, row_tiles * G * TC_ROWS, TC_KB, TC_ROWS);   // tile-major: one box = 16 KB in a row
     const CUtensorMap map_x = make_map(xq, M, K, TC_TOK);
     TcArgs a;
     a.N = N; a.K = K; a.G = G; a.M = M;
     a.c = L->c; a.m = L->m; a.sx = sx; a.mx = mx;
     a.error_flag = error_word();
     a.out = out;
-    const size_t smem = 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES + (size_t)G * TC_TOK * 2 + 16 + (2 * TC_STAGES + 4) * 8 + 16;
+    const size_t smem = 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES + (size_t)G * TC_TOK * 2 + 16 + (2 * TC_STAGES + 2 * Cfg::NBUF) * 8 + 16;
     static bool configured = false;
     if (!configured) {
-        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemm_tc<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin()));
+        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemm_tc<TOK, EC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin()));
         configured = true;
     }
     DETB_REQUIRE(smem <= smem_optin(), "K is too large for the tensor-core GEMM's multiplier table");
     const dim3 grid((M + TC_TOK - 1) / TC_TOK, (N + TC_ROWS - 1) / TC_ROWS);
-    k_gemm_tc<TOK><<<grid, TcCfg<TOK>::THREADS, smem, q>>>(map_w, map_x, a);
-    DETB_CUDA_OK(cudaGetLastError());
+    launch_pdl(k_gemm_tc<TOK, EC>, grid, dim3(Cfg::THREADS), smem, q, 1, map_w, map_x, a);
 }
 
-// Token-tile width.  Measured on B200 (K=5120 x N=17408, M=512): the 64-token tile reaches 385 TOPS, the 128-token
-// tile 315 TOPS (with the epilogue arithmetic removed: 520 vs 860 TOPS, i.e. the 128-wide tile is better fed from L2
-// but its sixteen epilogue warps are bound by the per-group 64-bit multiply-adds).  The 64-token tile is used for every M
-// until the epilogue is cheaper; the wider instantiation stays compiled for that work.
+// Tile choice, by shape only.  variant 0 = default rule; other values pin one instantiation (measurement switch).
+static int g_tc_variant = 0;
 void gemm_tc_launch(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
                     const OutSpec& out, cudaStream_t q) {
-    constexpr bool wide_tiles = false;
-    if (M <= 64 || !wide_tiles) gemm_tc_launch_tok<64>(L, xq, sx, mx, M, out, q);
-    else gemm_tc_launch_tok<128>(L, xq, sx, mx, M, out, q);
+    int v = g_tc_variant;
+    if (v == 0) v = M <= 32 ? 4 : 1;
+    switch (v) {
+        case 1: gemm_tc_launch_tok<64, 32>(L, xq, sx, mx, M, out, q); break;
+        case 2: gemm_tc_launch_tok<64, 16>(L, xq, sx, mx, M, out, q); break;
+        case 3: gemm_tc_launch_tok<32, 8>(L, xq, sx, mx, M, out, q); break;
+        case 4: gemm_tc_launch_tok<32, 16>(L, xq, sx, mx, M, out, q); break;
+        case 5: gemm_tc_launch_tok<128, 32>(L, xq, sx, mx, M, out, q); break;
+        default: DETB_REQUIRE(false, "unknown tensor-core GEMM variant");
+    }
 }
 
 }  // namespace detb
@@ -330,12 +385,16 @@ using namespace detb;
 
 extern "C" {
 
-size_t det_linear_expand_bytes(int N, int K) { return (size_t)N * (size_t)K; }
+// Measurement switch: 0 = tile chosen by shape; 1..5 pin (tokens, columns per epilogue warp) = (64,32) (64,16) (32,8)
+// (32,16) (128,32).  Results do not depend on it.
+void det_debug_set_tc_variant(int v) { g_tc_variant = v; }
+
+size_t det_linear_expand_bytes(int N, int K) { return (size_t)((N + TC_ROWS - 1) / TC_ROWS) * TC_ROWS * (size_t)K; }
 
 void det_linear_expand(const det_qlinear* src, void* dst, cudaStream_t st) {
     DETB_REQUIRE((src->bits == 4 || src->bits == 6 || src->bits == 8) && src->K % 128 == 0, "bad linear shape");
-    const long long nblocks = (long long)src->N * (src->K / 32);
-    k_expand_int8<<<(unsigned)((nblocks + 255) / 256), 256, 0, queue_of(st)>>>(src->wq, src->bits, nblocks,
+    const long long nblocks = (long long)((src->N + TC_ROWS - 1) / TC_ROWS) * TC_ROWS * (src->K / 32);
+    k_expand_int8<<<(unsigned)((nblocks + 255) / 256), 256, 0, queue_of(st)>>>(src->wq, src->bits, src->N, src->K,
                                                                               static_cast<int8_t*>(dst));
     DETB_CUDA_OK(cudaGetLastError());
 }

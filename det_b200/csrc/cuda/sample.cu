@@ -189,13 +189,28 @@ __global__ void __launch_bounds__(ST) k_sample_topkp(const float* __restrict__ l
         for (int i = threadIdx.x; i < DIGITS; i += ST) { cnt[i] = 0; sum[i] = 0; }
         __syncthreads();
         const u64 prefix = sel[0];
+        // Most weights of a peaked distribution share one digit (the smallest): a thread keeps the running (count, sum)
+        // of its current digit in registers and touches shared memory only when the digit changes.
+        unsigned run_d = 0, run_c = 0;
+        u64 run_s = 0;
         for (int i = threadIdx.x; i < V; i += ST) {
             const u64 wv = wbuf[i];
             if (pass == 0 || (wv >> (shift + 11)) == prefix) {
                 const unsigned d = (unsigned)(wv >> shift) & (DIGITS - 1);
-                atomicAdd(&cnt[d], 1u);
-                atomicAdd(&sum[d], wv);
+                if (d != run_d && run_c) {
+                    atomicAdd(&cnt[run_d], run_c);
+                    atomicAdd(&sum[run_d], run_s);
+                    run_c = 0;
+                    run_s = 0;
+                }
+                run_d = d;
+                run_c++;
+                run_s += wv;
             }
+        }
+        if (run_c) {
+            atomicAdd(&cnt[run_d], run_c);
+            atomicAdd(&sum[run_d], run_s);
         }
         __syncthreads();
         if (threadIdx.x == 0) {

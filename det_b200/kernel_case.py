@@ -2,7 +2,7 @@
 kernels that a profiler capture needs (a few hundred MB on the device, a handful of launches).
 
     python -m det_b200.kernel_case gemv    [N K bits M]    # k_gemv_stream, default 17408 5120 6 1
-    python -m det_b200.kernel_case gemm_tc [N K bits M]    # k_gemm_tc,     default 17408 5120 6 512
+    python -m det_b200.kernel_case gemm_tc [N K bits M [variant]]   # k_gemm_tc, default 17408 5120 6 512, tile by shape
 
 gemv: six copies of the weights (seeded, generated on the device, repacked into the streaming layout) are cycled through
 so that no launch finds its weights in the 126 MB L2; 6 warm-up launches, then 12 timed ones.
@@ -73,6 +73,8 @@ def main(argv):
         n, k, bits, m = map(int, argv[1:5])
     d = capi.cuda()
     assert d.det_init() == 0
+    if len(argv) >= 6:
+        d.det_debug_set_tc_variant(int(argv[5]))
     ev = _Events(d.det_cuda_stream())
     xq, sx, mx, y = _activations(d, m, k, n)
     g = k // 128

@@ -155,7 +155,8 @@ void det_test_prim(int op, const float* x, int M, int n, float* out, cudaStream_
 size_t det_linear_repack_bytes(int N, int K, int bits);
 void det_linear_repack(const det_qlinear* src, void* dst, cudaStream_t st);
 
-/* Tensor-core layout for prefill (M > 8): signed int8 codes, row-major [N][K] (det_linear_expand_bytes(N, K) bytes),
+/* Tensor-core layout for prefill (M > 8): signed int8 codes in tile-major order [ceil(N/128)][K/128][128 rows][128 codes]
+ * (each 16 KB box a TMA load fetches is contiguous; det_linear_expand_bytes(N, K) bytes, the last row tile zero padded),
  * tagged bits | DET_LAYOUT_INT8 in det_qlinear.  det_gemm_ex then runs the tcgen05 kind::i8 kernel.  Like the repack
  * above this belongs in Backend::linear (crates/det/src/cuda.rs:139-163).                                            */
 #define DET_LAYOUT_INT8 0x200
@@ -252,6 +253,9 @@ int det_sample_topkp_static(const float* logits, int M, int V, float inv_temp, i
 /* Measurement switch: programmatic dependent launch between the library's kernels on (default, non-zero) or off.
  * Results are identical either way; only the overlap of one kernel's prologue with its predecessor's tail changes.  */
 void det_debug_set_pdl(int on);
+/* Measurement switch: pins the tensor-core GEMM's tile, 1..5 = (tokens, columns per epilogue warp) (64,32) (64,16)
+ * (32,8) (32,16) (128,32); 0 = chosen by shape (default).  Results do not depend on it.                               */
+void det_debug_set_tc_variant(int v);
 
 /* Last error recorded by a bounded device-side wait (0 = none; see the DETB_ERR_* codes in csrc/cuda/runtime.cuh).
  * Waits for pending work.                                                                                            */

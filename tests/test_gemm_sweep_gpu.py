@@ -59,10 +59,15 @@ def test_gemm_matches_oracle(n, k, bits, ms, libs, oracle):
             d.det_memcpy(dx, xq.ctypes.data, xq.nbytes, None)
             d.det_memcpy(ds, sx.ctypes.data, sx.nbytes, None)
             d.det_memcpy(dm, mx.ctypes.data, mx.nbytes, None)
-            for name, lin in (("stream", stream), ("rowmajor", src), ("int8 tensor-core", tensor)):
+            cases = [("stream", stream, 0), ("rowmajor", src, 0)]
+            # every tile instantiation of the tensor-core kernel (0 = the one the shape selects)
+            cases += [(f"int8 tensor-core, tile variant {v}", tensor, v) for v in (0, 1, 2, 3, 4, 5)]
+            for name, lin, variant in cases:
                 got = np.zeros_like(want)
                 d.det_memset(dy, 0xFF, want.nbytes, None)
+                d.det_debug_set_tc_variant(variant)
                 d.det_gemm(C.byref(lin), dx, ds, dm, mtok, dy, None)
+                d.det_debug_set_tc_variant(0)
                 d.det_memcpy(got.ctypes.data, dy, got.nbytes, None)
                 d.det_sync()
                 bad = int((got.view(np.uint32) != want.view(np.uint32)).sum())
