@@ -40,6 +40,15 @@ __device__ __forceinline__ float conv_in(const GdnArgs& g, int t, int back, int 
     return tau < 0 ? g.conv_state[(size_t)(3 + tau) * g.conv_dim + c] : g.qkv[(size_t)tau * g.conv_dim + c];
 }
 
+// silu(causal conv) of channel c at token row t: ((w0*x[t-3] + w1*x[t-2]) + w2*x[t-1]) + w3*x[t]   (spec/layers.rs:135-140)
+__device__ __forceinline__ float conv_silu(const GdnArgs& g, int t, int c) {
+    const float4 w = *reinterpret_cast<const float4*>(g.conv + (size_t)c * 4);
+    float acc = fadd(fmul(w.x, conv_in(g, t, 3, c)), fmul(w.y, conv_in(g, t, 2, c)));
+    acc = fadd(acc, fmul(w.z, conv_in(g, t, 1, c)));
+    acc = fadd(acc, fmul(w.w, conv_in(g, t, 0, c)));
+    return silu_f(acc);
+}
+
 __global__ void __launch_bounds__(128) k_gdn_prep(const GdnArgs g) {
     pdl_trigger();
     pdl_wait();
@@ -111,8 +120,14 @@ constexpr int RR = DK / RL;   // rows per lane (16)
 
 constexpr int SLAB_STRIDE = RC + 4;   // floats per slab row: rows stay 16-byte aligned for the asynchronous copies
 
+// PREP: decode form (every CTA advances exactly one token and nothing is exported).  The CTA computes what k_gdn_prep
+// would have left in scratch for it — q and k of its k head (conv, silu, l2norm with the same per-lane runs and xor
+// order), its 16 v channels, beta and decay — so a decode step needs no separate prep launch.
+template <bool PREP>
 __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
     __shared__ __align__(16) float slab[DK][SLAB_STRIDE];
+    __shared__ __align__(16) float pq[DK], pk[DK];
+    __shared__ float pv[RC], pbd[2];
     pdl_trigger();
     pdl_wait();
     const int h = blockIdx.x / (DV / RC);
@@ -132,13 +147,12 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
 
+    float kq[2][2 * RR];   // [buffer][k rows | q rows]
+    float vv[2], be[2], de[2];
     const size_t ystride = g.conv_dim;
     const float* qrow = g.y + (size_t)kh * DK + p * RR;
     const float* krow = g.y + (size_t)g.n_k * DK + (size_t)kh * DK + p * RR;
     const float* vptr = g.y + (size_t)2 * g.n_k * DK + (size_t)h * DV + j0 + jj;
-
-    float kq[2][2 * RR];   // [buffer][k rows | q rows]
-    float vv[2], be[2], de[2];
     auto fetch = [&](int t, int b) {
 #pragma unroll
         for (int i = 0; i < RR; i += 4) {
@@ -151,12 +165,53 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
         be[b] = g.beta[(size_t)t * g.n_v + h];
         de[b] = g.decay[(size_t)t * g.n_v + h];
     };
-    fetch(t_begin, 0);
+    if (PREP) {
+        const int t = t_begin;
+        const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+        if (wib < 2) {
+            // warp 0: q of k head kh, warp 1: k — lane owns four consecutive channels, as in k_gdn_prep
+            const int c0 = (wib == 0 ? kh : g.n_k + kh) * DK + lane * 4;
+            float v[4], sq[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                v[e] = conv_silu(g, t, c0 + e);
+                sq[e] = fmul(v[e], v[e]);
+            }
+            const float ss = fold_lanes<32>(fold_run<4>(sq));
+            const float inv = fdiv(1.0f, fsqrt(fadd(ss, g.eps)));
+            float* dst = wib == 0 ? pq : pk;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                v[e] = fmul(v[e], inv);
+                if (wib == 0) v[e] = fmul(v[e], __uint_as_float(QSCALE_BITS));
+                dst[lane * 4 + e] = v[e];
+            }
+        } else if (wib == 2) {
+            if (lane < RC) pv[lane] = conv_silu(g, t, 2 * g.n_k * DK + h * DV + j0 + lane);
+            if (lane == RC) pbd[0] = sigmoid_f(g.b[(size_t)t * g.n_v + h]);
+            if (lane == RC + 1) {
+                const float sp = softplus_f(fadd(g.a[(size_t)t * g.n_v + h], g.dt_bias[h]));
+                pbd[1] = exp_f(-fmul(g.A[h], sp));
+            }
+        }
+    } else {
+        fetch(t_begin, 0);
+    }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     float s[RR];
 #pragma unroll
     for (int i = 0; i < RR; i++) s[i] = slab[p * RR + i][jj];
+    if (PREP) {
+#pragma unroll
+        for (int i = 0; i < RR; i++) {
+            kq[0][i] = pk[p * RR + i];
+            kq[0][RR + i] = pq[p * RR + i];
+        }
+        vv[0] = pv[jj];
+        be[0] = pbd[0];
+        de[0] = pbd[1];
+    }
 #pragma unroll 1
     for (int t = t_begin; t < t_end; t += 2) {
 #pragma unroll
@@ -282,8 +337,14 @@ static void gdn_entry(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_st
     g.gin = gin;
     cudaStream_t q = queue_of(st);
     const int heads = 2 * n_k + n_v;
-    launch_pdl(k_gdn_prep, dim3((heads + 3) / 4, M), dim3(128), 0, q, 1, g);
-    launch_pdl(k_gdn_recur, dim3(n_v * (DV / RC), rows ? M : 1), dim3(RC * RL), 0, q, 1, g);
+    // decode form: every CTA of the recurrence advances one token and prepares its own operands
+    const bool fused_prep = (rows != nullptr || M == 1) && gin == nullptr;
+    if (fused_prep) {
+        launch_pdl(k_gdn_recur<true>, dim3(n_v * (DV / RC), rows ? M : 1), dim3(RC * RL), 0, q, 1, g);
+    } else {
+        launch_pdl(k_gdn_prep, dim3((heads + 3) / 4, M), dim3(128), 0, q, 1, g);
+        launch_pdl(k_gdn_recur<false>, dim3(n_v * (DV / RC), rows ? M : 1), dim3(RC * RL), 0, q, 1, g);
+    }
     const int row_blocks = (int)(((long long)M * n_v + 3) / 4);
     const int state_blocks = ((g.conv_dim + 127) / 128) * (rows ? M : 1);
     launch_pdl(k_gdn_out, dim3(row_blocks + state_blocks), dim3(128), 0, q, 1, g, row_blocks);
