@@ -120,11 +120,47 @@ constexpr int RR = DK / RL;   // rows per lane (16)
 
 constexpr int SLAB_STRIDE = RC + 4;   // floats per slab row: rows stay 16-byte aligned for the asynchronous copies
 
-// PREP: decode form (every CTA advances exactly one token and nothing is exported).  The CTA computes what k_gdn_prep
-// would have left in scratch for it — q and k of its k head (conv, silu, l2norm with the same per-lane runs and xor
-// order), its 16 v channels, beta and decay — so a decode step needs no separate prep launch.
-template <bool PREP>
-__global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
+// One token of the recurrence for the thread's 16 rows of one state column (spec/layers.rs:104-131): decay, the
+// k-contraction (spec tree: the lane's aligned run, then xor 1, 2, 4 over the column's 8 lanes), the delta update, the
+// q-contraction.  Returns the output of the column.
+__device__ __forceinline__ float recur_step(float (&s)[RR], const float* k, const float* q, float v, float beta, float decay) {
+    float prod[RR];
+#pragma unroll
+    for (int i = 0; i < RR; i++) {
+        s[i] = fmul(s[i], decay);
+        prod[i] = fmul(s[i], k[i]);
+    }
+    const float kv_mem = fold_lanes<RL>(fold_run<RR>(prod));
+    const float delta = fmul(fsub(v, kv_mem), beta);
+#pragma unroll
+    for (int i = 0; i < RR; i++) {
+        s[i] = fadd(s[i], fmul(k[i], delta));
+        prod[i] = fmul(s[i], q[i]);
+    }
+    return fold_lanes<RL>(fold_run<RR>(prod));
+}
+
+// the CTA's 128 x 16 slab of the state <-> shared memory, 16-byte pieces (4 per thread)
+__device__ __forceinline__ void slab_load_async(float (*slab)[SLAB_STRIDE], const float* Sh, int j0) {
+    for (int i = threadIdx.x; i < DK * (RC / 4); i += RC * RL) {
+        const int row = i / (RC / 4), v = i % (RC / 4);
+        const unsigned dst = (unsigned)__cvta_generic_to_shared(&slab[row][v * 4]);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(Sh + (size_t)row * DV + j0 + v * 4) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void slab_store(float (*slab)[SLAB_STRIDE], float* Sh, int j0) {
+    for (int i = threadIdx.x; i < DK * (RC / 4); i += RC * RL) {
+        const int row = i / (RC / 4), v = i % (RC / 4);
+        *reinterpret_cast<float4*>(Sh + (size_t)row * DV + j0 + v * 4) = *reinterpret_cast<const float4*>(&slab[row][v * 4]);
+    }
+}
+
+// Decode form: every CTA advances exactly one token (of the one sequence, or of row blockIdx.y's sequence in a batched
+// step) and nothing is exported.  The CTA computes what k_gdn_prep would have left in scratch for it — q and k of its
+// k head (conv, silu, l2norm with the same per-lane runs and xor order), its 16 v channels, beta and decay — so a
+// decode step needs no separate prep launch.
+__global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
     __shared__ __align__(16) float slab[DK][SLAB_STRIDE];
     __shared__ __align__(16) float pq[DK], pk[DK];
     __shared__ float pv[RC], pbd[2];
@@ -134,39 +170,10 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
     const int j0 = (blockIdx.x % (DV / RC)) * RC;
     const int kh = h / g.rep;
     const int p = threadIdx.x % RL, jj = threadIdx.x / RL;
-    // one sequence: this CTA walks all M tokens; batched step: blockIdx.y is the row, one token of its own sequence
+    const int t = g.rows ? blockIdx.y : 0;
     float* Sh = (g.rows ? g.rows[blockIdx.y].S : g.S) + (size_t)h * DK * DV;
-    const int t_begin = g.rows ? blockIdx.y : 0, t_end = g.rows ? blockIdx.y + 1 : g.M;
-
-    // the CTA's 128 x 16 slab of the state: 16-byte asynchronous copies (4 per thread), in flight while the first
-    // token's operands are fetched
-    for (int i = threadIdx.x; i < DK * (RC / 4); i += RC * RL) {
-        const int row = i / (RC / 4), v = i % (RC / 4);
-        const unsigned dst = (unsigned)__cvta_generic_to_shared(&slab[row][v * 4]);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(Sh + (size_t)row * DV + j0 + v * 4) : "memory");
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-
-    float kq[2][2 * RR];   // [buffer][k rows | q rows]
-    float vv[2], be[2], de[2];
-    const size_t ystride = g.conv_dim;
-    const float* qrow = g.y + (size_t)kh * DK + p * RR;
-    const float* krow = g.y + (size_t)g.n_k * DK + (size_t)kh * DK + p * RR;
-    const float* vptr = g.y + (size_t)2 * g.n_k * DK + (size_t)h * DV + j0 + jj;
-    auto fetch = [&](int t, int b) {
-#pragma unroll
-        for (int i = 0; i < RR; i += 4) {
-            const float4 kk = *reinterpret_cast<const float4*>(krow + (size_t)t * ystride + i);
-            const float4 qq = *reinterpret_cast<const float4*>(qrow + (size_t)t * ystride + i);
-            kq[b][i] = kk.x; kq[b][i + 1] = kk.y; kq[b][i + 2] = kk.z; kq[b][i + 3] = kk.w;
-            kq[b][RR + i] = qq.x; kq[b][RR + i + 1] = qq.y; kq[b][RR + i + 2] = qq.z; kq[b][RR + i + 3] = qq.w;
-        }
-        vv[b] = vptr[(size_t)t * ystride];
-        be[b] = g.beta[(size_t)t * g.n_v + h];
-        de[b] = g.decay[(size_t)t * g.n_v + h];
-    };
-    if (PREP) {
-        const int t = t_begin;
+    slab_load_async(slab, Sh, j0);     // in flight while the operands are prepared
+    {
         const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
         if (wib < 2) {
             // warp 0: q of k head kh, warp 1: k — lane owns four consecutive channels, as in k_gdn_prep
@@ -194,57 +201,105 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur(const GdnArgs g) {
                 pbd[1] = exp_f(-fmul(g.A[h], sp));
             }
         }
-    } else {
-        fetch(t_begin, 0);
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    float s[RR], k[RR], q[RR];
+#pragma unroll
+    for (int i = 0; i < RR; i++) {
+        s[i] = slab[p * RR + i][jj];
+        k[i] = pk[p * RR + i];
+        q[i] = pq[p * RR + i];
+    }
+    const float ov = recur_step(s, k, q, pv[jj], pbd[0], pbd[1]);
+    if (p == 0) g.o[((size_t)t * g.n_v + h) * DV + j0 + jj] = ov;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < RR; i++) slab[p * RR + i][jj] = s[i];
+    __syncthreads();
+    slab_store(slab, Sh, j0);
+}
+
+// Sequence form (prefill): the CTA walks all M tokens of one sequence.  The recurrence is strictly sequential, so its
+// speed is the latency of one step; the per-token operands that k_gdn_prep left in scratch (k and q of the k head, the
+// 16 v values, beta, decay) are staged through shared memory in blocks of TB tokens, the next block in flight
+// (cp.async) while the current one is consumed, so no step waits for global memory.
+constexpr int TB = 8;
+constexpr int RUN_STRIDE = RR + 4;      // a lane's 16-row run, padded: the 8 runs of a token fall into distinct banks
+struct TokOps {
+    float k[RL][RUN_STRIDE];
+    float q[RL][RUN_STRIDE];
+    float v[RC];
+    float beta, decay, pad0, pad1;
+};
+static_assert(sizeof(TokOps) % 16 == 0, "token operands stay 16-byte aligned");
+
+__global__ void __launch_bounds__(RC * RL) k_gdn_recur_seq(const GdnArgs g) {
+    __shared__ __align__(16) float slab[DK][SLAB_STRIDE];
+    __shared__ __align__(16) TokOps ops[2][TB];
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.x / (DV / RC);
+    const int j0 = (blockIdx.x % (DV / RC)) * RC;
+    const int kh = h / g.rep;
+    const int p = threadIdx.x % RL, jj = threadIdx.x / RL;
+    float* Sh = g.S + (size_t)h * DK * DV;
+    slab_load_async(slab, Sh, j0);
+    const size_t ystride = g.conv_dim;
+    const float* qbase = g.y + (size_t)kh * DK;
+    const float* kbase = g.y + (size_t)g.n_k * DK + (size_t)kh * DK;
+    const float* vbase = g.y + (size_t)2 * g.n_k * DK + (size_t)h * DV + j0;
+    constexpr int CH = 2 * (DK / 4) + RC / 4;          // 16-byte pieces per token: k, q, v
+    auto stage = [&](int t0, int buf) {
+        const int n = min(TB, g.M - t0);
+        for (int i = threadIdx.x; i < n * CH; i += RC * RL) {
+            const int tok = i / CH, c = i % CH;
+            const float* src;
+            float* dst;
+            if (c < DK / 4) { src = kbase + (size_t)(t0 + tok) * ystride + c * 4; dst = &ops[buf][tok].k[c >> 2][(c & 3) * 4]; }
+            else if (c < 2 * (DK / 4)) { const int cc = c - DK / 4; src = qbase + (size_t)(t0 + tok) * ystride + cc * 4; dst = &ops[buf][tok].q[cc >> 2][(cc & 3) * 4]; }
+            else { const int cc = c - 2 * (DK / 4); src = vbase + (size_t)(t0 + tok) * ystride + cc * 4; dst = &ops[buf][tok].v[cc * 4]; }
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+        }
+        if ((int)threadIdx.x < 2 * n) {
+            const int tok = threadIdx.x >> 1;
+            const float* src = ((threadIdx.x & 1) ? g.decay : g.beta) + (size_t)(t0 + tok) * g.n_v + h;
+            float* dst = (threadIdx.x & 1) ? &ops[buf][tok].decay : &ops[buf][tok].beta;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, 0);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     float s[RR];
 #pragma unroll
     for (int i = 0; i < RR; i++) s[i] = slab[p * RR + i][jj];
-    if (PREP) {
-#pragma unroll
-        for (int i = 0; i < RR; i++) {
-            kq[0][i] = pk[p * RR + i];
-            kq[0][RR + i] = pq[p * RR + i];
-        }
-        vv[0] = pv[jj];
-        be[0] = pbd[0];
-        de[0] = pbd[1];
-    }
+    int buf = 0;
+    for (int t0 = 0; t0 < g.M; t0 += TB, buf ^= 1) {
+        if (t0 + TB < g.M) stage(t0 + TB, buf ^ 1);        // next block in flight
+        const int n = min(TB, g.M - t0);
 #pragma unroll 1
-    for (int t = t_begin; t < t_end; t += 2) {
+        for (int tok = 0; tok < n; tok++) {
+            const TokOps& o = ops[buf][tok];
+            float k[RR], q[RR];
 #pragma unroll
-        for (int b = 0; b < 2; b++) {
-            const int tt = t + b;
-            if (tt < t_end) {
-                if (tt + 1 < t_end) fetch(tt + 1, b ^ 1);
-                float prod[RR];
-#pragma unroll
-                for (int i = 0; i < RR; i++) {
-                    s[i] = fmul(s[i], de[b]);
-                    prod[i] = fmul(s[i], kq[b][i]);
-                }
-                const float kv_mem = fold_lanes<RL>(fold_run<RR>(prod));
-                const float delta = fmul(fsub(vv[b], kv_mem), be[b]);
-#pragma unroll
-                for (int i = 0; i < RR; i++) {
-                    s[i] = fadd(s[i], fmul(kq[b][i], delta));
-                    prod[i] = fmul(s[i], kq[b][RR + i]);
-                }
-                const float ov = fold_lanes<RL>(fold_run<RR>(prod));
-                if (p == 0) g.o[((size_t)tt * g.n_v + h) * DV + j0 + jj] = ov;
+            for (int i = 0; i < RR; i += 4) {
+                const float4 kk = *reinterpret_cast<const float4*>(&o.k[p][i]);
+                const float4 qq = *reinterpret_cast<const float4*>(&o.q[p][i]);
+                k[i] = kk.x; k[i + 1] = kk.y; k[i + 2] = kk.z; k[i + 3] = kk.w;
+                q[i] = qq.x; q[i + 1] = qq.y; q[i + 2] = qq.z; q[i + 3] = qq.w;
             }
+            const float ov = recur_step(s, k, q, o.v[jj], o.beta, o.decay);
+            if (p == 0) g.o[((size_t)(t0 + tok) * g.n_v + h) * DV + j0 + jj] = ov;
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                   // the next block has landed; this one may be overwritten
     }
-    __syncthreads();
 #pragma unroll
     for (int i = 0; i < RR; i++) slab[p * RR + i][jj] = s[i];
     __syncthreads();
-    for (int i = threadIdx.x; i < DK * (RC / 4); i += RC * RL) {
-        const int row = i / (RC / 4), v = i % (RC / 4);
-        *reinterpret_cast<float4*>(Sh + (size_t)row * DV + j0 + v * 4) = *reinterpret_cast<const float4*>(&slab[row][v * 4]);
-    }
+    slab_store(slab, Sh, j0);
 }
 
 // on = rmsnorm(o, norm, eps) * silu_f(z): one warp per (token, v head).  Extra CTAs past the rows move the conv state.
@@ -340,10 +395,10 @@ static void gdn_entry(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_st
     // decode form: every CTA of the recurrence advances one token and prepares its own operands
     const bool fused_prep = (rows != nullptr || M == 1) && gin == nullptr;
     if (fused_prep) {
-        launch_pdl(k_gdn_recur<true>, dim3(n_v * (DV / RC), rows ? M : 1), dim3(RC * RL), 0, q, 1, g);
+        launch_pdl(k_gdn_recur_dec, dim3(n_v * (DV / RC), rows ? M : 1), dim3(RC * RL), 0, q, 1, g);
     } else {
         launch_pdl(k_gdn_prep, dim3((heads + 3) / 4, M), dim3(128), 0, q, 1, g);
-        launch_pdl(k_gdn_recur<false>, dim3(n_v * (DV / RC), rows ? M : 1), dim3(RC * RL), 0, q, 1, g);
+        launch_pdl(k_gdn_recur_seq, dim3(n_v * (DV / RC)), dim3(RC * RL), 0, q, 1, g);
     }
     const int row_blocks = (int)(((long long)M * n_v + 3) / 4);
     const int state_blocks = ((g.conv_dim + 127) / 128) * (rows ? M : 1);
