@@ -123,9 +123,10 @@ SHAPES = {   # layers, hidden, ffn, attention (q heads, kv heads, head dim), GDN
 
 
 def launches_per_token(cfg: str) -> int:
-    """Kernels of one device-resident decode step: 12 per layer (norm+quant, 2-3 GEMVs, 3-4 mixer kernels, quant, GEMV,
-    norm+quant, GEMV, SwiGLU+quant, GEMV) plus embed, final norm, head GEMV, argmax and token feedback."""
-    return SHAPES[cfg]["layers"] * 12 + 5
+    """Kernels of one device-resident decode step: 10 per layer (norm+quant, fused input GEMV, 2 mixer kernels, quant,
+    output GEMV, norm+quant, gate|up GEMV, SwiGLU+quant, down GEMV) plus embed, final norm, head GEMV, argmax and token
+    feedback."""
+    return SHAPES[cfg]["layers"] * 10 + 5
 
 
 def _prompt(h, n, vocab):
@@ -202,6 +203,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     bk = h.dh_cuda_backend_new(1, 1)
     if not bk:
         raise RuntimeError(h.dh_last_error().decode())
+    if args.fuse_kinds:
+        h.dh_cuda_debug(bk, 0, args.fuse_kinds)
     # N > 1: tensor parallel over NVLink.  torch.distributed (gloo, CPU) only carries the NCCL id, the barriers and the
     # max-over-ranks of the timings; the data path uses the library's own NCCL communicator on its queue.
     dist, comm = None, None
@@ -369,8 +372,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                    "rot_dim": 64, "rope_theta": 1e7, "eps": 1e-6, "v_scale": 2 ** -10},
         "e2e": {"value": K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": shape["hidden"] * 4,
                 "d2h_bytes_per_step": 4},
-        # tensor parallel adds per layer: 2 residual adds, 1 extra quant, 4 exchange kernels
-        "gpu_launches": K * (launches_per_token(cfg) + (0 if world == 1 else SHAPES[cfg]["layers"] * 7 + 1)),
+        # tensor parallel: the exchanges ride in the row kernels (same count per layer) plus the logits gather; with
+        # stand-alone exchanges every layer adds 4 exchange kernels, 2 residual adds and 1 quant
+        "gpu_launches": K * (launches_per_token(cfg) + (0 if world == 1 else 1 if args.exchange == "peer"
+                                                         else SHAPES[cfg]["layers"] * 7 + 1)),
         "prefill": {"value": P / (prefill_ms * 1e-3), "unit": "tok/s", "tokens": P, "chunk": chunk},
         "roofline": None if achieved is None else
                     {"bound": "hbm", "kernel": "k_gemv_stream", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -517,6 +522,9 @@ def main():
     ap.add_argument("--compose-rows", action="store_true",
                     help="serving: per-sequence attention / GDN calls instead of the batched kernels (same tokens)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--fuse-kinds", type=int, default=0,
+                    help="measurement switch: mask of activation kinds quantized in the GEMV prologue instead of by their own "
+                         "kernel (2 RMSNorm, 4 plain, 8 SwiGLU); same values")
     ap.add_argument("--no-pdl", action="store_true", help="measurement switch: plain stream-ordered launches")
     args = ap.parse_args()
     if args.warmup < 3:

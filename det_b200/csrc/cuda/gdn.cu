@@ -29,7 +29,47 @@ struct GdnArgs {
     float* o;        // [M][n_v][DV] mixer output (gout when exported)
     float* gin;      // optional
     const det_gdn_state* rows;   // batched decode: token row t is the next token of the sequence with state rows[t]
+    // decode form with the a|b projection folded in (ab_wq != NULL): a[t][h] and b[t][h] are rows h and n_v + h of a W8
+    // linear in the reference layout applied to the quantized layer input xq / sx / mx (K wide); g.a and g.b are unused
+    const uint8_t* ab_wq;
+    const float* ab_c;
+    const uint16_t* ab_m;
+    const int8_t* xq;
+    const float* sx;
+    const uint16_t* mx;
+    int K;
 };
+
+// The CTA's share of one output of a W8 linear for token row t (spec gemm_row, spec/quant.rs:99-117): the int64 sum over
+// groups of (m * mx) * (int dot of the group).  Integer sums are order-free, so the K / 16 sixteen-byte chunks of the row
+// are dealt round-robin to the 128 threads (all loads independent and issued together); the caller adds the threads'
+// shares and applies ((f32)acc * c) * sx.
+__device__ __forceinline__ long long ab_partial(const GdnArgs& g, int t, int row) {
+    const int G = g.K >> 7, chunks = g.K >> 4;
+    const uint4* w = reinterpret_cast<const uint4*>(g.ab_wq + (size_t)row * g.K);
+    const uint4* x = reinterpret_cast<const uint4*>(g.xq + (size_t)t * g.K);
+    const uint16_t* m = g.ab_m + (size_t)row * G;
+    const uint16_t* mx = g.mx + (size_t)t * G;
+    long long acc = 0;
+#pragma unroll 4
+    for (int c = threadIdx.x; c < chunks; c += 128) {   // the decode kernel's 128 threads
+        const uint4 wv = w[c], xv = x[c];
+        const unsigned mult = (unsigned)m[c >> 3] * (unsigned)mx[c >> 3];
+        int d = __dp4a((int)wv.x, (int)xv.x, 0);
+        d = __dp4a((int)wv.y, (int)xv.y, d);
+        d = __dp4a((int)wv.z, (int)xv.z, d);
+        d = __dp4a((int)wv.w, (int)xv.w, d);
+        acc += (long long)d * (long long)mult;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        int lo = (int)(unsigned)acc, hi = (int)(acc >> 32);
+        lo = __shfl_xor_sync(FULL, lo, off);
+        hi = __shfl_xor_sync(FULL, hi, off);
+        acc += ((long long)hi << 32) | (unsigned)lo;
+    }
+    return acc;   // the warp's share, in every lane
+}
 
 // input of channel c `back` steps before token row t (times before the call reach into the conv state, which holds the
 // three inputs before the call's first token; in a batched step every row is the first token of its own sequence)
@@ -164,6 +204,7 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
     __shared__ __align__(16) float slab[DK][SLAB_STRIDE];
     __shared__ __align__(16) float pq[DK], pk[DK];
     __shared__ float pv[RC], pbd[2];
+    __shared__ long long ab_part[2][4];
     pdl_trigger();
     pdl_wait();
     const int h = blockIdx.x / (DV / RC);
@@ -173,6 +214,15 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
     const int t = g.rows ? blockIdx.y : 0;
     float* Sh = (g.rows ? g.rows[blockIdx.y].S : g.S) + (size_t)h * DK * DV;
     slab_load_async(slab, Sh, j0);     // in flight while the operands are prepared
+    if (g.ab_wq) {
+        // a[h] and b[h] of this token: all four warps share the two W8 rows
+        const long long pa = ab_partial(g, t, h), pb = ab_partial(g, t, g.n_v + h);
+        if ((threadIdx.x & 31) == 0) {
+            ab_part[0][threadIdx.x >> 5] = pa;
+            ab_part[1][threadIdx.x >> 5] = pb;
+        }
+        __syncthreads();
+    }
     {
         const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
         if (wib < 2) {
@@ -195,9 +245,26 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
             }
         } else if (wib == 2) {
             if (lane < RC) pv[lane] = conv_silu(g, t, 2 * g.n_k * DK + h * DV + j0 + lane);
-            if (lane == RC) pbd[0] = sigmoid_f(g.b[(size_t)t * g.n_v + h]);
-            if (lane == RC + 1) {
-                const float sp = softplus_f(fadd(g.a[(size_t)t * g.n_v + h], g.dt_bias[h]));
+            if (lane == 0) {
+                float bv;
+                if (g.ab_wq) {
+                    const long long acc = ab_part[1][0] + ab_part[1][1] + ab_part[1][2] + ab_part[1][3];
+                    bv = fmul(fmul(i64_to_f32(acc), g.ab_c[g.n_v + h]), g.sx[t]);
+                } else {
+                    bv = g.b[(size_t)t * g.n_v + h];
+                }
+                pbd[0] = sigmoid_f(bv);
+            }
+        } else {
+            if (lane == 0) {
+                float av;
+                if (g.ab_wq) {
+                    const long long acc = ab_part[0][0] + ab_part[0][1] + ab_part[0][2] + ab_part[0][3];
+                    av = fmul(fmul(i64_to_f32(acc), g.ab_c[h]), g.sx[t]);
+                } else {
+                    av = g.a[(size_t)t * g.n_v + h];
+                }
+                const float sp = softplus_f(fadd(av, g.dt_bias[h]));
                 pbd[1] = exp_f(-fmul(g.A[h], sp));
             }
         }
@@ -368,9 +435,15 @@ size_t det_gdn_scratch_bytes(int M, int n_k, int n_v, int dk, int dv) {
     return gdn_scratch(M > 0 ? M : 1, n_k, n_v).total;
 }
 
+struct AbSource {
+    const det_qlinear* lin;
+    const int8_t* xq;
+    const float* sx;
+    const uint16_t* mx;
+};
 static void gdn_entry(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_state* rows, const float* qkv, const float* z,
                       const float* a, const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on,
-                      void* scratch, float* gin, float* gout, cudaStream_t st) {
+                      void* scratch, float* gin, float* gout, cudaStream_t st, const AbSource* ab = nullptr) {
     if (M <= 0) return;
     DETB_REQUIRE(dk == DK && dv == DV, "Gated DeltaNet kernels are built for dk = dv = 128");
     DETB_REQUIRE(n_k > 0 && n_v % n_k == 0, "n_v must be a multiple of n_k");
@@ -379,6 +452,14 @@ static void gdn_entry(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_st
     GdnArgs g;
     g.conv = L->conv; g.A = L->A; g.dt_bias = L->dt_bias; g.norm = L->norm;
     g.rows = rows;
+    g.ab_wq = nullptr; g.ab_c = nullptr; g.ab_m = nullptr; g.xq = nullptr; g.sx = nullptr; g.mx = nullptr; g.K = 0;
+    if (ab) {
+        DETB_REQUIRE((rows != nullptr || M == 1) && gin == nullptr, "the a|b projection folds into decode steps only");
+        DETB_REQUIRE(ab->lin->bits == 8 && ab->lin->N == 2 * n_v && ab->lin->K % 128 == 0 && ab->mx != nullptr,
+                     "a|b must be a W8 reference-layout linear of 2 * n_v rows");
+        g.ab_wq = ab->lin->wq; g.ab_c = ab->lin->c; g.ab_m = ab->lin->m;
+        g.xq = ab->xq; g.sx = ab->sx; g.mx = ab->mx; g.K = ab->lin->K;
+    }
     g.conv_state = S ? S->conv_state : nullptr;
     g.S = S ? S->S : nullptr;
     g.qkv = qkv; g.z = z; g.a = a; g.b = b;
@@ -416,6 +497,18 @@ void det_gdn_rows(const det_gdn_layer* L, const det_gdn_state* rows, const float
                   const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
                   cudaStream_t st) {
     gdn_entry(L, nullptr, rows, qkv, z, a, b, eps, M, n_k, n_v, dk, dv, on, scratch, nullptr, nullptr, st);
+}
+
+// Decode step(s) with the layer's a|b projection folded into the mixer (no reference counterpart): `ab` is the fused
+// W8 linear [a rows | b rows] in the reference layout, xq / sx / mx the quantized layer input (det_rmsnorm_quant's output,
+// M rows).  S != NULL: one sequence, M = 1.  rows != NULL: M sequences, one token each (see det_gdn_rows).  Values equal
+// det_gemm_ex on `ab` followed by det_gdn / det_gdn_rows.
+void det_gdn_ab(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_state* rows, const det_qlinear* ab,
+                const int8_t* xq, const float* sx, const uint16_t* mx, const float* qkv, const float* z, float eps, int M,
+                int n_k, int n_v, int dk, int dv, float* on, void* scratch, cudaStream_t st) {
+    DETB_REQUIRE((S != nullptr) != (rows != nullptr), "det_gdn_ab takes one state or a table of states");
+    const AbSource src{ab, xq, sx, mx};
+    gdn_entry(L, S, rows, qkv, z, nullptr, nullptr, eps, M, n_k, n_v, dk, dv, on, scratch, nullptr, nullptr, st, &src);
 }
 
 void det_gdn(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a,

@@ -269,6 +269,32 @@ void CudaBackend::gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, 
                ST);
 }
 
+// ---- batched decode: device tables of the per-sequence caches / states of one layer
+namespace {
+struct CudaRowSet : RowSet {
+    Buf<uint8_t> table;   // det_kv_cache[rows] or det_gdn_state[rows] in device memory
+};
+}  // namespace
+
+bool CudaBackend::gdn_decode_ab(const GdnLayer& l, const GdnState* st, const RowSet* rows, const GdnShape& s,
+                                const Linear& ab, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx,
+                                const Buf<float>& qkv, const Buf<float>& z, const Buf<float>& on) {
+    const CudaLinear& lin = static_cast<const CudaLinear&>(ab);
+    const CudaRowSet* rs = rows ? dynamic_cast<const CudaRowSet*>(rows) : nullptr;
+    if (!fold_ab || lin.bits != 8 || lin.wq.len() == 0 || lin.n() != 2 * s.n_v || (rows && (!rs || !fuse_rows)) ||
+        (!rows && s.m != 1) || (skip_mask & (8 | 32)))
+        return false;
+    flush_pending();
+    det_gdn_layer layer{l.conv->ptr(), l.a->ptr(), l.dt_bias->ptr(), l.norm->ptr()};
+    det_gdn_state state{st ? st->conv_state.ptr() : nullptr, st ? st->s.ptr() : nullptr};
+    det_qlinear q{lin.wq.ptr(), lin.c.ptr(), lin.m.ptr(), (int)lin.n(), (int)lin.k, 8};
+    void* sc = scratch(gdn_scratch_, det_gdn_scratch_bytes((int)s.m, (int)s.n_k, (int)s.n_v, (int)s.dk, (int)s.dv));
+    det_gdn_ab(&layer, st ? &state : nullptr, rs ? reinterpret_cast<const det_gdn_state*>(rs->table.ptr()) : nullptr, &q,
+               xq.ptr(), sx.ptr(), mx.ptr(), qkv.ptr(), z.ptr(), s.eps, (int)s.m, (int)s.n_k, (int)s.n_v, (int)s.dk,
+               (int)s.dv, on.ptr(), sc, ST);
+    return true;
+}
+
 std::vector<int32_t> CudaBackend::argmax_rows(const Buf<float>& logits, size_t rows, size_t v) {
     if (!fuse_rows) return Backend::argmax_rows(logits, rows, v);
     flush_pending();
@@ -297,12 +323,6 @@ std::vector<int32_t> CudaBackend::sample_rows(const Buf<float>& logits, size_t r
     return out;
 }
 
-// ---- batched decode: device tables of the per-sequence caches / states of one layer
-namespace {
-struct CudaRowSet : RowSet {
-    Buf<uint8_t> table;   // det_kv_cache[rows] or det_gdn_state[rows] in device memory
-};
-}  // namespace
 
 std::unique_ptr<RowSet> CudaBackend::make_rowset(std::vector<const KvCache*> kv, std::vector<const GdnState*> st) {
     auto r = std::make_unique<CudaRowSet>();

@@ -51,6 +51,12 @@ class CudaBackend : public Backend {
     std::vector<int32_t> argmax_rows(const Buf<float>& logits, size_t rows, size_t v) override;
     std::vector<int32_t> sample_rows(const Buf<float>& logits, size_t rows, size_t v, float inv_temp, size_t top_k,
                                      float top_p, const std::vector<uint64_t>& z) override;
+    bool gdn_decode_ab(const GdnLayer& l, const GdnState* st, const RowSet* rows, const GdnShape& s, const Linear& ab,
+                       const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx, const Buf<float>& qkv,
+                       const Buf<float>& z, const Buf<float>& on) override;
+    // gdn_decode_ab is off by default: measured on the 27B shape it lengthens every recurrence CTA's critical path by more
+    // than the a|b GEMV launch it removes costs (6.79 vs 6.55 ms per token)
+    bool fold_ab = false;
     bool fuse_rows = true;
     void add(const Buf<float>& x, const Buf<float>& y, size_t n) override;
     void silu_mul(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<float>& h) override;

@@ -219,6 +219,14 @@ void det_gdn_rows(const det_gdn_layer* L, const det_gdn_state* rows, const float
                   const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
                   cudaStream_t st);
 
+/* Decode step(s) of a Gated DeltaNet layer with its a|b projection folded into the mixer kernel (no reference
+ * counterpart): `ab` is the fused W8 linear [a rows | b rows] in the reference layout, xq / sx / mx the quantized layer
+ * input (M rows of K).  Exactly one of S (one sequence, M = 1) and rows (M sequences, device table) is non-NULL.
+ * Values equal det_gemm_ex on `ab` followed by det_gdn / det_gdn_rows; one GEMV launch per layer less.                */
+void det_gdn_ab(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_state* rows, const det_qlinear* ab,
+                const int8_t* xq, const float* sx, const uint16_t* mx, const float* qkv, const float* z, float eps, int M,
+                int n_k, int n_v, int dk, int dv, float* on, void* scratch, cudaStream_t st);
+
 /* Tensor-parallel exchange over NVLink peer memory (no reference counterpart: the reference is single-device).  Every
  * rank creates a staging area of the same size, publishes its CUDA IPC handle (64 bytes) and opens the others'.
  * det_xchg_all_gather sends local[M][slice] to every rank as self-validating 16-byte packets (plain peer stores) and
