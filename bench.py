@@ -208,7 +208,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # N > 1: tensor parallel over NVLink.  torch.distributed (gloo, CPU) only carries the NCCL id, the barriers and the
     # max-over-ranks of the timings; the data path uses the library's own NCCL communicator on its queue.
     dist, comm = None, None
+    saved_stdout = None
     if world > 1:
+        # libraries loaded for the exchange (NCCL) may print banners on stdout; the contract is ONE JSON line there
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
         import torch
         import torch.distributed as dist_mod
         dist_mod.init_process_group("gloo")
@@ -350,6 +355,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if err:
         raise RuntimeError(f"device-side wait reported error {err}")
 
+    if saved_stdout is not None:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
     if rank != 0:
         return
     peak, peak_kind = _peaks()
