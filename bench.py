@@ -141,9 +141,10 @@ def _check(rc, h):
         raise RuntimeError(h.dh_last_error().decode())
 
 
-def cpu_baseline(h, cfg: str, threads: int, tokens: int = 2):
-    """The CPU reference port (oracle: restated `--backend ref`, OpenMP over independent rows) on a bounded slice of the
-    same model: the first 4 and the first 8 layers plus the output head; the per-token time of the full depth is
+def cpu_baseline(h, cfg: str, threads: int, tokens: int = 6):
+    """The CPU port (oracle/: the restated reference backend with the restated x86 integer GEMM of `--backend cpu` for the
+    linears — AVX-VNNI or AVX2, OpenMP over independent rows — and the scalar spec for everything else) on a bounded slice
+    of the same model: the first 4 and the first 8 layers plus the output head; the per-token time of the full depth is
     extrapolated from the two (every 4-layer block has the same shapes)."""
     import importlib.util
     import numpy as np
@@ -152,9 +153,10 @@ def cpu_baseline(h, cfg: str, threads: int, tokens: int = 2):
     spec.loader.exec_module(ob)
     os.environ.setdefault("OMP_NUM_THREADS", str(threads))
     o = C.CDLL(str(ob.build()))
-    o.orc_ref_backend_new.restype = C.c_void_p
+    o.orc_cpu_backend_new.restype = C.c_void_p
     o.orc_ref_backend_free.argtypes = [C.c_void_p]
-    rb = o.orc_ref_backend_new()
+    rb = o.orc_cpu_backend_new()
+    simd = {2: "AVX-VNNI vpdpbusd", 1: "AVX2 vpmaddubsw", 0: "no SIMD on this host: scalar spec"}[o.orc_cpu_simd_level()]
     vocab = SHAPES[cfg]["vocab"]
     ids = _prompt(h, 8, vocab)
     times = {}
@@ -184,7 +186,8 @@ def cpu_baseline(h, cfg: str, threads: int, tokens: int = 2):
         per_token = times[4]
     return {"value": 1.0 / per_token, "unit": "tok/s", "cores": threads, "kind": "port",
             "sample": f"{cfg} shape, first 4 and 8 layers + W8 head, {tokens} decode tokens each at position 8, "
-                      f"extrapolated linearly to {full} layers; restated --backend ref (scalar spec, OpenMP over rows)",
+                      f"extrapolated linearly to {full} layers; restated reference backend, linears through the restated "
+                      f"x86 integer GEMM ({simd}), OpenMP over rows, scalar spec for the other ops",
             "ms_per_token_4_layers": times[4] * 1e3, "ms_per_token_8_layers": times.get(8, 0) * 1e3}
 
 
@@ -405,8 +408,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
 def run_reference(args, rank: int, world: int):
     """`--impl reference`: the reference's own CPU path for the same metric.  The reference is Rust and cannot be built
-    here (no cargo / rustc), so this arm times the CPU port of its `--backend ref` (oracle/) with every host thread on a
-    bounded slice of the same workload; rank 0 alone runs."""
+    here (no cargo / rustc), so this arm times the CPU port under oracle/ — its reference backend with the restated x86
+    integer GEMM of `--backend cpu` for the linears — with every host thread on a bounded slice of the same workload;
+    rank 0 alone runs."""
     if rank != 0:
         return
     from det_b200 import capi
@@ -418,7 +422,7 @@ def run_reference(args, rank: int, world: int):
         pass
     threads = os.cpu_count() or 1
     K, W = args.steps, args.warmup
-    base = cpu_baseline(h, args.config, threads, tokens=max(1, min(K, 2)))
+    base = cpu_baseline(h, args.config, threads, tokens=max(1, min(K, 8)))
     cfg = args.config
     line = {
         "impl": "reference",

@@ -55,6 +55,14 @@ typedef void (*prim_hook_fn)(int op, const float* x, size_t len, size_t m, size_
 extern "C" {
 
 void* orc_ref_backend_new() { return static_cast<det::Backend*>(new oracle::RefBackend()); }
+// The timed CPU baseline: the same backend with the restated x86 integer GEMM (x86_gemm.hpp) for the linears.
+void* orc_cpu_backend_new() {
+    auto* b = new oracle::RefBackend();
+    b->simd = true;
+    return static_cast<det::Backend*>(b);
+}
+// 2: AVX-VNNI path, 1: AVX2 path, 0: no SIMD (the baseline then falls back to the scalar spec)
+int orc_cpu_simd_level() { return x86gemm::have_vnni() ? 2 : x86gemm::have_avx2() ? 1 : 0; }
 void orc_ref_backend_free(void* b) { delete static_cast<det::Backend*>(b); }
 
 // Element-wise spec primitives on host arrays (the oracle side of the det_test_prim comparison).
@@ -123,6 +131,21 @@ void orc_gemm(const uint8_t* rows, size_t n, size_t k, int bits, const int8_t* x
     l.bits = bits;
     float* dsts[1] = {y};
     refops::gemm(l, xq, sx, mx, m, accumulate ? refops::Out::Accumulate : refops::Out::Write, dsts);
+}
+// The restated x86 kernel on det rows (expanded here), for the check against gemm_row.
+void orc_gemm_x86(const uint8_t* rows, size_t n, size_t k, int bits, const int8_t* xq, const float* sx, const uint16_t* mx,
+                  size_t m, float* y) {
+    const size_t g = k / spec::GROUP, rb = spec::det_row_bytes(bits, k);
+    std::vector<int8_t> w8(n * k);
+    std::vector<float> c(n);
+    std::vector<uint16_t> mm(n * g);
+    for (size_t j = 0; j < n; j++) {
+        const spec::DetRow r = spec::det_row(bits, k, rows + j * rb);
+        spec::unpack_row(r.codes, bits, k, w8.data() + j * k);
+        c[j] = r.c;
+        for (size_t gi = 0; gi < g; gi++) mm[j * g + gi] = r.m(gi);
+    }
+    x86gemm::gemm(w8.data(), c.data(), mm.data(), n, k, xq, sx, mx, m, y);
 }
 void orc_unpack_row(const uint8_t* packed, int bits, size_t k, int8_t* out) { spec::unpack_row(packed, bits, k, out); }
 float orc_treesum(const float* x, size_t n) { return spec::treesum(x, n); }

@@ -4,6 +4,7 @@ import ctypes as C
 from pathlib import Path
 
 import numpy as np
+import pytest
 
 G = np.load(Path(__file__).resolve().parent / "golden" / "spec_vectors.npz")
 
@@ -101,3 +102,39 @@ def test_sampler_properties(oracle):
         a = oracle.orc_sample(logits.ctypes.data, len(logits), 0.5, 0, 1.0, z)
         b = oracle.orc_sample(logits.ctypes.data, len(logits), 0.5, len(logits) + 5, 1.0, z)
         assert a == b
+
+
+def test_restated_x86_gemm_equals_gemm_row(oracle):
+    """The SIMD integer GEMM behind the timed CPU baseline (oracle/x86_gemm.hpp, the restated crates/det/src/x86/gemm.rs
+    arithmetic) against the scalar spec gemm_row, on every weight width, extreme codes and ragged token counts."""
+    import ctypes as C
+    if oracle.orc_cpu_simd_level() == 0:
+        pytest.skip("no AVX2 on this host")
+    oracle.orc_gemm_x86.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                    C.c_size_t, C.c_void_p]
+    rng = np.random.default_rng(5)
+    for bits, n, k, m in [(6, 96, 1024, 3), (8, 40, 512, 1), (4, 64, 2560, 5), (6, 33, 128, 2)]:
+        per32 = {8: 32, 6: 24, 4: 16}[bits]
+        g = k // 128
+        nc = k // 32 * per32
+        rows = np.zeros((n, nc + 4 + 2 * g), np.uint8)
+        rows[:, :nc] = rng.integers(0, 256, (n, nc), dtype=np.uint8)
+        rows[0, :nc] = 0xFF          # extreme codes
+        rows[1, :nc] = 0x00
+        c = (1e-8 + rng.random(n) * 1e-6).astype(np.float32)
+        mm = rng.integers(1, 65536, (n, g)).astype(np.uint16)
+        mm[2] = 65535
+        rows[:, nc:nc + 4] = c.view(np.uint8).reshape(n, 4)
+        rows[:, nc + 4:] = mm.view(np.uint8).reshape(n, 2 * g)
+        xq = rng.integers(-127, 128, (m, k)).astype(np.int8)
+        xq[0] = 127
+        if m > 1:
+            xq[1] = -127
+        sx = (1e-3 * (0.5 + rng.random(m))).astype(np.float32)
+        mx = rng.integers(1, 65536, (m, g)).astype(np.uint16)
+        mx[0] = 65535
+        want = np.zeros((m, n), np.float32)
+        got = np.zeros((m, n), np.float32)
+        oracle.orc_gemm(rows.ctypes.data, n, k, bits, xq.ctypes.data, sx.ctypes.data, mx.ctypes.data, m, want.ctypes.data, 0)
+        oracle.orc_gemm_x86(rows.ctypes.data, n, k, bits, xq.ctypes.data, sx.ctypes.data, mx.ctypes.data, m, got.ctypes.data)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (bits, n, k, m)
