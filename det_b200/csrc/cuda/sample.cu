@@ -9,6 +9,9 @@
 // ceil(p24 * total / 2^24) — becomes true.  The draw then walks the kept weights in index order.
 // One CTA of 1024 threads per row.
 #include "runtime.cuh"
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 namespace detb {
 
@@ -69,46 +72,81 @@ struct Cut {
     u64 total;      // sum of kept weights
 };
 
-// The draw: smallest kept index whose inclusive prefix of kept weights exceeds u = z % total.
-// Warp `w` owns the contiguous index range [w * seg, (w + 1) * seg); W(i) returns the weight of index i.
+// The draw: smallest kept index whose inclusive prefix of kept weights exceeds u = z % total.  It runs over a
+// contiguous index range [lo, hi) owned by one CTA (the whole row, or one eighth of it in the cluster kernel) in three
+// steps, so that several CTAs can chain their ranges: count the elements equal to the cut weight, then the kept mass
+// given how many equal elements precede the range, then the walk inside the range that contains the draw.
+// Warp w owns [lo + w * wseg, lo + (w + 1) * wseg); W(i) returns the weight of index i.
+struct WalkRange {
+    int lo, hi, wseg;
+    __device__ WalkRange(int lo_, int hi_) : lo(lo_), hi(hi_) {
+        const int len = hi_ > lo_ ? hi_ - lo_ : 0;
+        wseg = (((len + SW - 1) / SW) + 31) & ~31;
+        if (wseg == 0) wseg = 32;
+    }
+    __device__ int wlo() const { return lo + (threadIdx.x >> 5) * wseg; }
+    __device__ int whi() const { return min(hi, wlo() + wseg); }
+};
+
+// elements of the range equal to the cut weight: per warp into sh32[], returns the range's total
 template <class WF>
-__device__ int walk(const WF& W, int V, const Cut& cut, u64 z, u64* sh64, unsigned* sh32) {
+__device__ unsigned range_eq(const WF& W, const WalkRange& r, const Cut& cut, unsigned* sh32) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int seg = (((V + SW - 1) / SW) + 31) & ~31;
-    const int lo = warp * seg, hi = min(V, lo + seg);
-    // equal-weight rank base per warp
     unsigned eq = 0;
     if (cut.filtered)
-        for (int i = lo + lane; i < hi; i += 32) eq += (W(i) == cut.wstar) ? 1u : 0u;
+        for (int i = r.wlo() + lane; i < r.whi(); i += 32) eq += (W(i) == cut.wstar) ? 1u : 0u;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) eq += __shfl_xor_sync(FULL, eq, off);
     __syncthreads();
     if (lane == 0) sh32[warp] = eq;
     __syncthreads();
-    u64 eq_base = 0;
-    for (int w = 0; w < warp; w++) eq_base += sh32[w];
-    // kept mass per warp
-    auto kept_weight = [&](int i, u64& eq_seen) -> u64 {
-        // called by all lanes of the warp for indices i = base + lane in lockstep
-        const bool in = i < hi;
-        const u64 wv = in ? W(i) : 0;
-        if (!cut.filtered) return wv;
-        const bool is_eq = in && wv == cut.wstar;
-        const unsigned mask = __ballot_sync(FULL, is_eq);
-        const u64 rank = eq_seen + __popc(mask & ((1u << lane) - 1u));
-        eq_seen += __popc(mask);
-        if (!in) return 0;
-        if (wv > cut.wstar) return wv;
-        return (is_eq && rank < cut.e) ? wv : 0;
-    };
-    u64 mass = 0, seen = eq_base;
-    for (int b = lo; b < lo + seg; b += 32) mass += kept_weight(b + lane, seen);
+    unsigned tot = 0;
+    for (int w = 0; w < SW; w++) tot += sh32[w];
+    return tot;
+}
+
+// kept weight of index base + lane (all lanes of the warp in lockstep); eq_seen counts the equal elements before it
+template <class WF>
+__device__ __forceinline__ u64 kept_weight(const WF& W, const Cut& cut, int i, int hi, u64& eq_seen) {
+    const int lane = threadIdx.x & 31;
+    const bool in = i < hi;
+    const u64 wv = in ? W(i) : 0;
+    if (!cut.filtered) return wv;
+    const bool is_eq = in && wv == cut.wstar;
+    const unsigned mask = __ballot_sync(FULL, is_eq);
+    const u64 rank = eq_seen + __popc(mask & ((1u << lane) - 1u));
+    eq_seen += __popc(mask);
+    if (!in) return 0;
+    if (wv > cut.wstar) return wv;
+    return (is_eq && rank < cut.e) ? wv : 0;
+}
+
+// kept mass of the range given `eq_before` equal elements in front of it: per warp into sh64[], returns the total.
+// sh32[] must still hold range_eq's per-warp counts.
+template <class WF>
+__device__ u64 range_mass(const WF& W, const WalkRange& r, const Cut& cut, u64 eq_before, const unsigned* sh32, u64* sh64) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    u64 seen = eq_before;
+    for (int w = 0; w < warp; w++) seen += sh32[w];
+    u64 mass = 0;
+    for (int b = r.wlo(); b < r.wlo() + r.wseg; b += 32) mass += kept_weight(W, cut, b + lane, r.whi(), seen);
     mass = warp_sum_u64(mass);
     __syncthreads();
     if (lane == 0) sh64[warp] = mass;
     __syncthreads();
-    const u64 u = z % cut.total;
-    u64 before = 0;
+    u64 tot = 0;
+    for (int w = 0; w < SW; w++) tot += sh64[w];
+    return tot;
+}
+
+// the walk inside the range that holds the draw: `before` is the kept mass in front of the range.  Returns the index
+// in every thread (through sh32[0]).
+template <class WF>
+__device__ int range_pick(const WF& W, const WalkRange& r, const Cut& cut, u64 eq_before, u64 before, u64 u,
+                          unsigned* sh32, const u64* sh64) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    u64 eq_base = eq_before;
+    for (int w = 0; w < warp; w++) eq_base += sh32[w];
     int target = -1;
     for (int w = 0; w < SW; w++) {
         const u64 m = sh64[w];
@@ -118,10 +156,9 @@ __device__ int walk(const WF& W, int V, const Cut& cut, u64 z, u64* sh64, unsign
     __syncthreads();
     int result = -1;
     if (warp == target) {
-        u64 run = before;
-        seen = eq_base;
-        for (int b = lo; b < lo + seg && result < 0; b += 32) {
-            const u64 kw = kept_weight(b + lane, seen);
+        u64 run = before, seen = eq_base;
+        for (int b = r.wlo(); b < r.wlo() + r.wseg && result < 0; b += 32) {
+            const u64 kw = kept_weight(W, cut, b + lane, r.whi(), seen);
             const u64 incl = warp_incl_scan_u64(kw, lane) + run;
             const unsigned hit = __ballot_sync(FULL, kw != 0 && incl > u);
             if (hit) result = b + __ffs(hit) - 1;
@@ -131,6 +168,15 @@ __device__ int walk(const WF& W, int V, const Cut& cut, u64 z, u64* sh64, unsign
     }
     __syncthreads();
     return (int)sh32[0];
+}
+
+// one CTA owns the whole row
+template <class WF>
+__device__ int walk(const WF& W, int V, const Cut& cut, u64 z, u64* sh64, unsigned* sh32) {
+    const WalkRange r(0, V);
+    (void)range_eq(W, r, cut, sh32);
+    (void)range_mass(W, r, cut, 0, sh32, sh64);
+    return range_pick(W, r, cut, 0, 0, z % cut.total, sh32, sh64);
 }
 
 __global__ void __launch_bounds__(ST) k_sample_plain(const float* __restrict__ logits, int V, float inv_temp,
@@ -253,6 +299,162 @@ __global__ void __launch_bounds__(ST) k_sample_topkp(const float* __restrict__ l
     if (threadIdx.x == 0) out[blockIdx.x] = r;
 }
 
+// ---- the same sampler with one thread-block CLUSTER per row (large vocabularies).  The histogram passes are bound by the
+// shared-memory atomics of one SM, so the row is cut into SCL contiguous index ranges, one CTA each: maxima, totals,
+// histograms, equal-element counts and kept masses are combined through distributed shared memory (all of them integer
+// sums or maxima: order-free), rank 0 picks the digit, and the CTA whose range holds the draw walks it.
+constexpr int SCL = 8;
+
+__device__ __forceinline__ u64 cluster_sum(cg::cluster_group& cluster, u64* slot, u64 mine, unsigned upto, u64* total) {
+    // publishes `mine`, returns the sum over ranks < upto; *total = sum over all ranks.  Two cluster barriers.
+    if (threadIdx.x == 0) *slot = mine;
+    cluster.sync();
+    u64 before = 0, all = 0;
+    for (unsigned r = 0; r < cluster.num_blocks(); r++) {
+        const u64 v = *cluster.map_shared_rank(slot, r);
+        if (r < upto) before += v;
+        all += v;
+    }
+    cluster.sync();
+    if (total) *total = all;
+    return before;
+}
+
+__global__ void __launch_bounds__(ST) k_sample_topkp_cl(const float* __restrict__ logits, int V, float inv_temp,
+                                                        int use_k, u64 top_k, int use_p, u64 p24,
+                                                        const u64* __restrict__ z, int* __restrict__ out,
+                                                        u64* __restrict__ wbuf_all) {
+    __shared__ float shf[32];
+    __shared__ u64 sh64[SW];
+    __shared__ unsigned sh32[SW];
+    __shared__ unsigned cnt[DIGITS];
+    __shared__ u64 sum[DIGITS];
+    __shared__ u64 sel[6];   // prefix value, k_left, s_left, sum_gt, cnt_sel
+    __shared__ u64 slot;     // this CTA's contribution to a cluster-wide sum
+    __shared__ float fslot;
+    pdl_trigger();
+    pdl_wait();
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned rank = cluster.block_rank();
+    const int rowi = blockIdx.y;
+    const float* row = logits + (size_t)rowi * V;
+    u64* wbuf = wbuf_all + (size_t)rowi * V;
+    const int seg = (((V + SCL - 1) / SCL) + 1023) & ~1023;
+    const int lo = min(V, (int)rank * seg), hi = min(V, lo + seg);
+
+    float mx = -INFINITY;
+    for (int i = lo + threadIdx.x; i < hi; i += ST) mx = fmaxf(mx, fmul(row[i], inv_temp));
+    mx = max_block<SW>(mx, shf);
+    if (threadIdx.x == 0) fslot = mx;
+    cluster.sync();
+    for (unsigned r = 0; r < SCL; r++) mx = fmaxf(mx, *cluster.map_shared_rank(&fslot, r));
+    cluster.sync();
+
+    u64 part = 0;
+    for (int i = lo + threadIdx.x; i < hi; i += ST) {
+        const u64 wv = weight_of(row[i], inv_temp, mx);
+        wbuf[i] = wv;
+        part += wv;
+    }
+    u64 total = 0;
+    (void)cluster_sum(cluster, &slot, block_sum_u64(part, sh64), 0, &total);
+    if (threadIdx.x == 0) {
+        const unsigned __int128 prod = (unsigned __int128)total * p24 + ((((unsigned __int128)1) << 24) - 1);
+        sel[0] = 0;
+        sel[1] = use_k ? top_k : (u64)V;
+        sel[2] = (u64)(prod >> 24);
+        sel[3] = 0;
+    }
+    __syncthreads();
+    for (int pass = 0; pass < 3; pass++) {
+        const int shift = 22 - 11 * pass;
+        for (int i = threadIdx.x; i < DIGITS; i += ST) { cnt[i] = 0; sum[i] = 0; }
+        __syncthreads();
+        const u64 prefix = sel[0];
+        unsigned run_d = 0, run_c = 0;
+        u64 run_s = 0;
+        for (int i = lo + threadIdx.x; i < hi; i += ST) {
+            const u64 wv = wbuf[i];
+            if (pass == 0 || (wv >> (shift + 11)) == prefix) {
+                const unsigned d = (unsigned)(wv >> shift) & (DIGITS - 1);
+                if (d != run_d && run_c) {
+                    atomicAdd(&cnt[run_d], run_c);
+                    atomicAdd(&sum[run_d], run_s);
+                    run_c = 0;
+                    run_s = 0;
+                }
+                run_d = d;
+                run_c++;
+                run_s += wv;
+            }
+        }
+        if (run_c) {
+            atomicAdd(&cnt[run_d], run_c);
+            atomicAdd(&sum[run_d], run_s);
+        }
+        cluster.sync();                 // every range's histogram is complete
+        if (rank == 0) {
+            for (int d = threadIdx.x; d < DIGITS; d += ST) {
+                unsigned c = cnt[d];
+                u64 sm = sum[d];
+                for (unsigned r = 1; r < SCL; r++) {
+                    c += cluster.map_shared_rank(cnt, r)[d];
+                    sm += cluster.map_shared_rank(sum, r)[d];
+                }
+                cnt[d] = c;
+                sum[d] = sm;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                u64 k_left = sel[1], s_left = sel[2], sum_gt = sel[3];
+                int chosen = 0;
+                for (int d = DIGITS - 1; d >= 0; d--) {
+                    const unsigned c = cnt[d];
+                    if (!c) continue;
+                    if ((u64)c >= k_left || (use_p && sum[d] >= s_left)) { chosen = d; break; }
+                    k_left -= c;
+                    s_left -= sum[d];
+                    sum_gt += sum[d];
+                    chosen = d;
+                }
+                sel[0] = (prefix << 11) | (u64)chosen;
+                sel[1] = k_left; sel[2] = s_left; sel[3] = sum_gt;
+                sel[4] = cnt[chosen];
+            }
+        }
+        cluster.sync();                 // rank 0 has read the histograms and published the digit
+        if (rank != 0 && threadIdx.x < 5) sel[threadIdx.x] = cluster.map_shared_rank(sel, 0)[threadIdx.x];
+        cluster.sync();                 // everyone holds the selection; histograms may be cleared again
+    }
+    Cut cut;
+    cut.filtered = 1;
+    cut.wstar = sel[0];
+    {
+        const u64 k_left = sel[1], s_left = sel[2], n_eq = sel[4];
+        u64 e = n_eq;
+        if (use_k && k_left < e) e = k_left;
+        if (use_p) {
+            u64 ep;
+            if (s_left == 0) ep = 1;
+            else if (cut.wstar == 0) ep = n_eq;
+            else ep = (s_left + cut.wstar - 1) / cut.wstar;
+            if (ep < e) e = ep;
+        }
+        cut.e = e;
+        cut.total = sel[3] + e * cut.wstar;
+    }
+    auto W = [&](int i) { return wbuf[i]; };
+    const WalkRange r(lo, hi);
+    const u64 eq_before = cluster_sum(cluster, &slot, (u64)range_eq(W, r, cut, sh32), rank, nullptr);
+    const u64 mass = range_mass(W, r, cut, eq_before, sh32, sh64);
+    const u64 before = cluster_sum(cluster, &slot, mass, rank, nullptr);
+    const u64 u = z[rowi] % cut.total;
+    if (before <= u && u < before + mass) {          // exactly one range holds the draw
+        const int pick = range_pick(W, r, cut, eq_before, before, u, sh32, sh64);
+        if (threadIdx.x == 0) out[rowi] = pick;
+    }
+}
+
 // ---- scratch that lives in the library image, for det_sample_topkp_static
 constexpr long long STATIC_SAMPLE_MAX = 1ll << 19;   // M * V weights of 8 bytes: 4 MiB per GPU that loads the library
 static __device__ __align__(256) unsigned long long g_static_weights[STATIC_SAMPLE_MAX];
@@ -284,6 +486,11 @@ void det_sample_topkp(const float* logits, int M, int V, float inv_temp, int top
     // p24 = rint(top_p * 2^24) in binary64; negative values (and NaN) become 0, as Rust's `as u128` does
     double pr = __builtin_nearbyint((double)top_p * 16777216.0);
     const u64 p24 = (pr != pr || pr <= 0.0) ? 0 : (u64)pr;
+    if (V >= 65536) {   // by shape only: a cluster of CTAs per row for large vocabularies
+        launch_pdl(k_sample_topkp_cl, dim3(SCL, M), dim3(ST), 0, queue_of(st), SCL, logits, V, inv_temp, use_k,
+                   (u64)(top_k > 0 ? top_k : 0), use_p, p24, z, out, static_cast<u64*>(scratch));
+        return;
+    }
     k_sample_topkp<<<M, ST, 0, queue_of(st)>>>(logits, V, inv_temp, use_k, (u64)(top_k > 0 ? top_k : 0), use_p, p24, z,
                                                 out, static_cast<u64*>(scratch));
     DETB_CUDA_OK(cudaGetLastError());
