@@ -299,11 +299,17 @@ __global__ void __launch_bounds__(ST) k_sample_topkp(const float* __restrict__ l
     if (threadIdx.x == 0) out[blockIdx.x] = r;
 }
 
-// ---- the same sampler with one thread-block CLUSTER per row (large vocabularies).  The histogram passes are bound by the
-// shared-memory atomics of one SM, so the row is cut into SCL contiguous index ranges, one CTA each: maxima, totals,
-// histograms, equal-element counts and kept masses are combined through distributed shared memory (all of them integer
-// sums or maxima: order-free), rank 0 picks the digit, and the CTA whose range holds the draw walks it.
+// ---- the sampler for vocabularies up to 262144: a thread-block cluster per row (8 CTAs above 32768 tokens, else 1), each
+// CTA owning a contiguous index range of at most 32768 weights that it keeps in shared memory (low 32 bits + one bit
+// plane for 2^32).  The cut weight w* is found by an 11-step radix select on 3-bit digits, most significant first: every
+// thread bins its elements that match the prefix so far into eight (count, sum) pairs held in REGISTERS — no atomics,
+// which is what bounded the histogram version — the pairs are reduced over the CTA by shuffles and over the cluster
+// through distributed shared memory (integer sums: order-free), and every CTA takes the same decision from the same
+// totals.  One cluster barrier per step (the exchange slots alternate).  The draw then walks the kept weights in index
+// order, range by range (WalkRange).
 constexpr int SCL = 8;
+constexpr int SEL_RANGE = 32768;                  // weights per CTA
+constexpr int SEL_SMEM = SEL_RANGE * 4 + SEL_RANGE / 8;
 
 __device__ __forceinline__ u64 cluster_sum(cg::cluster_group& cluster, u64* slot, u64 mine, unsigned upto, u64* total) {
     // publishes `mine`, returns the sum over ranks < upto; *total = sum over all ranks.  Two cluster barriers.
@@ -320,45 +326,60 @@ __device__ __forceinline__ u64 cluster_sum(cg::cluster_group& cluster, u64* slot
     return before;
 }
 
-__global__ void __launch_bounds__(ST) k_sample_topkp_cl(const float* __restrict__ logits, int V, float inv_temp,
-                                                        int use_k, u64 top_k, int use_p, u64 p24,
-                                                        const u64* __restrict__ z, int* __restrict__ out,
-                                                        u64* __restrict__ wbuf_all) {
+__global__ void __launch_bounds__(ST) k_sample_topkp_sel(const float* __restrict__ logits, int V, float inv_temp,
+                                                         int use_k, u64 top_k, int use_p, u64 p24,
+                                                         const u64* __restrict__ z, int* __restrict__ out,
+                                                         u64* __restrict__ wbuf_all) {
+    extern __shared__ __align__(16) unsigned sel_smem[];
+    unsigned* wlo = sel_smem;                     // low 32 bits of the range's weights
+    unsigned* whi = sel_smem + SEL_RANGE;         // bit 32, one bit per weight
     __shared__ float shf[32];
     __shared__ u64 sh64[SW];
     __shared__ unsigned sh32[SW];
-    __shared__ unsigned cnt[DIGITS];
-    __shared__ u64 sum[DIGITS];
-    __shared__ u64 sel[6];   // prefix value, k_left, s_left, sum_gt, cnt_sel
-    __shared__ u64 slot;     // this CTA's contribution to a cluster-wide sum
+    __shared__ unsigned red_c[SW][8];
+    __shared__ u64 red_s[SW][8];
+    __shared__ unsigned slot_c[2][8];             // this CTA's digit counts / sums of a step (read by the cluster)
+    __shared__ u64 slot_s[2][8];
+    __shared__ unsigned tot_c[8];
+    __shared__ u64 tot_s[8];
+    __shared__ u64 sel[6];                        // prefix value, k_left, s_left, sum_gt, cnt_sel
+    __shared__ u64 slot;
     __shared__ float fslot;
     pdl_trigger();
     pdl_wait();
     cg::cluster_group cluster = cg::this_cluster();
-    const unsigned rank = cluster.block_rank();
+    const unsigned rank = cluster.block_rank(), nranks = cluster.num_blocks();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int rowi = blockIdx.y;
     const float* row = logits + (size_t)rowi * V;
     u64* wbuf = wbuf_all + (size_t)rowi * V;
-    const int seg = (((V + SCL - 1) / SCL) + 1023) & ~1023;
-    const int lo = min(V, (int)rank * seg), hi = min(V, lo + seg);
+    const int seg = (((V + (int)nranks - 1) / (int)nranks) + 1023) & ~1023;      // <= SEL_RANGE by the launcher's rule
+    const int lo = min(V, (int)rank * seg), hi = min(V, lo + seg), len = hi - lo;
 
     float mx = -INFINITY;
     for (int i = lo + threadIdx.x; i < hi; i += ST) mx = fmaxf(mx, fmul(row[i], inv_temp));
     mx = max_block<SW>(mx, shf);
     if (threadIdx.x == 0) fslot = mx;
     cluster.sync();
-    for (unsigned r = 0; r < SCL; r++) mx = fmaxf(mx, *cluster.map_shared_rank(&fslot, r));
+    for (unsigned r = 0; r < nranks; r++) mx = fmaxf(mx, *cluster.map_shared_rank(&fslot, r));
     cluster.sync();
 
     u64 part = 0;
-    for (int i = lo + threadIdx.x; i < hi; i += ST) {
-        const u64 wv = weight_of(row[i], inv_temp, mx);
-        wbuf[i] = wv;
-        part += wv;
+    for (int j = threadIdx.x; j < seg; j += ST) {          // whole warps: the ballot needs every lane
+        u64 wv = 0;
+        if (j < len) {
+            wv = weight_of(row[lo + j], inv_temp, mx);
+            wbuf[lo + j] = wv;
+            wlo[j] = (unsigned)wv;
+            part += wv;
+        }
+        const unsigned top = __ballot_sync(FULL, (wv >> 32) != 0);
+        if (lane == 0 && j < len) whi[j >> 5] = top;
     }
     u64 total = 0;
     (void)cluster_sum(cluster, &slot, block_sum_u64(part, sh64), 0, &total);
     if (threadIdx.x == 0) {
+        // thresh = ceil(total * p24 / 2^24)  (spec/sample.rs:60-62), 128-bit intermediate
         const unsigned __int128 prod = (unsigned __int128)total * p24 + ((((unsigned __int128)1) << 24) - 1);
         sel[0] = 0;
         sel[1] = use_k ? top_k : (u64)V;
@@ -366,65 +387,74 @@ __global__ void __launch_bounds__(ST) k_sample_topkp_cl(const float* __restrict_
         sel[3] = 0;
     }
     __syncthreads();
-    for (int pass = 0; pass < 3; pass++) {
-        const int shift = 22 - 11 * pass;
-        for (int i = threadIdx.x; i < DIGITS; i += ST) { cnt[i] = 0; sum[i] = 0; }
-        __syncthreads();
+    // eleven 3-bit digits, most significant first: bits [32:30], [29:27], ..., [2:0]
+    for (int pass = 0; pass < 11; pass++) {
+        const int shift = 30 - 3 * pass;
         const u64 prefix = sel[0];
-        unsigned run_d = 0, run_c = 0;
-        u64 run_s = 0;
-        for (int i = lo + threadIdx.x; i < hi; i += ST) {
-            const u64 wv = wbuf[i];
-            if (pass == 0 || (wv >> (shift + 11)) == prefix) {
-                const unsigned d = (unsigned)(wv >> shift) & (DIGITS - 1);
-                if (d != run_d && run_c) {
-                    atomicAdd(&cnt[run_d], run_c);
-                    atomicAdd(&sum[run_d], run_s);
-                    run_c = 0;
-                    run_s = 0;
+        unsigned c[8];
+        u64 sm[8];
+#pragma unroll
+        for (int b = 0; b < 8; b++) { c[b] = 0; sm[b] = 0; }
+        for (int j = threadIdx.x; j < len; j += ST) {
+            const u64 wv = (u64)wlo[j] | ((u64)((whi[j >> 5] >> (j & 31)) & 1u) << 32);
+            if (pass == 0 || (wv >> (shift + 3)) == prefix) {
+                const unsigned d = (unsigned)(wv >> shift) & 7u;
+#pragma unroll
+                for (int b = 0; b < 8; b++) {
+                    const bool hit = d == (unsigned)b;
+                    c[b] += hit ? 1u : 0u;
+                    sm[b] += hit ? wv : 0ull;
                 }
-                run_d = d;
-                run_c++;
-                run_s += wv;
             }
         }
-        if (run_c) {
-            atomicAdd(&cnt[run_d], run_c);
-            atomicAdd(&sum[run_d], run_s);
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) c[b] += __shfl_xor_sync(FULL, c[b], off);
+            sm[b] = warp_sum_u64(sm[b]);
         }
-        cluster.sync();                 // every range's histogram is complete
-        if (rank == 0) {
-            for (int d = threadIdx.x; d < DIGITS; d += ST) {
-                unsigned c = cnt[d];
-                u64 sm = sum[d];
-                for (unsigned r = 1; r < SCL; r++) {
-                    c += cluster.map_shared_rank(cnt, r)[d];
-                    sm += cluster.map_shared_rank(sum, r)[d];
-                }
-                cnt[d] = c;
-                sum[d] = sm;
-            }
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                u64 k_left = sel[1], s_left = sel[2], sum_gt = sel[3];
-                int chosen = 0;
-                for (int d = DIGITS - 1; d >= 0; d--) {
-                    const unsigned c = cnt[d];
-                    if (!c) continue;
-                    if ((u64)c >= k_left || (use_p && sum[d] >= s_left)) { chosen = d; break; }
-                    k_left -= c;
-                    s_left -= sum[d];
-                    sum_gt += sum[d];
-                    chosen = d;
-                }
-                sel[0] = (prefix << 11) | (u64)chosen;
-                sel[1] = k_left; sel[2] = s_left; sel[3] = sum_gt;
-                sel[4] = cnt[chosen];
-            }
+        if (lane == 0) {
+#pragma unroll
+            for (int b = 0; b < 8; b++) { red_c[warp][b] = c[b]; red_s[warp][b] = sm[b]; }
         }
-        cluster.sync();                 // rank 0 has read the histograms and published the digit
-        if (rank != 0 && threadIdx.x < 5) sel[threadIdx.x] = cluster.map_shared_rank(sel, 0)[threadIdx.x];
-        cluster.sync();                 // everyone holds the selection; histograms may be cleared again
+        __syncthreads();
+        const int par = pass & 1;
+        if (threadIdx.x < 8) {
+            unsigned cc = 0;
+            u64 ss = 0;
+            for (int w = 0; w < SW; w++) { cc += red_c[w][threadIdx.x]; ss += red_s[w][threadIdx.x]; }
+            slot_c[par][threadIdx.x] = cc;
+            slot_s[par][threadIdx.x] = ss;
+        }
+        cluster.sync();                 // every range's digit sums of this step are published
+        if (threadIdx.x < 8) {
+            unsigned cc = 0;
+            u64 ss = 0;
+            for (unsigned r = 0; r < nranks; r++) {
+                cc += cluster.map_shared_rank(&slot_c[par][0], r)[threadIdx.x];
+                ss += cluster.map_shared_rank(&slot_s[par][0], r)[threadIdx.x];
+            }
+            tot_c[threadIdx.x] = cc;
+            tot_s[threadIdx.x] = ss;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            u64 k_left = sel[1], s_left = sel[2], sum_gt = sel[3];
+            int chosen = 0;
+            for (int d = 7; d >= 0; d--) {
+                const unsigned cd = tot_c[d];
+                if (!cd) continue;
+                if ((u64)cd >= k_left || (use_p && tot_s[d] >= s_left)) { chosen = d; break; }
+                k_left -= cd;
+                s_left -= tot_s[d];
+                sum_gt += tot_s[d];
+                chosen = d;   // stays the lowest non-empty digit when nothing triggers (cannot happen for valid input)
+            }
+            sel[0] = (prefix << 3) | (u64)chosen;
+            sel[1] = k_left; sel[2] = s_left; sel[3] = sum_gt;
+            sel[4] = tot_c[chosen];
+        }
+        __syncthreads();
     }
     Cut cut;
     cut.filtered = 1;
@@ -453,6 +483,26 @@ __global__ void __launch_bounds__(ST) k_sample_topkp_cl(const float* __restrict_
         const int pick = range_pick(W, r, cut, eq_before, before, u, sh32, sh64);
         if (threadIdx.x == 0) out[rowi] = pick;
     }
+}
+
+// Launches the top-k / top-p kernel for a shape: the register-binned cluster kernel up to 262144 tokens, the
+// shared-memory histogram kernel (one CTA per row) above.
+static cudaError_t launch_topkp(const float* logits, int M, int V, float inv_temp, int use_k, u64 top_k, int use_p, u64 p24,
+                                const u64* z, int* out, u64* wbuf, cudaStream_t q) {
+    if (V <= SCL * SEL_RANGE) {
+        const int cl = V > SEL_RANGE ? SCL : 1;
+        static bool attr = false;
+        if (!attr) {
+            const cudaError_t e = cudaFuncSetAttribute(k_sample_topkp_sel, cudaFuncAttributeMaxDynamicSharedMemorySize, SEL_SMEM);
+            if (e != cudaSuccess) return e;
+            attr = true;
+        }
+        launch_pdl(k_sample_topkp_sel, dim3(cl, M), dim3(ST), SEL_SMEM, q, cl, logits, V, inv_temp, use_k, top_k, use_p, p24,
+                   z, out, wbuf);
+        return cudaSuccess;
+    }
+    k_sample_topkp<<<M, ST, 0, q>>>(logits, V, inv_temp, use_k, top_k, use_p, p24, z, out, wbuf);
+    return cudaGetLastError();
 }
 
 // ---- scratch that lives in the library image, for det_sample_topkp_static
@@ -486,14 +536,8 @@ void det_sample_topkp(const float* logits, int M, int V, float inv_temp, int top
     // p24 = rint(top_p * 2^24) in binary64; negative values (and NaN) become 0, as Rust's `as u128` does
     double pr = __builtin_nearbyint((double)top_p * 16777216.0);
     const u64 p24 = (pr != pr || pr <= 0.0) ? 0 : (u64)pr;
-    if (V >= 65536) {   // by shape only: a cluster of CTAs per row for large vocabularies
-        launch_pdl(k_sample_topkp_cl, dim3(SCL, M), dim3(ST), 0, queue_of(st), SCL, logits, V, inv_temp, use_k,
-                   (u64)(top_k > 0 ? top_k : 0), use_p, p24, z, out, static_cast<u64*>(scratch));
-        return;
-    }
-    k_sample_topkp<<<M, ST, 0, queue_of(st)>>>(logits, V, inv_temp, use_k, (u64)(top_k > 0 ? top_k : 0), use_p, p24, z,
-                                                out, static_cast<u64*>(scratch));
-    DETB_CUDA_OK(cudaGetLastError());
+    DETB_CUDA_OK(launch_topkp(logits, M, V, inv_temp, use_k, (u64)(top_k > 0 ? top_k : 0), use_p, p24, z, out,
+                              static_cast<u64*>(scratch), queue_of(st)));
 }
 
 // Top-k / top-p sampling for callers that must not allocate.  Same result as det_sample_topkp, but the weight buffer is
@@ -546,8 +590,12 @@ int det_sample_topkp_static(const float* logits, int M, int V, float inv_temp, i
     } else {
         double pr = __builtin_nearbyint((double)top_p * 16777216.0);
         const u64 p24 = (pr != pr || pr <= 0.0) ? 0 : (u64)pr;
-        k_sample_topkp<<<M, ST, 0, queue_of(st)>>>(logits, V, inv_temp, use_k, (u64)(top_k > 0 ? top_k : 0), use_p, p24, z,
-                                                    out, addr[dev]);
+        const cudaError_t le = launch_topkp(logits, M, V, inv_temp, use_k, (u64)(top_k > 0 ? top_k : 0), use_p, p24, z, out,
+                                            addr[dev], queue_of(st));
+        if (le != cudaSuccess) {
+            fprintf(stderr, "det_b200: det_sample_topkp_static: launch failed: %s\n", cudaGetErrorString(le));
+            return 1;
+        }
     }
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
