@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Headline benchmark: greedy decode of the seeded random-init 27B-shape W6 model at batch 1 (BASELINE configs[3]):
+"""Headline benchmark: greedy decode of the seeded random-init 27B-shape W6 model at batch 1 (the 27B benchmark configuration):
 prefill of 2048 seeded tokens in 512-token chunks, then decode steps.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 27b|4b|tiny]
@@ -439,7 +439,7 @@ def run_reference(args, rank: int, world: int):
 
 
 def run_serving(args, local_rank: int):
-    """BASELINE configs[4]: `--seqs` independent sequences (contexts uniform in [ctx-min, ctx-max], seeded) decode
+    """The serving configuration: `--seqs` independent sequences (contexts uniform in [ctx-min, ctx-max], seeded) decode
     `--new` tokens each at temp 0.7 / top-p 0.95 / top-k 40 with per-sequence seeds, one batched step per token.  Not the
     headline line: a second workload, printed in the same format (one step = one token for every sequence)."""
     import numpy as np

@@ -15,6 +15,7 @@
 // the canonical K-major SWIZZLE_128B layout the UMMA shared-memory descriptor names.  No multicast anywhere.
 #include "gemm_common.cuh"
 #include <cuda.h>
+#include <algorithm>
 
 namespace detb {
 
@@ -119,6 +120,10 @@ struct TcArgs {
     const uint16_t* mx;   // may be NULL
     int* error_flag;
     OutSpec out;
+    // split K (gridDim.z > 1): each CTA takes a run of groups and adds its exact int64 partial sums into `part`
+    // ([tile][token][row]); the CTA that arrives last at the tile's counter converts and emits, and leaves both zeroed
+    unsigned long long* part;
+    unsigned* counters;
 };
 
 // Shared memory: [stages x (A 16 KB | B)] (1024-byte aligned) [mx table: G x TOK u16] [barriers] [tmem address]
@@ -143,6 +148,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.x * TC_TOK, n0 = blockIdx.y * TC_ROWS;
     const int G = a.G;
+    // this CTA's run of groups: [g0, g0 + GL)
+    const int gper = (G + gridDim.z - 1) / gridDim.z;
+    const int g0 = blockIdx.z * gper;
+    const int GL = max(0, min(G, g0 + gper) - g0);
     pdl_trigger();
 
     if (threadIdx.x == 0) {
@@ -172,24 +181,24 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         // ---------------- TMA producer.  Weights do not depend on the previous kernel: the first stages' weight boxes are
         // requested before griddepcontrol.wait, the activation boxes after it.
         if (lane == 0) {
-            const int lead = G < TC_STAGES ? G : TC_STAGES;
-            for (int g = 0; g < lead; g++) {
-                uint8_t* st = stages + (size_t)g * TC_STAGE_BYTES;
-                mbar_expect_tx(&full[g], TC_STAGE_BYTES);
-                tma_load_2d(st, &map_w, 0, (blockIdx.y * G + g) * TC_ROWS, &full[g]);
+            const int lead = GL < TC_STAGES ? GL : TC_STAGES;
+            for (int l = 0; l < lead; l++) {
+                uint8_t* st = stages + (size_t)l * TC_STAGE_BYTES;
+                mbar_expect_tx(&full[l], TC_STAGE_BYTES);
+                tma_load_2d(st, &map_w, 0, (blockIdx.y * G + g0 + l) * TC_ROWS, &full[l]);
             }
             pdl_wait();
-            for (int g = 0; g < lead; g++)
-                tma_load_2d(stages + (size_t)g * TC_STAGE_BYTES + TC_A_BYTES, &map_x, g * TC_KB, t0, &full[g]);
+            for (int l = 0; l < lead; l++)
+                tma_load_2d(stages + (size_t)l * TC_STAGE_BYTES + TC_A_BYTES, &map_x, (g0 + l) * TC_KB, t0, &full[l]);
             int issued = lead;
-            for (int g = lead; g < G; g++, issued++) {
-                const int s = g % TC_STAGES;
-                ok = mbar_wait(&empty[s], ((unsigned)(g / TC_STAGES) & 1u) ^ 1u);
+            for (int l = lead; l < GL; l++, issued++) {
+                const int s = l % TC_STAGES;
+                ok = mbar_wait(&empty[s], ((unsigned)(l / TC_STAGES) & 1u) ^ 1u);
                 if (!ok) break;
                 uint8_t* st = stages + (size_t)s * TC_STAGE_BYTES;
                 mbar_expect_tx(&full[s], TC_STAGE_BYTES);
-                tma_load_2d(st, &map_w, 0, (blockIdx.y * G + g) * TC_ROWS, &full[s]);
-                tma_load_2d(st + TC_A_BYTES, &map_x, g * TC_KB, t0, &full[s]);
+                tma_load_2d(st, &map_w, 0, (blockIdx.y * G + g0 + l) * TC_ROWS, &full[s]);
+                tma_load_2d(st + TC_A_BYTES, &map_x, (g0 + l) * TC_KB, t0, &full[s]);
             }
             if (!ok) {
                 atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
@@ -202,7 +211,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     } else if (warp == 1) {
         // ---------------- MMA issue: four K = 32 steps per group into TMEM buffer g & 1
         if (lane == 0) {
-            for (int g = 0; g < G; g++) {
+            for (int g = 0; g < GL; g++) {          // local group index
                 const int s = g % TC_STAGES, b = g % NBUF;
                 ok = mbar_wait(&full[s], (unsigned)(g / TC_STAGES) & 1u) &&
                      mbar_wait(&tempty[b], ((unsigned)(g / NBUF) & 1u) ^ 1u);
@@ -238,9 +247,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #pragma unroll
         for (int t = 0; t < EC; t++) acc[t] = 0;
         const uint16_t* mrow = a.m + (size_t)(n < a.N ? n : 0) * G;
-        for (int g = 0; g < G; g++) {
-            const int b = g % NBUF;
-            ok = mbar_wait(&tfull[b], (unsigned)(g / NBUF) & 1u);
+        for (int l = 0; l < GL; l++) {
+            const int b = l % NBUF, g = g0 + l;
+            ok = mbar_wait(&tfull[b], (unsigned)(l / NBUF) & 1u);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             int r[EC];
@@ -259,6 +268,26 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             }
         }
         if (!ok && lane == 0) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
+        if (gridDim.z > 1) {
+            // split K: add this CTA's partial sums to the tile's cells; the last of the tile's CTAs takes the totals
+            __shared__ unsigned last_cta;
+            const unsigned tile = blockIdx.y * gridDim.x + blockIdx.x;
+            unsigned long long* cell = a.part + ((size_t)tile * TC_TOK + half * EC) * TC_ROWS + (q * 32 + lane);
+#pragma unroll
+            for (int t = 0; t < EC; t++) atomicAdd(cell + (size_t)t * TC_ROWS, (unsigned long long)acc[t]);
+            __threadfence();
+            asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
+            if (et == 0) last_cta = atomicAdd(a.counters + tile, 1u) == gridDim.z - 1;
+            asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
+            if (last_cta) {
+                __threadfence();
+#pragma unroll
+                for (int t = 0; t < EC; t++) acc[t] = (long long)atomicExch(cell + (size_t)t * TC_ROWS, 0ull);
+                if (et == 0) a.counters[tile] = 0;
+            } else {
+                ok = false;        // nothing to emit from this CTA
+            }
+        }
         if (ok && n < a.N) {
             const float cn = a.c[n];
 #pragma unroll
@@ -353,13 +382,42 @@ static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const flo
     a.error_flag = error_word();
     a.out = out;
     const size_t smem = 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES + (size_t)G * TC_TOK * 2 + 16 + (2 * TC_STAGES + 2 * Cfg::NBUF) * 8 + 16;
-    static bool configured = false;
-    if (!configured) {
-        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemm_tc<TOK, EC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin()));
-        configured = true;
+    DETB_REQUIRE(smem + 64 <= smem_optin(), "K is too large for the tensor-core GEMM's multiplier table");
+    static size_t configured = 0;     // the kernel also has a few bytes of static shared memory
+    if (smem > configured) {
+        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemm_tc<TOK, EC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
     }
-    DETB_REQUIRE(smem <= smem_optin(), "K is too large for the tensor-core GEMM's multiplier table");
-    const dim3 grid((M + TC_TOK - 1) / TC_TOK, (N + TC_ROWS - 1) / TC_ROWS);
+    dim3 grid((M + TC_TOK - 1) / TC_TOK, (N + TC_ROWS - 1) / TC_ROWS);
+    // Few tiles (a narrow linear at a small batch) leave most SMs idle: split K over up to 4 CTAs per tile.  The partial
+    // sums are exact integers, so the split cannot change a result.  By shape only.
+    a.part = nullptr;
+    a.counters = nullptr;
+    const int tiles = (int)(grid.x * grid.y);
+    int ksplit = 1;
+    if (tiles * 2 <= sm_count() && G >= 16) ksplit = std::min(4, std::min(sm_count() / tiles, G / 8));
+    if (ksplit > 1) {
+        // scratch: int64 cells for at most sm_count()/2 tiles of 128 x 128, plus their counters; allocated at first
+        // use (never inside a stream capture: the captured decode step has M = 1 and does not come here)
+        static unsigned long long* cells = nullptr;
+        static unsigned* counters = nullptr;
+        if (!cells) {
+            cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+            DETB_CUDA_OK(cudaStreamIsCapturing(q, &cs));
+            if (cs == cudaStreamCaptureStatusNone) {
+                const size_t ncell = (size_t)(sm_count() / 2 + 1) * 128 * TC_ROWS;
+                DETB_CUDA_OK(cudaMalloc(&cells, ncell * 8));
+                DETB_CUDA_OK(cudaMemset(cells, 0, ncell * 8));
+                DETB_CUDA_OK(cudaMalloc(&counters, (sm_count() / 2 + 1) * sizeof(unsigned)));
+                DETB_CUDA_OK(cudaMemset(counters, 0, (sm_count() / 2 + 1) * sizeof(unsigned)));
+            }
+        }
+        if (cells) {
+            a.part = cells;
+            a.counters = counters;
+            grid.z = ksplit;
+        }
+    }
     launch_pdl(k_gemm_tc<TOK, EC>, grid, dim3(Cfg::THREADS), smem, q, 1, map_w, map_x, a);
 }
 

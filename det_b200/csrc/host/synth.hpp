@@ -28,7 +28,7 @@ struct Config {
     size_t conv_dim() const { return 2 * gdn_k_heads * gdn_dk + gdn_v_heads * gdn_dv; }             // config.rs:103-105
 };
 
-// The three shapes BASELINE's configs name.  `layers` overrides the depth when non-zero (bounded CPU-baseline samples).
+// The three model shapes of the benchmark configurations (tiny, 4B, 27B).  `layers` overrides the depth when non-zero (bounded CPU-baseline samples).
 Config config_tiny();
 Config config_4b();
 Config config_27b();

@@ -1,4 +1,4 @@
-// TEST / BASELINE INFRASTRUCTURE — not part of the product.  The integer GEMM of the reference's x86 backend
+// TEST AND CPU-BASELINE INFRASTRUCTURE — not part of the product.  The integer GEMM of the reference's x86 backend
 // (`--backend cpu`, crates/det/src/x86/gemm.rs:1-372) restated for the timed CPU baseline: weights are expanded once at
 // load to one signed byte per code (gemm.rs:59-134 repacks into unsigned-code strips; the arithmetic is the same), a
 // 128-group's dot product runs on 256-bit integer SIMD — `vpdpbusd` on unsigned codes u = wq + OFF with the OFF * sum(xq)

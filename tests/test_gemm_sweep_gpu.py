@@ -1,4 +1,4 @@
-"""Single-linear integer GEMM at the benchmark shapes (BASELINE configs[1]: K=5120 x N=17408 and the transposed FFN
+"""Single-linear integer GEMM at the benchmark shapes (the GEMM-sweep configuration: K=5120 x N=17408 and the transposed FFN
 shape), through det_gemm_ex on both weight layouts, bit for bit against the oracle's gemm_row."""
 import ctypes as C
 

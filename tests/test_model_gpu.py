@@ -1,4 +1,4 @@
-"""End-to-end parity on the tiny seeded model (BASELINE configs[0]): every logit of a 64-token prompt and 64 greedy
+"""End-to-end parity on the tiny seeded model (the benchmark's tiny configuration): every logit of a 64-token prompt and 64 greedy
 tokens, CUDA backend vs the CPU oracle running the same driver; plus invariance to the prefill chunking."""
 import ctypes as C
 
@@ -101,7 +101,7 @@ def test_long_context_decode_equals_chunked_prefill(libs, cuda_backend):
 
 
 def test_4b_chunking_1_64_512(libs, cuda_backend):
-    """BASELINE configs[2] shape (4B: 32 layers, hidden 2560, vocabulary 248320): a 512-token prompt prefilled in
+    """The 4B configuration (32 layers, hidden 2560, vocabulary 248320): a 512-token prompt prefilled in
     chunks of 512 (tensor-core GEMM), 64 and 1 (streaming GEMV), then 32 greedy tokens; last-position logits and all
     tokens must be the same bits for the three chunkings."""
     h = libs.host()

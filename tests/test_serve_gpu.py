@@ -1,4 +1,4 @@
-"""Batched serving decode on the CUDA backend (BASELINE configs[4] in miniature): sequences of different lengths advance
+"""Batched serving decode on the CUDA backend (the 32-sequence serving configuration in miniature): sequences of different lengths advance
 together, once through det_attention_rows / det_gdn_rows (one launch sequence over all rows) and once composed from the
 single-sequence calls; every stream must equal the stream that sequence produces alone, which test_model_gpu ties to the
 oracle."""
