@@ -365,6 +365,9 @@ static CUtensorMap make_map(const void* base, int rows, int K, int box_rows) {
     return map;
 }
 
+// Split K for narrow linears at a small batch (switched through det_debug_set_tc_variant: 0x100 on, 0x200 off).
+static bool g_tc_splitk = false;
+
 template <int TOK, int EC>
 static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
                                const OutSpec& out, cudaStream_t q) {
@@ -395,7 +398,7 @@ static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const flo
     a.counters = nullptr;
     const int tiles = (int)(grid.x * grid.y);
     int ksplit = 1;
-    if (tiles * 2 <= sm_count() && G >= 16) ksplit = std::min(4, std::min(sm_count() / tiles, G / 8));
+    if (g_tc_splitk && tiles * 2 <= sm_count() && G >= 16) ksplit = std::min(4, std::min(sm_count() / tiles, G / 8));
     if (ksplit > 1) {
         // scratch: int64 cells for at most sm_count()/2 tiles of 128 x 128, plus their counters; allocated at first
         // use (never inside a stream capture: the captured decode step has M = 1 and does not come here)
@@ -445,7 +448,10 @@ extern "C" {
 
 // Measurement switch: 0 = tile chosen by shape; 1..5 pin (tokens, columns per epilogue warp) = (64,32) (64,16) (32,8)
 // (32,16) (128,32).  Results do not depend on it.
-void det_debug_set_tc_variant(int v) { g_tc_variant = v; }
+void det_debug_set_tc_variant(int v) {
+    g_tc_variant = v & 0xff;
+    if (v & 0x300) g_tc_splitk = (v & 0x100) != 0;   // 0x100: split K on, 0x200: off
+}
 
 size_t det_linear_expand_bytes(int N, int K) { return (size_t)((N + TC_ROWS - 1) / TC_ROWS) * TC_ROWS * (size_t)K; }
 
