@@ -456,6 +456,8 @@ def run_serving(args, local_rank: int):
         raise RuntimeError(h.dh_last_error().decode())
     if args.compose_rows:
         h.dh_cuda_set_fuse_rows(bk, 0)
+    if args.tc_splitk:
+        d.det_debug_set_tc_variant(0x100)
     model = h.dh_model_new_synth(bk, cfg.encode(), args.layers, SEED, 16, max(args.chunk, B))
     if not model:
         raise RuntimeError(h.dh_last_error().decode())
@@ -532,6 +534,8 @@ def main():
     ap.add_argument("--ctx-min", type=int, default=512)
     ap.add_argument("--ctx-max", type=int, default=8192)
     ap.add_argument("--new", type=int, default=256)
+    ap.add_argument("--tc-splitk", action="store_true",
+                    help="measurement switch: the tensor-core GEMM splits K for linears with few row tiles (same values)")
     ap.add_argument("--compose-rows", action="store_true",
                     help="serving: per-sequence attention / GDN calls instead of the batched kernels (same tokens)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")

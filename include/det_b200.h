@@ -262,7 +262,8 @@ int det_sample_topkp_static(const float* logits, int M, int V, float inv_temp, i
  * Results are identical either way; only the overlap of one kernel's prologue with its predecessor's tail changes.  */
 void det_debug_set_pdl(int on);
 /* Measurement switch: pins the tensor-core GEMM's tile, 1..5 = (tokens, columns per epilogue warp) (64,32) (64,16)
- * (32,8) (32,16) (128,32); 0 = chosen by shape (default).  Results do not depend on it.                               */
+ * (32,8) (32,16) (128,32); 0 = chosen by shape (default).  Adding 0x100 / 0x200 switches the split of K over several
+ * CTAs for linears with few row tiles on / off.  Results do not depend on any of it.                                   */
 void det_debug_set_tc_variant(int v);
 
 /* Last error recorded by a bounded device-side wait (0 = none; see the DETB_ERR_* codes in csrc/cuda/runtime.cuh).

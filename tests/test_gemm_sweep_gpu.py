@@ -27,7 +27,7 @@ def _det_rows(rng, n, k, bits):
     (17408, 5120, 6, [1, 4, 8, 16, 70]),
     (17408, 5120, 8, [1, 3]),
     (17408, 5120, 4, [1, 5]),
-    (5120, 17408, 6, [1, 2]),
+    (5120, 17408, 6, [1, 2, 40]),
     (5120, 6144, 6, [1]),
 ])
 def test_gemm_matches_oracle(n, k, bits, ms, libs, oracle):
@@ -62,12 +62,14 @@ def test_gemm_matches_oracle(n, k, bits, ms, libs, oracle):
             cases = [("stream", stream, 0), ("rowmajor", src, 0)]
             # every tile instantiation of the tensor-core kernel (0 = the one the shape selects)
             cases += [(f"int8 tensor-core, tile variant {v}", tensor, v) for v in (0, 1, 2, 3, 4, 5)]
+            # K split over several CTAs per tile (takes effect on the shapes with few row tiles)
+            cases += [(f"int8 tensor-core, split K, tile variant {v}", tensor, v | 0x100) for v in (0, 1, 4)]
             for name, lin, variant in cases:
                 got = np.zeros_like(want)
                 d.det_memset(dy, 0xFF, want.nbytes, None)
                 d.det_debug_set_tc_variant(variant)
                 d.det_gemm(C.byref(lin), dx, ds, dm, mtok, dy, None)
-                d.det_debug_set_tc_variant(0)
+                d.det_debug_set_tc_variant(0x200)
                 d.det_memcpy(got.ctypes.data, dy, got.nbytes, None)
                 d.det_sync()
                 bad = int((got.view(np.uint32) != want.view(np.uint32)).sum())
