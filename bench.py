@@ -208,6 +208,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         raise RuntimeError(h.dh_last_error().decode())
     if args.fuse_kinds:
         h.dh_cuda_debug(bk, 0, args.fuse_kinds)
+    if args.attn_flags >= 0:
+        d.det_debug_set_attn(args.attn_flags)
+    if args.tc_splitk:
+        d.det_debug_set_tc_variant(0x100)
     # N > 1: tensor parallel over NVLink.  torch.distributed (gloo, CPU) only carries the NCCL id, the barriers and the
     # max-over-ranks of the timings; the data path uses the library's own NCCL communicator on its queue.
     dist, comm = None, None
@@ -534,6 +538,8 @@ def main():
     ap.add_argument("--ctx-min", type=int, default=512)
     ap.add_argument("--ctx-max", type=int, default=8192)
     ap.add_argument("--new", type=int, default=256)
+    ap.add_argument("--attn-flags", type=int, default=-1,
+                    help="measurement switch for the attention kernels (det_debug_set_attn): 1 token-tiled prefill, +2 two stages")
     ap.add_argument("--tc-splitk", action="store_true",
                     help="measurement switch: the tensor-core GEMM splits K for linears with few row tiles (same values)")
     ap.add_argument("--compose-rows", action="store_true",

@@ -52,3 +52,34 @@ def test_batched_streams_equal_solo_streams_on_the_reference_backend(libs, ref_b
     together, solo = run_streams(libs.host(), ref_backend, n_new=6)
     for i, (a, b) in enumerate(zip(together, solo)):
         assert np.array_equal(a, b), (i, a, b)
+
+
+def test_mixed_sampling_parameters_per_sequence(libs, ref_backend):
+    """Sequences with different sampling settings (greedy, plain temperature, top-k / top-p) in one batch: the step then
+    samples row by row; each stream must still equal its solo stream."""
+    h = libs.host()
+    settings = [(1, 1.0, 0, 1.0), (0, 1.0 / 0.9, 0, 1.0), (0, 1.0 / 0.7, 40, 0.95), (0, 2.0, 5, 1.0)]
+    n_new, ctx = 5, 64
+    model = h.dh_model_new_synth(ref_backend, b"tiny", 4, SEED, ctx, 16)
+    assert model, h.dh_last_error()
+    solo = []
+    for i, (n, (greedy, inv_temp, top_k, top_p)) in enumerate(zip(PROMPTS, settings)):
+        ids = _prompt(h, 200 + i, n)
+        out = np.zeros(n_new, np.int32)
+        cnt = C.c_size_t(0)
+        assert h.dh_model_reset(model) == 0
+        assert h.dh_model_generate(model, ids.ctypes.data, n, n_new, greedy, inv_temp, top_k, top_p, 9000 + i,
+                                   out.ctypes.data, C.byref(cnt)) == 0, h.dh_last_error()
+        solo.append(out[: cnt.value].copy())
+    batch = h.dh_batch_new(model, len(PROMPTS), ctx)
+    assert batch, h.dh_last_error()
+    for i, (n, (greedy, inv_temp, top_k, top_p)) in enumerate(zip(PROMPTS, settings)):
+        ids = _prompt(h, 200 + i, n)
+        assert h.dh_batch_prefill(batch, i, ids.ctypes.data, n, greedy, inv_temp, top_k, top_p, 9000 + i) == 0, h.dh_last_error()
+    assert h.dh_batch_step(batch, n_new - 1) == 0, h.dh_last_error()
+    for i in range(len(PROMPTS)):
+        out = np.zeros(n_new, np.int32)
+        assert h.dh_batch_tokens(batch, i, out.ctypes.data, n_new) == n_new
+        assert np.array_equal(out, solo[i]), (i, out, solo[i])
+    h.dh_batch_free(batch)
+    h.dh_model_free(model)
