@@ -121,6 +121,8 @@ CUDA_ABI = {
     "det_xchg_quant": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "det_debug_set_pdl": (None, [c_int]),
     "det_debug_set_tc_variant": (None, [c_int]),
+    "det_debug_set_attn": (None, [c_int]),
+    "det_debug_umma_peak": (C.c_double, [c_int]),
     "det_last_error": (c_int, []),
 }
 

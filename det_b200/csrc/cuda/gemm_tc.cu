@@ -304,6 +304,46 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                      : "memory");
 }
 
+// ---- tensor-pipe ceiling: tcgen05.mma kind::i8 issued back to back on resident shared-memory tiles (128 x 256 x 32 per
+// instruction, one CTA per SM, no loads, no epilogue).  The measured rate is the denominator for "tensor-pipe
+// utilisation" of the GEMM above.  Operand contents are irrelevant (zeros).
+__global__ void __launch_bounds__(64, 1) k_umma_peak(int iters, int* error_flag) {
+    extern __shared__ __align__(1024) uint8_t peak_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(peak_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* ta = smem;                    // 128 rows x 128 bytes
+    uint8_t* tb = smem + 16384;            // 256 rows x 128 bytes
+    unsigned long long* bar = reinterpret_cast<unsigned long long*>(smem + 16384 + 32768);
+    unsigned* slot = reinterpret_cast<unsigned*>(bar + 1);
+    for (int i = threadIdx.x; i < (16384 + 32768) / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem = *slot;
+    if (warp == 1 && lane == 0) {
+        constexpr unsigned IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+        const unsigned long long da = umma_desc(ta), db = umma_desc(tb);
+        for (int i = 0; i < iters; i++) {
+#pragma unroll
+            for (int k = 0; k < 4; k++) umma_i8(tmem, da + 2 * k, db + 2 * k, IDESC, (i | k) ? 1u : 0u);
+        }
+        umma_commit(bar);
+        if (!mbar_wait(bar, 0)) atomicExch(error_flag, DETB_ERR_WAIT_EXPIRED);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+}
+
 // One thread per 32-code block: reference layout -> signed int8 codes in tile-major order
 // [N / 128 row tiles][K / 128 groups][128 rows][128 codes], so that the (row tile, group) box one TMA load fetches is 16 KB
 // of consecutive memory (whole DRAM pages, whole L2 lines) and a CTA's K loop streams forward.  The last row tile is
@@ -366,7 +406,7 @@ static CUtensorMap make_map(const void* base, int rows, int K, int box_rows) {
 }
 
 // Split K for narrow linears at a small batch (switched through det_debug_set_tc_variant: 0x100 on, 0x200 off).
-static bool g_tc_splitk = false;
+static bool g_tc_splitk = true;
 
 template <int TOK, int EC>
 static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
@@ -451,6 +491,29 @@ extern "C" {
 void det_debug_set_tc_variant(int v) {
     g_tc_variant = v & 0xff;
     if (v & 0x300) g_tc_splitk = (v & 0x100) != 0;   // 0x100: split K on, 0x200: off
+}
+
+// Runs the tensor-pipe ceiling kernel (one CTA per SM, `iters` x 4 MMAs of 128 x 256 x 32 each) and returns its int8
+// rate in TOPS (2 * M * N * K per MMA), timed with events on the library queue; < 0 when a wait expired.
+double det_debug_umma_peak(int iters) {
+    cudaStream_t q = queue_of(nullptr);
+    const size_t smem = 1024 + 16384 + 32768 + 64;
+    DETB_CUDA_OK(cudaFuncSetAttribute(k_umma_peak, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaEvent_t e0, e1;
+    DETB_CUDA_OK(cudaEventCreate(&e0));
+    DETB_CUDA_OK(cudaEventCreate(&e1));
+    k_umma_peak<<<sm_count(), 64, smem, q>>>(iters > 64 ? 64 : iters, error_word());     // warm-up
+    DETB_CUDA_OK(cudaEventRecord(e0, q));
+    k_umma_peak<<<sm_count(), 64, smem, q>>>(iters, error_word());
+    DETB_CUDA_OK(cudaEventRecord(e1, q));
+    DETB_CUDA_OK(cudaEventSynchronize(e1));
+    DETB_CUDA_OK(cudaGetLastError());
+    float ms = 0.0f;
+    DETB_CUDA_OK(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    const double ops = 2.0 * 128 * 256 * 32 * 4.0 * (double)iters * sm_count();
+    return ops / (ms * 1e-3) / 1e12;
 }
 
 size_t det_linear_expand_bytes(int N, int K) { return (size_t)((N + TC_ROWS - 1) / TC_ROWS) * TC_ROWS * (size_t)K; }

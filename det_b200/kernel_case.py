@@ -3,6 +3,7 @@ kernels that a profiler capture needs (a few hundred MB on the device, a handful
 
     python -m det_b200.kernel_case gemv    [N K bits M]    # k_gemv_stream, default 17408 5120 6 1
     python -m det_b200.kernel_case gemm_tc [N K bits M [variant]]   # k_gemm_tc, default 17408 5120 6 512, tile by shape
+    python -m det_b200.kernel_case umma_peak                        # int8 tcgen05.mma issue rate with resident operands
 
 gemv: six copies of the weights (seeded, generated on the device, repacked into the streaming layout) are cycled through
 so that no launch finds its weights in the 126 MB L2; 6 warm-up launches, then 12 timed ones.
@@ -66,6 +67,13 @@ def _activations(d, m, k, n):
 
 def main(argv):
     kind = argv[0] if argv else "gemv"
+    if kind == "umma_peak":
+        d = capi.cuda()
+        assert d.det_init() == 0
+        for iters in (2048, 8192):
+            print(f"tcgen05.mma kind::i8 128x256x32, {iters} x 4 per SM: {d.det_debug_umma_peak(iters):.0f} TOPS; "
+                  f"device error word {d.det_last_error()}")
+        return
     if kind not in ("gemv", "gemm_tc"):
         raise SystemExit(__doc__)
     n, k, bits, m = (17408, 5120, 6, 1 if kind == "gemv" else 512)

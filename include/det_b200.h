@@ -261,10 +261,16 @@ int det_sample_topkp_static(const float* logits, int M, int V, float inv_temp, i
 /* Measurement switch: programmatic dependent launch between the library's kernels on (default, non-zero) or off.
  * Results are identical either way; only the overlap of one kernel's prologue with its predecessor's tail changes.  */
 void det_debug_set_pdl(int on);
+/* Measurement switches for the attention kernels: bit 0 = token-tiled prefill kernels (default on), bit 1 = two
+ * shared-memory stages in the tiled accumulate kernel (default off).  Same results.                                   */
+void det_debug_set_attn(int flags);
 /* Measurement switch: pins the tensor-core GEMM's tile, 1..5 = (tokens, columns per epilogue warp) (64,32) (64,16)
  * (32,8) (32,16) (128,32); 0 = chosen by shape (default).  Adding 0x100 / 0x200 switches the split of K over several
  * CTAs for linears with few row tiles on / off.  Results do not depend on any of it.                                   */
 void det_debug_set_tc_variant(int v);
+/* Tensor-pipe ceiling: tcgen05.mma kind::i8 (128 x 256 x 32) issued back to back from resident shared-memory tiles on
+ * every SM, no loads and no epilogue; returns the measured int8 rate in TOPS.                                         */
+double det_debug_umma_peak(int iters);
 
 /* Last error recorded by a bounded device-side wait (0 = none; see the DETB_ERR_* codes in csrc/cuda/runtime.cuh).
  * Waits for pending work.                                                                                            */
