@@ -287,8 +287,10 @@ template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
     static_assert(HD <= ATT_THREADS, "one thread per value dimension");
     extern __shared__ __align__(16) uint8_t asm_[];
+    int8_t* ktile = reinterpret_cast<int8_t*>(asm_);
+    int16_t* vtile = reinterpret_cast<int16_t*>(asm_ + AccSmem<HD>::KTILE);
     __shared__ __align__(16) int8_t qs[MAX_REP * HD];
-    __shared__ float sks[2][KT];
+    __shared__ float sks[KT];
     __shared__ float sqs[MAX_REP];
     __shared__ float mxs[MAX_REP];
     __shared__ int pq[MAX_REP][KT];
@@ -300,14 +302,6 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
     int k0, k1;
     key_range(a, cache.pos, k0, k1);
     if (k0 >= k1) return;
-    auto ktile_of = [&](int st) { return reinterpret_cast<int8_t*>(asm_ + st * AccSmem<HD>::STAGE); };
-    auto vtile_of = [&](int st) { return reinterpret_cast<int16_t*>(asm_ + st * AccSmem<HD>::STAGE + AccSmem<HD>::KTILE); };
-    auto fetch = [&](int key0, int st) {               // one commit group per tile (fetch_v_async commits)
-        const int nk = min(KT, k1 - key0);
-        fetch_k_async<HD>(ktile_of(st), sks[st], a, cache, kvh, key0, nk);
-        fetch_v_async<HD>(vtile_of(st), a, cache, kvh, key0, nk);
-    };
-    fetch(k0, 0);
     const int rep = a.rep;
     for (int i = threadIdx.x; i < rep * HD / 16; i += ATT_THREADS)
         reinterpret_cast<uint4*>(qs)[i] =
@@ -323,16 +317,12 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
     long long num[MAX_REP];
 #pragma unroll
     for (int r = 0; r < MAX_REP; r++) num[r] = 0;
-    int st = 0;
-    for (int key0 = k0; key0 < k1; key0 += KT, st ^= 1) {
+    for (int key0 = k0; key0 < k1; key0 += KT) {
         const int nkeys = min(KT, k1 - key0);
-        const bool more = key0 + KT < k1;
-        if (more) fetch(key0 + KT, st ^ 1);                // the other stage was released at the end of the last turn
-        if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");
-        else asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();                                   // this tile has landed (and qs / sqs / mxs on the first turn)
-        const int8_t* ktile = ktile_of(st);
-        const int16_t* vtile = vtile_of(st);
+        __syncthreads();                                   // the previous tile's K, V and pq are no longer read
+        fetch_v_async<HD>(vtile, a, cache, kvh, key0, nkeys);   // in flight while the scores are computed
+        KTile<HD>::load(ktile, sks, a, cache, kvh, key0, nkeys);
+        __syncthreads();
 #pragma unroll
         for (int i = 0; i < MAX_REP / 4 + 1; i++) {
             const int r = part + 4 * i;
@@ -340,12 +330,13 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
                 int p = 0;
                 if (j < nkeys) {
                     const int dt = KTile<HD>::dot(ktile, j, qs + r * HD);
-                    const float s = fmul(fmul((float)dt, sqs[r]), sks[st][j]);
+                    const float s = fmul(fmul((float)dt, sqs[r]), sks[j]);
                     p = f2i_sat(fmul(exp_f(fsub(s, mxs[r])), 16777216.0f));
                 }
                 pq[r][j] = p;
             }
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         if (threadIdx.x < rep) {
             long long s = 0;
@@ -360,8 +351,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
                     if (r < rep) num[r] += (long long)pq[r][q] * (long long)vv;
             }
         }
-        __syncthreads();                                   // stage st and pq are free again
     }
+    __syncthreads();
     if (a.nsplit == 1) {
         if (d < HD) {
             const float vs = a.v_scale[kvh];
@@ -812,7 +803,9 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_dec(const AttnArgs a) {
     }
 }
 
-static bool g_attn_token_tiles = true;   // measurement switches (det_debug_set_attn)
+// Token tiling measured no faster on B200 (27B, 2048- and 8192-token prompts: the accumulate kernel is bound by its
+// integer multiply-adds, not by K/V traffic), so it is off unless switched on.
+static bool g_attn_token_tiles = false;   // measurement switches (det_debug_set_attn)
 static int g_attn_tt_stages = 1;
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -883,7 +876,7 @@ static void run_attention(AttnArgs a, void* scratch, int max_total_keys, cudaStr
     const dim3 grid(nsplit, a.n_kv, a.M);
     static bool acc_attr = false;
     if (!acc_attr) {
-        DETB_CUDA_OK(cudaFuncSetAttribute(k_attn_acc<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, AccSmem<HD>::TOTAL));
+        DETB_CUDA_OK(cudaFuncSetAttribute(k_attn_acc<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, AccSmem<HD>::STAGE));
         acc_attr = true;
     }
     if (!a.rows && a.M >= TT && g_attn_token_tiles) {
@@ -900,7 +893,7 @@ static void run_attention(AttnArgs a, void* scratch, int max_total_keys, cudaStr
         else launch_pdl(k_attn_acc_tt<HD, 1>, tgrid, dim3(ATT_THREADS), AccSmem<HD>::STAGE, q, 1, a);
     } else {
         launch_pdl(k_attn_max<HD>, grid, dim3(ATT_THREADS), 0, q, 1, a);
-        launch_pdl(k_attn_acc<HD>, grid, dim3(ATT_THREADS), AccSmem<HD>::TOTAL, q, 1, a);
+        launch_pdl(k_attn_acc<HD>, grid, dim3(ATT_THREADS), AccSmem<HD>::STAGE, q, 1, a);
     }
     if (nsplit > 1) launch_pdl(k_attn_fin<HD>, dim3(a.M * a.n_h), dim3(HD), 0, q, 1, a);
 }
@@ -953,7 +946,7 @@ void det_attention_dev(const det_attn_layer* L, const det_kv_cache* kv, const fl
 }
 
 
-// Measurement switches: bit 0 = token-tiled prefill kernels (default on), bit 1 = two shared-memory stages in the tiled
+// Measurement switches: bit 0 = token-tiled prefill kernels (default off), bit 1 = two shared-memory stages in the tiled
 // accumulate kernel (default off).  Results do not depend on them.
 void det_debug_set_attn(int flags) {
     g_attn_token_tiles = (flags & 1) != 0;

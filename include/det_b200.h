@@ -261,7 +261,7 @@ int det_sample_topkp_static(const float* logits, int M, int V, float inv_temp, i
 /* Measurement switch: programmatic dependent launch between the library's kernels on (default, non-zero) or off.
  * Results are identical either way; only the overlap of one kernel's prologue with its predecessor's tail changes.  */
 void det_debug_set_pdl(int on);
-/* Measurement switches for the attention kernels: bit 0 = token-tiled prefill kernels (default on), bit 1 = two
+/* Measurement switches for the attention kernels: bit 0 = token-tiled prefill kernels (default off), bit 1 = two
  * shared-memory stages in the tiled accumulate kernel (default off).  Same results.                                   */
 void det_debug_set_attn(int flags);
 /* Measurement switch: pins the tensor-core GEMM's tile, 1..5 = (tokens, columns per epilogue warp) (64,32) (64,16)
