@@ -186,6 +186,40 @@ struct KTile {
     }
 };
 
+// P.V of one tile for value dimension d: num[r] += sum_q pq[r][q] * v[q][d], exact in int64.  Four keys per turn (one
+// 128-bit load of four p values per head, REP a compile-time count so nothing is predicated); rows of pq past the tile's
+// keys hold p = 0, so the turn may run over the end of a short tile.
+template <int HD, int REP>
+__device__ __forceinline__ void pv_tile_n(const int (*pq)[KT], const int16_t* vtile, int nkeys, int d, long long (&num)[MAX_REP]) {
+    const int n4 = (nkeys + 3) & ~3;
+    for (int q = 0; q < n4; q += 4) {
+        const long long v0 = vtile[(q + 0) * HD + d], v1 = vtile[(q + 1) * HD + d];
+        const long long v2 = vtile[(q + 2) * HD + d], v3 = vtile[(q + 3) * HD + d];
+#pragma unroll
+        for (int r = 0; r < REP; r++) {
+            const int4 p = *reinterpret_cast<const int4*>(&pq[r][q]);
+            num[r] += (long long)p.x * v0;
+            num[r] += (long long)p.y * v1;
+            num[r] += (long long)p.z * v2;
+            num[r] += (long long)p.w * v3;
+        }
+    }
+}
+template <int HD>
+__device__ __forceinline__ void pv_tile(const int (*pq)[KT], const int16_t* vtile, int nkeys, int d, int rep,
+                                        long long (&num)[MAX_REP]) {
+    switch (rep) {
+        case 1: pv_tile_n<HD, 1>(pq, vtile, nkeys, d, num); break;
+        case 2: pv_tile_n<HD, 2>(pq, vtile, nkeys, d, num); break;
+        case 3: pv_tile_n<HD, 3>(pq, vtile, nkeys, d, num); break;
+        case 4: pv_tile_n<HD, 4>(pq, vtile, nkeys, d, num); break;
+        case 5: pv_tile_n<HD, 5>(pq, vtile, nkeys, d, num); break;
+        case 6: pv_tile_n<HD, 6>(pq, vtile, nkeys, d, num); break;
+        case 7: pv_tile_n<HD, 7>(pq, vtile, nkeys, d, num); break;
+        default: pv_tile_n<HD, 8>(pq, vtile, nkeys, d, num); break;
+    }
+}
+
 // key range of this CTA for a token at position pos: [k0, k1) within [0, pos]
 __device__ __forceinline__ void key_range(const AttnArgs& a, int pos, int& k0, int& k1) {
     const int total = pos + 1;
@@ -293,7 +327,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
     __shared__ float sks[KT];
     __shared__ float sqs[MAX_REP];
     __shared__ float mxs[MAX_REP];
-    __shared__ int pq[MAX_REP][KT];
+    __shared__ __align__(16) int pq[MAX_REP][KT];
     __shared__ long long den_sh[MAX_REP];
     pdl_trigger();
     pdl_wait();
@@ -343,14 +377,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
             for (int q = 0; q < nkeys; q++) s += pq[threadIdx.x][q];
             den_sh[threadIdx.x] += s;
         }
-        if (d < HD) {
-            for (int q = 0; q < nkeys; q++) {
-                const int vv = vtile[q * HD + d];
-#pragma unroll
-                for (int r = 0; r < MAX_REP; r++)
-                    if (r < rep) num[r] += (long long)pq[r][q] * (long long)vv;
-            }
-        }
+        if (d < HD) pv_tile<HD>(pq, vtile, nkeys, d, rep, num);
     }
     __syncthreads();
     if (a.nsplit == 1) {
@@ -465,7 +492,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc_tt(const AttnArgs a) {
     __shared__ float sks[2][KT];
     __shared__ float sqs[TT][MAX_REP];
     __shared__ float mxs[TT][MAX_REP];
-    __shared__ int pq[TT][MAX_REP][KT];
+    __shared__ __align__(16) int pq[TT][MAX_REP][KT];
     __shared__ long long den_sh[TT][MAX_REP];
     pdl_trigger();
     pdl_wait();
@@ -543,14 +570,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc_tt(const AttnArgs a) {
             }
         }
         if (d < HD) {
-            for (int q = 0; q < nkeys; q++) {
-                const int vv = vtile[q * HD + d];
 #pragma unroll
-                for (int tt = 0; tt < TT; tt++)
-#pragma unroll
-                    for (int r = 0; r < MAX_REP; r++)
-                        if (r < rep) num[tt][r] += (long long)pq[tt][r][q] * (long long)vv;
-            }
+            for (int tt = 0; tt < TT; tt++) pv_tile<HD>(pq[tt], vtile, nkeys, d, rep, num[tt]);
         }
         __syncthreads();
     }
@@ -749,14 +770,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_dec(const AttnArgs a) {
             for (int q = 0; q < nkeys; q++) sum += pq[threadIdx.x][q];
             den_sh[threadIdx.x] += sum;
         }
-        if (d < HD) {
-            for (int q = 0; q < nkeys; q++) {
-                const int vv = vtile[q * HD + d];
-#pragma unroll
-                for (int r = 0; r < MAX_REP; r++)
-                    if (r < rep) num[r] += (long long)pq[r][q] * (long long)vv;
-            }
-        }
+        if (d < HD) pv_tile<HD>(pq, vtile, nkeys, d, rep, num);
     }
     __syncthreads();
     (void)vstride;

@@ -158,7 +158,14 @@ constexpr int RC = 16;    // columns per CTA
 constexpr int RL = 8;     // lanes per column
 constexpr int RR = DK / RL;   // rows per lane (16)
 
-constexpr int SLAB_STRIDE = RC + 4;   // floats per slab row: rows stay 16-byte aligned for the asynchronous copies
+// The CTA's 128 x 16 slab of the state in shared memory.  A thread (p = row block, jj = column) reads rows p * 16 + i of
+// column jj, so the 32 lanes of a warp touch 8 row blocks x 4 columns at once: element (r, c) lives at
+// r * SLAB_STRIDE + c + 4 * (r / 16), which puts those 32 words into 32 different banks (a plain padded row-major slab
+// is an 8-way conflict), and keeps every 4-column piece 16-byte aligned for the asynchronous copies.
+constexpr int SLAB_STRIDE = 44;
+constexpr int SLAB_FLOATS = DK * SLAB_STRIDE;
+__device__ __forceinline__ int slab_at(int r, int c) { return r * SLAB_STRIDE + c + 4 * (r >> 4); }
+constexpr int RUN_STRIDE = RR + 4;      // a lane's 16-row run, padded: the 8 runs of a token fall into distinct banks
 
 // One token of the recurrence for the thread's 16 rows of one state column (spec/layers.rs:104-131): decay, the
 // k-contraction (spec tree: the lane's aligned run, then xor 1, 2, 4 over the column's 8 lanes), the delta update, the
@@ -181,18 +188,18 @@ __device__ __forceinline__ float recur_step(float (&s)[RR], const float* k, cons
 }
 
 // the CTA's 128 x 16 slab of the state <-> shared memory, 16-byte pieces (4 per thread)
-__device__ __forceinline__ void slab_load_async(float (*slab)[SLAB_STRIDE], const float* Sh, int j0) {
+__device__ __forceinline__ void slab_load_async(float* slab, const float* Sh, int j0) {
     for (int i = threadIdx.x; i < DK * (RC / 4); i += RC * RL) {
         const int row = i / (RC / 4), v = i % (RC / 4);
-        const unsigned dst = (unsigned)__cvta_generic_to_shared(&slab[row][v * 4]);
+        const unsigned dst = (unsigned)__cvta_generic_to_shared(slab + slab_at(row, v * 4));
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(Sh + (size_t)row * DV + j0 + v * 4) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
-__device__ __forceinline__ void slab_store(float (*slab)[SLAB_STRIDE], float* Sh, int j0) {
+__device__ __forceinline__ void slab_store(const float* slab, float* Sh, int j0) {
     for (int i = threadIdx.x; i < DK * (RC / 4); i += RC * RL) {
         const int row = i / (RC / 4), v = i % (RC / 4);
-        *reinterpret_cast<float4*>(Sh + (size_t)row * DV + j0 + v * 4) = *reinterpret_cast<const float4*>(&slab[row][v * 4]);
+        *reinterpret_cast<float4*>(Sh + (size_t)row * DV + j0 + v * 4) = *reinterpret_cast<const float4*>(slab + slab_at(row, v * 4));
     }
 }
 
@@ -201,8 +208,8 @@ __device__ __forceinline__ void slab_store(float (*slab)[SLAB_STRIDE], float* Sh
 // k head (conv, silu, l2norm with the same per-lane runs and xor order), its 16 v channels, beta and decay — so a
 // decode step needs no separate prep launch.
 __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
-    __shared__ __align__(16) float slab[DK][SLAB_STRIDE];
-    __shared__ __align__(16) float pq[DK], pk[DK];
+    __shared__ __align__(16) float slab[SLAB_FLOATS];
+    __shared__ __align__(16) float pq[RL][RUN_STRIDE], pk[RL][RUN_STRIDE];   // runs of 16 rows, padded against conflicts
     __shared__ float pv[RC], pbd[2];
     __shared__ long long ab_part[2][4];
     pdl_trigger();
@@ -236,12 +243,12 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
             }
             const float ss = fold_lanes<32>(fold_run<4>(sq));
             const float inv = fdiv(1.0f, fsqrt(fadd(ss, g.eps)));
-            float* dst = wib == 0 ? pq : pk;
+            float (*dst)[RUN_STRIDE] = wib == 0 ? pq : pk;
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 v[e] = fmul(v[e], inv);
                 if (wib == 0) v[e] = fmul(v[e], __uint_as_float(QSCALE_BITS));
-                dst[lane * 4 + e] = v[e];
+                dst[(lane * 4 + e) / RR][(lane * 4 + e) % RR] = v[e];
             }
         } else if (wib == 2) {
             if (lane < RC) pv[lane] = conv_silu(g, t, 2 * g.n_k * DK + h * DV + j0 + lane);
@@ -274,15 +281,15 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
     float s[RR], k[RR], q[RR];
 #pragma unroll
     for (int i = 0; i < RR; i++) {
-        s[i] = slab[p * RR + i][jj];
-        k[i] = pk[p * RR + i];
-        q[i] = pq[p * RR + i];
+        s[i] = slab[slab_at(p * RR + i, jj)];
+        k[i] = pk[p][i];
+        q[i] = pq[p][i];
     }
     const float ov = recur_step(s, k, q, pv[jj], pbd[0], pbd[1]);
     if (p == 0) g.o[((size_t)t * g.n_v + h) * DV + j0 + jj] = ov;
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < RR; i++) slab[p * RR + i][jj] = s[i];
+    for (int i = 0; i < RR; i++) slab[slab_at(p * RR + i, jj)] = s[i];
     __syncthreads();
     slab_store(slab, Sh, j0);
 }
@@ -292,7 +299,6 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
 // 16 v values, beta, decay) are staged through shared memory in blocks of TB tokens, the next block in flight
 // (cp.async) while the current one is consumed, so no step waits for global memory.
 constexpr int TB = 8;
-constexpr int RUN_STRIDE = RR + 4;      // a lane's 16-row run, padded: the 8 runs of a token fall into distinct banks
 struct TokOps {
     float k[RL][RUN_STRIDE];
     float q[RL][RUN_STRIDE];
@@ -302,7 +308,7 @@ struct TokOps {
 static_assert(sizeof(TokOps) % 16 == 0, "token operands stay 16-byte aligned");
 
 __global__ void __launch_bounds__(RC * RL) k_gdn_recur_seq(const GdnArgs g) {
-    __shared__ __align__(16) float slab[DK][SLAB_STRIDE];
+    __shared__ __align__(16) float slab[SLAB_FLOATS];
     __shared__ __align__(16) TokOps ops[2][TB];
     pdl_trigger();
     pdl_wait();
@@ -341,7 +347,7 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_seq(const GdnArgs g) {
     __syncthreads();
     float s[RR];
 #pragma unroll
-    for (int i = 0; i < RR; i++) s[i] = slab[p * RR + i][jj];
+    for (int i = 0; i < RR; i++) s[i] = slab[slab_at(p * RR + i, jj)];
     int buf = 0;
     for (int t0 = 0; t0 < g.M; t0 += TB, buf ^= 1) {
         if (t0 + TB < g.M) stage(t0 + TB, buf ^ 1);        // next block in flight
@@ -364,7 +370,7 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_seq(const GdnArgs g) {
         __syncthreads();                                   // the next block has landed; this one may be overwritten
     }
 #pragma unroll
-    for (int i = 0; i < RR; i++) slab[p * RR + i][jj] = s[i];
+    for (int i = 0; i < RR; i++) slab[slab_at(p * RR + i, jj)] = s[i];
     __syncthreads();
     slab_store(slab, Sh, j0);
 }
