@@ -122,6 +122,7 @@ CUDA_ABI = {
     "det_debug_set_pdl": (None, [c_int]),
     "det_debug_set_tc_variant": (None, [c_int]),
     "det_debug_set_attn": (None, [c_int]),
+    "det_debug_set_rows": (None, [c_int]),
     "det_debug_umma_peak": (C.c_double, [c_int]),
     "det_last_error": (c_int, []),
 }

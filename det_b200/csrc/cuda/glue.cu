@@ -193,6 +193,142 @@ __global__ void __launch_bounds__(1024) k_row(RowArgs p, int spc /* slices per C
     }
 }
 
+// The same row operations for MANY rows (prefill chunks): one CTA per row, each warp walks several 128-wide slices, no
+// cluster.  A single row finishes later than in the cluster kernel, but hundreds of rows are in flight at once and
+// nothing waits on a cluster barrier.  The arithmetic per slice, the tree over the slice sums and the maxima are the
+// same expressions as above, so the values are the same bits.
+constexpr int WIDE_MAXK = 8;     // slices per warp: rows up to 32 * 8 * 128 = 32768 values
+
+template <int MODE>
+__global__ void __launch_bounds__(1024) k_row_wide(RowArgs p, int pslices /* P / 128 */) {
+    __shared__ float all_sums[MAX_SLICES];
+    __shared__ float shf[32];
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const int n = p.n;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float* a = p.a + (size_t)row * n;
+    const float* b = (MODE == ROW_SWIGLU) ? p.b + (size_t)row * n : p.b;
+    const int slices = (n + 127) >> 7;
+
+    float raw[WIDE_MAXK][4];
+#pragma unroll
+    for (int k = 0; k < WIDE_MAXK; k++) {
+        const int g = warp + k * nw, base = g * 128 + lane * 4;
+#pragma unroll
+        for (int e = 0; e < 4; e++) raw[k][e] = 0.0f;
+        if (g < slices) {
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                if (base + e < n) raw[k][e] = a[base + e];
+            if (MODE != ROW_SWIGLU && p.acc) {
+                float* acc = p.acc + (size_t)row * n;
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (base + e < n) acc[base + e] = raw[k][e] = fadd(acc[base + e], raw[k][e]);
+            }
+        }
+    }
+    float inv_rms = 0.0f;
+    if (MODE == ROW_RMSNORM) {
+        for (int i = threadIdx.x; i < pslices; i += blockDim.x) all_sums[i] = 0.0f;   // zero padding of the tree
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < WIDE_MAXK; k++) {
+            const int g = warp + k * nw;
+            float sq[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) sq[e] = fmul(raw[k][e], raw[k][e]);
+            const float ssum = fold_lanes<32>(fold_run<4>(sq));
+            if (lane == 0 && g < slices) all_sums[g] = ssum;
+        }
+        __syncthreads();
+        float tot;
+        if (pslices >= 32) {
+            const int per = pslices >> 5;   // 1, 2, 4 or 8
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = i < per ? all_sums[lane * per + i] : 0.0f;
+#pragma unroll
+            for (int step = 1; step < 8; step <<= 1) {
+#pragma unroll
+                for (int i = 0; i < 8; i += 2 * step)
+                    if (step < per) v[i] = fadd(v[i], v[i + step]);
+            }
+            tot = fold_lanes<32>(v[0]);
+        } else {
+            float v = lane < pslices ? all_sums[lane] : 0.0f;
+            for (int off = 1; off < pslices; off <<= 1) v = fadd(v, __shfl_xor_sync(FULL, v, off));
+            tot = __shfl_sync(FULL, v, 0);
+        }
+        const float mean = fdiv(tot, (float)n);
+        inv_rms = fdiv(1.0f, fsqrt(fadd(mean, p.eps)));
+    }
+    float s_slice[WIDE_MAXK];
+    float smax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < WIDE_MAXK; k++) {
+        const int g = warp + k * nw, base = g * 128 + lane * 4;
+        s_slice[k] = 0.0f;
+        if (g < slices) {
+            float amax = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int idx = base + e;
+                float v = 0.0f;
+                if (idx < n) {
+                    if (MODE == ROW_RMSNORM) v = fmul(fmul(raw[k][e], inv_rms), b[idx]);
+                    else if (MODE == ROW_PLAIN) v = raw[k][e];
+                    else v = fmul(silu_f(raw[k][e]), b[idx]);
+                    if (p.y) p.y[(size_t)row * n + idx] = v;
+                }
+                raw[k][e] = v;                      // from here on the row values
+                amax = fmaxf(amax, fabsf(v));
+            }
+            amax = max_lanes(amax);
+            s_slice[k] = p.mx ? fdiv(amax, 127.0f) : amax;
+            smax = fmaxf(smax, s_slice[k]);
+        }
+    }
+    if (!p.q) return;
+    const float top = max_block_rt(smax, shf, nw);
+    if (p.mx) {
+        const float sx = (top == 0.0f) ? 1.0f : fdiv(top, 65535.0f);
+        if (threadIdx.x == 0) p.sx[row] = sx;
+#pragma unroll
+        for (int k = 0; k < WIDE_MAXK; k++) {
+            const int g = warp + k * nw, base = g * 128 + lane * 4;
+            if (g < slices) {
+                const unsigned mult = group_mult(s_slice[k], sx);
+                const float inv = fdiv(1.0f, fmul(sx, (float)mult));
+                char4 c;
+                c.x = (signed char)quant_code(raw[k][0], inv);
+                c.y = (signed char)quant_code(raw[k][1], inv);
+                c.z = (signed char)quant_code(raw[k][2], inv);
+                c.w = (signed char)quant_code(raw[k][3], inv);
+                *reinterpret_cast<char4*>(p.q + (size_t)row * n + base) = c;
+                if (lane == 0) p.mx[(size_t)row * (n >> 7) + g] = (uint16_t)mult;
+            }
+        }
+    } else {
+        const float s = (top == 0.0f) ? 1.0f : fdiv(top, 127.0f);
+        const float inv = fdiv(1.0f, s);
+        if (threadIdx.x == 0) p.sx[row] = s;
+#pragma unroll
+        for (int k = 0; k < WIDE_MAXK; k++) {
+            const int g = warp + k * nw, base = g * 128 + lane * 4;
+            if (g < slices) {
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (base + e < n) p.q[(size_t)row * n + base + e] = (int8_t)quant_code(raw[k][e], inv);
+            }
+        }
+    }
+}
+
+static bool g_row_wide = true;   // measurement switch (det_debug_set_rows)
+
 template <int MODE, bool XCHG = false>
 static void launch_row(const RowArgs& p, int M, cudaStream_t q, const XchgArgs* xa = nullptr) {
     const int n = p.n;
@@ -202,6 +338,11 @@ static void launch_row(const RowArgs& p, int M, cudaStream_t q, const XchgArgs* 
     int P = 128;
     while (P < n) P <<= 1;
     const int slices = (n + 127) >> 7;
+    if (!XCHG && M >= 32 && g_row_wide) {          // many rows: one CTA per row (a choice by shape only)
+        const int warps = slices < 32 ? slices : 32;
+        launch_pdl(k_row_wide<MODE>, dim3(M), dim3(warps * 32), 0, q, 1, p, P / 128);
+        return;
+    }
     int cs = 8;                                   // cluster size: by shape only
     while (cs > 1 && slices / cs < 4) cs >>= 1;
     const int spc = (slices + cs - 1) / cs;       // <= 32
@@ -381,6 +522,8 @@ void det_xchg_quant(void* h, const float* local, const float* local_b, int slice
     RowArgs p{nullptr, nullptr, 0.0f, slice * xc->size, nullptr, xq, sx, mx, nullptr};
     launch_row<ROW_PLAIN, true>(p, M, queue_of(st), &xa);
 }
+// Measurement switch: 0 keeps the cluster-per-row kernel for every M (results are the same).
+void det_debug_set_rows(int wide) { g_row_wide = wide != 0; }
 void det_embed(const uint16_t* table_bf16, const int* ids, int M, int H, float* x, cudaStream_t st) {
     if (M <= 0) return;
     launch_pdl(k_embed_rows, dim3(M), dim3(256), 0, queue_of(st), 1, table_bf16, ids, H, x);
