@@ -210,6 +210,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         h.dh_cuda_debug(bk, 0, args.fuse_kinds)
     if args.attn_flags >= 0:
         d.det_debug_set_attn(args.attn_flags)
+    if args.rows_wide_min >= 0:
+        d.det_debug_set_rows(args.rows_wide_min)
     if args.tc_splitk:
         d.det_debug_set_tc_variant(0x100)
     # N > 1: tensor parallel over NVLink.  torch.distributed (gloo, CPU) only carries the NCCL id, the barriers and the
@@ -540,6 +542,8 @@ def main():
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--attn-flags", type=int, default=-1,
                     help="measurement switch for the attention kernels (det_debug_set_attn): 1 token-tiled prefill, +2 two stages")
+    ap.add_argument("--rows-wide-min", type=int, default=-1,
+                    help="measurement switch: rows from which the row kernels use one CTA per row (det_debug_set_rows)")
     ap.add_argument("--tc-splitk", action="store_true",
                     help="measurement switch: the tensor-core GEMM splits K for linears with few row tiles (same values)")
     ap.add_argument("--compose-rows", action="store_true",

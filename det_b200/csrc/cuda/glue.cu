@@ -327,7 +327,7 @@ __global__ void __launch_bounds__(1024) k_row_wide(RowArgs p, int pslices /* P /
     }
 }
 
-static bool g_row_wide = true;   // measurement switch (det_debug_set_rows)
+static int g_row_wide_min = 32;   // rows from which the one-CTA-per-row kernel is used (det_debug_set_rows; 0 = never)
 
 template <int MODE, bool XCHG = false>
 static void launch_row(const RowArgs& p, int M, cudaStream_t q, const XchgArgs* xa = nullptr) {
@@ -338,7 +338,7 @@ static void launch_row(const RowArgs& p, int M, cudaStream_t q, const XchgArgs* 
     int P = 128;
     while (P < n) P <<= 1;
     const int slices = (n + 127) >> 7;
-    if (!XCHG && M >= 32 && g_row_wide) {          // many rows: one CTA per row (a choice by shape only)
+    if (!XCHG && g_row_wide_min > 0 && M >= g_row_wide_min) {   // many rows: one CTA per row (a choice by shape only)
         const int warps = slices < 32 ? slices : 32;
         launch_pdl(k_row_wide<MODE>, dim3(M), dim3(warps * 32), 0, q, 1, p, P / 128);
         return;
@@ -522,8 +522,8 @@ void det_xchg_quant(void* h, const float* local, const float* local_b, int slice
     RowArgs p{nullptr, nullptr, 0.0f, slice * xc->size, nullptr, xq, sx, mx, nullptr};
     launch_row<ROW_PLAIN, true>(p, M, queue_of(st), &xa);
 }
-// Measurement switch: 0 keeps the cluster-per-row kernel for every M (results are the same).
-void det_debug_set_rows(int wide) { g_row_wide = wide != 0; }
+// Measurement switch: the number of rows from which the one-CTA-per-row kernel is used (default 32; 0 = never).
+void det_debug_set_rows(int min_rows) { g_row_wide_min = min_rows; }
 void det_embed(const uint16_t* table_bf16, const int* ids, int M, int H, float* x, cudaStream_t st) {
     if (M <= 0) return;
     launch_pdl(k_embed_rows, dim3(M), dim3(256), 0, queue_of(st), 1, table_bf16, ids, H, x);

@@ -264,9 +264,9 @@ void det_debug_set_pdl(int on);
 /* Measurement switches for the attention kernels: bit 0 = token-tiled prefill kernels (default off), bit 1 = two
  * shared-memory stages in the tiled accumulate kernel (default off).  Same results.                                   */
 void det_debug_set_attn(int flags);
-/* Measurement switch for the row kernels: non-zero (default) lets calls with 32 or more rows use one CTA per row instead
- * of a cluster per row.  Same results.                                                                               */
-void det_debug_set_rows(int wide);
+/* Measurement switch for the row kernels: calls with at least min_rows rows (default 32; 0 = never) use one CTA per row
+ * instead of a cluster per row.  Same results.                                                                       */
+void det_debug_set_rows(int min_rows);
 /* Measurement switch: pins the tensor-core GEMM's tile, 1..5 = (tokens, columns per epilogue warp) (64,32) (64,16)
  * (32,8) (32,16) (128,32); 0 = chosen by shape (default).  Adding 0x100 / 0x200 switches the split of K over several
  * CTAs for linears with few row tiles on / off.  Results do not depend on any of it.                                   */
