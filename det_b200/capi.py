@@ -107,6 +107,8 @@ CUDA_ABI = {
                                   c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "det_gdn_rows": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int,
                             c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "det_gdn_quant": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int,
+                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "det_gdn_ab": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                           c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "det_xchg_create": (c_void_p, [c_size_t, c_int, c_int]),
@@ -158,6 +160,7 @@ HOST_API = {
                                   c_void_p, C.POINTER(c_size_t)]),
     "dh_cuda_set_fuse_rows": (None, [c_void_p, c_int]),
     "dh_cuda_set_fold_ab": (None, [c_void_p, c_int]),
+    "dh_cuda_set_fuse_gdn_quant": (None, [c_void_p, c_int]),
     "dh_batch_new": (c_void_p, [c_void_p, c_size_t, c_size_t]),
     "dh_batch_free": (None, [c_void_p]),
     "dh_batch_prefill": (c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_int, c_float, c_size_t, c_float, c_u64]),

@@ -38,6 +38,12 @@ struct GdnArgs {
     const float* sx;
     const uint16_t* mx;
     int K;
+    // decode form with the activation quantization of the mixer output folded into k_gdn_out (oq != NULL, M = 1): the
+    // CTA that finishes last quantizes the row exactly as det_quant would (quant_act_i8g); `out_done` counts the CTAs
+    int8_t* oq;
+    float* osx;
+    uint16_t* omx;
+    unsigned* out_done;
 };
 
 // The CTA's share of one output of a W8 linear for token row t (spec gemm_row, spec/quant.rs:99-117): the int64 sum over
@@ -398,32 +404,87 @@ __global__ void __launch_bounds__(128) k_gdn_out(const GdnArgs g, int row_blocks
     }
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const long long row = (long long)blockIdx.x * 4 + wib;   // t * n_v + h
-    if (row >= (long long)g.M * g.n_v) return;
-    const float* o = g.o + row * DV + lane * 4;
-    float v[4], sq[4];
+    if (row < (long long)g.M * g.n_v) {
+        const float* o = g.o + row * DV + lane * 4;
+        float v[4], sq[4];
 #pragma unroll
-    for (int e = 0; e < 4; e++) {
-        v[e] = o[e];
-        sq[e] = fmul(v[e], v[e]);
+        for (int e = 0; e < 4; e++) {
+            v[e] = o[e];
+            sq[e] = fmul(v[e], v[e]);
+        }
+        const float ss = fold_lanes<32>(fold_run<4>(sq));
+        const float inv = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)DV), g.eps)));
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float yn = fmul(fmul(v[e], inv), g.norm[lane * 4 + e]);
+            g.on[row * DV + lane * 4 + e] = fmul(yn, silu_f(g.z[row * DV + lane * 4 + e]));
+        }
     }
-    const float ss = fold_lanes<32>(fold_run<4>(sq));
-    const float inv = fdiv(1.0f, fsqrt(fadd(fdiv(ss, (float)DV), g.eps)));
+    if (!g.oq) return;
+    // ---- M = 1 with the quantization folded in: the row-block CTA that finishes last quantizes the whole row
+    // (n_v groups of 128 = one head each) with the expressions of the row kernel: group scale amax / 127, row scale
+    // max / 65535, integer multiplier per group, codes.
+    __shared__ bool last;
+    __shared__ float wmax[4];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(g.out_done, 1u) == (unsigned)row_blocks - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    constexpr int MAXG = 16;                       // groups per warp: up to 64 v heads
+    float val[MAXG][4], s_grp[MAXG];
+    float smax = 0.0f;
 #pragma unroll
-    for (int e = 0; e < 4; e++) {
-        const float yn = fmul(fmul(v[e], inv), g.norm[lane * 4 + e]);
-        g.on[row * DV + lane * 4 + e] = fmul(yn, silu_f(g.z[row * DV + lane * 4 + e]));
+    for (int k = 0; k < MAXG; k++) {
+        const int grp = wib + 4 * k;
+        s_grp[k] = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 4; e++) val[k][e] = 0.0f;
+        if (grp < g.n_v) {
+            const float4 x = __ldcg(reinterpret_cast<const float4*>(g.on + (size_t)grp * DV + lane * 4));
+            val[k][0] = x.x; val[k][1] = x.y; val[k][2] = x.z; val[k][3] = x.w;
+            float amax = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+            amax = max_lanes(amax);
+            s_grp[k] = fdiv(amax, 127.0f);
+            smax = fmaxf(smax, s_grp[k]);
+        }
+    }
+    if (lane == 0) wmax[wib] = smax;
+    __syncthreads();
+    const float top = fmaxf(fmaxf(wmax[0], wmax[1]), fmaxf(wmax[2], wmax[3]));
+    const float sx = (top == 0.0f) ? 1.0f : fdiv(top, 65535.0f);
+    if (threadIdx.x == 0) {
+        g.osx[0] = sx;
+        *g.out_done = 0;
+    }
+#pragma unroll
+    for (int k = 0; k < MAXG; k++) {
+        const int grp = wib + 4 * k;
+        if (grp < g.n_v) {
+            const unsigned mult = group_mult(s_grp[k], sx);
+            const float inv = fdiv(1.0f, fmul(sx, (float)mult));
+            char4 c;
+            c.x = (signed char)quant_code(val[k][0], inv);
+            c.y = (signed char)quant_code(val[k][1], inv);
+            c.z = (signed char)quant_code(val[k][2], inv);
+            c.w = (signed char)quant_code(val[k][3], inv);
+            *reinterpret_cast<char4*>(g.oq + (size_t)grp * DV + lane * 4) = c;
+            if (lane == 0) g.omx[grp] = (uint16_t)mult;
+        }
     }
 }
 
 static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 struct GdnScratch {
-    size_t y, beta, decay, o, total;
+    size_t done, y, beta, decay, o, total;
 };
 static GdnScratch gdn_scratch(int M, int n_k, int n_v) {
     GdnScratch s;
     const size_t conv_dim = (size_t)2 * n_k * DK + (size_t)n_v * DV;
-    s.y = 0;
-    s.beta = up256((size_t)M * conv_dim * 4);
+    s.done = 0;          // a counter at a fixed place (it must stay zero between calls whatever M is)
+    s.y = 256;
+    s.beta = s.y + up256((size_t)M * conv_dim * 4);
     s.decay = s.beta + up256((size_t)M * n_v * 4);
     s.o = s.decay + up256((size_t)M * n_v * 4);
     s.total = s.o + up256((size_t)M * n_v * DV * 4);
@@ -441,6 +502,11 @@ size_t det_gdn_scratch_bytes(int M, int n_k, int n_v, int dk, int dv) {
     return gdn_scratch(M > 0 ? M : 1, n_k, n_v).total;
 }
 
+struct QuantOut {
+    int8_t* q;
+    float* sx;
+    uint16_t* mx;
+};
 struct AbSource {
     const det_qlinear* lin;
     const int8_t* xq;
@@ -449,7 +515,8 @@ struct AbSource {
 };
 static void gdn_entry(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_state* rows, const float* qkv, const float* z,
                       const float* a, const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on,
-                      void* scratch, float* gin, float* gout, cudaStream_t st, const AbSource* ab = nullptr) {
+                      void* scratch, float* gin, float* gout, cudaStream_t st, const AbSource* ab = nullptr,
+                      const QuantOut* qo = nullptr) {
     if (M <= 0) return;
     DETB_REQUIRE(dk == DK && dv == DV, "Gated DeltaNet kernels are built for dk = dv = 128");
     DETB_REQUIRE(n_k > 0 && n_v % n_k == 0, "n_v must be a multiple of n_k");
@@ -465,6 +532,12 @@ static void gdn_entry(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_st
                      "a|b must be a W8 reference-layout linear of 2 * n_v rows");
         g.ab_wq = ab->lin->wq; g.ab_c = ab->lin->c; g.ab_m = ab->lin->m;
         g.xq = ab->xq; g.sx = ab->sx; g.mx = ab->mx; g.K = ab->lin->K;
+    }
+    g.oq = nullptr; g.osx = nullptr; g.omx = nullptr;
+    g.out_done = reinterpret_cast<unsigned*>(base + sm.done);
+    if (qo) {
+        DETB_REQUIRE(M == 1 && rows == nullptr && n_v <= 64, "the output quantization folds into single-token steps only");
+        g.oq = qo->q; g.osx = qo->sx; g.omx = qo->mx;
     }
     g.conv_state = S ? S->conv_state : nullptr;
     g.S = S ? S->S : nullptr;
@@ -503,6 +576,16 @@ void det_gdn_rows(const det_gdn_layer* L, const det_gdn_state* rows, const float
                   const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
                   cudaStream_t st) {
     gdn_entry(L, nullptr, rows, qkv, z, a, b, eps, M, n_k, n_v, dk, dv, on, scratch, nullptr, nullptr, st);
+}
+
+// One decode token with the activation quantization of the mixer output folded in (no reference counterpart): det_gdn
+// followed by det_quant(on, 1, n_v * dv) -> oq, osx, omx, one launch less.  The scratch must come zero-filled from
+// det_malloc and be used for nothing else (a counter lives in its first bytes).
+void det_gdn_quant(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a, const float* b,
+                   float eps, int n_k, int n_v, int dk, int dv, float* on, int8_t* oq, float* osx, uint16_t* omx,
+                   void* scratch, cudaStream_t st) {
+    const QuantOut qo{oq, osx, omx};
+    gdn_entry(L, S, nullptr, qkv, z, a, b, eps, 1, n_k, n_v, dk, dv, on, scratch, nullptr, nullptr, st, nullptr, &qo);
 }
 
 // Decode step(s) with the layer's a|b projection folded into the mixer (no reference counterpart): `ab` is the fused

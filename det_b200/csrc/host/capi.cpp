@@ -201,6 +201,12 @@ size_t dh_graph_decoder_finish(void* d, int32_t* out, size_t cap) {
 void dh_cuda_set_fuse_rows(void* backend, int on) {
     if (auto* c = dynamic_cast<det::CudaBackend*>(static_cast<det::Backend*>(backend))) c->fuse_rows = on != 0;
 }
+void dh_cuda_set_fuse_gdn_quant(void* backend, int on) {
+    if (auto* c = dynamic_cast<det::CudaBackend*>(static_cast<det::Backend*>(backend))) {
+        c->flush();
+        c->fuse_gdn_quant = on != 0;
+    }
+}
 void dh_cuda_set_fold_ab(void* backend, int on) {
     if (auto* c = dynamic_cast<det::CudaBackend*>(static_cast<det::Backend*>(backend))) c->fold_ab = on != 0;
 }

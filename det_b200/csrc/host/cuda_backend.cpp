@@ -66,7 +66,16 @@ bool CudaBackend::hold(int kind, const float* a, const float* b, float eps, size
     pending_.xq = xq; pending_.sx = sx; pending_.mx = mx;
     return true;
 }
+void CudaBackend::flush_gdn() {
+    if (!pending_gdn_.on) return;
+    const PendingGdn g = pending_gdn_;
+    pending_gdn_.on = false;
+    det_gdn_state st = g.state;
+    void* sc = scratch(gdn_scratch_, det_gdn_scratch_bytes(1, g.n_k, g.n_v, g.dk, g.dv));
+    det_gdn_ex(&g.layer, &st, g.qkv, g.z, g.a, g.b, g.eps, 1, g.n_k, g.n_v, g.dk, g.dv, g.out, sc, nullptr, nullptr, ST);
+}
 void CudaBackend::flush_pending() {
+    flush_gdn();
     if (!pending_.kind) return;
     const PendingAct p = pending_;
     pending_.kind = 0;
@@ -163,6 +172,17 @@ void CudaBackend::rmsnorm_quant(const Buf<float>& x, const Buf<float>& w, float 
 void CudaBackend::quant(const Buf<float>& x, size_t m, size_t n, const Buf<int8_t>& xq, const Buf<float>& sx,
                         const Buf<uint16_t>& mx) {
     if (skip_mask & 2) return;
+    if (pending_gdn_.on && m == 1 && x.ptr() == pending_gdn_.out && n == (size_t)pending_gdn_.n_v * pending_gdn_.dv) {
+        // the single-token Gated DeltaNet step that was held back, with this quantization folded into its last kernel
+        const PendingGdn g = pending_gdn_;
+        pending_gdn_.on = false;
+        flush_pending();
+        det_gdn_state st = g.state;
+        void* sc = scratch(gdn_scratch_, det_gdn_scratch_bytes(1, g.n_k, g.n_v, g.dk, g.dv));
+        det_gdn_quant(&g.layer, &st, g.qkv, g.z, g.a, g.b, g.eps, g.n_k, g.n_v, g.dk, g.dv, g.out, xq.ptr(), sx.ptr(), mx.ptr(),
+                      sc, ST);
+        return;
+    }
     if (hold(DET_ACT_PLAIN, x.ptr(), nullptr, 0.0f, m, n, xq.ptr(), sx.ptr(), mx.ptr())) return;
     det_quant(x.ptr(), (int)m, (int)n, xq.ptr(), sx.ptr(), mx.ptr(), ST);
 }
@@ -171,6 +191,7 @@ void CudaBackend::quant(const Buf<float>& x, size_t m, size_t n, const Buf<int8_
 void CudaBackend::gemm(const Linear& lin_, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx,
                        size_t m, const GemmOut& out) {
     const CudaLinear& lin = static_cast<const CudaLinear&>(lin_);
+    flush_gdn();
     if (skip_mask & 8) {
         pending_.kind = 0;
         return;
@@ -263,6 +284,16 @@ void CudaBackend::gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, 
     flush_pending();
     det_gdn_layer layer{l.conv->ptr(), l.a->ptr(), l.dt_bias->ptr(), l.norm->ptr()};
     det_gdn_state state{st.conv_state.ptr(), st.s.ptr()};
+    if (fuse_gdn_quant && s.m == 1 && !ex.gin && !ex.gout && s.n_v <= 64) {
+        pending_gdn_.on = true;
+        pending_gdn_.layer = layer;
+        pending_gdn_.state = state;
+        pending_gdn_.qkv = qkv.ptr(); pending_gdn_.z = z.ptr(); pending_gdn_.a = a.ptr(); pending_gdn_.b = b.ptr();
+        pending_gdn_.out = on.ptr();
+        pending_gdn_.eps = s.eps;
+        pending_gdn_.n_k = (int)s.n_k; pending_gdn_.n_v = (int)s.n_v; pending_gdn_.dk = (int)s.dk; pending_gdn_.dv = (int)s.dv;
+        return;
+    }
     void* sc = scratch(gdn_scratch_, det_gdn_scratch_bytes((int)s.m, (int)s.n_k, (int)s.n_v, (int)s.dk, (int)s.dv));
     det_gdn_ex(&layer, &state, qkv.ptr(), z.ptr(), a.ptr(), b.ptr(), s.eps, (int)s.m, (int)s.n_k, (int)s.n_v,
                (int)s.dk, (int)s.dv, on.ptr(), sc, ex.gin ? ex.gin->ptr() : nullptr, ex.gout ? ex.gout->ptr() : nullptr,

@@ -57,6 +57,9 @@ class CudaBackend : public Backend {
     // gdn_decode_ab is off by default: measured on the 27B shape it lengthens every recurrence CTA's critical path by more
     // than the a|b GEMV launch it removes costs (6.79 vs 6.55 ms per token)
     bool fold_ab = false;
+    // held-back single-token gdn() + quant as det_gdn_quant: off by default — measured slower on the 27B shape (6.57 vs
+    // 6.21 ms per token: the one CTA that quantizes the row is slower than the cluster kernel it replaces)
+    bool fuse_gdn_quant = false;
     bool fuse_rows = true;
     void add(const Buf<float>& x, const Buf<float>& y, size_t n) override;
     void silu_mul(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<float>& h) override;
@@ -101,9 +104,21 @@ class CudaBackend : public Backend {
         float* sx = nullptr;
         uint16_t* mx = nullptr;
     } pending_;
+    // A single-token gdn() is held back for one call: when the quantization of its output follows, both run as
+    // det_gdn_quant (one launch less); anything else issues it as it is.
+    struct PendingGdn {
+        bool on = false;
+        det_gdn_layer layer{};
+        det_gdn_state state{};
+        const float *qkv = nullptr, *z = nullptr, *a = nullptr, *b = nullptr;
+        float* out = nullptr;
+        float eps = 0.0f;
+        int n_k = 0, n_v = 0, dk = 0, dv = 0;
+    } pending_gdn_;
     bool hold(int kind, const float* a, const float* b, float eps, size_t m, size_t n, int8_t* xq, float* sx,
               uint16_t* mx);
     void flush_pending();
+    void flush_gdn();
     void* scratch(Buf<uint8_t>& slot, size_t bytes);
     void finish_linear(CudaLinear& l);
     Buf<uint8_t> attn_scratch_, gdn_scratch_, sample_scratch_, synth_scratch_;

@@ -219,6 +219,13 @@ void det_gdn_rows(const det_gdn_layer* L, const det_gdn_state* rows, const float
                   const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
                   cudaStream_t st);
 
+/* One decode token of a Gated DeltaNet layer with the activation quantization of its output folded in (no reference
+ * counterpart): det_gdn(M = 1) followed by det_quant(on, 1, n_v * dv, oq, osx, omx) in one launch less.  `scratch` must be
+ * zero-filled memory from det_malloc that nothing else writes (a counter lives in its first bytes).                   */
+void det_gdn_quant(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a, const float* b,
+                   float eps, int n_k, int n_v, int dk, int dv, float* on, int8_t* oq, float* osx, uint16_t* omx,
+                   void* scratch, cudaStream_t st);
+
 /* Decode step(s) of a Gated DeltaNet layer with its a|b projection folded into the mixer kernel (no reference
  * counterpart): `ab` is the fused W8 linear [a rows | b rows] in the reference layout, xq / sx / mx the quantized layer
  * input (M rows of K).  Exactly one of S (one sequence, M = 1) and rows (M sequences, device table) is non-NULL.

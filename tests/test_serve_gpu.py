@@ -50,3 +50,30 @@ def test_folded_ab_projection_gives_the_same_tokens(libs, cuda_backend):
             h.dh_cuda_set_fold_ab(cuda_backend, 0)
     assert np.array_equal(runs[0][0], runs[1][0])
     assert np.array_equal(runs[0][1], runs[1][1])
+
+
+def test_gdn_step_with_folded_quantization_gives_the_same_tokens(libs, cuda_backend):
+    """det_gdn_quant (the quantization of the mixer output done by the last CTA of the Gated DeltaNet output kernel)
+    against det_gdn followed by det_quant."""
+    import ctypes as C
+    h = libs.host()
+    ids = np.zeros(20, np.int32)
+    h.dh_synth_prompt(4, ids.size, 32768, ids.ctypes.data)
+    runs = []
+    for fuse in (0, 1):
+        h.dh_cuda_set_fuse_gdn_quant(cuda_backend, fuse)
+        try:
+            m = h.dh_model_new_synth(cuda_backend, b"tiny", 8, 20261125, 96, 16)
+            assert m, h.dh_last_error()
+            out = np.zeros(48, np.int32)
+            n = C.c_size_t(0)
+            assert h.dh_model_generate(m, ids.ctypes.data, ids.size, 48, 1, 1.0, 0, 1.0, 0, out.ctypes.data, C.byref(n)) == 0
+            logits = np.zeros(32768, np.float32)
+            h.dh_model_logits(m, logits.ctypes.data, logits.size)
+            runs.append((out[: n.value].copy(), logits.view(np.uint32).copy()))
+            h.dh_model_free(m)
+        finally:
+            h.dh_cuda_set_fuse_gdn_quant(cuda_backend, 0)
+    assert np.array_equal(runs[0][0], runs[1][0])
+    assert np.array_equal(runs[0][1], runs[1][1])
+    assert libs.cuda().det_last_error() == 0
