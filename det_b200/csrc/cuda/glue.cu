@@ -47,6 +47,9 @@ constexpr int MAX_SLICES = 256;   // rows up to 32768 values
 __device__ __forceinline__ float* peer_smem(float* local, unsigned rank) {
     return cg::this_cluster().map_shared_rank(local, rank);
 }
+// The two halves of a cluster barrier; every thread of every CTA executes both, alternately.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 // XCHG: the rows come out of the tensor-parallel exchange, which is this kernel's prologue: every CTA of the grid sends its
 // share of the local slice to all ranks, then each lane polls the staging packets that hold its four values (the grid is
@@ -54,10 +57,16 @@ __device__ __forceinline__ float* peer_smem(float* local, unsigned rank) {
 template <int MODE, bool XCHG>
 __global__ void __launch_bounds__(1024) k_row(RowArgs p, int spc /* slices per CTA */, int pslices /* P / 128 */,
                                               const XchgArgs xa) {
-    __shared__ float slice_sum[32];     // this CTA's slice sums (read by the peers)
-    __shared__ float cta_max;           // this CTA's largest group scale (read by the peers)
-    __shared__ float all_sums[MAX_SLICES];
+    __shared__ float all_sums[MAX_SLICES];   // slice sums of the whole row: every CTA's are PUSHED into every peer's copy
+    __shared__ float cta_maxes[8];           // largest group scale of every CTA of the cluster, pushed the same way
     __shared__ float shf[32];
+    // Exchanges are stores into the peers' shared memory followed by one cluster barrier (arrive + wait): nobody reads
+    // remote memory, so a round costs one barrier and no CTA has to stay alive for a late reader.  The first arrive
+    // is posted at entry and waited for just before the first remote store (a peer's shared memory may only be touched
+    // once that peer runs); by then it has usually completed.
+    for (int i = threadIdx.x; i < pslices; i += blockDim.x) all_sums[i] = 0.0f;   // zero padding of the tree
+    __syncthreads();
+    cluster_arrive();
     pdl_trigger();
     pdl_wait();
     unsigned seq = 0;
@@ -101,14 +110,10 @@ __global__ void __launch_bounds__(1024) k_row(RowArgs p, int spc /* slices per C
 #pragma unroll
         for (int e = 0; e < 4; e++) sq[e] = fmul(raw[e], raw[e]);
         const float ssum = fold_lanes<32>(fold_run<4>(sq));
-        if (lane == 0 && warp < spc) slice_sum[warp] = have ? ssum : 0.0f;
-        cluster.sync();
-        // gather the slice sums of the whole row in slice order, zero padded to the tree width
-        for (int i = threadIdx.x; i < pslices; i += blockDim.x) {
-            const int owner = i / spc, idx = i - owner * spc;
-            all_sums[i] = (owner < (int)cs && i < slices) ? peer_smem(slice_sum, owner)[idx] : 0.0f;
-        }
-        __syncthreads();
+        cluster_wait();                                   // every CTA of the cluster is running
+        if (have && lane < (int)cs) peer_smem(all_sums, lane)[g] = ssum;   // lane r stores into CTA r's copy
+        cluster_arrive();
+        cluster_wait();                                   // all slice sums of the row have landed here
         // finish the tree: lane owns pslices / 32 consecutive slice sums (or one each when there are fewer than 32)
         float tot;
         if (pslices >= 32) {
@@ -155,15 +160,16 @@ __global__ void __launch_bounds__(1024) k_row(RowArgs p, int spc /* slices per C
         s_slice = p.mx ? fdiv(amax, 127.0f) : amax;
     }
     if (!p.q) {
-        if (MODE == ROW_RMSNORM) cluster.sync();   // peers may still be reading slice_sum
+        if (MODE != ROW_RMSNORM) cluster_wait();   // pair the arrive posted at entry
         return;
     }
     const float cmax = max_block_rt(s_slice, shf, nw);
-    if (threadIdx.x == 0) cta_max = cmax;
-    cluster.sync();
+    if (MODE != ROW_RMSNORM) cluster_wait();       // (the RMSNorm path has already waited for the start of its peers)
+    if (threadIdx.x < cs) peer_smem(cta_maxes, threadIdx.x)[rank] = cmax;
+    cluster_arrive();
+    cluster_wait();
     float top = 0.0f;
-    for (unsigned r = 0; r < cs; r++) top = fmaxf(top, *peer_smem(&cta_max, r));
-    cluster.sync();   // nobody exits (or rewrites shared memory) while a peer is still reading it
+    for (unsigned r = 0; r < cs; r++) top = fmaxf(top, cta_maxes[r]);
 
     if (p.mx) {
         // quant_act_i8g: sx = smax / 65535 (1 when smax == 0); per group mult, eff = sx * mult, inv = 1 / eff
