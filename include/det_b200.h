@@ -271,7 +271,7 @@ void det_debug_set_pdl(int on);
 /* Measurement switches for the attention kernels: bit 0 = token-tiled prefill kernels (default off), bit 1 = two
  * shared-memory stages in the tiled accumulate kernel (default off).  Same results.                                   */
 void det_debug_set_attn(int flags);
-/* Measurement switch for the row kernels: calls with at least min_rows rows (default 32; 0 = never) use one CTA per row
+/* Measurement switch for the row kernels: calls with at least min_rows rows (default 128; 0 = never) use one CTA per row
  * instead of a cluster per row.  Same results.                                                                       */
 void det_debug_set_rows(int min_rows);
 /* Measurement switch: pins the tensor-core GEMM's tile, 1..5 = (tokens, columns per epilogue warp) (64,32) (64,16)
