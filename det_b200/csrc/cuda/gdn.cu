@@ -213,6 +213,9 @@ __device__ __forceinline__ void slab_store(const float* slab, float* Sh, int j0)
 // step) and nothing is exported.  The CTA computes what k_gdn_prep would have left in scratch for it — q and k of its
 // k head (conv, silu, l2norm with the same per-lane runs and xor order), its 16 v channels, beta and decay — so a
 // decode step needs no separate prep launch.
+// PREP = false: the operands come from k_gdn_prep's scratch instead (a batched step with many sequences: preparing them
+// once per head instead of in each of a head's 8 column CTAs and rep heads' worth of k heads is less work overall).
+template <bool PREP>
 __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
     __shared__ __align__(16) float slab[SLAB_FLOATS];
     __shared__ __align__(16) float pq[RL][RUN_STRIDE], pk[RL][RUN_STRIDE];   // runs of 16 rows, padded against conflicts
@@ -227,6 +230,34 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
     const int t = g.rows ? blockIdx.y : 0;
     float* Sh = (g.rows ? g.rows[blockIdx.y].S : g.S) + (size_t)h * DK * DV;
     slab_load_async(slab, Sh, j0);     // in flight while the operands are prepared
+    if (!PREP) {
+        // operands from scratch: this thread's 16 rows of k and q, its column's v, the head's beta and decay
+        const float* qrow = g.y + (size_t)t * g.conv_dim + (size_t)kh * DK + p * RR;
+        const float* krow = g.y + (size_t)t * g.conv_dim + (size_t)g.n_k * DK + (size_t)kh * DK + p * RR;
+        float k[RR], q[RR];
+#pragma unroll
+        for (int i = 0; i < RR; i += 4) {
+            const float4 kk = *reinterpret_cast<const float4*>(krow + i);
+            const float4 qq = *reinterpret_cast<const float4*>(qrow + i);
+            k[i] = kk.x; k[i + 1] = kk.y; k[i + 2] = kk.z; k[i + 3] = kk.w;
+            q[i] = qq.x; q[i + 1] = qq.y; q[i + 2] = qq.z; q[i + 3] = qq.w;
+        }
+        const float vv = g.y[(size_t)t * g.conv_dim + (size_t)2 * g.n_k * DK + (size_t)h * DV + j0 + jj];
+        const float be = g.beta[(size_t)t * g.n_v + h], de = g.decay[(size_t)t * g.n_v + h];
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        float s[RR];
+#pragma unroll
+        for (int i = 0; i < RR; i++) s[i] = slab[slab_at(p * RR + i, jj)];
+        const float ov = recur_step(s, k, q, vv, be, de);
+        if (p == 0) g.o[((size_t)t * g.n_v + h) * DV + j0 + jj] = ov;
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < RR; i++) slab[slab_at(p * RR + i, jj)] = s[i];
+        __syncthreads();
+        slab_store(slab, Sh, j0);
+        return;
+    }
     if (g.ab_wq) {
         // a[h] and b[h] of this token: all four warps share the two W8 rows
         const long long pa = ab_partial(g, t, h), pb = ab_partial(g, t, g.n_v + h);
@@ -553,12 +584,14 @@ static void gdn_entry(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_st
     cudaStream_t q = queue_of(st);
     const int heads = 2 * n_k + n_v;
     // decode form: every CTA of the recurrence advances one token and prepares its own operands
-    const bool fused_prep = (rows != nullptr || M == 1) && gin == nullptr;
+    // (with many sequences the shared prep kernel is less work than preparing inside every recurrence CTA)
+    const bool fused_prep = (rows ? (M < 8 || ab != nullptr) : M == 1) && gin == nullptr;
     if (fused_prep) {
-        launch_pdl(k_gdn_recur_dec, dim3(n_v * (DV / RC), rows ? M : 1), dim3(RC * RL), 0, q, 1, g);
+        launch_pdl(k_gdn_recur_dec<true>, dim3(n_v * (DV / RC), rows ? M : 1), dim3(RC * RL), 0, q, 1, g);
     } else {
         launch_pdl(k_gdn_prep, dim3((heads + 3) / 4, M), dim3(128), 0, q, 1, g);
-        launch_pdl(k_gdn_recur_seq, dim3(n_v * (DV / RC)), dim3(RC * RL), 0, q, 1, g);
+        if (rows) launch_pdl(k_gdn_recur_dec<false>, dim3(n_v * (DV / RC), M), dim3(RC * RL), 0, q, 1, g);
+        else launch_pdl(k_gdn_recur_seq, dim3(n_v * (DV / RC)), dim3(RC * RL), 0, q, 1, g);
     }
     const int row_blocks = (int)(((long long)M * n_v + 3) / 4);
     const int state_blocks = ((g.conv_dim + 127) / 128) * (rows ? M : 1);

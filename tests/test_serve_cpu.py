@@ -18,8 +18,9 @@ def _prompt(h, seed, n):
     return ids
 
 
-def run_streams(h, backend, n_new, layers=4, ctx=64):
-    """(batched streams, solo streams) for the prompts above."""
+def run_streams(h, backend, n_new, layers=4, ctx=64, prompts=None):
+    """(batched streams, solo streams) for the prompts above (or the given prompt lengths)."""
+    PROMPTS = prompts or globals()["PROMPTS"]
     model = h.dh_model_new_synth(backend, b"tiny", layers, SEED, ctx, 16)
     assert model, h.dh_last_error()
     solo = []

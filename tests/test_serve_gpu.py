@@ -10,6 +10,16 @@ from test_serve_cpu import run_streams
 pytestmark = pytest.mark.gpu
 
 
+def test_nine_sequences_use_the_shared_prep_kernel(libs, cuda_backend):
+    """From 8 sequences on the batched Gated DeltaNet step prepares its operands once per head (k_gdn_prep) instead of in
+    every recurrence CTA; the streams must still equal the solo streams."""
+    h = libs.host()
+    together, solo = run_streams(h, cuda_backend, n_new=24, layers=8, ctx=96, prompts=[5, 17, 33, 9, 12, 3, 40, 21, 8])
+    for i, (a, b) in enumerate(zip(together, solo)):
+        assert np.array_equal(a, b), (i, a, b)
+    assert libs.cuda().det_last_error() == 0
+
+
 @pytest.mark.parametrize("fused,fold_ab", [(1, 0), (0, 0), (1, 1)])
 def test_batched_streams_equal_solo_streams(fused, fold_ab, libs, cuda_backend):
     """fold_ab = 1 also routes both the solo decode and the batched step through det_gdn_ab (a|b projection inside the
