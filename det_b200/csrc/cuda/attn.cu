@@ -228,10 +228,14 @@ __device__ __forceinline__ void key_range(const AttnArgs& a, int pos, int& k0, i
 }
 
 template <int HD>
+__device__ __forceinline__ void fetch_k_async(int8_t* ktile, float* sks, const AttnArgs& a, const RowCache& c, int kvh,
+                                              int key0, int nkeys);
+
+template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS) k_attn_max(const AttnArgs a) {
-    __shared__ __align__(16) int8_t ktile[KT * KTile<HD>::STRIDE];
+    __shared__ __align__(16) int8_t ktiles[2][KT * KTile<HD>::STRIDE];   // the next K tile is in flight while this one is used
     __shared__ __align__(16) int8_t qs[MAX_REP * HD];
-    __shared__ float sks[KT];
+    __shared__ float sks2[2][KT];
     __shared__ float sqs[MAX_REP];
     __shared__ unsigned best[MAX_REP];
     pdl_trigger();
@@ -253,11 +257,21 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_max(const AttnArgs a) {
     unsigned mine[MAX_REP / 4 + 1];
 #pragma unroll
     for (int i = 0; i < MAX_REP / 4 + 1; i++) mine[i] = 0u;
-    for (int key0 = k0; key0 < k1; key0 += KT) {
+    auto fetch = [&](int key0, int st) {
+        fetch_k_async<HD>(ktiles[st], sks2[st], a, cache, kvh, key0, min(KT, k1 - key0));
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(k0, 0);
+    int st = 0;
+    for (int key0 = k0; key0 < k1; key0 += KT, st ^= 1) {
         const int nkeys = min(KT, k1 - key0);
+        const bool more = key0 + KT < k1;
+        if (more) fetch(key0 + KT, st ^ 1);
+        if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
-        KTile<HD>::load(ktile, sks, a, cache, kvh, key0, nkeys);
-        __syncthreads();
+        const int8_t* ktile = ktiles[st];
+        const float* sks = sks2[st];
         if (j < nkeys) {
 #pragma unroll
             for (int i = 0; i < MAX_REP / 4 + 1; i++) {
@@ -269,6 +283,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_max(const AttnArgs a) {
                 }
             }
         }
+        __syncthreads();                                   // this stage may be refilled
     }
 #pragma unroll
     for (int i = 0; i < MAX_REP / 4 + 1; i++) {
