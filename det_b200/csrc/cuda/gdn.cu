@@ -389,19 +389,33 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_seq(const GdnArgs g) {
     for (int t0 = 0; t0 < g.M; t0 += TB, buf ^= 1) {
         if (t0 + TB < g.M) stage(t0 + TB, buf ^ 1);        // next block in flight
         const int n = min(TB, g.M - t0);
-#pragma unroll 1
-        for (int tok = 0; tok < n; tok++) {
+        // two register sets: the next token's operands come out of shared memory while this token's step runs
+        float kr[2][RR], qr[2][RR], vr[2], br[2], dr[2];
+        auto take = [&](int tok, int b) {
             const TokOps& o = ops[buf][tok];
-            float k[RR], q[RR];
 #pragma unroll
             for (int i = 0; i < RR; i += 4) {
                 const float4 kk = *reinterpret_cast<const float4*>(&o.k[p][i]);
                 const float4 qq = *reinterpret_cast<const float4*>(&o.q[p][i]);
-                k[i] = kk.x; k[i + 1] = kk.y; k[i + 2] = kk.z; k[i + 3] = kk.w;
-                q[i] = qq.x; q[i + 1] = qq.y; q[i + 2] = qq.z; q[i + 3] = qq.w;
+                kr[b][i] = kk.x; kr[b][i + 1] = kk.y; kr[b][i + 2] = kk.z; kr[b][i + 3] = kk.w;
+                qr[b][i] = qq.x; qr[b][i + 1] = qq.y; qr[b][i + 2] = qq.z; qr[b][i + 3] = qq.w;
             }
-            const float ov = recur_step(s, k, q, o.v[jj], o.beta, o.decay);
-            if (p == 0) g.o[((size_t)(t0 + tok) * g.n_v + h) * DV + j0 + jj] = ov;
+            vr[b] = o.v[jj];
+            br[b] = o.beta;
+            dr[b] = o.decay;
+        };
+        take(0, 0);
+#pragma unroll 1
+        for (int tok = 0; tok < n; tok += 2) {
+#pragma unroll
+            for (int b = 0; b < 2; b++) {
+                const int tk = tok + b;
+                if (tk < n) {
+                    if (tk + 1 < n) take(tk + 1, b ^ 1);
+                    const float ov = recur_step(s, kr[b], qr[b], vr[b], br[b], dr[b]);
+                    if (p == 0) g.o[((size_t)(t0 + tk) * g.n_v + h) * DV + j0 + jj] = ov;
+                }
+            }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();                                   // the next block has landed; this one may be overwritten
