@@ -247,8 +247,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #pragma unroll
         for (int t = 0; t < EC; t++) acc[t] = 0;
         const uint16_t* mrow = a.m + (size_t)(n < a.N ? n : 0) * G;
+        unsigned mw_next = GL > 0 ? mrow[g0] : 0u;          // the row's multiplier, fetched one group ahead
         for (int l = 0; l < GL; l++) {
             const int b = l % NBUF, g = g0 + l;
+            const unsigned mw = mw_next;
+            if (l + 1 < GL) mw_next = mrow[g + 1];
             ok = mbar_wait(&tfull[b], (unsigned)(l / NBUF) & 1u);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -258,7 +261,6 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&tempty[b]);
-            const unsigned mw = mrow[g];
             const unsigned* mxg = reinterpret_cast<const unsigned*>(mxs + g * TC_TOK + half * EC);
 #pragma unroll
             for (int t = 0; t < EC; t += 2) {
