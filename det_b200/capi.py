@@ -48,6 +48,8 @@ class ActSource(C.Structure):
 DET_LAYOUT_STREAM = 0x100
 DET_LAYOUT_INT8 = 0x200
 DET_ACT_RMSNORM, DET_ACT_PLAIN, DET_ACT_SWIGLU = 1, 2, 3
+# tile pins of the tensor-core GEMM (det_debug_set_tc_variant) that take large batches; 0 = chosen by shape
+TC_VARIANTS_LARGE = (0, 1, 5)
 
 # every symbol include/det_b200.h declares: name -> (restype, argtypes)
 CUDA_ABI = {
@@ -127,6 +129,9 @@ CUDA_ABI = {
     "det_debug_set_rows": (None, [c_int]),
     "det_debug_umma_peak": (C.c_double, [c_int]),
     "det_last_error": (c_int, []),
+    "det_clear_error": (None, []),
+    "det_debug_set_wait_limit": (None, [C.c_longlong]),
+    "det_debug_xchg_drop": (None, [c_void_p, c_int]),
 }
 
 HOST_API = {

@@ -740,7 +740,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_dec(const AttnArgs a) {
             bool ok = *reinterpret_cast<volatile int*>(a.error_flag) != 0;
             while (!ok) {
                 if (*reinterpret_cast<volatile unsigned*>(a.bar + cell) >= active) { ok = true; break; }
-                if (clock64() - start > 4000000000ll) break;      // about two seconds: report and carry on
+                if (clock64() - start > wait_limit(a.error_flag)) break;      // about two seconds by default: report and carry on
             }
             if (!ok) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
             __threadfence();

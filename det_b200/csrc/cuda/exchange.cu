@@ -69,6 +69,14 @@ void det_xchg_open_loopback(void* h) {
     for (int r = 0; r < x->size; r++) x->peer[r] = x->base;
     x->loopback = true;
 }
+// Test aid for the bounded wait (loopback handles only): the packets of column block `rank` are not sent from now on, so
+// a receiver's wait for them runs out; rank < 0 sends everything again.  Nothing faults or hangs: the wait gives up after
+// the wait limit, sets the error word and the kernel returns zeros for the missing packets.
+void det_debug_xchg_drop(void* h, int rank) {
+    Xchg* x = static_cast<Xchg*>(h);
+    DETB_REQUIRE(x->loopback, "det_debug_xchg_drop works on loopback handles only");
+    x->drop = rank;
+}
 // Largest exchange the staging takes, in gathered fp32 values (M * size * slice).
 size_t det_xchg_capacity(void* h) { return static_cast<Xchg*>(h)->slot_bytes / 8; }
 

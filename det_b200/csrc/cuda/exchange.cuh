@@ -19,6 +19,7 @@ struct Xchg {
     size_t slot_bytes = 0;
     int rank = 0, size = 1;
     bool loopback = false;        // timing aid: every "peer" is this rank's own staging (one process stands in for a rank of `size`)
+    int drop = -1;                // test aid (loopback only): packets of this rank's column block are never sent
     uint8_t* peer[XCHG_MAX_RANKS] = {};   // every rank's staging as seen from here (peer[rank] == base)
     unsigned* words = nullptr;    // device words: [0] exchanges completed so far, [1] CTAs of the running launch that have pushed
 };
@@ -26,7 +27,7 @@ struct Xchg {
 struct XchgArgs {
     const float* local;           // [M][slice]
     const float* local_b;         // optional: the pushed value is silu(local) * local_b (SwiGLU product of the local columns)
-    int M, slice, rank, size, loopback;
+    int M, slice, rank, size, loopback, drop;
     size_t slot_bytes;
     uint8_t* peer[XCHG_MAX_RANKS];
     unsigned* words;
@@ -37,7 +38,7 @@ inline XchgArgs xchg_args(const Xchg* x, const float* local, const float* local_
     XchgArgs a;
     a.local = local;
     a.local_b = local_b;
-    a.M = M; a.slice = slice; a.rank = x->rank; a.size = x->size; a.loopback = x->loopback;
+    a.M = M; a.slice = slice; a.rank = x->rank; a.size = x->size; a.loopback = x->loopback; a.drop = x->loopback ? x->drop : -1;
     a.slot_bytes = x->slot_bytes;
     for (int r = 0; r < XCHG_MAX_RANKS; r++) a.peer[r] = x->peer[r];
     a.words = x->words;
@@ -65,6 +66,7 @@ __device__ __forceinline__ void xchg_push(const XchgArgs& a, unsigned seq) {
         }
         const unsigned d0 = __float_as_uint(val.x), d1 = __float_as_uint(val.y);
         for (int p = 0; p < a.size; p++) {
+            if (p == a.drop) continue;
             const int col = a.loopback ? p : a.rank;
             uint8_t* dst = a.peer[p] + slot + (((size_t)t * a.size + col) * half + v) * 16;
             asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(d0), "r"(seq), "r"(d1), "r"(seq)
@@ -82,8 +84,8 @@ __device__ __forceinline__ void xchg_push(const XchgArgs& a, unsigned seq) {
 }
 
 // Values 2*pk and 2*pk+1 of the gathered data in this rank's staging slot (pk counts packets over [M][size*slice]).
-// Polls until the packet of this exchange has arrived; bounded (about two seconds, then the error word is set and zeros
-// come back; once the error word is set nothing spins again).
+// Polls until the packet of this exchange has arrived; bounded (wait_limit cycles, about two seconds by default; then
+// the error word is set and zeros come back; while the error word is set nothing spins again — det_clear_error resets it).
 __device__ __forceinline__ float2 xchg_read(const XchgArgs& a, unsigned seq, size_t pk) {
     const uint8_t* src = a.peer[a.rank] + (size_t)(seq & 1u) * a.slot_bytes + pk * 16;
     unsigned d0, f0, d1, f1;
@@ -93,7 +95,7 @@ __device__ __forceinline__ float2 xchg_read(const XchgArgs& a, unsigned seq, siz
         if (f0 == seq && f1 == seq) break;
         if ((spins & 63u) == 63u) {
             if (start == 0) start = clock64();
-            if (*reinterpret_cast<volatile int*>(a.error_flag) != 0 || clock64() - start > 4000000000ll) {
+            if (*reinterpret_cast<volatile int*>(a.error_flag) != 0 || clock64() - start > wait_limit(a.error_flag)) {
                 atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
                 d0 = d1 = 0;
                 break;

@@ -74,16 +74,16 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
         : "memory");
     return ok != 0;
 }
-// Bounded wait: polls until the phase completes or about two seconds of SM clock have passed; returns false then.
-constexpr long long WAIT_CYCLES = 4000000000ll;
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+// Bounded wait: polls until the phase completes or `limit` SM clock cycles have passed (wait_limit(error_flag): about two
+// seconds by default); returns false then.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 256; i++)
             if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - start > WAIT_CYCLES) return false;
+        if (clock64() - start > limit) return false;
     }
 }
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, unsigned bytes, unsigned long long* bar) {

@@ -148,6 +148,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.x * TC_TOK, n0 = blockIdx.y * TC_ROWS;
     const int G = a.G;
+    const long long wl = wait_limit(a.error_flag);
     // this CTA's run of groups: [g0, g0 + GL)
     const int gper = (G + gridDim.z - 1) / gridDim.z;
     const int g0 = blockIdx.z * gper;
@@ -193,7 +194,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             int issued = lead;
             for (int l = lead; l < GL; l++, issued++) {
                 const int s = l % TC_STAGES;
-                ok = mbar_wait(&empty[s], ((unsigned)(l / TC_STAGES) & 1u) ^ 1u);
+                ok = mbar_wait(&empty[s], ((unsigned)(l / TC_STAGES) & 1u) ^ 1u, wl);
                 if (!ok) break;
                 uint8_t* st = stages + (size_t)s * TC_STAGE_BYTES;
                 mbar_expect_tx(&full[s], TC_STAGE_BYTES);
@@ -204,7 +205,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
                 for (int k = 0; k < TC_STAGES && k < issued; k++) {
                     const int i = issued - 1 - k;
-                    (void)mbar_wait(&full[i % TC_STAGES], (unsigned)(i / TC_STAGES) & 1u);
+                    (void)mbar_wait(&full[i % TC_STAGES], (unsigned)(i / TC_STAGES) & 1u, wl);
                 }
             }
         }
@@ -213,8 +214,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         if (lane == 0) {
             for (int g = 0; g < GL; g++) {          // local group index
                 const int s = g % TC_STAGES, b = g % NBUF;
-                ok = mbar_wait(&full[s], (unsigned)(g / TC_STAGES) & 1u) &&
-                     mbar_wait(&tempty[b], ((unsigned)(g / NBUF) & 1u) ^ 1u);
+                ok = mbar_wait(&full[s], (unsigned)(g / TC_STAGES) & 1u, wl) &&
+                     mbar_wait(&tempty[b], ((unsigned)(g / NBUF) & 1u) ^ 1u, wl);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint8_t* st = stages + (size_t)s * TC_STAGE_BYTES;
@@ -252,7 +253,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             const int b = l % NBUF, g = g0 + l;
             const unsigned mw = mw_next;
             if (l + 1 < GL) mw_next = mrow[g + 1];
-            ok = mbar_wait(&tfull[b], (unsigned)(l / NBUF) & 1u);
+            ok = mbar_wait(&tfull[b], (unsigned)(l / NBUF) & 1u, wl);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             int r[EC];
@@ -322,6 +323,7 @@ __global__ void __launch_bounds__(64, 1) k_umma_peak(int iters, int* error_flag)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long wl = wait_limit(error_flag);
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)), "r"(256) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -339,7 +341,7 @@ __global__ void __launch_bounds__(64, 1) k_umma_peak(int iters, int* error_flag)
             for (int k = 0; k < 4; k++) umma_i8(tmem, da + 2 * k, db + 2 * k, IDESC, (i | k) ? 1u : 0u);
         }
         umma_commit(bar);
-        if (!mbar_wait(bar, 0)) atomicExch(error_flag, DETB_ERR_WAIT_EXPIRED);
+        if (!mbar_wait(bar, 0, wl)) atomicExch(error_flag, DETB_ERR_WAIT_EXPIRED);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();

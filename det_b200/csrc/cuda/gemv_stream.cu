@@ -303,6 +303,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
     float* sxs = wmax + NCW;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const long long wl = wait_limit(a.error_flag);
     pdl_trigger();
     if (tid == 0) {
         for (int s = 0; s < a.slots; s++) {
@@ -320,7 +321,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
             int issued = 0;
             for (int rec = blockIdx.x; rec < g.nrec; rec += gridDim.x, issued++) {
                 const int s = issued % a.slots;
-                ok = mbar_wait(&empty[s], ((unsigned)(issued / a.slots) & 1u) ^ 1u);
+                ok = mbar_wait(&empty[s], ((unsigned)(issued / a.slots) & 1u) ^ 1u, wl);
                 if (!ok) break;
                 mbar_expect_tx(&full[s], (unsigned)g.rec_bytes);
                 bulk_g2s(ring + (size_t)s * g.rec_bytes, a.w + (size_t)rec * g.rec_bytes, (unsigned)g.rec_bytes, &full[s]);
@@ -330,7 +331,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
                 // copies already issued still target this CTA's shared memory: wait (bounded) for each to land
                 for (int k = 0; k < a.slots && k < issued; k++) {
                     const int i = issued - 1 - k;
-                    (void)mbar_wait(&full[i % a.slots], (unsigned)(i / a.slots) & 1u);
+                    (void)mbar_wait(&full[i % a.slots], (unsigned)(i / a.slots) & 1u, wl);
                 }
             }
         }
@@ -386,7 +387,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
         const int rec_id = blockIdx.x + i * gridDim.x;   // i-th record of this CTA
         if (rec_id >= g.nrec) break;
         const int s = i % a.slots;
-        ok = mbar_wait(&full[s], (unsigned)(i / a.slots) & 1u);
+        ok = mbar_wait(&full[s], (unsigned)(i / a.slots) & 1u, wl);
         if (!ok) break;
         const uint8_t* rec = ring + (size_t)s * g.rec_bytes;
         const uint8_t* wp = rec + (size_t)r * g.row_bytes + j * 16;

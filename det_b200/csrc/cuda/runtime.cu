@@ -46,8 +46,10 @@ void bring_up() {
     rt->sm_count = prop.multiProcessorCount;
     rt->smem_optin = prop.sharedMemPerBlockOptin;
     if (cudaStreamCreateWithFlags(&rt->queue, cudaStreamNonBlocking) != cudaSuccess) { delete rt; return; }
-    if (cudaMalloc(&rt->error_word, sizeof(int)) != cudaSuccess) { delete rt; return; }
-    if (cudaMemset(rt->error_word, 0, sizeof(int)) != cudaSuccess) { delete rt; return; }
+    if (cudaMalloc(&rt->error_word, 4 * sizeof(int)) != cudaSuccess) { delete rt; return; }
+    if (cudaMemset(rt->error_word, 0, 4 * sizeof(int)) != cudaSuccess) { delete rt; return; }
+    const long long limit = DEFAULT_WAIT_CYCLES;
+    if (cudaMemcpy(rt->error_word + 2, &limit, sizeof limit, cudaMemcpyHostToDevice) != cudaSuccess) { delete rt; return; }
     g_rt = rt;
 }
 }  // namespace
@@ -147,6 +149,20 @@ int det_last_error(void) {
     DETB_CUDA_OK(cudaDeviceSynchronize());
     DETB_CUDA_OK(cudaMemcpy(&code, g_rt->error_word, sizeof(int), cudaMemcpyDeviceToHost));
     return code;
+}
+
+// Clears the error word after the caller has dealt with the error (waits for pending work first).
+void det_clear_error(void) {
+    if (!runtime_ready()) return;
+    DETB_CUDA_OK(cudaDeviceSynchronize());
+    DETB_CUDA_OK(cudaMemset(g_rt->error_word, 0, sizeof(int)));
+}
+// Limit of every bounded device-side wait, in SM clock cycles; <= 0 restores the default (about two seconds).
+void det_debug_set_wait_limit(long long cycles) {
+    if (!runtime_ready()) return;
+    const long long limit = cycles > 0 ? cycles : DEFAULT_WAIT_CYCLES;
+    DETB_CUDA_OK(cudaDeviceSynchronize());
+    DETB_CUDA_OK(cudaMemcpy(g_rt->error_word + 2, &limit, sizeof limit, cudaMemcpyHostToDevice));
 }
 
 void* det_malloc(size_t bytes) {

@@ -9,14 +9,23 @@ bool runtime_is_up();   // true once det_init (or any earlier call) has brought 
 cudaStream_t queue_of(cudaStream_t st);   // maps the ABI's stream 0 onto the library's queue
 int sm_count();
 size_t smem_optin();
-int* error_word();   // device word that bounded waits report into
+// Device words that bounded waits use: [0] the error code they report into, [2..3] (one 64-bit word) the wait limit in
+// SM clock cycles (about two seconds unless det_debug_set_wait_limit changed it).
+int* error_word();
+constexpr long long DEFAULT_WAIT_CYCLES = 4000000000ll;
+#ifdef __CUDACC__
+__device__ __forceinline__ long long wait_limit(const int* error_flag) {
+    return *reinterpret_cast<const volatile long long*>(error_flag + 2);
+}
+#endif
 
 bool pdl_enabled();
 
-// Launches `kernel` on `q` with the programmatic-dependent-launch attribute (and an optional cluster width).
+// Launches `kernel` on `q` with the programmatic-dependent-launch attribute (and an optional cluster width) and returns
+// the runtime's verdict on the launch.
 template <class... KArgs, class... Args>
-inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t q, int cluster_x,
-                       Args&&... args) {
+inline cudaError_t launch_pdl_try(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t q,
+                                  int cluster_x, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -38,7 +47,13 @@ inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    DETB_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+// Same; a failed launch is fatal (the reference's error convention, kernels/cuda/common.cuh:8-9).
+template <class... KArgs, class... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t q, int cluster_x,
+                       Args&&... args) {
+    DETB_CUDA_OK(launch_pdl_try(kernel, grid, block, smem, q, cluster_x, static_cast<Args&&>(args)...));
 }
 
 // Error codes reported by det_last_error().

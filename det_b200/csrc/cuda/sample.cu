@@ -491,15 +491,18 @@ static cudaError_t launch_topkp(const float* logits, int M, int V, float inv_tem
                                 const u64* z, int* out, u64* wbuf, cudaStream_t q) {
     if (V <= SCL * SEL_RANGE) {
         const int cl = V > SEL_RANGE ? SCL : 1;
-        static bool attr = false;
-        if (!attr) {
-            const cudaError_t e = cudaFuncSetAttribute(k_sample_topkp_sel, cudaFuncAttributeMaxDynamicSharedMemorySize, SEL_SMEM);
+        // the opt-in shared-memory size is a per-device property of the function: set it once on every device used
+        static bool attr[64] = {};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= 64 || !attr[dev]) {
+            e = cudaFuncSetAttribute(k_sample_topkp_sel, cudaFuncAttributeMaxDynamicSharedMemorySize, SEL_SMEM);
             if (e != cudaSuccess) return e;
-            attr = true;
+            if (dev >= 0 && dev < 64) attr[dev] = true;
         }
-        launch_pdl(k_sample_topkp_sel, dim3(cl, M), dim3(ST), SEL_SMEM, q, cl, logits, V, inv_temp, use_k, top_k, use_p, p24,
-                   z, out, wbuf);
-        return cudaSuccess;
+        return launch_pdl_try(k_sample_topkp_sel, dim3(cl, M), dim3(ST), SEL_SMEM, q, cl, logits, V, inv_temp, use_k, top_k,
+                              use_p, p24, z, out, wbuf);
     }
     k_sample_topkp<<<M, ST, 0, q>>>(logits, V, inv_temp, use_k, top_k, use_p, p24, z, out, wbuf);
     return cudaGetLastError();
@@ -542,23 +545,32 @@ void det_sample_topkp(const float* logits, int M, int V, float inv_temp, int top
 
 // Top-k / top-p sampling for callers that must not allocate.  Same result as det_sample_topkp, but the weight buffer is
 // a fixed array inside the library image instead of a caller-provided scratch, and the call itself never reaches an
-// allocator: no cudaMalloc, no cudaFree, nothing that allocates behind the scenes.  That is for hosts that fix their
-// device-memory budget at start-up and ban allocation afterwards (an allocation can stall on the driver lock or fail
-// once the KV cache owns the rest of HBM), and for plug-ins that only ever receive pointers and own no allocator.
+// allocator: no cudaMalloc, no cudaFree, no allocating library routine.  That is for hosts that fix their device-memory
+// budget at start-up and ban allocation afterwards (an allocation can stall on the driver lock or fail once the KV cache
+// owns the rest of HBM), and for plug-ins that only ever receive pointers and own no allocator.
 //
 // Limits and rules:
-//   * M * V <= 524288 weights (4 MiB; one row of a 248320-token vocabulary fits twice over).  Larger requests are
-//     refused: the function prints the reason, launches nothing and returns 1.  0 means the work was queued.
+//   * M * V <= 524288 weights (4 MiB; one row of a 248320-token vocabulary fits twice over) whenever a top-k or top-p
+//     filter is active.  Larger filtered requests are refused: the function prints the reason, launches nothing and
+//     returns 1.  A request without an active filter (top_k <= 0 or >= V, top_p >= 1) needs no scratch and is taken at
+//     any size.  0 means the work was queued; a launch the runtime rejects also returns 1 (it never aborts).
 //   * det_init() must have succeeded earlier (this call does not bring the runtime up, since that allocates).
-//   * The first call on a device looks the array's device address up (cudaGetSymbolAddress, with that device current)
-//     and keeps it; make that first call outside any stream capture.
+//   * The first call on a device looks the array's device address up (cudaGetSymbolAddress, with that device current),
+//     which is also when the driver loads the module that holds the array; make that first call at start-up, outside any
+//     stream capture.
 //   * Every call uses the same array and finds the previous call's weights in it.  Nothing has to be cleared: the kernel
 //     writes every weight of its rows before it reads any.  Two calls that overlap on the GPU (different streams) race
 //     on the array; keep them on one stream or order them yourself.
 int det_sample_topkp_static(const float* logits, int M, int V, float inv_temp, int top_k, float top_p,
                             const unsigned long long* z, int* out, cudaStream_t st) {
     if (M <= 0) return 0;
-    if (V <= 0 || (long long)M * V > STATIC_SAMPLE_MAX) {
+    if (V <= 0) {
+        fprintf(stderr, "det_b200: det_sample_topkp_static: V = %d is not a vocabulary size\n", V);
+        return 1;
+    }
+    const int use_k = top_k > 0 && top_k < V;
+    const int use_p = top_p < 1.0f;
+    if ((use_k || use_p) && (long long)M * V > STATIC_SAMPLE_MAX) {
         fprintf(stderr, "det_b200: det_sample_topkp_static: M * V = %lld exceeds the built-in scratch of %lld weights\n",
                 (long long)M * V, STATIC_SAMPLE_MAX);
         return 1;
@@ -583,8 +595,6 @@ int det_sample_topkp_static(const float* logits, int M, int V, float inv_temp, i
         }
         addr[dev] = static_cast<unsigned long long*>(p);
     }
-    const int use_k = top_k > 0 && top_k < V;
-    const int use_p = top_p < 1.0f;
     if (!use_k && !use_p) {
         k_sample_plain<<<M, ST, 0, queue_of(st)>>>(logits, V, inv_temp, z, out);
     } else {

@@ -58,6 +58,16 @@ std::string BatchDecoder::prefill(size_t i, const int32_t* ids, size_t n, const 
     Sequence& s = seqs[i];
     s.sampling = sampling;
     s.out.clear();
+    // a slot that served an earlier conversation starts over: position 0 and zeroed recurrent state, as Model::reset
+    // does (model.rs:378-387); cache rows need no clearing, positions >= pos are never read
+    if (s.pos != 0) {
+        m_.backend->sync();
+        s.pos = 0;
+        for (GdnState& st : s.st) {
+            m_.backend->zero(st.conv_state);
+            m_.backend->zero(st.s);
+        }
+    }
     const size_t max_ctx = m_.max_ctx;
     m_.max_ctx = ctx_;
     m_.all_logits = false;   // last-row logits into the first row of the (rows x vocab) buffer

@@ -257,11 +257,14 @@ void det_xchg_add_rmsnorm_quant(void* h, const float* local, int slice, float* x
 void det_xchg_quant(void* h, const float* local, const float* local_b, int slice, int M, int8_t* xq, float* sx,
                     uint16_t* mx, cudaStream_t st);
 
-/* No counterpart in the reference.  det_sample_topkp for callers that may not allocate device memory: the weight
- * scratch is a fixed 4 MiB array inside the library (M * V <= 524288), so no scratch argument and no allocation of any
- * kind inside the call.  Returns 0 when the work was queued, 1 when the request was refused (too large, or det_init was
- * never called); a refusal prints its reason and launches nothing.  The first call on a device resolves the array's
- * address and should be made outside stream capture; calls share the array, so calls that overlap on the GPU race.     */
+/* No counterpart in the reference.  det_sample_topkp for callers that may not allocate device memory (hosts that fix
+ * their memory budget at start-up, plug-ins that are only handed pointers): the weight scratch is a fixed 4 MiB array
+ * inside the library, so there is no scratch argument and no allocation of any kind inside the call.  Limit: M * V <=
+ * 524288 whenever top-k or top-p is active; a request without an active filter needs no scratch and is taken at any size.
+ * Returns 0 when the work was queued, 1 when the request was refused (too large, V <= 0, det_init never called) or the
+ * launch was rejected; a refusal prints its reason and launches nothing; the call never aborts.  The first call on a
+ * device resolves the array's address (and makes the driver load the module holding it): make it at start-up, outside
+ * stream capture.  Calls share the array, so calls that overlap on the GPU race.                                       */
 int det_sample_topkp_static(const float* logits, int M, int V, float inv_temp, int top_k, float top_p,
                             const unsigned long long* z, int* out, cudaStream_t st);
 
@@ -282,9 +285,19 @@ void det_debug_set_tc_variant(int v);
  * every SM, no loads and no epilogue; returns the measured int8 rate in TOPS.                                         */
 double det_debug_umma_peak(int iters);
 
-/* Last error recorded by a bounded device-side wait (0 = none; see the DETB_ERR_* codes in csrc/cuda/runtime.cuh).
- * Waits for pending work.                                                                                            */
+/* Last error recorded by a bounded device-side wait (0 = none, 1 = a wait ran out, 2 = a size check failed on the
+ * device).  Waits for pending work.  While the word is set, exchange waits return at once (with zeros) instead of
+ * polling, so a caller that has dealt with the error clears it with det_clear_error before it carries on.  Ranks of a
+ * tensor-parallel group must pass a host barrier before their first exchange (a start-up skew longer than the wait limit
+ * would otherwise expire the first wait).                                                                            */
 int det_last_error(void);
+void det_clear_error(void);
+/* Limit of every bounded device-side wait (mbarrier waits of the GEMM kernels, packet polls of the exchange, the counter
+ * of the fused decode attention) in SM clock cycles; <= 0 restores the default of 4e9 (about two seconds).  With
+ * det_debug_xchg_drop — loopback exchange handles only: column block `rank` is no longer sent, rank < 0 undoes it — a
+ * test can make a wait run out without faulting or hanging anything.                                                  */
+void det_debug_set_wait_limit(long long cycles);
+void det_debug_xchg_drop(void* h, int rank);
 
 #ifdef __cplusplus
 }

@@ -5,6 +5,7 @@
 #include "../det_b200/csrc/host/conformance.hpp"
 #include <cstdio>
 #include <string>
+#include <omp.h>
 
 namespace oracle {
 
@@ -63,6 +64,9 @@ void* orc_cpu_backend_new() {
 }
 // 2: AVX-VNNI path, 1: AVX2 path, 0: no SIMD (the baseline then falls back to the scalar spec)
 int orc_cpu_simd_level() { return x86gemm::have_vnni() ? 2 : x86gemm::have_avx2() ? 1 : 0; }
+// Thread count of the OpenMP loops (a launcher may have exported OMP_NUM_THREADS=1: the timed baseline sets its own).
+void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int orc_max_threads() { return omp_get_max_threads(); }
 void orc_ref_backend_free(void* b) { delete static_cast<det::Backend*>(b); }
 
 // Element-wise spec primitives on host arrays (the oracle side of the det_test_prim comparison).

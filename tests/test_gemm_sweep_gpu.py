@@ -80,3 +80,78 @@ def test_gemm_matches_oracle(n, k, bits, ms, libs, oracle):
     finally:
         for p in (wq, cc, mm, sp, w8):
             d.det_free(p)
+
+
+def _upload(d, arr):
+    p = d.det_malloc(arr.nbytes)
+    d.det_memcpy(p, arr.ctypes.data, arr.nbytes, None)
+    return p
+
+
+@pytest.mark.parametrize("n,k,bits,ms", [
+    (17408, 5120, 6, [64, 512, 2048]),
+    (17408, 5120, 8, [512]),
+    (17408, 5120, 4, [512]),
+    (5120, 17408, 6, [64, 512]),
+])
+def test_large_batch_gemm_matches_oracle(n, k, bits, ms, libs, oracle):
+    """The prefill sizes of the GEMM sweep (M = 64, 512, 2048 at K=5120 x N=17408, W6 / W8 / W4, and the transposed FFN
+    shape): every tile instantiation of the tensor-core kernel against spec gemm_row.  gemm_row over all M * N outputs
+    would take minutes of scalar CPU time, so the oracle computes complete 128-row tiles — the first, the last and three
+    seeded ones, every token — and the remaining rows are compared with this backend's row-major CUDA-core kernel, a
+    different kernel that the small-M test above pins to gemm_row on its own."""
+    d = libs.cuda()
+    rng = np.random.default_rng(7 * n + k + bits)
+    rows, c, m, nc = _det_rows(rng, n, k, bits)
+    g = k // 128
+    codes = np.ascontiguousarray(rows[:, :nc])
+    wq, cc, mm = _upload(d, codes), _upload(d, c), _upload(d, m)
+    src = libs.QLinear(wq, cc, mm, n, k, bits)
+    w8 = d.det_malloc(d.det_linear_expand_bytes(n, k))
+    d.det_linear_expand(C.byref(src), w8, None)
+    tensor = libs.QLinear(w8, cc, mm, n, k, bits | libs.DET_LAYOUT_INT8)
+    tiles = sorted({0, n // 128 - 1, *(int(x) for x in rng.integers(1, n // 128 - 1, 3))})
+    pick = np.concatenate([np.arange(t * 128, t * 128 + 128) for t in tiles])
+    sub = np.ascontiguousarray(rows[pick])
+    try:
+        for mtok in ms:
+            xq = rng.integers(-127, 128, (mtok, k)).astype(np.int8)
+            sx = (1e-3 * (0.5 + rng.random(mtok))).astype(np.float32)
+            mx = rng.integers(1, 65536, (mtok, g)).astype(np.uint16)
+            want = np.zeros((mtok, len(pick)), np.float32)
+            oracle.orc_gemm(sub.ctypes.data, len(pick), k, bits, xq.ctypes.data, sx.ctypes.data, mx.ctypes.data, mtok,
+                            want.ctypes.data, 0)
+            dx, ds, dm = _upload(d, xq), _upload(d, sx), _upload(d, mx)
+            dy = d.det_malloc(mtok * n * 4)
+            base = np.zeros((mtok, n), np.float32)
+            d.det_gemm(C.byref(src), dx, ds, dm, mtok, dy, None)
+            d.det_memcpy(base.ctypes.data, dy, base.nbytes, None)
+            d.det_sync()
+            bad = int((base[:, pick].view(np.uint32) != want.view(np.uint32)).sum())
+            assert bad == 0, f"row-major kernel, M={mtok}: {bad} of {want.size} outputs differ from gemm_row"
+            for variant in libs.TC_VARIANTS_LARGE:
+                got = np.zeros_like(base)
+                d.det_memset(dy, 0xFF, base.nbytes, None)
+                d.det_debug_set_tc_variant(variant)
+                d.det_gemm(C.byref(tensor), dx, ds, dm, mtok, dy, None)
+                d.det_debug_set_tc_variant(0x200)
+                d.det_memcpy(got.ctypes.data, dy, got.nbytes, None)
+                d.det_sync()
+                bad = int((got[:, pick].view(np.uint32) != want.view(np.uint32)).sum())
+                assert bad == 0, f"tensor-core variant {variant:#x}, M={mtok}: {bad} of {want.size} outputs differ from gemm_row"
+                bad = int((got.view(np.uint32) != base.view(np.uint32)).sum())
+                assert bad == 0, f"tensor-core variant {variant:#x}, M={mtok}: {bad} of {base.size} outputs differ from the row-major kernel"
+            # accumulate form on the tile the shape selects: y += result is one fp32 add per element
+            prev = (rng.random((mtok, n), dtype=np.float32) - 0.5).astype(np.float32)
+            d.det_memcpy(dy, prev.ctypes.data, prev.nbytes, None)
+            d.det_gemm_ex(C.byref(tensor), dx, ds, dm, mtok, dy, 1, 0, None, None, None)
+            got = np.zeros_like(base)
+            d.det_memcpy(got.ctypes.data, dy, got.nbytes, None)
+            d.det_sync()
+            assert np.array_equal(got.view(np.uint32), (prev + base).view(np.uint32)), f"accumulate, M={mtok}"
+            for p in (dx, ds, dm, dy):
+                d.det_free(p)
+        assert d.det_last_error() == 0
+    finally:
+        for p in (wq, cc, mm, w8):
+            d.det_free(p)

@@ -84,3 +84,33 @@ def test_mixed_sampling_parameters_per_sequence(libs, ref_backend):
         assert np.array_equal(out, solo[i]), (i, out, solo[i])
     h.dh_batch_free(batch)
     h.dh_model_free(model)
+
+
+def test_prefilling_a_slot_again_starts_a_fresh_conversation(libs, ref_backend):
+    """A slot that is prefilled a second time must forget its first conversation (position, recurrent state): the second
+    stream equals the stream of a decoder that only ever saw the second prompt."""
+    h = libs.host()
+    n_new, ctx = 5, 64
+    model = h.dh_model_new_synth(ref_backend, b"tiny", 4, SEED, ctx, 16)
+    assert model, h.dh_last_error()
+    first, second = _prompt(h, 300, 21), _prompt(h, 301, 12)
+
+    def stream(prompts):
+        batch = h.dh_batch_new(model, 2, ctx)
+        assert batch, h.dh_last_error()
+        other = _prompt(h, 302, 7)
+        assert h.dh_batch_prefill(batch, 1, other.ctypes.data, len(other), 0, 1.0 / 0.7, 40, 0.95, 5) == 0
+        for ids in prompts:
+            assert h.dh_batch_prefill(batch, 0, ids.ctypes.data, len(ids), 0, 1.0 / 0.7, 40, 0.95, 4242) == 0, h.dh_last_error()
+            if ids is not prompts[-1]:
+                assert h.dh_batch_step(batch, 3) == 0, h.dh_last_error()
+                assert h.dh_batch_prefill(batch, 1, other.ctypes.data, len(other), 0, 1.0 / 0.7, 40, 0.95, 5) == 0
+        assert h.dh_batch_step(batch, n_new - 1) == 0, h.dh_last_error()
+        out = np.zeros(n_new, np.int32)
+        assert h.dh_batch_tokens(batch, 0, out.ctypes.data, n_new) == n_new
+        h.dh_batch_free(batch)
+        return out
+
+    again, fresh = stream([first, second]), stream([second])
+    h.dh_model_free(model)
+    assert np.array_equal(again, fresh), (again, fresh)
