@@ -1,7 +1,7 @@
 // TEST INFRASTRUCTURE — not part of the product.  C entry points (ctypes) onto the CPU oracle: the reference backend as a
 // det::Backend object, the spec primitives under the test hook's op numbers, and a runner that feeds both a reference
 // backend and a backend under test to the driver library's conformance suites.
-#include "ref_backend.hpp"
+#include "x86_backend.hpp"
 #include "../det_b200/csrc/host/conformance.hpp"
 #include <cstdio>
 #include <string>
@@ -56,14 +56,27 @@ typedef void (*prim_hook_fn)(int op, const float* x, size_t len, size_t m, size_
 extern "C" {
 
 void* orc_ref_backend_new() { return static_cast<det::Backend*>(new oracle::RefBackend()); }
-// The timed CPU baseline: the same backend with the restated x86 integer GEMM (x86_gemm.hpp) for the linears.
-void* orc_cpu_backend_new() {
-    auto* b = new oracle::RefBackend();
-    b->simd = true;
-    return static_cast<det::Backend*>(b);
+// The timed CPU baseline and large-model parity reference: the restated x86 backend (x86_backend.hpp).  vnni: 1 = the
+// AVX-VNNI build, 0 = the plain AVX2 build, -1 = whichever this CPU has.  NULL when the CPU lacks the instructions.
+void* orc_cpu_backend_new(int vnni) {
+#if defined(__x86_64__)
+    try {
+        const bool v = vnni < 0 ? x86port::have_vnni() : vnni != 0;
+        return static_cast<det::Backend*>(new oracle::X86Backend(v));
+    } catch (const std::exception& e) {
+        fprintf(stderr, "oracle: %s\n", e.what());
+    }
+#endif
+    return nullptr;
 }
-// 2: AVX-VNNI path, 1: AVX2 path, 0: no SIMD (the baseline then falls back to the scalar spec)
-int orc_cpu_simd_level() { return x86gemm::have_vnni() ? 2 : x86gemm::have_avx2() ? 1 : 0; }
+// 2: AVX-VNNI available, 1: AVX2 only, 0: neither (no x86 port on this host)
+int orc_cpu_simd_level() {
+#if defined(__x86_64__)
+    return x86port::have_vnni() ? 2 : x86port::have_avx2() ? 1 : 0;
+#else
+    return 0;
+#endif
+}
 // Thread count of the OpenMP loops (a launcher may have exported OMP_NUM_THREADS=1: the timed baseline sets its own).
 void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
 int orc_max_threads() { return omp_get_max_threads(); }
@@ -136,20 +149,23 @@ void orc_gemm(const uint8_t* rows, size_t n, size_t k, int bits, const int8_t* x
     float* dsts[1] = {y};
     refops::gemm(l, xq, sx, mx, m, accumulate ? refops::Out::Accumulate : refops::Out::Write, dsts);
 }
-// The restated x86 kernel on det rows (expanded here), for the check against gemm_row.
+// The restated x86 GEMM (strip repack + blocked kernel) on det rows, for the check against gemm_row.
 void orc_gemm_x86(const uint8_t* rows, size_t n, size_t k, int bits, const int8_t* xq, const float* sx, const uint16_t* mx,
-                  size_t m, float* y) {
-    const size_t g = k / spec::GROUP, rb = spec::det_row_bytes(bits, k);
-    std::vector<int8_t> w8(n * k);
-    std::vector<float> c(n);
-    std::vector<uint16_t> mm(n * g);
-    for (size_t j = 0; j < n; j++) {
-        const spec::DetRow r = spec::det_row(bits, k, rows + j * rb);
-        spec::unpack_row(r.codes, bits, k, w8.data() + j * k);
-        c[j] = r.c;
-        for (size_t gi = 0; gi < g; gi++) mm[j * g + gi] = r.m(gi);
-    }
-    x86gemm::gemm(w8.data(), c.data(), mm.data(), n, k, xq, sx, mx, m, y);
+                  size_t m, float* y, int vnni) {
+#if defined(__x86_64__)
+    refops::Linear l;
+    l.parts = {rows};
+    l.widths = {n};
+    l.k = k;
+    l.bits = bits;
+    x86port::StripLinear strips;
+    x86port::repack(l, strips);
+    float* dsts[1] = {y};
+    if (vnni) x86vnni::gemm(strips, xq, sx, mx, m, refops::Out::Write, dsts, l.widths);
+    else x86avx2::gemm(strips, xq, sx, mx, m, refops::Out::Write, dsts, l.widths);
+#else
+    (void)rows; (void)n; (void)k; (void)bits; (void)xq; (void)sx; (void)mx; (void)m; (void)y; (void)vnni;
+#endif
 }
 void orc_unpack_row(const uint8_t* packed, int bits, size_t k, int8_t* out) { spec::unpack_row(packed, bits, k, out); }
 float orc_treesum(const float* x, size_t n) { return spec::treesum(x, n); }

@@ -4,26 +4,18 @@
 #pragma once
 #include "../det_b200/csrc/host/backend.hpp"
 #include "ref_ops.hpp"
+#include <omp.h>
 
 namespace oracle {
 
 struct RefLinear : det::Linear {
     std::vector<std::vector<uint8_t>> rows;   // owned copies of the det rows, one per fused part
     refops::Linear view;
-    // expanded copy for the SIMD baseline GEMM (only when RefBackend::simd is set)
-    std::vector<int8_t> w8;
-    std::vector<float> c8;
-    std::vector<uint16_t> m8;
 };
 
 class RefBackend : public det::Backend {
   public:
-    // simd: linears also keep an expanded copy and gemm runs the restated x86 backend kernel (x86_gemm.hpp) — the timed CPU
-    // baseline.  Off: every op is the scalar spec (the parity checker).
-    bool simd = false;
-    std::string name() const override {
-        return simd ? "ref with the restated x86 integer GEMM (crates/det/src/x86/gemm.rs)" : "ref (restated crates/det/src/cpu.rs)";
-    }
+    std::string name() const override { return "ref (restated crates/det/src/cpu.rs)"; }
     void* alloc_bytes(size_t bytes) override { return std::calloc(bytes ? bytes : 1, 1); }
     void free_bytes(void* p) override { std::free(p); }
     void write_bytes(void* dst, const void* src, size_t bytes) override { std::memcpy(dst, src, bytes); }
@@ -44,22 +36,6 @@ class RefBackend : public det::Backend {
             l->view.widths.push_back(p.n);
         }
         for (auto& r : l->rows) l->view.parts.push_back(r.data());
-        if (simd && x86gemm::have_avx2()) {
-            const size_t n = l->n(), g = k / spec::GROUP;
-            l->w8.resize(n * k);
-            l->c8.resize(n);
-            l->m8.resize(n * g);
-#pragma omp parallel for schedule(static)
-            for (long j = 0; j < (long)n; j++) {
-                const spec::DetRow r = spec::det_row(bits, k, l->view.row(j));
-                spec::unpack_row(r.codes, bits, k, l->w8.data() + (size_t)j * k);
-                l->c8[j] = r.c;
-                for (size_t gi = 0; gi < g; gi++) l->m8[(size_t)j * g + gi] = r.m(gi);
-            }
-            l->view.w8 = l->w8.data();
-            l->view.c8 = l->c8.data();
-            l->view.m8 = l->m8.data();
-        }
         return l;
     }
 

@@ -3,7 +3,6 @@
 // rows, heads or output columns, which cannot change a result (cpu.rs:1-3).
 #pragma once
 #include "spec.hpp"
-#include "x86_gemm.hpp"
 
 namespace refops {
 
@@ -13,10 +12,6 @@ struct Linear {
     std::vector<size_t> widths;
     size_t k = 0;
     int bits = 0;
-    // optional expanded copy for the SIMD baseline path (x86_gemm.hpp): signed codes [n][k], c[n], m[n][k/128]
-    const int8_t* w8 = nullptr;
-    const float* c8 = nullptr;
-    const uint16_t* m8 = nullptr;
     size_t n() const {
         size_t s = 0;
         for (size_t w : widths) s += w;
@@ -57,9 +52,6 @@ inline void gemm(const Linear& lin, const int8_t* xq, const float* sx, const uin
                  float* const* dsts /* Write/Accumulate: dsts[0] */, const std::vector<size_t>* out_widths = nullptr) {
     const size_t k = lin.k, n = lin.n(), g = k / spec::GROUP;
     std::vector<float> y(m * n);
-    if (lin.w8) {
-        x86gemm::gemm(lin.w8, lin.c8, lin.m8, n, k, xq, sx, mx, m, y.data());
-    } else {
 #pragma omp parallel for schedule(static)
     for (long j = 0; j < (long)n; j++) {
         spec::DetRow r = spec::det_row(lin.bits, k, lin.row(j));
@@ -69,7 +61,6 @@ inline void gemm(const Linear& lin, const int8_t* xq, const float* sx, const uin
         for (size_t gi = 0; gi < g; gi++) mrow[gi] = r.m(gi);
         for (size_t t = 0; t < m; t++)
             y[t * n + j] = spec::gemm_row(wq.data(), r.c, mrow.data(), xq + t * k, sx[t], mx ? mx + t * g : nullptr, k);
-    }
     }
     for (size_t t = 0; t < m; t++) {
         const float* yt = y.data() + t * n;

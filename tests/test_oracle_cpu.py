@@ -105,15 +105,18 @@ def test_sampler_properties(oracle):
 
 
 def test_restated_x86_gemm_equals_gemm_row(oracle):
-    """The SIMD integer GEMM behind the timed CPU baseline (oracle/x86_gemm.hpp, the restated crates/det/src/x86/gemm.rs
-    arithmetic) against the scalar spec gemm_row, on every weight width, extreme codes and ragged token counts."""
+    """The strip-repacked, K-blocked integer GEMM of the timed CPU baseline (oracle/x86_backend.hpp, the restated
+    crates/det/src/x86/gemm.rs) against the scalar spec gemm_row, on both dot-product paths, every weight width, extreme
+    codes, ragged row counts (a partial strip pair) and token counts on both sides of the 4-token tile and the 64-token
+    chunk."""
     import ctypes as C
     if oracle.orc_cpu_simd_level() == 0:
         pytest.skip("no AVX2 on this host")
     oracle.orc_gemm_x86.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
-                                    C.c_size_t, C.c_void_p]
+                                    C.c_size_t, C.c_void_p, C.c_int]
     rng = np.random.default_rng(5)
-    for bits, n, k, m in [(6, 96, 1024, 3), (8, 40, 512, 1), (4, 64, 2560, 5), (6, 33, 128, 2)]:
+    paths = [0, 1] if oracle.orc_cpu_simd_level() == 2 else [0]
+    for bits, n, k, m in [(6, 96, 1024, 3), (8, 40, 512, 1), (4, 64, 2560, 5), (6, 33, 128, 2), (6, 50, 2560, 70), (8, 17, 1152, 9)]:
         per32 = {8: 32, 6: 24, 4: 16}[bits]
         g = k // 128
         nc = k // 32 * per32
@@ -136,5 +139,8 @@ def test_restated_x86_gemm_equals_gemm_row(oracle):
         want = np.zeros((m, n), np.float32)
         got = np.zeros((m, n), np.float32)
         oracle.orc_gemm(rows.ctypes.data, n, k, bits, xq.ctypes.data, sx.ctypes.data, mx.ctypes.data, m, want.ctypes.data, 0)
-        oracle.orc_gemm_x86(rows.ctypes.data, n, k, bits, xq.ctypes.data, sx.ctypes.data, mx.ctypes.data, m, got.ctypes.data)
-        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (bits, n, k, m)
+        for vnni in paths:
+            got[:] = 0
+            oracle.orc_gemm_x86(rows.ctypes.data, n, k, bits, xq.ctypes.data, sx.ctypes.data, mx.ctypes.data, m,
+                                got.ctypes.data, vnni)
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (bits, n, k, m, vnni)
