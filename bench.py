@@ -141,11 +141,35 @@ def _check(rc, h):
         raise RuntimeError(h.dh_last_error().decode())
 
 
-def cpu_baseline(h, cfg: str, threads: int, tokens: int = 6):
-    """The CPU port (oracle/: the restated reference backend with the restated x86 integer GEMM of `--backend cpu` for the
-    linears — AVX-VNNI or AVX2, OpenMP over independent rows — and the scalar spec for everything else) on a bounded slice
-    of the same model: the first 4 and the first 8 layers plus the output head; the per-token time of the full depth is
-    extrapolated from the two (every 4-layer block has the same shapes)."""
+def _mem_available_gb() -> float:
+    try:
+        for line in open("/proc/meminfo"):
+            if line.startswith("MemAvailable:"):
+                return int(line.split()[1]) / 1e6
+    except OSError:
+        pass
+    return 0.0
+
+
+def _weights_gb(cfg: str) -> float:
+    """Packed linear weights of a configuration (W6 body, W8 head and GDN a|b) as the CPU port keeps them."""
+    s = SHAPES[cfg]
+    h, f, hd, nh, nkv, nk, nv = s["hidden"], s["ffn"], s["hd"], s["n_h"], s["n_kv"], s["n_k"], s["n_v"]
+    row = lambda k, bits: k * bits // 8 + 4 + k // 128 * 2
+    attn = (nh * 2 * hd + 2 * nkv * hd) * row(h, 6) + h * row(nh * hd, 6)
+    gdn = (2 * nk * 128 + 2 * nv * 128) * row(h, 6) + 2 * nv * row(h, 8) + h * row(nv * 128, 6)
+    ffn = 2 * f * row(h, 6) + h * row(f, 6)
+    n_attn = s["layers"] // 4
+    return (n_attn * attn + (s["layers"] - n_attn) * gdn + s["layers"] * ffn + s["vocab"] * row(h, 8)) / 1e9
+
+
+def cpu_baseline(h, cfg: str, threads: int, tokens: int = 8, warmup: int = 1, context: int = 2048, chunk: int = 256):
+    """The CPU port of the reference's x86 backend (oracle/x86_backend.hpp: strip-repacked packed weights, K-blocked
+    vpdpbusd / vpmaddubsw GEMM, SIMD glue, attention and Gated DeltaNet, OpenMP where the reference uses rayon) on the
+    same model at full depth: prefill `context` tokens of the benchmark prompt in `chunk`-token batches (the reference's
+    `det bench` default, crates/det-cli/src/main.rs:297), then `warmup` untimed and `tokens` timed greedy decode steps
+    (forward + argmax, wall clock).  When the host has too little memory for the full model the first 4 and 8 layers
+    are timed instead and the line says "extrapolated"."""
     import importlib.util
     import numpy as np
     spec = importlib.util.spec_from_file_location("oracle_build", ROOT / "oracle" / "build.py")
@@ -156,41 +180,62 @@ def cpu_baseline(h, cfg: str, threads: int, tokens: int = 6):
     o.orc_set_threads(threads)                     # also when the OpenMP runtime was loaded before the variable changed
     threads = o.orc_max_threads()
     o.orc_cpu_backend_new.restype = C.c_void_p
+    o.orc_cpu_backend_new.argtypes = [C.c_int]
     o.orc_ref_backend_free.argtypes = [C.c_void_p]
-    rb = o.orc_cpu_backend_new()
-    simd = {2: "AVX-VNNI vpdpbusd", 1: "AVX2 vpmaddubsw", 0: "no SIMD on this host: scalar spec"}[o.orc_cpu_simd_level()]
+    level = o.orc_cpu_simd_level()
+    if level == 0:
+        raise RuntimeError("the CPU port needs AVX2")
+    rb = o.orc_cpu_backend_new(-1)
+    simd = {2: "AVX-VNNI vpdpbusd", 1: "AVX2 vpmaddubsw"}[level]
     vocab = SHAPES[cfg]["vocab"]
-    ids = _prompt(h, 8, vocab)
-    times = {}
-    for layers in (4, 8):
-        if layers > SHAPES[cfg]["layers"]:
-            continue
-        m = h.dh_model_new_synth(rb, cfg.encode(), layers, SEED, 64, 8)
+    need_gb, have_gb = _weights_gb(cfg) * 2.2 + 4, _mem_available_gb()   # det rows of one linear + strips + working set
+    ids = _prompt(h, max(context, 8), vocab)
+
+    def run(layers: int, ctx: int):
+        m = h.dh_model_new_synth(rb, cfg.encode(), layers, SEED, ctx + tokens + warmup + 8, chunk)
         if not m:
             raise RuntimeError(h.dh_last_error().decode())
-        _check(h.dh_model_prefill(m, ids.ctypes.data, len(ids)), h)
-        tok = C.c_int32(0)
-        rng = C.c_uint64(0)
-        _check(h.dh_model_pick(m, 1, 1.0, 0, 1.0, C.byref(rng), C.byref(tok)), h)
         t0 = time.perf_counter()
-        for _ in range(tokens):
+        _check(h.dh_model_prefill(m, ids.ctypes.data, ctx), h)
+        t_prefill = time.perf_counter() - t0
+        tok, rng = C.c_int32(0), C.c_uint64(0)
+        _check(h.dh_model_pick(m, 1, 1.0, 0, 1.0, C.byref(rng), C.byref(tok)), h)
+        toks = [tok.value]
+        t_dec = 0.0
+        for i in range(warmup + tokens):
+            t0 = time.perf_counter()
             one = np.array([tok.value], np.int32)
             _check(h.dh_model_forward(m, one.ctypes.data, 1), h)
             _check(h.dh_model_pick(m, 1, 1.0, 0, 1.0, C.byref(rng), C.byref(tok)), h)
-        times[layers] = (time.perf_counter() - t0) / tokens
+            if i >= warmup:
+                t_dec += time.perf_counter() - t0
+            toks.append(tok.value)
         h.dh_model_free(m)
-    o.orc_ref_backend_free(rb)
+        return t_dec / tokens, t_prefill, toks
+
     full = SHAPES[cfg]["layers"]
-    if 8 in times:
-        block = times[8] - times[4]
-        per_token = times[4] + block * (full // 4 - 1)
+    base = {"unit": "tok/s", "cores": threads, "kind": "port", "ram_gb": round(have_gb, 1)}
+    if have_gb >= need_gb:
+        per_token, t_prefill, toks = run(0, context)
+        base.update({"value": 1.0 / per_token, "extrapolated": False, "steps_timed": tokens, "ms_per_step": per_token * 1e3,
+                     "context": context, "prefill": {"value": context / t_prefill, "unit": "tok/s", "tokens": context, "chunk": chunk},
+                     "tokens": toks,
+                     "sample": f"{cfg} shape at full depth ({full} layers + W8 head): prefill {context} tokens of the benchmark "
+                               f"prompt in {chunk}-token chunks, {warmup} untimed + {tokens} timed greedy decode tokens; restated "
+                               f"x86 backend of the reference ({simd}, packed strip weights), {threads} OpenMP threads"})
     else:
-        per_token = times[4]
-    return {"value": 1.0 / per_token, "unit": "tok/s", "cores": threads, "kind": "port",
-            "sample": f"{cfg} shape, first 4 and 8 layers + W8 head, {tokens} decode tokens each at position 8, "
-                      f"extrapolated linearly to {full} layers; restated reference backend, linears through the restated "
-                      f"x86 integer GEMM ({simd}), OpenMP over rows, scalar spec for the other ops",
-            "ms_per_token_4_layers": times[4] * 1e3, "ms_per_token_8_layers": times.get(8, 0) * 1e3}
+        times = {}
+        for layers in (4, 8):
+            times[layers], _, _ = run(layers, 8)
+        per_token = times[4] + (times[8] - times[4]) * (full // 4 - 1)
+        base.update({"value": 1.0 / per_token, "extrapolated": True, "steps_timed": tokens, "ms_per_step": per_token * 1e3,
+                     "context": 8,
+                     "sample": f"{cfg} shape, first 4 and 8 layers + W8 head ({have_gb:.0f} GB of host memory available, "
+                               f"{need_gb:.0f} GB needed for the full depth), {tokens} decode tokens each at position 8, "
+                               f"extrapolated linearly to {full} layers; restated x86 backend of the reference ({simd}), "
+                               f"{threads} OpenMP threads"})
+    o.orc_ref_backend_free(rb)
+    return base
 
 
 def run_ours(args, rank: int, world: int, local_rank: int):
@@ -306,6 +351,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     tok = C.c_int32(0)
     rng = C.c_uint64(0)
     _check(h.dh_model_pick(model, 1, 1.0, 0, 1.0, C.byref(rng), C.byref(tok)), h)
+    first_token = tok.value
+    prompt_logits = None
+    if world > 1 and rank == 0:
+        prompt_logits = np.zeros(shape["vocab"], np.float32)
+        h.dh_model_logits(model, prompt_logits.ctypes.data, prompt_logits.size)
 
     # ---- decode, device-resident (value): W warm-up steps (the first one captures the graph), then exactly K
     dec = h.dh_graph_decoder_new(model)
@@ -315,6 +365,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     _check(h.dh_graph_decoder_enqueue(dec, tok.value, W, 1), h)
     n = h.dh_graph_decoder_finish(dec, out.ctypes.data, out.size)
     last = int(out[n - 1])
+    stream_head = [first_token] + [int(x) for x in out[:n]]     # greedy tokens from the end of the prompt on
     barrier()
     rt.cudaProfilerStart()      # a profiler started with "--profile-from-start off" sees the timed decode steps only
     w0 = time.time()
@@ -326,6 +377,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     n = h.dh_graph_decoder_finish(dec, out.ctypes.data, out.size)
     rt.cudaProfilerStop()
     graph_tokens = out[:n].copy()
+    stream_head += [int(x) for x in graph_tokens]
     last = int(graph_tokens[-1])
 
     # ---- decode end to end through the plugin calls (host embedding -> H2D, forward, argmax, D2H) as model.rs drives it
@@ -365,6 +417,18 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     err = d.det_last_error()
     if err:
         raise RuntimeError(f"device-side wait reported error {err}")
+    # N > 1: rank 0 also runs the same prompt through an UNSHARDED copy of the model on its own GPU and compares the
+    # last-position logits with the sharded run's, bit for bit (after every timed region; the other ranks are done)
+    logits_equal = None
+    if prompt_logits is not None and args.emulate_tp <= 1:
+        solo = h.dh_model_new_synth(bk, cfg.encode(), args.layers, SEED, P + 16, chunk)
+        if not solo:
+            raise RuntimeError(h.dh_last_error().decode())
+        _check(h.dh_model_prefill(solo, ids.ctypes.data, P), h)
+        solo_logits = np.zeros(shape["vocab"], np.float32)
+        h.dh_model_logits(solo, solo_logits.ctypes.data, solo_logits.size)
+        h.dh_model_free(solo)
+        logits_equal = bool(np.array_equal(solo_logits.view(np.uint32), prompt_logits.view(np.uint32)))
 
     if saved_stdout is not None:
         sys.stdout.flush()
@@ -409,8 +473,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "load_s": t_load,
         "tokens_head": [int(x) for x in graph_tokens[:8]],
     }
+    if logits_equal is not None:
+        line["logits_equal_1gpu"] = logits_equal     # sharded vs unsharded last-position logits after the prompt
     if world == 1 and not args.no_cpu:
-        line["cpu_baseline"] = cpu_baseline(h, cfg, os.cpu_count() or 1)
+        base = cpu_baseline(h, cfg, os.cpu_count() or 1, tokens=args.cpu_tokens, context=min(P, args.cpu_context))
+        if base.get("context") == P and "tokens" in base:
+            # the same prompt through the CPU port: its greedy tokens must be the GPU's (27B parity at the full config)
+            cpu_toks = base["tokens"]
+            k = min(len(cpu_toks), len(stream_head))
+            base["tokens_equal_gpu"] = cpu_toks[:k] == stream_head[:k]
+            base["tokens_compared"] = k
+        line["cpu_baseline"] = base
     print(json.dumps(line), flush=True)
 
 
@@ -423,24 +496,26 @@ def run_reference(args, rank: int, world: int):
         return
     from det_b200 import capi
     h = capi.host()
-    try:
-        h.dh_use_cuda_synth_rows(1)   # build the CPU-side weights with the device generator when a GPU is present
-        capi.cuda().det_init()
-    except Exception:
-        pass
+    # build the CPU-side weights with the device generator when a GPU is present (identical rows, seconds instead of
+    # minutes of f64 scale search on the host)
+    if capi.cuda().det_init() == 0:
+        h.dh_use_cuda_synth_rows(1)
     threads = os.cpu_count() or 1
     K, W = args.steps, args.warmup
-    base = cpu_baseline(h, args.config, threads, tokens=max(1, min(K, 8)))
+    K = max(1, min(K, args.cpu_tokens))     # a bounded sample: the CPU needs 0.1 - 0.3 s per 27B token
+    base = cpu_baseline(h, args.config, threads, tokens=K, warmup=min(W, 3), context=min(args.prefill, args.cpu_context))
     cfg = args.config
     line = {
         "impl": "reference",
         "metric": "27B W6 decode tok/s bs1" if cfg == "27b" else f"{cfg} W6 decode tok/s bs1",
-        "value": base["value"], "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": 1e3 / base["value"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "value": base["value"], "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": min(W, 3),
+        "ms_per_step": 1e3 / base["value"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8 x W6 -> int64 (fp32 glue)", "data": "synthetic",
-        "config": {"workload": f"{cfg}-shape seeded random-init W6 model, batch 1 greedy decode on host cores",
-                   "sample": base["sample"]},
+        "config": {"workload": f"{cfg}-shape seeded random-init W6 model (W8 head and GDN a/b), batch 1: prefill "
+                               f"{base['context']} tokens, then greedy decode, on host cores",
+                   "context_at_timing": base["context"] + min(W, 3), "sample": base["sample"]},
         "cpu_baseline": base,
+        "prefill": base.get("prefill"),
         "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -551,6 +626,9 @@ def main():
     ap.add_argument("--compose-rows", action="store_true",
                     help="serving: per-sequence attention / GDN calls instead of the batched kernels (same tokens)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--cpu-tokens", type=int, default=8, help="decode tokens the CPU baseline times")
+    ap.add_argument("--cpu-context", type=int, default=2048,
+                    help="prompt tokens the CPU baseline prefills before timing (capped by --prefill)")
     ap.add_argument("--fuse-kinds", type=int, default=0,
                     help="measurement switch: mask of activation kinds quantized in the GEMV prologue instead of by their own "
                          "kernel (2 RMSNorm, 4 plain, 8 SwiGLU); same values")
@@ -569,7 +647,7 @@ def main():
     else:
         if world == 1:
             from det_b200 import capi
-            capi.host().dh_use_cuda_synth_rows(1)
+            capi.host().dh_use_cuda_synth_rows(1)   # the cpu_baseline leg builds its weights with the device generator
         if args.workload == "serving":
             if world != 1:
                 raise SystemExit("the serving workload runs on one GPU")
