@@ -122,11 +122,17 @@ SHAPES = {   # layers, hidden, ffn, attention (q heads, kv heads, head dim), GDN
 }
 
 
-def launches_per_token(cfg: str) -> int:
-    """Kernels of one device-resident decode step: 10 per layer (norm+quant, fused input GEMV, 2 mixer kernels, quant,
-    output GEMV, norm+quant, gate|up GEMV, SwiGLU+quant, down GEMV) plus embed, final norm, head GEMV, argmax and token
-    feedback."""
-    return SHAPES[cfg]["layers"] * 10 + 5
+def launches_per_token(cfg: str, fused: bool = True) -> int:
+    """Kernels of one device-resident decode step.  Fused (default): a Gated DeltaNet layer is 5 launches (qkv|z + a|b
+    GEMV with the RMSNorm prologue, the mixer step, output GEMV with the quantization prologue, gate|up GEMV with the
+    RMSNorm prologue and the SwiGLU epilogue, down GEMV with the quantization prologue), an attention layer 6 (q|k|v GEMV,
+    prep, attention, output GEMV, gate|up, down), plus embed, head GEMV, argmax and token feedback.  Unfused: every op on
+    its own (11 / 10 per layer, plus the final norm)."""
+    layers = SHAPES[cfg]["layers"]
+    n_attn = layers // 4
+    if fused:
+        return (layers - n_attn) * 5 + n_attn * 6 + 4
+    return (layers - n_attn) * 11 + n_attn * 10 + 5
 
 
 def _prompt(h, n, vocab):
@@ -253,10 +259,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     bk = h.dh_cuda_backend_new(1, 1)
     if not bk:
         raise RuntimeError(h.dh_last_error().decode())
-    if args.fuse_kinds:
-        h.dh_cuda_debug(bk, 0, args.fuse_kinds)
-    if args.attn_flags >= 0:
-        d.det_debug_set_attn(args.attn_flags)
+    if args.no_fuse:
+        h.dh_cuda_debug(bk, 0, 0)
+    if args.gemv_flags:
+        d.det_debug_set_gemv(args.gemv_flags)
     if args.rows_wide_min >= 0:
         d.det_debug_set_rows(args.rows_wide_min)
     if args.tc_splitk:
@@ -458,8 +464,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 "d2h_bytes_per_step": 4},
         # tensor parallel: the exchanges ride in the row kernels (same count per layer) plus the logits gather; with
         # stand-alone exchanges every layer adds 4 exchange kernels, 2 residual adds and 1 quant
-        "gpu_launches": K * (launches_per_token(cfg) + (0 if world == 1 else 1 if args.exchange == "peer"
-                                                         else SHAPES[cfg]["layers"] * 7 + 1)),
+        "gpu_launches": K * (launches_per_token(cfg, fused=(world == 1 and not args.no_fuse)) +
+                             (0 if world == 1 else 1 if args.exchange == "peer" else SHAPES[cfg]["layers"] * 7 + 1)),
         "prefill": {"value": P / (prefill_ms * 1e-3), "unit": "tok/s", "tokens": P, "chunk": chunk},
         "roofline": None if achieved is None else
                     {"bound": "hbm", "kernel": "k_gemv_stream", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -617,8 +623,10 @@ def main():
     ap.add_argument("--ctx-min", type=int, default=512)
     ap.add_argument("--ctx-max", type=int, default=8192)
     ap.add_argument("--new", type=int, default=256)
-    ap.add_argument("--attn-flags", type=int, default=-1,
-                    help="measurement switch for the attention kernels (det_debug_set_attn): 1 token-tiled prefill, +2 two stages")
+    ap.add_argument("--no-fuse", action="store_true",
+                    help="measurement switch: every decode op as its own launch (no prologue / epilogue / dual fusion)")
+    ap.add_argument("--gemv-flags", type=int, default=0,
+                    help="measurement switch of the decode GEMV (det_debug_set_gemv): 1 = whole-SM CTAs, n << 8 = n CTAs per SM")
     ap.add_argument("--rows-wide-min", type=int, default=-1,
                     help="measurement switch: rows from which the row kernels use one CTA per row (det_debug_set_rows)")
     ap.add_argument("--tc-splitk", action="store_true",
@@ -629,9 +637,6 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=8, help="decode tokens the CPU baseline times")
     ap.add_argument("--cpu-context", type=int, default=2048,
                     help="prompt tokens the CPU baseline prefills before timing (capped by --prefill)")
-    ap.add_argument("--fuse-kinds", type=int, default=0,
-                    help="measurement switch: mask of activation kinds quantized in the GEMV prologue instead of by their own "
-                         "kernel (2 RMSNorm, 4 plain, 8 SwiGLU); same values")
     ap.add_argument("--no-pdl", action="store_true", help="measurement switch: plain stream-ordered launches")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -45,9 +45,20 @@ class ActSource(C.Structure):
                 ("mx", c_void_p)]
 
 
+class GemvOp(C.Structure):
+    """det_gemv_op (include/det_b200.h): one decode GEMV launch with its fused neighbours."""
+    _fields_ = [("lin", C.POINTER(QLinear)), ("lin2", C.POINTER(QLinear)), ("src", C.POINTER(ActSource)),
+                ("xq", c_void_p), ("sx", c_void_p), ("mx", c_void_p), ("M", c_int),
+                ("y", c_void_p), ("accumulate", c_int), ("nparts", c_int), ("offs", C.POINTER(c_int)),
+                ("dsts", C.POINTER(c_void_p)),
+                ("y2", c_void_p), ("nparts2", c_int), ("offs2", C.POINTER(c_int)), ("dsts2", C.POINTER(c_void_p)),
+                ("h", c_void_p)]
+
+
 DET_LAYOUT_STREAM = 0x100
 DET_LAYOUT_INT8 = 0x200
-DET_ACT_RMSNORM, DET_ACT_PLAIN, DET_ACT_SWIGLU = 1, 2, 3
+DET_LAYOUT_PAIRS = 0x400
+DET_ACT_RMSNORM, DET_ACT_PLAIN = 1, 2
 # tile pins of the tensor-core GEMM (det_debug_set_tc_variant) that take large batches; 0 = chosen by shape
 TC_VARIANTS_LARGE = (0, 1, 5)
 
@@ -72,8 +83,7 @@ CUDA_ABI = {
     "det_gemm": (None, [C.POINTER(QLinear), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "det_gemm_ex": (None, [C.POINTER(QLinear), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                            C.POINTER(c_int), C.POINTER(c_void_p), c_void_p]),
-    "det_gemm_fused": (None, [C.POINTER(QLinear), C.POINTER(ActSource), c_int, c_void_p, c_int, c_int, C.POINTER(c_int),
-                              C.POINTER(c_void_p), c_void_p]),
+    "det_gemv": (None, [C.POINTER(GemvOp), c_void_p]),
     "det_gemm_scratch_bytes": (c_size_t, [c_int, c_int]),
     "det_gemm_set_scratch": (None, [c_void_p, c_size_t]),
     "det_attention": (None, [C.POINTER(AttnLayer), C.POINTER(KvCache), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -94,6 +104,7 @@ CUDA_ABI = {
     "det_test_prim": (None, [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "det_linear_repack_bytes": (c_size_t, [c_int, c_int, c_int]),
     "det_linear_repack": (None, [C.POINTER(QLinear), c_void_p, c_void_p]),
+    "det_linear_repack_pairs": (None, [C.POINTER(QLinear), c_void_p, c_void_p]),
     "det_linear_expand_bytes": (c_size_t, [c_int, c_int]),
     "det_linear_expand": (None, [C.POINTER(QLinear), c_void_p, c_void_p]),
     "det_synth_linear": (None, [c_u64, c_u64, C.c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
@@ -109,10 +120,6 @@ CUDA_ABI = {
                                   c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "det_gdn_rows": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int,
                             c_int, c_int, c_void_p, c_void_p, c_void_p]),
-    "det_gdn_quant": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int,
-                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
-    "det_gdn_ab": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
-                          c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "det_xchg_create": (c_void_p, [c_size_t, c_int, c_int]),
     "det_xchg_ipc_handle": (None, [c_void_p, c_void_p]),
     "det_xchg_open": (None, [c_void_p, c_void_p]),
@@ -125,7 +132,7 @@ CUDA_ABI = {
     "det_xchg_quant": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "det_debug_set_pdl": (None, [c_int]),
     "det_debug_set_tc_variant": (None, [c_int]),
-    "det_debug_set_attn": (None, [c_int]),
+    "det_debug_set_gemv": (None, [c_int]),
     "det_debug_set_rows": (None, [c_int]),
     "det_debug_umma_peak": (C.c_double, [c_int]),
     "det_last_error": (c_int, []),
@@ -164,8 +171,6 @@ HOST_API = {
     "dh_model_generate": (c_int, [c_void_p, c_void_p, c_size_t, c_size_t, c_int, c_float, c_size_t, c_float, c_u64,
                                   c_void_p, C.POINTER(c_size_t)]),
     "dh_cuda_set_fuse_rows": (None, [c_void_p, c_int]),
-    "dh_cuda_set_fold_ab": (None, [c_void_p, c_int]),
-    "dh_cuda_set_fuse_gdn_quant": (None, [c_void_p, c_int]),
     "dh_batch_new": (c_void_p, [c_void_p, c_size_t, c_size_t]),
     "dh_batch_free": (None, [c_void_p]),
     "dh_batch_prefill": (c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_int, c_float, c_size_t, c_float, c_u64]),

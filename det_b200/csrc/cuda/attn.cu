@@ -422,213 +422,6 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_acc(const AttnArgs a) {
     }
 }
 
-// ---- token-tiled forms for a multi-token call on one sequence (prefill): a CTA serves TT consecutive tokens, so a K / V
-// tile is fetched once for all of them instead of once per token (the 512 tokens of a chunk read almost the same keys).
-// Token tt of the tile sees the keys up to its own position; later keys of a tile are masked (p = 0, no maximum).
-constexpr int TT = 4;
-
-template <int HD>
-__global__ void __launch_bounds__(ATT_THREADS) k_attn_max_tt(const AttnArgs a) {
-    __shared__ __align__(16) int8_t ktile[KT * KTile<HD>::STRIDE];
-    __shared__ __align__(16) int8_t qs[TT][MAX_REP * HD];
-    __shared__ float sks[KT];
-    __shared__ float sqs[TT][MAX_REP];
-    __shared__ unsigned best[TT][MAX_REP];
-    pdl_trigger();
-    pdl_wait();
-    const int kvh = blockIdx.y, t0 = blockIdx.z * TT;
-    const int nt = min(TT, a.M - t0);
-    const RowCache cache = row_cache(a, t0);                 // position of the tile's first token
-    int k0, k1;
-    key_range(a, cache.pos + nt - 1, k0, k1);                // the last token sees the most keys
-    if (k0 >= k1) return;
-    const int rep = a.rep;
-    for (int i = threadIdx.x; i < TT * rep * HD / 16; i += ATT_THREADS) {
-        const int tt = i / (rep * HD / 16), v = i % (rep * HD / 16);
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if (tt < nt) val = reinterpret_cast<const uint4*>(a.qq + ((size_t)(t0 + tt) * a.n_h + (size_t)kvh * rep) * HD)[v];
-        reinterpret_cast<uint4*>(qs[tt])[v] = val;
-    }
-    if (threadIdx.x < TT * MAX_REP) {
-        const int tt = threadIdx.x / MAX_REP, r = threadIdx.x % MAX_REP;
-        sqs[tt][r] = (tt < nt && r < rep) ? a.sq[(size_t)(t0 + tt) * a.n_h + kvh * rep + r] : 0.0f;
-        best[tt][r] = 0u;
-    }
-    const int j = threadIdx.x % KT, part = threadIdx.x / KT;   // 4 parts share the heads
-    unsigned mine[TT][MAX_REP / 4 + 1];
-#pragma unroll
-    for (int tt = 0; tt < TT; tt++)
-#pragma unroll
-        for (int i = 0; i < MAX_REP / 4 + 1; i++) mine[tt][i] = 0u;
-    for (int key0 = k0; key0 < k1; key0 += KT) {
-        const int nkeys = min(KT, k1 - key0);
-        __syncthreads();
-        KTile<HD>::load(ktile, sks, a, cache, kvh, key0, nkeys);
-        __syncthreads();
-        if (j < nkeys) {
-#pragma unroll
-            for (int tt = 0; tt < TT; tt++) {
-                if (tt < nt && key0 + j <= cache.pos + tt) {
-#pragma unroll
-                    for (int i = 0; i < MAX_REP / 4 + 1; i++) {
-                        const int r = part + 4 * i;
-                        if (r < rep) {
-                            const int d = KTile<HD>::dot(ktile, j, qs[tt] + r * HD);
-                            const float s = fmul(fmul((float)d, sqs[tt][r]), sks[j]);
-                            mine[tt][i] = max(mine[tt][i], f32_key(s));
-                        }
-                    }
-                }
-            }
-        }
-    }
-#pragma unroll
-    for (int tt = 0; tt < TT; tt++)
-#pragma unroll
-        for (int i = 0; i < MAX_REP / 4 + 1; i++) {
-            const int r = part + 4 * i;
-            if (r < rep && mine[tt][i]) atomicMax(&best[tt][r], mine[tt][i]);
-        }
-    __syncthreads();
-    if (threadIdx.x < TT * MAX_REP) {
-        const int tt = threadIdx.x / MAX_REP, r = threadIdx.x % MAX_REP;
-        if (tt < nt && r < rep && best[tt][r])
-            atomicMax(a.mxkey + (size_t)(t0 + tt) * a.n_h + kvh * rep + r, best[tt][r]);
-    }
-}
-
-// NST = 2: the next tile is fetched while this one is consumed (100 KB of shared memory: one CTA per SM);
-// NST = 1: fetch, wait, consume (50 KB: three CTAs per SM hide the wait instead).
-template <int HD, int NST>
-__global__ void __launch_bounds__(ATT_THREADS) k_attn_acc_tt(const AttnArgs a) {
-    static_assert(HD <= ATT_THREADS, "one thread per value dimension");
-    extern __shared__ __align__(16) uint8_t asm_[];
-    __shared__ __align__(16) int8_t qs[TT][MAX_REP * HD];
-    __shared__ float sks[2][KT];
-    __shared__ float sqs[TT][MAX_REP];
-    __shared__ float mxs[TT][MAX_REP];
-    __shared__ __align__(16) int pq[TT][MAX_REP][KT];
-    __shared__ long long den_sh[TT][MAX_REP];
-    pdl_trigger();
-    pdl_wait();
-    const int kvh = blockIdx.y, t0 = blockIdx.z * TT;
-    const int nt = min(TT, a.M - t0);
-    const RowCache cache = row_cache(a, t0);
-    int k0, k1;
-    key_range(a, cache.pos + nt - 1, k0, k1);
-    if (k0 >= k1) return;
-    auto ktile_of = [&](int st) { return reinterpret_cast<int8_t*>(asm_ + st * AccSmem<HD>::STAGE); };
-    auto vtile_of = [&](int st) { return reinterpret_cast<int16_t*>(asm_ + st * AccSmem<HD>::STAGE + AccSmem<HD>::KTILE); };
-    auto fetch = [&](int key0, int st) {
-        const int nk = min(KT, k1 - key0);
-        fetch_k_async<HD>(ktile_of(st), sks[st], a, cache, kvh, key0, nk);
-        fetch_v_async<HD>(vtile_of(st), a, cache, kvh, key0, nk);
-    };
-    if (NST == 2) fetch(k0, 0);
-    const int rep = a.rep;
-    for (int i = threadIdx.x; i < TT * rep * HD / 16; i += ATT_THREADS) {
-        const int tt = i / (rep * HD / 16), v = i % (rep * HD / 16);
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if (tt < nt) val = reinterpret_cast<const uint4*>(a.qq + ((size_t)(t0 + tt) * a.n_h + (size_t)kvh * rep) * HD)[v];
-        reinterpret_cast<uint4*>(qs[tt])[v] = val;
-    }
-    if (threadIdx.x < TT * MAX_REP) {
-        const int tt = threadIdx.x / MAX_REP, r = threadIdx.x % MAX_REP;
-        const bool live = tt < nt && r < rep;
-        const size_t hh = (size_t)(t0 + (live ? tt : 0)) * a.n_h + kvh * rep + (live ? r : 0);
-        sqs[tt][r] = live ? a.sq[hh] : 0.0f;
-        mxs[tt][r] = live ? key_f32(a.mxkey[hh]) : 0.0f;
-        den_sh[tt][r] = 0;
-    }
-    const int j = threadIdx.x % KT, part = threadIdx.x / KT;
-    const int d = threadIdx.x;
-    long long num[TT][MAX_REP];
-#pragma unroll
-    for (int tt = 0; tt < TT; tt++)
-#pragma unroll
-        for (int r = 0; r < MAX_REP; r++) num[tt][r] = 0;
-    int st = 0;
-    for (int key0 = k0; key0 < k1; key0 += KT, st ^= (NST - 1)) {
-        const int nkeys = min(KT, k1 - key0);
-        const bool more = NST == 2 && key0 + KT < k1;
-        if (NST == 1) fetch(key0, 0);
-        if (more) fetch(key0 + KT, st ^ 1);
-        if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");
-        else asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
-        const int8_t* ktile = ktile_of(st);
-        const int16_t* vtile = vtile_of(st);
-#pragma unroll
-        for (int tt = 0; tt < TT; tt++) {
-            const bool sees = tt < nt && j < nkeys && key0 + j <= cache.pos + tt;
-#pragma unroll
-            for (int i = 0; i < MAX_REP / 4 + 1; i++) {
-                const int r = part + 4 * i;
-                if (r < rep) {
-                    int p = 0;
-                    if (sees) {
-                        const int dt = KTile<HD>::dot(ktile, j, qs[tt] + r * HD);
-                        const float s = fmul(fmul((float)dt, sqs[tt][r]), sks[st][j]);
-                        p = f2i_sat(fmul(exp_f(fsub(s, mxs[tt][r])), 16777216.0f));
-                    }
-                    pq[tt][r][j] = p;
-                }
-            }
-        }
-        __syncthreads();
-        if (threadIdx.x < TT * MAX_REP) {
-            const int tt = threadIdx.x / MAX_REP, r = threadIdx.x % MAX_REP;
-            if (tt < nt && r < rep) {
-                long long s = 0;
-                for (int q = 0; q < nkeys; q++) s += pq[tt][r][q];
-                den_sh[tt][r] += s;
-            }
-        }
-        if (d < HD) {
-#pragma unroll
-            for (int tt = 0; tt < TT; tt++) pv_tile<HD>(pq[tt], vtile, nkeys, d, rep, num[tt]);
-        }
-        __syncthreads();
-    }
-    if (a.nsplit == 1) {
-        if (d < HD) {
-            const float vs = a.v_scale[kvh];
-#pragma unroll
-            for (int tt = 0; tt < TT; tt++) {
-                if (tt < nt) {
-#pragma unroll
-                    for (int r = 0; r < MAX_REP; r++) {
-                        if (r < rep) {
-                            const int h = kvh * rep + r;
-                            const size_t row = (size_t)(t0 + tt) * a.n_h + h;
-                            const float gate = a.qg[row * 2 * HD + HD + d];
-                            const float val = fmul(fdiv(i64_to_f32(num[tt][r]), i64_to_f32(den_sh[tt][r])), vs);
-                            a.o[row * HD + d] = fmul(val, sigmoid_f(gate));
-                        }
-                    }
-                }
-            }
-        }
-    } else {
-        if (d < HD) {
-#pragma unroll
-            for (int tt = 0; tt < TT; tt++)
-                if (tt < nt)
-#pragma unroll
-                    for (int r = 0; r < MAX_REP; r++)
-                        if (r < rep)
-                            atomicAdd(reinterpret_cast<unsigned long long*>(a.num + ((size_t)(t0 + tt) * a.n_h + kvh * rep + r) * HD + d),
-                                      (unsigned long long)num[tt][r]);
-        }
-        if (threadIdx.x < TT * MAX_REP) {
-            const int tt = threadIdx.x / MAX_REP, r = threadIdx.x % MAX_REP;
-            if (tt < nt && r < rep)
-                atomicAdd(reinterpret_cast<unsigned long long*>(a.den + (size_t)(t0 + tt) * a.n_h + kvh * rep + r),
-                          (unsigned long long)den_sh[tt][r]);
-        }
-    }
-}
-
 template <int HD>
 __global__ void k_attn_fin(const AttnArgs a) {
     pdl_trigger();
@@ -834,8 +627,6 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_dec(const AttnArgs a) {
 
 // Token tiling measured no faster on B200 (27B, 2048- and 8192-token prompts: the accumulate kernel is bound by its
 // integer multiply-adds, not by K/V traffic), so it is off unless switched on.
-static bool g_attn_token_tiles = false;   // measurement switches (det_debug_set_attn)
-static int g_attn_tt_stages = 1;
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 struct ScratchMap {
@@ -908,22 +699,8 @@ static void run_attention(AttnArgs a, void* scratch, int max_total_keys, cudaStr
         DETB_CUDA_OK(cudaFuncSetAttribute(k_attn_acc<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, AccSmem<HD>::STAGE));
         acc_attr = true;
     }
-    if (!a.rows && a.M >= TT && g_attn_token_tiles) {
-        // one sequence, many tokens: TT tokens per CTA share every K / V tile
-        static bool tt_attr = false;
-        if (!tt_attr) {
-            DETB_CUDA_OK(cudaFuncSetAttribute(k_attn_acc_tt<HD, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, AccSmem<HD>::TOTAL));
-            DETB_CUDA_OK(cudaFuncSetAttribute(k_attn_acc_tt<HD, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, AccSmem<HD>::STAGE));
-            tt_attr = true;
-        }
-        const dim3 tgrid(nsplit, a.n_kv, (a.M + TT - 1) / TT);
-        launch_pdl(k_attn_max_tt<HD>, tgrid, dim3(ATT_THREADS), 0, q, 1, a);
-        if (g_attn_tt_stages == 2) launch_pdl(k_attn_acc_tt<HD, 2>, tgrid, dim3(ATT_THREADS), AccSmem<HD>::TOTAL, q, 1, a);
-        else launch_pdl(k_attn_acc_tt<HD, 1>, tgrid, dim3(ATT_THREADS), AccSmem<HD>::STAGE, q, 1, a);
-    } else {
-        launch_pdl(k_attn_max<HD>, grid, dim3(ATT_THREADS), 0, q, 1, a);
-        launch_pdl(k_attn_acc<HD>, grid, dim3(ATT_THREADS), AccSmem<HD>::STAGE, q, 1, a);
-    }
+    launch_pdl(k_attn_max<HD>, grid, dim3(ATT_THREADS), 0, q, 1, a);
+    launch_pdl(k_attn_acc<HD>, grid, dim3(ATT_THREADS), AccSmem<HD>::STAGE, q, 1, a);
     if (nsplit > 1) launch_pdl(k_attn_fin<HD>, dim3(a.M * a.n_h), dim3(HD), 0, q, 1, a);
 }
 
@@ -974,13 +751,6 @@ void det_attention_dev(const det_attn_layer* L, const det_kv_cache* kv, const fl
     attention_entry(L, kv, qg, k, v, rope_cos, rope_sin, rot, eps, M, 0, pos0_dev, max_pos, n_h, n_kv, hd, o, scratch, st);
 }
 
-
-// Measurement switches: bit 0 = token-tiled prefill kernels (default off), bit 1 = two shared-memory stages in the tiled
-// accumulate kernel (default off).  Results do not depend on them.
-void det_debug_set_attn(int flags) {
-    g_attn_token_tiles = (flags & 1) != 0;
-    g_attn_tt_stages = (flags & 2) ? 2 : 1;
-}
 
 // Batched decode (no reference counterpart): M sequences advance one token each.  Row t of qg / k / v / o belongs to the
 // sequence whose cache is rows[t] (a DEVICE array of M det_kv_cache) at position pos[t] (device array); max_pos is a host

@@ -8,7 +8,14 @@
 //           contractions over dk are the spec tree: fold of the lane's aligned run, then xor offsets 1, 2, 4 across the
 //           8 lanes.  State enters and leaves through a shared-memory slab so global traffic stays coalesced.
 //   out     on = rmsnorm(o, norm) * silu_f(z) per (token, v head); the last three raw inputs become the conv state.
+//   step    decode (one token per sequence): all three in ONE launch.  The 8 CTAs of a v head form a thread-block
+//           cluster; each prepares its own operands, advances its 16 state columns, and the head-wide RMSNorm of the
+//           outputs is finished over distributed shared memory (every CTA stores the spec-tree sum of its 16 squares
+//           into its peers' shared memory, one cluster barrier).  The conv state is shifted by whoever read it last.
 #include "runtime.cuh"
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 namespace detb {
 
@@ -29,53 +36,7 @@ struct GdnArgs {
     float* o;        // [M][n_v][DV] mixer output (gout when exported)
     float* gin;      // optional
     const det_gdn_state* rows;   // batched decode: token row t is the next token of the sequence with state rows[t]
-    // decode form with the a|b projection folded in (ab_wq != NULL): a[t][h] and b[t][h] are rows h and n_v + h of a W8
-    // linear in the reference layout applied to the quantized layer input xq / sx / mx (K wide); g.a and g.b are unused
-    const uint8_t* ab_wq;
-    const float* ab_c;
-    const uint16_t* ab_m;
-    const int8_t* xq;
-    const float* sx;
-    const uint16_t* mx;
-    int K;
-    // decode form with the activation quantization of the mixer output folded into k_gdn_out (oq != NULL, M = 1): the
-    // CTA that finishes last quantizes the row exactly as det_quant would (quant_act_i8g); `out_done` counts the CTAs
-    int8_t* oq;
-    float* osx;
-    uint16_t* omx;
-    unsigned* out_done;
 };
-
-// The CTA's share of one output of a W8 linear for token row t (spec gemm_row, spec/quant.rs:99-117): the int64 sum over
-// groups of (m * mx) * (int dot of the group).  Integer sums are order-free, so the K / 16 sixteen-byte chunks of the row
-// are dealt round-robin to the 128 threads (all loads independent and issued together); the caller adds the threads'
-// shares and applies ((f32)acc * c) * sx.
-__device__ __forceinline__ long long ab_partial(const GdnArgs& g, int t, int row) {
-    const int G = g.K >> 7, chunks = g.K >> 4;
-    const uint4* w = reinterpret_cast<const uint4*>(g.ab_wq + (size_t)row * g.K);
-    const uint4* x = reinterpret_cast<const uint4*>(g.xq + (size_t)t * g.K);
-    const uint16_t* m = g.ab_m + (size_t)row * G;
-    const uint16_t* mx = g.mx + (size_t)t * G;
-    long long acc = 0;
-#pragma unroll 4
-    for (int c = threadIdx.x; c < chunks; c += 128) {   // the decode kernel's 128 threads
-        const uint4 wv = w[c], xv = x[c];
-        const unsigned mult = (unsigned)m[c >> 3] * (unsigned)mx[c >> 3];
-        int d = __dp4a((int)wv.x, (int)xv.x, 0);
-        d = __dp4a((int)wv.y, (int)xv.y, d);
-        d = __dp4a((int)wv.z, (int)xv.z, d);
-        d = __dp4a((int)wv.w, (int)xv.w, d);
-        acc += (long long)d * (long long)mult;
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        int lo = (int)(unsigned)acc, hi = (int)(acc >> 32);
-        lo = __shfl_xor_sync(FULL, lo, off);
-        hi = __shfl_xor_sync(FULL, hi, off);
-        acc += ((long long)hi << 32) | (unsigned)lo;
-    }
-    return acc;   // the warp's share, in every lane
-}
 
 // input of channel c `back` steps before token row t (times before the call reach into the conv state, which holds the
 // three inputs before the call's first token; in a batched step every row is the first token of its own sequence)
@@ -209,18 +170,10 @@ __device__ __forceinline__ void slab_store(const float* slab, float* Sh, int j0)
     }
 }
 
-// Decode form: every CTA advances exactly one token (of the one sequence, or of row blockIdx.y's sequence in a batched
-// step) and nothing is exported.  The CTA computes what k_gdn_prep would have left in scratch for it — q and k of its
-// k head (conv, silu, l2norm with the same per-lane runs and xor order), its 16 v channels, beta and decay — so a
-// decode step needs no separate prep launch.
-// PREP = false: the operands come from k_gdn_prep's scratch instead (a batched step with many sequences: preparing them
-// once per head instead of in each of a head's 8 column CTAs and rep heads' worth of k heads is less work overall).
-template <bool PREP>
+// Batched decode with many sequences: every CTA advances one token of row blockIdx.y's sequence with the operands that
+// k_gdn_prep left in scratch (preparing them once per head is less work than in each of a head's 8 column CTAs).
 __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
     __shared__ __align__(16) float slab[SLAB_FLOATS];
-    __shared__ __align__(16) float pq[RL][RUN_STRIDE], pk[RL][RUN_STRIDE];   // runs of 16 rows, padded against conflicts
-    __shared__ float pv[RC], pbd[2];
-    __shared__ long long ab_part[2][4];
     pdl_trigger();
     pdl_wait();
     const int h = blockIdx.x / (DV / RC);
@@ -229,88 +182,99 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
     const int p = threadIdx.x % RL, jj = threadIdx.x / RL;
     const int t = g.rows ? blockIdx.y : 0;
     float* Sh = (g.rows ? g.rows[blockIdx.y].S : g.S) + (size_t)h * DK * DV;
+    slab_load_async(slab, Sh, j0);     // in flight while the operands are fetched
+    const float* qrow = g.y + (size_t)t * g.conv_dim + (size_t)kh * DK + p * RR;
+    const float* krow = g.y + (size_t)t * g.conv_dim + (size_t)g.n_k * DK + (size_t)kh * DK + p * RR;
+    float k[RR], q[RR];
+#pragma unroll
+    for (int i = 0; i < RR; i += 4) {
+        const float4 kk = *reinterpret_cast<const float4*>(krow + i);
+        const float4 qq = *reinterpret_cast<const float4*>(qrow + i);
+        k[i] = kk.x; k[i + 1] = kk.y; k[i + 2] = kk.z; k[i + 3] = kk.w;
+        q[i] = qq.x; q[i + 1] = qq.y; q[i + 2] = qq.z; q[i + 3] = qq.w;
+    }
+    const float vv = g.y[(size_t)t * g.conv_dim + (size_t)2 * g.n_k * DK + (size_t)h * DV + j0 + jj];
+    const float be = g.beta[(size_t)t * g.n_v + h], de = g.decay[(size_t)t * g.n_v + h];
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    float s[RR];
+#pragma unroll
+    for (int i = 0; i < RR; i++) s[i] = slab[slab_at(p * RR + i, jj)];
+    const float ov = recur_step(s, k, q, vv, be, de);
+    if (p == 0) g.o[((size_t)t * g.n_v + h) * DV + j0 + jj] = ov;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < RR; i++) slab[slab_at(p * RR + i, jj)] = s[i];
+    __syncthreads();
+    slab_store(slab, Sh, j0);
+}
+
+// Decode step in one launch: conv + silu + l2norm + gates, the recurrence, the gated output norm and the conv-state
+// shift.  Grid (n_v * 8, sequences), cluster (8, 1, 1): the 8 CTAs of a cluster own the 8 x 16 state columns of one v head.
+// Every CTA computes what k_gdn_prep would have left in scratch for it — q and k of its k head (conv, silu, l2norm with
+// the same per-lane runs and xor order), its 16 v channels, beta and decay — then advances its columns.  The RMSNorm over
+// the head's 128 outputs is the spec tree: a CTA's 16 squares are an aligned subtree (xor 1, 2, 4, 8 over 16 lanes), the 8
+// subtree sums are stored into every peer's shared memory and each CTA finishes the same tree over them (xor 1, 2, 4).
+// Conv state: a CTA alone reads its 16 v channels and shifts them itself; the q / k channels of a k head are read by all
+// CTAs of its rep heads — each counts itself in when it has read them, and the one that arrives last does the shift and
+// resets the counter (nobody waits on the counter).
+constexpr int GDN_CL = DV / RC;            // CTAs per head = cluster size
+constexpr int CONV_COUNTERS = 4096;        // (sequence, k head) pairs of one launch
+static __device__ unsigned g_conv_done[CONV_COUNTERS];
+
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+__global__ void __launch_bounds__(RC * RL) k_gdn_step(const GdnArgs g) {
+    __shared__ __align__(16) float slab[SLAB_FLOATS];
+    __shared__ __align__(16) float pq[RL][RUN_STRIDE], pk[RL][RUN_STRIDE];   // runs of 16 rows, padded against conflicts
+    __shared__ float pv[RC], pbd[2], so[RC];
+    __shared__ float peer_ss[GDN_CL];          // subtree sums of the head's 8 CTAs, stored here by the peers
+    __shared__ bool last_reader;
+    cluster_arrive();                          // paired with the wait before the first store into a peer
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.x / GDN_CL;
+    const unsigned rank = blockIdx.x % GDN_CL;
+    const int j0 = (int)rank * RC;
+    const int kh = h / g.rep;
+    const int p = threadIdx.x % RL, jj = threadIdx.x / RL;
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int t = g.rows ? blockIdx.y : 0;
+    float* Sh = (g.rows ? g.rows[blockIdx.y].S : g.S) + (size_t)h * DK * DV;
+    float* cstate = g.rows ? g.rows[blockIdx.y].conv_state : g.conv_state;
     slab_load_async(slab, Sh, j0);     // in flight while the operands are prepared
-    if (!PREP) {
-        // operands from scratch: this thread's 16 rows of k and q, its column's v, the head's beta and decay
-        const float* qrow = g.y + (size_t)t * g.conv_dim + (size_t)kh * DK + p * RR;
-        const float* krow = g.y + (size_t)t * g.conv_dim + (size_t)g.n_k * DK + (size_t)kh * DK + p * RR;
-        float k[RR], q[RR];
-#pragma unroll
-        for (int i = 0; i < RR; i += 4) {
-            const float4 kk = *reinterpret_cast<const float4*>(krow + i);
-            const float4 qq = *reinterpret_cast<const float4*>(qrow + i);
-            k[i] = kk.x; k[i + 1] = kk.y; k[i + 2] = kk.z; k[i + 3] = kk.w;
-            q[i] = qq.x; q[i + 1] = qq.y; q[i + 2] = qq.z; q[i + 3] = qq.w;
-        }
-        const float vv = g.y[(size_t)t * g.conv_dim + (size_t)2 * g.n_k * DK + (size_t)h * DV + j0 + jj];
-        const float be = g.beta[(size_t)t * g.n_v + h], de = g.decay[(size_t)t * g.n_v + h];
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
-        float s[RR];
-#pragma unroll
-        for (int i = 0; i < RR; i++) s[i] = slab[slab_at(p * RR + i, jj)];
-        const float ov = recur_step(s, k, q, vv, be, de);
-        if (p == 0) g.o[((size_t)t * g.n_v + h) * DV + j0 + jj] = ov;
-        __syncthreads();
-#pragma unroll
-        for (int i = 0; i < RR; i++) slab[slab_at(p * RR + i, jj)] = s[i];
-        __syncthreads();
-        slab_store(slab, Sh, j0);
-        return;
+    // the gate input and the norm weight of this CTA's 16 outputs, fetched early
+    float zv = 0.0f, nw = 0.0f;
+    if (threadIdx.x < RC) {
+        zv = g.z[((size_t)t * g.n_v + h) * DV + j0 + threadIdx.x];
+        nw = g.norm[j0 + threadIdx.x];
     }
-    if (g.ab_wq) {
-        // a[h] and b[h] of this token: all four warps share the two W8 rows
-        const long long pa = ab_partial(g, t, h), pb = ab_partial(g, t, g.n_v + h);
-        if ((threadIdx.x & 31) == 0) {
-            ab_part[0][threadIdx.x >> 5] = pa;
-            ab_part[1][threadIdx.x >> 5] = pb;
+    if (wib < 2) {
+        // warp 0: q of k head kh, warp 1: k — lane owns four consecutive channels, as in k_gdn_prep
+        const int c0 = (wib == 0 ? kh : g.n_k + kh) * DK + lane * 4;
+        float v[4], sq[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            v[e] = conv_silu(g, t, c0 + e);
+            sq[e] = fmul(v[e], v[e]);
         }
-        __syncthreads();
-    }
-    {
-        const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-        if (wib < 2) {
-            // warp 0: q of k head kh, warp 1: k — lane owns four consecutive channels, as in k_gdn_prep
-            const int c0 = (wib == 0 ? kh : g.n_k + kh) * DK + lane * 4;
-            float v[4], sq[4];
+        const float ss = fold_lanes<32>(fold_run<4>(sq));
+        const float inv = fdiv(1.0f, fsqrt(fadd(ss, g.eps)));
+        float (*dst)[RUN_STRIDE] = wib == 0 ? pq : pk;
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                v[e] = conv_silu(g, t, c0 + e);
-                sq[e] = fmul(v[e], v[e]);
-            }
-            const float ss = fold_lanes<32>(fold_run<4>(sq));
-            const float inv = fdiv(1.0f, fsqrt(fadd(ss, g.eps)));
-            float (*dst)[RUN_STRIDE] = wib == 0 ? pq : pk;
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                v[e] = fmul(v[e], inv);
-                if (wib == 0) v[e] = fmul(v[e], __uint_as_float(QSCALE_BITS));
-                dst[(lane * 4 + e) / RR][(lane * 4 + e) % RR] = v[e];
-            }
-        } else if (wib == 2) {
-            if (lane < RC) pv[lane] = conv_silu(g, t, 2 * g.n_k * DK + h * DV + j0 + lane);
-            if (lane == 0) {
-                float bv;
-                if (g.ab_wq) {
-                    const long long acc = ab_part[1][0] + ab_part[1][1] + ab_part[1][2] + ab_part[1][3];
-                    bv = fmul(fmul(i64_to_f32(acc), g.ab_c[g.n_v + h]), g.sx[t]);
-                } else {
-                    bv = g.b[(size_t)t * g.n_v + h];
-                }
-                pbd[0] = sigmoid_f(bv);
-            }
-        } else {
-            if (lane == 0) {
-                float av;
-                if (g.ab_wq) {
-                    const long long acc = ab_part[0][0] + ab_part[0][1] + ab_part[0][2] + ab_part[0][3];
-                    av = fmul(fmul(i64_to_f32(acc), g.ab_c[h]), g.sx[t]);
-                } else {
-                    av = g.a[(size_t)t * g.n_v + h];
-                }
-                const float sp = softplus_f(fadd(av, g.dt_bias[h]));
-                pbd[1] = exp_f(-fmul(g.A[h], sp));
-            }
+        for (int e = 0; e < 4; e++) {
+            v[e] = fmul(v[e], inv);
+            if (wib == 0) v[e] = fmul(v[e], __uint_as_float(QSCALE_BITS));
+            dst[(lane * 4 + e) / RR][(lane * 4 + e) % RR] = v[e];
+        }
+    } else if (wib == 2) {
+        if (lane < RC) pv[lane] = conv_silu(g, t, 2 * g.n_k * DK + h * DV + j0 + lane);
+        if (lane == 0) pbd[0] = sigmoid_f(g.b[(size_t)t * g.n_v + h]);
+    } else {
+        if (lane == 0) {
+            const float sp = softplus_f(fadd(g.a[(size_t)t * g.n_v + h], g.dt_bias[h]));
+            pbd[1] = exp_f(-fmul(g.A[h], sp));
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -323,12 +287,60 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
         q[i] = pq[p][i];
     }
     const float ov = recur_step(s, k, q, pv[jj], pbd[0], pbd[1]);
-    if (p == 0) g.o[((size_t)t * g.n_v + h) * DV + j0 + jj] = ov;
+    if (p == 0) so[jj] = ov;
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < RR; i++) slab[slab_at(p * RR + i, jj)] = s[i];
+    // ---- gated output norm of the head: this CTA's subtree sum to every peer, then the tree over the 8 sums
+    float mine = 0.0f, ss16 = 0.0f;
+    if (wib == 0) {
+        mine = lane < RC ? so[lane] : 0.0f;
+        ss16 = fold_lanes<RC>(fmul(mine, mine));                 // lanes 0..15: the subtree over this CTA's 16 squares
+    }
+    cluster_wait();                                               // every CTA of the cluster is running
+    if (wib == 0 && lane < GDN_CL) cg::this_cluster().map_shared_rank(peer_ss, lane)[rank] = ss16;
+    cluster_arrive();
+    cluster_wait();                                               // all eight sums have landed here
+    if (wib == 0) {
+        const float part = lane < GDN_CL ? peer_ss[lane] : 0.0f;
+        const float tot = __shfl_sync(FULL, fold_lanes<GDN_CL>(part), 0);
+        const float inv = fdiv(1.0f, fsqrt(fadd(fdiv(tot, (float)DV), g.eps)));
+        if (lane < RC) {
+            const float yn = fmul(fmul(mine, inv), nw);
+            g.on[((size_t)t * g.n_v + h) * DV + j0 + lane] = fmul(yn, silu_f(zv));
+        }
+    }
     __syncthreads();
     slab_store(slab, Sh, j0);
+    // ---- conv state <- the last three raw inputs.  Every read of it by this CTA is behind the barriers above.
+    if (threadIdx.x < RC) {
+        const size_t c = (size_t)2 * g.n_k * DK + (size_t)h * DV + j0 + threadIdx.x;
+        const float s1 = cstate[(size_t)g.conv_dim + c], s2 = cstate[(size_t)2 * g.conv_dim + c];
+        const float x0 = g.qkv[(size_t)t * g.conv_dim + c];
+        cstate[c] = s1;
+        cstate[(size_t)g.conv_dim + c] = s2;
+        cstate[(size_t)2 * g.conv_dim + c] = x0;
+    }
+    if (threadIdx.x == 0) {
+        unsigned* cnt = &g_conv_done[t * g.n_k + kh];
+        __threadfence();
+        last_reader = atomicAdd(cnt, 1u) == (unsigned)(g.rep * GDN_CL) - 1u;
+        if (last_reader) *cnt = 0;
+    }
+    __syncthreads();
+    if (last_reader) {
+        __threadfence();
+        // q channels kh * 128 .. and k channels (n_k + kh) * 128 ..: 256 channels, two per thread
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const size_t c = (size_t)(e == 0 ? kh : g.n_k + kh) * DK + threadIdx.x;
+            const float s1 = __ldcg(cstate + (size_t)g.conv_dim + c), s2 = __ldcg(cstate + (size_t)2 * g.conv_dim + c);
+            const float x0 = g.qkv[(size_t)t * g.conv_dim + c];
+            cstate[c] = s1;
+            cstate[(size_t)g.conv_dim + c] = s2;
+            cstate[(size_t)2 * g.conv_dim + c] = x0;
+        }
+    }
 }
 
 // Sequence form (prefill): the CTA walks all M tokens of one sequence.  The recurrence is strictly sequential, so its
@@ -465,59 +477,6 @@ __global__ void __launch_bounds__(128) k_gdn_out(const GdnArgs g, int row_blocks
             g.on[row * DV + lane * 4 + e] = fmul(yn, silu_f(g.z[row * DV + lane * 4 + e]));
         }
     }
-    if (!g.oq) return;
-    // ---- M = 1 with the quantization folded in: the row-block CTA that finishes last quantizes the whole row
-    // (n_v groups of 128 = one head each) with the expressions of the row kernel: group scale amax / 127, row scale
-    // max / 65535, integer multiplier per group, codes.
-    __shared__ bool last;
-    __shared__ float wmax[4];
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) last = atomicAdd(g.out_done, 1u) == (unsigned)row_blocks - 1;
-    __syncthreads();
-    if (!last) return;
-    __threadfence();
-    constexpr int MAXG = 16;                       // groups per warp: up to 64 v heads
-    float val[MAXG][4], s_grp[MAXG];
-    float smax = 0.0f;
-#pragma unroll
-    for (int k = 0; k < MAXG; k++) {
-        const int grp = wib + 4 * k;
-        s_grp[k] = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 4; e++) val[k][e] = 0.0f;
-        if (grp < g.n_v) {
-            const float4 x = __ldcg(reinterpret_cast<const float4*>(g.on + (size_t)grp * DV + lane * 4));
-            val[k][0] = x.x; val[k][1] = x.y; val[k][2] = x.z; val[k][3] = x.w;
-            float amax = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
-            amax = max_lanes(amax);
-            s_grp[k] = fdiv(amax, 127.0f);
-            smax = fmaxf(smax, s_grp[k]);
-        }
-    }
-    if (lane == 0) wmax[wib] = smax;
-    __syncthreads();
-    const float top = fmaxf(fmaxf(wmax[0], wmax[1]), fmaxf(wmax[2], wmax[3]));
-    const float sx = (top == 0.0f) ? 1.0f : fdiv(top, 65535.0f);
-    if (threadIdx.x == 0) {
-        g.osx[0] = sx;
-        *g.out_done = 0;
-    }
-#pragma unroll
-    for (int k = 0; k < MAXG; k++) {
-        const int grp = wib + 4 * k;
-        if (grp < g.n_v) {
-            const unsigned mult = group_mult(s_grp[k], sx);
-            const float inv = fdiv(1.0f, fmul(sx, (float)mult));
-            char4 c;
-            c.x = (signed char)quant_code(val[k][0], inv);
-            c.y = (signed char)quant_code(val[k][1], inv);
-            c.z = (signed char)quant_code(val[k][2], inv);
-            c.w = (signed char)quant_code(val[k][3], inv);
-            *reinterpret_cast<char4*>(g.oq + (size_t)grp * DV + lane * 4) = c;
-            if (lane == 0) g.omx[grp] = (uint16_t)mult;
-        }
-    }
 }
 
 static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -547,21 +506,9 @@ size_t det_gdn_scratch_bytes(int M, int n_k, int n_v, int dk, int dv) {
     return gdn_scratch(M > 0 ? M : 1, n_k, n_v).total;
 }
 
-struct QuantOut {
-    int8_t* q;
-    float* sx;
-    uint16_t* mx;
-};
-struct AbSource {
-    const det_qlinear* lin;
-    const int8_t* xq;
-    const float* sx;
-    const uint16_t* mx;
-};
 static void gdn_entry(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_state* rows, const float* qkv, const float* z,
                       const float* a, const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on,
-                      void* scratch, float* gin, float* gout, cudaStream_t st, const AbSource* ab = nullptr,
-                      const QuantOut* qo = nullptr) {
+                      void* scratch, float* gin, float* gout, cudaStream_t st) {
     if (M <= 0) return;
     DETB_REQUIRE(dk == DK && dv == DV, "Gated DeltaNet kernels are built for dk = dv = 128");
     DETB_REQUIRE(n_k > 0 && n_v % n_k == 0, "n_v must be a multiple of n_k");
@@ -570,20 +517,6 @@ static void gdn_entry(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_st
     GdnArgs g;
     g.conv = L->conv; g.A = L->A; g.dt_bias = L->dt_bias; g.norm = L->norm;
     g.rows = rows;
-    g.ab_wq = nullptr; g.ab_c = nullptr; g.ab_m = nullptr; g.xq = nullptr; g.sx = nullptr; g.mx = nullptr; g.K = 0;
-    if (ab) {
-        DETB_REQUIRE((rows != nullptr || M == 1) && gin == nullptr, "the a|b projection folds into decode steps only");
-        DETB_REQUIRE(ab->lin->bits == 8 && ab->lin->N == 2 * n_v && ab->lin->K % 128 == 0 && ab->mx != nullptr,
-                     "a|b must be a W8 reference-layout linear of 2 * n_v rows");
-        g.ab_wq = ab->lin->wq; g.ab_c = ab->lin->c; g.ab_m = ab->lin->m;
-        g.xq = ab->xq; g.sx = ab->sx; g.mx = ab->mx; g.K = ab->lin->K;
-    }
-    g.oq = nullptr; g.osx = nullptr; g.omx = nullptr;
-    g.out_done = reinterpret_cast<unsigned*>(base + sm.done);
-    if (qo) {
-        DETB_REQUIRE(M == 1 && rows == nullptr && n_v <= 64, "the output quantization folds into single-token steps only");
-        g.oq = qo->q; g.osx = qo->sx; g.omx = qo->mx;
-    }
     g.conv_state = S ? S->conv_state : nullptr;
     g.S = S ? S->S : nullptr;
     g.qkv = qkv; g.z = z; g.a = a; g.b = b;
@@ -597,16 +530,17 @@ static void gdn_entry(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_st
     g.gin = gin;
     cudaStream_t q = queue_of(st);
     const int heads = 2 * n_k + n_v;
-    // decode form: every CTA of the recurrence advances one token and prepares its own operands
-    // (with many sequences the shared prep kernel is less work than preparing inside every recurrence CTA)
-    const bool fused_prep = (rows ? (M < 8 || ab != nullptr) : M == 1) && gin == nullptr;
-    if (fused_prep) {
-        launch_pdl(k_gdn_recur_dec<true>, dim3(n_v * (DV / RC), rows ? M : 1), dim3(RC * RL), 0, q, 1, g);
-    } else {
-        launch_pdl(k_gdn_prep, dim3((heads + 3) / 4, M), dim3(128), 0, q, 1, g);
-        if (rows) launch_pdl(k_gdn_recur_dec<false>, dim3(n_v * (DV / RC), M), dim3(RC * RL), 0, q, 1, g);
-        else launch_pdl(k_gdn_recur_seq, dim3(n_v * (DV / RC)), dim3(RC * RL), 0, q, 1, g);
+    // decode form (one token per sequence, nothing exported): the whole mixer in one launch, a cluster per v head.  With
+    // many sequences the shared prep kernel is less work than preparing inside every recurrence CTA.
+    const int seqs = rows ? M : 1;
+    const bool one_launch = (rows ? M < 8 : M == 1) && gin == nullptr && gout == nullptr && seqs * n_k <= CONV_COUNTERS;
+    if (one_launch) {
+        launch_pdl(k_gdn_step, dim3(n_v * GDN_CL, seqs), dim3(RC * RL), 0, q, GDN_CL, g);
+        return;
     }
+    launch_pdl(k_gdn_prep, dim3((heads + 3) / 4, M), dim3(128), 0, q, 1, g);
+    if (rows) launch_pdl(k_gdn_recur_dec, dim3(n_v * (DV / RC), M), dim3(RC * RL), 0, q, 1, g);
+    else launch_pdl(k_gdn_recur_seq, dim3(n_v * (DV / RC)), dim3(RC * RL), 0, q, 1, g);
     const int row_blocks = (int)(((long long)M * n_v + 3) / 4);
     const int state_blocks = ((g.conv_dim + 127) / 128) * (rows ? M : 1);
     launch_pdl(k_gdn_out, dim3(row_blocks + state_blocks), dim3(128), 0, q, 1, g, row_blocks);
@@ -623,28 +557,6 @@ void det_gdn_rows(const det_gdn_layer* L, const det_gdn_state* rows, const float
                   const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
                   cudaStream_t st) {
     gdn_entry(L, nullptr, rows, qkv, z, a, b, eps, M, n_k, n_v, dk, dv, on, scratch, nullptr, nullptr, st);
-}
-
-// One decode token with the activation quantization of the mixer output folded in (no reference counterpart): det_gdn
-// followed by det_quant(on, 1, n_v * dv) -> oq, osx, omx, one launch less.  The scratch must come zero-filled from
-// det_malloc and be used for nothing else (a counter lives in its first bytes).
-void det_gdn_quant(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a, const float* b,
-                   float eps, int n_k, int n_v, int dk, int dv, float* on, int8_t* oq, float* osx, uint16_t* omx,
-                   void* scratch, cudaStream_t st) {
-    const QuantOut qo{oq, osx, omx};
-    gdn_entry(L, S, nullptr, qkv, z, a, b, eps, 1, n_k, n_v, dk, dv, on, scratch, nullptr, nullptr, st, nullptr, &qo);
-}
-
-// Decode step(s) with the layer's a|b projection folded into the mixer (no reference counterpart): `ab` is the fused
-// W8 linear [a rows | b rows] in the reference layout, xq / sx / mx the quantized layer input (det_rmsnorm_quant's output,
-// M rows).  S != NULL: one sequence, M = 1.  rows != NULL: M sequences, one token each (see det_gdn_rows).  Values equal
-// det_gemm_ex on `ab` followed by det_gdn / det_gdn_rows.
-void det_gdn_ab(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_state* rows, const det_qlinear* ab,
-                const int8_t* xq, const float* sx, const uint16_t* mx, const float* qkv, const float* z, float eps, int M,
-                int n_k, int n_v, int dk, int dv, float* on, void* scratch, cudaStream_t st) {
-    DETB_REQUIRE((S != nullptr) != (rows != nullptr), "det_gdn_ab takes one state or a table of states");
-    const AbSource src{ab, xq, sx, mx};
-    gdn_entry(L, S, rows, qkv, z, nullptr, nullptr, eps, M, n_k, n_v, dk, dv, on, scratch, nullptr, nullptr, st, &src);
 }
 
 void det_gdn(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a,

@@ -115,20 +115,14 @@ extern "C" {
 size_t det_gemm_scratch_bytes(int M, int K) { return (size_t)(M > 0 ? M : 1) * (size_t)(K / 128) * sizeof(int); }
 void det_gemm_set_scratch(void* p, size_t bytes) { (void)p; (void)bytes; }
 
-static void gemm_entry(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx,
-                       const det_act_source* src, int M, float* y, int accumulate, int nparts, const int* offs,
-                       float* const* dsts, cudaStream_t st) {
-    if (M <= 0) return;
-    const int bits = L->bits & 0xff;
-    const bool stream = (L->bits & DET_LAYOUT_STREAM) != 0;
-    DETB_REQUIRE(bits == 4 || bits == 6 || bits == 8, "bits must be 4, 6 or 8");
-    DETB_REQUIRE(L->K > 0 && L->K % 128 == 0 && L->N > 0, "K must be a positive multiple of 128");
+static OutSpec make_out(const det_qlinear* L, float* y, int accumulate, int nparts, const int* offs, float* const* dsts) {
     DETB_REQUIRE(nparts <= 4, "at most 4 fused parts");
     OutSpec out;
     out.y = y;
     out.N = L->N;
     out.accumulate = accumulate;
     out.nparts = nparts > 1 ? nparts : 0;
+    out.pairs = (L->bits & DET_LAYOUT_PAIRS) ? 1 : 0;
     for (int i = 0; i < 5; i++) out.offs[i] = L->N;
     for (int i = 0; i < 4; i++) out.dsts[i] = nullptr;
     if (nparts > 1) {
@@ -140,14 +134,31 @@ static void gemm_entry(const det_qlinear* L, const int8_t* xq, const float* sx, 
     } else if (nparts == 1 && dsts && !y) {
         out.y = dsts[0];
     }
+    return out;
+}
+static void check_linear(const det_qlinear* L) {
+    const int bits = L->bits & 0xff;
+    DETB_REQUIRE(bits == 4 || bits == 6 || bits == 8, "bits must be 4, 6 or 8");
+    DETB_REQUIRE(L->K > 0 && L->K % 128 == 0 && L->N > 0, "K must be a positive multiple of 128");
+    DETB_REQUIRE(!(L->bits & DET_LAYOUT_PAIRS) || (L->bits & DET_LAYOUT_STREAM), "the pairs layout is a streaming layout");
+}
+
+void det_gemm_ex(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M, float* y,
+                 int accumulate, int nparts, const int* offs, float* const* dsts, cudaStream_t st) {
+    if (M <= 0) return;
+    check_linear(L);
+    const int bits = L->bits & 0xff;
+    const OutSpec out = make_out(L, y, accumulate, nparts, offs, dsts);
     cudaStream_t q = queue_of(st);
-    if (src) {
-        DETB_REQUIRE(stream, "det_gemm_fused needs the streaming weight layout");
-        gemv_stream_launch(L, bits, nullptr, nullptr, nullptr, M, out, q, src);
-    } else if (L->bits & DET_LAYOUT_INT8) {
+    if (L->bits & DET_LAYOUT_INT8) {
         gemm_tc_launch(L, xq, sx, mx, M, out, q);
-    } else if (stream) {
-        gemv_stream_launch(L, bits, xq, sx, mx, M, out, q);
+    } else if (L->bits & DET_LAYOUT_STREAM) {
+        GemvCall call;
+        call.lin = L;
+        call.xq = xq; call.sx = sx; call.mx = mx;
+        call.M = M;
+        call.out = out;
+        gemv_stream_launch(call, q);
     } else {
         if (bits == 8) gemm_rowmajor_bits<8>(L, xq, sx, mx, M, out, q);
         else if (bits == 6) gemm_rowmajor_bits<6>(L, xq, sx, mx, M, out, q);
@@ -155,15 +166,24 @@ static void gemm_entry(const det_qlinear* L, const int8_t* xq, const float* sx, 
     }
 }
 
-void det_gemm_ex(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M, float* y,
-                 int accumulate, int nparts, const int* offs, float* const* dsts, cudaStream_t st) {
-    gemm_entry(L, xq, sx, mx, nullptr, M, y, accumulate, nparts, offs, dsts, st);
-}
-
-void det_gemm_fused(const det_qlinear* L, const det_act_source* src, int M, float* y, int accumulate, int nparts,
-                    const int* offs, float* const* dsts, cudaStream_t st) {
-    DETB_REQUIRE(src != nullptr, "det_gemm_fused needs an activation source");
-    gemm_entry(L, nullptr, nullptr, nullptr, src, M, y, accumulate, nparts, offs, dsts, st);
+void det_gemv(const det_gemv_op* op, cudaStream_t st) {
+    DETB_REQUIRE(op && op->lin, "det_gemv needs a linear");
+    if (op->M <= 0) return;
+    check_linear(op->lin);
+    DETB_REQUIRE(op->lin->bits & DET_LAYOUT_STREAM, "det_gemv needs the streaming weight layout");
+    GemvCall call;
+    call.lin = op->lin;
+    call.lin2 = op->lin2;
+    call.src = op->src;
+    call.xq = op->xq; call.sx = op->sx; call.mx = op->mx;
+    call.M = op->M;
+    call.out = make_out(op->lin, op->y, op->accumulate, op->nparts, op->offs, op->dsts);
+    if (op->lin2) {
+        check_linear(op->lin2);
+        call.out2 = make_out(op->lin2, op->y2, 0, op->nparts2, op->offs2, op->dsts2);
+    }
+    call.h = op->h;
+    gemv_stream_launch(call, queue_of(st));
 }
 
 void det_gemm(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M, float* y,

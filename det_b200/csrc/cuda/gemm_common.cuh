@@ -14,8 +14,10 @@ struct OutSpec {
     int nparts;          // 0 or 1: plain y
     int offs[5];         // part i = columns [offs[i], offs[i+1])
     float* dsts[4];
+    int pairs;           // rows come in the pairs layout: physical row n is column (n & 1) * N / 2 + n / 2
 };
 __device__ __forceinline__ void emit(const OutSpec& o, int t, int n, float v) {
+    if (o.pairs) n = (n & 1) * (o.N >> 1) + (n >> 1);
     if (o.nparts > 1) {
         int i = 0;
 #pragma unroll
@@ -95,8 +97,18 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
 
 
 // Entry of the streaming GEMV (gemv_stream.cu): M tokens against a det_linear_repack layout.
-void gemv_stream_launch(const det_qlinear* L, int bits, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
-                        const OutSpec& out, cudaStream_t q, const det_act_source* src = nullptr);
+struct GemvCall {
+    const det_qlinear* lin = nullptr;      // streaming layout
+    const det_qlinear* lin2 = nullptr;     // optional W8 streaming-layout linear over the same input rows
+    const det_act_source* src = nullptr;   // activation prologue; otherwise xq / sx / mx
+    const int8_t* xq = nullptr;
+    const float* sx = nullptr;
+    const uint16_t* mx = nullptr;
+    int M = 0;
+    OutSpec out{}, out2{};
+    float* h = nullptr;                    // SwiGLU product instead of `out` (pairs layout)
+};
+void gemv_stream_launch(const GemvCall& call, cudaStream_t q);
 
 // Entry of the tensor-core GEMM (gemm_tc.cu): L->wq is the int8-expanded layout.
 void gemm_tc_launch(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,

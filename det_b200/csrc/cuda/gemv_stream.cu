@@ -1,14 +1,20 @@
 // Decode GEMV (M <= 8 tokens per pass) on the streaming weight layout: the HBM-bound kernel of the token loop.
 // Replaces the reference's k_decode (kernels/cuda/gemm.cu:201-337) with a B200 design:
 //
-//   * persistent CTAs (one per SM), warp-specialised: one producer thread streams weight records HBM -> shared memory
-//     with cp.async.bulk into a ring of slots guarded by full/empty mbarriers; sixteen consumer warps each own whole
-//     records, so consumers never synchronise with each other;
-//   * a record holds TR complete output rows (TR chosen from K so a record is 8-20 KB); the 32 lanes of the owning warp
-//     split into TR groups of 32/TR lanes, one group per row, and walk the row in units of 64 codes;
-//   * codes are unpacked in registers from 128-bit shared loads (W6: 48 bytes per unit -> 16 words of four unsigned
-//     codes), multiplied with dp4a against int8 activations staged once per CTA, and widened to int64 with the
-//     group multiplier m * mx per unit;  sum(code * x) = sum(u * x) - offset * sum(x) for the unsigned W4/W6 codes.
+//   * persistent CTAs, warp-specialised: one producer thread streams weight records HBM -> shared memory with
+//     cp.async.bulk into a ring of slots guarded by full/empty mbarriers; twelve consumer warps each own whole groups of
+//     four output rows and a private set of ring slots, so consumers never synchronise with each other;
+//   * a CTA takes about half of an SM's shared memory, and a launch puts one CTA on every SM: the CTAs of the NEXT GEMV of
+//     the token loop (launched with programmatic dependent launch) become resident beside the running ones and pull
+//     their first weights while the running GEMV still computes and while the row operations between the two run, so
+//     HBM does not idle at kernel boundaries;
+//   * a record is a 1024-wide K chunk of four rows: the 32 lanes of the owning warp are 4 rows x 8 lanes, and a lane
+//     walks one whole 128-group of its row per record — unsigned codes unpacked in registers from 128-bit shared loads,
+//     dp4a against int8 activations staged once per CTA, ONE exact 64-bit multiply-add per group;
+//   * the activation quantization that feeds the GEMV (RMSNorm + quant_act_i8g, or plain quant_act_i8g) can run as the
+//     kernel's prologue while the ring fills (the reference runs it as a separate kernel, qwen35.rs:33, 62, 121), a second
+//     small W8 linear reading the same row (the GDN a|b projection) can ride in the same launch, and a gate|up linear
+//     stored with interleaved rows can emit the SwiGLU product silu_f(gate) * up from its epilogue.
 //
 // Algorithmic bytes per launch: N * (K*bits/8 + 4 + K/128*2) weights + M * (K + 4 + K/128*2) in + M * N * 4 out.
 #include "gemm_common.cuh"
@@ -16,62 +22,66 @@
 namespace detb {
 
 // ------------------------------------------------------------------------------------------------------------------
-// Streaming layout.  TR consecutive rows form a record
-//     [ codes row 0 | ... | codes row TR-1 | c[TR] fp32 (padded to 16 B) | m[TR][K/128] u16 | pad to 16 B ]
-// and records are contiguous.  Inside a row the codes are cut into units of 64 consecutive k (half a 128-group); a unit
-// is NP = bits/2 pieces of 16 bytes, and piece p of unit u lives at byte (p * U + u) * 16 of the row (U = K / 64), so
-// lanes that own neighbouring units read neighbouring 16-byte words of shared memory (no bank conflicts).
+// Streaming layout.  Four consecutive rows ("quad") x one K chunk of UC units (a unit = 64 consecutive k = half a
+// 128-group; UC = 16, or 8 when K is an odd multiple of 512) form one record
+//     [ row 0: pieces | row 1 | row 2 | row 3 | m[4][UC/2] u16 ]                      (16-byte aligned)
+// and the records of a quad follow each other in K order, quads in row order.  A unit is NP = bits/2 pieces of 16 bytes;
+// piece pp of physical unit p of row r lives at byte ((r * NP + pp) * UC + p) * 16, so the 8 lanes of a row read
+// neighbouring 16-byte words (no bank conflicts).  With UC = 16 the units of a chunk are stored permuted — physical unit
+// p is logical unit (p & 7) * 2 + (p >> 3) — so that lane j, which reads physical units j and j + 8, owns exactly the
+// group j of the chunk.  c stays in its own array (one load per row).
 //   W8 unit: 64 signed bytes in k order (4 pieces).
 //   W4 unit: words W[0..7]; byte b of W[i] = u[4i+b] | u[32+4i+b] << 4,  u = code + 8 (2 pieces).
 //   W6 unit: words W[0..7] as W4 with the low nibbles of u = code + 32, then H[0..3]; byte b of H[j] holds, in bit
 //            field f (bits 2f, 2f+1), the top two bits of u[4(j+4f) + b] (3 pieces).
 // The consumer rebuilds sixteen words o[i] of four consecutive-k unsigned codes: o[i] = nibbles | shifted H field.
+// Pairs layout (DET_LAYOUT_PAIRS): physical row 2i is row i of the linear's first half (gate), row 2i+1 row i of its
+// second half (up), so a quad holds two complete (gate, up) pairs.
+constexpr int QR = 4;     // rows per record
+constexpr int LPR = 8;    // lanes per row
+
 struct StreamGeom {
     int N, K, bits;
-    int U;            // units per row
-    int np;           // 16-byte pieces per unit
-    int row_bytes;    // U * np * 16
-    int G;
-    int TR;           // rows per record: 1, 2, 4 or 8
-    int c_off;        // TR * row_bytes
-    int m_off;
-    int rec_bytes;    // padded to 16
-    int nrec;         // ceil(N / TR)
+    int U, G, np;
+    int UC;            // units per chunk
+    int NCH;           // chunks per row
+    int m_off;         // QR * np * UC * 16
+    int rec_bytes;
+    int nquads;
 };
 __host__ __device__ inline StreamGeom stream_geom(int N, int K, int bits) {
     StreamGeom g;
     g.N = N; g.K = K; g.bits = bits;
     g.U = K / 64;
-    g.np = bits / 2;
-    g.row_bytes = g.U * g.np * 16;
     g.G = K / 128;
-    int tr = 8;
-    while (tr > 1 && tr * g.row_bytes > 20 * 1024) tr >>= 1;   // a function of (K, bits) only
-    g.TR = tr;
-    g.c_off = tr * g.row_bytes;
-    g.m_off = g.c_off + (tr * 4 + 15) / 16 * 16;
-    g.rec_bytes = (g.m_off + tr * g.G * 2 + 15) & ~15;
-    g.nrec = (N + tr - 1) / tr;
+    g.np = bits / 2;
+    g.UC = (g.U % 16 != 0 && g.U % 8 == 0) ? 8 : 16;     // a function of K only
+    g.NCH = (g.U + g.UC - 1) / g.UC;
+    g.m_off = QR * g.np * g.UC * 16;
+    g.rec_bytes = (g.m_off + QR * (g.UC / 2) * 2 + 15) & ~15;
+    g.nquads = (N + QR - 1) / QR;
     return g;
 }
+__host__ __device__ inline int phys_unit(int UC, int l) { return UC == 16 ? (l >> 1) + (l & 1) * 8 : l; }
 
-// One thread per (row, unit): decode 64 codes from the reference layout (spec/quant.rs:62-97), write the unit's pieces.
-__global__ void k_repack_stream(const uint8_t* __restrict__ wq, const float* __restrict__ c,
-                                const uint16_t* __restrict__ m, StreamGeom g, uint8_t* __restrict__ dst) {
+// One thread per (padded row, unit slot of the padded K): decode 64 codes from the reference layout
+// (spec/quant.rs:62-97), write the unit's pieces.  Padding (rows past N, units past K) holds the code of value 0.
+__global__ void k_repack_stream(const uint8_t* __restrict__ wq, const uint16_t* __restrict__ m, StreamGeom g, int pairs,
+                                uint8_t* __restrict__ dst) {
     const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long rows_padded = (long long)g.nrec * g.TR;
-    if (id >= rows_padded * g.U) return;
-    const int n = (int)(id / g.U), u = (int)(id % g.U);
-    const int rr = n % g.TR;
-    uint8_t* rec = dst + (size_t)(n / g.TR) * g.rec_bytes;
-    uint8_t* row = rec + (size_t)rr * g.row_bytes;
-    const bool live = n < g.N;
+    const int slots = g.NCH * g.UC;
+    if (id >= (long long)g.nquads * QR * slots) return;
+    const int n = (int)(id / slots), lu = (int)(id % slots);
+    const int r = n % QR, c = lu / g.UC, l = lu % g.UC;
+    const int src_row = pairs ? ((n & 1) ? g.N / 2 + (n >> 1) : (n >> 1)) : n;
+    const bool live = n < g.N && lu < g.U;
+    uint8_t* rec = dst + ((size_t)(n / QR) * g.NCH + c) * g.rec_bytes;
     __align__(16) uint8_t code[64];   // unsigned code (+offset), or the raw signed byte for W8
     const int bp32 = bytes_per_32(g.bits);
     for (int h = 0; h < 2; h++) {
-        const uint8_t* blk = wq + ((size_t)n * (g.K >> 5) + (size_t)(2 * u + h)) * bp32;
+        const uint8_t* blk = live ? wq + ((size_t)src_row * (g.K >> 5) + (size_t)(2 * lu + h)) * bp32 : nullptr;
         for (int i = 0; i < 32; i++) {
-            uint8_t v = 0;
+            uint8_t v = (uint8_t)code_offset(g.bits);
             if (live) {
                 if (g.bits == 8) v = blk[i];
                 else {
@@ -96,48 +106,55 @@ __global__ void k_repack_stream(const uint8_t* __restrict__ wq, const float* __r
                     piece[32 + 4 * j + b] = v;
                 }
     }
-    for (int p = 0; p < g.np; p++)
-        *reinterpret_cast<uint4*>(row + ((size_t)p * g.U + u) * 16) = *reinterpret_cast<const uint4*>(piece + 16 * p);
-    if (u == 0) {
-        reinterpret_cast<float*>(rec + g.c_off)[rr] = live ? c[n] : 0.0f;
-        uint16_t* mrow = reinterpret_cast<uint16_t*>(rec + g.m_off) + rr * g.G;
-        for (int gi = 0; gi < g.G; gi++) mrow[gi] = live ? m[(size_t)n * g.G + gi] : (uint16_t)1;
-    }
+    const int p = phys_unit(g.UC, l);
+    for (int pp = 0; pp < g.np; pp++)
+        *reinterpret_cast<uint4*>(rec + ((size_t)(r * g.np + pp) * g.UC + p) * 16) = *reinterpret_cast<const uint4*>(piece + 16 * pp);
+    if ((l & 1) == 0)
+        reinterpret_cast<uint16_t*>(rec + g.m_off)[r * (g.UC / 2) + (l >> 1)] = live ? m[(size_t)src_row * g.G + (lu >> 1)] : (uint16_t)1;
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-constexpr int NCW = 16;                          // consumer warps
+constexpr int NCW = 12;                          // consumer warps
 constexpr int GEMV_THREADS = (NCW + 1) * 32;     // + one producer warp
-constexpr int MAX_SLOTS = 24;
+constexpr int MAX_SLOTS = 3 * NCW;
+constexpr int RREG = 4;                          // 128-slices per warp kept in registers by the prologue
 
-struct GemvArgs {
+struct GemvSeg {
     const uint8_t* w;         // streaming layout
-    StreamGeom g;
+    const float* c;           // [N]
+    int N, nquads, rec_bytes, m_off;
+    OutSpec out;
+};
+struct GemvArgs {
+    GemvSeg seg[2];           // seg[1] (DUAL instantiations only) is a W8 linear over the same input row
+    int K, U, G, UC, NCH;
+    int slot_bytes;
     const int8_t* xq;         // rows of this pass
     const float* sx;
     const uint16_t* mx;       // may be NULL
     int t0;                   // first token of this pass (for routing)
     int mt;                   // live tokens in this pass (<= MT)
-    int slots;                // ring depth, a multiple of `workers`
-    int workers;              // consumer warps that take records (<= NCW); warp w owns slots w, w + workers, ...
+    int spw;                  // ring slots per worker warp; warp w owns slots [w * spw, (w + 1) * spw)
+    int workers;              // consumer warps that take quads (<= NCW)
     int* error_flag;
-    OutSpec out;
-    // Fused activation prologue (k_gemv_stream<.., FUSED = true>): the rows are produced from fp32 inputs inside the
-    // kernel — the op sequences of RMSNorm + quant_act_i8g, plain quant_act_i8g or SwiGLU + quant_act_i8g — instead of
-    // being read as codes.  CTA 0 also stores the codes / scale / multipliers for later consumers when asked to.
-    int pro;                  // PRO_RMS, PRO_PLAIN, PRO_SWIGLU
-    const float* pa;          // x, or the gate rows
-    const float* pb;          // norm weight, or the up rows
+    // Activation prologue: the rows are produced from fp32 inputs inside the kernel — the op sequences of RMSNorm +
+    // quant_act_i8g or plain quant_act_i8g — instead of being read as codes.  CTA 0 also stores the codes / scale /
+    // multipliers for later consumers when asked to.
+    int pro;                  // 0, PRO_RMS, PRO_PLAIN
+    const float* pa;          // x
+    const float* pb;          // norm weight
     float eps;
     int pslices;              // next power of two >= K, over 128
     int8_t* xq_out;
     float* sx_out;
     uint16_t* mx_out;
+    // SwiGLU epilogue (seg[0] in the pairs layout): h[t][i] = silu_f(y[2i]) * y[2i+1] instead of y
+    float* h;
+    int h_width;
 };
-enum : int { PRO_RMS = 1, PRO_PLAIN = 2, PRO_SWIGLU = 3 };
-constexpr int FUSED_MAX_ROUNDS = 9;   // slices per consumer warp: K <= 9 * 16 * 128 = 18432
+enum : int { PRO_RMS = 1, PRO_PLAIN = 2 };
 
-// Sixteen words of four consecutive-k codes from one unit; `pu` is the byte distance between pieces (U * 16).
+// Sixteen words of four consecutive-k codes from one unit; `pu` is the byte distance between pieces (UC * 16).
 template <int BITS>
 __device__ __forceinline__ void unpack_unit(const uint8_t* wp, int pu, unsigned (&o)[16]) {
     if (BITS == 8) {
@@ -169,37 +186,72 @@ __device__ __forceinline__ void unpack_unit(const uint8_t* wp, int pu, unsigned 
     }
 }
 
-
-// Produces the int8 rows of this pass from fp32 inputs, straight into the staged (piece-transposed) layout.
-// One warp owns one 128-wide slice at a time, 4 consecutive values per lane, values held in registers between phases;
-// the row-wide sum of squares is the spec tree (slice sums are aligned subtrees; every warp finishes the same tree over
-// them), the row-wide maximum is order-free.  Same fp32 operation sequence as k_row in glue.cu.
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory"); }
 
-__device__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2* xmeta, float* slice_sum, float* wmax, float* sxs) {
-    const StreamGeom& g = a.g;
-    const int K = g.K, U = g.U, G = g.G;
+// Where the 16-byte piece holding activation codes k0 .. k0+15 of token row t lives in the staged copy: the same chunk /
+// piece / physical-unit order as the weights.
+__device__ __forceinline__ int stage_piece(const GemvArgs& a, int t, int q /* piece index k0 / 16 */) {
+    const int lu = q >> 2, pp = q & 3;
+    const int c = lu / a.UC, l = lu - c * a.UC;
+    return (((t * a.NCH + c) * 4 + pp) * a.UC + phys_unit(a.UC, l)) * 16;
+}
+__device__ __forceinline__ int stage_unit(const GemvArgs& a, int t, int lu) {
+    const int c = lu / a.UC, l = lu - c * a.UC;
+    return (t * a.NCH + c) * a.UC + phys_unit(a.UC, l);
+}
+
+// Produces the int8 rows of this pass from fp32 inputs, straight into the staged layout.  One warp owns one 128-wide
+// slice at a time, 4 consecutive values per lane; the first RREG slices of a warp stay in registers between the phases,
+// later ones (rows longer than RREG * NCW * 128 values) are read again.  The row-wide sum of squares is the spec tree
+// (slice sums are aligned subtrees; every warp finishes the same tree over them), the row-wide maximum is order-free.
+// Same fp32 operation sequence as k_row in glue.cu.
+__device__ __forceinline__ float4 pro_value(const GemvArgs& a, const float4 x, const float4 w, float inv_rms) {
+    if (a.pro != PRO_RMS) return x;
+    return make_float4(fmul(fmul(x.x, inv_rms), w.x), fmul(fmul(x.y, inv_rms), w.y), fmul(fmul(x.z, inv_rms), w.z),
+                       fmul(fmul(x.w, inv_rms), w.w));
+}
+__device__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2* xmeta, float* slice_sum, float* s_slices, float* wmax,
+                            float* sxs) {
+    const int K = a.K, G = a.G;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool keep = blockIdx.x == 0 && a.xq_out != nullptr;
+    const int rounds = (G + NCW - 1) / NCW;
     for (int t = 0; t < a.mt; t++) {
         const float* pa = a.pa + (size_t)t * K;
-        const float* pb = a.pro == PRO_SWIGLU ? a.pb + (size_t)t * K : a.pb;
-        float v[FUSED_MAX_ROUNDS][4];
+        float4 v[RREG], wv[RREG];
 #pragma unroll
-        for (int r = 0; r < FUSED_MAX_ROUNDS; r++) {
+        for (int r = 0; r < RREG; r++) {
             const int s = warp + r * NCW;
-            float4 x4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (s < G) x4 = *reinterpret_cast<const float4*>(pa + s * 128 + lane * 4);
-            v[r][0] = x4.x; v[r][1] = x4.y; v[r][2] = x4.z; v[r][3] = x4.w;
+            v[r] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            wv[r] = v[r];
+            if (s < G) {
+                v[r] = *reinterpret_cast<const float4*>(pa + s * 128 + lane * 4);
+                if (a.pro == PRO_RMS) wv[r] = *reinterpret_cast<const float4*>(a.pb + s * 128 + lane * 4);
+            }
         }
+        auto value_of = [&](int r, int s) -> float4 {      // fp32 input of slice s (round r of this warp)
+            float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int i = 0; i < RREG; i++)
+                if (r == i) x = v[i];
+            if (r >= RREG && s < G) x = *reinterpret_cast<const float4*>(pa + s * 128 + lane * 4);
+            return x;
+        };
+        auto weight_of = [&](int r, int s) -> float4 {
+            float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (a.pro != PRO_RMS) return x;
+#pragma unroll
+            for (int i = 0; i < RREG; i++)
+                if (r == i) x = wv[i];
+            if (r >= RREG && s < G) x = *reinterpret_cast<const float4*>(a.pb + s * 128 + lane * 4);
+            return x;
+        };
         float inv_rms = 0.0f;
         if (a.pro == PRO_RMS) {
-#pragma unroll
-            for (int r = 0; r < FUSED_MAX_ROUNDS; r++) {
+            for (int r = 0; r < rounds; r++) {
                 const int s = warp + r * NCW;
-                float sq[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++) sq[e] = fmul(v[r][e], v[r][e]);
+                const float4 x = value_of(r, s);
+                float sq[4] = {fmul(x.x, x.x), fmul(x.y, x.y), fmul(x.z, x.z), fmul(x.w, x.w)};
                 const float ssum = fold_lanes<32>(fold_run<4>(sq));
                 if (lane == 0 && s < G) slice_sum[s] = ssum;
             }
@@ -225,28 +277,16 @@ __device__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2* xmeta, float* 
             }
             inv_rms = fdiv(1.0f, fsqrt(fadd(fdiv(tot, (float)K), a.eps)));
         }
-        float s_slice[FUSED_MAX_ROUNDS];
         float local_max = 0.0f;
-#pragma unroll
-        for (int r = 0; r < FUSED_MAX_ROUNDS; r++) {
+        for (int r = 0; r < rounds; r++) {
             const int s = warp + r * NCW;
-            s_slice[r] = 0.0f;
             if (s < G) {
-                float amax = 0.0f;
-                float4 b4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (a.pro != PRO_PLAIN) b4 = *reinterpret_cast<const float4*>(pb + s * 128 + lane * 4);
-                const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    float val = v[r][e];
-                    if (a.pro == PRO_RMS) val = fmul(fmul(val, inv_rms), bb[e]);
-                    else if (a.pro == PRO_SWIGLU) val = fmul(silu_f(val), bb[e]);
-                    v[r][e] = val;
-                    amax = fmaxf(amax, fabsf(val));
-                }
+                const float4 y = pro_value(a, value_of(r, s), weight_of(r, s), inv_rms);
+                float amax = fmaxf(fmaxf(fabsf(y.x), fabsf(y.y)), fmaxf(fabsf(y.z), fabsf(y.w)));
                 amax = max_lanes(amax);
-                s_slice[r] = fdiv(amax, 127.0f);
-                local_max = fmaxf(local_max, s_slice[r]);
+                const float sg = fdiv(amax, 127.0f);
+                if (lane == 0) s_slices[s] = sg;
+                local_max = fmaxf(local_max, sg);
             }
         }
         if (lane == 0) wmax[warp] = local_max;
@@ -259,54 +299,106 @@ __device__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2* xmeta, float* 
             sxs[t] = sx;
             if (keep) a.sx_out[t] = sx;
         }
-#pragma unroll
-        for (int r = 0; r < FUSED_MAX_ROUNDS; r++) {
+        for (int r = 0; r < rounds; r++) {
             const int s = warp + r * NCW;
             if (s < G) {
-                const unsigned mult = group_mult(s_slice[r], sx);
+                const float4 y = pro_value(a, value_of(r, s), weight_of(r, s), inv_rms);
+                const unsigned mult = group_mult(s_slices[s], sx);
                 const float inv = fdiv(1.0f, fmul(sx, (float)mult));
-                unsigned word = (unsigned)(quant_code(v[r][0], inv) & 0xff);
-                word |= (unsigned)(quant_code(v[r][1], inv) & 0xff) << 8;
-                word |= (unsigned)(quant_code(v[r][2], inv) & 0xff) << 16;
-                word |= (unsigned)(quant_code(v[r][3], inv) & 0xff) << 24;
-                // value index e = s * 128 + lane * 4: unit 2s + lane / 16, piece (lane % 16) / 4, word lane % 4
-                const int u = 2 * s + (lane >> 4), pc = (lane & 15) >> 2;
-                *reinterpret_cast<unsigned*>(xs + ((size_t)(t * 4 + pc) * U + u) * 16 + (lane & 3) * 4) = word;
+                unsigned word = (unsigned)(quant_code(y.x, inv) & 0xff);
+                word |= (unsigned)(quant_code(y.y, inv) & 0xff) << 8;
+                word |= (unsigned)(quant_code(y.z, inv) & 0xff) << 16;
+                word |= (unsigned)(quant_code(y.w, inv) & 0xff) << 24;
+                // value index e = s * 128 + lane * 4: 16-byte piece s * 8 + lane / 4, word lane % 4 of it
+                *reinterpret_cast<unsigned*>(xs + stage_piece(a, t, s * 8 + (lane >> 2)) + (lane & 3) * 4) = word;
                 int sum = __dp4a((int)word, 0x01010101, 0);
 #pragma unroll
                 for (int off = 1; off < 16; off <<= 1) sum += __shfl_xor_sync(FULL, sum, off);
-                if ((lane & 15) == 0) xmeta[t * U + u] = make_int2(sum, (int)mult);
+                if ((lane & 15) == 0) xmeta[stage_unit(a, t, 2 * s + (lane >> 4))] = make_int2(sum, (int)mult);
                 if (keep) {
                     *reinterpret_cast<unsigned*>(a.xq_out + (size_t)t * K + s * 128 + lane * 4) = word;
                     if (lane == 0) a.mx_out[(size_t)t * G + s] = (uint16_t)mult;
                 }
             }
         }
-        consumer_barrier();
+        consumer_barrier();     // the slice tables are reused by the next row
     }
 }
 
-// Shared memory: [slots x rec_bytes] [x pieces: MT*K] [xmeta: MT*U int2 = (sum of x over the unit, mx of its group)]
-//                [full[MAX_SLOTS]] [empty[MAX_SLOTS]] [slice sums: 256 f32] [warp maxima: NCW f32] [row scales: 8 f32]
-template <int BITS, int MT, bool FUSED>
-__global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs a) {
+// One record (K chunk c of the quad) for this lane's row: the lane's whole 128-group (two units; one unit = half a group
+// when UC = 8), all MT tokens.  acc gathers dot * (m * mx - 2^31) exactly in 64 bits with ONE signed multiply-add per
+// group and token, accs the plain sum of the dots: the caller adds accs * 2^31 back at the end of the row.
+template <int BITS, int MT>
+__device__ __forceinline__ void quad_chunk(const GemvArgs& a, const uint8_t* rec, int m_off, int c, int r, int j,
+                                           const uint8_t* xs, const int2* xmeta, long long (&acc)[MT], int (&accs)[MT]) {
+    constexpr int NP = BITS / 2;
+    const int UC = a.UC, pu = UC * 16;
+    const uint8_t* wp = rec + ((size_t)(r * NP) * UC + j) * 16;
+    const unsigned mw = reinterpret_cast<const uint16_t*>(rec + m_off)[r * (UC >> 1) + (UC == 16 ? j : (j >> 1))];
+    int dots[MT], mxv[MT];
+#pragma unroll
+    for (int t = 0; t < MT; t++) { dots[t] = 0; mxv[t] = 1; }
+    const int upl = UC >> 3;     // units per lane: 2 (a whole group) or 1
+    for (int uu = 0; uu < upl; uu++) {
+        unsigned o[16];
+        unpack_unit<BITS>(wp + uu * (LPR * 16), pu, o);
+        const int p = j + LPR * uu;
+#pragma unroll
+        for (int t = 0; t < MT; t++) {
+            int d0 = 0, d1 = 0, d2 = 0, d3 = 0;   // independent chains, summed below
+            const uint8_t* xt = xs + (((size_t)(t * a.NCH + c) * 4) * UC + p) * 16;
+            const uint4 x0 = *reinterpret_cast<const uint4*>(xt);
+            const uint4 x1 = *reinterpret_cast<const uint4*>(xt + pu);
+            const uint4 x2 = *reinterpret_cast<const uint4*>(xt + 2 * (size_t)pu);
+            const uint4 x3 = *reinterpret_cast<const uint4*>(xt + 3 * (size_t)pu);
+            d0 = dot4<BITS>(o[0], (int)x0.x, d0); d1 = dot4<BITS>(o[1], (int)x0.y, d1);
+            d2 = dot4<BITS>(o[2], (int)x0.z, d2); d3 = dot4<BITS>(o[3], (int)x0.w, d3);
+            d0 = dot4<BITS>(o[4], (int)x1.x, d0); d1 = dot4<BITS>(o[5], (int)x1.y, d1);
+            d2 = dot4<BITS>(o[6], (int)x1.z, d2); d3 = dot4<BITS>(o[7], (int)x1.w, d3);
+            d0 = dot4<BITS>(o[8], (int)x2.x, d0); d1 = dot4<BITS>(o[9], (int)x2.y, d1);
+            d2 = dot4<BITS>(o[10], (int)x2.z, d2); d3 = dot4<BITS>(o[11], (int)x2.w, d3);
+            d0 = dot4<BITS>(o[12], (int)x3.x, d0); d1 = dot4<BITS>(o[13], (int)x3.y, d1);
+            d2 = dot4<BITS>(o[14], (int)x3.z, d2); d3 = dot4<BITS>(o[15], (int)x3.w, d3);
+            const int2 meta = xmeta[(t * a.NCH + c) * UC + p];
+            int dot = (d0 + d1) + (d2 + d3);
+            if (BITS != 8) dot -= code_offset(BITS) * meta.x;
+            dots[t] += dot;
+            mxv[t] = meta.y;
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < MT; t++) {
+        const int mults = (int)(mw * (unsigned)mxv[t] + 0x80000000u);     // m * mx - 2^31 as a signed word
+        acc[t] += (long long)dots[t] * (long long)mults;
+        accs[t] += dots[t];
+    }
+}
+
+// Shared memory: [ring: workers * spw slots] [x pieces: MT * NCH * UC * 64] [xmeta: MT * NCH * UC int2 = (sum of x over
+// the unit, mx of its group)] [full[MAX_SLOTS]] [empty[MAX_SLOTS]] [slice sums: 256 f32] [slice scales: 256 f32]
+// [warp maxima: NCW f32] [row scales: 8 f32]
+template <int BITS, int MT, bool DUAL>
+__global__ void __launch_bounds__(GEMV_THREADS, MT <= 2 ? 2 : 1) k_gemv_stream(const GemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    const StreamGeom& g = a.g;
-    const int U = g.U, G = g.G;
+    const int UC = a.UC, NCH = a.NCH;
+    const int upad = NCH * UC;
     uint8_t* ring = smem;
-    uint8_t* xs = ring + (size_t)a.slots * g.rec_bytes;
-    int2* xmeta = reinterpret_cast<int2*>(xs + (size_t)MT * g.K);
-    unsigned long long* full = reinterpret_cast<unsigned long long*>(xmeta + MT * U);
+    uint8_t* xs = ring + (size_t)a.workers * a.spw * a.slot_bytes;
+    int2* xmeta = reinterpret_cast<int2*>(xs + (size_t)MT * upad * 64);
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(xmeta + MT * upad);
     unsigned long long* empty = full + MAX_SLOTS;
     float* slice_sum = reinterpret_cast<float*>(empty + MAX_SLOTS);
-    float* wmax = slice_sum + 256;
+    float* s_slices = slice_sum + 256;
+    float* wmax = s_slices + 256;
     float* sxs = wmax + NCW;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const long long wl = wait_limit(a.error_flag);
+    const int W = a.workers, SPW = a.spw;
+    const int total = a.seg[0].nquads + (DUAL ? a.seg[1].nquads : 0);
     pdl_trigger();
     if (tid == 0) {
-        for (int s = 0; s < a.slots; s++) {
+        for (int s = 0; s < W * SPW; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -315,48 +407,65 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
     __syncthreads();
 
     if (warp == NCW) {
-        // ---------------- producer: one thread keeps the ring full; weights do not depend on earlier kernels
+        // ---------------- producer: one thread keeps every worker's slots full; weights do not depend on earlier
+        // kernels.  Order: round li (the li-th quad of every worker), chunk c, worker w.
         if (lane == 0) {
             bool ok = true;
             int issued = 0;
-            for (int rec = blockIdx.x; rec < g.nrec; rec += gridDim.x, issued++) {
-                const int s = issued % a.slots;
-                ok = mbar_wait(&empty[s], ((unsigned)(issued / a.slots) & 1u) ^ 1u, wl);
-                if (!ok) break;
-                mbar_expect_tx(&full[s], (unsigned)g.rec_bytes);
-                bulk_g2s(ring + (size_t)s * g.rec_bytes, a.w + (size_t)rec * g.rec_bytes, (unsigned)g.rec_bytes, &full[s]);
+            for (int li = 0; ok && (long long)blockIdx.x + (long long)li * W * gridDim.x < total; li++) {
+                for (int c = 0; ok && c < NCH; c++) {
+                    for (int w = 0; w < W; w++) {
+                        const long long Q = (long long)blockIdx.x + (long long)(li * W + w) * gridDim.x;
+                        if (Q >= total) break;
+                        const int sg = (DUAL && Q >= a.seg[0].nquads) ? 1 : 0;
+                        const long long q = sg ? Q - a.seg[0].nquads : Q;
+                        const int lr = li * NCH + c;
+                        const int s = w * SPW + lr % SPW;
+                        ok = mbar_wait(&empty[s], ((unsigned)(lr / SPW) & 1u) ^ 1u, wl);
+                        if (!ok) break;
+                        const unsigned bytes = (unsigned)a.seg[sg].rec_bytes;
+                        mbar_expect_tx(&full[s], bytes);
+                        bulk_g2s(ring + (size_t)s * a.slot_bytes, a.seg[sg].w + ((size_t)q * NCH + c) * bytes, bytes, &full[s]);
+                        issued++;
+                    }
+                }
             }
             if (!ok) {
                 atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
-                // copies already issued still target this CTA's shared memory: wait (bounded) for each to land
-                for (int k = 0; k < a.slots && k < issued; k++) {
-                    const int i = issued - 1 - k;
-                    (void)mbar_wait(&full[i % a.slots], (unsigned)(i / a.slots) & 1u, wl);
+                // copies already issued still target this CTA's shared memory: give each slot a (bounded) chance to land
+                for (int s = 0; s < W * SPW && s < issued; s++) {
+                    (void)mbar_wait(&full[s], 0u, wl >> 5);
+                    (void)mbar_wait(&full[s], 1u, wl >> 5);
                 }
             }
         }
         return;
     }
 
-    // ---------------- consumers: stage the activations once (piece-transposed like the weights), then drain records.
-    // The activations (and the output rows) belong to earlier kernels: wait for them here, while the producer is
-    // already pulling weights.
+    // ---------------- consumers: stage the activations once (same chunk / piece order as the weights), then drain
+    // records.  The activations (and the output rows) belong to earlier kernels: wait for them here, while the producer
+    // is already pulling weights.
     pdl_wait();
-    if (FUSED) {
-        fused_stage(a, xs, xmeta, slice_sum, wmax, sxs);
+    if (upad != a.U) {     // ragged last chunk: the padding units must read as zero
+        for (int i = tid; i < MT * upad * 4; i += NCW * 32) reinterpret_cast<uint4*>(xs)[i] = make_uint4(0, 0, 0, 0);
+        for (int i = tid; i < MT * upad; i += NCW * 32) xmeta[i] = make_int2(0, 1);
+        consumer_barrier();
+    }
+    if (a.pro) {
+        fused_stage(a, xs, xmeta, slice_sum, s_slices, wmax, sxs);
     } else {
-        const int pieces_per_tok = g.K >> 4;
-        const int total = MT * pieces_per_tok;
-        for (int base = 0; base < total; base += NCW * 32) {
+        const int pieces_per_tok = a.K >> 4;
+        const int total_pieces = MT * pieces_per_tok;
+        for (int base = 0; base < total_pieces; base += NCW * 32) {
             const int pid = base + tid;
-            const bool live = pid < total;
+            const bool live = pid < total_pieces;
             int t = 0, q = 0;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (live) {
                 t = pid / pieces_per_tok;
                 q = pid - t * pieces_per_tok;
-                if (t < a.mt) v = *reinterpret_cast<const uint4*>(a.xq + (size_t)t * g.K + (size_t)q * 16);
-                *reinterpret_cast<uint4*>(xs + ((size_t)(t * 4 + (q & 3)) * U + (q >> 2)) * 16) = v;
+                if (t < a.mt) v = *reinterpret_cast<const uint4*>(a.xq + (size_t)t * a.K + (size_t)q * 16);
+                *reinterpret_cast<uint4*>(xs + stage_piece(a, t, q)) = v;
             }
             int s = __dp4a((int)v.x, 0x01010101, 0);
             s = __dp4a((int)v.y, 0x01010101, s);
@@ -365,77 +474,67 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
             s += __shfl_xor_sync(FULL, s, 1);
             s += __shfl_xor_sync(FULL, s, 2);
             if (live && (q & 3) == 0) {
-                const int u = q >> 2;
-                const int mxv = (a.mx && t < a.mt) ? (int)a.mx[(size_t)t * G + (u >> 1)] : 1;
-                xmeta[t * U + u] = make_int2(s, mxv);
+                const int lu = q >> 2;
+                const int mxv = (a.mx && t < a.mt) ? (int)a.mx[(size_t)t * a.G + (lu >> 1)] : 1;
+                xmeta[stage_unit(a, t, lu)] = make_int2(s, mxv);
             }
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+        consumer_barrier();
     }
 
-    // Record i of this CTA lands in slot i % slots and belongs to warp i % workers.  slots is a multiple of workers, so
-    // a warp meets the phases of each of its slots strictly in order (a parity wait can tell only two phases apart).
-    if (warp >= a.workers) return;
+    // Quad i of this CTA (global quad blockIdx.x + i * gridDim.x) belongs to warp i % workers; its NCH records land in
+    // that warp's own slots in order, so a warp meets the phases of each of its slots strictly in sequence (a parity
+    // wait can tell only two phases apart).
+    if (warp >= W) return;
     float sxr[MT];                               // row scales, fetched once (not once per record)
 #pragma unroll
-    for (int t = 0; t < MT; t++) sxr[t] = FUSED ? sxs[t] : (t < a.mt ? a.sx[t] : 0.0f);
-    const int lpr = 32 / g.TR;                   // lanes per row
-    const int r = lane / lpr, j = lane - r * lpr;
-    const int pu = U * 16;
+    for (int t = 0; t < MT; t++) sxr[t] = a.pro ? sxs[t] : (t < a.mt ? a.sx[t] : 0.0f);
+    const int r = lane / LPR, j = lane - r * LPR;
     bool ok = true;
-    for (int i = warp;; i += a.workers) {
-        const int rec_id = blockIdx.x + i * gridDim.x;   // i-th record of this CTA
-        if (rec_id >= g.nrec) break;
-        const int s = i % a.slots;
-        ok = mbar_wait(&full[s], (unsigned)(i / a.slots) & 1u, wl);
-        if (!ok) break;
-        const uint8_t* rec = ring + (size_t)s * g.rec_bytes;
-        const uint8_t* wp = rec + (size_t)r * g.row_bytes + j * 16;
-        const uint8_t* xp = xs + j * 16;
-        const uint16_t* mrow = reinterpret_cast<const uint16_t*>(rec + g.m_off) + r * G;
-        const int n = rec_id * g.TR + r;
-
+    for (int li = 0; ok; li++) {
+        const long long Q = (long long)blockIdx.x + (long long)(li * W + warp) * gridDim.x;
+        if (Q >= total) break;
+        const int sg = (DUAL && Q >= a.seg[0].nquads) ? 1 : 0;
+        const GemvSeg& S = a.seg[sg];
+        const int n = (int)(sg ? Q - a.seg[0].nquads : Q) * QR + r;
+        // the row's scale, in flight while the row is summed (c is indexed by the linear's own row order)
+        const float cn = (j == 0 && n < S.N) ? S.c[S.out.pairs ? (n & 1) * (S.N >> 1) + (n >> 1) : n] : 0.0f;
         long long acc[MT];
+        int accs[MT];
 #pragma unroll
-        for (int t = 0; t < MT; t++) acc[t] = 0;
-        for (int u = j; u < U; u += lpr, wp += lpr * 16, xp += lpr * 16) {
-            unsigned o[16];
-            unpack_unit<BITS>(wp, pu, o);
-            const unsigned mw = mrow[u >> 1];
+        for (int t = 0; t < MT; t++) { acc[t] = 0; accs[t] = 0; }
+        for (int c = 0; c < NCH; c++) {
+            const int lr = li * NCH + c;
+            const int s = warp * SPW + lr % SPW;
+            ok = mbar_wait(&full[s], (unsigned)(lr / SPW) & 1u, wl);
+            if (!ok) break;
+            const uint8_t* rec = ring + (size_t)s * a.slot_bytes;
+            if (DUAL && sg) quad_chunk<8, MT>(a, rec, S.m_off, c, r, j, xs, xmeta, acc, accs);
+            else quad_chunk<BITS, MT>(a, rec, S.m_off, c, r, j, xs, xmeta, acc, accs);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);   // the slot may be refilled
+        }
+        if (!ok) break;
+        float y[MT];
+#pragma unroll
+        for (int t = 0; t < MT; t++) {
+            long long tot = acc[t] + ((long long)accs[t] << 31);
+#pragma unroll
+            for (int off = 1; off < LPR; off <<= 1) tot += shfl_xor_i64(tot, off);
+            y[t] = fmul(fmul(i64_to_f32(tot), cn), sxr[t]);
+        }
+        if (a.h && !sg) {
+            // pairs layout: rows r = 0, 2 are gate rows, r + 1 their up rows; lane (r, 0) fetches up from lane (r + 1, 0)
 #pragma unroll
             for (int t = 0; t < MT; t++) {
-                int d0 = 0, d1 = 0, d2 = 0, d3 = 0;   // independent chains, summed below
-                const uint8_t* xt = xp + (size_t)t * 4 * pu;
-                const uint4 x0 = *reinterpret_cast<const uint4*>(xt);
-                const uint4 x1 = *reinterpret_cast<const uint4*>(xt + pu);
-                const uint4 x2 = *reinterpret_cast<const uint4*>(xt + 2 * (size_t)pu);
-                const uint4 x3 = *reinterpret_cast<const uint4*>(xt + 3 * (size_t)pu);
-                d0 = dot4<BITS>(o[0], (int)x0.x, d0); d1 = dot4<BITS>(o[1], (int)x0.y, d1);
-                d2 = dot4<BITS>(o[2], (int)x0.z, d2); d3 = dot4<BITS>(o[3], (int)x0.w, d3);
-                d0 = dot4<BITS>(o[4], (int)x1.x, d0); d1 = dot4<BITS>(o[5], (int)x1.y, d1);
-                d2 = dot4<BITS>(o[6], (int)x1.z, d2); d3 = dot4<BITS>(o[7], (int)x1.w, d3);
-                d0 = dot4<BITS>(o[8], (int)x2.x, d0); d1 = dot4<BITS>(o[9], (int)x2.y, d1);
-                d2 = dot4<BITS>(o[10], (int)x2.z, d2); d3 = dot4<BITS>(o[11], (int)x2.w, d3);
-                d0 = dot4<BITS>(o[12], (int)x3.x, d0); d1 = dot4<BITS>(o[13], (int)x3.y, d1);
-                d2 = dot4<BITS>(o[14], (int)x3.z, d2); d3 = dot4<BITS>(o[15], (int)x3.w, d3);
-                const int2 meta = xmeta[t * U + u];
-                int dot = (d0 + d1) + (d2 + d3);
-                if (BITS != 8) dot -= code_offset(BITS) * meta.x;
-                const unsigned mult = mw * (unsigned)meta.y;
-                acc[t] += (long long)dot * (long long)mult;
+                const float up = __shfl_down_sync(FULL, y[t], LPR);
+                if (j == 0 && (r & 1) == 0 && n < S.N && t < a.mt)
+                    a.h[(size_t)(a.t0 + t) * a.h_width + (n >> 1)] = fmul(silu_f(y[t]), up);
             }
-        }
-        const float cn = reinterpret_cast<const float*>(rec + g.c_off)[r];
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);   // the slot may be refilled
-
-#pragma unroll
-        for (int t = 0; t < MT; t++)
-            for (int off = 1; off < lpr; off <<= 1) acc[t] += shfl_xor_i64(acc[t], off);
-        if (j == 0 && n < g.N) {
+        } else if (j == 0 && n < S.N) {
 #pragma unroll
             for (int t = 0; t < MT; t++)
-                if (t < a.mt) emit(a.out, a.t0 + t, n, fmul(fmul(i64_to_f32(acc[t]), cn), sxr[t]));
+                if (t < a.mt) emit(S.out, a.t0 + t, n, y[t]);
         }
     }
     if (!ok && lane == 0) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
@@ -443,73 +542,101 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
 
 // ------------------------------------------------------------------------------------------------------------------
 struct GemvPlan {
-    int slots, workers;
+    int spw, workers;
     size_t smem;
     int grid;
 };
-// A plan by shape only: the ring takes whatever shared memory the staged activations leave, up to MAX_SLOTS records.
-static bool plan_gemv(const StreamGeom& g, int MT, GemvPlan& p) {
-    const size_t budget = smem_optin() - 1024;
-    const size_t fixed = (size_t)MT * g.K + (size_t)MT * g.U * 8 + 2 * MAX_SLOTS * 8 + (256 + NCW + 8) * 4;
-    if (fixed + 2 * (size_t)g.rec_bytes > budget) return false;
-    int slots = (int)((budget - fixed) / g.rec_bytes);
+// Measurement switch (det_debug_set_gemv): bit 0 = a CTA may take a whole SM's shared memory (no co-residency with the
+// next launch); bits 8.. = CTAs per SM of one launch (default 1).  Results do not depend on it.
+static int g_gemv_flags = 0;
+
+// A plan by shape only.  The ring takes what the staged activations leave of HALF an SM's shared memory (so that the
+// next launch's CTAs fit beside this one's), two or three slots per worker warp; passes whose staged activations do not
+// fit that (many tokens of a long row) take the whole SM.
+static bool plan_gemv(int K, int slot_bytes, int MT, long long total_quads, GemvPlan& p) {
+    const StreamGeom g = stream_geom(QR, K, 8);
+    const int upad = g.NCH * g.UC;
+    const size_t fixed = (size_t)MT * upad * 64 + (size_t)MT * upad * 8 + 2 * MAX_SLOTS * 8 + (512 + NCW + 8) * 4;
+    const size_t whole = smem_optin() - 1024;
+    const size_t half = (smem_optin() + 1024) / 2 - 1024 - 512;      // two CTAs per SM: 1 KB of each is reserved
+    size_t budget = (MT <= 2 && !(g_gemv_flags & 1)) ? half : whole;
+    if (fixed + 2 * (size_t)slot_bytes > budget) budget = whole;
+    if (fixed + 2 * (size_t)slot_bytes > budget) return false;
+    int slots = (int)((budget - fixed) / slot_bytes);
     if (slots > MAX_SLOTS) slots = MAX_SLOTS;
-    p.workers = slots < NCW ? slots : NCW;
-    slots -= slots % p.workers;
-    p.slots = slots;
-    p.smem = fixed + (size_t)slots * g.rec_bytes;
-    const int sms = sm_count();
-    p.grid = g.nrec < sms ? g.nrec : sms;
+    p.workers = slots / 2 < NCW ? slots / 2 : NCW;
+    if (p.workers < 1) p.workers = 1;
+    p.spw = slots / p.workers;
+    if (p.spw > 3) p.spw = 3;
+    p.smem = fixed + (size_t)p.workers * p.spw * slot_bytes;
+    const int per_sm = (g_gemv_flags >> 8) > 0 ? (g_gemv_flags >> 8) : 1;
+    const long long cap = (long long)sm_count() * per_sm;
+    p.grid = (int)(total_quads < cap ? total_quads : cap);
     return true;
 }
 
-template <int BITS, int MT, bool FUSED>
+template <int BITS, int MT, bool DUAL>
 static void launch_gemv_one(const GemvArgs& a, const GemvPlan& p, cudaStream_t q) {
     static bool configured = false;
     if (!configured) {
-        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemv_stream<BITS, MT, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemv_stream<BITS, MT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)(smem_optin())));
         configured = true;
     }
-    launch_pdl(k_gemv_stream<BITS, MT, FUSED>, dim3(p.grid), dim3(GEMV_THREADS), p.smem, q, 1, a);
+    launch_pdl(k_gemv_stream<BITS, MT, DUAL>, dim3(p.grid), dim3(GEMV_THREADS), p.smem, q, 1, a);
 }
 template <int BITS, int MT>
-static void launch_gemv(const GemvArgs& a, const GemvPlan& p, cudaStream_t q) {
-    if (a.pro) launch_gemv_one<BITS, MT, true>(a, p, q);
+static void launch_gemv(const GemvArgs& a, const GemvPlan& p, bool dual, cudaStream_t q) {
+    if (dual) launch_gemv_one<BITS, MT, true>(a, p, q);
     else launch_gemv_one<BITS, MT, false>(a, p, q);
 }
 
 template <int BITS>
-static void gemv_stream_bits(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
-                             const OutSpec& out, cudaStream_t q, const det_act_source* src) {
+static void gemv_stream_bits(const GemvCall& call, cudaStream_t q) {
+    const det_qlinear* L = call.lin;
     const StreamGeom g = stream_geom(L->N, L->K, BITS);
+    DETB_REQUIRE(g.G <= 256, "K is too large for the streaming GEMV");
+    const bool dual = call.lin2 != nullptr;
+    StreamGeom g2 = g;
+    if (dual) {
+        DETB_REQUIRE((call.lin2->bits & 0xff) == 8 && (call.lin2->bits & DET_LAYOUT_STREAM) && call.lin2->K == L->K,
+                     "the second linear of a GEMV launch is a W8 streaming-layout linear over the same input");
+        g2 = stream_geom(call.lin2->N, call.lin2->K, 8);
+    }
+    const det_act_source* src = call.src;
     int t0 = 0;
-    while (t0 < M) {
-        const int left = M - t0;
+    while (t0 < call.M) {
+        const int left = call.M - t0;
         int MT = left >= 5 ? 8 : (left >= 3 ? 4 : left);
+        const int slot_bytes = dual && g2.rec_bytes > g.rec_bytes ? g2.rec_bytes : g.rec_bytes;
         GemvPlan p;
-        while (!plan_gemv(g, MT, p)) {
+        while (!plan_gemv(L->K, slot_bytes, MT, (long long)g.nquads + (dual ? g2.nquads : 0), p)) {
             DETB_REQUIRE(MT > 1, "K is too large for the streaming GEMV");
             MT >>= 1;
         }
         GemvArgs a;
-        a.w = L->wq;
-        a.g = g;
-        a.xq = xq + (size_t)t0 * g.K;
-        a.sx = sx + t0;
-        a.mx = mx ? mx + (size_t)t0 * g.G : nullptr;
+        a.seg[0] = GemvSeg{L->wq, L->c, L->N, g.nquads, g.rec_bytes, g.m_off, call.out};
+        a.seg[1] = a.seg[0];
+        if (dual) a.seg[1] = GemvSeg{call.lin2->wq, call.lin2->c, call.lin2->N, g2.nquads, g2.rec_bytes, g2.m_off, call.out2};
+        a.K = g.K; a.U = g.U; a.G = g.G; a.UC = g.UC; a.NCH = g.NCH;
+        a.slot_bytes = slot_bytes;
+        a.xq = call.xq ? call.xq + (size_t)t0 * g.K : nullptr;
+        a.sx = call.sx ? call.sx + t0 : nullptr;
+        a.mx = call.mx ? call.mx + (size_t)t0 * g.G : nullptr;
         a.t0 = t0;
         a.mt = left < MT ? left : MT;
-        a.slots = p.slots;
+        a.spw = p.spw;
         a.workers = p.workers;
         a.error_flag = error_word();
-        a.out = out;
         a.pro = 0;
+        a.pa = a.pb = nullptr;
+        a.eps = 0.0f;
+        a.pslices = 0;
+        a.xq_out = nullptr; a.sx_out = nullptr; a.mx_out = nullptr;
         if (src) {
-            DETB_REQUIRE(g.G <= FUSED_MAX_ROUNDS * NCW, "K is too large for the fused activation prologue");
             a.pro = src->kind;
             a.pa = src->a + (size_t)t0 * g.K;
-            a.pb = src->kind == PRO_SWIGLU ? src->b + (size_t)t0 * g.K : src->b;
+            a.pb = src->b;
             a.eps = src->eps;
             int P = 128;
             while (P < g.K) P <<= 1;
@@ -518,26 +645,32 @@ static void gemv_stream_bits(const det_qlinear* L, const int8_t* xq, const float
             a.sx_out = src->sx ? src->sx + t0 : nullptr;
             a.mx_out = src->mx ? src->mx + (size_t)t0 * g.G : nullptr;
         }
+        a.h = call.h;
+        a.h_width = L->N / 2;
         switch (MT) {
-            case 1: launch_gemv<BITS, 1>(a, p, q); break;
-            case 2: launch_gemv<BITS, 2>(a, p, q); break;
-            case 4: launch_gemv<BITS, 4>(a, p, q); break;
-            default: launch_gemv<BITS, 8>(a, p, q); break;
+            case 1: launch_gemv<BITS, 1>(a, p, dual, q); break;
+            case 2: launch_gemv<BITS, 2>(a, p, dual, q); break;
+            case 4: launch_gemv<BITS, 4>(a, p, dual, q); break;
+            default: launch_gemv<BITS, 8>(a, p, dual, q); break;
         }
         t0 += a.mt;
     }
 }
 
-void gemv_stream_launch(const det_qlinear* L, int bits, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
-                        const OutSpec& out, cudaStream_t q, const det_act_source* src) {
-    if (src) {
-        DETB_REQUIRE(src->kind >= PRO_RMS && src->kind <= PRO_SWIGLU && src->a, "bad activation source");
-        DETB_REQUIRE((src->xq != nullptr) == (src->sx != nullptr) && (src->xq != nullptr) == (src->mx != nullptr),
+void gemv_stream_launch(const GemvCall& call, cudaStream_t q) {
+    const int bits = call.lin->bits & 0xff;
+    if (call.src) {
+        DETB_REQUIRE((call.src->kind == PRO_RMS || call.src->kind == PRO_PLAIN) && call.src->a, "bad activation source");
+        DETB_REQUIRE(call.src->kind != PRO_RMS || call.src->b, "RMSNorm needs its weight");
+        DETB_REQUIRE((call.src->xq != nullptr) == (call.src->sx != nullptr) && (call.src->xq != nullptr) == (call.src->mx != nullptr),
                      "the quantized-row outputs come all together or not at all");
+    } else {
+        DETB_REQUIRE(call.xq && call.sx, "a GEMV needs its quantized input rows");
     }
-    if (bits == 8) gemv_stream_bits<8>(L, xq, sx, mx, M, out, q, src);
-    else if (bits == 6) gemv_stream_bits<6>(L, xq, sx, mx, M, out, q, src);
-    else gemv_stream_bits<4>(L, xq, sx, mx, M, out, q, src);
+    if (call.h) DETB_REQUIRE((call.lin->bits & DET_LAYOUT_PAIRS) && call.lin->N % 2 == 0, "the SwiGLU epilogue needs the pairs layout");
+    if (bits == 8) gemv_stream_bits<8>(call, q);
+    else if (bits == 6) gemv_stream_bits<6>(call, q);
+    else gemv_stream_bits<4>(call, q);
 }
 
 }  // namespace detb
@@ -549,16 +682,20 @@ extern "C" {
 size_t det_linear_repack_bytes(int N, int K, int bits) {
     DETB_REQUIRE((bits == 4 || bits == 6 || bits == 8) && K > 0 && K % 128 == 0 && N > 0, "bad linear shape");
     const StreamGeom g = stream_geom(N, K, bits);
-    return (size_t)g.nrec * g.rec_bytes;
+    return (size_t)g.nquads * g.NCH * g.rec_bytes;
 }
 
-void det_linear_repack(const det_qlinear* src, void* dst, cudaStream_t st) {
+static void repack(const det_qlinear* src, void* dst, int pairs, cudaStream_t st) {
     DETB_REQUIRE((src->bits == 4 || src->bits == 6 || src->bits == 8) && src->K % 128 == 0, "bad linear shape");
+    DETB_REQUIRE(!pairs || src->N % 2 == 0, "the pairs layout needs an even number of rows");
     const StreamGeom g = stream_geom(src->N, src->K, src->bits);
-    const long long work = (long long)g.nrec * g.TR * g.U;
-    k_repack_stream<<<(unsigned)((work + 127) / 128), 128, 0, queue_of(st)>>>(src->wq, src->c, src->m, g,
-                                                                             (uint8_t*)dst);
+    const long long work = (long long)g.nquads * QR * g.NCH * g.UC;
+    k_repack_stream<<<(unsigned)((work + 127) / 128), 128, 0, queue_of(st)>>>(src->wq, src->m, g, pairs, (uint8_t*)dst);
     DETB_CUDA_OK(cudaGetLastError());
 }
+void det_linear_repack(const det_qlinear* src, void* dst, cudaStream_t st) { repack(src, dst, 0, st); }
+void det_linear_repack_pairs(const det_qlinear* src, void* dst, cudaStream_t st) { repack(src, dst, 1, st); }
+
+void det_debug_set_gemv(int flags) { g_gemv_flags = flags; }
 
 }  // extern "C"

@@ -186,15 +186,6 @@ class Backend {
                                 const Buf<float>& v, const Buf<float>& o);
     virtual void gdn_rows(const GdnLayer& l, const RowSet& rows, const GdnShape& s /* m = rows */, const Buf<float>& qkv,
                           const Buf<float>& z, const Buf<float>& a, const Buf<float>& b, const Buf<float>& on);
-    // Decode step of a Gated DeltaNet layer that also computes the layer's a and b projections (`ab`: the fused linear
-    // [a | b] applied to the quantized layer input xq / sx / mx) inside the mixer: st != nullptr for one sequence (s.m = 1),
-    // rows != nullptr for a batched step.  Returns false when the backend has no such form; the caller then projects a and b
-    // itself and calls gdn() / gdn_rows().  Same values either way.
-    virtual bool gdn_decode_ab(const GdnLayer&, const GdnState*, const RowSet*, const GdnShape&, const Linear&,
-                               const Buf<int8_t>&, const Buf<float>&, const Buf<uint16_t>&, const Buf<float>&,
-                               const Buf<float>&, const Buf<float>&) {
-        return false;
-    }
     // argmax / sample of `rows` logits rows at once (row r uses draw z[r]); the defaults loop over the single-row ops.
     virtual std::vector<int32_t> argmax_rows(const Buf<float>& logits, size_t rows, size_t v) {
         std::vector<int32_t> out(rows);

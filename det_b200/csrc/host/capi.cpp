@@ -48,13 +48,13 @@ int dh_backend_name(void* b, char* out, size_t cap) {
         return std::string();
     });
 }
-// Profiling / measurement switches of a CUDA backend handle (see CudaBackend::skip_mask, fuse_activations).
-void dh_cuda_debug(void* b, unsigned skip_mask, int fuse_activations) {
+// Profiling / measurement switches of a CUDA backend handle (see CudaBackend::skip_mask, fuse_decode).
+void dh_cuda_debug(void* b, unsigned skip_mask, int fuse_decode) {
     auto* cb = dynamic_cast<det::CudaBackend*>(static_cast<det::Backend*>(b));
     if (!cb) return;
+    cb->flush();
     cb->skip_mask = skip_mask;
-    cb->fuse_activations = fuse_activations != 0;
-    if (fuse_activations > 1) cb->fuse_kinds = (unsigned)fuse_activations;   // a mask of DET_ACT_* bits
+    cb->fuse_decode = fuse_decode != 0;
 }
 // The primitive test hook of the CUDA backend (cuda.rs:474-490).
 void dh_cuda_test_prim(int op, const float* x, size_t len, size_t m, size_t n, float* out, size_t out_len) {
@@ -200,15 +200,6 @@ size_t dh_graph_decoder_finish(void* d, int32_t* out, size_t cap) {
 // Measurement switch of the CUDA backend: 0 composes a batched step from per-sequence attention / GDN calls.
 void dh_cuda_set_fuse_rows(void* backend, int on) {
     if (auto* c = dynamic_cast<det::CudaBackend*>(static_cast<det::Backend*>(backend))) c->fuse_rows = on != 0;
-}
-void dh_cuda_set_fuse_gdn_quant(void* backend, int on) {
-    if (auto* c = dynamic_cast<det::CudaBackend*>(static_cast<det::Backend*>(backend))) {
-        c->flush();
-        c->fuse_gdn_quant = on != 0;
-    }
-}
-void dh_cuda_set_fold_ab(void* backend, int on) {
-    if (auto* c = dynamic_cast<det::CudaBackend*>(static_cast<det::Backend*>(backend))) c->fold_ab = on != 0;
 }
 // ---- batched serving decode (serve.hpp)
 void* dh_batch_new(void* model, size_t n_seq, size_t ctx) {

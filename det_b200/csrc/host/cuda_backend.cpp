@@ -59,32 +59,84 @@ void CudaBackend::sync() {
 bool CudaBackend::hold(int kind, const float* a, const float* b, float eps, size_t m, size_t n, int8_t* xq, float* sx,
                        uint16_t* mx) {
     flush_pending();
-    if (!fuse_activations || !(fuse_kinds & (1u << kind)) || !stream_layout || m > (size_t)stream_max_m || n % 128 != 0 || n > 18432 || !mx) return false;
+    if (!fuse_decode || !stream_layout || m > (size_t)stream_max_m || n % 128 != 0 || n > 32768 || !mx) return false;
     pending_.kind = kind;
     pending_.a = a; pending_.b = b; pending_.eps = eps;
     pending_.m = m; pending_.n = n;
     pending_.xq = xq; pending_.sx = sx; pending_.mx = mx;
     return true;
 }
-void CudaBackend::flush_gdn() {
-    if (!pending_gdn_.on) return;
-    const PendingGdn g = pending_gdn_;
-    pending_gdn_.on = false;
-    det_gdn_state st = g.state;
-    void* sc = scratch(gdn_scratch_, det_gdn_scratch_bytes(1, g.n_k, g.n_v, g.dk, g.dv));
-    det_gdn_ex(&g.layer, &st, g.qkv, g.z, g.a, g.b, g.eps, 1, g.n_k, g.n_v, g.dk, g.dv, g.out, sc, nullptr, nullptr, ST);
-}
 void CudaBackend::flush_pending() {
-    flush_gdn();
+    if (pending_gemm_.on) {
+        const PendingGemm g = pending_gemm_;
+        pending_gemm_.on = false;
+        issue_gemv(g, nullptr, nullptr, nullptr);
+    }
     if (!pending_.kind) return;
     const PendingAct p = pending_;
     pending_.kind = 0;
     if (p.kind == DET_ACT_RMSNORM)
         det_rmsnorm_quant(p.a, p.b, p.eps, (int)p.m, (int)p.n, nullptr, p.xq, p.sx, p.mx, ST);
-    else if (p.kind == DET_ACT_PLAIN)
-        det_quant(p.a, (int)p.m, (int)p.n, p.xq, p.sx, p.mx, ST);
     else
-        det_silu_mul_quant(p.a, p.b, (int)p.m, (int)p.n, nullptr, p.xq, p.sx, p.mx, ST);
+        det_quant(p.a, (int)p.m, (int)p.n, p.xq, p.sx, p.mx, ST);
+}
+
+// One decode GEMV launch: linear g.lin (with the quantization it absorbed as its prologue), optionally a second W8
+// linear over the same rows, optionally the SwiGLU product instead of the outputs of g.lin.
+void CudaBackend::issue_gemv(const PendingGemm& g, const CudaLinear* second, const std::vector<float*>* dsts2, float* h) {
+    auto describe = [](const CudaLinear& l) {
+        det_qlinear q;
+        q.wq = l.stream.ptr();
+        q.c = l.c.ptr();
+        q.m = l.m.ptr();
+        q.N = (int)l.n();
+        q.K = (int)l.k;
+        q.bits = l.bits | DET_LAYOUT_STREAM | (l.pairs ? DET_LAYOUT_PAIRS : 0);
+        return q;
+    };
+    auto offsets = [](const CudaLinear& l) {
+        std::vector<int> offs;
+        int acc = 0;
+        for (size_t w : l.widths) {
+            offs.push_back(acc);
+            acc += (int)w;
+        }
+        return offs;
+    };
+    const det_qlinear q1 = describe(*g.lin);
+    det_qlinear q2{};
+    const std::vector<int> offs1 = offsets(*g.lin);
+    std::vector<int> offs2;
+    det_act_source src{};
+    det_gemv_op op{};
+    op.lin = &q1;
+    if (g.act.kind) {
+        src.kind = g.act.kind;
+        src.a = g.act.a; src.b = g.act.b; src.eps = g.act.eps;
+        src.xq = g.act.xq; src.sx = g.act.sx; src.mx = g.act.mx;
+        op.src = &src;
+    } else {
+        op.xq = g.xq; op.sx = g.sx; op.mx = g.mx;
+    }
+    op.M = (int)g.m;
+    if (g.accumulate) {
+        op.y = g.dsts[0];
+        op.accumulate = 1;
+    } else {
+        op.nparts = (int)g.dsts.size();
+        op.offs = offs1.data();
+        op.dsts = g.dsts.data();
+    }
+    if (second) {
+        q2 = describe(*second);
+        offs2 = offsets(*second);
+        op.lin2 = &q2;
+        op.nparts2 = (int)dsts2->size();
+        op.offs2 = offs2.data();
+        op.dsts2 = dsts2->data();
+    }
+    op.h = h;
+    det_gemv(&op, ST);
 }
 
 void* CudaBackend::scratch(Buf<uint8_t>& slot, size_t bytes) {   // cuda.rs:81-87
@@ -99,8 +151,12 @@ void CudaBackend::finish_linear(CudaLinear& l) {
         det_linear_expand(&src, l.wq8.ptr(), ST);
     }
     if (!stream_layout) return;
+    // two equal halves of a narrow-code linear (gate | up): rows interleaved, so that a decode GEMV can emit the SwiGLU
+    // product of a (gate, up) pair from its epilogue (det_linear_repack_pairs); plain outputs are routed back per part
+    l.pairs = l.widths.size() == 2 && l.widths[0] == l.widths[1] && l.bits != 8;
     l.stream = alloc<uint8_t>(det_linear_repack_bytes((int)l.n(), (int)l.k, l.bits));
-    det_linear_repack(&src, l.stream.ptr(), ST);
+    if (l.pairs) det_linear_repack_pairs(&src, l.stream.ptr(), ST);
+    else det_linear_repack(&src, l.stream.ptr(), ST);
     if (!keep_rowmajor) {
         det_sync();
         l.wq = Buf<uint8_t>();
@@ -172,17 +228,6 @@ void CudaBackend::rmsnorm_quant(const Buf<float>& x, const Buf<float>& w, float 
 void CudaBackend::quant(const Buf<float>& x, size_t m, size_t n, const Buf<int8_t>& xq, const Buf<float>& sx,
                         const Buf<uint16_t>& mx) {
     if (skip_mask & 2) return;
-    if (pending_gdn_.on && m == 1 && x.ptr() == pending_gdn_.out && n == (size_t)pending_gdn_.n_v * pending_gdn_.dv) {
-        // the single-token Gated DeltaNet step that was held back, with this quantization folded into its last kernel
-        const PendingGdn g = pending_gdn_;
-        pending_gdn_.on = false;
-        flush_pending();
-        det_gdn_state st = g.state;
-        void* sc = scratch(gdn_scratch_, det_gdn_scratch_bytes(1, g.n_k, g.n_v, g.dk, g.dv));
-        det_gdn_quant(&g.layer, &st, g.qkv, g.z, g.a, g.b, g.eps, g.n_k, g.n_v, g.dk, g.dv, g.out, xq.ptr(), sx.ptr(), mx.ptr(),
-                      sc, ST);
-        return;
-    }
     if (hold(DET_ACT_PLAIN, x.ptr(), nullptr, 0.0f, m, n, xq.ptr(), sx.ptr(), mx.ptr())) return;
     det_quant(x.ptr(), (int)m, (int)n, xq.ptr(), sx.ptr(), mx.ptr(), ST);
 }
@@ -191,63 +236,85 @@ void CudaBackend::quant(const Buf<float>& x, size_t m, size_t n, const Buf<int8_
 void CudaBackend::gemm(const Linear& lin_, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx,
                        size_t m, const GemmOut& out) {
     const CudaLinear& lin = static_cast<const CudaLinear&>(lin_);
-    flush_gdn();
     if (skip_mask & 8) {
         pending_.kind = 0;
+        pending_gemm_.on = false;
         return;
     }
-    det_qlinear q;
     const bool use_stream = lin.stream.ptr() && (m <= (size_t)stream_max_m || !lin.wq.ptr());
-    q.wq = use_stream ? lin.stream.ptr() : lin.wq.ptr();
-    q.c = lin.c.ptr();
-    q.m = lin.m.ptr();
-    q.N = (int)lin.n();
-    q.K = (int)lin.k;
-    q.bits = use_stream ? (lin.bits | DET_LAYOUT_STREAM) : lin.bits;
-    if (!use_stream && lin.wq8.ptr()) {
-        q.wq = lin.wq8.ptr();
-        q.bits = lin.bits | DET_LAYOUT_INT8;
+    if (out.kind == GemmOut::Parts && out.dst.size() != lin.widths.size()) throw std::logic_error("gemm: part count mismatch");
+    std::vector<float*> ptrs;
+    for (const Buf<float>* d : out.dst) ptrs.push_back(d->ptr());
+    // a held multi-part GEMV takes a small W8 linear over the same rows into its launch (qkv|z + a|b)
+    if (pending_gemm_.on) {
+        const PendingGemm& g = pending_gemm_;
+        const bool same_rows = g.act.kind ? (g.act.xq == xq.ptr() && g.act.sx == sx.ptr() && g.act.mx == mx.ptr())
+                                          : (g.xq == xq.ptr() && g.sx == sx.ptr() && g.mx == mx.ptr());
+        if (use_stream && same_rows && g.m == m && lin.bits == 8 && !lin.pairs && lin.k == g.lin->k && lin.n() <= 4096 &&
+            out.kind != GemmOut::Accumulate) {
+            const PendingGemm first = g;
+            pending_gemm_.on = false;
+            issue_gemv(first, &lin, &ptrs, nullptr);
+            return;
+        }
+        flush_pending();
     }
     // absorb a held activation quantization when this GEMM is its consumer and nothing it writes feeds the producer
-    det_act_source src{};
-    const det_act_source* fused = nullptr;
+    PendingAct act;
     if (pending_.kind) {
         bool ok = use_stream && pending_.xq == xq.ptr() && pending_.sx == sx.ptr() && pending_.mx == mx.ptr() &&
                   pending_.m == m && pending_.n == lin.k;
-        for (const Buf<float>* d : out.dst)
-            if (d->ptr() == pending_.a || d->ptr() == pending_.b) ok = false;
+        for (float* d : ptrs)
+            if (d == pending_.a || d == pending_.b) ok = false;
         if (ok) {
-            src.kind = pending_.kind;
-            src.a = pending_.a; src.b = pending_.b; src.eps = pending_.eps;
-            src.xq = pending_.xq; src.sx = pending_.sx; src.mx = pending_.mx;
-            fused = &src;
+            act = pending_;
             pending_.kind = 0;
         } else {
             flush_pending();
         }
     }
-    auto run = [&](float* y, int accumulate, int nparts, const int* offs, float* const* dsts) {
-        if (fused) det_gemm_fused(&q, fused, (int)m, y, accumulate, nparts, offs, dsts, ST);
-        else det_gemm_ex(&q, xq.ptr(), sx.ptr(), mx.ptr(), (int)m, y, accumulate, nparts, offs, dsts, ST);
-    };
+    if (use_stream && m <= (size_t)stream_max_m) {
+        PendingGemm g;
+        g.on = true;
+        g.lin = &lin;
+        g.act = act;
+        g.xq = xq.ptr(); g.sx = sx.ptr(); g.mx = mx.ptr();
+        g.m = m;
+        g.dsts = ptrs;
+        g.accumulate = out.kind == GemmOut::Accumulate;
+        if (fuse_decode && out.kind == GemmOut::Parts) {      // may still grow into a dual or a SwiGLU launch
+            pending_gemm_ = g;
+            return;
+        }
+        issue_gemv(g, nullptr, nullptr, nullptr);
+        return;
+    }
+    det_qlinear q;
+    q.wq = use_stream ? lin.stream.ptr() : lin.wq.ptr();
+    q.c = lin.c.ptr();
+    q.m = lin.m.ptr();
+    q.N = (int)lin.n();
+    q.K = (int)lin.k;
+    q.bits = use_stream ? (lin.bits | DET_LAYOUT_STREAM | (lin.pairs ? DET_LAYOUT_PAIRS : 0)) : lin.bits;
+    if (!use_stream && lin.wq8.ptr()) {
+        q.wq = lin.wq8.ptr();
+        q.bits = lin.bits | DET_LAYOUT_INT8;
+    }
     switch (out.kind) {
         case GemmOut::Write:
-            run(out.dst[0]->ptr(), 0, 0, nullptr, nullptr);
+            det_gemm_ex(&q, xq.ptr(), sx.ptr(), mx.ptr(), (int)m, ptrs[0], 0, 0, nullptr, nullptr, ST);
             break;
         case GemmOut::Accumulate:
-            run(out.dst[0]->ptr(), 1, 0, nullptr, nullptr);
+            det_gemm_ex(&q, xq.ptr(), sx.ptr(), mx.ptr(), (int)m, ptrs[0], 1, 0, nullptr, nullptr, ST);
             break;
         case GemmOut::Parts: {
-            if (out.dst.size() != lin.widths.size()) throw std::logic_error("gemm: part count mismatch");
             std::vector<int> offs;
-            std::vector<float*> ptrs;
             int acc = 0;
-            for (size_t i = 0; i < lin.widths.size(); i++) {
+            for (size_t w : lin.widths) {
                 offs.push_back(acc);
-                acc += (int)lin.widths[i];
-                ptrs.push_back(out.dst[i]->ptr());
+                acc += (int)w;
             }
-            run(nullptr, 0, (int)offs.size(), offs.data(), ptrs.data());
+            det_gemm_ex(&q, xq.ptr(), sx.ptr(), mx.ptr(), (int)m, nullptr, 0, (int)offs.size(), offs.data(), ptrs.data(), ST);
             break;
         }
     }
@@ -256,7 +323,18 @@ void CudaBackend::gemm(const Linear& lin_, const Buf<int8_t>& xq, const Buf<floa
 void CudaBackend::silu_mul_quant(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<int8_t>& hq,
                                  const Buf<float>& sh, const Buf<uint16_t>& mh) {
     if (skip_mask & 4) return;
-    if (hold(DET_ACT_SWIGLU, g.ptr(), u.ptr(), 0.0f, m, n, hq.ptr(), sh.ptr(), mh.ptr())) return;
+    // the held gate|up GEMV emits the product itself; its quantization becomes the next GEMV's prologue
+    if (pending_gemm_.on && pending_gemm_.lin->pairs && pending_gemm_.dsts.size() == 2 && pending_gemm_.dsts[0] == g.ptr() &&
+        pending_gemm_.dsts[1] == u.ptr() && pending_gemm_.m == m && pending_gemm_.lin->n() == 2 * n && n % 128 == 0) {
+        const PendingGemm first = pending_gemm_;
+        pending_gemm_.on = false;
+        if (swiglu_h_.len() < (size_t)stream_max_m * n) swiglu_h_ = alloc<float>((size_t)stream_max_m * n);
+        issue_gemv(first, nullptr, nullptr, swiglu_h_.ptr());
+        if (hold(DET_ACT_PLAIN, swiglu_h_.ptr(), nullptr, 0.0f, m, n, hq.ptr(), sh.ptr(), mh.ptr())) return;
+        det_quant(swiglu_h_.ptr(), (int)m, (int)n, hq.ptr(), sh.ptr(), mh.ptr(), ST);
+        return;
+    }
+    flush_pending();
     det_silu_mul_quant(g.ptr(), u.ptr(), (int)m, (int)n, nullptr, hq.ptr(), sh.ptr(), mh.ptr(), ST);
 }
 
@@ -284,16 +362,6 @@ void CudaBackend::gdn(const GdnLayer& l, const GdnState& st, const GdnShape& s, 
     flush_pending();
     det_gdn_layer layer{l.conv->ptr(), l.a->ptr(), l.dt_bias->ptr(), l.norm->ptr()};
     det_gdn_state state{st.conv_state.ptr(), st.s.ptr()};
-    if (fuse_gdn_quant && s.m == 1 && !ex.gin && !ex.gout && s.n_v <= 64) {
-        pending_gdn_.on = true;
-        pending_gdn_.layer = layer;
-        pending_gdn_.state = state;
-        pending_gdn_.qkv = qkv.ptr(); pending_gdn_.z = z.ptr(); pending_gdn_.a = a.ptr(); pending_gdn_.b = b.ptr();
-        pending_gdn_.out = on.ptr();
-        pending_gdn_.eps = s.eps;
-        pending_gdn_.n_k = (int)s.n_k; pending_gdn_.n_v = (int)s.n_v; pending_gdn_.dk = (int)s.dk; pending_gdn_.dv = (int)s.dv;
-        return;
-    }
     void* sc = scratch(gdn_scratch_, det_gdn_scratch_bytes((int)s.m, (int)s.n_k, (int)s.n_v, (int)s.dk, (int)s.dv));
     det_gdn_ex(&layer, &state, qkv.ptr(), z.ptr(), a.ptr(), b.ptr(), s.eps, (int)s.m, (int)s.n_k, (int)s.n_v,
                (int)s.dk, (int)s.dv, on.ptr(), sc, ex.gin ? ex.gin->ptr() : nullptr, ex.gout ? ex.gout->ptr() : nullptr,
@@ -306,25 +374,6 @@ struct CudaRowSet : RowSet {
     Buf<uint8_t> table;   // det_kv_cache[rows] or det_gdn_state[rows] in device memory
 };
 }  // namespace
-
-bool CudaBackend::gdn_decode_ab(const GdnLayer& l, const GdnState* st, const RowSet* rows, const GdnShape& s,
-                                const Linear& ab, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx,
-                                const Buf<float>& qkv, const Buf<float>& z, const Buf<float>& on) {
-    const CudaLinear& lin = static_cast<const CudaLinear&>(ab);
-    const CudaRowSet* rs = rows ? dynamic_cast<const CudaRowSet*>(rows) : nullptr;
-    if (!fold_ab || lin.bits != 8 || lin.wq.len() == 0 || lin.n() != 2 * s.n_v || (rows && (!rs || !fuse_rows)) ||
-        (!rows && s.m != 1) || (skip_mask & (8 | 32)))
-        return false;
-    flush_pending();
-    det_gdn_layer layer{l.conv->ptr(), l.a->ptr(), l.dt_bias->ptr(), l.norm->ptr()};
-    det_gdn_state state{st ? st->conv_state.ptr() : nullptr, st ? st->s.ptr() : nullptr};
-    det_qlinear q{lin.wq.ptr(), lin.c.ptr(), lin.m.ptr(), (int)lin.n(), (int)lin.k, 8};
-    void* sc = scratch(gdn_scratch_, det_gdn_scratch_bytes((int)s.m, (int)s.n_k, (int)s.n_v, (int)s.dk, (int)s.dv));
-    det_gdn_ab(&layer, st ? &state : nullptr, rs ? reinterpret_cast<const det_gdn_state*>(rs->table.ptr()) : nullptr, &q,
-               xq.ptr(), sx.ptr(), mx.ptr(), qkv.ptr(), z.ptr(), s.eps, (int)s.m, (int)s.n_k, (int)s.n_v, (int)s.dk,
-               (int)s.dv, on.ptr(), sc, ST);
-    return true;
-}
 
 std::vector<int32_t> CudaBackend::argmax_rows(const Buf<float>& logits, size_t rows, size_t v) {
     if (!fuse_rows) return Backend::argmax_rows(logits, rows, v);

@@ -12,6 +12,7 @@ struct CudaLinear : Linear {
     Buf<uint16_t> m;       // [N][K/128]
     Buf<uint8_t> stream;   // det_linear_repack layout
     Buf<uint8_t> wq8;      // det_linear_expand layout (signed int8 codes) for the tensor-core GEMM
+    bool pairs = false;    // the streaming copy interleaves the rows of two equal halves (det_linear_repack_pairs)
 };
 
 class CudaBackend : public Backend {
@@ -51,15 +52,6 @@ class CudaBackend : public Backend {
     std::vector<int32_t> argmax_rows(const Buf<float>& logits, size_t rows, size_t v) override;
     std::vector<int32_t> sample_rows(const Buf<float>& logits, size_t rows, size_t v, float inv_temp, size_t top_k,
                                      float top_p, const std::vector<uint64_t>& z) override;
-    bool gdn_decode_ab(const GdnLayer& l, const GdnState* st, const RowSet* rows, const GdnShape& s, const Linear& ab,
-                       const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx, const Buf<float>& qkv,
-                       const Buf<float>& z, const Buf<float>& on) override;
-    // gdn_decode_ab is off by default: measured on the 27B shape it lengthens every recurrence CTA's critical path by more
-    // than the a|b GEMV launch it removes costs (6.79 vs 6.55 ms per token)
-    bool fold_ab = false;
-    // held-back single-token gdn() + quant as det_gdn_quant: off by default — measured slower on the 27B shape (6.57 vs
-    // 6.21 ms per token: the one CTA that quantizes the row is slower than the cluster kernel it replaces)
-    bool fuse_gdn_quant = false;
     bool fuse_rows = true;
     void add(const Buf<float>& x, const Buf<float>& y, size_t n) override;
     void silu_mul(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<float>& h) override;
@@ -75,14 +67,14 @@ class CudaBackend : public Backend {
     int stream_max_m = 8;         // batches up to this many tokens go through the streaming GEMV
     bool int8_layout = true;      // build the int8-expanded copy; larger batches then run on the tensor cores
 
-    // Fuse the activation quantization (rmsnorm_quant / quant / silu_mul_quant) into the prologue of the GEMM that
-    // consumes it when that GEMM is a decode-sized streaming GEMV (det_gemm_fused).  The quantization call is held
-    // back until the next op: a matching gemm() absorbs it, anything else runs it on its own first.  Results are
-    // bit-identical either way.  Off by default: measured on the 27B decode step the redundant per-CTA prologue costs
-    // more than the separate cluster kernels it removes (+0.3 to +0.9 ms per token depending on the kind).
-    bool fuse_activations = false;
-    unsigned fuse_kinds = 0xE;   // bit DET_ACT_* set: that kind may be fused
-
+    // Decode-sized calls (at most stream_max_m rows on the streaming layout) are fused across ops.  A quantization call
+    // (rmsnorm_quant / quant) is held back until the next op: a matching gemm() absorbs it as its prologue, anything else
+    // runs it on its own first.  A gemm() with several output parts is held back the same way: when a small W8 linear
+    // over the same input follows (the GDN a|b projection after qkv|z) both go out as ONE launch; when
+    // silu_mul_quant() over its two parts follows and the linear is stored in the pairs layout, the GEMV emits the SwiGLU
+    // product from its epilogue and the quantization of that product becomes the next GEMV's prologue.  Results are
+    // bit-identical either way (tests/test_gemv_fused_gpu.py); `fuse_decode = false` issues every op on its own.
+    bool fuse_decode = true;
     // Profiling aid: op families in this mask are not launched at all (results are then meaningless); the time a
     // decode step loses without a family is that family's cost.  1 rmsnorm_quant, 2 quant, 4 silu_mul_quant, 8 gemm,
     // 16 attention, 32 gdn.
@@ -104,24 +96,25 @@ class CudaBackend : public Backend {
         float* sx = nullptr;
         uint16_t* mx = nullptr;
     } pending_;
-    // A single-token gdn() is held back for one call: when the quantization of its output follows, both run as
-    // det_gdn_quant (one launch less); anything else issues it as it is.
-    struct PendingGdn {
+    struct PendingGemm {
         bool on = false;
-        det_gdn_layer layer{};
-        det_gdn_state state{};
-        const float *qkv = nullptr, *z = nullptr, *a = nullptr, *b = nullptr;
-        float* out = nullptr;
-        float eps = 0.0f;
-        int n_k = 0, n_v = 0, dk = 0, dv = 0;
-    } pending_gdn_;
+        const CudaLinear* lin = nullptr;
+        PendingAct act;                 // the quantization it absorbed (kind 0: none)
+        const int8_t* xq = nullptr;
+        const float* sx = nullptr;
+        const uint16_t* mx = nullptr;
+        size_t m = 0;
+        std::vector<float*> dsts;       // one per part
+        bool accumulate = false;
+    } pending_gemm_;
     bool hold(int kind, const float* a, const float* b, float eps, size_t m, size_t n, int8_t* xq, float* sx,
               uint16_t* mx);
     void flush_pending();
-    void flush_gdn();
+    void issue_gemv(const PendingGemm& g, const CudaLinear* second, const std::vector<float*>* dsts2, float* h);
     void* scratch(Buf<uint8_t>& slot, size_t bytes);
     void finish_linear(CudaLinear& l);
     Buf<uint8_t> attn_scratch_, gdn_scratch_, sample_scratch_, synth_scratch_;
+    Buf<float> swiglu_h_;            // SwiGLU product of a fused gate|up GEMV (the next GEMV quantizes it in its prologue)
     Buf<int32_t> pick_, picks_;
     Buf<uint64_t> z_, zs_;
 };

@@ -30,6 +30,7 @@ void GraphDecoder::step() {
     bk_->pos_dev = pos_.ptr();
     bk_->max_pos = (int)m_.max_ctx - 1;
     m_.network(0, 1);
+    bk_->flush();             // anything the backend still holds back goes out before the pick
     bk_->pos_dev = nullptr;
     det_argmax(m_.w.logits.ptr(), 1, (int)m_.cfg.vocab, pick_.ptr(), ST);
     det_token_feedback(pick_.ptr(), pos_.ptr(), log_.ptr(), 0, (int)m_.max_ctx, ST);

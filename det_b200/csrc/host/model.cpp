@@ -213,12 +213,8 @@ void Model::network(size_t pos0, size_t t) {
             project(g.qkvz, w.xq, w.sx, w.mx, t, {&w.qkv, &w.z});
             GdnLayer layer{&g.conv, &g.a, &g.dt_bias, &g.norm};
             GdnShape shape{t, c.gdn_k_heads, c.gdn_v_heads, c.gdn_dk, c.gdn_dv, c.eps};
-            // decode: a backend may compute the a and b projections inside the mixer (one launch less per layer)
-            if (!(t == 1 && g.ab.lins.size() == 1 &&
-                  bk->gdn_decode_ab(layer, &g.state, nullptr, shape, *g.ab.lins[0], w.xq, w.sx, w.mx, w.qkv, w.z, w.on))) {
-                project(g.ab, w.xq, w.sx, w.mx, t, {&w.a, &w.b});
-                bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.on, GdnExport{});
-            }
+            project(g.ab, w.xq, w.sx, w.mx, t, {&w.a, &w.b});
+            bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.on, GdnExport{});
             bk->quant(w.on, t, c.gdn_v_heads * c.gdn_dv, w.onq, w.son, w.mon);
             bk->gemm(*g.out.lins[0], w.onq, w.son, w.mon, t, GemmOut::accumulate(w.x));
         }
@@ -408,11 +404,8 @@ void Model::network_tp(size_t pos0, size_t t) {
             project(g.qkvz, w.xq, w.sx, w.mx, t, {&w.qkv, &w.z});
             GdnLayer layer{&g.conv, &g.a, &g.dt_bias, &g.norm};
             GdnShape shape{t, tp.k_heads, tp.v_heads, c.gdn_dk, c.gdn_dv, c.eps};
-            if (!(t == 1 && g.ab.lins.size() == 1 &&
-                  bk->gdn_decode_ab(layer, &g.state, nullptr, shape, *g.ab.lins[0], w.xq, w.sx, w.mx, w.qkv, w.z, w.o))) {
-                project(g.ab, w.xq, w.sx, w.mx, t, {&w.a, &w.b});
-                bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.o, GdnExport{});
-            }
+            project(g.ab, w.xq, w.sx, w.mx, t, {&w.a, &w.b});
+            bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.o, GdnExport{});
             comm->gather_quant(*bk, w.o, tp.tmp, tp.mix_full, t, tp.v_heads * c.gdn_dv, w.oq, w.so, w.mo);
             project_back(*g.out.lins[0], w.oq, w.so, w.mo);
         }

@@ -110,11 +110,8 @@ void BatchDecoder::network_rows(size_t t) {
             m.project(g.qkvz, w.xq, w.sx, w.mx, t, {&w.qkv, &w.z});
             GdnLayer layer{&g.conv, &g.a, &g.dt_bias, &g.norm};
             GdnShape shape{t, c.gdn_k_heads, c.gdn_v_heads, c.gdn_dk, c.gdn_dv, c.eps};
-            if (!(g.ab.lins.size() == 1 &&
-                  bk->gdn_decode_ab(layer, nullptr, &rows, shape, *g.ab.lins[0], w.xq, w.sx, w.mx, w.qkv, w.z, w.on))) {
-                m.project(g.ab, w.xq, w.sx, w.mx, t, {&w.a, &w.b});
-                bk->gdn_rows(layer, rows, shape, w.qkv, w.z, w.a, w.b, w.on);
-            }
+            m.project(g.ab, w.xq, w.sx, w.mx, t, {&w.a, &w.b});
+            bk->gdn_rows(layer, rows, shape, w.qkv, w.z, w.a, w.b, w.on);
             bk->quant(w.on, t, c.gdn_v_heads * c.gdn_dv, w.onq, w.son, w.mon);
             bk->gemm(*g.out.lins[0], w.onq, w.son, w.mon, t, GemmOut::accumulate(w.x));
         }

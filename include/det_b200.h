@@ -68,9 +68,8 @@ void det_gemm(const det_qlinear* L, const int8_t* xq, const float* sx, const uin
               cudaStream_t st);
 void det_gemm_ex(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M, float* y,
                  int accumulate, int nparts, const int* offs, float* const* dsts, cudaStream_t st);
-/* Scratch protocol of the reference's large-M path (det_cuda.h:52-57).  Kept for callers that follow it; this backend's
- * large-M path needs det_gemm_scratch_bytes(M, K) bytes of per-(token, group) activation sums and falls back to an
- * internal buffer when none (or a too small one) was registered.                                                    */
+/* Scratch protocol of the reference's large-M path (det_cuda.h:52-57).  Kept so that callers that follow it link and
+ * run: this backend's kernels need no such scratch, so the registration is accepted and ignored.                    */
 size_t det_gemm_scratch_bytes(int M, int K);
 void det_gemm_set_scratch(void* p, size_t bytes);
 
@@ -146,14 +145,20 @@ void det_test_prim(int op, const float* x, int M, int n, float* out, cudaStream_
 
 /* Layout tag OR-ed into det_qlinear.bits once wq points at a det_linear_repack buffer. */
 #define DET_LAYOUT_STREAM 0x100
+/* ... whose rows are interleaved: a linear of two equal halves (gate | up), physical row 2i = row i of the first half,
+ * row 2i+1 = row i of the second (det_linear_repack_pairs).  Outputs are still delivered in the linear's own order.  */
+#define DET_LAYOUT_PAIRS 0x400
 
 /* Streaming layout for the decode GEMV.  The reference's Rust glue builds its device layout in Backend::linear
  * (crates/det/src/cuda.rs:139-163: row-major codes, c and m split out); Metal and x86 repack there
  * (metal.rs:95-122, x86/gemm.rs:59-134).  This is that hook for B200: `src` describes device arrays in the reference
- * layout; `dst` receives det_linear_repack_bytes(N, K, bits) bytes in which every tile of 4 output rows is one
- * contiguous 16-byte-aligned record [codes of 4 rows | c[4] | m[4][K/128] | pad]; any run of records is one bulk copy. */
+ * layout; `dst` receives det_linear_repack_bytes(N, K, bits) bytes in which four output rows x one 1024-wide chunk of K
+ * form one contiguous 16-byte-aligned record [codes of the 4 rows, regrouped for 128-bit shared-memory loads |
+ * m[4][8]]; a record is one bulk copy.  c and m of `src` stay in use (c is read from its own array), so the
+ * det_qlinear that names the repacked buffer keeps src's c and m pointers.                                         */
 size_t det_linear_repack_bytes(int N, int K, int bits);
 void det_linear_repack(const det_qlinear* src, void* dst, cudaStream_t st);
+void det_linear_repack_pairs(const det_qlinear* src, void* dst, cudaStream_t st);   /* N even; tag with DET_LAYOUT_PAIRS */
 
 /* Tensor-core layout for prefill (M > 8): signed int8 codes in tile-major order [ceil(N/128)][K/128][128 rows][128 codes]
  * (each 16 KB box a TMA load fetches is contiguous; det_linear_expand_bytes(N, K) bytes, the last row tile zero padded),
@@ -163,16 +168,20 @@ void det_linear_repack(const det_qlinear* src, void* dst, cudaStream_t st);
 size_t det_linear_expand_bytes(int N, int K);
 void det_linear_expand(const det_qlinear* src, void* dst, cudaStream_t st);
 
-/* GEMM with the activation quantization fused into its prologue (decode: M <= 8 per pass, streaming layout,
- * K <= 18432).  The reference runs these as separate kernels (det_rmsnorm_quant / det_quant / det_silu_mul_quant, then
- * det_gemm_ex; crates/det/src/qwen35.rs:33-36,121-129,133-143); here every CTA of the GEMV rebuilds the quantized row
- * from the fp32 inputs while its weight ring fills — the same fp32 operation sequence, so y and the optional xq / sx / mx
- * outputs (stored by one CTA, for other consumers of the same row) equal the unfused results bit for bit.
- *   kind DET_ACT_RMSNORM: a = x[M][K], b = norm weight [K], eps;   DET_ACT_PLAIN: a = x[M][K];
- *   kind DET_ACT_SWIGLU:  a = gate[M][K], b = up[M][K]   (row = silu_f(gate) * up)                                    */
+/* Decode GEMV with its neighbours fused in (M <= 8 rows, streaming layout; no reference counterpart as one call).  The
+ * reference runs a decode sub-block as separate kernels — det_rmsnorm_quant / det_quant, det_gemm_ex per linear,
+ * det_silu_mul_quant (crates/det/src/qwen35.rs:33-36, 73-74, 121-143); here one launch can carry
+ *   - src != NULL: the activation quantization as the GEMV's prologue.  Every CTA rebuilds the quantized row from the
+ *     fp32 input while its weight ring fills: kind DET_ACT_RMSNORM (a = x[M][K], b = norm weight [K], eps) or
+ *     DET_ACT_PLAIN (a = x[M][K]).  xq / sx / mx of src, when given, receive the row as det_rmsnorm_quant / det_quant
+ *     would have written it (stored by one CTA, for other consumers).  src == NULL: xq, sx, mx are the input rows.
+ *   - lin2 != NULL: a second, small W8 streaming-layout linear over the same rows (the GDN a|b projection beside
+ *     qkv|z), with its own outputs (y2 / nparts2 / offs2 / dsts2).
+ *   - h != NULL (lin in the pairs layout): h[M][N/2] = silu_f(gate) * up, the product det_silu_mul_quant forms before it
+ *     quantizes, instead of the outputs of lin.
+ * Every fp32 value is produced by the same operation sequence as the separate calls, so results are bit-identical.    */
 #define DET_ACT_RMSNORM 1
 #define DET_ACT_PLAIN 2
-#define DET_ACT_SWIGLU 3
 typedef struct {
     int kind;
     const float* a;
@@ -182,8 +191,26 @@ typedef struct {
     float* sx;
     uint16_t* mx;
 } det_act_source;
-void det_gemm_fused(const det_qlinear* L, const det_act_source* src, int M, float* y, int accumulate, int nparts,
-                    const int* offs, float* const* dsts, cudaStream_t st);
+typedef struct {
+    const det_qlinear* lin;
+    const det_qlinear* lin2;
+    const det_act_source* src;
+    const int8_t* xq;
+    const float* sx;
+    const uint16_t* mx;
+    int M;
+    float* y;                 /* outputs of lin, as det_gemm_ex: y / accumulate, or nparts / offs / dsts (host arrays) */
+    int accumulate;
+    int nparts;
+    const int* offs;
+    float* const* dsts;
+    float* y2;                /* outputs of lin2 */
+    int nparts2;
+    const int* offs2;
+    float* const* dsts2;
+    float* h;
+} det_gemv_op;
+void det_gemv(const det_gemv_op* op, cudaStream_t st);
 
 /* Seeded synthetic weights generated in device memory (the benchmarks' stand-in for a converted checkpoint; the host
  * twin is det_b200/csrc/host/synth.cpp and follows crates/det/src/quantize.rs:33-85).  det_synth_linear writes rows
@@ -218,21 +245,6 @@ void det_attention_rows(const det_attn_layer* L, const det_kv_cache* rows, const
 void det_gdn_rows(const det_gdn_layer* L, const det_gdn_state* rows, const float* qkv, const float* z, const float* a,
                   const float* b, float eps, int M, int n_k, int n_v, int dk, int dv, float* on, void* scratch,
                   cudaStream_t st);
-
-/* One decode token of a Gated DeltaNet layer with the activation quantization of its output folded in (no reference
- * counterpart): det_gdn(M = 1) followed by det_quant(on, 1, n_v * dv, oq, osx, omx) in one launch less.  `scratch` must be
- * zero-filled memory from det_malloc that nothing else writes (a counter lives in its first bytes).                   */
-void det_gdn_quant(const det_gdn_layer* L, det_gdn_state* S, const float* qkv, const float* z, const float* a, const float* b,
-                   float eps, int n_k, int n_v, int dk, int dv, float* on, int8_t* oq, float* osx, uint16_t* omx,
-                   void* scratch, cudaStream_t st);
-
-/* Decode step(s) of a Gated DeltaNet layer with its a|b projection folded into the mixer kernel (no reference
- * counterpart): `ab` is the fused W8 linear [a rows | b rows] in the reference layout, xq / sx / mx the quantized layer
- * input (M rows of K).  Exactly one of S (one sequence, M = 1) and rows (M sequences, device table) is non-NULL.
- * Values equal det_gemm_ex on `ab` followed by det_gdn / det_gdn_rows; one GEMV launch per layer less.                */
-void det_gdn_ab(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_state* rows, const det_qlinear* ab,
-                const int8_t* xq, const float* sx, const uint16_t* mx, const float* qkv, const float* z, float eps, int M,
-                int n_k, int n_v, int dk, int dv, float* on, void* scratch, cudaStream_t st);
 
 /* Tensor-parallel exchange over NVLink peer memory (no reference counterpart: the reference is single-device).  Every
  * rank creates a staging area of the same size, publishes its CUDA IPC handle (64 bytes) and opens the others'.
@@ -271,9 +283,6 @@ int det_sample_topkp_static(const float* logits, int M, int V, float inv_temp, i
 /* Measurement switch: programmatic dependent launch between the library's kernels on (default, non-zero) or off.
  * Results are identical either way; only the overlap of one kernel's prologue with its predecessor's tail changes.  */
 void det_debug_set_pdl(int on);
-/* Measurement switches for the attention kernels: bit 0 = token-tiled prefill kernels (default off), bit 1 = two
- * shared-memory stages in the tiled accumulate kernel (default off).  Same results.                                   */
-void det_debug_set_attn(int flags);
 /* Measurement switch for the row kernels: calls with at least min_rows rows (default 128; 0 = never) use one CTA per row
  * instead of a cluster per row.  Same results.                                                                       */
 void det_debug_set_rows(int min_rows);
@@ -281,6 +290,9 @@ void det_debug_set_rows(int min_rows);
  * (32,8) (32,16) (128,32); 0 = chosen by shape (default).  Adding 0x100 / 0x200 switches the split of K over several
  * CTAs for linears with few row tiles on / off.  Results do not depend on any of it.                                   */
 void det_debug_set_tc_variant(int v);
+/* Measurement switch of the decode GEMV: bit 0 = a CTA takes a whole SM's shared memory (no co-residency with the next
+ * launch); bits 8.. = CTAs per SM of one launch (default 1).  Results do not depend on it.                           */
+void det_debug_set_gemv(int flags);
 /* Tensor-pipe ceiling: tcgen05.mma kind::i8 (128 x 256 x 32) issued back to back from resident shared-memory tiles on
  * every SM, no loads and no epilogue; returns the measured int8 rate in TOPS.                                         */
 double det_debug_umma_peak(int iters);

@@ -49,8 +49,10 @@ def test_size_queries_need_no_device(libs):
     assert lib.det_attn_scratch_bytes(1, 24, 256) > 24 * 256 * 9
     assert lib.det_gdn_scratch_bytes(1, 16, 48, 128, 128) >= (10240 + 2 * 48 + 48 * 128) * 4
     assert lib.det_sample_scratch_bytes(1, 248320) == 248320 * 8
-    # W6, K = 5120: records of 4 rows: 4 * 3840 code bytes + 16 (c) + 4 * 40 * 2 (m)
-    assert lib.det_linear_repack_bytes(17408, 5120, 6) == 17408 // 4 * (4 * 3840 + 16 + 320)
+    # W6, K = 5120: a record = 4 rows x one 1024-wide K chunk = 4 * 768 code bytes + 4 * 8 * 2 (m); 5 chunks per row quad
+    assert lib.det_linear_repack_bytes(17408, 5120, 6) == 17408 // 4 * 5 * (4 * 768 + 64)
+    # K = 2560 (an odd multiple of 512): 512-wide chunks
+    assert lib.det_linear_repack_bytes(10240, 2560, 6) == 10240 // 4 * 5 * (4 * 384 + 32)
 
 
 def test_host_library_loads(libs):

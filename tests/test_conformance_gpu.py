@@ -19,19 +19,3 @@ def test_suite(suite, libs, oracle, ref_backend, cuda_backend):
     bad = [l for l in text.splitlines() if not l.startswith("ok ")]
     assert failed == 0 and not bad, f"{suite}: {failed} failed checks\n" + "\n".join(bad[:40])
     assert text.count("ok ") > 0
-
-
-@pytest.mark.parametrize("flags", [1, 3])
-def test_attention_suite_with_token_tiled_kernels(flags, libs, oracle, ref_backend, cuda_backend):
-    """The attention suite again with the token-tiled prefill kernels switched on (one and two shared-memory stages):
-    they are off by default, and must give the same bits when used."""
-    h, d = libs.host(), libs.cuda()
-    report = C.create_string_buffer(1 << 20)
-    hook = C.cast(h.dh_cuda_test_prim, C.c_void_p)
-    d.det_debug_set_attn(flags)
-    try:
-        failed = oracle.orc_conformance(ref_backend, cuda_backend, b"attention", hook, report, len(report))
-    finally:
-        d.det_debug_set_attn(0)
-    bad = [l for l in report.value.decode().splitlines() if not l.startswith("ok ")]
-    assert failed == 0 and not bad, f"{failed} failed checks\n" + "\n".join(bad[:40])

@@ -20,58 +20,30 @@ def test_nine_sequences_use_the_shared_prep_kernel(libs, cuda_backend):
     assert libs.cuda().det_last_error() == 0
 
 
-@pytest.mark.parametrize("fused,fold_ab", [(1, 0), (0, 0), (1, 1)])
-def test_batched_streams_equal_solo_streams(fused, fold_ab, libs, cuda_backend):
-    """fold_ab = 1 also routes both the solo decode and the batched step through det_gdn_ab (a|b projection inside the
-    Gated DeltaNet kernel), whose prefill still goes through the separate GEMM: the streams tie the two together."""
+@pytest.mark.parametrize("fused", [1, 0])
+def test_batched_streams_equal_solo_streams(fused, libs, cuda_backend):
     h = libs.host()
     h.dh_cuda_set_fuse_rows(cuda_backend, fused)
-    h.dh_cuda_set_fold_ab(cuda_backend, fold_ab)
     try:
         together, solo = run_streams(h, cuda_backend, n_new=40, layers=8, ctx=96)
     finally:
         h.dh_cuda_set_fuse_rows(cuda_backend, 1)
-        h.dh_cuda_set_fold_ab(cuda_backend, 0)
     for i, (a, b) in enumerate(zip(together, solo)):
         assert np.array_equal(a, b), (i, a, b)
     assert libs.cuda().det_last_error() == 0
 
 
-def test_folded_ab_projection_gives_the_same_tokens(libs, cuda_backend):
-    """det_gdn_ab (a and b computed inside the Gated DeltaNet decode kernel) against the separate a|b GEMV + det_gdn."""
+def test_fused_decode_launches_give_the_same_tokens_and_logits(libs, cuda_backend):
+    """The decode step with its ops fused across launches (quantization as the GEMV prologue, a|b riding with qkv|z, the
+    SwiGLU product from the gate|up epilogue, the Gated DeltaNet step in one cluster launch) against every op issued on its
+    own: same tokens, same final logits."""
     import ctypes as C
     h = libs.host()
     ids = np.zeros(20, np.int32)
     h.dh_synth_prompt(3, ids.size, 32768, ids.ctypes.data)
     runs = []
-    for fold in (0, 1):
-        h.dh_cuda_set_fold_ab(cuda_backend, fold)
-        try:
-            m = h.dh_model_new_synth(cuda_backend, b"tiny", 8, 20261125, 96, 16)
-            assert m, h.dh_last_error()
-            out = np.zeros(48, np.int32)
-            n = C.c_size_t(0)
-            assert h.dh_model_generate(m, ids.ctypes.data, ids.size, 48, 1, 1.0, 0, 1.0, 0, out.ctypes.data, C.byref(n)) == 0
-            logits = np.zeros(32768, np.float32)
-            h.dh_model_logits(m, logits.ctypes.data, logits.size)
-            runs.append((out[: n.value].copy(), logits.view(np.uint32).copy()))
-            h.dh_model_free(m)
-        finally:
-            h.dh_cuda_set_fold_ab(cuda_backend, 0)
-    assert np.array_equal(runs[0][0], runs[1][0])
-    assert np.array_equal(runs[0][1], runs[1][1])
-
-
-def test_gdn_step_with_folded_quantization_gives_the_same_tokens(libs, cuda_backend):
-    """det_gdn_quant (the quantization of the mixer output done by the last CTA of the Gated DeltaNet output kernel)
-    against det_gdn followed by det_quant."""
-    import ctypes as C
-    h = libs.host()
-    ids = np.zeros(20, np.int32)
-    h.dh_synth_prompt(4, ids.size, 32768, ids.ctypes.data)
-    runs = []
     for fuse in (0, 1):
-        h.dh_cuda_set_fuse_gdn_quant(cuda_backend, fuse)
+        h.dh_cuda_debug(cuda_backend, 0, fuse)
         try:
             m = h.dh_model_new_synth(cuda_backend, b"tiny", 8, 20261125, 96, 16)
             assert m, h.dh_last_error()
@@ -83,7 +55,7 @@ def test_gdn_step_with_folded_quantization_gives_the_same_tokens(libs, cuda_back
             runs.append((out[: n.value].copy(), logits.view(np.uint32).copy()))
             h.dh_model_free(m)
         finally:
-            h.dh_cuda_set_fuse_gdn_quant(cuda_backend, 0)
+            h.dh_cuda_debug(cuda_backend, 0, 1)
     assert np.array_equal(runs[0][0], runs[1][0])
     assert np.array_equal(runs[0][1], runs[1][1])
     assert libs.cuda().det_last_error() == 0
