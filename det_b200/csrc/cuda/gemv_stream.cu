@@ -1,13 +1,13 @@
 // Decode GEMV (M <= 8 tokens per pass) on the streaming weight layout: the HBM-bound kernel of the token loop.
 // Replaces the reference's k_decode (kernels/cuda/gemm.cu:201-337) with a B200 design:
 //
-//   * persistent CTAs, warp-specialised: one producer thread streams weight records HBM -> shared memory with
-//     cp.async.bulk into a ring of slots guarded by full/empty mbarriers; twelve consumer warps each own whole groups of
-//     four output rows and a private set of ring slots, so consumers never synchronise with each other;
-//   * a CTA takes about half of an SM's shared memory, and a launch puts one CTA on every SM: the CTAs of the NEXT GEMV of
-//     the token loop (launched with programmatic dependent launch) become resident beside the running ones and pull
-//     their first weights while the running GEMV still computes and while the row operations between the two run, so
-//     HBM does not idle at kernel boundaries;
+//   * persistent CTAs of sixteen worker warps.  A warp owns whole groups of four output rows and a private set of
+//     shared-memory slots: it streams its own weight records HBM -> shared memory with cp.async.bulk (one elected lane
+//     issues the copy of record i + SPW into the slot the warp has just finished reading, so no "empty" barrier and no
+//     producer thread is needed) and waits on one mbarrier per slot, so warps never synchronise with each other;
+//   * one CTA per SM with up to 150 KB of weight records in flight; with programmatic dependent launch every warp
+//     requests its first records before it waits for the kernel's predecessor, so the slots fill while the row operation
+//     in front of the GEMV (or its own prologue) still runs;
 //   * a record is a 1024-wide K chunk of four rows: the 32 lanes of the owning warp are 4 rows x 8 lanes, and a lane
 //     walks one whole 128-group of its row per record — unsigned codes unpacked in registers from 128-bit shared loads,
 //     dp4a against int8 activations staged once per CTA, ONE exact 64-bit multiply-add per group;
@@ -114,9 +114,10 @@ __global__ void k_repack_stream(const uint8_t* __restrict__ wq, const uint16_t* 
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-constexpr int NCW = 12;                          // consumer warps
-constexpr int GEMV_THREADS = (NCW + 1) * 32;     // + one producer warp
-constexpr int MAX_SLOTS = 3 * NCW;
+constexpr int NCW = 16;                          // warps per CTA
+constexpr int GEMV_THREADS = NCW * 32;
+constexpr int MAX_SPW = 5;                       // slots per worker warp
+constexpr int MAX_SLOTS = MAX_SPW * NCW;
 constexpr int RREG = 4;                          // 128-slices per warp kept in registers by the prologue
 
 struct GemvSeg {
@@ -134,8 +135,8 @@ struct GemvArgs {
     const uint16_t* mx;       // may be NULL
     int t0;                   // first token of this pass (for routing)
     int mt;                   // live tokens in this pass (<= MT)
-    int spw;                  // ring slots per worker warp; warp w owns slots [w * spw, (w + 1) * spw)
-    int workers;              // consumer warps that take quads (<= NCW)
+    int spw;                  // slots per worker warp; warp w owns slots [w * spw, (w + 1) * spw)
+    int workers;              // warps that take quads (<= NCW); the others only help staging the activations
     int* error_flag;
     // Activation prologue: the rows are produced from fp32 inputs inside the kernel — the op sequences of RMSNorm +
     // quant_act_i8g or plain quant_act_i8g — instead of being read as codes.  CTA 0 also stores the codes / scale /
@@ -186,36 +187,35 @@ __device__ __forceinline__ void unpack_unit(const uint8_t* wp, int pu, unsigned 
     }
 }
 
-__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory"); }
+__device__ __forceinline__ void consumer_barrier() { __syncthreads(); }
 
 // Where the 16-byte piece holding activation codes k0 .. k0+15 of token row t lives in the staged copy: the same chunk /
 // piece / physical-unit order as the weights.
-__device__ __forceinline__ int stage_piece(const GemvArgs& a, int t, int q /* piece index k0 / 16 */) {
+template <int UC>
+__device__ __forceinline__ int stage_piece(int NCH, int t, int q /* piece index k0 / 16 */) {
     const int lu = q >> 2, pp = q & 3;
-    const int c = lu / a.UC, l = lu - c * a.UC;
-    return (((t * a.NCH + c) * 4 + pp) * a.UC + phys_unit(a.UC, l)) * 16;
+    const int c = lu / UC, l = lu % UC;
+    return (((t * NCH + c) * 4 + pp) * UC + phys_unit(UC, l)) * 16;
 }
-__device__ __forceinline__ int stage_unit(const GemvArgs& a, int t, int lu) {
-    const int c = lu / a.UC, l = lu - c * a.UC;
-    return (t * a.NCH + c) * a.UC + phys_unit(a.UC, l);
+template <int UC>
+__device__ __forceinline__ int stage_unit(int NCH, int t, int lu) {
+    const int c = lu / UC, l = lu % UC;
+    return (t * NCH + c) * UC + phys_unit(UC, l);
 }
 
-// Produces the int8 rows of this pass from fp32 inputs, straight into the staged layout.  One warp owns one 128-wide
-// slice at a time, 4 consecutive values per lane; the first RREG slices of a warp stay in registers between the phases,
-// later ones (rows longer than RREG * NCW * 128 values) are read again.  The row-wide sum of squares is the spec tree
-// (slice sums are aligned subtrees; every warp finishes the same tree over them), the row-wide maximum is order-free.
-// Same fp32 operation sequence as k_row in glue.cu.
-__device__ __forceinline__ float4 pro_value(const GemvArgs& a, const float4 x, const float4 w, float inv_rms) {
-    if (a.pro != PRO_RMS) return x;
-    return make_float4(fmul(fmul(x.x, inv_rms), w.x), fmul(fmul(x.y, inv_rms), w.y), fmul(fmul(x.z, inv_rms), w.z),
-                       fmul(fmul(x.w, inv_rms), w.w));
-}
-__device__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2* xmeta, float* slice_sum, float* s_slices, float* wmax,
-                            float* sxs) {
-    const int K = a.K, G = a.G;
+// Produces the int8 rows of this pass from fp32 inputs, straight into the staged layout (rows of at most RREG * NCW
+// 128-slices = 8192 values).  One warp owns one 128-wide slice per round, 4 consecutive values per lane, values held in
+// registers between the phases.  The per-slice scalars (group scale, multiplier, reciprocal) are computed for all of a
+// warp's slices at once, one slice per lane, so the exact divisions run once per warp instead of once per slice.  The
+// row-wide sum of squares is the spec tree (slice sums are aligned subtrees; every warp finishes the same tree over
+// them), the row-wide maximum is order-free.  Same fp32 operation sequence per value as k_row in glue.cu.
+template <int UC>
+__device__ __forceinline__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2* xmeta, float* slice_sum, float* wmax,
+                                            float* sxs) {
+    const int K = a.K, G = a.G, NCH = a.NCH;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool keep = blockIdx.x == 0 && a.xq_out != nullptr;
-    const int rounds = (G + NCW - 1) / NCW;
+    const bool rms = a.pro == PRO_RMS;
     for (int t = 0; t < a.mt; t++) {
         const float* pa = a.pa + (size_t)t * K;
         float4 v[RREG], wv[RREG];
@@ -226,32 +226,14 @@ __device__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2* xmeta, float* 
             wv[r] = v[r];
             if (s < G) {
                 v[r] = *reinterpret_cast<const float4*>(pa + s * 128 + lane * 4);
-                if (a.pro == PRO_RMS) wv[r] = *reinterpret_cast<const float4*>(a.pb + s * 128 + lane * 4);
+                if (rms) wv[r] = *reinterpret_cast<const float4*>(a.pb + s * 128 + lane * 4);
             }
         }
-        auto value_of = [&](int r, int s) -> float4 {      // fp32 input of slice s (round r of this warp)
-            float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (rms) {
 #pragma unroll
-            for (int i = 0; i < RREG; i++)
-                if (r == i) x = v[i];
-            if (r >= RREG && s < G) x = *reinterpret_cast<const float4*>(pa + s * 128 + lane * 4);
-            return x;
-        };
-        auto weight_of = [&](int r, int s) -> float4 {
-            float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (a.pro != PRO_RMS) return x;
-#pragma unroll
-            for (int i = 0; i < RREG; i++)
-                if (r == i) x = wv[i];
-            if (r >= RREG && s < G) x = *reinterpret_cast<const float4*>(a.pb + s * 128 + lane * 4);
-            return x;
-        };
-        float inv_rms = 0.0f;
-        if (a.pro == PRO_RMS) {
-            for (int r = 0; r < rounds; r++) {
+            for (int r = 0; r < RREG; r++) {
                 const int s = warp + r * NCW;
-                const float4 x = value_of(r, s);
-                float sq[4] = {fmul(x.x, x.x), fmul(x.y, x.y), fmul(x.z, x.z), fmul(x.w, x.w)};
+                float sq[4] = {fmul(v[r].x, v[r].x), fmul(v[r].y, v[r].y), fmul(v[r].z, v[r].z), fmul(v[r].w, v[r].w)};
                 const float ssum = fold_lanes<32>(fold_run<4>(sq));
                 if (lane == 0 && s < G) slice_sum[s] = ssum;
             }
@@ -275,20 +257,23 @@ __device__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2* xmeta, float* 
                 for (int off = 1; off < a.pslices; off <<= 1) w1 = fadd(w1, __shfl_xor_sync(FULL, w1, off));
                 tot = __shfl_sync(FULL, w1, 0);
             }
-            inv_rms = fdiv(1.0f, fsqrt(fadd(fdiv(tot, (float)K), a.eps)));
+            const float inv_rms = fdiv(1.0f, fsqrt(fadd(fdiv(tot, (float)K), a.eps)));
+#pragma unroll
+            for (int r = 0; r < RREG; r++)
+                v[r] = make_float4(fmul(fmul(v[r].x, inv_rms), wv[r].x), fmul(fmul(v[r].y, inv_rms), wv[r].y),
+                                   fmul(fmul(v[r].z, inv_rms), wv[r].z), fmul(fmul(v[r].w, inv_rms), wv[r].w));
         }
-        float local_max = 0.0f;
-        for (int r = 0; r < rounds; r++) {
-            const int s = warp + r * NCW;
-            if (s < G) {
-                const float4 y = pro_value(a, value_of(r, s), weight_of(r, s), inv_rms);
-                float amax = fmaxf(fmaxf(fabsf(y.x), fabsf(y.y)), fmaxf(fabsf(y.z), fabsf(y.w)));
-                amax = max_lanes(amax);
-                const float sg = fdiv(amax, 127.0f);
-                if (lane == 0) s_slices[s] = sg;
-                local_max = fmaxf(local_max, sg);
-            }
+        // group scales: lane r of the warp takes slice warp + r * NCW
+        float amax_sel = 0.0f;
+#pragma unroll
+        for (int r = 0; r < RREG; r++) {
+            float am = fmaxf(fmaxf(fabsf(v[r].x), fabsf(v[r].y)), fmaxf(fabsf(v[r].z), fabsf(v[r].w)));
+            am = max_lanes(am);
+            if (lane == r) amax_sel = am;
         }
+        const bool have = lane < RREG && warp + lane * NCW < G;
+        const float sg_sel = have ? fdiv(amax_sel, 127.0f) : 0.0f;
+        const float local_max = max_lanes(sg_sel);
         if (lane == 0) wmax[warp] = local_max;
         consumer_barrier();
         float top = 0.0f;
@@ -299,58 +284,58 @@ __device__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2* xmeta, float* 
             sxs[t] = sx;
             if (keep) a.sx_out[t] = sx;
         }
-        for (int r = 0; r < rounds; r++) {
+        const unsigned mult_sel = have ? group_mult(sg_sel, sx) : 1u;
+        const float inv_sel = fdiv(1.0f, fmul(sx, (float)mult_sel));
+#pragma unroll
+        for (int r = 0; r < RREG; r++) {
             const int s = warp + r * NCW;
+            const unsigned mult = __shfl_sync(FULL, mult_sel, r);
+            const float inv = __shfl_sync(FULL, inv_sel, r);
             if (s < G) {
-                const float4 y = pro_value(a, value_of(r, s), weight_of(r, s), inv_rms);
-                const unsigned mult = group_mult(s_slices[s], sx);
-                const float inv = fdiv(1.0f, fmul(sx, (float)mult));
-                unsigned word = (unsigned)(quant_code(y.x, inv) & 0xff);
-                word |= (unsigned)(quant_code(y.y, inv) & 0xff) << 8;
-                word |= (unsigned)(quant_code(y.z, inv) & 0xff) << 16;
-                word |= (unsigned)(quant_code(y.w, inv) & 0xff) << 24;
+                unsigned word = (unsigned)(quant_code(v[r].x, inv) & 0xff);
+                word |= (unsigned)(quant_code(v[r].y, inv) & 0xff) << 8;
+                word |= (unsigned)(quant_code(v[r].z, inv) & 0xff) << 16;
+                word |= (unsigned)(quant_code(v[r].w, inv) & 0xff) << 24;
                 // value index e = s * 128 + lane * 4: 16-byte piece s * 8 + lane / 4, word lane % 4 of it
-                *reinterpret_cast<unsigned*>(xs + stage_piece(a, t, s * 8 + (lane >> 2)) + (lane & 3) * 4) = word;
+                *reinterpret_cast<unsigned*>(xs + stage_piece<UC>(NCH, t, s * 8 + (lane >> 2)) + (lane & 3) * 4) = word;
                 int sum = __dp4a((int)word, 0x01010101, 0);
 #pragma unroll
                 for (int off = 1; off < 16; off <<= 1) sum += __shfl_xor_sync(FULL, sum, off);
-                if ((lane & 15) == 0) xmeta[stage_unit(a, t, 2 * s + (lane >> 4))] = make_int2(sum, (int)mult);
+                if ((lane & 15) == 0) xmeta[stage_unit<UC>(NCH, t, 2 * s + (lane >> 4))] = make_int2(sum, (int)mult);
                 if (keep) {
                     *reinterpret_cast<unsigned*>(a.xq_out + (size_t)t * K + s * 128 + lane * 4) = word;
                     if (lane == 0) a.mx_out[(size_t)t * G + s] = (uint16_t)mult;
                 }
             }
         }
-        consumer_barrier();     // the slice tables are reused by the next row
+        consumer_barrier();     // the tables are reused by the next row; the staged row is complete
     }
 }
 
-// One record (K chunk c of the quad) for this lane's row: the lane's whole 128-group (two units; one unit = half a group
+// One record (a K chunk of the quad) for this lane's row: the lane's whole 128-group (two units; one unit = half a group
 // when UC = 8), all MT tokens.  acc gathers dot * (m * mx - 2^31) exactly in 64 bits with ONE signed multiply-add per
 // group and token, accs the plain sum of the dots: the caller adds accs * 2^31 back at the end of the row.
-template <int BITS, int MT>
-__device__ __forceinline__ void quad_chunk(const GemvArgs& a, const uint8_t* rec, int m_off, int c, int r, int j,
-                                           const uint8_t* xs, const int2* xmeta, long long (&acc)[MT], int (&accs)[MT]) {
-    constexpr int NP = BITS / 2;
-    const int UC = a.UC, pu = UC * 16;
-    const uint8_t* wp = rec + ((size_t)(r * NP) * UC + j) * 16;
-    const unsigned mw = reinterpret_cast<const uint16_t*>(rec + m_off)[r * (UC >> 1) + (UC == 16 ? j : (j >> 1))];
+// wp: the lane's first piece in the record; xp / mp: the lane's first activation piece / unit entry of this chunk.
+template <int BITS, int MT, int UC>
+__device__ __forceinline__ void quad_chunk(const uint8_t* wp, unsigned mw, const uint8_t* xp, const int2* mp, int tok_bytes,
+                                           int tok_units, long long (&acc)[MT], int (&accs)[MT]) {
+    constexpr int PU = UC * 16;          // byte distance between the pieces of a unit
+    constexpr int UPL = UC / 8;          // units per lane: 2 (a whole group) or 1
     int dots[MT], mxv[MT];
 #pragma unroll
     for (int t = 0; t < MT; t++) { dots[t] = 0; mxv[t] = 1; }
-    const int upl = UC >> 3;     // units per lane: 2 (a whole group) or 1
-    for (int uu = 0; uu < upl; uu++) {
+#pragma unroll
+    for (int uu = 0; uu < UPL; uu++) {
         unsigned o[16];
-        unpack_unit<BITS>(wp + uu * (LPR * 16), pu, o);
-        const int p = j + LPR * uu;
+        unpack_unit<BITS>(wp + uu * (LPR * 16), PU, o);
 #pragma unroll
         for (int t = 0; t < MT; t++) {
             int d0 = 0, d1 = 0, d2 = 0, d3 = 0;   // independent chains, summed below
-            const uint8_t* xt = xs + (((size_t)(t * a.NCH + c) * 4) * UC + p) * 16;
+            const uint8_t* xt = xp + (size_t)t * tok_bytes + uu * (LPR * 16);
             const uint4 x0 = *reinterpret_cast<const uint4*>(xt);
-            const uint4 x1 = *reinterpret_cast<const uint4*>(xt + pu);
-            const uint4 x2 = *reinterpret_cast<const uint4*>(xt + 2 * (size_t)pu);
-            const uint4 x3 = *reinterpret_cast<const uint4*>(xt + 3 * (size_t)pu);
+            const uint4 x1 = *reinterpret_cast<const uint4*>(xt + PU);
+            const uint4 x2 = *reinterpret_cast<const uint4*>(xt + 2 * PU);
+            const uint4 x3 = *reinterpret_cast<const uint4*>(xt + 3 * PU);
             d0 = dot4<BITS>(o[0], (int)x0.x, d0); d1 = dot4<BITS>(o[1], (int)x0.y, d1);
             d2 = dot4<BITS>(o[2], (int)x0.z, d2); d3 = dot4<BITS>(o[3], (int)x0.w, d3);
             d0 = dot4<BITS>(o[4], (int)x1.x, d0); d1 = dot4<BITS>(o[5], (int)x1.y, d1);
@@ -359,7 +344,7 @@ __device__ __forceinline__ void quad_chunk(const GemvArgs& a, const uint8_t* rec
             d2 = dot4<BITS>(o[10], (int)x2.z, d2); d3 = dot4<BITS>(o[11], (int)x2.w, d3);
             d0 = dot4<BITS>(o[12], (int)x3.x, d0); d1 = dot4<BITS>(o[13], (int)x3.y, d1);
             d2 = dot4<BITS>(o[14], (int)x3.z, d2); d3 = dot4<BITS>(o[15], (int)x3.w, d3);
-            const int2 meta = xmeta[(t * a.NCH + c) * UC + p];
+            const int2 meta = mp[t * tok_units + uu * LPR];
             int dot = (d0 + d1) + (d2 + d3);
             if (BITS != 8) dot -= code_offset(BITS) * meta.x;
             dots[t] += dot;
@@ -374,22 +359,19 @@ __device__ __forceinline__ void quad_chunk(const GemvArgs& a, const uint8_t* rec
     }
 }
 
-// Shared memory: [ring: workers * spw slots] [x pieces: MT * NCH * UC * 64] [xmeta: MT * NCH * UC int2 = (sum of x over
-// the unit, mx of its group)] [full[MAX_SLOTS]] [empty[MAX_SLOTS]] [slice sums: 256 f32] [slice scales: 256 f32]
-// [warp maxima: NCW f32] [row scales: 8 f32]
-template <int BITS, int MT, bool DUAL>
-__global__ void __launch_bounds__(GEMV_THREADS, MT <= 2 ? 2 : 1) k_gemv_stream(const GemvArgs a) {
+// Shared memory: [slots: workers * spw] [x pieces: MT * NCH * UC * 64] [xmeta: MT * NCH * UC int2 = (sum of x over
+// the unit, mx of its group)] [full[MAX_SLOTS]] [slice sums: 256 f32] [warp maxima: NCW f32] [row scales: 8 f32]
+template <int BITS, int MT, bool DUAL, int UC>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    const int UC = a.UC, NCH = a.NCH;
+    const int NCH = a.NCH;
     const int upad = NCH * UC;
     uint8_t* ring = smem;
     uint8_t* xs = ring + (size_t)a.workers * a.spw * a.slot_bytes;
     int2* xmeta = reinterpret_cast<int2*>(xs + (size_t)MT * upad * 64);
     unsigned long long* full = reinterpret_cast<unsigned long long*>(xmeta + MT * upad);
-    unsigned long long* empty = full + MAX_SLOTS;
-    float* slice_sum = reinterpret_cast<float*>(empty + MAX_SLOTS);
-    float* s_slices = slice_sum + 256;
-    float* wmax = s_slices + 256;
+    float* slice_sum = reinterpret_cast<float*>(full + MAX_SLOTS);
+    float* wmax = slice_sum + 256;
     float* sxs = wmax + NCW;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -398,53 +380,35 @@ __global__ void __launch_bounds__(GEMV_THREADS, MT <= 2 ? 2 : 1) k_gemv_stream(c
     const int total = a.seg[0].nquads + (DUAL ? a.seg[1].nquads : 0);
     pdl_trigger();
     if (tid == 0) {
-        for (int s = 0; s < W * SPW; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 1);
-        }
+        for (int s = 0; s < W * SPW; s++) mbar_init(&full[s], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    if (warp == NCW) {
-        // ---------------- producer: one thread keeps every worker's slots full; weights do not depend on earlier
-        // kernels.  Order: round li (the li-th quad of every worker), chunk c, worker w.
-        if (lane == 0) {
-            bool ok = true;
-            int issued = 0;
-            for (int li = 0; ok && (long long)blockIdx.x + (long long)li * W * gridDim.x < total; li++) {
-                for (int c = 0; ok && c < NCH; c++) {
-                    for (int w = 0; w < W; w++) {
-                        const long long Q = (long long)blockIdx.x + (long long)(li * W + w) * gridDim.x;
-                        if (Q >= total) break;
-                        const int sg = (DUAL && Q >= a.seg[0].nquads) ? 1 : 0;
-                        const long long q = sg ? Q - a.seg[0].nquads : Q;
-                        const int lr = li * NCH + c;
-                        const int s = w * SPW + lr % SPW;
-                        ok = mbar_wait(&empty[s], ((unsigned)(lr / SPW) & 1u) ^ 1u, wl);
-                        if (!ok) break;
-                        const unsigned bytes = (unsigned)a.seg[sg].rec_bytes;
-                        mbar_expect_tx(&full[s], bytes);
-                        bulk_g2s(ring + (size_t)s * a.slot_bytes, a.seg[sg].w + ((size_t)q * NCH + c) * bytes, bytes, &full[s]);
-                        issued++;
-                    }
-                }
-            }
-            if (!ok) {
-                atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
-                // copies already issued still target this CTA's shared memory: give each slot a (bounded) chance to land
-                for (int s = 0; s < W * SPW && s < issued; s++) {
-                    (void)mbar_wait(&full[s], 0u, wl >> 5);
-                    (void)mbar_wait(&full[s], 1u, wl >> 5);
-                }
-            }
-        }
-        return;
-    }
+    // Quad i of this CTA (global quad blockIdx.x + i * gridDim.x) belongs to warp i % workers.  The warp's records —
+    // NCH per quad, quads in order — land in the warp's slots round-robin, so the warp meets the phases of each of its
+    // slots strictly in sequence (a parity wait can tell only two phases apart).  (ili, ic, islot) = the next record to
+    // request: quad number within the warp, chunk, slot.
+    const long long qstep = (long long)W * gridDim.x;
+    long long iq = (long long)blockIdx.x + (long long)warp * gridDim.x;     // global quad of the next request
+    int ic = 0, islot = 0;
+    auto issue = [&]() {        // one lane: request the warp's next record, if there is one
+        if (iq >= total) return;
+        const int sg = (DUAL && iq >= a.seg[0].nquads) ? 1 : 0;
+        const long long q = sg ? iq - a.seg[0].nquads : iq;
+        const int s = warp * SPW + islot;
+        const unsigned bytes = (unsigned)a.seg[sg].rec_bytes;
+        mbar_expect_tx(&full[s], bytes);
+        bulk_g2s(ring + (size_t)s * a.slot_bytes, a.seg[sg].w + ((size_t)q * NCH + ic) * bytes, bytes, &full[s]);
+        if (++islot == SPW) islot = 0;
+        if (++ic == NCH) { ic = 0; iq += qstep; }
+    };
+    // weights do not depend on earlier kernels: every worker fills its slots before waiting for its predecessor
+    if (warp < W && lane == 0)
+        for (int i = 0; i < SPW; i++) issue();
 
-    // ---------------- consumers: stage the activations once (same chunk / piece order as the weights), then drain
-    // records.  The activations (and the output rows) belong to earlier kernels: wait for them here, while the producer
-    // is already pulling weights.
+    // ---------------- stage the activations once (same chunk / piece order as the weights).  The activations (and the
+    // output rows) belong to earlier kernels: wait for them here, while the first weights are already on their way.
     pdl_wait();
     if (upad != a.U) {     // ragged last chunk: the padding units must read as zero
         for (int i = tid; i < MT * upad * 4; i += NCW * 32) reinterpret_cast<uint4*>(xs)[i] = make_uint4(0, 0, 0, 0);
@@ -452,7 +416,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, MT <= 2 ? 2 : 1) k_gemv_stream(c
         consumer_barrier();
     }
     if (a.pro) {
-        fused_stage(a, xs, xmeta, slice_sum, s_slices, wmax, sxs);
+        fused_stage<UC>(a, xs, xmeta, slice_sum, wmax, sxs);
     } else {
         const int pieces_per_tok = a.K >> 4;
         const int total_pieces = MT * pieces_per_tok;
@@ -465,7 +429,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, MT <= 2 ? 2 : 1) k_gemv_stream(c
                 t = pid / pieces_per_tok;
                 q = pid - t * pieces_per_tok;
                 if (t < a.mt) v = *reinterpret_cast<const uint4*>(a.xq + (size_t)t * a.K + (size_t)q * 16);
-                *reinterpret_cast<uint4*>(xs + stage_piece(a, t, q)) = v;
+                *reinterpret_cast<uint4*>(xs + stage_piece<UC>(NCH, t, q)) = v;
             }
             int s = __dp4a((int)v.x, 0x01010101, 0);
             s = __dp4a((int)v.y, 0x01010101, s);
@@ -476,24 +440,28 @@ __global__ void __launch_bounds__(GEMV_THREADS, MT <= 2 ? 2 : 1) k_gemv_stream(c
             if (live && (q & 3) == 0) {
                 const int lu = q >> 2;
                 const int mxv = (a.mx && t < a.mt) ? (int)a.mx[(size_t)t * a.G + (lu >> 1)] : 1;
-                xmeta[stage_unit(a, t, lu)] = make_int2(s, mxv);
+                xmeta[stage_unit<UC>(NCH, t, lu)] = make_int2(s, mxv);
             }
         }
         consumer_barrier();
     }
 
-    // Quad i of this CTA (global quad blockIdx.x + i * gridDim.x) belongs to warp i % workers; its NCH records land in
-    // that warp's own slots in order, so a warp meets the phases of each of its slots strictly in sequence (a parity
-    // wait can tell only two phases apart).
     if (warp >= W) return;
     float sxr[MT];                               // row scales, fetched once (not once per record)
 #pragma unroll
     for (int t = 0; t < MT; t++) sxr[t] = a.pro ? sxs[t] : (t < a.mt ? a.sx[t] : 0.0f);
     const int r = lane / LPR, j = lane - r * LPR;
+    constexpr int NP = BITS / 2;
+    const int tok_bytes = NCH * UC * 64, tok_units = NCH * UC;      // one token's staged row
+    const int chunk_bytes = UC * 64;
+    const uint8_t* xlane = xs + j * 16;
+    const int2* mlane = xmeta + j;
+    const int woff = (r * NP * UC + j) * 16, woff8 = (r * 4 * UC + j) * 16;   // the lane's first piece (W8 for a DUAL tail)
+    const int moff = (r * (UC >> 1) + (UC == 16 ? j : (j >> 1))) * 2;
+    int cslot = 0;
+    unsigned cphase = 0;
     bool ok = true;
-    for (int li = 0; ok; li++) {
-        const long long Q = (long long)blockIdx.x + (long long)(li * W + warp) * gridDim.x;
-        if (Q >= total) break;
+    for (long long Q = (long long)blockIdx.x + (long long)warp * gridDim.x; ok && Q < total; Q += qstep) {
         const int sg = (DUAL && Q >= a.seg[0].nquads) ? 1 : 0;
         const GemvSeg& S = a.seg[sg];
         const int n = (int)(sg ? Q - a.seg[0].nquads : Q) * QR + r;
@@ -503,16 +471,19 @@ __global__ void __launch_bounds__(GEMV_THREADS, MT <= 2 ? 2 : 1) k_gemv_stream(c
         int accs[MT];
 #pragma unroll
         for (int t = 0; t < MT; t++) { acc[t] = 0; accs[t] = 0; }
-        for (int c = 0; c < NCH; c++) {
-            const int lr = li * NCH + c;
-            const int s = warp * SPW + lr % SPW;
-            ok = mbar_wait(&full[s], (unsigned)(lr / SPW) & 1u, wl);
+        const uint8_t* xp = xlane;
+        const int2* mp = mlane;
+        for (int c = 0; c < NCH; c++, xp += chunk_bytes, mp += UC) {
+            const int s = warp * SPW + cslot;
+            ok = mbar_wait(&full[s], cphase, wl);
             if (!ok) break;
             const uint8_t* rec = ring + (size_t)s * a.slot_bytes;
-            if (DUAL && sg) quad_chunk<8, MT>(a, rec, S.m_off, c, r, j, xs, xmeta, acc, accs);
-            else quad_chunk<BITS, MT>(a, rec, S.m_off, c, r, j, xs, xmeta, acc, accs);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);   // the slot may be refilled
+            const unsigned mw = *reinterpret_cast<const uint16_t*>(rec + S.m_off + moff);
+            if (DUAL && sg) quad_chunk<8, MT, UC>(rec + woff8, mw, xp, mp, tok_bytes, tok_units, acc, accs);
+            else quad_chunk<BITS, MT, UC>(rec + woff, mw, xp, mp, tok_bytes, tok_units, acc, accs);
+            if (++cslot == SPW) { cslot = 0; cphase ^= 1u; }
+            __syncwarp();                            // every lane has finished reading the slot
+            if (lane == 0) issue();                  // refill it with the warp's record SPW ahead
         }
         if (!ok) break;
         float y[MT];
@@ -537,7 +508,14 @@ __global__ void __launch_bounds__(GEMV_THREADS, MT <= 2 ? 2 : 1) k_gemv_stream(c
                 if (t < a.mt) emit(S.out, a.t0 + t, n, y[t]);
         }
     }
-    if (!ok && lane == 0) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
+    if (!ok && lane == 0) {
+        atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
+        // copies this warp has requested still target this CTA's shared memory: give each slot a (bounded) chance to land
+        for (int s = warp * SPW; s < (warp + 1) * SPW; s++) {
+            (void)mbar_wait(&full[s], 0u, wl >> 5);
+            (void)mbar_wait(&full[s], 1u, wl >> 5);
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -546,49 +524,59 @@ struct GemvPlan {
     size_t smem;
     int grid;
 };
-// Measurement switch (det_debug_set_gemv): bit 0 = a CTA may take a whole SM's shared memory (no co-residency with the
-// next launch); bits 8.. = CTAs per SM of one launch (default 1).  Results do not depend on it.
+// Measurement switch (det_debug_set_gemv): bits 4..8 = worker warps per CTA (0 = all sixteen); bits 9.. = slots per
+// worker (0 = as many as fit, at most 5).  Results do not depend on it.
 static int g_gemv_flags = 0;
 
-// A plan by shape only.  The ring takes what the staged activations leave of HALF an SM's shared memory (so that the
-// next launch's CTAs fit beside this one's), two or three slots per worker warp; passes whose staged activations do not
-// fit that (many tokens of a long row) take the whole SM.
+// A plan by shape only: one CTA per SM, sixteen workers, as many slots per worker as the staged activations leave room
+// for (bytes in flight per CTA = workers * (spw - 1) records).
 static bool plan_gemv(int K, int slot_bytes, int MT, long long total_quads, GemvPlan& p) {
     const StreamGeom g = stream_geom(QR, K, 8);
     const int upad = g.NCH * g.UC;
-    const size_t fixed = (size_t)MT * upad * 64 + (size_t)MT * upad * 8 + 2 * MAX_SLOTS * 8 + (512 + NCW + 8) * 4;
-    const size_t whole = smem_optin() - 1024;
-    const size_t half = (smem_optin() + 1024) / 2 - 1024 - 512;      // two CTAs per SM: 1 KB of each is reserved
-    size_t budget = (MT <= 2 && !(g_gemv_flags & 1)) ? half : whole;
-    if (fixed + 2 * (size_t)slot_bytes > budget) budget = whole;
+    const size_t fixed = (size_t)MT * upad * 64 + (size_t)MT * upad * 8 + MAX_SLOTS * 8 + (256 + NCW + 8) * 4;
+    const size_t budget = smem_optin() - 1024;
     if (fixed + 2 * (size_t)slot_bytes > budget) return false;
-    int slots = (int)((budget - fixed) / slot_bytes);
-    if (slots > MAX_SLOTS) slots = MAX_SLOTS;
-    p.workers = slots / 2 < NCW ? slots / 2 : NCW;
-    if (p.workers < 1) p.workers = 1;
-    p.spw = slots / p.workers;
-    if (p.spw > 3) p.spw = 3;
+    const int slots = (int)((budget - fixed) / slot_bytes);
+    int workers = (g_gemv_flags >> 4) & 31;
+    if (workers < 1 || workers > NCW) workers = NCW;
+    while (workers > 1 && slots / workers < 2) workers--;
+    p.workers = workers;
+    p.spw = slots / workers;
+    const int cap_spw = (g_gemv_flags >> 9) > 0 ? (g_gemv_flags >> 9) : MAX_SPW;
+    if (p.spw > cap_spw) p.spw = cap_spw;
+    if (p.spw > MAX_SPW) p.spw = MAX_SPW;
+    if (p.spw < 1) return false;
     p.smem = fixed + (size_t)p.workers * p.spw * slot_bytes;
-    const int per_sm = (g_gemv_flags >> 8) > 0 ? (g_gemv_flags >> 8) : 1;
-    const long long cap = (long long)sm_count() * per_sm;
+    const long long cap = (long long)sm_count();
     p.grid = (int)(total_quads < cap ? total_quads : cap);
     return true;
 }
 
-template <int BITS, int MT, bool DUAL>
+template <int BITS, int MT, bool DUAL, int UC>
 static void launch_gemv_one(const GemvArgs& a, const GemvPlan& p, cudaStream_t q) {
     static bool configured = false;
     if (!configured) {
-        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemv_stream<BITS, MT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemv_stream<BITS, MT, DUAL, UC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)(smem_optin())));
         configured = true;
     }
-    launch_pdl(k_gemv_stream<BITS, MT, DUAL>, dim3(p.grid), dim3(GEMV_THREADS), p.smem, q, 1, a);
+    launch_pdl(k_gemv_stream<BITS, MT, DUAL, UC>, dim3(p.grid), dim3(GEMV_THREADS), p.smem, q, 1, a);
 }
 template <int BITS, int MT>
 static void launch_gemv(const GemvArgs& a, const GemvPlan& p, bool dual, cudaStream_t q) {
-    if (dual) launch_gemv_one<BITS, MT, true>(a, p, q);
-    else launch_gemv_one<BITS, MT, false>(a, p, q);
+    if (a.UC == 16) {
+        if (dual) {
+            if constexpr (MT <= 2) launch_gemv_one<BITS, MT, true, 16>(a, p, q);
+        } else {
+            launch_gemv_one<BITS, MT, false, 16>(a, p, q);
+        }
+    } else {
+        if (dual) {
+            if constexpr (MT <= 2) launch_gemv_one<BITS, MT, true, 8>(a, p, q);
+        } else {
+            launch_gemv_one<BITS, MT, false, 8>(a, p, q);
+        }
+    }
 }
 
 template <int BITS>
@@ -596,6 +584,23 @@ static void gemv_stream_bits(const GemvCall& call, cudaStream_t q) {
     const det_qlinear* L = call.lin;
     const StreamGeom g = stream_geom(L->N, L->K, BITS);
     DETB_REQUIRE(g.G <= 256, "K is too large for the streaming GEMV");
+    if (call.lin2 && call.M > 2) {
+        // more than two rows: the two linears go out as two launches (the second one reads the rows the first one's
+        // prologue stored, or quantizes them again when nothing was stored: same values either way)
+        GemvCall first = call, second = call;
+        first.lin2 = nullptr;
+        second.lin = call.lin2;
+        second.lin2 = nullptr;
+        second.out = call.out2;
+        second.h = nullptr;
+        if (call.src && call.src->xq) {
+            second.src = nullptr;
+            second.xq = call.src->xq; second.sx = call.src->sx; second.mx = call.src->mx;
+        }
+        gemv_stream_launch(first, q);
+        gemv_stream_launch(second, q);
+        return;
+    }
     const bool dual = call.lin2 != nullptr;
     StreamGeom g2 = g;
     if (dual) {
@@ -660,6 +665,7 @@ static void gemv_stream_bits(const GemvCall& call, cudaStream_t q) {
 void gemv_stream_launch(const GemvCall& call, cudaStream_t q) {
     const int bits = call.lin->bits & 0xff;
     if (call.src) {
+        DETB_REQUIRE(call.lin->K <= RREG * NCW * 128, "the activation prologue takes rows of at most 8192 values");
         DETB_REQUIRE((call.src->kind == PRO_RMS || call.src->kind == PRO_PLAIN) && call.src->a, "bad activation source");
         DETB_REQUIRE(call.src->kind != PRO_RMS || call.src->b, "RMSNorm needs its weight");
         DETB_REQUIRE((call.src->xq != nullptr) == (call.src->sx != nullptr) && (call.src->xq != nullptr) == (call.src->mx != nullptr),

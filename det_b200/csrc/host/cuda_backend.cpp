@@ -59,7 +59,7 @@ void CudaBackend::sync() {
 bool CudaBackend::hold(int kind, const float* a, const float* b, float eps, size_t m, size_t n, int8_t* xq, float* sx,
                        uint16_t* mx) {
     flush_pending();
-    if (!fuse_decode || !stream_layout || m > (size_t)stream_max_m || n % 128 != 0 || n > 32768 || !mx) return false;
+    if (!fuse_decode || !stream_layout || m > (size_t)stream_max_m || n % 128 != 0 || n > 8192 || !mx) return false;
     pending_.kind = kind;
     pending_.a = a; pending_.b = b; pending_.eps = eps;
     pending_.m = m; pending_.n = n;

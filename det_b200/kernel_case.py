@@ -82,7 +82,10 @@ def main(argv):
     d = capi.cuda()
     assert d.det_init() == 0
     if len(argv) >= 6:
-        d.det_debug_set_tc_variant(int(argv[5]))
+        if kind == "gemv":
+            d.det_debug_set_gemv(int(argv[5]))
+        else:
+            d.det_debug_set_tc_variant(int(argv[5]))
     ev = _Events(d.det_cuda_stream())
     xq, sx, mx, y = _activations(d, m, k, n)
     g = k // 128
