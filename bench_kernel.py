@@ -1,9 +1,9 @@
 """One linear of a chosen shape through the C ABI, timed with CUDA events: the small stand-alone case of the two GEMM
 kernels that a profiler capture needs (a few hundred MB on the device, a handful of launches).
 
-    python -m det_b200.kernel_case gemv    [N K bits M]    # k_gemv_stream, default 17408 5120 6 1
-    python -m det_b200.kernel_case gemm_tc [N K bits M [variant]]   # k_gemm_tc, default 17408 5120 6 512, tile by shape
-    python -m det_b200.kernel_case umma_peak                        # int8 tcgen05.mma issue rate with resident operands
+    python bench_kernel.py gemv    [N K bits M]    # k_gemv_stream, default 17408 5120 6 1
+    python bench_kernel.py gemm_tc [N K bits M [variant]]   # k_gemm_tc, default 17408 5120 6 512, tile by shape
+    python bench_kernel.py umma_peak                        # int8 tcgen05.mma issue rate with resident operands
 
 gemv: six copies of the weights (seeded, generated on the device, repacked into the streaming layout) are cycled through
 so that no launch finds its weights in the 126 MB L2; 6 warm-up launches, then 12 timed ones.
@@ -16,6 +16,8 @@ import sys
 
 import numpy as np
 
+import os
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 from det_b200 import capi
 
 PER32 = {8: 32, 6: 24, 4: 16}

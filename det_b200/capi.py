@@ -60,7 +60,7 @@ DET_LAYOUT_INT8 = 0x200
 DET_LAYOUT_PAIRS = 0x400
 DET_ACT_RMSNORM, DET_ACT_PLAIN = 1, 2
 # tile pins of the tensor-core GEMM (det_debug_set_tc_variant) that take large batches; 0 = chosen by shape
-TC_VARIANTS_LARGE = (0, 1, 5)
+TC_VARIANTS_LARGE = (0, 2, 3)
 
 # every symbol include/det_b200.h declares: name -> (restype, argtypes)
 CUDA_ABI = {

@@ -6,7 +6,15 @@
 // The inner sum of one 128-wide group is four UMMA steps (K = 32 bytes each) into a TMEM tile; the group multiplier
 // m * mx is a 32-bit integer that differs per (row, token, group), so every group's s32 tile is drained from TMEM and
 // folded into int64 registers by the epilogue warps while the tensor core already works on the following groups in the
-// other TMEM buffers (4 or 8 of them).  CTA tile: 128 weight rows (UMMA M, one TMEM lane per row) x 64 tokens (UMMA N).
+// other TMEM buffers.  CTA tile: 128 weight rows (UMMA M, one TMEM lane per row) x 32 / 64 / 128 tokens (UMMA N).
+//
+// The fold is ONE signed 32 x 32 + 64 multiply-add per (row, token, group): with S the group's s32 sum and u = m * mx
+// (up to 2^32 - 2^17, so it does not fit a signed word), the kernel adds S * (u - 2^31), where u - 2^31 does fit, and
+// repairs the difference at the end with 2^31 * (sum of S over all groups) — and that plain sum over the whole of K comes
+// from the tensor core as well: every UMMA step is issued a second time into a TMEM tile that is never reset (|sum| <=
+// K * 128 * 127 < 2^31 for K < 132096).  The tensor pipe has the room; the multiply pipe of the CUDA cores is what the
+// fold is short of (measured: with the loads, the MMAs or the TMEM reads switched off the kernel is no faster; without the
+// fold arithmetic it is).
 //
 // Warp roles (320 threads): warp 0 = TMA producer (one thread), warp 1 = TMEM allocation + MMA issue (one thread),
 // warps 2.. = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31 and a block of the token columns).  Operands come from an
@@ -35,8 +43,9 @@ struct TcCfg {
     static constexpr int THREADS = (2 + EPI_WARPS) * 32;
     // TMEM accumulator buffers: the MMA warp runs up to NBUF groups ahead of the epilogue, which hides the
     // commit -> mbarrier -> tcgen05.ld -> release round trip between the two
-    static constexpr int NBUF = TOK == 32 ? 8 : 4;
-    static constexpr int TMEM_COLS = NBUF * TOK;       // 256 or 512: a power of two
+    static constexpr int NBUF = TOK == 32 ? 8 : (TOK == 64 ? 4 : 3);
+    static constexpr int TOTAL_COL = NBUF * TOK;       // the running plain sum over K lives behind the group buffers
+    static constexpr int TMEM_COLS = 512;              // NBUF * TOK + TOK rounded up to a power of two
     // UMMA instruction descriptor (kind::i8): D = s32, A = B = signed 8-bit, both K-major, N = TOK, M = 128.
     static constexpr unsigned IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TOK >> 3) << 17) | ((TC_ROWS >> 4) << 24);
 };
@@ -98,18 +107,9 @@ __device__ __forceinline__ void tmem_ld(unsigned taddr, int (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
-// acc += (s32) p * (u32) mult, exactly, in three integer instructions: an unsigned 32x32+64 multiply-add, then the
-// high word loses `mult` when p is negative (p as unsigned is p + 2^32).
-__device__ __forceinline__ void mad_s32_u32(long long& acc, int p, unsigned mult) {
-    asm("{\n\t.reg .u32 lo, hi, corr;\n\t.reg .s32 sg;\n\t"
-        "mad.wide.u32 %0, %1, %2, %0;\n\t"
-        "shr.s32 sg, %1, 31;\n\t"
-        "and.b32 corr, sg, %2;\n\t"
-        "mov.b64 {lo, hi}, %0;\n\t"
-        "sub.u32 hi, hi, corr;\n\t"
-        "mov.b64 %0, {lo, hi};\n\t}"
-        : "+l"(acc)
-        : "r"(p), "r"(mult));
+// acc += (s32) p * (s32) mult: one signed 32 x 32 + 64 multiply-add.
+__device__ __forceinline__ void mad_s32_s32(long long& acc, int p, int mult) {
+    asm("mad.wide.s32 %0, %1, %2, %0;" : "+l"(acc) : "r"(p), "r"(mult));
 }
 
 struct TcArgs {
@@ -221,8 +221,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 const uint8_t* st = stages + (size_t)s * TC_STAGE_BYTES;
                 const unsigned long long da = umma_desc(st), db = umma_desc(st + TC_A_BYTES);
 #pragma unroll
-                for (int k = 0; k < 4; k++)
+                for (int k = 0; k < 4; k++) {
                     umma_i8(tmem_base + b * TC_TOK, da + 2 * k, db + 2 * k, Cfg::IDESC, k > 0 ? 1u : 0u);
+                    umma_i8(tmem_base + Cfg::TOTAL_COL, da + 2 * k, db + 2 * k, Cfg::IDESC, (g | k) ? 1u : 0u);
+                }
                 umma_commit(&empty[s]);
                 umma_commit(&tfull[b]);
             }
@@ -241,9 +243,6 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             mxs[i] = (a.mx && t0 + t < a.M) ? a.mx[(size_t)(t0 + t) * G + g] : (uint16_t)1;
         }
         asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
-        // Measured alternatives for the per-(row, token, group) step that did not pay: shifting the group sum to a
-        // non-negative value so that one unsigned multiply-add needs no sign fix (the sum of multipliers it needs costs
-        // as much as it saves), and more, narrower epilogue warps (same time per group).
         long long acc[EC];
 #pragma unroll
         for (int t = 0; t < EC; t++) acc[t] = 0;
@@ -266,9 +265,18 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #pragma unroll
             for (int t = 0; t < EC; t += 2) {
                 const unsigned pair = mxg[t >> 1];     // two u16 multipliers
-                mad_s32_u32(acc[t], r[t], mw * (pair & 0xffffu));
-                mad_s32_u32(acc[t + 1], r[t + 1], mw * (pair >> 16));
+                mad_s32_s32(acc[t], r[t], (int)(mw * (pair & 0xffffu) + 0x80000000u));
+                mad_s32_s32(acc[t + 1], r[t + 1], (int)(mw * (pair >> 16) + 0x80000000u));
             }
+        }
+        if (ok && GL > 0) {
+            // the last group's commit also covers every step into the running total: add 2^31 * (sum of S) back
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            int r[EC];
+            tmem_ld(tmem_base + ((unsigned)(q * 32) << 16) + Cfg::TOTAL_COL + half * EC, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int t = 0; t < EC; t++) acc[t] += (long long)r[t] << 31;
         }
         if (!ok && lane == 0) atomicExch(a.error_flag, DETB_ERR_WAIT_EXPIRED);
         if (gridDim.z > 1) {
@@ -468,18 +476,17 @@ static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const flo
     launch_pdl(k_gemm_tc<TOK, EC>, grid, dim3(Cfg::THREADS), smem, q, 1, map_w, map_x, a);
 }
 
-// Tile choice, by shape only.  variant 0 = default rule; other values pin one instantiation (measurement switch).
+// Tile choice, by shape only: 32 tokens per CTA up to 32 rows (the serving step), 64 up to 64, else 128.  variant 1 / 2 /
+// 3 pins the 32 / 64 / 128-token tile (measurement switch).
 static int g_tc_variant = 0;
 void gemm_tc_launch(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
                     const OutSpec& out, cudaStream_t q) {
     int v = g_tc_variant;
-    if (v == 0) v = M <= 32 ? 4 : 1;
+    if (v == 0) v = M <= 32 ? 1 : (M <= 64 ? 2 : 3);
     switch (v) {
-        case 1: gemm_tc_launch_tok<64, 32>(L, xq, sx, mx, M, out, q); break;
-        case 2: gemm_tc_launch_tok<64, 16>(L, xq, sx, mx, M, out, q); break;
-        case 3: gemm_tc_launch_tok<32, 8>(L, xq, sx, mx, M, out, q); break;
-        case 4: gemm_tc_launch_tok<32, 16>(L, xq, sx, mx, M, out, q); break;
-        case 5: gemm_tc_launch_tok<128, 32>(L, xq, sx, mx, M, out, q); break;
+        case 1: gemm_tc_launch_tok<32, 16>(L, xq, sx, mx, M, out, q); break;
+        case 2: gemm_tc_launch_tok<64, 32>(L, xq, sx, mx, M, out, q); break;
+        case 3: gemm_tc_launch_tok<128, 32>(L, xq, sx, mx, M, out, q); break;
         default: DETB_REQUIRE(false, "unknown tensor-core GEMM variant");
     }
 }
@@ -490,8 +497,7 @@ using namespace detb;
 
 extern "C" {
 
-// Measurement switch: 0 = tile chosen by shape; 1..5 pin (tokens, columns per epilogue warp) = (64,32) (64,16) (32,8)
-// (32,16) (128,32).  Results do not depend on it.
+// Measurement switch: 0 = tile chosen by shape; 1 / 2 / 3 pin the 32 / 64 / 128-token tile.  Results do not depend on it.
 void det_debug_set_tc_variant(int v) {
     g_tc_variant = v & 0xff;
     if (v & 0x300) g_tc_splitk = (v & 0x100) != 0;   // 0x100: split K on, 0x200: off

@@ -286,9 +286,9 @@ void det_debug_set_pdl(int on);
 /* Measurement switch for the row kernels: calls with at least min_rows rows (default 128; 0 = never) use one CTA per row
  * instead of a cluster per row.  Same results.                                                                       */
 void det_debug_set_rows(int min_rows);
-/* Measurement switch: pins the tensor-core GEMM's tile, 1..5 = (tokens, columns per epilogue warp) (64,32) (64,16)
- * (32,8) (32,16) (128,32); 0 = chosen by shape (default).  Adding 0x100 / 0x200 switches the split of K over several
- * CTAs for linears with few row tiles on / off.  Results do not depend on any of it.                                   */
+/* Measurement switch: pins the tensor-core GEMM's tile, 1 / 2 / 3 = 32 / 64 / 128 tokens per CTA; 0 = chosen by shape
+ * (default).  Adding 0x100 / 0x200 switches the split of K over several CTAs for linears with few row tiles on / off.
+ * Results do not depend on any of it.                                                                                 */
 void det_debug_set_tc_variant(int v);
 /* Measurement switch of the decode GEMV: bit 0 = a CTA takes a whole SM's shared memory (no co-residency with the next
  * launch); bits 8.. = CTAs per SM of one launch (default 1).  Results do not depend on it.                           */

@@ -61,9 +61,9 @@ def test_gemm_matches_oracle(n, k, bits, ms, libs, oracle):
             d.det_memcpy(dm, mx.ctypes.data, mx.nbytes, None)
             cases = [("stream", stream, 0), ("rowmajor", src, 0)]
             # every tile instantiation of the tensor-core kernel (0 = the one the shape selects)
-            cases += [(f"int8 tensor-core, tile variant {v}", tensor, v) for v in (0, 1, 2, 3, 4, 5)]
+            cases += [(f"int8 tensor-core, tile variant {v}", tensor, v) for v in (0, 1, 2, 3)]
             # K split over several CTAs per tile (takes effect on the shapes with few row tiles)
-            cases += [(f"int8 tensor-core, split K, tile variant {v}", tensor, v | 0x100) for v in (0, 1, 4)]
+            cases += [(f"int8 tensor-core, split K, tile variant {v}", tensor, v | 0x100) for v in (0, 1, 2)]
             for name, lin, variant in cases:
                 got = np.zeros_like(want)
                 d.det_memset(dy, 0xFF, want.nbytes, None)
