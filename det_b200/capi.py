@@ -130,6 +130,9 @@ CUDA_ABI = {
     "det_xchg_add_rmsnorm_quant": (None, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int,
                                           c_void_p, c_void_p, c_void_p, c_void_p]),
     "det_xchg_quant": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "det_quantize_rows": (None, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "det_absmax_heads": (None, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "det_embed_table": (None, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "det_debug_set_pdl": (None, [c_int]),
     "det_debug_set_tc_variant": (None, [c_int]),
     "det_debug_set_gemv": (None, [c_int]),
@@ -149,6 +152,31 @@ HOST_API = {
     "dh_cuda_debug": (None, [c_void_p, C.c_uint, c_int]),
     "dh_cuda_test_prim": (None, [c_int, c_void_p, c_size_t, c_size_t, c_size_t, c_void_p, c_size_t]),
     "dh_model_new_synth": (c_void_p, [c_void_p, c_char_p, c_size_t, c_u64, c_size_t, c_size_t]),
+    "dh_model_load": (c_void_p, [c_void_p, c_char_p, c_size_t, c_size_t]),
+    "dh_model_calibrated": (c_int, [c_void_p]),
+    "dh_write_synthetic_gguf": (c_int, [c_char_p, c_size_t, c_u64, c_char_p, c_size_t]),
+    "dh_write_synthetic_source_gguf": (c_int, [c_char_p, c_size_t, c_u64, c_char_p, c_size_t, c_int]),
+    "dh_convert": (c_int, [c_char_p, c_char_p, c_char_p, c_size_t, c_int]),
+    "dh_convert_default_output": (c_int, [c_char_p, c_char_p, c_char_p, c_size_t]),
+    "dh_v_scales": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p, c_size_t, C.POINTER(c_size_t)]),
+    "dh_calibration_ids": (None, [c_void_p, c_size_t, c_size_t, c_size_t, c_void_p]),
+    "dh_write_scales_in_place": (c_int, [c_void_p, c_void_p, c_size_t, c_char_p]),
+    "dh_write_scales_copy": (c_int, [c_void_p, c_void_p, c_size_t, c_char_p]),
+    "dh_gguf_open": (c_void_p, [c_char_p]),
+    "dh_gguf_close": (None, [c_void_p]),
+    "dh_gguf_n_tensors": (c_size_t, [c_void_p]),
+    "dh_gguf_data_start": (c_size_t, [c_void_p]),
+    "dh_gguf_tensor": (c_int, [c_void_p, c_size_t, c_char_p, c_size_t, c_void_p, C.POINTER(c_size_t),
+                               C.POINTER(C.c_uint32), C.POINTER(c_size_t), C.POINTER(c_size_t)]),
+    "dh_gguf_get": (c_int, [c_void_p, c_char_p, c_char_p, c_size_t]),
+    "dh_gguf_config": (c_int, [c_void_p, c_char_p, c_size_t]),
+    "dh_gguf_check_finite": (c_int, [c_void_p]),
+    "dh_dequant_row": (c_int, [C.c_uint32, c_void_p, c_size_t, c_void_p]),
+    "dh_quantize_row": (None, [c_void_p, c_size_t, c_int, c_void_p]),
+    "dh_model_forward_observed": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_int]),
+    "dh_model_generate_observed": (c_int, [c_void_p, c_void_p, c_size_t, c_size_t, c_int, c_float, c_size_t, c_float, c_u64,
+                                           c_void_p, C.POINTER(c_size_t), c_void_p, c_void_p, c_int]),
+    "dh_backend_read": (None, [c_void_p, c_void_p, c_void_p, c_size_t]),
     "dh_nccl_unique_id": (None, [c_void_p]),
     "dh_nccl_comm_new": (c_void_p, [c_void_p, c_int, c_int]),
     "dh_callback_comm_new": (c_void_p, [c_int, c_int, c_void_p]),
@@ -186,6 +214,10 @@ HOST_API = {
     "dh_synth_det_rows": (None, [c_u64, c_u64, c_size_t, c_size_t, c_int, c_void_p]),
     "dh_det_row_bytes": (c_size_t, [c_int, c_size_t]),
 }
+
+# The tap callback of dh_model_forward_observed: (user, kind, layer, pos0, t, data, len, id, rng)
+TAP_FN = C.CFUNCTYPE(None, c_void_p, c_int, c_size_t, c_size_t, c_size_t, c_void_p, c_size_t, c_i32, c_u64)
+TAP_KINDS = ("Residual", "MixerOut", "PostMixer", "AttnV", "Kv", "AttnOut", "GdnIn", "GdnOut", "GdnState", "Logits", "Token")
 
 _cache: dict[str, C.CDLL] = {}
 

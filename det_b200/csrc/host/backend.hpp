@@ -3,6 +3,7 @@
 // GdnShape, trait Backend).  Names, argument order and meaning follow the trait so that the driver
 // (model.hpp, the mirror of qwen35.rs / model.rs) and the conformance suites read like the reference's.
 #pragma once
+#include <cmath>
 #include <cstddef>
 #include <cstdint>
 #include <cstring>
@@ -170,6 +171,24 @@ class Backend {
     // SwiGLU product without quantization (h[i] = silu_f(g[i]) * u[i]) — each exactly one spec operation per element.
     virtual void add(const Buf<float>& x, const Buf<float>& y, size_t n) = 0;
     virtual void silu_mul(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<float>& h) = 0;
+    // The calibration fold (crates/det/src/calibrate.rs:21-36; an observer's own work in the reference):
+    // slots[h] = max(slots[h], largest |v[row][h][0..hd)|) over the t rows.  The default reads v back and folds on the
+    // host; a device backend may fold in place on its queue.
+    virtual void absmax_heads(const Buf<float>& v, size_t t, size_t heads, size_t hd, const Buf<float>& slots) {
+        std::vector<float> x(t * heads * hd), s(heads);
+        read(v, 0, x.data(), x.size());
+        read(slots, 0, s.data(), heads);
+        for (size_t r = 0; r < t; r++)
+            for (size_t h = 0; h < heads; h++) {
+                float m = 0.0f;
+                for (size_t i = 0; i < hd; i++) {
+                    const float a = std::fabs(x[(r * heads + h) * hd + i]);
+                    m = a > m ? a : m;   // a NaN never wins, as with f32::max
+                }
+                s[h] = m > s[h] ? m : s[h];
+            }
+        write(slots, 0, s.data(), heads);
+    }
     // Batched serving decode (not in the reference trait, whose Model holds one sequence): `rows` sequences advance one
     // token each.  Row b of qg/k/v/o (or qkv/z/a/b/on) belongs to sequence b, with its own cache or state and its own
     // position pos[b] (a backend buffer of rows int32).  The defaults compose the step from the unchanged single-

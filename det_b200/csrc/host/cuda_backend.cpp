@@ -501,6 +501,38 @@ std::vector<uint8_t> cuda_synth_det_rows(uint64_t seed, uint64_t tid, size_t src
     return out;
 }
 
+void cuda_quantize_rows(const uint8_t* src, int ggml_type, size_t src_rows, const std::vector<int>* row_perm,
+                        const std::vector<int>* col_perm, size_t n, size_t k, int bits, uint8_t* out) {
+    const size_t esz = ggml_type == 0 ? 4 : 2, g = k / 128, rb = k / 32 * bytes_per_32(bits) + 4 + 2 * g;
+    const size_t chunk = std::min<size_t>(n, std::max<size_t>(1, ((size_t)256 << 20) / rb));   // <= 256 MB of rows per pass
+    void* dsrc = det_malloc(src_rows * k * esz);
+    void* drows = det_malloc(chunk * rb);
+    void* tmp = det_malloc(chunk * g * sizeof(double));
+    void* drp = row_perm ? det_malloc(n * sizeof(int)) : nullptr;
+    void* dcp = col_perm ? det_malloc(k * sizeof(int)) : nullptr;
+    if (!dsrc || !drows || !tmp || (row_perm && !drp) || (col_perm && !dcp))
+        throw std::runtime_error("cuda_quantize_rows: out of device memory");
+    det_memcpy(dsrc, src, src_rows * k * esz, ST);
+    if (drp) det_memcpy(drp, row_perm->data(), n * sizeof(int), ST);
+    if (dcp) det_memcpy(dcp, col_perm->data(), k * sizeof(int), ST);
+    for (size_t r0 = 0; r0 < n; r0 += chunk) {
+        const size_t rows = std::min(chunk, n - r0);
+        // without a row permutation the chunk starts at source row r0; with one, the permutation is offset instead
+        const void* base = drp ? dsrc : static_cast<const uint8_t*>(dsrc) + r0 * k * esz;
+        det_quantize_rows(base, ggml_type, drp ? static_cast<const int*>(drp) + r0 : nullptr, static_cast<const int*>(dcp),
+                          (int)rows, (int)k, bits, static_cast<uint8_t*>(drows), static_cast<double*>(tmp), ST);
+        det_memcpy(out + r0 * rb, drows, rows * rb, ST);
+        det_sync();
+    }
+    for (void* p : {dsrc, drows, tmp, drp, dcp})
+        if (p) det_free(p);
+}
+
+void CudaBackend::absmax_heads(const Buf<float>& v, size_t t, size_t heads, size_t hd, const Buf<float>& slots) {
+    flush_pending();
+    det_absmax_heads(v.ptr(), (int)t, (int)heads, (int)hd, slots.ptr(), ST);
+}
+
 // Every linear of the model once at M = 1 (the launches of one decoded token's GEMVs), `reps` times.
 GemvSweep gemv_sweep(Model& m, int reps) {
     GemvSweep r{0, 0};

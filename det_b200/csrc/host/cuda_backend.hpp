@@ -53,6 +53,7 @@ class CudaBackend : public Backend {
     std::vector<int32_t> sample_rows(const Buf<float>& logits, size_t rows, size_t v, float inv_temp, size_t top_k,
                                      float top_p, const std::vector<uint64_t>& z) override;
     bool fuse_rows = true;
+    void absmax_heads(const Buf<float>& v, size_t t, size_t heads, size_t hd, const Buf<float>& slots) override;
     void add(const Buf<float>& x, const Buf<float>& y, size_t n) override;
     void silu_mul(const Buf<float>& g, const Buf<float>& u, size_t m, size_t n, const Buf<float>& h) override;
     int32_t argmax(const Buf<float>& logits, size_t v) override;
@@ -120,6 +121,10 @@ class CudaBackend : public Backend {
 };
 
 std::vector<uint8_t> cuda_synth_det_rows(uint64_t seed, uint64_t tid, size_t src0, size_t n, size_t k, int bits);
+// The device row quantizer for convert() (a RowQuantizer, convert.hpp): uploads the source tensor, runs
+// det_quantize_rows in chunks of rows and copies the det file rows back.  Same bytes as host_quantize_rows.
+void cuda_quantize_rows(const uint8_t* src, int ggml_type, size_t src_rows, const std::vector<int>* row_perm,
+                        const std::vector<int>* col_perm, size_t n, size_t k, int bits, uint8_t* out);
 
 class Model;
 struct GemvSweep {

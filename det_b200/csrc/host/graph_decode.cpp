@@ -10,8 +10,16 @@ constexpr cudaStream_t ST = nullptr;
 GraphDecoder::GraphDecoder(Model& m) : m_(m), bk_(dynamic_cast<CudaBackend*>(m.backend)) {
     if (!bk_) throw std::runtime_error("GraphDecoder needs a model on the CUDA backend");
     const size_t count = m.cfg.vocab * m.cfg.hidden;
-    table_ = bk_->alloc<uint16_t>(count);
-    det_synth_bf16(m.seed, tensor_id(GLOBAL_LAYER, T_EMBED), (long long)count, table_.ptr(), ST);
+    if (m.gguf) {   // the file's own table, whatever float type it has (model.rs:389-413 reads it row by row on the host)
+        GgmlType ty = GgmlType::BF16;
+        m.embed.type(ty);
+        table_type_ = (int)ty;
+        table_ = bk_->alloc<uint8_t>(m.embed.bytes());
+        bk_->write_bytes(table_.ptr(), m.gguf->data(m.embed), m.embed.bytes());
+    } else {
+        table_ = bk_->alloc<uint8_t>(count * 2);
+        det_synth_bf16(m.seed, tensor_id(GLOBAL_LAYER, T_EMBED), (long long)count, reinterpret_cast<uint16_t*>(table_.ptr()), ST);
+    }
     pick_ = bk_->alloc<int32_t>(1);
     pos_ = bk_->alloc<int32_t>(1);
     log_ = bk_->alloc<int32_t>(m.max_ctx);   // the pick made after the step at position p lands in log_[p]
@@ -26,7 +34,7 @@ GraphDecoder::~GraphDecoder() {
 
 // embed(token in device memory) -> network at the device position -> argmax -> log the pick, advance the position
 void GraphDecoder::step() {
-    det_embed(table_.ptr(), pick_.ptr(), 1, (int)m_.cfg.hidden, m_.w.x.ptr(), ST);
+    det_embed_table(table_.ptr(), table_type_, pick_.ptr(), 1, (int)m_.cfg.hidden, m_.w.x.ptr(), ST);
     bk_->pos_dev = pos_.ptr();
     bk_->max_pos = (int)m_.max_ctx - 1;
     m_.network(0, 1);

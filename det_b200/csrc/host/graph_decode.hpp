@@ -22,7 +22,8 @@ class GraphDecoder {
     void step();   // one decode step through the C ABI, device-resident token and position
     Model& m_;
     CudaBackend* bk_;
-    Buf<uint16_t> table_;   // bf16 embedding table [vocab][hidden]
+    Buf<uint8_t> table_;    // embedding table [vocab][hidden] of ggml type table_type_ (30 = bf16 for a synthetic model)
+    int table_type_ = 30;
     Buf<int32_t> pick_, pos_, log_;
     void* graph_ = nullptr;
     size_t queued_ = 0, log_base_ = 0;

@@ -1,5 +1,6 @@
 // Model loading (synthetic), the network's op sequence and the token loop.  See model.hpp for the reference map.
 #include "model.hpp"
+#include "gguf.hpp"
 #include <algorithm>
 #include <cmath>
 #include <stdexcept>
@@ -9,13 +10,16 @@ namespace det {
 static SynthRowsProvider g_rows_provider = nullptr;
 void set_synth_rows_provider(SynthRowsProvider p) { g_rows_provider = p; }
 
+std::vector<uint8_t> synth_det_rows_any(uint64_t seed, uint64_t tid, size_t row0, size_t n, size_t k, int bits) {
+    return g_rows_provider ? g_rows_provider(seed, tid, row0, n, k, bits) : synth_det_rows(seed, tid, n, k, bits, row0);
+}
+
 // Default of Backend::linear_synth: det rows on the host, then the ordinary weight-ingestion path.
 std::unique_ptr<Linear> Backend::linear_synth(uint64_t seed, const std::vector<SynthPart>& parts, size_t k, int bits) {
     std::vector<std::vector<uint8_t>> rows;
     std::vector<LinearPart> lp;
     for (const SynthPart& p : parts) {
-        rows.push_back(g_rows_provider ? g_rows_provider(seed, p.tensor_id, p.row0, p.n, k, bits)
-                                       : synth_det_rows(seed, p.tensor_id, p.n, k, bits, p.row0));
+        rows.push_back(synth_det_rows_any(seed, p.tensor_id, p.row0, p.n, k, bits));
         lp.push_back(LinearPart{rows.back().data(), p.n});
     }
     return linear(lp, k, bits);
@@ -46,6 +50,44 @@ Buf<float> ones(Backend* bk, size_t n) { return bk->upload(std::vector<float>(n,
 }  // namespace
 
 static void load_shard(Model& m, const Config& cfg, uint64_t seed, Backend* bk, size_t max_ctx, size_t max_batch);
+
+// model.rs:316-347 — the activation buffers of a single-device model for max_batch rows.
+static void alloc_work(Model& m) {
+    const Config& cfg = m.cfg;
+    Backend* bk = m.backend;
+    const size_t h = cfg.hidden, inter = cfg.intermediate;
+    const size_t n_h = cfg.n_heads, n_kv = cfg.n_kv, hd = cfg.head_dim;
+    const size_t n_v = cfg.gdn_v_heads, dv = cfg.gdn_dv;
+    const size_t conv_dim = cfg.conv_dim();
+    const size_t mb = m.max_batch;
+    Work& w = m.w;
+    w.x = bk->alloc<float>(mb * h);
+    w.xq = bk->alloc<int8_t>(mb * h);
+    w.sx = bk->alloc<float>(mb);
+    w.mx = bk->alloc<uint16_t>(mb * h / 128);
+    w.qg = bk->alloc<float>(mb * n_h * 2 * hd);
+    w.k = bk->alloc<float>(mb * n_kv * hd);
+    w.v = bk->alloc<float>(mb * n_kv * hd);
+    w.o = bk->alloc<float>(mb * n_h * hd);
+    w.oq = bk->alloc<int8_t>(mb * n_h * hd);
+    w.so = bk->alloc<float>(mb);
+    w.mo = bk->alloc<uint16_t>(mb * n_h * hd / 128);
+    w.qkv = bk->alloc<float>(mb * conv_dim);
+    w.z = bk->alloc<float>(mb * n_v * dv);
+    w.a = bk->alloc<float>(mb * n_v);
+    w.b = bk->alloc<float>(mb * n_v);
+    w.on = bk->alloc<float>(mb * n_v * dv);
+    w.onq = bk->alloc<int8_t>(mb * n_v * dv);
+    w.son = bk->alloc<float>(mb);
+    w.mon = bk->alloc<uint16_t>(mb * n_v * dv / 128);
+    w.g = bk->alloc<float>(mb * inter);
+    w.u = bk->alloc<float>(mb * inter);
+    w.hq = bk->alloc<int8_t>(mb * inter);
+    w.sh = bk->alloc<float>(mb);
+    w.mh = bk->alloc<uint16_t>(mb * inter / 128);
+    w.logits = bk->alloc<float>(cfg.vocab);
+}
+
 
 std::unique_ptr<Model> Model::load_synthetic(const Config& cfg, uint64_t seed, Backend* bk, size_t max_ctx,
                                              size_t max_batch, Comm* comm) {
@@ -116,33 +158,138 @@ std::unique_ptr<Model> Model::load_synthetic(const Config& cfg, uint64_t seed, B
         l.gu = make_proj(bk, seed, i, {{T_FFN_GATE, inter, h, wb}, {T_FFN_UP, inter, h, wb}});
         l.down = make_proj(bk, seed, i, {{T_FFN_DOWN, h, inter, wb}});
     }
-    const size_t mb = max_batch;
-    Work& w = m.w;   // model.rs:316-347
-    w.x = bk->alloc<float>(mb * h);
-    w.xq = bk->alloc<int8_t>(mb * h);
-    w.sx = bk->alloc<float>(mb);
-    w.mx = bk->alloc<uint16_t>(mb * h / 128);
-    w.qg = bk->alloc<float>(mb * n_h * 2 * hd);
-    w.k = bk->alloc<float>(mb * n_kv * hd);
-    w.v = bk->alloc<float>(mb * n_kv * hd);
-    w.o = bk->alloc<float>(mb * n_h * hd);
-    w.oq = bk->alloc<int8_t>(mb * n_h * hd);
-    w.so = bk->alloc<float>(mb);
-    w.mo = bk->alloc<uint16_t>(mb * n_h * hd / 128);
-    w.qkv = bk->alloc<float>(mb * conv_dim);
-    w.z = bk->alloc<float>(mb * n_v * dv);
-    w.a = bk->alloc<float>(mb * n_v);
-    w.b = bk->alloc<float>(mb * n_v);
-    w.on = bk->alloc<float>(mb * n_v * dv);
-    w.onq = bk->alloc<int8_t>(mb * n_v * dv);
-    w.son = bk->alloc<float>(mb);
-    w.mon = bk->alloc<uint16_t>(mb * n_v * dv / 128);
-    w.g = bk->alloc<float>(mb * inter);
-    w.u = bk->alloc<float>(mb * inter);
-    w.hq = bk->alloc<int8_t>(mb * inter);
-    w.sh = bk->alloc<float>(mb);
-    w.mh = bk->alloc<uint16_t>(mb * inter / 128);
-    w.logits = bk->alloc<float>(cfg.vocab);
+    alloc_work(m);
+    return mp;
+}
+
+// model.rs:164-365
+std::unique_ptr<Model> Model::load(const std::string& path, Backend* bk, size_t max_ctx, size_t max_batch, std::string& err) {
+    std::shared_ptr<Gguf> g = Gguf::open(path, err);
+    if (!g) return nullptr;
+    auto mp = std::make_unique<Model>();
+    Model& m = *mp;
+    if (!(err = config_from_gguf(*g, m.cfg)).empty()) return nullptr;
+    if (!(err = check_finite(*g)).empty()) return nullptr;
+    const Config& cfg = m.cfg;
+    m.backend = bk;
+    m.max_ctx = max_ctx;
+    m.max_batch = max_batch;
+    m.gguf = g;
+    try {
+        auto tensor = [&](const std::string& name) -> const GgufTensor& {
+            const GgufTensor* t = g->tensor(name);
+            if (!t) throw std::runtime_error("missing tensor " + name);
+            return *t;
+        };
+        auto vec = [&](const std::string& name) {
+            const GgufTensor& t = tensor(name);
+            GgmlType ty;
+            if (!t.type(ty)) throw std::runtime_error(name + ": unsupported type");
+            std::vector<float> out(t.n_elems());
+            dequant_row(ty, g->data(t), out.size(), out.data());
+            return bk->upload(out);
+        };
+        // model.rs:180-197 — consecutive tensors of equal type and row length become one fused linear
+        auto proj = [&](const std::vector<std::string>& names) {
+            std::vector<const GgufTensor*> infos;
+            for (const std::string& n : names) infos.push_back(&tensor(n));
+            Proj p;
+            size_t i = 0;
+            while (i < infos.size()) {
+                size_t j = i + 1;
+                while (j < infos.size() && infos[j]->type_id == infos[i]->type_id && infos[j]->dims[0] == infos[i]->dims[0]) j++;
+                GgmlType ty;
+                if (!infos[i]->type(ty) || !ggml_type_bits(ty) || infos[i]->dims.size() != 2)
+                    throw std::runtime_error(infos[i]->name + ": not a det linear");
+                std::vector<LinearPart> parts;
+                for (size_t q = i; q < j; q++) parts.push_back(LinearPart{g->data(*infos[q]), infos[q]->dims[1]});
+                p.lins.push_back(bk->linear(parts, infos[i]->dims[0], ggml_type_bits(ty)));
+                i = j;
+            }
+            return p;
+        };
+        m.embed = tensor("token_embd.weight");
+        GgmlType ety;
+        if (!m.embed.type(ety) || ggml_type_bits(ety) || m.embed.dims != std::vector<size_t>{cfg.hidden, cfg.vocab})
+            throw std::runtime_error("token_embd.weight: not a float [hidden][vocab] table");
+        m.final_norm = vec("output_norm.weight");
+        const GgufTensor* rope = g->tensor("rope_cos");
+        if (!rope) throw std::runtime_error("no rope tables; run `det convert`");
+        if (rope->dims.size() < 2 || rope->dims[1] < max_ctx)
+            throw std::runtime_error("rope tables cover " + std::to_string(rope->dims.size() < 2 ? 0 : rope->dims[1]) +
+                                     " positions, context " + std::to_string(max_ctx) + " requested");
+        m.rope_cos = vec("rope_cos");
+        m.rope_sin = vec("rope_sin");
+        m.lm_head = proj({"output.weight"});
+
+        std::vector<float> v_scales;
+        bool have_scales = false;
+        if (const GgufValue* a = g->get(V_SCALE_KEY); a && a->type == 9) {
+            have_scales = true;
+            const size_t want = cfg.n_attention_layers() * cfg.n_kv;
+            bool ok = a->arr.size() == want;
+            for (const GgufValue& x : a->arr) {
+                float s = 0.0f;
+                ok = ok && x.as_f32(s) && std::isfinite(s) && s > 0.0f;
+                v_scales.push_back(s);
+            }
+            if (!ok) throw std::runtime_error(std::string(V_SCALE_KEY) + ": expected " + std::to_string(want) + " positive floats");
+        }
+        for (float s : v_scales) m.calibrated = m.calibrated || s != DEFAULT_V_SCALE;
+
+        const size_t n_h = cfg.n_heads, n_kv = cfg.n_kv, hd = cfg.head_dim;
+        const size_t n_v = cfg.gdn_v_heads, dk = cfg.gdn_dk, dv = cfg.gdn_dv, conv_dim = cfg.conv_dim();
+        (void)n_h;
+        size_t attn_index = 0;
+        m.layers.resize(cfg.n_layers);
+        for (size_t i = 0; i < cfg.n_layers; i++) {
+            Layer& l = m.layers[i];
+            auto n = [&](const char* s) { return "blk." + std::to_string(i) + "." + s; };
+            l.is_attn = cfg.is_attention(i);
+            if (l.is_attn) {
+                Attn& a = l.attn;
+                std::vector<float> vs(n_kv, DEFAULT_V_SCALE), vis(n_kv);
+                if (have_scales) vs.assign(v_scales.begin() + attn_index * n_kv, v_scales.begin() + (attn_index + 1) * n_kv);
+                attn_index++;
+                for (size_t q = 0; q < n_kv; q++) vis[q] = 1.0f / vs[q];
+                a.kv.kq = bk->alloc<int8_t>(max_ctx * n_kv * hd);
+                a.kv.sk = bk->alloc<float>(max_ctx * n_kv);
+                a.kv.vq = bk->alloc<int16_t>(max_ctx * n_kv * hd);
+                a.kv.capacity = max_ctx;
+                a.qkv = proj({n("attn_q.weight"), n("attn_k.weight"), n("attn_v.weight")});
+                a.o = proj({n("attn_output.weight")});
+                a.q_norm = vec(n("attn_q_norm.weight"));
+                a.k_norm = vec(n("attn_k_norm.weight"));
+                a.v_scale = bk->upload(vs);
+                a.v_inv_scale = bk->upload(vis);
+            } else {
+                Gdn& gd = l.gdn;
+                const GgufTensor& at = tensor(n("ssm_a"));
+                GgmlType aty;
+                if (!at.type(aty) || ggml_type_bits(aty)) throw std::runtime_error(at.name + ": not a float vector");
+                std::vector<float> av(at.n_elems());
+                dequant_row(aty, g->data(at), av.size(), av.data());
+                for (float& v : av) v = -v;
+                gd.qkvz = proj({n("attn_qkv.weight"), n("attn_gate.weight")});
+                gd.ab = proj({n("ssm_alpha.weight"), n("ssm_beta.weight")});
+                gd.out = proj({n("ssm_out.weight")});
+                gd.conv = vec(n("ssm_conv1d.weight"));
+                gd.a = bk->upload(av);
+                gd.dt_bias = vec(n("ssm_dt.bias"));
+                gd.norm = vec(n("ssm_norm.weight"));
+                gd.state.conv_state = bk->alloc<float>((cfg.conv_k - 1) * conv_dim);
+                gd.state.s = bk->alloc<float>(n_v * dk * dv);
+            }
+            l.attn_norm = vec(n("attn_norm.weight"));
+            l.ffn_norm = vec(n("post_attention_norm.weight"));
+            l.gu = proj({n("ffn_gate.weight"), n("ffn_up.weight")});
+            l.down = proj({n("ffn_down.weight")});
+        }
+        alloc_work(m);
+    } catch (const std::exception& ex) {
+        err = ex.what();
+        return nullptr;
+    }
     return mp;
 }
 
@@ -167,11 +314,16 @@ std::string Model::embed_rows(const int32_t* ids, size_t t) {
     const size_t h = cfg.hidden;
     std::vector<float> x(t * h);
     const uint64_t tid = tensor_id(GLOBAL_LAYER, T_EMBED);
+    GgmlType ety = GgmlType::BF16;
+    if (gguf) embed.type(ety);
+    const size_t rb = ggml_row_bytes(ety, h);
     for (size_t i = 0; i < t; i++) {
         if (ids[i] < 0 || (size_t)ids[i] >= cfg.vocab)
             return "token id " + std::to_string(ids[i]) + " is outside the embedding table (" +
                    std::to_string(cfg.vocab) + " rows)";
-        for (size_t j = 0; j < h; j++) x[i * h + j] = synth_weight(seed, tid, (uint64_t)ids[i] * h + j);
+        if (gguf) dequant_row(ety, gguf->data(embed) + (size_t)ids[i] * rb, h, x.data() + i * h);
+        else
+            for (size_t j = 0; j < h; j++) x[i * h + j] = synth_weight(seed, tid, (uint64_t)ids[i] * h + j);
     }
     backend->write(w.x, 0, x.data(), x.size());
     return "";
@@ -190,22 +342,42 @@ void Model::project(const Proj& p, const Buf<int8_t>& xq, const Buf<float>& sx, 
 }
 
 // qwen35.rs:31-170
-void Model::network(size_t pos0, size_t t) {
+void Model::network(size_t pos0, size_t t, Observer* obs) {
     if (comm) {
+        if (obs) throw std::logic_error("observers are not supported on a tensor-parallel shard");
         network_tp(pos0, t);
         return;
     }
     const Config& c = cfg;
     Backend* bk = backend;
     const size_t h = c.hidden;
-    for (Layer& l : layers) {
+    const Ctx ctx{pos0, t, bk};
+    const bool gdn_io = obs && obs->wants_gdn_io();
+    auto observe = [&](Tap::Kind kind, size_t layer, const Buf<float>* x, const KvCache* kv = nullptr,
+                       const GdnState* st = nullptr) {
+        if (!obs) return;
+        Tap tap;
+        tap.kind = kind;
+        tap.layer = layer;
+        tap.x = x;
+        tap.kv = kv;
+        tap.state = st;
+        obs->observe(ctx, tap);
+    };
+    for (size_t li = 0; li < layers.size(); li++) {
+        Layer& l = layers[li];
+        observe(Tap::Residual, li, &w.x);
         bk->rmsnorm_quant(w.x, l.attn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
         if (l.is_attn) {
             Attn& a = l.attn;
             project(a.qkv, w.xq, w.sx, w.mx, t, {&w.qg, &w.k, &w.v});
+            observe(Tap::AttnV, li, &w.v);
             AttnLayer layer{&a.q_norm, &a.k_norm, &a.v_scale, &a.v_inv_scale, &rope_cos, &rope_sin};
             Shape shape{t, pos0, c.n_heads, c.n_kv, c.head_dim, c.rot_dim, c.eps};
             bk->attention(layer, a.kv, shape, w.qg, w.k, w.v, w.o);
+            observe(Tap::Kv, li, nullptr, &a.kv);
+            observe(Tap::AttnOut, li, &w.o);
+            observe(Tap::MixerOut, li, &w.o);
             bk->quant(w.o, t, c.n_heads * c.head_dim, w.oq, w.so, w.mo);
             bk->gemm(*a.o.lins[0], w.oq, w.so, w.mo, t, GemmOut::accumulate(w.x));
         } else {
@@ -214,15 +386,32 @@ void Model::network(size_t pos0, size_t t) {
             GdnLayer layer{&g.conv, &g.a, &g.dt_bias, &g.norm};
             GdnShape shape{t, c.gdn_k_heads, c.gdn_v_heads, c.gdn_dk, c.gdn_dv, c.eps};
             project(g.ab, w.xq, w.sx, w.mx, t, {&w.a, &w.b});
-            bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.on, GdnExport{});
+            GdnExport ex;
+            if (gdn_io) {
+                const size_t rep = c.gdn_v_heads / c.gdn_k_heads;
+                const size_t gw = 2 * c.gdn_dk + c.gdn_dv * rep + 2 * rep;   // model.rs:315
+                if (w.gin.len() < max_batch * c.gdn_k_heads * gw) w.gin = bk->alloc<float>(max_batch * c.gdn_k_heads * gw);
+                if (w.gout.len() < max_batch * c.gdn_v_heads * c.gdn_dv) w.gout = bk->alloc<float>(max_batch * c.gdn_v_heads * c.gdn_dv);
+                ex.gin = &w.gin;
+                ex.gout = &w.gout;
+            }
+            bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.on, ex);
+            if (gdn_io) {
+                observe(Tap::GdnIn, li, &w.gin);
+                observe(Tap::GdnOut, li, &w.gout);
+            }
+            observe(Tap::GdnStateTap, li, nullptr, nullptr, &g.state);
+            observe(Tap::MixerOut, li, &w.on);
             bk->quant(w.on, t, c.gdn_v_heads * c.gdn_dv, w.onq, w.son, w.mon);
             bk->gemm(*g.out.lins[0], w.onq, w.son, w.mon, t, GemmOut::accumulate(w.x));
         }
+        observe(Tap::PostMixer, li, &w.x);
         bk->rmsnorm_quant(w.x, l.ffn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
         project(l.gu, w.xq, w.sx, w.mx, t, {&w.g, &w.u});
         bk->silu_mul_quant(w.g, w.u, t, c.intermediate, w.hq, w.sh, w.mh);
         bk->gemm(*l.down.lins[0], w.hq, w.sh, w.mh, t, GemmOut::accumulate(w.x));
     }
+    observe(Tap::Residual, layers.size(), &w.x);
     if (all_logits) {
         bk->rmsnorm_quant(w.x, final_norm, c.eps, t, h, w.xq, w.sx, w.mx);
         bk->gemm(*lm_head.lins[0], w.xq, w.sx, w.mx, t, GemmOut::write(w.logits));
@@ -231,6 +420,7 @@ void Model::network(size_t pos0, size_t t) {
         bk->rmsnorm_quant(last, final_norm, c.eps, 1, h, w.xq, w.sx, w.mx);
         bk->gemm(*lm_head.lins[0], w.xq, w.sx, w.mx, 1, GemmOut::write(w.logits));
     }
+    observe(Tap::Logits, 0, &w.logits);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -432,7 +622,7 @@ void Model::network_tp(size_t pos0, size_t t) {
     (void)P;
 }
 
-std::string Model::forward(const int32_t* ids, size_t t) {
+std::string Model::forward(const int32_t* ids, size_t t, Observer* obs) {
     if (t == 0 || t > max_batch)
         return "batch of " + std::to_string(t) + " tokens (1 to " + std::to_string(max_batch) + " allowed)";
     if (pos + t > max_ctx)
@@ -440,7 +630,7 @@ std::string Model::forward(const int32_t* ids, size_t t) {
                std::to_string(max_ctx);
     std::string e = embed_rows(ids, t);
     if (!e.empty()) return e;
-    network(pos, t);
+    network(pos, t, obs);
     pos += t;
     return "";
 }
@@ -469,9 +659,9 @@ uint64_t Model::next_draw(Sampling& s) {
     return z ^ (z >> 31);
 }
 
-std::string Model::prefill(const int32_t* ids, size_t n) {
+std::string Model::prefill(const int32_t* ids, size_t n, Observer* obs) {
     for (size_t i = 0; i < n; i += max_batch) {
-        std::string e = forward(ids + i, std::min(max_batch, n - i));
+        std::string e = forward(ids + i, std::min(max_batch, n - i), obs);
         if (!e.empty()) return e;
     }
     return "";
@@ -479,18 +669,25 @@ std::string Model::prefill(const int32_t* ids, size_t n) {
 
 std::string Model::generate(const int32_t* prompt, size_t n_prompt, size_t n_new, Sampling s,
                             const std::vector<int32_t>& stop, std::vector<int32_t>& out,
-                            const std::function<void(int32_t)>& on_token) {
-    std::string e = prefill(prompt, n_prompt);
+                            const std::function<void(int32_t)>& on_token, Observer* obs) {
+    std::string e = prefill(prompt, n_prompt, obs);
     if (!e.empty()) return e;
     out.clear();
     for (size_t i = 0; i < n_new; i++) {
         int32_t id = 0;
         e = pick(s, id);
         if (!e.empty()) return e;
+        if (obs) {   // model.rs:524-538
+            Tap tap;
+            tap.kind = Tap::Token;
+            tap.id = id;
+            tap.rng = s.rng;
+            obs->observe(Ctx{pos - 1, 1, backend}, tap);
+        }
         out.push_back(id);
         if (on_token) on_token(id);
         if (std::find(stop.begin(), stop.end(), id) != stop.end() || i + 1 == n_new) break;
-        e = forward(&id, 1);
+        e = forward(&id, 1, obs);
         if (!e.empty()) return e;
     }
     return "";

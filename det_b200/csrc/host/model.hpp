@@ -5,6 +5,8 @@
 #pragma once
 #include "backend.hpp"
 #include "comm.hpp"
+#include "gguf.hpp"
+#include "hooks.hpp"
 #include "synth.hpp"
 #include <functional>
 #include <memory>
@@ -53,6 +55,7 @@ struct Work {   // model.rs:89-118
     Buf<float> sh;
     Buf<uint16_t> mh;
     Buf<float> logits;
+    Buf<float> gin, gout;   // GDN mixer export (model.rs:343-344); sized on the first observed step that asks for them
 };
 struct Sampling {   // model.rs:120-141
     bool greedy = true;
@@ -71,24 +74,32 @@ class Model {
     static std::unique_ptr<Model> load_synthetic(const Config& cfg, uint64_t seed, Backend* backend, size_t max_ctx,
                                                  size_t max_batch, Comm* comm = nullptr);
 
+    // Model::load (model.rs:164-365): a det GGUF written by `det convert` (or write_synthetic_gguf).  Null and a message in
+    // `err` when the file is unreadable, not a qwen35 det file, holds a non-finite value, or lacks a tensor.
+    static std::unique_ptr<Model> load(const std::string& path, Backend* backend, size_t max_ctx, size_t max_batch,
+                                       std::string& err);
+
     void set_all_logits(bool all);                                   // model.rs:367-375
     void reset();                                                    // model.rs:377-387
     std::string embed_rows(const int32_t* ids, size_t t);            // model.rs:389-413; "" on success
     void project(const Proj& p, const Buf<int8_t>& xq, const Buf<float>& sx, const Buf<uint16_t>& mx, size_t t,
                  const std::vector<const Buf<float>*>& dsts);        // model.rs:415-437
-    std::string forward(const int32_t* ids, size_t t);               // model.rs:439-465
+    std::string forward(const int32_t* ids, size_t t, Observer* obs = nullptr);            // model.rs:439-465
     std::vector<float> logits();                                     // model.rs:467-470
     std::string pick(Sampling& s, int32_t& id);                      // model.rs:472-496
     std::string pick_row(const Buf<float>& logits_row, Sampling& s, int32_t& id);   // the same draw on a given logits row
     static uint64_t next_draw(Sampling& s);   // advances the generator once, returns z (model.rs:484-485)
-    std::string prefill(const int32_t* ids, size_t n);               // model.rs:498-508
+    std::string prefill(const int32_t* ids, size_t n, Observer* obs = nullptr);            // model.rs:498-508
     std::string generate(const int32_t* prompt, size_t n_prompt, size_t n_new, Sampling s,
                          const std::vector<int32_t>& stop, std::vector<int32_t>& out,
-                         const std::function<void(int32_t)>& on_token = nullptr);   // model.rs:510-547
+                         const std::function<void(int32_t)>& on_token = nullptr, Observer* obs = nullptr);   // model.rs:510-547
 
     Config cfg;
     Backend* backend = nullptr;
     uint64_t seed = 0;
+    std::shared_ptr<Gguf> gguf;   // the mapped file of a loaded model (null for a synthetic one); owns the embedding rows
+    GgufTensor embed;             // token_embd.weight of `gguf`
+    bool calibrated = false;      // the file carries value scales other than the default (model.rs:236-244)
     Buf<float> final_norm, rope_cos, rope_sin;
     Proj lm_head;
     std::vector<Layer> layers;
@@ -96,7 +107,7 @@ class Model {
     size_t max_ctx = 0, max_batch = 0, pos = 0;
     bool all_logits = false;
 
-    void network(size_t pos0, size_t t);   // qwen35.rs:8-172
+    void network(size_t pos0, size_t t, Observer* obs = nullptr);   // qwen35.rs:8-172
 
     // ---- tensor parallel state (comm == nullptr: none of it is used)
     Comm* comm = nullptr;

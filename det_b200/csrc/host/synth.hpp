@@ -86,6 +86,9 @@ void quantize_row(const float* w, size_t k, int bits, uint8_t* out_row);      //
 // `n` det rows of a synthetic tensor (rows generated on the fly, threads over rows).
 std::vector<uint8_t> synth_det_rows(uint64_t seed, uint64_t tid, size_t n, size_t k, int bits, size_t row0 = 0);
 
+// The same rows through the provider set with set_synth_rows_provider when there is one (backend.hpp), else the host path.
+std::vector<uint8_t> synth_det_rows_any(uint64_t seed, uint64_t tid, size_t row0, size_t n, size_t k, int bits);
+
 // ---- rope tables [pos][rot/2], computed in binary64 and rounded once (convert.rs:370-385)
 void rope_tables(const Config& c, size_t n_pos, std::vector<float>& cos, std::vector<float>& sin);
 

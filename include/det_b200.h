@@ -222,6 +222,19 @@ void det_synth_linear(unsigned long long seed, unsigned long long tid, long long
 void det_unshard(const float* tmp, float* full, int P, int M, int slice, cudaStream_t st);
 void det_synth_bf16(unsigned long long seed, unsigned long long tid, long long count, uint16_t* out, cudaStream_t st);
 
+/* Conversion and calibration on the device (the reference does both on the host: crates/det/src/convert.rs:346-369,
+ * crates/det/src/quantize.rs:33-100, crates/det/src/calibrate.rs:21-36; crates/det/src/model.rs:389-413 for the table).
+ * det_quantize_rows: `n` rows of K floats of a device tensor of ggml type 0 (F32), 1 (F16) or 30 (BF16) become det file
+ * rows ([codes][c fp32][m u16 x K/128], crates/det/src/spec/tensor.rs:43-55) at rows_out; output row r reads source row
+ * row_perm[r] (NULL: r) and its element k reads column col_perm[k] (NULL: k); `scratch` needs n * (K/128) doubles.  The
+ * rows equal the host quantizer's byte for byte.
+ * det_absmax_heads: slots[h] = max(slots[h], max |v[row][h][0..hd)|) over the t rows (slots start at zero; NaN skipped).
+ * det_embed_table: det_embed for a table of ggml type 0, 1 or 30.                                                      */
+void det_quantize_rows(const void* src, int ggml_type, const int* row_perm, const int* col_perm, int n, int K, int bits,
+                       uint8_t* rows_out, double* scratch, cudaStream_t st);
+void det_absmax_heads(const float* v, int t, int heads, int hd, float* slots, cudaStream_t st);
+void det_embed_table(const void* table, int ggml_type, const int* ids, int M, int H, float* x, cudaStream_t st);
+
 /* Decode-step graph (the reference lists "CUDA graphs for decode" as future work, README.md:115; its C side only has the
  * graph-capturable det_attention_dev).  det_graph_begin starts capturing everything issued on the library queue;
  * det_graph_end returns an executable graph (NULL on failure); det_graph_launch replays it on the queue.  Ops captured
