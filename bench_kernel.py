@@ -4,6 +4,10 @@ kernels that a profiler capture needs (a few hundred MB on the device, a handful
     python bench_kernel.py gemv    [N K bits M]    # k_gemv_stream, default 17408 5120 6 1
     python bench_kernel.py gemm_tc [N K bits M [variant]]   # k_gemm_tc, default 17408 5120 6 512, tile by shape
     python bench_kernel.py umma_peak                        # int8 tcgen05.mma issue rate with resident operands
+    python bench_kernel.py attn [n_h n_kv M pos0 [tc]]      # prefill attention, default 24 4 512 1536, tensor path on
+
+attn: one det_attention call of M tokens behind pos0 cached positions (head_dim 256, random cache contents); tc = 0
+keeps it on the CUDA-core kernels; 2 warm-up calls, then 5 timed ones.
 
 gemv: six copies of the weights (seeded, generated on the device, repacked into the streaming layout) are cycled through
 so that no launch finds its weights in the 126 MB L2; 6 warm-up launches, then 12 timed ones.
@@ -67,6 +71,51 @@ def _activations(d, m, k, n):
     return xq, sx, mx, y
 
 
+def attn(argv):
+    n_h, n_kv, m, pos0 = (24, 4, 512, 1536) if len(argv) < 5 else map(int, argv[1:5])
+    tc = int(argv[5]) if len(argv) >= 6 else 1
+    hd, rot, ctx = 256, 64, pos0 + m
+    d = capi.cuda()
+    assert d.det_init() == 0
+    d.det_debug_set_attn_tc(tc, 0)
+    rng = np.random.default_rng(1)
+
+    def up(a):
+        a = np.ascontiguousarray(a)
+        p = d.det_malloc(a.nbytes)
+        d.det_memcpy(p, a.ctypes.data, a.nbytes, None)
+        return p
+
+    layer = capi.AttnLayer(up(np.ones(hd, np.float32)), up(np.ones(hd, np.float32)), up(np.full(n_kv, 1 / 1024, np.float32)),
+                           up(np.full(n_kv, 1024.0, np.float32)))
+    cache = capi.KvCache(up(rng.integers(-127, 128, (ctx, n_kv, hd), dtype=np.int8)),
+                         up(rng.uniform(0.001, 0.02, (ctx, n_kv)).astype(np.float32)),
+                         up(rng.integers(-32767, 32768, (ctx, n_kv, hd), dtype=np.int16)), ctx, None, None)
+    ang = np.arange(ctx)[:, None] * (1e7 ** (-np.arange(rot // 2) * 2.0 / rot))[None, :]
+    cos, sin = up(np.cos(ang).astype(np.float32)), up(np.sin(ang).astype(np.float32))
+    qg = up(rng.standard_normal((m, n_h, 2 * hd)).astype(np.float32))
+    k = up(rng.standard_normal((m, n_kv, hd)).astype(np.float32))
+    v = up(rng.standard_normal((m, n_kv, hd)).astype(np.float32))
+    o, scratch = d.det_malloc(m * n_h * hd * 4), d.det_malloc(d.det_attn_scratch_bytes(m, n_h, hd))
+    ev = _Events(d.det_cuda_stream())
+
+    def call():
+        d.det_attention(C.byref(layer), C.byref(cache), qg, k, v, cos, sin, rot, 1e-6, m, pos0, n_h, n_kv, hd, o, scratch, None)
+
+    for _ in range(2):
+        call()
+    a = ev.record()
+    for _ in range(5):
+        call()
+    b = ev.record()
+    us = ev.ms(a, b) / 5 * 1e3
+    # causal pairs: token t sees pos0 + t + 1 keys; two contractions of hd MACs per (q head, token, key) pair
+    pairs = n_h * sum(pos0 + t + 1 for t in range(m))
+    print(f"det_attention n_h={n_h} n_kv={n_kv} M={m} pos0={pos0} {'tensor' if tc else 'cuda-core'} path: {us:.1f} us/call, "
+          f"{4 * pairs * hd / us / 1e6:.1f} TOPS of 2 x hd MACs per pair; device error word {d.det_last_error()}")
+    d.det_sync()
+
+
 def main(argv):
     kind = argv[0] if argv else "gemv"
     if kind == "umma_peak":
@@ -76,6 +125,8 @@ def main(argv):
             print(f"tcgen05.mma kind::i8 128x256x32, {iters} x 4 per SM: {d.det_debug_umma_peak(iters):.0f} TOPS; "
                   f"device error word {d.det_last_error()}")
         return
+    if kind == "attn":
+        return attn(argv)
     if kind not in ("gemv", "gemm_tc"):
         raise SystemExit(__doc__)
     n, k, bits, m = (17408, 5120, 6, 1 if kind == "gemv" else 512)

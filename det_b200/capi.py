@@ -133,6 +133,8 @@ CUDA_ABI = {
     "det_quantize_rows": (None, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "det_absmax_heads": (None, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "det_embed_table": (None, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "det_attn_set_workspace": (None, [c_void_p, c_size_t]),
+    "det_debug_set_attn_tc": (None, [c_int, c_int]),
     "det_debug_set_pdl": (None, [c_int]),
     "det_debug_set_tc_variant": (None, [c_int]),
     "det_debug_set_gemv": (None, [c_int]),

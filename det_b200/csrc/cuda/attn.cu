@@ -9,7 +9,7 @@
 //          exact in any order, so key ranges are split over CTAs and merged with 64-bit atomic adds.
 //   fin    o = (((float)num / (float)den) * v_scale) * sigmoid_f(gate)
 // All query heads that share a kv head are handled by the same CTA so K and V tiles are read once per group.
-#include "runtime.cuh"
+#include "attn_tc.cuh"
 
 namespace detb {
 
@@ -44,7 +44,16 @@ struct AttnArgs {
     unsigned* done;          // [M][n_kv] CTAs that have added their partial sums
     int* error_flag;
     int nsplit, keys_per_split;
+    int tc_rpad;             // > 0: the tile layout of the tensor-core path (attn_tc.cuh), rows per kv head
 };
+// scratch cell of query row (token t, head h)
+__device__ __forceinline__ size_t q_cell(const AttnArgs& a, int t, int h) {
+    if (a.tc_rpad) {
+        const int g = h / a.rep;
+        return (size_t)g * a.tc_rpad + (size_t)t * a.rep + (h - g * a.rep);
+    }
+    return (size_t)t * a.n_h + h;
+}
 // cache and position of token row t
 struct RowCache {
     int8_t* kq;
@@ -89,14 +98,15 @@ __global__ void __launch_bounds__(256) k_attn_prep(const AttnArgs a) {
     const bool is_q = row < n_q;
     if (is_q) {
         // this (token, head)'s reduction cells start from zero (0 is below every order-preserving score key)
+        const size_t cell = q_cell(a, (int)(row / a.n_h), (int)(row % a.n_h));
         if (lane == 0) {
-            a.mxkey[row] = 0u;
-            a.den[row] = 0;
+            a.mxkey[cell] = 0u;
+            a.den[cell] = 0;
             a.bar[row] = 0u;     // indexed by (token, kv head) <= (token, q head)
             a.done[row] = 0u;
         }
 #pragma unroll
-        for (int i = 0; i < PER; i++) a.num[row * HD + lane * PER + i] = 0;
+        for (int i = 0; i < PER; i++) a.num[cell * HD + lane * PER + i] = 0;
     }
     int t, h;
     const float *src, *wn;
@@ -146,11 +156,11 @@ __global__ void __launch_bounds__(256) k_attn_prep(const AttnArgs a) {
     amax = max_lanes(amax);
     const float s = (amax == 0.0f) ? 1.0f : fdiv(amax, 127.0f);   // spec/quant.rs:7-16
     const float inv = fdiv(1.0f, s);
-    int8_t* dst = is_q ? a.qq + ((size_t)t * a.n_h + h) * HD : cache.kq + ((size_t)cache.pos * a.n_kv + h) * HD;
+    int8_t* dst = is_q ? a.qq + q_cell(a, t, h) * HD : cache.kq + ((size_t)cache.pos * a.n_kv + h) * HD;
 #pragma unroll
     for (int i = 0; i < PER; i++) dst[lane * PER + i] = (int8_t)quant_code(x[i], inv);
     if (lane == 0) {
-        if (is_q) a.sq[(size_t)t * a.n_h + h] = s;
+        if (is_q) a.sq[q_cell(a, t, h)] = s;
         else cache.sk[(size_t)cache.pos * a.n_kv + h] = s;
     }
 }
@@ -634,7 +644,7 @@ struct ScratchMap {
 };
 static ScratchMap scratch_map(int M, int n_h, int hd) {
     ScratchMap s;
-    const size_t rows = (size_t)M * n_h;
+    const size_t rows = (size_t)(M + 128) * n_h;   // room for the tile layout: every kv head's rows padded to 128
     s.qq = 0;
     s.sq = align256(rows * hd);
     s.mx = s.sq + align256(rows * 4);
@@ -647,7 +657,7 @@ static ScratchMap scratch_map(int M, int n_h, int hd) {
 }
 
 template <int HD>
-static void run_attention(AttnArgs a, void* scratch, int max_total_keys, cudaStream_t q) {
+static void run_attention(AttnArgs a, void* scratch, int max_total_keys, int capacity, cudaStream_t q) {
     const ScratchMap sm = scratch_map(a.M, a.n_h, HD);
     uint8_t* base = static_cast<uint8_t*>(scratch);
     a.qq = reinterpret_cast<int8_t*>(base + sm.qq);
@@ -668,6 +678,18 @@ static void run_attention(AttnArgs a, void* scratch, int max_total_keys, cudaStr
     a.keys_per_split = tiles_per_split * KT;
 
     const long long rows = (long long)a.M * (a.n_h + 2 * a.n_kv);
+    a.tc_rpad = 0;
+    if (attn_tc_applies(a.M, HD, a.rows != nullptr, a.pos0_dev != nullptr, a.n_kv, max_total_keys)) {
+        // prefill on the tensor cores: prep writes the query rows in the tile layout, the rest is attn_tc.cu
+        a.tc_rpad = (a.M * a.rep + 127) / 128 * 128;
+        launch_pdl(k_attn_prep<HD>, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, q, 1, a);
+        AttnTcCall c;
+        c.M = a.M; c.n_h = a.n_h; c.n_kv = a.n_kv; c.pos0 = a.pos0; c.capacity = capacity; c.Rpad = a.tc_rpad;
+        c.qq = a.qq; c.sq = a.sq; c.mxkey = a.mxkey; c.den = a.den; c.num = a.num;
+        c.kq = a.kq; c.sk = a.sk; c.vq = a.vq; c.qg = a.qg; c.v_scale = a.v_scale; c.o = a.o;
+        attn_tc_run(c, q);
+        return;
+    }
     launch_pdl(k_attn_prep<HD>, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, q, 1, a);
     // decode-sized calls: one fused launch, at most one CTA per SM so that all of them are resident at the counter
     const int fit = sm_count() / (a.n_kv * a.M);
@@ -726,8 +748,9 @@ static void attention_entry(const det_attn_layer* L, const det_kv_cache* kv, con
     a.pos0 = pos0; a.pos0_dev = pos0_dev; a.o = o;
     cudaStream_t q = queue_of(st);
     const int keys = rows ? max_pos + 1 : max_pos + M;
-    if (hd == 256) run_attention<256>(a, scratch, keys, q);
-    else run_attention<64>(a, scratch, keys, q);
+    const int capacity = kv ? kv->capacity : 0;
+    if (hd == 256) run_attention<256>(a, scratch, keys, capacity, q);
+    else run_attention<64>(a, scratch, keys, capacity, q);
 }
 
 }  // namespace detb

@@ -21,8 +21,7 @@
 // int8-expanded tile-major copy of the weights (det_linear_expand) and from the int8 activations, both through
 // 128-byte-swizzled TMA boxes, which is
 // the canonical K-major SWIZZLE_128B layout the UMMA shared-memory descriptor names.  No multicast anywhere.
-#include "gemm_common.cuh"
-#include <cuda.h>
+#include "umma.cuh"
 #include <algorithm>
 
 namespace detb {
@@ -50,63 +49,6 @@ struct TcCfg {
     static constexpr unsigned IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TOK >> 3) << 17) | ((TC_ROWS >> 4) << 24);
 };
 
-// Shared-memory matrix descriptor, K-major, SWIZZLE_128B: 8-row groups 1024 bytes apart, descriptor version 1.
-__device__ __forceinline__ unsigned long long umma_desc(const void* smem) {
-    const unsigned addr = smem_addr(smem);
-    unsigned long long d = 0;
-    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);          // start address
-    d |= (unsigned long long)1 << 16;                           // leading byte offset (unused with swizzle)
-    d |= (unsigned long long)(1024 >> 4) << 32;                 // stride byte offset
-    d |= (unsigned long long)1 << 46;                           // version
-    d |= (unsigned long long)2 << 61;                           // SWIZZLE_128B
-    return d;
-}
-__device__ __forceinline__ void umma_i8(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc,
-                                        unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld(unsigned taddr, int (&r)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_ld(unsigned taddr, int (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld(unsigned taddr, int (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
 // acc += (s32) p * (s32) mult: one signed 32 x 32 + 64 multiply-add.
 __device__ __forceinline__ void mad_s32_s32(long long& acc, int p, int mult) {
     asm("mad.wide.s32 %0, %1, %2, %0;" : "+l"(acc) : "r"(p), "r"(mult));
@@ -389,20 +331,6 @@ __global__ void k_expand_int8(const uint8_t* __restrict__ wq, int bits, int N, i
     d4[1] = reinterpret_cast<const uint4*>(out)[1];
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qr;
-        DETB_CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr));
-        DETB_REQUIRE(p != nullptr && qr == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available");
-        fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
 // A [rows][K] int8 matrix as a 2-D tensor map with a (128 bytes x box_rows) box, 128-byte swizzle, zero fill.
 static CUtensorMap make_map(const void* base, int rows, int K, int box_rows) {
     CUtensorMap map;
@@ -452,26 +380,9 @@ static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const flo
     int ksplit = 1;
     if (g_tc_splitk && tiles * 2 <= sm_count() && G >= 16) ksplit = std::min(4, std::min(sm_count() / tiles, G / 8));
     if (ksplit > 1) {
-        // scratch: int64 cells for at most sm_count()/2 tiles of 128 x 128, plus their counters; allocated at first
-        // use (never inside a stream capture: the captured decode step has M = 1 and does not come here)
-        static unsigned long long* cells = nullptr;
-        static unsigned* counters = nullptr;
-        if (!cells) {
-            cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-            DETB_CUDA_OK(cudaStreamIsCapturing(q, &cs));
-            if (cs == cudaStreamCaptureStatusNone) {
-                const size_t ncell = (size_t)(sm_count() / 2 + 1) * 128 * TC_ROWS;
-                DETB_CUDA_OK(cudaMalloc(&cells, ncell * 8));
-                DETB_CUDA_OK(cudaMemset(cells, 0, ncell * 8));
-                DETB_CUDA_OK(cudaMalloc(&counters, (sm_count() / 2 + 1) * sizeof(unsigned)));
-                DETB_CUDA_OK(cudaMemset(counters, 0, (sm_count() / 2 + 1) * sizeof(unsigned)));
-            }
-        }
-        if (cells) {
-            a.part = cells;
-            a.counters = counters;
-            grid.z = ksplit;
-        }
+        a.part = splitk_cells();          // (sm_count()/2 + 1) tiles of 128 x 128 int64, owned by the runtime
+        a.counters = splitk_counters();
+        grid.z = ksplit;
     }
     launch_pdl(k_gemm_tc<TOK, EC>, grid, dim3(Cfg::THREADS), smem, q, 1, map_w, map_x, a);
 }

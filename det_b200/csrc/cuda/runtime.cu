@@ -5,6 +5,7 @@
 // non-blocking stream instead, which keeps the same program-order semantics for every det_* call while allowing the
 // decode step to be captured into a CUDA graph (the legacy stream cannot be captured).
 #include "runtime.cuh"
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -21,6 +22,12 @@ struct Runtime {
     std::unordered_map<void*, size_t> live;
     size_t live_bytes = 0;
     int* error_word = nullptr;
+    // scratch owned by the library, allocated once here so that no call path ever allocates:
+    unsigned long long* splitk_cells = nullptr;   // split-K partial sums of the tensor-core GEMM, zero between calls
+    unsigned* splitk_counters = nullptr;
+    void* attn_ws = nullptr;                      // workspace of the tensor-core prefill attention
+    size_t attn_ws_bytes = 0;
+    bool attn_ws_owned = false;
 };
 Runtime* g_rt = nullptr;
 std::once_flag g_once;
@@ -50,6 +57,23 @@ void bring_up() {
     if (cudaMemset(rt->error_word, 0, 4 * sizeof(int)) != cudaSuccess) { delete rt; return; }
     const long long limit = DEFAULT_WAIT_CYCLES;
     if (cudaMemcpy(rt->error_word + 2, &limit, sizeof limit, cudaMemcpyHostToDevice) != cudaSuccess) { delete rt; return; }
+    const size_t tiles = (size_t)rt->sm_count / 2 + 1, ncell = tiles * 128 * 128;
+    if (cudaMalloc(&rt->splitk_cells, ncell * 8) != cudaSuccess || cudaMemset(rt->splitk_cells, 0, ncell * 8) != cudaSuccess ||
+        cudaMalloc(&rt->splitk_counters, tiles * sizeof(unsigned)) != cudaSuccess ||
+        cudaMemset(rt->splitk_counters, 0, tiles * sizeof(unsigned)) != cudaSuccess) { delete rt; return; }
+    // DET_B200_ATTN_WS_MB sizes the attention workspace (default 256; 0: none, prefill attention then stays on the CUDA cores
+    // until det_attn_set_workspace provides one)
+    size_t ws_mb = 256;
+    if (const char* e = getenv("DET_B200_ATTN_WS_MB")) ws_mb = (size_t)strtoull(e, nullptr, 10);
+    if (ws_mb) {
+        if (cudaMalloc(&rt->attn_ws, ws_mb << 20) == cudaSuccess) {
+            rt->attn_ws_bytes = ws_mb << 20;
+            rt->attn_ws_owned = true;
+        } else {
+            (void)cudaGetLastError();
+            fprintf(stderr, "det_b200: no room for a %zu MB attention workspace; prefill attention stays on the CUDA cores\n", ws_mb);
+        }
+    }
     g_rt = rt;
 }
 }  // namespace
@@ -70,6 +94,12 @@ cudaStream_t queue_of(cudaStream_t st) { return st ? st : rt().queue; }
 int sm_count() { return rt().sm_count; }
 size_t smem_optin() { return rt().smem_optin; }
 int* error_word() { return rt().error_word; }
+unsigned long long* splitk_cells() { return rt().splitk_cells; }
+unsigned* splitk_counters() { return rt().splitk_counters; }
+void* attn_workspace(size_t* bytes) {
+    *bytes = rt().attn_ws_bytes;
+    return rt().attn_ws;
+}
 static bool g_pdl = true;
 bool pdl_enabled() { return g_pdl; }
 
@@ -149,6 +179,17 @@ int det_last_error(void) {
     DETB_CUDA_OK(cudaDeviceSynchronize());
     DETB_CUDA_OK(cudaMemcpy(&code, g_rt->error_word, sizeof(int), cudaMemcpyDeviceToHost));
     return code;
+}
+
+// Replaces the attention workspace with caller memory (device, 1024-byte aligned); p == NULL returns to none.  Waits for
+// pending work first.  The tensor-core prefill attention processes as many query rows per round as the workspace holds.
+void det_attn_set_workspace(void* p, size_t bytes) {
+    Runtime& r = rt();
+    DETB_CUDA_OK(cudaDeviceSynchronize());
+    if (r.attn_ws_owned) cudaFree(r.attn_ws);
+    r.attn_ws_owned = false;
+    r.attn_ws = p;
+    r.attn_ws_bytes = p ? bytes : 0;
 }
 
 // Clears the error word after the caller has dealt with the error (waits for pending work first).

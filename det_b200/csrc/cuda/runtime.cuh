@@ -19,6 +19,13 @@ __device__ __forceinline__ long long wait_limit(const int* error_flag) {
 }
 #endif
 
+// Scratch the library owns from the moment the runtime comes up (no call path allocates): the split-K cells of the
+// tensor-core GEMM ((sm_count()/2 + 1) tiles of 128 x 128 int64, zero between calls) with their counters, and the workspace
+// of the tensor-core prefill attention (may be absent: bytes == 0).
+unsigned long long* splitk_cells();
+unsigned* splitk_counters();
+void* attn_workspace(size_t* bytes);
+
 bool pdl_enabled();
 
 // Launches `kernel` on `q` with the programmatic-dependent-launch attribute (and an optional cluster width) and returns

@@ -222,6 +222,17 @@ void det_synth_linear(unsigned long long seed, unsigned long long tid, long long
 void det_unshard(const float* tmp, float* full, int P, int M, int slice, cudaStream_t st);
 void det_synth_bf16(unsigned long long seed, unsigned long long tid, long long count, uint16_t* out, cudaStream_t st);
 
+/* Prefill attention on the tensor cores (batches of 16 tokens and more, head_dim 256, host-known position; the
+ * reference's counterpart is the mma.sync path of kernels/cuda/attn.cu:405-852).  It stages the byte slices of the
+ * probabilities and a transposed copy of V in a workspace the library allocates when it comes up (256 MB; the environment
+ * variable DET_B200_ATTN_WS_MB changes the size, 0 = none).  det_attn_set_workspace replaces it with caller memory
+ * (1024-byte aligned; NULL = none).  A call needs 512 * n_kv * Kpad bytes for V plus 512 * n_kv * Kpad bytes per tile of
+ * 128 query rows (Kpad = keys rounded up to 128) and runs as many tiles per round as fit; without room for one tile the
+ * call runs on the CUDA-core kernels.  Outputs are bit-identical either way.  det_debug_set_attn_tc: on = 0 switches the
+ * tensor path off, min_m > 0 moves the batch threshold (measurement switch).                                          */
+void det_attn_set_workspace(void* p, size_t bytes);
+void det_debug_set_attn_tc(int on, int min_m);
+
 /* Conversion and calibration on the device (the reference does both on the host: crates/det/src/convert.rs:346-369,
  * crates/det/src/quantize.rs:33-100, crates/det/src/calibrate.rs:21-36; crates/det/src/model.rs:389-413 for the table).
  * det_quantize_rows: `n` rows of K floats of a device tensor of ggml type 0 (F32), 1 (F16) or 30 (BF16) become det file
