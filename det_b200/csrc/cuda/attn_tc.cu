@@ -16,12 +16,14 @@
 //                  [byte plane][g][d][key]: keys become the contraction dimension of a K-major UMMA operand.
 //   k_attn_tc_s<1> scores of a (row tile, key tile) pair as 8 UMMA steps (K = 32 bytes of the 256-byte head) into a
 //                  128 x 128 s32 TMEM tile, two tiles in flight; the epilogue warps fold the masked maxima.
-//   k_attn_tc_s<2> the same scores again, then p, den, and the four byte slices of p written as u8 planes
-//                  [slice][g][row][key] into the workspace (keys contiguous: again a K-major operand).
-//   k_attn_tc_pv   num as byte-sliced integer GEMMs over the keys: (p slice i, u8) x (V low byte, u8) carries weight
-//                  2^(8i), (p slice i) x (V high byte, s8) weight 2^(8i+8); the eight products go into five TMEM
-//                  accumulators by weight (128 rows x 64 value dims each) that run over ALL key tiles of the CTA — each
-//                  s32 sum stays below 2 * 255 * 255 * 16384 < 2^31 — and are widened to int64 once, at the end.
+//   k_attn_tc_s<2> the same scores again, then p and den; p = q + e with e = [p == 2^24] and q = p - e < 2^24, and the
+//                  three byte slices of q plus e go out as four u8 planes [plane][g][row][key] into the workspace (keys
+//                  contiguous: again a K-major operand).
+//   k_attn_tc_pv   num as byte-sliced integer GEMMs over the keys: (q slice i, u8) x (V low byte, u8) carries weight
+//                  2^(8i), (q slice i) x (V high byte, s8) weight 2^(8i+8), e x low / high byte weights 1 and 2^8.  The
+//                  eight products go into four TMEM accumulators by weight (128 rows x 128 value dims each: all 512
+//                  columns) that run over ALL key tiles of the CTA — an s32 sum grows by at most 255*255 + 255*128 + 128
+//                  per key, so 16384 keys stay below 2^31 — and are widened to int64 once, at the end.
 //
 // No value ever depends on the tiling: integer sums and maxima only.  Waits are bounded (runtime.cuh); no multicast.
 #include "attn_tc.cuh"
@@ -33,7 +35,7 @@ namespace detb {
 constexpr int AQ = 128;            // query rows per tile (UMMA M)
 constexpr int AK = 128;            // keys per tile
 constexpr int AT_HD = 256;         // head dimension of the tensor path
-constexpr int PV_DIMS = 64;        // value dimensions per k_attn_tc_pv CTA
+constexpr int PV_DIMS = 128;       // value dimensions per k_attn_tc_pv CTA
 constexpr int PV_MAX_TILES = 128;  // key tiles per k_attn_tc_pv CTA: 16384 keys keep every s32 accumulator below 2^31
 
 struct AttnTc {
@@ -245,6 +247,8 @@ k_attn_tc_s(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ C
                             const int pv = f2i_sat(fmul(exp_f(fsub(s, mx)), 16777216.0f));
                             p[u] = (valid && key0 + i <= pos) ? (unsigned)pv : 0u;
                             tsum += p[u];           // 32 values of at most 2^24
+                            const unsigned e = p[u] >> 24;          // p = q + e, e = [p == 2^24]
+                            p[u] = (p[u] - e) | (e << 24);          // three bytes of q, e in the fourth
                         }
 #pragma unroll
                         for (int sl = 0; sl < 4; sl++) {   // byte sl of four consecutive keys into one word
@@ -362,11 +366,13 @@ k_attn_tc_pv(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ 
                     const bool first = l == 0 && k == 0;
 #pragma unroll
                     for (int sl = 0; sl < 4; sl++) {
-                        // accumulator w (TMEM columns 64 w ..) holds weight 2^(8 w): slice sl x low byte -> w = sl, x high
-                        // byte -> w = sl + 1; in the first step the high-byte product is what initialises w = sl + 1
+                        // accumulator w (TMEM columns 128 w ..) holds weight 2^(8 w): q slice sl x low byte -> w = sl, x high
+                        // byte -> w = sl + 1 (in the first step that product is what initialises w = sl + 1); e x low byte
+                        // -> w = 0, e x high byte -> w = 1
                         const unsigned long long da = umma_desc(st + sl * PV_A_BYTES) + 2 * k;
-                        umma_i8(tmem_base + PV_DIMS * sl, da, dlo + 2 * k, UU, (first && sl == 0) ? 0u : 1u);
-                        umma_i8(tmem_base + PV_DIMS * (sl + 1), da, dhi + 2 * k, US, first ? 0u : 1u);
+                        const int wl_ = sl < 3 ? sl : 0, wh_ = sl < 3 ? sl + 1 : 1;
+                        umma_i8(tmem_base + PV_DIMS * wl_, da, dlo + 2 * k, UU, (first && sl == 0) ? 0u : 1u);
+                        umma_i8(tmem_base + PV_DIMS * wh_, da, dhi + 2 * k, US, (first && sl < 3) ? 0u : 1u);
                     }
                 }
                 umma_commit(&empty[s]);
@@ -387,10 +393,10 @@ k_attn_tc_pv(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ 
             const float denf = (valid && a.nz == 1) ? i64_to_f32(a.den[cell]) : 1.0f;
 #pragma unroll 1
             for (int c = 0; c < PV_DIMS / 16; c++) {
-                int w[5][16];
+                int w[4][16];
                 const unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + c * 16;
 #pragma unroll
-                for (int i = 0; i < 5; i++) tmem_ld(taddr + PV_DIMS * i, w[i]);
+                for (int i = 0; i < 4; i++) tmem_ld(taddr + PV_DIMS * i, w[i]);
                 tmem_wait_ld();
                 if (!valid) continue;
 #pragma unroll
@@ -399,7 +405,6 @@ k_attn_tc_pv(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ 
                     num += (long long)w[1][i] << 8;
                     num += (long long)w[2][i] << 16;
                     num += (long long)w[3][i] << 24;
-                    num += (long long)w[4][i] << 32;
                     const int d = dc * PV_DIMS + c * 16 + i;
                     if (a.nz == 1) {
                         const float gate = a.qg[((size_t)t * a.n_h + h) * 2 * AT_HD + AT_HD + d];
