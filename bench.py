@@ -244,6 +244,51 @@ def cpu_baseline(h, cfg: str, threads: int, tokens: int = 8, warmup: int = 1, co
     return base
 
 
+def _tensor_parallel(args, h, rank: int, world: int, shape: dict, rows: int):
+    """N > 1: tensor parallel over NVLink.  torch.distributed (gloo, CPU) only carries the NCCL id, the IPC handles, the
+    barriers and the max-over-ranks of the timings; the data path uses the library's own exchange on its queue.  `rows` is
+    the largest batch whose exchanges should fit the peer staging.  Returns (dist, comm handle, saved stdout fd)."""
+    import numpy as np
+    if world == 1:
+        return None, None, None
+    # libraries loaded for the exchange (NCCL) may print banners on stdout; the contract is ONE JSON line there
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+    import torch
+    import torch.distributed as dist
+    dist.init_process_group("gloo")
+    nid = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        buf = np.zeros(128, np.uint8)
+        h.dh_nccl_unique_id(buf.ctypes.data)
+        nid = torch.from_numpy(buf)
+    dist.broadcast(nid, 0)
+    nid_np = nid.numpy().copy()
+    if args.exchange == "nccl":
+        comm = h.dh_nccl_comm_new(nid_np.ctypes.data, rank, world)
+        if not comm:
+            raise RuntimeError(h.dh_last_error().decode())
+        return dist, comm, saved_stdout
+    # decode-sized exchanges: one kernel per rank storing packets into every peer's staging (CUDA IPC mapped);
+    # prefill chunks (megabytes) stay on NCCL.  16 staging bytes per gathered value of the largest exchange.
+    mixw = shape["n_h"] * shape["hd"]
+    staging = 16 * max(rows * max(mixw, shape["ffn"], shape["hidden"]), shape["vocab"]) + 4096
+    comm = h.dh_peer_comm_new(nid_np.ctypes.data, rank, world, staging)
+    if not comm:
+        raise RuntimeError(h.dh_last_error().decode())
+    mine = np.zeros(64, np.uint8)
+    h.dh_peer_comm_handle(comm, mine.ctypes.data)
+    every = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
+    dist.all_gather(every, torch.from_numpy(mine))
+    handles = np.concatenate([e.numpy() for e in every]).copy()
+    h.dh_peer_comm_open(comm, handles.ctypes.data)
+    if args.exchange == "peer-unfused":
+        h.dh_peer_comm_set_fuse(comm, 0)
+    dist.barrier()
+    return dist, comm, saved_stdout
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     import numpy as np
     from det_b200 import capi
@@ -261,53 +306,15 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         raise RuntimeError(h.dh_last_error().decode())
     if args.no_fuse:
         h.dh_cuda_debug(bk, 0, 0)
+    elif args.no_swiglu_amax:
+        h.dh_cuda_debug(bk, 0, 3)
     if args.gemv_flags:
         d.det_debug_set_gemv(args.gemv_flags)
     if args.rows_wide_min >= 0:
         d.det_debug_set_rows(args.rows_wide_min)
     if args.tc_splitk:
         d.det_debug_set_tc_variant(0x100)
-    # N > 1: tensor parallel over NVLink.  torch.distributed (gloo, CPU) only carries the NCCL id, the barriers and the
-    # max-over-ranks of the timings; the data path uses the library's own NCCL communicator on its queue.
-    dist, comm = None, None
-    saved_stdout = None
-    if world > 1:
-        # libraries loaded for the exchange (NCCL) may print banners on stdout; the contract is ONE JSON line there
-        sys.stdout.flush()
-        saved_stdout = os.dup(1)
-        os.dup2(2, 1)
-        import torch
-        import torch.distributed as dist_mod
-        dist_mod.init_process_group("gloo")
-        dist = dist_mod
-        nid = torch.zeros(128, dtype=torch.uint8)
-        if rank == 0:
-            buf = np.zeros(128, np.uint8)
-            h.dh_nccl_unique_id(buf.ctypes.data)
-            nid = torch.from_numpy(buf)
-        dist.broadcast(nid, 0)
-        nid_np = nid.numpy().copy()
-        if args.exchange == "nccl":
-            comm = h.dh_nccl_comm_new(nid_np.ctypes.data, rank, world)
-            if not comm:
-                raise RuntimeError(h.dh_last_error().decode())
-        else:
-            # decode-sized exchanges: one kernel per rank storing packets into every peer's staging (CUDA IPC mapped);
-            # prefill chunks (megabytes) stay on NCCL.  16 staging bytes per gathered value of the largest exchange.
-            mixw = shape["n_h"] * shape["hd"]
-            staging = 16 * max(8 * max(mixw, shape["ffn"], shape["hidden"]), shape["vocab"]) + 4096
-            comm = h.dh_peer_comm_new(nid_np.ctypes.data, rank, world, staging)
-            if not comm:
-                raise RuntimeError(h.dh_last_error().decode())
-            mine = np.zeros(64, np.uint8)
-            h.dh_peer_comm_handle(comm, mine.ctypes.data)
-            every = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
-            dist.all_gather(every, torch.from_numpy(mine))
-            handles = np.concatenate([e.numpy() for e in every]).copy()
-            h.dh_peer_comm_open(comm, handles.ctypes.data)
-            if args.exchange == "peer-unfused":
-                h.dh_peer_comm_set_fuse(comm, 0)
-            dist.barrier()
+    dist, comm, saved_stdout = _tensor_parallel(args, h, rank, world, shape, rows=8)
     if world == 1 and args.emulate_tp > 1:
         # timing aid: this process runs the launch sequence of rank 0 of an N-way shard with every exchange looped back
         # to its own memory (no peer latency, meaningless values): what one rank costs without waiting for the others
@@ -527,10 +534,12 @@ def run_reference(args, rank: int, world: int):
     print(json.dumps(line), flush=True)
 
 
-def run_serving(args, local_rank: int):
+def run_serving(args, rank: int, world: int, local_rank: int):
     """The serving configuration: `--seqs` independent sequences (contexts uniform in [ctx-min, ctx-max], seeded) decode
     `--new` tokens each at temp 0.7 / top-p 0.95 / top-k 40 with per-sequence seeds, one batched step per token.  Not the
-    headline line: a second workload, printed in the same format (one step = one token for every sequence)."""
+    headline line: a second workload, printed in the same format (one step = one token for every sequence).  At N > 1 the
+    model is tensor parallel: every GPU serves every sequence with its share of the heads, columns and rows (the weights
+    are read once per step for all rows), so `value` is the whole job's rate and the timing is the maximum over ranks."""
     import numpy as np
     from det_b200 import capi
     rt = C.CDLL("libcudart.so.12")
@@ -547,7 +556,8 @@ def run_serving(args, local_rank: int):
         h.dh_cuda_set_fuse_rows(bk, 0)
     if args.tc_splitk:
         d.det_debug_set_tc_variant(0x100)
-    model = h.dh_model_new_synth(bk, cfg.encode(), args.layers, SEED, 16, max(args.chunk, B))
+    dist, comm, saved_stdout = _tensor_parallel(args, h, rank, world, shape, rows=max(8, B))
+    model = h.dh_model_new_synth_tp(bk, cfg.encode(), args.layers, SEED, 16, max(args.chunk, B), comm)
     if not model:
         raise RuntimeError(h.dh_last_error().decode())
     batch = h.dh_batch_new(model, B, max(ctxs) + new + 1)
@@ -566,6 +576,8 @@ def run_serving(args, local_rank: int):
     W = args.warmup
     _check(h.dh_batch_step(batch, W), h)
     d.det_sync()
+    if dist:
+        dist.barrier()
     rt.cudaProfilerStart()      # a profiler started with "--profile-from-start off" sees the timed steps only
     w0 = time.time()
     marks = [ev.record()]
@@ -579,21 +591,56 @@ def run_serving(args, local_rank: int):
     sampler.stop()
     if d.det_last_error():
         raise RuntimeError("device-side wait reported an error")
-    total_ms = sum(steps_ms)
     K = len(steps_ms)
     head = np.zeros(4, np.int32)
     h.dh_batch_tokens(batch, 0, head.ctypes.data, 4)
+    if dist:
+        # every rank steps through the same exchanges, so step i ends at about the same time everywhere: take the
+        # slowest rank per step; all ranks must have drawn the same tokens
+        import torch
+        t = torch.tensor(steps_ms, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        steps_ms = [float(x) for x in t]
+        heads = [torch.zeros(4, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(heads, torch.from_numpy(head.copy()))
+        if any(not torch.equal(heads[0], x) for x in heads):
+            raise RuntimeError("ranks disagree on the sampled tokens")
+        dist.barrier()
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
+        if rank != 0:
+            h.dh_batch_free(batch)
+            return
+    total_ms = sum(steps_ms)
+    # algorithmic bytes of one step: every linear's packed weights once, each sequence's K and V rows up to its position
+    # (int8 + int16 per element, plus the fp32 key scales) and its Gated DeltaNet state read and written
+    n_attn = shape["layers"] // 4 if not args.layers else args.layers // 4
+    n_layers = args.layers or shape["layers"]
+    kv_row = shape["n_kv"] * (shape["hd"] * 3 + 4)
+    mid = [c + W + (new - 1 - W) // 2 for c in ctxs]
+    state = shape["n_v"] * 128 * 128 * 4 * 2
+    step_bytes = (_weights_gb(cfg) * 1e9 * (n_layers / shape["layers"] if args.layers else 1.0)
+                  + n_attn * kv_row * sum(mid) + (n_layers - n_attn) * state * B)
+    hbm, kind = _peaks()
+    achieved = step_bytes / (total_ms / K * 1e-3) / 1e9 / world
     print(json.dumps({
         "metric": f"{cfg} W6 serving decode tok/s, {B} sequences", "value": B * K / (total_ms * 1e-3), "unit": "tok/s",
-        "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": total_ms / K, "higher_is_better": True,
+        "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": None, "dtype": "int8 x W6 -> int64 (fp32 glue)", "data": "synthetic",
         "config": {"workload": f"{cfg}-shape seeded random-init W6 model, {B} sequences with contexts uniform in "
                                f"[{args.ctx_min}, {args.ctx_max}], {new} tokens each at temp 0.7 / top-k 40 / top-p 0.95, "
                                f"per-sequence seeds; one batched step per token",
                    "contexts": ctxs, **({"layers_built": args.layers, "note": "reduced depth: not a result"} if args.layers else {}),
+                   "parallelism": f"tp{world}: every GPU serves every sequence with 1/{world} of the heads, FFN columns and "
+                                  f"output rows; exchange {args.exchange}" if world > 1 else "1 GPU",
                    "rows_path": "composed per-sequence calls" if args.compose_rows else
                    "det_attention_rows / det_gdn_rows", "l2": "weights streamed per step exceed the 126 MB L2"},
         "per_token_ms": {"p50": float(np.percentile(steps_ms, 50)), "p99": float(np.percentile(steps_ms, 99))},
+        "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": achieved, "peak": hbm, "unit": "GB/s per GPU",
+                     "frac": achieved / hbm, "peak_kind": f"of {kind}", "traffic": None, "bytes": int(step_bytes),
+                     "how": "weights + KV rows + GDN state bytes of one step / mean step time / GPUs"},
         "prefill": {"tokens": int(sum(ctxs)), "value": sum(ctxs) / prefill_s, "unit": "tok/s (host wall clock, sequence by sequence)"},
         "clocks": sampler.summary([window]),
         "tokens_head": [int(x) for x in head],
@@ -625,6 +672,8 @@ def main():
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--no-fuse", action="store_true",
                     help="measurement switch: every decode op as its own launch (no prologue / epilogue / dual fusion)")
+    ap.add_argument("--no-swiglu-amax", action="store_true",
+                    help="measurement switch: quantize the SwiGLU product with its own launch (same tokens)")
     ap.add_argument("--gemv-flags", type=int, default=0,
                     help="measurement switch of the decode GEMV (det_debug_set_gemv): 1 = whole-SM CTAs, n << 8 = n CTAs per SM")
     ap.add_argument("--rows-wide-min", type=int, default=-1,
@@ -654,9 +703,7 @@ def main():
             from det_b200 import capi
             capi.host().dh_use_cuda_synth_rows(1)   # the cpu_baseline leg builds its weights with the device generator
         if args.workload == "serving":
-            if world != 1:
-                raise SystemExit("the serving workload runs on one GPU")
-            run_serving(args, local_rank)
+            run_serving(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
 

@@ -42,7 +42,7 @@ class GdnState(C.Structure):
 class ActSource(C.Structure):
     """det_act_source (include/det_b200.h): fp32 inputs of a GEMM whose activation quantization is fused in."""
     _fields_ = [("kind", c_int), ("a", c_void_p), ("b", c_void_p), ("eps", c_float), ("xq", c_void_p), ("sx", c_void_p),
-                ("mx", c_void_p)]
+                ("mx", c_void_p), ("amax", c_void_p)]
 
 
 class GemvOp(C.Structure):
@@ -52,7 +52,7 @@ class GemvOp(C.Structure):
                 ("y", c_void_p), ("accumulate", c_int), ("nparts", c_int), ("offs", C.POINTER(c_int)),
                 ("dsts", C.POINTER(c_void_p)),
                 ("y2", c_void_p), ("nparts2", c_int), ("offs2", C.POINTER(c_int)), ("dsts2", C.POINTER(c_void_p)),
-                ("h", c_void_p)]
+                ("h", c_void_p), ("h_amax", c_void_p)]
 
 
 DET_LAYOUT_STREAM = 0x100
@@ -127,6 +127,7 @@ CUDA_ABI = {
     "det_xchg_capacity": (c_size_t, [c_void_p]),
     "det_xchg_all_gather": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "det_xchg_destroy": (None, [c_void_p]),
+    "det_xchg_fusable": (c_int, [c_int, c_int]),
     "det_xchg_add_rmsnorm_quant": (None, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int,
                                           c_void_p, c_void_p, c_void_p, c_void_p]),
     "det_xchg_quant": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),

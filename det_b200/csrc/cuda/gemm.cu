@@ -183,6 +183,7 @@ void det_gemv(const det_gemv_op* op, cudaStream_t st) {
         call.out2 = make_out(op->lin2, op->y2, 0, op->nparts2, op->offs2, op->dsts2);
     }
     call.h = op->h;
+    call.h_amax = op->h_amax;
     gemv_stream_launch(call, queue_of(st));
 }
 

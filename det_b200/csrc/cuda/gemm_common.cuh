@@ -107,6 +107,7 @@ struct GemvCall {
     int M = 0;
     OutSpec out{}, out2{};
     float* h = nullptr;                    // SwiGLU product instead of `out` (pairs layout)
+    unsigned* h_amax = nullptr;            // with h: the buffer the epilogue folds the group maxima of h into
 };
 void gemv_stream_launch(const GemvCall& call, cudaStream_t q);
 

@@ -152,6 +152,15 @@ struct GemvArgs {
     // SwiGLU epilogue (seg[0] in the pairs layout): h[t][i] = silu_f(y[2i]) * y[2i+1] instead of y
     float* h;
     int h_width;
+    // Group maxima handed from a SwiGLU epilogue to the prologue of the GEMV that quantizes h: word 0 of the buffer counts
+    // the CTAs that have read the maxima; from word 4 on, eight words per (row t, group g) — at 4 + (t * groups + g) * 8 —
+    // hold max |h| over an eighth of the group's values each, as fp32 bit patterns (non-negative floats order like their
+    // bits, so an integer atomic maximum folds them; the maximum is order-free; eight cells per group keep the number of
+    // atomics that meet on one address small).
+    // The producer folds into them; the consumer reads them instead of scanning the row — which is what lets a row longer
+    // than 8192 values go through the prologue — and its last CTA leaves them zero for the next producer.
+    unsigned* h_amax;         // producer side (NULL: none)
+    unsigned* pamax;          // consumer side (NULL: the prologue scans the row)
 };
 enum : int { PRO_RMS = 1, PRO_PLAIN = 2 };
 
@@ -312,6 +321,85 @@ __device__ __forceinline__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2
     }
 }
 
+// The same staging for a plain row whose group maxima are already known (a.pamax): no scan of the row and no values held
+// in registers, so any row length goes.  Every warp derives the row scale from the maxima on its own (order-free), lane r
+// computes the multiplier and reciprocal of the warp's r-th slice, then the slices are quantized one after the other.
+// Same fp32 operation sequence per value as quant_act_i8g (spec/quant.rs:21-49).  The last CTA of the grid to finish
+// reading leaves the maxima zero.
+template <int UC>
+__device__ __forceinline__ void fused_stage_amax(const GemvArgs& a, uint8_t* xs, int2* xmeta, float* sxs) {
+    const int K = a.K, G = a.G, NCH = a.NCH;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool keep = blockIdx.x == 0 && a.xq_out != nullptr;
+    for (int t = 0; t < a.mt; t++) {
+        const float* pa = a.pa + (size_t)t * K;
+        const uint4* am4 = reinterpret_cast<const uint4*>(a.pamax + 4 + (size_t)(a.t0 + t) * G * 8);
+        auto group_max = [&](int s) {
+            const uint4 lo = am4[2 * s], hi = am4[2 * s + 1];
+            return max(max(max(lo.x, lo.y), max(lo.z, lo.w)), max(max(hi.x, hi.y), max(hi.z, hi.w)));
+        };
+        // the largest group scale: x -> x / 127 is monotone, so it is the scale of the largest maximum (one division)
+        unsigned topbits = 0u;
+        for (int s = lane; s < G; s += 32) topbits = max(topbits, group_max(s));
+#pragma unroll
+        for (int off = 16; off; off >>= 1) topbits = max(topbits, __shfl_xor_sync(FULL, topbits, off));
+        const float top = fdiv(__uint_as_float(topbits), 127.0f);
+        const float sx = (top == 0.0f) ? 1.0f : fdiv(top, 65535.0f);
+        if (tid == 0) {
+            sxs[t] = sx;
+            if (keep) a.sx_out[t] = sx;
+        }
+        for (int r0 = 0; warp + r0 * NCW < G; r0 += 32) {
+            const int s_sel = warp + (r0 + lane) * NCW;
+            const bool have = s_sel < G;
+            const float sg_sel = have ? fdiv(__uint_as_float(group_max(s_sel)), 127.0f) : 0.0f;
+            const unsigned mult_sel = have ? group_mult(sg_sel, sx) : 1u;
+            const float inv_sel = fdiv(1.0f, fmul(sx, (float)mult_sel));
+            for (int rb = 0; rb < 32 && warp + (r0 + rb) * NCW < G; rb += 4) {
+                float4 v[4];           // four slices in flight
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int s = warp + (r0 + rb + u) * NCW;
+                    v[u] = s < G ? *reinterpret_cast<const float4*>(pa + s * 128 + lane * 4) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int s = warp + (r0 + rb + u) * NCW;
+                    const unsigned mult = __shfl_sync(FULL, mult_sel, (rb + u) & 31);
+                    const float inv = __shfl_sync(FULL, inv_sel, (rb + u) & 31);
+                    if (s < G) {
+                        unsigned word = (unsigned)(quant_code(v[u].x, inv) & 0xff);
+                        word |= (unsigned)(quant_code(v[u].y, inv) & 0xff) << 8;
+                        word |= (unsigned)(quant_code(v[u].z, inv) & 0xff) << 16;
+                        word |= (unsigned)(quant_code(v[u].w, inv) & 0xff) << 24;
+                        *reinterpret_cast<unsigned*>(xs + stage_piece<UC>(NCH, t, s * 8 + (lane >> 2)) + (lane & 3) * 4) = word;
+                        int sum = __dp4a((int)word, 0x01010101, 0);
+#pragma unroll
+                        for (int off = 1; off < 16; off <<= 1) sum += __shfl_xor_sync(FULL, sum, off);
+                        if ((lane & 15) == 0) xmeta[stage_unit<UC>(NCH, t, 2 * s + (lane >> 4))] = make_int2(sum, (int)mult);
+                        if (keep) {
+                            *reinterpret_cast<unsigned*>(a.xq_out + (size_t)t * K + s * 128 + lane * 4) = word;
+                            if (lane == 0) a.mx_out[(size_t)t * G + s] = (uint16_t)mult;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    consumer_barrier();     // the staged rows are complete; every read of the maxima by this CTA is done
+    if (tid < 32) {
+        unsigned last = 0;
+        if (lane == 0) {
+            __threadfence();
+            last = atomicAdd(a.pamax, 1u) == gridDim.x - 1 ? 1u : 0u;
+        }
+        if (__shfl_sync(FULL, last, 0)) {
+            for (int i = lane; i < a.mt * G * 8; i += 32) a.pamax[4 + (size_t)a.t0 * G * 8 + i] = 0u;
+            if (lane == 0) a.pamax[0] = 0u;
+        }
+    }
+}
+
 // One record (a K chunk of the quad) for this lane's row: the lane's whole 128-group (two units; one unit = half a group
 // when UC = 8), all MT tokens.  acc gathers dot * (m * mx - 2^31) exactly in 64 bits with ONE signed multiply-add per
 // group and token, accs the plain sum of the dots: the caller adds accs * 2^31 back at the end of the row.
@@ -415,7 +503,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
         for (int i = tid; i < MT * upad; i += NCW * 32) xmeta[i] = make_int2(0, 1);
         consumer_barrier();
     }
-    if (a.pro) {
+    if (a.pro && a.pamax) {
+        fused_stage_amax<UC>(a, xs, xmeta, sxs);
+    } else if (a.pro) {
         fused_stage<UC>(a, xs, xmeta, slice_sum, wmax, sxs);
     } else {
         const int pieces_per_tok = a.K >> 4;
@@ -499,8 +589,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
 #pragma unroll
             for (int t = 0; t < MT; t++) {
                 const float up = __shfl_down_sync(FULL, y[t], LPR);
-                if (j == 0 && (r & 1) == 0 && n < S.N && t < a.mt)
-                    a.h[(size_t)(a.t0 + t) * a.h_width + (n >> 1)] = fmul(silu_f(y[t]), up);
+                if (j == 0 && (r & 1) == 0 && n < S.N && t < a.mt) {
+                    const float hv = fmul(silu_f(y[t]), up);
+                    a.h[(size_t)(a.t0 + t) * a.h_width + (n >> 1)] = hv;
+                    if (a.h_amax)
+                        atomicMax(a.h_amax + 4 + ((size_t)(a.t0 + t) * (a.h_width >> 7) + (n >> 8)) * 8 + ((n >> 2) & 7),
+                                  __float_as_uint(fabsf(hv)));
+                }
             }
         } else if (j == 0 && n < S.N) {
 #pragma unroll
@@ -638,7 +733,10 @@ static void gemv_stream_bits(const GemvCall& call, cudaStream_t q) {
         a.eps = 0.0f;
         a.pslices = 0;
         a.xq_out = nullptr; a.sx_out = nullptr; a.mx_out = nullptr;
+        a.pamax = nullptr;
+        a.h_amax = call.h ? call.h_amax : nullptr;
         if (src) {
+            a.pamax = src->amax;
             a.pro = src->kind;
             a.pa = src->a + (size_t)t0 * g.K;
             a.pb = src->b;
@@ -665,7 +763,10 @@ static void gemv_stream_bits(const GemvCall& call, cudaStream_t q) {
 void gemv_stream_launch(const GemvCall& call, cudaStream_t q) {
     const int bits = call.lin->bits & 0xff;
     if (call.src) {
-        DETB_REQUIRE(call.lin->K <= RREG * NCW * 128, "the activation prologue takes rows of at most 8192 values");
+        DETB_REQUIRE(call.lin->K <= RREG * NCW * 128 || (call.src->kind == PRO_PLAIN && call.src->amax),
+                     "the activation prologue takes rows of at most 8192 values unless their group maxima are given");
+        DETB_REQUIRE(!call.src->amax || (call.src->kind == PRO_PLAIN && !call.lin2),
+                     "group maxima go with the plain quantization of a single linear only");
         DETB_REQUIRE((call.src->kind == PRO_RMS || call.src->kind == PRO_PLAIN) && call.src->a, "bad activation source");
         DETB_REQUIRE(call.src->kind != PRO_RMS || call.src->b, "RMSNorm needs its weight");
         DETB_REQUIRE((call.src->xq != nullptr) == (call.src->sx != nullptr) && (call.src->xq != nullptr) == (call.src->mx != nullptr),

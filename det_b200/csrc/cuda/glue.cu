@@ -352,8 +352,10 @@ static void launch_row(const RowArgs& p, int M, cudaStream_t q, const XchgArgs* 
     }
     int cs = 8;                                   // cluster size: by shape only
     while (cs > 1 && slices / cs < 4) cs >>= 1;
+    if (XCHG)                                     // every CTA of a fused exchange must be resident: at most 64 of them
+        while (cs > 1 && cs * M > 64) cs >>= 1;
     const int spc = (slices + cs - 1) / cs;       // <= 32
-    if (XCHG) DETB_REQUIRE(cs * M <= 64 && spc * 32 >= XCHG_MAX_RANKS, "fused exchange: at most 8 rows");
+    if (XCHG) DETB_REQUIRE(cs * M <= 64 && spc <= 32 && spc * 32 >= XCHG_MAX_RANKS, "fused exchange: rows too many or too long");
     launch_pdl(k_row<MODE, XCHG>, dim3(cs, M, 1), dim3(spc * 32, 1, 1), 0, q, cs, p, spc, P / 128,
                xa ? *xa : XchgArgs{});
 }
@@ -506,9 +508,20 @@ void det_silu_mul_quant(const float* g, const float* u, int M, int n, float* h, 
 }
 // ---- tensor-parallel decode: the exchange that produces a gathered row, and the row operation that consumes it, as
 // one launch; n = size * slice.   x[M][n] += gathered; then det_rmsnorm_quant of x.
+// Whether M gathered rows of n values can go through the fused exchange kernels: all their CTAs (clusters of up to 8 per
+// row, at most 32 slices of 128 values per CTA) have to be resident at once, which 64 CTAs always are.
+static bool fused_shape(int M, int n) {
+    if (M < 1 || M > 64 || n % 128 != 0) return false;
+    const int slices = n >> 7;
+    int cs = 8;
+    while (cs > 1 && slices / cs < 4) cs >>= 1;
+    while (cs > 1 && cs * M > 64) cs >>= 1;
+    return cs * M <= 64 && (slices + cs - 1) / cs <= 32;
+}
+int det_xchg_fusable(int M, int n) { return fused_shape(M, n) ? 1 : 0; }
 static void check_fused(const Xchg* xc, int M, int slice) {
-    DETB_REQUIRE(M >= 1 && M <= 8 && slice % 2 == 0 && (slice * xc->size) % 128 == 0,
-                 "fused exchange: 1..8 rows of whole 128-value groups");
+    DETB_REQUIRE(slice % 2 == 0 && fused_shape(M, slice * xc->size),
+                 "fused exchange: rows of whole 128-value groups, det_xchg_fusable(M, n) must hold");
     DETB_REQUIRE((size_t)M * xc->size * slice * 8 <= xc->slot_bytes, "exchange larger than the staging slot");
 }
 void det_xchg_add_rmsnorm_quant(void* h, const float* local, int slice, float* x, const float* w, float eps, int M,

@@ -56,7 +56,8 @@ void dh_cuda_debug(void* b, unsigned skip_mask, int fuse_decode) {
     if (!cb) return;
     cb->flush();
     cb->skip_mask = skip_mask;
-    cb->fuse_decode = fuse_decode != 0;
+    cb->fuse_decode = (fuse_decode & 1) != 0;
+    cb->swiglu_amax = (fuse_decode & 2) == 0;   // bit 1 set: the SwiGLU product is quantized by its own launch again
 }
 // The primitive test hook of the CUDA backend (cuda.rs:474-490).
 void dh_cuda_test_prim(int op, const float* x, size_t len, size_t m, size_t n, float* out, size_t out_len) {

@@ -79,7 +79,8 @@ class NcclComm : public Comm {
 };
 
 // Decode-sized exchanges as ONE kernel per rank over NVLink peer memory (det_xchg_* of the C ABI): the local slice is
-// stored into every rank's staging area as self-validating packets.  Exchanges of more than `small_rows` rows
+// stored into every rank's staging area as self-validating packets; where det_xchg_fusable(rows, row length) holds the
+// consumer (residual add + RMSNorm + quantization, or quantization) runs in the same launch.  Exchanges of more than `small_rows` rows
 // (prefill chunks: megabytes, bandwidth-bound) go through the NCCL communicator given at construction.
 // Set-up is collective: construct on every rank, pass every rank's handle() to open() in rank order.
 class PeerComm : public Comm {
@@ -99,7 +100,7 @@ class PeerComm : public Comm {
     void silu_gather_quant(Backend& bk, const Buf<float>& g, const Buf<float>& u, const Buf<float>& h_l,
                            const Buf<float>& tmp, const Buf<float>& h_full, size_t t, size_t slice, const Buf<int8_t>& q,
                            const Buf<float>& s, const Buf<uint16_t>& mm) override;
-    size_t small_rows = 8;
+    size_t small_rows = 32;   // the serving step of 32 sequences still goes through the peer kernels
     bool fuse = true;   // run exchange + consumer as one launch (measurement switch; results are the same)
 
   private:

@@ -57,10 +57,12 @@ void CudaBackend::sync() {
 
 // Holds an activation quantization back so that the next gemm() can absorb it.  Returns false when it does not qualify.
 bool CudaBackend::hold(int kind, const float* a, const float* b, float eps, size_t m, size_t n, int8_t* xq, float* sx,
-                       uint16_t* mx) {
+                       uint16_t* mx, unsigned* amax) {
     flush_pending();
-    if (!fuse_decode || !stream_layout || m > (size_t)stream_max_m || n % 128 != 0 || n > 8192 || !mx) return false;
+    // rows of more than 8192 values only qualify when their group maxima come with them
+    if (!fuse_decode || !stream_layout || m > (size_t)stream_max_m || n % 128 != 0 || (n > 8192 && !amax) || !mx) return false;
     pending_.kind = kind;
+    pending_.amax = amax;
     pending_.a = a; pending_.b = b; pending_.eps = eps;
     pending_.m = m; pending_.n = n;
     pending_.xq = xq; pending_.sx = sx; pending_.mx = mx;
@@ -79,11 +81,14 @@ void CudaBackend::flush_pending() {
         det_rmsnorm_quant(p.a, p.b, p.eps, (int)p.m, (int)p.n, nullptr, p.xq, p.sx, p.mx, ST);
     else
         det_quant(p.a, (int)p.m, (int)p.n, p.xq, p.sx, p.mx, ST);
+    // group maxima that no GEMV consumed: clear them for the next producer
+    if (p.amax) det_memset(p.amax, 0, (4 + 8 * p.m * (p.n / 128)) * sizeof(unsigned), ST);
 }
 
 // One decode GEMV launch: linear g.lin (with the quantization it absorbed as its prologue), optionally a second W8
 // linear over the same rows, optionally the SwiGLU product instead of the outputs of g.lin.
-void CudaBackend::issue_gemv(const PendingGemm& g, const CudaLinear* second, const std::vector<float*>* dsts2, float* h) {
+void CudaBackend::issue_gemv(const PendingGemm& g, const CudaLinear* second, const std::vector<float*>* dsts2, float* h,
+                             unsigned* h_amax) {
     auto describe = [](const CudaLinear& l) {
         det_qlinear q;
         q.wq = l.stream.ptr();
@@ -114,6 +119,7 @@ void CudaBackend::issue_gemv(const PendingGemm& g, const CudaLinear* second, con
         src.kind = g.act.kind;
         src.a = g.act.a; src.b = g.act.b; src.eps = g.act.eps;
         src.xq = g.act.xq; src.sx = g.act.sx; src.mx = g.act.mx;
+        src.amax = g.act.amax;
         op.src = &src;
     } else {
         op.xq = g.xq; op.sx = g.sx; op.mx = g.mx;
@@ -136,6 +142,7 @@ void CudaBackend::issue_gemv(const PendingGemm& g, const CudaLinear* second, con
         op.dsts2 = dsts2->data();
     }
     op.h = h;
+    op.h_amax = h_amax;
     det_gemv(&op, ST);
 }
 
@@ -328,10 +335,15 @@ void CudaBackend::silu_mul_quant(const Buf<float>& g, const Buf<float>& u, size_
         pending_gemm_.dsts[1] == u.ptr() && pending_gemm_.m == m && pending_gemm_.lin->n() == 2 * n && n % 128 == 0) {
         const PendingGemm first = pending_gemm_;
         pending_gemm_.on = false;
-        if (swiglu_h_.len() < (size_t)stream_max_m * n) swiglu_h_ = alloc<float>((size_t)stream_max_m * n);
-        issue_gemv(first, nullptr, nullptr, swiglu_h_.ptr());
-        if (hold(DET_ACT_PLAIN, swiglu_h_.ptr(), nullptr, 0.0f, m, n, hq.ptr(), sh.ptr(), mh.ptr())) return;
+        if (swiglu_h_.len() < (size_t)stream_max_m * n) {
+            swiglu_h_ = alloc<float>((size_t)stream_max_m * n);
+            swiglu_amax_ = alloc<uint32_t>(4 + 8 * (size_t)stream_max_m * (n / 128));   // zero-filled
+        }
+        unsigned* amax = swiglu_amax ? swiglu_amax_.ptr() : nullptr;
+        issue_gemv(first, nullptr, nullptr, swiglu_h_.ptr(), amax);
+        if (hold(DET_ACT_PLAIN, swiglu_h_.ptr(), nullptr, 0.0f, m, n, hq.ptr(), sh.ptr(), mh.ptr(), amax)) return;
         det_quant(swiglu_h_.ptr(), (int)m, (int)n, hq.ptr(), sh.ptr(), mh.ptr(), ST);
+        if (amax) det_memset(amax, 0, swiglu_amax_.bytes(), ST);
         return;
     }
     flush_pending();

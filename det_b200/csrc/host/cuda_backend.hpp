@@ -76,6 +76,9 @@ class CudaBackend : public Backend {
     // product from its epilogue and the quantization of that product becomes the next GEMV's prologue.  Results are
     // bit-identical either way (tests/test_gemv_fused_gpu.py); `fuse_decode = false` issues every op on its own.
     bool fuse_decode = true;
+    // The SwiGLU epilogue also folds the group maxima of its product, and the down projection's GEMV quantizes the product
+    // in its prologue from them (no separate quantization launch for the 17408-value row).  Same values either way.
+    bool swiglu_amax = true;
     // Profiling aid: op families in this mask are not launched at all (results are then meaningless); the time a
     // decode step loses without a family is that family's cost.  1 rmsnorm_quant, 2 quant, 4 silu_mul_quant, 8 gemm,
     // 16 attention, 32 gdn.
@@ -96,6 +99,7 @@ class CudaBackend : public Backend {
         int8_t* xq = nullptr;
         float* sx = nullptr;
         uint16_t* mx = nullptr;
+        unsigned* amax = nullptr;   // group maxima of `a` left by the SwiGLU epilogue that produced it (det_gemv_op.h_amax)
     } pending_;
     struct PendingGemm {
         bool on = false;
@@ -109,13 +113,15 @@ class CudaBackend : public Backend {
         bool accumulate = false;
     } pending_gemm_;
     bool hold(int kind, const float* a, const float* b, float eps, size_t m, size_t n, int8_t* xq, float* sx,
-              uint16_t* mx);
+              uint16_t* mx, unsigned* amax = nullptr);
     void flush_pending();
-    void issue_gemv(const PendingGemm& g, const CudaLinear* second, const std::vector<float*>* dsts2, float* h);
+    void issue_gemv(const PendingGemm& g, const CudaLinear* second, const std::vector<float*>* dsts2, float* h,
+                    unsigned* h_amax = nullptr);
     void* scratch(Buf<uint8_t>& slot, size_t bytes);
     void finish_linear(CudaLinear& l);
     Buf<uint8_t> attn_scratch_, gdn_scratch_, sample_scratch_, synth_scratch_;
     Buf<float> swiglu_h_;            // SwiGLU product of a fused gate|up GEMV (the next GEMV quantizes it in its prologue)
+    Buf<uint32_t> swiglu_amax_;      // its group maxima, folded by that GEMV's epilogue and consumed by the next one's prologue
     Buf<int32_t> pick_, picks_;
     Buf<uint64_t> z_, zs_;
 };

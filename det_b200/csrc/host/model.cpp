@@ -297,6 +297,7 @@ void Model::set_all_logits(bool all) {
     backend->sync();
     const size_t n = (all ? max_batch : 1) * cfg.vocab;
     if (w.logits.len() != n) w.logits = backend->alloc<float>(n);
+    if (comm && tp.tmp.len() < n) tp.tmp = backend->alloc<float>(n);   // the logits gather of a tensor-parallel shard
     all_logits = all;
 }
 
@@ -342,12 +343,13 @@ void Model::project(const Proj& p, const Buf<int8_t>& xq, const Buf<float>& sx, 
 }
 
 // qwen35.rs:31-170
-void Model::network(size_t pos0, size_t t, Observer* obs) {
+void Model::network(size_t pos0, size_t t, Observer* obs, const RowsCtx* rows) {
     if (comm) {
         if (obs) throw std::logic_error("observers are not supported on a tensor-parallel shard");
-        network_tp(pos0, t);
+        network_tp(pos0, t, rows);
         return;
     }
+    if (obs && rows) throw std::logic_error("observers are not supported on a batched decode step");
     const Config& c = cfg;
     Backend* bk = backend;
     const size_t h = c.hidden;
@@ -374,7 +376,8 @@ void Model::network(size_t pos0, size_t t, Observer* obs) {
             observe(Tap::AttnV, li, &w.v);
             AttnLayer layer{&a.q_norm, &a.k_norm, &a.v_scale, &a.v_inv_scale, &rope_cos, &rope_sin};
             Shape shape{t, pos0, c.n_heads, c.n_kv, c.head_dim, c.rot_dim, c.eps};
-            bk->attention(layer, a.kv, shape, w.qg, w.k, w.v, w.o);
+            if (rows) bk->attention_rows(layer, *(*rows->sets)[li], *rows->pos, rows->max_pos, shape, w.qg, w.k, w.v, w.o);
+            else bk->attention(layer, a.kv, shape, w.qg, w.k, w.v, w.o);
             observe(Tap::Kv, li, nullptr, &a.kv);
             observe(Tap::AttnOut, li, &w.o);
             observe(Tap::MixerOut, li, &w.o);
@@ -395,7 +398,8 @@ void Model::network(size_t pos0, size_t t, Observer* obs) {
                 ex.gin = &w.gin;
                 ex.gout = &w.gout;
             }
-            bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.on, ex);
+            if (rows) bk->gdn_rows(layer, *(*rows->sets)[li], shape, w.qkv, w.z, w.a, w.b, w.on);
+            else bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.on, ex);
             if (gdn_io) {
                 observe(Tap::GdnIn, li, &w.gin);
                 observe(Tap::GdnOut, li, &w.gout);
@@ -565,7 +569,7 @@ static void load_shard(Model& m, const Config& cfg, uint64_t seed, Backend* bk, 
     tp.tmp = bk->alloc<float>(std::max(mb * std::max(inter, mix), cfg.vocab));
 }
 
-void Model::network_tp(size_t pos0, size_t t) {
+void Model::network_tp(size_t pos0, size_t t, const RowsCtx* rows) {
     const Config& c = cfg;
     Backend* bk = backend;
     const size_t h = c.hidden, P = (size_t)comm->size;
@@ -578,7 +582,8 @@ void Model::network_tp(size_t pos0, size_t t) {
         comm->gather_add_norm_quant(*bk, tp.y_l, tp.tmp, tp.y_full, t, tp.hid, w.x, norm_w, c.eps, w.xq, w.sx, w.mx);
     };
     bool pending = false;   // y_l of the previous layer's down projection has not been added to x yet
-    for (Layer& l : layers) {
+    for (size_t li = 0; li < layers.size(); li++) {
+        Layer& l = layers[li];
         if (pending) add_norm_quant(l.attn_norm);
         else bk->rmsnorm_quant(w.x, l.attn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
         if (l.is_attn) {
@@ -586,7 +591,8 @@ void Model::network_tp(size_t pos0, size_t t) {
             project(a.qkv, w.xq, w.sx, w.mx, t, {&w.qg, &w.k, &w.v});
             AttnLayer layer{&a.q_norm, &a.k_norm, &a.v_scale, &a.v_inv_scale, &rope_cos, &rope_sin};
             Shape shape{t, pos0, tp.heads, tp.kv, c.head_dim, c.rot_dim, c.eps};
-            bk->attention(layer, a.kv, shape, w.qg, w.k, w.v, w.o);
+            if (rows) bk->attention_rows(layer, *(*rows->sets)[li], *rows->pos, rows->max_pos, shape, w.qg, w.k, w.v, w.o);
+            else bk->attention(layer, a.kv, shape, w.qg, w.k, w.v, w.o);
             comm->gather_quant(*bk, w.o, tp.tmp, tp.mix_full, t, tp.heads * c.head_dim, w.oq, w.so, w.mo);
             project_back(*a.o.lins[0], w.oq, w.so, w.mo);
         } else {
@@ -595,7 +601,8 @@ void Model::network_tp(size_t pos0, size_t t) {
             GdnLayer layer{&g.conv, &g.a, &g.dt_bias, &g.norm};
             GdnShape shape{t, tp.k_heads, tp.v_heads, c.gdn_dk, c.gdn_dv, c.eps};
             project(g.ab, w.xq, w.sx, w.mx, t, {&w.a, &w.b});
-            bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.o, GdnExport{});
+            if (rows) bk->gdn_rows(layer, *(*rows->sets)[li], shape, w.qkv, w.z, w.a, w.b, w.o);
+            else bk->gdn(layer, g.state, shape, w.qkv, w.z, w.a, w.b, w.o, GdnExport{});
             comm->gather_quant(*bk, w.o, tp.tmp, tp.mix_full, t, tp.v_heads * c.gdn_dv, w.oq, w.so, w.mo);
             project_back(*g.out.lins[0], w.oq, w.so, w.mo);
         }
@@ -605,7 +612,7 @@ void Model::network_tp(size_t pos0, size_t t) {
         project_back(*l.down.lins[0], w.hq, w.sh, w.mh);
         pending = true;
     }
-    const size_t rows = all_logits ? t : 1;
+    const size_t out_rows = all_logits ? t : 1;
     if (all_logits || t == 1) {
         if (pending) add_norm_quant(final_norm);
         else bk->rmsnorm_quant(w.x, final_norm, c.eps, t, h, w.xq, w.sx, w.mx);
@@ -617,8 +624,8 @@ void Model::network_tp(size_t pos0, size_t t) {
         Buf<float> last = Buf<float>::view(w.x.ptr_at((t - 1) * h), h);
         bk->rmsnorm_quant(last, final_norm, c.eps, 1, h, w.xq, w.sx, w.mx);
     }
-    bk->gemm(*lm_head.lins[0], w.xq, w.sx, w.mx, rows, GemmOut::write(tp.logits_l));
-    comm->all_gather(*bk, tp.logits_l, tp.tmp, w.logits, rows, tp.voc);
+    bk->gemm(*lm_head.lins[0], w.xq, w.sx, w.mx, out_rows, GemmOut::write(tp.logits_l));
+    comm->all_gather(*bk, tp.logits_l, tp.tmp, w.logits, out_rows, tp.voc);
     (void)P;
 }
 

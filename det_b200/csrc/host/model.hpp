@@ -65,6 +65,14 @@ struct Sampling {   // model.rs:120-141
     uint64_t rng = 0;
 };
 
+// The per-sequence caches / states behind the rows of a batched decode step (serve.hpp): with it the network takes row b
+// of the step's activations as the current token of sequence b, at the position pos[b] of that sequence.
+struct RowsCtx {
+    const std::vector<std::unique_ptr<RowSet>>* sets;   // one per layer
+    const Buf<int32_t>* pos;                            // [rows], backend memory
+    size_t max_pos;                                     // host bound on the positions
+};
+
 class Model {
   public:
     // A seeded random-init model of shape `cfg` (the stand-in for Model::load on a converted checkpoint).
@@ -107,7 +115,7 @@ class Model {
     size_t max_ctx = 0, max_batch = 0, pos = 0;
     bool all_logits = false;
 
-    void network(size_t pos0, size_t t, Observer* obs = nullptr);   // qwen35.rs:8-172
+    void network(size_t pos0, size_t t, Observer* obs = nullptr, const RowsCtx* rows = nullptr);   // qwen35.rs:8-172
 
     // ---- tensor parallel state (comm == nullptr: none of it is used)
     Comm* comm = nullptr;
@@ -123,7 +131,7 @@ class Model {
     } tp;
 
   private:
-    void network_tp(size_t pos0, size_t t);
+    void network_tp(size_t pos0, size_t t, const RowsCtx* rows);
 };
 
 }  // namespace det

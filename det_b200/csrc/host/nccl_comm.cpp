@@ -109,14 +109,14 @@ void PeerComm::all_gather(Backend& bk, const Buf<float>& local, const Buf<float>
 void PeerComm::gather_add_norm_quant(Backend& bk, const Buf<float>& y_l, const Buf<float>& tmp, const Buf<float>& y_full,
                                      size_t t, size_t slice, const Buf<float>& x, const Buf<float>& w, float eps,
                                      const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
-    if (!(fuse && t <= 8 && (slice * size) % 128 == 0 && small(t, slice)))
+    if (!(fuse && det_xchg_fusable((int)t, (int)(slice * size)) && small(t, slice)))
         return Comm::gather_add_norm_quant(bk, y_l, tmp, y_full, t, slice, x, w, eps, q, s, mm);
     bk.flush();
     det_xchg_add_rmsnorm_quant(x_, y_l.ptr(), (int)slice, x.ptr(), w.ptr(), eps, (int)t, q.ptr(), s.ptr(), mm.ptr(), nullptr);
 }
 void PeerComm::gather_quant(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full, size_t t,
                             size_t slice, const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
-    if (!(fuse && t <= 8 && (slice * size) % 128 == 0 && small(t, slice)))
+    if (!(fuse && det_xchg_fusable((int)t, (int)(slice * size)) && small(t, slice)))
         return Comm::gather_quant(bk, local, tmp, full, t, slice, q, s, mm);
     bk.flush();
     det_xchg_quant(x_, local.ptr(), nullptr, (int)slice, (int)t, q.ptr(), s.ptr(), mm.ptr(), nullptr);
@@ -124,7 +124,7 @@ void PeerComm::gather_quant(Backend& bk, const Buf<float>& local, const Buf<floa
 void PeerComm::silu_gather_quant(Backend& bk, const Buf<float>& g, const Buf<float>& u, const Buf<float>& h_l,
                                  const Buf<float>& tmp, const Buf<float>& h_full, size_t t, size_t slice,
                                  const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
-    if (!(fuse && t <= 8 && (slice * size) % 128 == 0 && small(t, slice)))
+    if (!(fuse && det_xchg_fusable((int)t, (int)(slice * size)) && small(t, slice)))
         return Comm::silu_gather_quant(bk, g, u, h_l, tmp, h_full, t, slice, q, s, mm);
     bk.flush();
     det_xchg_quant(x_, g.ptr(), u.ptr(), (int)slice, (int)t, q.ptr(), s.ptr(), mm.ptr(), nullptr);

@@ -6,23 +6,26 @@
 namespace det {
 
 BatchDecoder::BatchDecoder(Model& model, size_t n_seq, size_t ctx) : seqs(n_seq), m_(model), ctx_(ctx) {
-    if (model.comm) throw std::runtime_error("batched decode runs on an unsharded model");
     if (n_seq == 0 || n_seq > model.max_batch) throw std::runtime_error("the model's max_batch is smaller than the number of sequences");
     Backend* bk = model.backend;
     const Config& c = model.cfg;
+    // a tensor-parallel shard keeps this rank's kv heads and GDN heads of every sequence (model.hpp, Model::Tp)
+    const size_t n_kv = model.comm ? model.tp.kv : c.n_kv;
+    const size_t k_heads = model.comm ? model.tp.k_heads : c.gdn_k_heads, v_heads = model.comm ? model.tp.v_heads : c.gdn_v_heads;
+    const size_t conv_dim = 2 * k_heads * c.gdn_dk + v_heads * c.gdn_dv;
     for (Sequence& s : seqs) {
         for (const Layer& l : model.layers) {
             if (l.is_attn) {
                 KvCache kv;   // model.rs:278-283
-                kv.kq = bk->alloc<int8_t>(ctx * c.n_kv * c.head_dim);
-                kv.sk = bk->alloc<float>(ctx * c.n_kv);
-                kv.vq = bk->alloc<int16_t>(ctx * c.n_kv * c.head_dim);
+                kv.kq = bk->alloc<int8_t>(ctx * n_kv * c.head_dim);
+                kv.sk = bk->alloc<float>(ctx * n_kv);
+                kv.vq = bk->alloc<int16_t>(ctx * n_kv * c.head_dim);
                 kv.capacity = ctx;
                 s.kv.push_back(std::move(kv));
             } else {
                 GdnState st;   // model.rs:300-303
-                st.conv_state = bk->alloc<float>((c.conv_k - 1) * c.conv_dim());
-                st.s = bk->alloc<float>(c.gdn_v_heads * c.gdn_dk * c.gdn_dv);
+                st.conv_state = bk->alloc<float>((c.conv_k - 1) * conv_dim);
+                st.s = bk->alloc<float>(v_heads * c.gdn_dk * c.gdn_dv);
                 s.st.push_back(std::move(st));
             }
         }
@@ -84,44 +87,13 @@ std::string BatchDecoder::prefill(size_t i, const int32_t* ids, size_t n, const 
     return "";
 }
 
-// qwen35.rs:31-170 with the two sequence-dependent ops taken per row
+// qwen35.rs:31-170 with the two sequence-dependent ops taken per row (Model::network with a RowsCtx; on a tensor-parallel
+// shard the same exchanges as a batch of t tokens)
 void BatchDecoder::network_rows(size_t t) {
-    Model& m = m_;
-    const Config& c = m.cfg;
-    Backend* bk = m.backend;
-    Work& w = m.w;
-    const size_t h = c.hidden;
     size_t max_pos = 0;
     for (const Sequence& s : seqs) max_pos = std::max(max_pos, s.pos);
-    size_t li = 0;
-    for (Layer& l : m.layers) {
-        const RowSet& rows = *rowsets_[li++];
-        bk->rmsnorm_quant(w.x, l.attn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
-        if (l.is_attn) {
-            Attn& a = l.attn;
-            m.project(a.qkv, w.xq, w.sx, w.mx, t, {&w.qg, &w.k, &w.v});
-            AttnLayer layer{&a.q_norm, &a.k_norm, &a.v_scale, &a.v_inv_scale, &m.rope_cos, &m.rope_sin};
-            Shape shape{t, 0, c.n_heads, c.n_kv, c.head_dim, c.rot_dim, c.eps};
-            bk->attention_rows(layer, rows, pos_, max_pos, shape, w.qg, w.k, w.v, w.o);
-            bk->quant(w.o, t, c.n_heads * c.head_dim, w.oq, w.so, w.mo);
-            bk->gemm(*a.o.lins[0], w.oq, w.so, w.mo, t, GemmOut::accumulate(w.x));
-        } else {
-            Gdn& g = l.gdn;
-            m.project(g.qkvz, w.xq, w.sx, w.mx, t, {&w.qkv, &w.z});
-            GdnLayer layer{&g.conv, &g.a, &g.dt_bias, &g.norm};
-            GdnShape shape{t, c.gdn_k_heads, c.gdn_v_heads, c.gdn_dk, c.gdn_dv, c.eps};
-            m.project(g.ab, w.xq, w.sx, w.mx, t, {&w.a, &w.b});
-            bk->gdn_rows(layer, rows, shape, w.qkv, w.z, w.a, w.b, w.on);
-            bk->quant(w.on, t, c.gdn_v_heads * c.gdn_dv, w.onq, w.son, w.mon);
-            bk->gemm(*g.out.lins[0], w.onq, w.son, w.mon, t, GemmOut::accumulate(w.x));
-        }
-        bk->rmsnorm_quant(w.x, l.ffn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
-        m.project(l.gu, w.xq, w.sx, w.mx, t, {&w.g, &w.u});
-        bk->silu_mul_quant(w.g, w.u, t, c.intermediate, w.hq, w.sh, w.mh);
-        bk->gemm(*l.down.lins[0], w.hq, w.sh, w.mh, t, GemmOut::accumulate(w.x));
-    }
-    bk->rmsnorm_quant(w.x, m.final_norm, c.eps, t, h, w.xq, w.sx, w.mx);
-    bk->gemm(*m.lm_head.lins[0], w.xq, w.sx, w.mx, t, GemmOut::write(w.logits));
+    const RowsCtx rows{&rowsets_, &pos_, max_pos};
+    m_.network(0, t, nullptr, &rows);
 }
 
 std::string BatchDecoder::step() {

@@ -190,6 +190,7 @@ typedef struct {
     int8_t* xq;       /* optional outputs: all three or none */
     float* sx;
     uint16_t* mx;
+    unsigned* amax;   /* DET_ACT_PLAIN only, may be NULL: the group maxima of a, see det_gemv_op.h_amax */
 } det_act_source;
 typedef struct {
     const det_qlinear* lin;
@@ -209,6 +210,13 @@ typedef struct {
     const int* offs2;
     float* const* dsts2;
     float* h;
+    /* With h, may be NULL: a buffer of 4 + 8 * M * (N/2)/128 words (16-byte aligned), zero before its first use.  The epilogue
+     * folds max |h| of every 128-group into eight cells per group from word 4 on (fp32 bit patterns, integer atomic
+     * maximum: order-free).  The det_gemv call that
+     * quantizes h (src.kind = DET_ACT_PLAIN, src.a = h, src.amax = this buffer) reads them instead of scanning the rows,
+     * which lifts the 8192-value limit of the prologue, and leaves the buffer zero again (word 0 counts its readers).
+     * A buffer that was folded into must be consumed by exactly one such call (or cleared) before the next producer.  */
+    unsigned* h_amax;
 } det_gemv_op;
 void det_gemv(const det_gemv_op* op, cudaStream_t st);
 
@@ -284,10 +292,13 @@ void det_xchg_open_loopback(void* h);   /* timing aid: all rank slots map to thi
 size_t det_xchg_capacity(void* h);
 void det_xchg_all_gather(void* h, const float* local, float* full, int M, int slice, cudaStream_t st);
 void det_xchg_destroy(void* h);
-/* The exchange fused with the row operation that consumes the gathered rows (decode: M <= 8), n = size * slice:
+/* The exchange fused with the row operation that consumes the gathered rows, n = size * slice.  All CTAs of such a launch
+ * wait for packets of the other ranks, so they have to be resident together: det_xchg_fusable(M, n) says whether M rows of
+ * n values qualify (single-token decode always does; a serving step of 32 rows does for rows up to 8192 values):
  *   det_xchg_add_rmsnorm_quant   gather local[M][slice]; x[M][n] += gathered; det_rmsnorm_quant(x, w) -> xq, sx, mx
  *   det_xchg_quant               gather local (or silu(local) * local_b when local_b != NULL); det_quant -> xq, sx, mx
  * Results equal det_xchg_all_gather followed by det_add / det_rmsnorm_quant / det_silu_mul_quant / det_quant.       */
+int det_xchg_fusable(int M, int n);
 void det_xchg_add_rmsnorm_quant(void* h, const float* local, int slice, float* x, const float* w, float eps, int M,
                                 int8_t* xq, float* sx, uint16_t* mx, cudaStream_t st);
 void det_xchg_quant(void* h, const float* local, const float* local_b, int slice, int M, int8_t* xq, float* sx,

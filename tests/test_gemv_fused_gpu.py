@@ -147,7 +147,7 @@ def test_second_linear_rides_in_the_same_launch(n1, n2, k, m, libs):
         d.det_free(p)
 
 
-@pytest.mark.parametrize("half,k,m", [(1536, 1024, 1), (17408, 5120, 1), (640, 2560, 4)])
+@pytest.mark.parametrize("half,k,m", [(1536, 1024, 1), (17408, 5120, 1), (640, 2560, 4), (17408, 5120, 3), (9216, 2560, 8)])
 def test_pairs_layout_plain_outputs_and_swiglu_epilogue(half, k, m, libs):
     """gate|up stored with interleaved rows: plain two-part outputs come back in the linear's own order, and the SwiGLU
     product from the epilogue followed by the plain-quantization prologue of a second GEMV equals det_silu_mul_quant +
@@ -193,6 +193,25 @@ def test_pairs_layout_plain_outputs_and_swiglu_epilogue(half, k, m, libs):
     d.det_gemv(C.byref(op2), None)
     assert np.array_equal(_host(d, yd, np.zeros(m * n_down, np.float32)).view(np.uint32), want_y)
     assert np.array_equal(_host(d, hq, want_hq), want_hq)
+    # the same pair with the group maxima handed from the epilogue to the prologue (any row length), twice in a row: the
+    # consumer has to leave the maxima zero for the next producer
+    groups = half // 128
+    amax = d.det_malloc((4 + 8 * m * groups) * 4)
+    for _ in range(2):
+        d.det_memset(hq, 0, m * half, None)
+        d.det_memset(yd, 0xFF, m * n_down * 4, None)
+        op = libs.GemvOp(lin=C.pointer(lin), xq=xq, sx=sx, mx=mx, M=m, h=h, h_amax=amax)
+        d.det_gemv(C.byref(op), None)
+        got_amax = _host(d, amax, np.zeros(4 + 8 * m * groups, np.uint32))
+        hv = _host(d, h, np.zeros((m, groups, 128), np.float32))
+        folded = got_amax[4:].reshape(m, groups, 8).max(axis=2)     # eight cells per group
+        assert got_amax[0] == 0 and np.array_equal(folded.reshape(-1), np.abs(hv).max(axis=2).reshape(-1).view(np.uint32))
+        s = libs.ActSource(libs.DET_ACT_PLAIN, h, None, 0.0, hq, sh, mh, amax)
+        op2 = libs.GemvOp(lin=C.pointer(lin_d), src=C.pointer(s), M=m, y=yd)
+        d.det_gemv(C.byref(op2), None)
+        assert np.array_equal(_host(d, yd, np.zeros(m * n_down, np.float32)).view(np.uint32), want_y)
+        assert np.array_equal(_host(d, hq, want_hq), want_hq)
+        assert not _host(d, amax, np.zeros(4 + 8 * m * groups, np.uint32)).any()
     assert d.det_last_error() == 0
-    for p in b1 + b2 + [xq, sx, mx, pg, pu, hq, sh, mh, yd, h]:
+    for p in b1 + b2 + [xq, sx, mx, pg, pu, hq, sh, mh, yd, h, amax]:
         d.det_free(p)

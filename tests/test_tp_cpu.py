@@ -74,3 +74,69 @@ def test_sharded_model_equals_single_rank(world, libs, oracle, tmp_path):
     r = np.load(tmp_path / "result.npz")
     assert int(r["logit_diff"]) == 0, f"{int(r['logit_diff'])} logits differ between world_size {world} and 1"
     assert bool(r["tok_ok"])
+
+
+def _run_rank_serving(rank, world, port, out_dir):
+    """Three sequences of different prompt lengths advance together on a sharded model (each rank holds its heads'
+    caches and states of every sequence); rank 0 also produces every stream alone on the unsharded model."""
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, str(ROOT))
+    from det_b200 import capi
+    os.environ["OMP_NUM_THREADS"] = "2"
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    h = capi.host()
+    o = C.CDLL(str(ROOT / "oracle" / "_build" / "liboracle.so"))
+    o.orc_ref_backend_new.restype = C.c_void_p
+    backend = o.orc_ref_backend_new()
+
+    @C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_size_t)
+    def gather(local, gathered, nbytes):
+        src = torch.from_numpy(np.ctypeslib.as_array(C.cast(local, C.POINTER(C.c_uint8)), shape=(nbytes,)).copy())
+        parts = [torch.empty(nbytes, dtype=torch.uint8) for _ in range(world)]
+        dist.all_gather(parts, src)
+        dst = np.ctypeslib.as_array(C.cast(gathered, C.POINTER(C.c_uint8)), shape=(world * nbytes,))
+        dst[:] = torch.cat(parts).numpy()
+
+    comm = h.dh_callback_comm_new(rank, world, C.cast(gather, C.c_void_p))
+    prompts, n_new = [5, 11, 3], 5
+    sampling = (0, 1.0 / 0.7, 40, 0.95)
+
+    def prompt(i, n):
+        ids = np.zeros(n, np.int32)
+        h.dh_synth_prompt(100 + i, n, 32768, ids.ctypes.data)
+        return ids
+
+    shard = h.dh_model_new_synth_tp(backend, b"tiny", 4, SEED, 48, 8, comm)
+    assert shard, h.dh_last_error()
+    batch = h.dh_batch_new(shard, len(prompts), 48)
+    assert batch, h.dh_last_error()
+    for i, n in enumerate(prompts):
+        assert h.dh_batch_prefill(batch, i, prompt(i, n).ctypes.data, n, *sampling, 7000 + i) == 0, h.dh_last_error()
+    assert h.dh_batch_step(batch, n_new - 1) == 0, h.dh_last_error()
+    together = []
+    for i in range(len(prompts)):
+        out = np.zeros(n_new, np.int32)
+        assert h.dh_batch_tokens(batch, i, out.ctypes.data, n_new) == n_new
+        together.append(out)
+    if rank == 0:
+        full = h.dh_model_new_synth(backend, b"tiny", 4, SEED, 48, 8)
+        ok = True
+        for i, n in enumerate(prompts):
+            out = np.zeros(n_new, np.int32)
+            cnt = C.c_size_t(0)
+            assert h.dh_model_reset(full) == 0
+            assert h.dh_model_generate(full, prompt(i, n).ctypes.data, n, n_new, *sampling, 7000 + i, out.ctypes.data,
+                                       C.byref(cnt)) == 0, h.dh_last_error()
+            ok = ok and cnt.value == n_new and np.array_equal(out, together[i])
+        np.savez(Path(out_dir) / "serving.npz", ok=ok, streams=np.stack(together))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_serving_streams_equal_solo_streams(libs, oracle, tmp_path):
+    import torch.multiprocessing as mp
+    port = _free_port()
+    mp.spawn(_run_rank_serving, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r = np.load(tmp_path / "serving.npz")
+    assert bool(r["ok"]), r["streams"]
