@@ -269,7 +269,8 @@ void det_token_feedback(const int* pick, int* pos, int* log, int log_base, int l
 
 /* Batched serving decode (no reference counterpart: its Model holds one sequence).  M sequences advance one token each;
  * row t of the activations belongs to the sequence whose cache / state is rows[t] — a DEVICE array of M structs — and,
- * for attention, whose position is pos[t] (device array; max_pos is a host bound on them).  Row t equals
+ * for attention, whose position is pos[t] (device array; max_pos is a host bound on them; the caller guarantees
+ * pos[t] < rows[t].capacity, which lives in device memory and is not checked here).  Row t equals
  * det_attention(M = 1, pos0 = pos[t]) / det_gdn(M = 1) on that sequence.  Scratch as for the single-sequence calls.  */
 void det_attention_rows(const det_attn_layer* L, const det_kv_cache* rows, const int* pos, int max_pos, const float* qg,
                         const float* k, const float* v, const float* rope_cos, const float* rope_sin, int rot, float eps,
