@@ -469,17 +469,18 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                    "rot_dim": 64, "rope_theta": 1e7, "eps": 1e-6, "v_scale": 2 ** -10},
         "e2e": {"value": K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": shape["hidden"] * 4,
                 "d2h_bytes_per_step": 4},
-        # tensor parallel: the exchanges ride in the row kernels (same count per layer) plus the logits gather; with
-        # stand-alone exchanges every layer adds 4 exchange kernels, 2 residual adds and 1 quant
-        "gpu_launches": K * (launches_per_token(cfg, fused=(world == 1 and not args.no_fuse)) +
-                             (0 if world == 1 else 1 if args.exchange == "peer" else SHAPES[cfg]["layers"] * 7 + 1)),
+        # tensor parallel (fused peer exchange): every layer is 10 launches — four exchange + row kernels, five GEMVs, the
+        # mixer step (prep + decode attention on an attention layer, which then has one GEMV less) — plus embed, the final
+        # exchange + norm, the head GEMV, the logits gather, argmax and token feedback; with stand-alone exchanges every
+        # layer adds 4 exchange kernels, 2 residual adds and 1 quant
+        "gpu_launches": K * (launches_per_token(cfg, fused=not args.no_fuse) if world == 1 else
+                             SHAPES[cfg]["layers"] * (10 if args.exchange == "peer" else 17) + 6),
         "prefill": {"value": P / (prefill_ms * 1e-3), "unit": "tok/s", "tokens": P, "chunk": chunk},
         "roofline": None if achieved is None else
                     {"bound": "hbm", "kernel": "k_gemv_stream", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                     # DRAM bytes per launch: ncu on the K=5120 x N=17408 W6 launch read+wrote 1.0073x its algorithmic
-                     # bytes (profiles/k_gemv_stream_w6_k5120_n17408.md); scaled to the average launch of the sweep
-                     "traffic": nbytes.value / nlaunch.value * 1.0073,
+                     # DRAM traffic needs a profiler capture, which never runs inside a timed benchmark
+                     "traffic": None,
                      "launches": nlaunch.value, "bytes": nbytes.value, "ms": sweep_ms,
                      "how": "every linear of the model at M=1, 3 passes back to back, CUDA events on the launch queue"},
         "clocks": sampler.summary(windows),
