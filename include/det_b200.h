@@ -284,7 +284,11 @@ void det_gdn_rows(const det_gdn_layer* L, const det_gdn_state* rows, const float
  * det_xchg_all_gather sends local[M][slice] to every rank as self-validating 16-byte packets (plain peer stores) and
  * fills full[M][size*slice] — ordinary local memory, column block r = rank r's slice — as the packets of all ranks
  * arrive (bounded polling; a timeout sets the error word read by det_last_error).  One launch per rank, no host
- * involvement, capturable into the decode graph.  Every rank must issue the same sequence of exchanges.
+ * involvement, capturable into the decode graph.  Every rank must issue the same sequence of exchanges, and the ranks
+ * must pass a host barrier after det_xchg_open and before their first exchange: a receiver only waits for the wait limit
+ * (about two seconds; det_debug_set_wait_limit), so a peer that is still loading its module or capturing its graph would
+ * make the first exchange time out — the error word is then set, later reads return zeros at once, and det_clear_error
+ * is the only way back.
  * `bytes` of staging take exchanges of up to det_xchg_capacity() gathered values (bytes / 16).                       */
 void* det_xchg_create(size_t bytes, int rank, int size);
 void det_xchg_ipc_handle(void* h, uint8_t out[64]);
