@@ -185,6 +185,7 @@ int det_last_error(void) {
 // pending work first.  The tensor-core prefill attention processes as many query rows per round as the workspace holds.
 void det_attn_set_workspace(void* p, size_t bytes) {
     Runtime& r = rt();
+    DETB_REQUIRE((reinterpret_cast<uintptr_t>(p) & 1023) == 0, "the attention workspace must be 1024-byte aligned");
     DETB_CUDA_OK(cudaDeviceSynchronize());
     if (r.attn_ws_owned) cudaFree(r.attn_ws);
     r.attn_ws_owned = false;

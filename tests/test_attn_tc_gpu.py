@@ -122,7 +122,8 @@ def test_context_past_16384_keys_uses_the_key_split(libs):
 
 
 def test_probabilities_of_exactly_two_to_the_24(libs):
-    """All scores equal: every unmasked p is 2^24, so the fourth byte slice carries the whole sum."""
+    """All scores equal: every unmasked p is 2^24 = (2^24 - 1) + 1, so all three byte slices are 255 everywhere and the
+    separate plane of ones carries the rest."""
     assert libs.cuda().det_init() == 0
     a = run_case(libs, np.random.default_rng(3), 24, 4, [128], 300, tc=True, equal_scores=True)
     b = run_case(libs, np.random.default_rng(3), 24, 4, [128], 300, tc=False, equal_scores=True)
