@@ -558,6 +558,14 @@ def run_serving(args, rank: int, world: int, local_rank: int):
     if args.tc_splitk:
         d.det_debug_set_tc_variant(0x100)
     dist, comm, saved_stdout = _tensor_parallel(args, h, rank, world, shape, rows=max(8, B))
+    if world == 1 and args.emulate_tp > 1:
+        # timing aid: the launch sequence of rank 0 of an N-way shard, every exchange looped back to local memory
+        mixw = shape["n_h"] * shape["hd"]
+        staging = 16 * max(max(args.chunk, B) * max(mixw, shape["ffn"], shape["hidden"]), shape["vocab"]) + 4096
+        comm = h.dh_peer_comm_new(None, 0, args.emulate_tp, staging)
+        if not comm:
+            raise RuntimeError(h.dh_last_error().decode())
+        h.dh_peer_comm_open_loopback(comm)
     model = h.dh_model_new_synth_tp(bk, cfg.encode(), args.layers, SEED, 16, max(args.chunk, B), comm)
     if not model:
         raise RuntimeError(h.dh_last_error().decode())
@@ -635,7 +643,9 @@ def run_serving(args, rank: int, world: int, local_rank: int):
                                f"per-sequence seeds; one batched step per token",
                    "contexts": ctxs, **({"layers_built": args.layers, "note": "reduced depth: not a result"} if args.layers else {}),
                    "parallelism": f"tp{world}: every GPU serves every sequence with 1/{world} of the heads, FFN columns and "
-                                  f"output rows; exchange {args.exchange}" if world > 1 else "1 GPU",
+                                  f"output rows; exchange {args.exchange}" if world > 1 else
+                                  (f"EMULATED rank 0 of tp{args.emulate_tp}, exchanges looped back: not a result"
+                                   if args.emulate_tp > 1 else "1 GPU"),
                    "rows_path": "composed per-sequence calls" if args.compose_rows else
                    "det_attention_rows / det_gdn_rows", "l2": "weights streamed per step exceed the 126 MB L2"},
         "per_token_ms": {"p50": float(np.percentile(steps_ms, 50)), "p99": float(np.percentile(steps_ms, 99))},
