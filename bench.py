@@ -285,6 +285,8 @@ def _tensor_parallel(args, h, rank: int, world: int, shape: dict, rows: int):
     h.dh_peer_comm_open(comm, handles.ctypes.data)
     if args.exchange == "peer-unfused":
         h.dh_peer_comm_set_fuse(comm, 0)
+    elif args.exchange == "peer-rows":
+        h.dh_peer_comm_set_fuse(comm, 1)     # exchanges fused with their row kernels, not with the GEMVs
     dist.barrier()
     return dist, comm, saved_stdout
 
@@ -469,12 +471,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                    "rot_dim": 64, "rope_theta": 1e7, "eps": 1e-6, "v_scale": 2 ** -10},
         "e2e": {"value": K / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": shape["hidden"] * 4,
                 "d2h_bytes_per_step": 4},
-        # tensor parallel (fused peer exchange): every layer is 10 launches — four exchange + row kernels, five GEMVs, the
-        # mixer step (prep + decode attention on an attention layer, which then has one GEMV less) — plus embed, the final
-        # exchange + norm, the head GEMV, the logits gather, argmax and token feedback; with stand-alone exchanges every
-        # layer adds 4 exchange kernels, 2 residual adds and 1 quant
+        # tensor parallel: three of a layer's four exchanges run as prologues of the GEMVs they feed, so a Gated DeltaNet
+        # layer is 6 launches (qkv|z + a|b, mixer step, out, gate|up, SwiGLU exchange + quantization, down) and an attention
+        # layer 7, plus embed, head GEMV, logits gather, argmax and token feedback; "peer-rows" keeps every exchange in a
+        # row kernel of its own (10 per layer), stand-alone exchanges add 4 exchange kernels, 2 residual adds and 1 quant
         "gpu_launches": K * (launches_per_token(cfg, fused=not args.no_fuse) if world == 1 else
-                             SHAPES[cfg]["layers"] * (10 if args.exchange == "peer" else 17) + 6),
+                             (SHAPES[cfg]["layers"] * 6 + SHAPES[cfg]["layers"] // 4 + 5) if args.exchange == "peer" and not args.no_fuse else
+                             SHAPES[cfg]["layers"] * (10 if args.exchange in ("peer", "peer-rows") else 17) + 6),
         "prefill": {"value": P / (prefill_ms * 1e-3), "unit": "tok/s", "tokens": P, "chunk": chunk},
         "roofline": None if achieved is None else
                     {"bound": "hbm", "kernel": "k_gemv_stream", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -668,7 +671,7 @@ def main():
     ap.add_argument("--config", default="27b", choices=sorted(SHAPES))
     ap.add_argument("--prefill", type=int, default=2048)
     ap.add_argument("--chunk", type=int, default=512)
-    ap.add_argument("--exchange", default="peer", choices=["peer", "peer-unfused", "nccl"],
+    ap.add_argument("--exchange", default="peer", choices=["peer", "peer-rows", "peer-unfused", "nccl"],
                     help="N > 1: decode exchanges as one peer-memory kernel per rank (default) or as NCCL all-gathers")
     ap.add_argument("--emulate-tp", type=int, default=0,
                     help="timing aid at N = 1: run rank 0 of a P-way shard with exchanges looped back (values meaningless)")

@@ -42,7 +42,8 @@ class GdnState(C.Structure):
 class ActSource(C.Structure):
     """det_act_source (include/det_b200.h): fp32 inputs of a GEMM whose activation quantization is fused in."""
     _fields_ = [("kind", c_int), ("a", c_void_p), ("b", c_void_p), ("eps", c_float), ("xq", c_void_p), ("sx", c_void_p),
-                ("mx", c_void_p), ("amax", c_void_p)]
+                ("mx", c_void_p), ("amax", c_void_p), ("xchg", c_void_p), ("local", c_void_p), ("slice", c_int),
+                ("acc_out", c_void_p)]
 
 
 class GemvOp(C.Structure):

@@ -18,6 +18,7 @@
 //
 // Algorithmic bytes per launch: N * (K*bits/8 + 4 + K/128*2) weights + M * (K + 4 + K/128*2) in + M * N * 4 out.
 #include "gemm_common.cuh"
+#include "exchange.cuh"
 
 namespace detb {
 
@@ -161,6 +162,14 @@ struct GemvArgs {
     // than 8192 values go through the prologue — and its last CTA leaves them zero for the next producer.
     unsigned* h_amax;         // producer side (NULL: none)
     unsigned* pamax;          // consumer side (NULL: the prologue scans the row)
+    // Tensor-parallel prologue: the fp32 rows are not read from `pa` but gathered from every rank's slice through the
+    // packet exchange of exchange.cuh — every CTA pushes its share of this rank's slice, then polls the packets of the
+    // rows it stages.  With acc_in the staged value is acc_in + gathered (the residual add; CTA 0 stores the sums to
+    // acc_out, a different buffer: the other CTAs still read acc_in).
+    int xchg;
+    XchgArgs xa;
+    const float* acc_in;
+    float* acc_out;
 };
 enum : int { PRO_RMS = 1, PRO_PLAIN = 2 };
 
@@ -225,6 +234,11 @@ __device__ __forceinline__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool keep = blockIdx.x == 0 && a.xq_out != nullptr;
     const bool rms = a.pro == PRO_RMS;
+    unsigned seq = 0;
+    if (a.xchg) {               // this rank's slice goes out to every rank before anybody polls
+        seq = xchg_seq(a.xa);
+        xchg_push(a.xa, seq);
+    }
     for (int t = 0; t < a.mt; t++) {
         const float* pa = a.pa + (size_t)t * K;
         float4 v[RREG], wv[RREG];
@@ -234,7 +248,18 @@ __device__ __forceinline__ void fused_stage(const GemvArgs& a, uint8_t* xs, int2
             v[r] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             wv[r] = v[r];
             if (s < G) {
-                v[r] = *reinterpret_cast<const float4*>(pa + s * 128 + lane * 4);
+                if (a.xchg) {
+                    const size_t e0 = (size_t)(a.t0 + t) * K + s * 128 + lane * 4;     // first of the lane's four values
+                    const float2 lo = xchg_read(a.xa, seq, e0 >> 1), hi = xchg_read(a.xa, seq, (e0 >> 1) + 1);
+                    v[r] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                    if (a.acc_in) {
+                        const float4 x = *reinterpret_cast<const float4*>(a.acc_in + e0);
+                        v[r] = make_float4(fadd(x.x, v[r].x), fadd(x.y, v[r].y), fadd(x.z, v[r].z), fadd(x.w, v[r].w));
+                        if (blockIdx.x == 0) *reinterpret_cast<float4*>(a.acc_out + e0) = v[r];
+                    }
+                } else {
+                    v[r] = *reinterpret_cast<const float4*>(pa + s * 128 + lane * 4);
+                }
                 if (rms) wv[r] = *reinterpret_cast<const float4*>(a.pb + s * 128 + lane * 4);
             }
         }
@@ -735,6 +760,22 @@ static void gemv_stream_bits(const GemvCall& call, cudaStream_t q) {
         a.xq_out = nullptr; a.sx_out = nullptr; a.mx_out = nullptr;
         a.pamax = nullptr;
         a.h_amax = call.h ? call.h_amax : nullptr;
+        a.xchg = 0;
+        a.acc_in = nullptr;
+        a.acc_out = nullptr;
+        if (src && src->xchg) {
+            const Xchg* xc = static_cast<const Xchg*>(src->xchg);
+            DETB_REQUIRE(xc->size * src->slice == g.K && src->slice % 2 == 0, "exchange prologue: size * slice must be K");
+            DETB_REQUIRE((size_t)call.M * g.K * 8 <= xc->slot_bytes, "exchange larger than the staging slot");
+            DETB_REQUIRE(t0 == 0 && call.M <= MT, "exchange prologue: all rows in one launch");
+            a.xchg = 1;
+            a.xa = xchg_args(xc, src->local, nullptr, call.M, src->slice);
+            if (src->kind == PRO_RMS && src->acc_out) {
+                DETB_REQUIRE(src->a && src->acc_out != src->a, "the summed rows need a buffer of their own");
+                a.acc_in = src->a;
+                a.acc_out = src->acc_out;
+            }
+        }
         if (src) {
             a.pamax = src->amax;
             a.pro = src->kind;
@@ -767,7 +808,9 @@ void gemv_stream_launch(const GemvCall& call, cudaStream_t q) {
                      "the activation prologue takes rows of at most 8192 values unless their group maxima are given");
         DETB_REQUIRE(!call.src->amax || (call.src->kind == PRO_PLAIN && !call.lin2),
                      "group maxima go with the plain quantization of a single linear only");
-        DETB_REQUIRE((call.src->kind == PRO_RMS || call.src->kind == PRO_PLAIN) && call.src->a, "bad activation source");
+        DETB_REQUIRE((call.src->kind == PRO_RMS || call.src->kind == PRO_PLAIN) && (call.src->a || call.src->xchg), "bad activation source");
+        DETB_REQUIRE(!call.src->xchg || (call.src->local && !call.src->amax && (!call.lin2 || call.M <= 2)),
+                     "exchange prologue: needs the local slice, no group maxima, one launch");
         DETB_REQUIRE(call.src->kind != PRO_RMS || call.src->b, "RMSNorm needs its weight");
         DETB_REQUIRE((call.src->xq != nullptr) == (call.src->sx != nullptr) && (call.src->xq != nullptr) == (call.src->mx != nullptr),
                      "the quantized-row outputs come all together or not at all");

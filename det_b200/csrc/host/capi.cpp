@@ -307,7 +307,12 @@ void dh_peer_comm_handle(void* c, uint8_t* out64) { static_cast<det::PeerComm*>(
 void dh_peer_comm_open(void* c, const uint8_t* handles) { static_cast<det::PeerComm*>(static_cast<det::Comm*>(c))->open(handles); }
 void dh_peer_comm_open_loopback(void* c) { static_cast<det::PeerComm*>(static_cast<det::Comm*>(c))->open_loopback(); }
 // Measurement switch: 0 runs every exchange as its own launch followed by the consumer kernels (same values).
-void dh_peer_comm_set_fuse(void* c, int on) { static_cast<det::PeerComm*>(static_cast<det::Comm*>(c))->fuse = on != 0; }
+// bit 0: exchange + consumer row kernel as one launch; bit 1: exchanges as prologues of the decode GEMVs they feed
+void dh_peer_comm_set_fuse(void* c, int on) {
+    auto* p = static_cast<det::PeerComm*>(static_cast<det::Comm*>(c));
+    p->fuse = (on & 1) != 0;
+    p->fuse_gemv = (on & 2) != 0;
+}
 // gather(local, gathered, bytes): fills gathered[size][bytes] with every rank's block (host memory).
 void* dh_callback_comm_new(int rank, int size, void (*gather)(const void*, void*, size_t)) {
     return static_cast<det::Comm*>(new det::CallbackComm(rank, size, gather));

@@ -27,6 +27,17 @@ class Comm {
         bk.add(x, y_full, t * slice * size);
         bk.rmsnorm_quant(x, w, eps, t, slice * size, q, s, mm);
     }
+    // The same step for callers that keep two copies of the residual stream: the sums may land in x_alt instead of x
+    // (returns true then; the caller swaps its buffers).  An exchange that runs as the prologue of the GEMV consuming
+    // q / s / mm needs this: the CTAs of that launch read x while one of them stores the sums.
+    virtual bool gather_add_norm_quant_alt(Backend& bk, const Buf<float>& y_l, const Buf<float>& tmp, const Buf<float>& y_full,
+                                           size_t t, size_t slice, const Buf<float>& x, const Buf<float>& x_alt,
+                                           const Buf<float>& w, float eps, const Buf<int8_t>& q, const Buf<float>& s,
+                                           const Buf<uint16_t>& mm) {
+        (void)x_alt;
+        gather_add_norm_quant(bk, y_l, tmp, y_full, t, slice, x, w, eps, q, s, mm);
+        return false;
+    }
     // quant(gather(local)) -> q, s, mm
     virtual void gather_quant(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full, size_t t,
                               size_t slice, const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
@@ -95,6 +106,9 @@ class PeerComm : public Comm {
     void gather_add_norm_quant(Backend& bk, const Buf<float>& y_l, const Buf<float>& tmp, const Buf<float>& y_full, size_t t,
                                size_t slice, const Buf<float>& x, const Buf<float>& w, float eps, const Buf<int8_t>& q,
                                const Buf<float>& s, const Buf<uint16_t>& mm) override;
+    bool gather_add_norm_quant_alt(Backend& bk, const Buf<float>& y_l, const Buf<float>& tmp, const Buf<float>& y_full, size_t t,
+                                   size_t slice, const Buf<float>& x, const Buf<float>& x_alt, const Buf<float>& w, float eps,
+                                   const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) override;
     void gather_quant(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full, size_t t,
                       size_t slice, const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) override;
     void silu_gather_quant(Backend& bk, const Buf<float>& g, const Buf<float>& u, const Buf<float>& h_l,
@@ -102,6 +116,7 @@ class PeerComm : public Comm {
                            const Buf<float>& s, const Buf<uint16_t>& mm) override;
     size_t small_rows = 32;   // the serving step of 32 sequences still goes through the peer kernels
     bool fuse = true;   // run exchange + consumer as one launch (measurement switch; results are the same)
+    bool fuse_gemv = true;   // ... and, where the consumer's output feeds a decode GEMV, as that GEMV's prologue
 
   private:
     bool small(size_t t, size_t slice) const;   // the exchange fits the staging and is decode-sized

@@ -61,11 +61,26 @@ bool CudaBackend::hold(int kind, const float* a, const float* b, float eps, size
     flush_pending();
     // rows of more than 8192 values only qualify when their group maxima come with them
     if (!fuse_decode || !stream_layout || m > (size_t)stream_max_m || n % 128 != 0 || (n > 8192 && !amax) || !mx) return false;
+    pending_ = PendingAct();
     pending_.kind = kind;
     pending_.amax = amax;
     pending_.a = a; pending_.b = b; pending_.eps = eps;
     pending_.m = m; pending_.n = n;
     pending_.xq = xq; pending_.sx = sx; pending_.mx = mx;
+    return true;
+}
+bool CudaBackend::hold_exchange(int kind, void* xchg, const float* local, size_t slice, size_t size, const float* x_in,
+                                float* x_out, const float* w, float eps, size_t m, int8_t* xq, float* sx, uint16_t* mx) {
+    flush_pending();
+    const size_t n = slice * size;
+    if (!fuse_decode || !stream_layout || m > 2 || n % 128 != 0 || n > 8192 || slice % 2 != 0 || !mx) return false;
+    pending_ = PendingAct();
+    pending_.kind = kind;
+    pending_.a = x_in; pending_.b = w; pending_.eps = eps;
+    pending_.m = m; pending_.n = n;
+    pending_.xq = xq; pending_.sx = sx; pending_.mx = mx;
+    pending_.xchg = xchg; pending_.local = local; pending_.slice = slice;
+    pending_.acc_out = x_out;
     return true;
 }
 void CudaBackend::flush_pending() {
@@ -76,7 +91,18 @@ void CudaBackend::flush_pending() {
     }
     if (!pending_.kind) return;
     const PendingAct p = pending_;
-    pending_.kind = 0;
+    pending_ = PendingAct();
+    if (p.xchg) {
+        // no GEMV took the exchange as its prologue: the exchange kernels run it (in place on x, then the sums are copied
+        // to where the fused form would have put them)
+        if (p.kind == DET_ACT_RMSNORM) {
+            det_xchg_add_rmsnorm_quant(p.xchg, p.local, (int)p.slice, const_cast<float*>(p.a), p.b, p.eps, (int)p.m, p.xq, p.sx, p.mx, ST);
+            det_memcpy(p.acc_out, p.a, p.m * p.n * sizeof(float), ST);
+        } else {
+            det_xchg_quant(p.xchg, p.local, nullptr, (int)p.slice, (int)p.m, p.xq, p.sx, p.mx, ST);
+        }
+        return;
+    }
     if (p.kind == DET_ACT_RMSNORM)
         det_rmsnorm_quant(p.a, p.b, p.eps, (int)p.m, (int)p.n, nullptr, p.xq, p.sx, p.mx, ST);
     else
@@ -120,6 +146,7 @@ void CudaBackend::issue_gemv(const PendingGemm& g, const CudaLinear* second, con
         src.a = g.act.a; src.b = g.act.b; src.eps = g.act.eps;
         src.xq = g.act.xq; src.sx = g.act.sx; src.mx = g.act.mx;
         src.amax = g.act.amax;
+        src.xchg = g.act.xchg; src.local = g.act.local; src.slice = (int)g.act.slice; src.acc_out = g.act.acc_out;
         op.src = &src;
     } else {
         op.xq = g.xq; op.sx = g.sx; op.mx = g.mx;
@@ -272,10 +299,10 @@ void CudaBackend::gemm(const Linear& lin_, const Buf<int8_t>& xq, const Buf<floa
         bool ok = use_stream && pending_.xq == xq.ptr() && pending_.sx == sx.ptr() && pending_.mx == mx.ptr() &&
                   pending_.m == m && pending_.n == lin.k;
         for (float* d : ptrs)
-            if (d == pending_.a || d == pending_.b) ok = false;
+            if (d == pending_.a || d == pending_.b || d == pending_.local || d == pending_.acc_out) ok = false;
         if (ok) {
             act = pending_;
-            pending_.kind = 0;
+            pending_ = PendingAct();
         } else {
             flush_pending();
         }

@@ -76,6 +76,12 @@ class CudaBackend : public Backend {
     // product from its epilogue and the quantization of that product becomes the next GEMV's prologue.  Results are
     // bit-identical either way (tests/test_gemv_fused_gpu.py); `fuse_decode = false` issues every op on its own.
     bool fuse_decode = true;
+    // Tensor parallel: an exchange whose gathered rows feed a decode GEMV is held back like a quantization and becomes that
+    // GEMV's prologue (det_act_source.xchg).  Returns false when the shape does not qualify (the caller then runs the
+    // exchange kernel itself).  kind DET_ACT_RMSNORM: rows = x_in + gathered, stored to x_out (!= x_in), then RMSNorm with w;
+    // DET_ACT_PLAIN: rows = gathered.  Either way the codes / scale / multipliers also land in xq / sx / mx.
+    bool hold_exchange(int kind, void* xchg, const float* local, size_t slice, size_t size, const float* x_in, float* x_out,
+                       const float* w, float eps, size_t m, int8_t* xq, float* sx, uint16_t* mx);
     // The SwiGLU epilogue also folds the group maxima of its product, and the down projection's GEMV quantizes the product
     // in its prologue from them (no separate quantization launch for the 17408-value row).  Same values either way.
     bool swiglu_amax = true;
@@ -100,6 +106,12 @@ class CudaBackend : public Backend {
         float* sx = nullptr;
         uint16_t* mx = nullptr;
         unsigned* amax = nullptr;   // group maxima of `a` left by the SwiGLU epilogue that produced it (det_gemv_op.h_amax)
+        // tensor parallel: the rows are gathered from every rank's `local` slice through the exchange handle `xchg`; with
+        // acc_out the residual `a` plus the gathered rows is what gets normalized, and lands in acc_out
+        void* xchg = nullptr;
+        const float* local = nullptr;
+        size_t slice = 0;
+        float* acc_out = nullptr;
     } pending_;
     struct PendingGemm {
         bool on = false;

@@ -567,25 +567,32 @@ static void load_shard(Model& m, const Config& cfg, uint64_t seed, Backend* bk, 
     tp.y_full = bk->alloc<float>(mb * h);
     tp.logits_l = bk->alloc<float>(mb * tp.voc);
     tp.tmp = bk->alloc<float>(std::max(mb * std::max(inter, mix), cfg.vocab));
+    tp.x_alt = bk->alloc<float>(mb * h);
 }
 
 void Model::network_tp(size_t pos0, size_t t, const RowsCtx* rows) {
     const Config& c = cfg;
     Backend* bk = backend;
-    const size_t h = c.hidden, P = (size_t)comm->size;
+    const size_t h = c.hidden;
+    // The residual stream lives in w.x or in tp.x_alt: an exchange that runs as the prologue of the GEMV it feeds stores
+    // x + gathered into the other copy (every CTA of that launch still reads the old one).  `xc` is the current copy.
+    const Buf<float>* xc = &w.x;
+    const Buf<float>* xo = &tp.x_alt;
     // A projection back to the hidden size leaves this rank's rows in y_l; the exchange, the residual add and the
-    // RMSNorm + quantization that follows are one step of the communicator (one launch on the peer-memory exchange).
+    // RMSNorm + quantization that follows are one step of the communicator (one launch on the peer-memory exchange, or
+    // the prologue of the next GEMV).
     auto project_back = [&](const Linear& lin, const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
         bk->gemm(lin, q, s, mm, t, GemmOut::write(tp.y_l));
     };
     auto add_norm_quant = [&](const Buf<float>& norm_w) {
-        comm->gather_add_norm_quant(*bk, tp.y_l, tp.tmp, tp.y_full, t, tp.hid, w.x, norm_w, c.eps, w.xq, w.sx, w.mx);
+        if (comm->gather_add_norm_quant_alt(*bk, tp.y_l, tp.tmp, tp.y_full, t, tp.hid, *xc, *xo, norm_w, c.eps, w.xq, w.sx, w.mx))
+            std::swap(xc, xo);
     };
     bool pending = false;   // y_l of the previous layer's down projection has not been added to x yet
     for (size_t li = 0; li < layers.size(); li++) {
         Layer& l = layers[li];
         if (pending) add_norm_quant(l.attn_norm);
-        else bk->rmsnorm_quant(w.x, l.attn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
+        else bk->rmsnorm_quant(*xc, l.attn_norm, c.eps, t, h, w.xq, w.sx, w.mx);
         if (l.is_attn) {
             Attn& a = l.attn;
             project(a.qkv, w.xq, w.sx, w.mx, t, {&w.qg, &w.k, &w.v});
@@ -615,18 +622,17 @@ void Model::network_tp(size_t pos0, size_t t, const RowsCtx* rows) {
     const size_t out_rows = all_logits ? t : 1;
     if (all_logits || t == 1) {
         if (pending) add_norm_quant(final_norm);
-        else bk->rmsnorm_quant(w.x, final_norm, c.eps, t, h, w.xq, w.sx, w.mx);
+        else bk->rmsnorm_quant(*xc, final_norm, c.eps, t, h, w.xq, w.sx, w.mx);
     } else {
         if (pending) {
             comm->all_gather(*bk, tp.y_l, tp.tmp, tp.y_full, t, tp.hid);
-            bk->add(w.x, tp.y_full, t * h);
+            bk->add(*xc, tp.y_full, t * h);
         }
-        Buf<float> last = Buf<float>::view(w.x.ptr_at((t - 1) * h), h);
+        Buf<float> last = Buf<float>::view(xc->ptr_at((t - 1) * h), h);
         bk->rmsnorm_quant(last, final_norm, c.eps, 1, h, w.xq, w.sx, w.mx);
     }
     bk->gemm(*lm_head.lins[0], w.xq, w.sx, w.mx, out_rows, GemmOut::write(tp.logits_l));
     comm->all_gather(*bk, tp.logits_l, tp.tmp, w.logits, out_rows, tp.voc);
-    (void)P;
 }
 
 std::string Model::forward(const int32_t* ids, size_t t, Observer* obs) {

@@ -128,6 +128,7 @@ class Model {
         Buf<float> y_l, y_full;      // projection back to hidden, local rows and gathered
         Buf<float> logits_l;
         Buf<float> tmp;              // all-gather scratch
+        Buf<float> x_alt;            // second copy of the residual stream (an exchange fused into a GEMV stores the sums here)
     } tp;
 
   private:

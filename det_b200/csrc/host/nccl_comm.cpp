@@ -114,8 +114,25 @@ void PeerComm::gather_add_norm_quant(Backend& bk, const Buf<float>& y_l, const B
     bk.flush();
     det_xchg_add_rmsnorm_quant(x_, y_l.ptr(), (int)slice, x.ptr(), w.ptr(), eps, (int)t, q.ptr(), s.ptr(), mm.ptr(), nullptr);
 }
+bool PeerComm::gather_add_norm_quant_alt(Backend& bk, const Buf<float>& y_l, const Buf<float>& tmp, const Buf<float>& y_full,
+                                         size_t t, size_t slice, const Buf<float>& x, const Buf<float>& x_alt,
+                                         const Buf<float>& w, float eps, const Buf<int8_t>& q, const Buf<float>& s,
+                                         const Buf<uint16_t>& mm) {
+    CudaBackend* cb = dynamic_cast<CudaBackend*>(&bk);
+    if (fuse && fuse_gemv && cb && small(t, slice) &&
+        cb->hold_exchange(DET_ACT_RMSNORM, x_, y_l.ptr(), slice, (size_t)size, x.ptr(), x_alt.ptr(), w.ptr(), eps, t, q.ptr(),
+                          s.ptr(), mm.ptr()))
+        return true;
+    gather_add_norm_quant(bk, y_l, tmp, y_full, t, slice, x, w, eps, q, s, mm);
+    return false;
+}
 void PeerComm::gather_quant(Backend& bk, const Buf<float>& local, const Buf<float>& tmp, const Buf<float>& full, size_t t,
                             size_t slice, const Buf<int8_t>& q, const Buf<float>& s, const Buf<uint16_t>& mm) {
+    CudaBackend* cb = dynamic_cast<CudaBackend*>(&bk);
+    if (fuse && fuse_gemv && cb && small(t, slice) &&
+        cb->hold_exchange(DET_ACT_PLAIN, x_, local.ptr(), slice, (size_t)size, nullptr, nullptr, nullptr, 0.0f, t, q.ptr(), s.ptr(),
+                          mm.ptr()))
+        return;
     if (!(fuse && det_xchg_fusable((int)t, (int)(slice * size)) && small(t, slice)))
         return Comm::gather_quant(bk, local, tmp, full, t, slice, q, s, mm);
     bk.flush();

@@ -191,6 +191,15 @@ typedef struct {
     float* sx;
     uint16_t* mx;
     unsigned* amax;   /* DET_ACT_PLAIN only, may be NULL: the group maxima of a, see det_gemv_op.h_amax */
+    /* Tensor parallel, may be NULL: a det_xchg handle.  The fp32 rows are then not read from memory: every rank's
+     * local[M][slice] is exchanged as by det_xchg_all_gather (size * slice = K) and the gathered rows are the input.  With
+     * kind DET_ACT_RMSNORM and acc_out != NULL, `a` is the residual stream: the normalized rows are a + gathered, and
+     * acc_out (a buffer of its own, not `a`) receives those sums — det_xchg_add_rmsnorm_quant as the prologue of the GEMV
+     * that consumes it.  Every rank must issue the same call; all rows go in one launch (M <= 8, M <= 2 with lin2).     */
+    void* xchg;
+    const float* local;
+    int slice;
+    float* acc_out;
 } det_act_source;
 typedef struct {
     const det_qlinear* lin;
