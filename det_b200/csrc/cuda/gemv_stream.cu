@@ -492,8 +492,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stream(const GemvArgs 
     const int W = a.workers, SPW = a.spw;
     const int total = a.seg[0].nquads + (DUAL ? a.seg[1].nquads : 0);
     pdl_trigger();
-    if (tid == 0) {
-        for (int s = 0; s < W * SPW; s++) mbar_init(&full[s], 1);
+    if (tid < W * SPW) {          // one barrier per thread (at most 80)
+        mbar_init(&full[tid], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();

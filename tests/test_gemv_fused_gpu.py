@@ -215,3 +215,45 @@ def test_pairs_layout_plain_outputs_and_swiglu_epilogue(half, k, m, libs):
     assert d.det_last_error() == 0
     for p in b1 + b2 + [xq, sx, mx, pg, pu, hq, sh, mh, yd, h, amax]:
         d.det_free(p)
+
+
+@pytest.mark.parametrize("kind,m", [("rms", 1), ("plain", 1), ("rms", 2)])
+def test_exchange_prologue_on_a_loopback_handle(kind, m, libs):
+    """The tensor-parallel prologue (push the local slice, poll the gathered row, residual add, RMSNorm / quantization
+    inside the GEMV) on a loopback exchange of size 2, where the gathered row is the local slice twice: it must equal
+    the ordinary prologue on that doubled row (plus the residual), twice in a row (two staging slots)."""
+    d = libs.cuda()
+    rng = np.random.default_rng(5)
+    k, n_out, slice_ = 2048, 1024, 1024
+    _, lin, bufs = _linear(d, libs, rng, n_out, k, 6)
+    x = d.det_xchg_create(16 * 8 * k + 4096, 0, 2)
+    d.det_xchg_open_loopback(x)
+    w = _dev(d, (1 + 0.1 * rng.standard_normal(k)).astype(np.float32))
+    y1, y2 = d.det_malloc(m * n_out * 4), d.det_malloc(m * n_out * 4)
+    hq, sh, mh = d.det_malloc(m * k), d.det_malloc(m * 4), d.det_malloc(m * (k // 128) * 2)
+    for it in range(2):
+        local = (rng.standard_normal((m, slice_)) * (0.3 + it)).astype(np.float32)
+        resid = (rng.standard_normal((m, k)) * 0.5).astype(np.float32)
+        full = np.concatenate([local, local], axis=1)
+        p_local, p_res, p_out = _dev(d, local), _dev(d, resid), d.det_malloc(m * k * 4)
+        if kind == "rms":
+            want_rows = _dev(d, (resid + full).astype(np.float32))      # one fp32 add per element, as the kernel does
+            s_ref = libs.ActSource(libs.DET_ACT_RMSNORM, want_rows, w, 1e-6, None, None, None, None, None, None, 0, None)
+            s_x = libs.ActSource(libs.DET_ACT_RMSNORM, p_res, w, 1e-6, hq, sh, mh, None, x, p_local, slice_, p_out)
+        else:
+            want_rows = _dev(d, full)
+            s_ref = libs.ActSource(libs.DET_ACT_PLAIN, want_rows, None, 0.0, None, None, None, None, None, None, 0, None)
+            s_x = libs.ActSource(libs.DET_ACT_PLAIN, None, None, 0.0, hq, sh, mh, None, x, p_local, slice_, None)
+        d.det_gemv(C.byref(libs.GemvOp(lin=C.pointer(lin), src=C.pointer(s_ref), M=m, y=y1)), None)
+        d.det_gemv(C.byref(libs.GemvOp(lin=C.pointer(lin), src=C.pointer(s_x), M=m, y=y2)), None)
+        a, b = _host(d, y1, np.zeros(m * n_out, np.float32)), _host(d, y2, np.zeros(m * n_out, np.float32))
+        assert a.any() and np.array_equal(a.view(np.uint32), b.view(np.uint32))
+        if kind == "rms":
+            got = _host(d, p_out, np.zeros((m, k), np.float32))
+            assert np.array_equal(got.view(np.uint32), (resid + full).astype(np.float32).view(np.uint32))
+        for p in (p_local, p_res, p_out, want_rows):
+            d.det_free(p)
+    assert d.det_last_error() == 0
+    d.det_xchg_destroy(x)
+    for p in bufs + [w, y1, y2, hq, sh, mh]:
+        d.det_free(p)
