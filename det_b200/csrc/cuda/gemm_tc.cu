@@ -372,13 +372,15 @@ static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const flo
         configured = smem;
     }
     dim3 grid((M + TC_TOK - 1) / TC_TOK, (N + TC_ROWS - 1) / TC_ROWS);
-    // Few tiles (a narrow linear at a small batch) leave most SMs idle: split K over up to 4 CTAs per tile.  The partial
+    // Few tiles (a narrow linear at a small batch) leave most SMs idle: split K over up to 16 CTAs per tile.  The partial
     // sums are exact integers, so the split cannot change a result.  By shape only.
     a.part = nullptr;
     a.counters = nullptr;
     const int tiles = (int)(grid.x * grid.y);
     int ksplit = 1;
-    if (g_tc_splitk && tiles * 2 <= sm_count() && G >= 16) ksplit = std::min(4, std::min(sm_count() / tiles, G / 8));
+    // A CTA walks its groups one after the other (about 0.6 us each), so with few tiles the launch time is the K loop of one
+    // CTA: split it over as many CTAs as there are idle SMs, down to three groups per CTA.
+    if (g_tc_splitk && tiles * 2 <= sm_count() && G >= 16) ksplit = std::min(16, std::min(sm_count() / tiles, G / 3));
     if (ksplit > 1) {
         a.part = splitk_cells();          // (sm_count()/2 + 1) tiles of 128 x 128 int64, owned by the runtime
         a.counters = splitk_counters();
