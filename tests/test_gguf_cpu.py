@@ -299,3 +299,101 @@ def test_row_helpers_round_trip(libs):
         for g in range(2):
             step = np.abs(x[g * 128 : (g + 1) * 128]).max() / qmax
             assert np.abs(out[g * 128 : (g + 1) * 128] - x[g * 128 : (g + 1) * 128]).max() <= max(0.55, 0.2 * qmax + 0.05) * step  # the scale search may go down to 0.8 x amax / qmax, clipping the largest values by 0.2 x amax
+
+
+def _py_gguf(path):
+    """An independent reading of the GGUF v3 container (little-endian header: magic, version, tensor count, kv count;
+    kv = string key, u32 type, value; tensor = string name, u32 rank, u64 dims, u32 type, u64 offset; data section at the
+    next multiple of general.alignment, default 32)."""
+    blob = path.read_bytes()
+    pos = 0
+
+    def take(fmt):
+        nonlocal pos
+        v = struct.unpack_from("<" + fmt, blob, pos)
+        pos += struct.calcsize("<" + fmt)
+        return v[0] if len(v) == 1 else v
+
+    def string():
+        nonlocal pos
+        n = take("Q")
+        s = blob[pos : pos + n].decode()
+        pos += n
+        return s
+
+    scalar = {0: "B", 1: "b", 2: "H", 3: "h", 4: "I", 5: "i", 6: "f", 7: "?", 10: "Q", 11: "q", 12: "d"}
+
+    def value(ty):
+        if ty == 8:
+            return string()
+        if ty == 9:
+            et, n = take("I"), take("Q")
+            return [value(et) for _ in range(n)]
+        return take(scalar[ty])
+
+    assert blob[:4] == b"GGUF"
+    pos = 4
+    version, n_tensors, n_kv = take("I"), take("Q"), take("Q")
+    kv = []
+    for _ in range(n_kv):
+        key = string()
+        kv.append((key, value(take("I"))))
+    tensors = []
+    for _ in range(n_tensors):
+        name = string()
+        dims = [take("Q") for _ in range(take("I"))]
+        tensors.append((name, dims, take("I"), take("Q")))
+    align = dict(kv).get("general.alignment", 32)
+    return version, kv, tensors, (pos + align - 1) // align * align, blob
+
+
+def test_written_file_reads_back_through_an_independent_parser(libs, det_file):
+    """The container this library writes, read by a parser written from the format description alone, and the tensor
+    payloads it points at checked against what they must hold (rope tables in binary64 rounded once, convert.rs:370-385;
+    unit norm weights; negative decay rates; the W8 head's row layout [codes][c][m], spec/tensor.rs:43-55)."""
+    h = libs.host()
+    version, kv, tensors, data_start, blob = _py_gguf(det_file)
+    assert version == 3
+    meta = dict(kv)
+    assert [k for k, _ in kv][:3] == ["general.architecture", "general.name", "qwen35.block_count"]
+    assert meta["general.architecture"] == "qwen35" and meta["qwen35.block_count"] == LAYERS
+    assert meta["qwen35.embedding_length"] == HIDDEN and meta["qwen35.full_attention_interval"] == 4
+    assert meta["qwen35.ssm.inner_size"] == 16 * 128 and meta["qwen35.ssm.time_step_rank"] == 16
+    assert meta["qwen35.rope.freq_base"] == 1e7 and abs(meta["qwen35.attention.layer_norm_rms_epsilon"] - 1e-6) < 1e-12
+    assert meta["det.v_scale"] == [1.0 / 1024] * 2
+    g = h.dh_gguf_open(str(det_file).encode())
+    assert h.dh_gguf_data_start(g) == data_start
+    mine = _tensors(h, g)
+    h.dh_gguf_close(g)
+    assert [t[0] for t in tensors] == list(mine)            # same order
+    table = {name: (dims, ty, off) for name, dims, ty, off in tensors}
+    for name, (dims, ty, off, _) in mine.items():
+        assert table[name] == (dims, ty, off)
+    # payloads
+    def f32s(name):
+        dims, ty, off = table[name]
+        assert ty == 0
+        return np.frombuffer(blob, np.float32, int(np.prod(dims)), data_start + off)
+
+    half, theta = 32, 1e7
+    ang = np.arange(N_POS, dtype=np.float64)[:, None] * (theta ** (-(2.0 * np.arange(half)) / 64.0))[None, :]
+    assert np.array_equal(f32s("rope_cos"), np.cos(ang).astype(np.float32).reshape(-1))
+    assert np.array_equal(f32s("rope_sin"), np.sin(ang).astype(np.float32).reshape(-1))
+    assert np.all(f32s("output_norm.weight") == 1.0) and np.all(f32s("blk.3.attn_q_norm.weight") == 1.0)
+    a = f32s("blk.0.ssm_a")
+    assert a.shape == (16,) and np.all(a <= -1.0) and np.all(a > -16.0)
+    dims, ty, off = table["output.weight"]
+    assert ty == 0xDE08 and dims == [HIDDEN, VOCAB]
+    rb = HIDDEN + 4 + HIDDEN // 128 * 2
+    row = np.frombuffer(blob, np.uint8, rb, data_start + off + 5 * rb)
+    c = row[HIDDEN : HIDDEN + 4].view(np.float32)[0]
+    m = row[HIDDEN + 4 :].view(np.uint16)
+    assert np.isfinite(c) and c > 0 and m.max() == 65535 and m.min() >= 1     # the widest group takes the full multiplier
+    out = np.zeros(HIDDEN, np.float32)
+    assert h.dh_dequant_row(0xDE08, row.ctypes.data, HIDDEN, out.ctypes.data) == 0
+    want = (np.float32(c) * m.astype(np.float32)).repeat(128) * row[:HIDDEN].view(np.int8).astype(np.float32)
+    assert np.array_equal(out, want)
+    # the W8 head quantizes the bf16 embedding table: row 5 of both must agree to half a step of the row's scale
+    dims_e, ty_e, off_e = table["token_embd.weight"]
+    emb = (np.frombuffer(blob, np.uint16, HIDDEN, data_start + off_e + 5 * HIDDEN * 2).astype(np.uint32) << 16).view(np.float32)
+    assert np.abs(out - emb).max() <= 0.62 * np.abs(emb).reshape(-1, 128).max(axis=1).repeat(128).max() / 127
