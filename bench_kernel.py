@@ -4,6 +4,7 @@ kernels that a profiler capture needs (a few hundred MB on the device, a handful
     python bench_kernel.py gemv    [N K bits M]    # k_gemv_stream, default 17408 5120 6 1
     python bench_kernel.py gemm_tc [N K bits M [variant]]   # k_gemm_tc, default 17408 5120 6 512, tile by shape
     python bench_kernel.py umma_peak                        # int8 tcgen05.mma issue rate with resident operands
+    python bench_kernel.py stream_peak                      # HBM read rate with nothing to compute: plain loads, GEMV rings
     python bench_kernel.py attn [n_h n_kv M pos0 [tc]]      # prefill attention, default 24 4 512 1536, tensor path on
 
 attn: one det_attention call of M tokens behind pos0 cached positions (head_dim 256, random cache contents); tc = 0
@@ -124,6 +125,32 @@ def main(argv):
         for iters in (2048, 8192):
             print(f"tcgen05.mma kind::i8 128x256x32, {iters} x 4 per SM: {d.det_debug_umma_peak(iters):.0f} TOPS; "
                   f"device error word {d.det_last_error()}")
+        return
+    if kind == "stream_peak":
+        d = capi.cuda()
+        assert d.det_init() == 0
+        size = 2 << 30
+        buf = d.det_malloc(size)
+        d.det_memset(buf, 1, size, None)
+        d.det_sync()
+        # (record bytes, warps, slots per warp, records per quad); 3136 x 16 x 4 x 5 is the 27B W6 GEMV at K = 5120
+        rings = ((3136, 16, 4, 5), (3136, 16, 2, 5), (3136, 16, 3, 5), (4096, 16, 3, 4), (8192, 16, 1, 2), (8192, 8, 3, 2),
+                 (16384, 4, 3, 1), (2048, 16, 6, 8),
+                 # half an SM or less: the successor's CTA is resident while this one runs
+                 (3136, 8, 4, 5), (3136, 8, 3, 5), (6272, 8, 2, 5), (4096, 8, 3, 4), (8192, 4, 3, 2), (8192, 6, 2, 2), (3136, 16, 1, 5))
+        # per launch: the whole buffer, then the size of one 17408 x 5120 W6 linear, then of a 5120 x 6144 one
+        for piece, regions, reps in ((size, 1, 5), (68 * 1024 * 1024 // 256 * 256, 30, 60), (24 * 1024 * 1024, 85, 170)):
+            label = f"{piece / 1e6:.0f} MB per launch"
+            r = d.det_debug_stream_peak(buf, piece, regions, 0, 0, 0, 0, 0, reps)
+            print(f"{label}: plain 16-byte loads {r:.0f} GB/s = {piece / r / 1e3:.2f} us")
+            for rec, warps, slots, nch in rings:
+                out = []
+                for mode in (1, 2):
+                    r = d.det_debug_stream_peak(buf, piece, regions, mode, rec, warps, slots, nch, reps)
+                    out.append(f"{r:.0f} GB/s = {piece / r / 1e3:.2f} us")
+                print(f"{label}: ring of {rec} B records, {warps} warps x {slots} slots ({rec * warps * slots >> 10} KB per SM), "
+                      f"{nch} per quad: dealt {out[0]}, contiguous {out[1]}; device error word {d.det_last_error()}")
+        d.det_free(buf)
         return
     if kind == "attn":
         return attn(argv)

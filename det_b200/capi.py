@@ -142,6 +142,7 @@ CUDA_ABI = {
     "det_debug_set_gemv": (None, [c_int]),
     "det_debug_set_rows": (None, [c_int]),
     "det_debug_umma_peak": (C.c_double, [c_int]),
+    "det_debug_stream_peak": (C.c_double, [c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     "det_last_error": (c_int, []),
     "det_clear_error": (None, []),
     "det_debug_set_wait_limit": (None, [C.c_longlong]),

@@ -345,6 +345,14 @@ void det_debug_set_gemv(int flags);
 /* Tensor-pipe ceiling: tcgen05.mma kind::i8 (128 x 256 x 32) issued back to back from resident shared-memory tiles on
  * every SM, no loads and no epilogue; returns the measured int8 rate in TOPS.                                         */
 double det_debug_umma_peak(int iters);
+/* Transport ceiling of a weight stream: `reps` launches that each read `bytes` of device memory with nothing to compute
+ * (launch r reads piece r % regions of a buffer of regions * bytes; launches chained by programmatic dependent launch);
+ * returns GB/s (events on the library queue).  mode 0 = plain 16-byte loads, grid-stride; mode 1 = the decode GEMV's transport (one
+ * CTA per SM, `warps` warps with `slots` shared-memory slots each, records of rec_bytes by cp.async.bulk, nch consecutive
+ * records per quad, quads dealt round-robin over CTAs and warps); mode 2 = the same ring over one contiguous span per
+ * CTA.  regions * bytes well above the L2 size measures HBM.                                                                */
+double det_debug_stream_peak(const void* p, size_t bytes, int regions, int mode, int rec_bytes, int warps, int slots,
+                             int nch, int reps);
 
 /* Last error recorded by a bounded device-side wait (0 = none, 1 = a wait ran out, 2 = a size check failed on the
  * device).  Waits for pending work.  While the word is set, exchange waits return at once (with zeros) instead of
