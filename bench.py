@@ -689,7 +689,8 @@ def main():
     ap.add_argument("--no-swiglu-amax", action="store_true",
                     help="measurement switch: quantize the SwiGLU product with its own launch (same tokens)")
     ap.add_argument("--gemv-flags", type=int, default=0,
-                    help="measurement switch of the decode GEMV (det_debug_set_gemv): 1 = whole-SM CTAs, n << 8 = n CTAs per SM")
+                    help="measurement switch of the decode GEMV (det_debug_set_gemv): n << 4 = n worker warps per CTA, "
+                         "n << 9 = n slots per worker")
     ap.add_argument("--rows-wide-min", type=int, default=-1,
                     help="measurement switch: rows from which the row kernels use one CTA per row (det_debug_set_rows)")
     ap.add_argument("--tc-splitk", action="store_true",

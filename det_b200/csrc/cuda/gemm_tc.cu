@@ -37,14 +37,21 @@ template <int TOK, int EC>
 struct TcCfg {
     static constexpr int B_BYTES = TOK * TC_KB;
     static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
-    static constexpr int STAGES = TOK <= 64 ? 6 : 5;
+    // The 32-token tile (the serving step) is sized for two CTAs per SM — four stages, half of TMEM: a launch of up to
+    // 296 tiles is one wave, and the next launch's CTAs come up beside this launch's last ones.
+    static constexpr int MIN_CTAS = TOK == 32 ? 2 : 1;
+    static constexpr int STAGES = TOK == 32 ? 4 : (TOK == 64 ? 6 : 5);
     static constexpr int EPI_WARPS = 4 * (TOK / EC);
     static constexpr int THREADS = (2 + EPI_WARPS) * 32;
     // TMEM accumulator buffers: the MMA warp runs up to NBUF groups ahead of the epilogue, which hides the
     // commit -> mbarrier -> tcgen05.ld -> release round trip between the two
     static constexpr int NBUF = TOK == 32 ? 8 : (TOK == 64 ? 4 : 3);
     static constexpr int TOTAL_COL = NBUF * TOK;       // the running plain sum over K lives behind the group buffers
-    static constexpr int TMEM_COLS = 512;              // NBUF * TOK + TOK rounded up to a power of two
+    static constexpr int TMEM_COLS = TOK == 32 ? 256 : 512;     // NBUF * TOK (+ TOK for the running sum) as a power of two
+    // Where the plain sum over K is kept: in a TMEM tile fed by a second UMMA per step, or — for the 32-token tile, whose
+    // K loop is paced by the MMA issue thread and not by the fold — in 32-bit registers of the epilogue threads (one add
+    // per accumulator and group, half the UMMAs).
+    static constexpr bool SUM_IN_REGS = TOK == 32;
     // UMMA instruction descriptor (kind::i8): D = s32, A = B = signed 8-bit, both K-major, N = TOK, M = 128.
     static constexpr unsigned IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TOK >> 3) << 17) | ((TC_ROWS >> 4) << 24);
 };
@@ -70,7 +77,7 @@ struct TcArgs {
 
 // Shared memory: [stages x (A 16 KB | B)] (1024-byte aligned) [mx table: G x TOK u16] [barriers] [tmem address]
 template <int TOK, int ECW>
-__global__ void __launch_bounds__(TcCfg<TOK, ECW>::THREADS, 1)
+__global__ void __launch_bounds__(TcCfg<TOK, ECW>::THREADS, TcCfg<TOK, ECW>::MIN_CTAS)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
     using Cfg = TcCfg<TOK, ECW>;
     constexpr int TC_TOK = TOK, TC_STAGES = Cfg::STAGES, TC_STAGE_BYTES = Cfg::STAGE_BYTES;
@@ -165,7 +172,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #pragma unroll
                 for (int k = 0; k < 4; k++) {
                     umma_i8(tmem_base + b * TC_TOK, da + 2 * k, db + 2 * k, Cfg::IDESC, k > 0 ? 1u : 0u);
-                    umma_i8(tmem_base + Cfg::TOTAL_COL, da + 2 * k, db + 2 * k, Cfg::IDESC, (g | k) ? 1u : 0u);
+                    if (!Cfg::SUM_IN_REGS)
+                        umma_i8(tmem_base + Cfg::TOTAL_COL, da + 2 * k, db + 2 * k, Cfg::IDESC, (g | k) ? 1u : 0u);
                 }
                 umma_commit(&empty[s]);
                 umma_commit(&tfull[b]);
@@ -186,8 +194,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         }
         asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
         long long acc[EC];
+        int plain[Cfg::SUM_IN_REGS ? EC : 1];
 #pragma unroll
         for (int t = 0; t < EC; t++) acc[t] = 0;
+#pragma unroll
+        for (int t = 0; t < (Cfg::SUM_IN_REGS ? EC : 1); t++) plain[t] = 0;
         const uint16_t* mrow = a.m + (size_t)(n < a.N ? n : 0) * G;
         unsigned mw_next = GL > 0 ? mrow[g0] : 0u;          // the row's multiplier, fetched one group ahead
         for (int l = 0; l < GL; l++) {
@@ -210,8 +221,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 mad_s32_s32(acc[t], r[t], (int)(mw * (pair & 0xffffu) + 0x80000000u));
                 mad_s32_s32(acc[t + 1], r[t + 1], (int)(mw * (pair >> 16) + 0x80000000u));
             }
+            if constexpr (Cfg::SUM_IN_REGS) {
+#pragma unroll
+                for (int t = 0; t < EC; t++) plain[t] += r[t];
+            }
         }
-        if (ok && GL > 0) {
+        if constexpr (Cfg::SUM_IN_REGS) {
+#pragma unroll
+            for (int t = 0; t < EC; t++) acc[t] += (long long)plain[t] << 31;
+        } else if (ok && GL > 0) {
             // the last group's commit also covers every step into the running total: add 2^31 * (sum of S) back
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             int r[EC];
@@ -380,7 +398,9 @@ static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const flo
     int ksplit = 1;
     // A CTA walks its groups one after the other (about 0.6 us each), so with few tiles the launch time is the K loop of one
     // CTA: split it over as many CTAs as there are idle SMs, down to three groups per CTA.
-    if (g_tc_splitk && tiles * 2 <= sm_count() && G >= 16) ksplit = std::min(16, std::min(sm_count() / tiles, G / 3));
+    // (the runtime's cells hold sm_count()/2 + 1 tiles of 128 x 128: four times as many 32-token tiles)
+    if (g_tc_splitk && tiles * 2 <= Cfg::MIN_CTAS * sm_count() && G >= 16)
+        ksplit = std::min(16, std::min(Cfg::MIN_CTAS * sm_count() / tiles, G / 3));
     if (ksplit > 1) {
         a.part = splitk_cells();          // (sm_count()/2 + 1) tiles of 128 x 128 int64, owned by the runtime
         a.counters = splitk_counters();

@@ -59,8 +59,8 @@ void bring_up() {
     if (cudaMemcpy(rt->error_word + 2, &limit, sizeof limit, cudaMemcpyHostToDevice) != cudaSuccess) { delete rt; return; }
     const size_t tiles = (size_t)rt->sm_count / 2 + 1, ncell = tiles * 128 * 128;
     if (cudaMalloc(&rt->splitk_cells, ncell * 8) != cudaSuccess || cudaMemset(rt->splitk_cells, 0, ncell * 8) != cudaSuccess ||
-        cudaMalloc(&rt->splitk_counters, tiles * sizeof(unsigned)) != cudaSuccess ||
-        cudaMemset(rt->splitk_counters, 0, tiles * sizeof(unsigned)) != cudaSuccess) { delete rt; return; }
+        cudaMalloc(&rt->splitk_counters, 4 * tiles * sizeof(unsigned)) != cudaSuccess ||      // tiles as narrow as 32 tokens
+        cudaMemset(rt->splitk_counters, 0, 4 * tiles * sizeof(unsigned)) != cudaSuccess) { delete rt; return; }
     // DET_B200_ATTN_WS_MB sizes the attention workspace (default 256; 0: none, prefill attention then stays on the CUDA cores
     // until det_attn_set_workspace provides one)
     size_t ws_mb = 256;

@@ -339,8 +339,8 @@ void det_debug_set_rows(int min_rows);
  * (default).  Adding 0x100 / 0x200 switches the split of K over several CTAs for linears with few row tiles on / off.
  * Results do not depend on any of it.                                                                                 */
 void det_debug_set_tc_variant(int v);
-/* Measurement switch of the decode GEMV: bit 0 = a CTA takes a whole SM's shared memory (no co-residency with the next
- * launch); bits 8.. = CTAs per SM of one launch (default 1).  Results do not depend on it.                           */
+/* Measurement switch of the decode GEMV: bits 4..8 = worker warps per CTA (0 = all sixteen); bits 9.. = shared-memory
+ * slots per worker warp (0 = as many as fit, at most 5).  Results do not depend on it.                                */
 void det_debug_set_gemv(int flags);
 /* Tensor-pipe ceiling: tcgen05.mma kind::i8 (128 x 256 x 32) issued back to back from resident shared-memory tiles on
  * every SM, no loads and no epilogue; returns the measured int8 rate in TOPS.                                         */
