@@ -127,10 +127,11 @@ constexpr int RR = DK / RL;   // rows per lane (16)
 
 // The CTA's 128 x 16 slab of the state in shared memory.  A thread (p = row block, jj = column) reads rows p * 16 + i of
 // column jj, so the 32 lanes of a warp touch 8 row blocks x 4 columns at once: element (r, c) lives at
-// r * SLAB_STRIDE + c + 4 * (r / 16), which puts those 32 words into 32 different banks (a plain padded row-major slab
+// r * SLAB_STRIDE + c + 4 * (r / 16) (the stride leaves room for that shift: a block of 16 rows starts 4 words later
+// than the one before), which puts those 32 words into 32 different banks (a plain padded row-major slab
 // is an 8-way conflict), and keeps every 4-column piece 16-byte aligned for the asynchronous copies.
-constexpr int SLAB_STRIDE = 44;
-constexpr int SLAB_FLOATS = DK * SLAB_STRIDE;
+constexpr int SLAB_STRIDE = 20;
+constexpr int SLAB_FLOATS = DK * SLAB_STRIDE + 4 * (DK / 16);
 __device__ __forceinline__ int slab_at(int r, int c) { return r * SLAB_STRIDE + c + 4 * (r >> 4); }
 constexpr int RUN_STRIDE = RR + 4;      // a lane's 16-row run, padded: the 8 runs of a token fall into distinct banks
 
@@ -171,18 +172,24 @@ __device__ __forceinline__ void slab_store(const float* slab, float* Sh, int j0)
 }
 
 // Batched decode with many sequences: every CTA advances one token of row blockIdx.y's sequence with the operands that
-// k_gdn_prep left in scratch (preparing them once per head is less work than in each of a head's 8 column CTAs).
+// k_gdn_prep left in scratch (preparing them once per head is less work than in each of a head's column CTAs).  A CTA
+// walks DEC_SLABS neighbouring 16-column slabs of its head: the next slab is in flight (asynchronous copies into the other
+// shared-memory buffer) while the current one is advanced and written back, and the head's k and q stay in registers.
+// The launch moves every state once in and once out and is bound by how many bytes its CTAs keep in flight; a CTA with
+// a single slab spends more than half of its life not loading.
+constexpr int DEC_SLABS = 4;
 __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
-    __shared__ __align__(16) float slab[SLAB_FLOATS];
+    __shared__ __align__(16) float slabs[2][SLAB_FLOATS];
     pdl_trigger();
     pdl_wait();
-    const int h = blockIdx.x / (DV / RC);
-    const int j0 = (blockIdx.x % (DV / RC)) * RC;
+    constexpr int CPH = DV / RC / DEC_SLABS;                     // CTAs per head
+    const int h = blockIdx.x / CPH;
+    const int c0 = (blockIdx.x % CPH) * DEC_SLABS;               // first slab of this CTA
     const int kh = h / g.rep;
     const int p = threadIdx.x % RL, jj = threadIdx.x / RL;
     const int t = g.rows ? blockIdx.y : 0;
     float* Sh = (g.rows ? g.rows[blockIdx.y].S : g.S) + (size_t)h * DK * DV;
-    slab_load_async(slab, Sh, j0);     // in flight while the operands are fetched
+    slab_load_async(slabs[0], Sh, c0 * RC);     // in flight while the operands are fetched
     const float* qrow = g.y + (size_t)t * g.conv_dim + (size_t)kh * DK + p * RR;
     const float* krow = g.y + (size_t)t * g.conv_dim + (size_t)g.n_k * DK + (size_t)kh * DK + p * RR;
     float k[RR], q[RR];
@@ -193,20 +200,28 @@ __global__ void __launch_bounds__(RC * RL) k_gdn_recur_dec(const GdnArgs g) {
         k[i] = kk.x; k[i + 1] = kk.y; k[i + 2] = kk.z; k[i + 3] = kk.w;
         q[i] = qq.x; q[i + 1] = qq.y; q[i + 2] = qq.z; q[i + 3] = qq.w;
     }
-    const float vv = g.y[(size_t)t * g.conv_dim + (size_t)2 * g.n_k * DK + (size_t)h * DV + j0 + jj];
     const float be = g.beta[(size_t)t * g.n_v + h], de = g.decay[(size_t)t * g.n_v + h];
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();
-    float s[RR];
+    for (int c = 0; c < DEC_SLABS; c++) {
+        const int j0 = (c0 + c) * RC;
+        float* slab = slabs[c & 1];
+        // the other buffer was written back in the last turn (the barrier at its end is behind every thread)
+        if (c + 1 < DEC_SLABS) slab_load_async(slabs[(c + 1) & 1], Sh, j0 + RC);
+        const float vv = g.y[(size_t)t * g.conv_dim + (size_t)2 * g.n_k * DK + (size_t)h * DV + j0 + jj];
+        if (c + 1 < DEC_SLABS) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        float s[RR];
 #pragma unroll
-    for (int i = 0; i < RR; i++) s[i] = slab[slab_at(p * RR + i, jj)];
-    const float ov = recur_step(s, k, q, vv, be, de);
-    if (p == 0) g.o[((size_t)t * g.n_v + h) * DV + j0 + jj] = ov;
-    __syncthreads();
+        for (int i = 0; i < RR; i++) s[i] = slab[slab_at(p * RR + i, jj)];
+        const float ov = recur_step(s, k, q, vv, be, de);
+        if (p == 0) g.o[((size_t)t * g.n_v + h) * DV + j0 + jj] = ov;
+        __syncthreads();
 #pragma unroll
-    for (int i = 0; i < RR; i++) slab[slab_at(p * RR + i, jj)] = s[i];
-    __syncthreads();
-    slab_store(slab, Sh, j0);
+        for (int i = 0; i < RR; i++) slab[slab_at(p * RR + i, jj)] = s[i];
+        __syncthreads();
+        slab_store(slab, Sh, j0);
+        __syncthreads();
+    }
 }
 
 // Decode step in one launch: conv + silu + l2norm + gates, the recurrence, the gated output norm and the conv-state
@@ -539,7 +554,7 @@ static void gdn_entry(const det_gdn_layer* L, det_gdn_state* S, const det_gdn_st
         return;
     }
     launch_pdl(k_gdn_prep, dim3((heads + 3) / 4, M), dim3(128), 0, q, 1, g);
-    if (rows) launch_pdl(k_gdn_recur_dec, dim3(n_v * (DV / RC), M), dim3(RC * RL), 0, q, 1, g);
+    if (rows) launch_pdl(k_gdn_recur_dec, dim3(n_v * (DV / RC / DEC_SLABS), M), dim3(RC * RL), 0, q, 1, g);
     else launch_pdl(k_gdn_recur_seq, dim3(n_v * (DV / RC)), dim3(RC * RL), 0, q, 1, g);
     const int row_blocks = (int)(((long long)M * n_v + 3) / 4);
     const int state_blocks = ((g.conv_dim + 127) / 128) * (rows ? M : 1);
