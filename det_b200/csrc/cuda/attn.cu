@@ -196,6 +196,12 @@ struct KTile {
     }
 };
 
+// acc += (s32) a * (s32) b as ONE 32 x 32 + 64 multiply-add (written out: the compiler otherwise widens both factors and
+// multiplies 64-bit values, several instructions per product).
+__device__ __forceinline__ void mad_wide(long long& acc, int a, int b) {
+    asm("mad.wide.s32 %0, %1, %2, %0;" : "+l"(acc) : "r"(a), "r"(b));
+}
+
 // P.V of one tile for value dimension d: num[r] += sum_q pq[r][q] * v[q][d], exact in int64.  Four keys per turn (one
 // 128-bit load of four p values per head, REP a compile-time count so nothing is predicated); rows of pq past the tile's
 // keys hold p = 0, so the turn may run over the end of a short tile.
@@ -203,15 +209,15 @@ template <int HD, int REP>
 __device__ __forceinline__ void pv_tile_n(const int (*pq)[KT], const int16_t* vtile, int nkeys, int d, long long (&num)[MAX_REP]) {
     const int n4 = (nkeys + 3) & ~3;
     for (int q = 0; q < n4; q += 4) {
-        const long long v0 = vtile[(q + 0) * HD + d], v1 = vtile[(q + 1) * HD + d];
-        const long long v2 = vtile[(q + 2) * HD + d], v3 = vtile[(q + 3) * HD + d];
+        const int v0 = vtile[(q + 0) * HD + d], v1 = vtile[(q + 1) * HD + d];
+        const int v2 = vtile[(q + 2) * HD + d], v3 = vtile[(q + 3) * HD + d];
 #pragma unroll
         for (int r = 0; r < REP; r++) {
             const int4 p = *reinterpret_cast<const int4*>(&pq[r][q]);
-            num[r] += (long long)p.x * v0;
-            num[r] += (long long)p.y * v1;
-            num[r] += (long long)p.z * v2;
-            num[r] += (long long)p.w * v3;
+            mad_wide(num[r], p.x, v0);
+            mad_wide(num[r], p.y, v1);
+            mad_wide(num[r], p.z, v2);
+            mad_wide(num[r], p.w, v3);
         }
     }
 }

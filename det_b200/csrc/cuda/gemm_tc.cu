@@ -187,10 +187,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         const int half = (warp - 2) >> 2;              // which block of 32 token columns
         const int n = n0 + q * 32 + lane;
         const int et = threadIdx.x - 64;
+        // the row's scale belongs to the weights: on its way before the previous kernel is waited for
+        const float cn = n < a.N ? a.c[n] : 0.0f;
         pdl_wait();   // activations, their multipliers and the output rows belong to the previous kernels
-        for (int i = et; i < G * TC_TOK; i += TC_EPI_WARPS * 32) {
-            const int g = i / TC_TOK, t = i - g * TC_TOK;
-            mxs[i] = (a.mx && t0 + t < a.M) ? a.mx[(size_t)(t0 + t) * G + g] : (uint16_t)1;
+        // token multipliers of this CTA's groups only (a split launch walks a fraction of K)
+        for (int i = et; i < GL * TC_TOK; i += TC_EPI_WARPS * 32) {
+            const int gl = i / TC_TOK, t = i - gl * TC_TOK;
+            mxs[(g0 + gl) * TC_TOK + t] = (a.mx && t0 + t < a.M) ? a.mx[(size_t)(t0 + t) * G + g0 + gl] : (uint16_t)1;
         }
         asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
         long long acc[EC];
@@ -260,7 +263,6 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             }
         }
         if (ok && n < a.N) {
-            const float cn = a.c[n];
 #pragma unroll
             for (int t = 0; t < EC; t++) {
                 const int tt = t0 + half * EC + t;
