@@ -93,6 +93,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     unsigned long long* tfull = bars + 2 * TC_STAGES;      // [NBUF]       group result complete in TMEM buffer
     unsigned long long* tempty = tfull + NBUF;             // [NBUF]       epilogue drained the buffer
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(tempty + NBUF);
+    float* sxs = reinterpret_cast<float*>(tmem_slot + 4);     // [TOK] token scales, staged with the multipliers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.x * TC_TOK, n0 = blockIdx.y * TC_ROWS;
@@ -195,6 +196,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             const int gl = i / TC_TOK, t = i - gl * TC_TOK;
             mxs[(g0 + gl) * TC_TOK + t] = (a.mx && t0 + t < a.M) ? a.mx[(size_t)(t0 + t) * G + g0 + gl] : (uint16_t)1;
         }
+        if (et < TC_TOK) sxs[et] = t0 + et < a.M ? a.sx[t0 + et] : 0.0f;
         asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
         long long acc[EC];
         int plain[Cfg::SUM_IN_REGS ? EC : 1];
@@ -266,7 +268,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #pragma unroll
             for (int t = 0; t < EC; t++) {
                 const int tt = t0 + half * EC + t;
-                if (tt < a.M) emit(a.out, tt, n, fmul(fmul(i64_to_f32(acc[t]), cn), a.sx[tt]));
+                if (tt < a.M) emit(a.out, tt, n, fmul(fmul(i64_to_f32(acc[t]), cn), sxs[half * EC + t]));
             }
         }
     }
@@ -384,7 +386,8 @@ static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const flo
     a.c = L->c; a.m = L->m; a.sx = sx; a.mx = mx;
     a.error_flag = error_word();
     a.out = out;
-    const size_t smem = 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES + (size_t)G * TC_TOK * 2 + 16 + (2 * TC_STAGES + 2 * Cfg::NBUF) * 8 + 16;
+    const size_t smem = 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES + (size_t)G * TC_TOK * 2 + 16 + (2 * TC_STAGES + 2 * Cfg::NBUF) * 8 + 16 +
+                        (size_t)TC_TOK * 4;
     DETB_REQUIRE(smem + 64 <= smem_optin(), "K is too large for the tensor-core GEMM's multiplier table");
     static size_t configured = 0;     // the kernel also has a few bytes of static shared memory
     if (smem > configured) {
