@@ -14,7 +14,8 @@
 // from the tensor core as well: every UMMA step is issued a second time into a TMEM tile that is never reset (|sum| <=
 // K * 128 * 127 < 2^31 for K < 132096).  The tensor pipe has the room; the multiply pipe of the CUDA cores is what the
 // fold is short of (measured: with the loads, the MMAs or the TMEM reads switched off the kernel is no faster; without the
-// fold arithmetic it is).
+// fold arithmetic it is).  The 32-token tile is the exception: its fold is short, the thread that issues the UMMAs sets
+// the pace, and the plain sum is kept in registers of the epilogue threads instead (TcCfg::SUM_IN_REGS).
 //
 // Warp roles (320 threads): warp 0 = TMA producer (one thread), warp 1 = TMEM allocation + MMA issue (one thread),
 // warps 2.. = epilogue (warp w reads TMEM lanes 32*(w%4) .. +31 and a block of the token columns).  Operands come from an
