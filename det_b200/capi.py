@@ -84,6 +84,8 @@ CUDA_ABI = {
     "det_gemm": (None, [C.POINTER(QLinear), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "det_gemm_ex": (None, [C.POINTER(QLinear), c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                            C.POINTER(c_int), C.POINTER(c_void_p), c_void_p]),
+    "det_gemm_pair": (None, [C.POINTER(QLinear), C.POINTER(QLinear), c_void_p, c_void_p, c_void_p, c_int,
+                             c_int, C.POINTER(c_int), C.POINTER(c_void_p), c_int, C.POINTER(c_int), C.POINTER(c_void_p), c_void_p]),
     "det_gemv": (None, [C.POINTER(GemvOp), c_void_p]),
     "det_gemm_scratch_bytes": (c_size_t, [c_int, c_int]),
     "det_gemm_set_scratch": (None, [c_void_p, c_size_t]),

@@ -166,6 +166,23 @@ void det_gemm_ex(const det_qlinear* L, const int8_t* xq, const float* sx, const 
     }
 }
 
+void det_gemm_pair(const det_qlinear* L1, const det_qlinear* L2, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
+                   int nparts1, const int* offs1, float* const* dsts1, int nparts2, const int* offs2, float* const* dsts2,
+                   cudaStream_t st) {
+    if (M <= 0) return;
+    DETB_REQUIRE(L1 && L2 && nparts1 >= 1 && nparts2 >= 1 && dsts1 && dsts2, "det_gemm_pair needs two linears and their outputs");
+    if ((L1->bits & DET_LAYOUT_INT8) && (L2->bits & DET_LAYOUT_INT8) && L1->K == L2->K) {
+        check_linear(L1);
+        check_linear(L2);
+        const OutSpec out1 = make_out(L1, nullptr, 0, nparts1, offs1, dsts1);
+        const OutSpec out2 = make_out(L2, nullptr, 0, nparts2, offs2, dsts2);
+        gemm_tc_launch(L1, xq, sx, mx, M, out1, queue_of(st), L2, &out2);
+        return;
+    }
+    det_gemm_ex(L1, xq, sx, mx, M, nullptr, 0, nparts1, offs1, dsts1, st);
+    det_gemm_ex(L2, xq, sx, mx, M, nullptr, 0, nparts2, offs2, dsts2, st);
+}
+
 void det_gemv(const det_gemv_op* op, cudaStream_t st) {
     DETB_REQUIRE(op && op->lin, "det_gemv needs a linear");
     if (op->M <= 0) return;

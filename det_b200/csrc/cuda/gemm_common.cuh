@@ -112,7 +112,8 @@ struct GemvCall {
 void gemv_stream_launch(const GemvCall& call, cudaStream_t q);
 
 // Entry of the tensor-core GEMM (gemm_tc.cu): L->wq is the int8-expanded layout.
+// L2 / out2 (optional): a second int8-layout linear over the same rows, taken into the same launch.
 void gemm_tc_launch(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
-                    const OutSpec& out, cudaStream_t q);
+                    const OutSpec& out, cudaStream_t q, const det_qlinear* L2 = nullptr, const OutSpec* out2 = nullptr);
 
 }  // namespace detb

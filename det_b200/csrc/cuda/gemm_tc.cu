@@ -74,12 +74,20 @@ struct TcArgs {
     // ([tile][token][row]); the CTA that arrives last at the tile's counter converts and emits, and leaves both zeroed
     unsigned long long* part;
     unsigned* counters;
+    // A second linear over the same input rows in the same launch (row tiles tiles1 .. of the grid; tiles1 = all of them
+    // when there is none): a small linear next to a wide one — the a|b projection beside qkv|z — costs a launch of its own
+    // about 10 us whatever its size.
+    int tiles1, N2;
+    const float* c2;
+    const uint16_t* m2;
+    OutSpec out2;
 };
 
 // Shared memory: [stages x (A 16 KB | B)] (1024-byte aligned) [mx table: G x TOK u16] [barriers] [tmem address]
-template <int TOK, int ECW>
+template <int TOK, int ECW, bool PAIR>
 __global__ void __launch_bounds__(TcCfg<TOK, ECW>::THREADS, TcCfg<TOK, ECW>::MIN_CTAS)
-k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
+k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+          const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
     using Cfg = TcCfg<TOK, ECW>;
     constexpr int TC_TOK = TOK, TC_STAGES = Cfg::STAGES, TC_STAGE_BYTES = Cfg::STAGE_BYTES;
     constexpr int TC_EPI_WARPS = Cfg::EPI_WARPS, TC_TMEM_COLS = Cfg::TMEM_COLS, NBUF = Cfg::NBUF;
@@ -97,7 +105,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     float* sxs = reinterpret_cast<float*>(tmem_slot + 4);     // [TOK] token scales, staged with the multipliers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t0 = blockIdx.x * TC_TOK, n0 = blockIdx.y * TC_ROWS;
+    const bool second = PAIR && (int)blockIdx.y >= a.tiles1;  // this CTA's row tile belongs to the second linear
+    const int ty = second ? (int)blockIdx.y - a.tiles1 : (int)blockIdx.y;
+    const CUtensorMap* mapw = second ? &map_w2 : &map_w;
+    const int t0 = blockIdx.x * TC_TOK, n0 = ty * TC_ROWS;
     const int G = a.G;
     const long long wl = wait_limit(a.error_flag);
     // this CTA's run of groups: [g0, g0 + GL)
@@ -137,7 +148,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             for (int l = 0; l < lead; l++) {
                 uint8_t* st = stages + (size_t)l * TC_STAGE_BYTES;
                 mbar_expect_tx(&full[l], TC_STAGE_BYTES);
-                tma_load_2d(st, &map_w, 0, (blockIdx.y * G + g0 + l) * TC_ROWS, &full[l]);
+                tma_load_2d(st, mapw, 0, (ty * G + g0 + l) * TC_ROWS, &full[l]);
             }
             pdl_wait();
             for (int l = 0; l < lead; l++)
@@ -149,7 +160,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 if (!ok) break;
                 uint8_t* st = stages + (size_t)s * TC_STAGE_BYTES;
                 mbar_expect_tx(&full[s], TC_STAGE_BYTES);
-                tma_load_2d(st, &map_w, 0, (blockIdx.y * G + g0 + l) * TC_ROWS, &full[s]);
+                tma_load_2d(st, mapw, 0, (ty * G + g0 + l) * TC_ROWS, &full[s]);
                 tma_load_2d(st + TC_A_BYTES, &map_x, (g0 + l) * TC_KB, t0, &full[s]);
             }
             if (!ok) {
@@ -190,7 +201,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         const int n = n0 + q * 32 + lane;
         const int et = threadIdx.x - 64;
         // the row's scale belongs to the weights: on its way before the previous kernel is waited for
-        const float cn = n < a.N ? a.c[n] : 0.0f;
+        const int N = second ? a.N2 : a.N;
+        // (the 128-token tile has no register to spare for it and fetches the scale when it emits)
+        float cn = 0.0f;
+        if constexpr (TOK <= 64) cn = n < N ? (second ? a.c2 : a.c)[n] : 0.0f;
         pdl_wait();   // activations, their multipliers and the output rows belong to the previous kernels
         // token multipliers of this CTA's groups only (a split launch walks a fraction of K)
         for (int i = et; i < GL * TC_TOK; i += TC_EPI_WARPS * 32) {
@@ -205,7 +219,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         for (int t = 0; t < EC; t++) acc[t] = 0;
 #pragma unroll
         for (int t = 0; t < (Cfg::SUM_IN_REGS ? EC : 1); t++) plain[t] = 0;
-        const uint16_t* mrow = a.m + (size_t)(n < a.N ? n : 0) * G;
+        const uint16_t* mrow = (second ? a.m2 : a.m) + (size_t)(n < N ? n : 0) * G;
         unsigned mw_next = GL > 0 ? mrow[g0] : 0u;          // the row's multiplier, fetched one group ahead
         for (int l = 0; l < GL; l++) {
             const int b = l % NBUF, g = g0 + l;
@@ -265,11 +279,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 ok = false;        // nothing to emit from this CTA
             }
         }
-        if (ok && n < a.N) {
+        if (ok && n < N) {
+            const OutSpec& out = second ? a.out2 : a.out;
+            if constexpr (TOK > 64) cn = (second ? a.c2 : a.c)[n];
 #pragma unroll
             for (int t = 0; t < EC; t++) {
                 const int tt = t0 + half * EC + t;
-                if (tt < a.M) emit(a.out, tt, n, fmul(fmul(i64_to_f32(acc[t]), cn), sxs[half * EC + t]));
+                if (tt < a.M) emit(out, tt, n, fmul(fmul(i64_to_f32(acc[t]), cn), sxs[half * EC + t]));
             }
         }
     }
@@ -371,9 +387,9 @@ static CUtensorMap make_map(const void* base, int rows, int K, int box_rows) {
 // Split K for narrow linears at a small batch (switched through det_debug_set_tc_variant: 0x100 on, 0x200 off).
 static bool g_tc_splitk = true;
 
-template <int TOK, int EC>
+template <int TOK, int EC, bool PAIR>
 static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
-                               const OutSpec& out, cudaStream_t q) {
+                               const OutSpec& out, const det_qlinear* L2, const OutSpec* out2, cudaStream_t q) {
     using Cfg = TcCfg<TOK, EC>;
     constexpr int TC_TOK = TOK, TC_STAGES = Cfg::STAGES, TC_STAGE_BYTES = Cfg::STAGE_BYTES;
     const int N = L->N, K = L->K, G = K / 128;
@@ -385,6 +401,16 @@ static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const flo
     TcArgs a;
     a.N = N; a.K = K; a.G = G; a.M = M;
     a.c = L->c; a.m = L->m; a.sx = sx; a.mx = mx;
+    a.tiles1 = row_tiles;
+    a.N2 = 0; a.c2 = nullptr; a.m2 = nullptr; a.out2 = out;
+    CUtensorMap map_w2 = map_w;
+    int row_tiles2 = 0;
+    if (L2) {
+        DETB_REQUIRE(L2->K == K && (reinterpret_cast<uintptr_t>(L2->wq) & 15) == 0, "the second linear shares the input rows");
+        row_tiles2 = (L2->N + TC_ROWS - 1) / TC_ROWS;
+        map_w2 = make_map(L2->wq, row_tiles2 * G * TC_ROWS, TC_KB, TC_ROWS);
+        a.N2 = L2->N; a.c2 = L2->c; a.m2 = L2->m; a.out2 = *out2;
+    }
     a.error_flag = error_word();
     a.out = out;
     const size_t smem = 1024 + (size_t)TC_STAGES * TC_STAGE_BYTES + (size_t)G * TC_TOK * 2 + 16 + (2 * TC_STAGES + 2 * Cfg::NBUF) * 8 + 16 +
@@ -392,10 +418,10 @@ static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const flo
     DETB_REQUIRE(smem + 64 <= smem_optin(), "K is too large for the tensor-core GEMM's multiplier table");
     static size_t configured = 0;     // the kernel also has a few bytes of static shared memory
     if (smem > configured) {
-        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemm_tc<TOK, EC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DETB_CUDA_OK(cudaFuncSetAttribute(k_gemm_tc<TOK, EC, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
-    dim3 grid((M + TC_TOK - 1) / TC_TOK, (N + TC_ROWS - 1) / TC_ROWS);
+    dim3 grid((M + TC_TOK - 1) / TC_TOK, row_tiles + row_tiles2);
     // Few tiles (a narrow linear at a small batch) leave most SMs idle: split K over up to 16 CTAs per tile.  The partial
     // sums are exact integers, so the split cannot change a result.  By shape only.
     a.part = nullptr;
@@ -412,20 +438,32 @@ static void gemm_tc_launch_tok(const det_qlinear* L, const int8_t* xq, const flo
         a.counters = splitk_counters();
         grid.z = ksplit;
     }
-    launch_pdl(k_gemm_tc<TOK, EC>, grid, dim3(Cfg::THREADS), smem, q, 1, map_w, map_x, a);
+    launch_pdl(k_gemm_tc<TOK, EC, PAIR>, grid, dim3(Cfg::THREADS), smem, q, 1, map_w, map_w2, map_x, a);
 }
 
 // Tile choice, by shape only: 32 tokens per CTA up to 32 rows (the serving step), 64 up to 64, else 128.  variant 1 / 2 /
 // 3 pins the 32 / 64 / 128-token tile (measurement switch).
 static int g_tc_variant = 0;
 void gemm_tc_launch(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
-                    const OutSpec& out, cudaStream_t q) {
+                    const OutSpec& out, cudaStream_t q, const det_qlinear* L2, const OutSpec* out2) {
     int v = g_tc_variant;
     if (v == 0) v = M <= 32 ? 1 : (M <= 64 ? 2 : 3);
+    if (L2 && v == 3) {
+        // the 128-token tile is short of registers as it is: two launches
+        gemm_tc_launch_tok<128, 32, false>(L, xq, sx, mx, M, out, nullptr, nullptr, q);
+        gemm_tc_launch_tok<128, 32, false>(L2, xq, sx, mx, M, *out2, nullptr, nullptr, q);
+        return;
+    }
     switch (v) {
-        case 1: gemm_tc_launch_tok<32, 16>(L, xq, sx, mx, M, out, q); break;
-        case 2: gemm_tc_launch_tok<64, 32>(L, xq, sx, mx, M, out, q); break;
-        case 3: gemm_tc_launch_tok<128, 32>(L, xq, sx, mx, M, out, q); break;
+        case 1:
+            if (L2) gemm_tc_launch_tok<32, 16, true>(L, xq, sx, mx, M, out, L2, out2, q);
+            else gemm_tc_launch_tok<32, 16, false>(L, xq, sx, mx, M, out, nullptr, nullptr, q);
+            break;
+        case 2:
+            if (L2) gemm_tc_launch_tok<64, 32, true>(L, xq, sx, mx, M, out, L2, out2, q);
+            else gemm_tc_launch_tok<64, 32, false>(L, xq, sx, mx, M, out, nullptr, nullptr, q);
+            break;
+        case 3: gemm_tc_launch_tok<128, 32, false>(L, xq, sx, mx, M, out, nullptr, nullptr, q); break;
         default: DETB_REQUIRE(false, "unknown tensor-core GEMM variant");
     }
 }

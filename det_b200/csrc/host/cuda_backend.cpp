@@ -87,7 +87,8 @@ void CudaBackend::flush_pending() {
     if (pending_gemm_.on) {
         const PendingGemm g = pending_gemm_;
         pending_gemm_.on = false;
-        issue_gemv(g, nullptr, nullptr, nullptr);
+        if (g.tc) issue_gemm_tc(g, nullptr, nullptr);
+        else issue_gemv(g, nullptr, nullptr, nullptr);
     }
     if (!pending_.kind) return;
     const PendingAct p = pending_;
@@ -171,6 +172,33 @@ void CudaBackend::issue_gemv(const PendingGemm& g, const CudaLinear* second, con
     op.h = h;
     op.h_amax = h_amax;
     det_gemv(&op, ST);
+}
+
+// One tensor-core GEMM launch over a batch: linear g.lin with one output buffer per part, optionally a second linear over
+// the same rows in the same launch (det_gemm_pair).
+void CudaBackend::issue_gemm_tc(const PendingGemm& g, const CudaLinear* second, const std::vector<float*>* dsts2) {
+    auto describe = [](const CudaLinear& l) {
+        return det_qlinear{l.wq8.ptr(), l.c.ptr(), l.m.ptr(), (int)l.n(), (int)l.k, l.bits | DET_LAYOUT_INT8};
+    };
+    auto offsets = [](const CudaLinear& l) {
+        std::vector<int> offs;
+        int acc = 0;
+        for (size_t w : l.widths) {
+            offs.push_back(acc);
+            acc += (int)w;
+        }
+        return offs;
+    };
+    const det_qlinear q1 = describe(*g.lin);
+    const std::vector<int> offs1 = offsets(*g.lin);
+    if (!second) {
+        det_gemm_ex(&q1, g.xq, g.sx, g.mx, (int)g.m, nullptr, 0, (int)offs1.size(), offs1.data(), g.dsts.data(), ST);
+        return;
+    }
+    const det_qlinear q2 = describe(*second);
+    const std::vector<int> offs2 = offsets(*second);
+    det_gemm_pair(&q1, &q2, g.xq, g.sx, g.mx, (int)g.m, (int)offs1.size(), offs1.data(), g.dsts.data(), (int)offs2.size(),
+                  offs2.data(), dsts2->data(), ST);
 }
 
 void* CudaBackend::scratch(Buf<uint8_t>& slot, size_t bytes) {   // cuda.rs:81-87
@@ -284,7 +312,15 @@ void CudaBackend::gemm(const Linear& lin_, const Buf<int8_t>& xq, const Buf<floa
         const PendingGemm& g = pending_gemm_;
         const bool same_rows = g.act.kind ? (g.act.xq == xq.ptr() && g.act.sx == sx.ptr() && g.act.mx == mx.ptr())
                                           : (g.xq == xq.ptr() && g.sx == sx.ptr() && g.mx == mx.ptr());
-        if (use_stream && same_rows && g.m == m && lin.bits == 8 && !lin.pairs && lin.k == g.lin->k && lin.n() <= 4096 &&
+        // a held batch GEMM takes a small W8 linear over the same rows into its launch too (qkv|z + a|b)
+        if (g.tc && !use_stream && same_rows && g.m == m && lin.bits == 8 && lin.wq8.ptr() && lin.k == g.lin->k &&
+            lin.n() <= 4096 && out.kind == GemmOut::Parts) {
+            const PendingGemm first = g;
+            pending_gemm_.on = false;
+            issue_gemm_tc(first, &lin, &ptrs);
+            return;
+        }
+        if (!g.tc && use_stream && same_rows && g.m == m && lin.bits == 8 && !lin.pairs && lin.k == g.lin->k && lin.n() <= 4096 &&
             out.kind != GemmOut::Accumulate) {
             const PendingGemm first = g;
             pending_gemm_.on = false;
@@ -323,6 +359,17 @@ void CudaBackend::gemm(const Linear& lin_, const Buf<int8_t>& xq, const Buf<floa
         issue_gemv(g, nullptr, nullptr, nullptr);
         return;
     }
+    if (!use_stream && lin.wq8.ptr() && fuse_decode && out.kind == GemmOut::Parts && lin.widths.size() <= 4) {
+        PendingGemm g;      // may still grow into a pair launch
+        g.on = true;
+        g.tc = true;
+        g.lin = &lin;
+        g.xq = xq.ptr(); g.sx = sx.ptr(); g.mx = mx.ptr();
+        g.m = m;
+        g.dsts = ptrs;
+        pending_gemm_ = g;
+        return;
+    }
     det_qlinear q;
     q.wq = use_stream ? lin.stream.ptr() : lin.wq.ptr();
     q.c = lin.c.ptr();
@@ -358,7 +405,7 @@ void CudaBackend::silu_mul_quant(const Buf<float>& g, const Buf<float>& u, size_
                                  const Buf<float>& sh, const Buf<uint16_t>& mh) {
     if (skip_mask & 4) return;
     // the held gate|up GEMV emits the product itself; its quantization becomes the next GEMV's prologue
-    if (pending_gemm_.on && pending_gemm_.lin->pairs && pending_gemm_.dsts.size() == 2 && pending_gemm_.dsts[0] == g.ptr() &&
+    if (pending_gemm_.on && !pending_gemm_.tc && pending_gemm_.lin->pairs && pending_gemm_.dsts.size() == 2 && pending_gemm_.dsts[0] == g.ptr() &&
         pending_gemm_.dsts[1] == u.ptr() && pending_gemm_.m == m && pending_gemm_.lin->n() == 2 * n && n % 128 == 0) {
         const PendingGemm first = pending_gemm_;
         pending_gemm_.on = false;

@@ -123,12 +123,14 @@ class CudaBackend : public Backend {
         size_t m = 0;
         std::vector<float*> dsts;       // one per part
         bool accumulate = false;
+        bool tc = false;                // a batch for the tensor-core GEMM (int8 layout), held for a second linear only
     } pending_gemm_;
     bool hold(int kind, const float* a, const float* b, float eps, size_t m, size_t n, int8_t* xq, float* sx,
               uint16_t* mx, unsigned* amax = nullptr);
     void flush_pending();
     void issue_gemv(const PendingGemm& g, const CudaLinear* second, const std::vector<float*>* dsts2, float* h,
                     unsigned* h_amax = nullptr);
+    void issue_gemm_tc(const PendingGemm& g, const CudaLinear* second, const std::vector<float*>* dsts2);
     void* scratch(Buf<uint8_t>& slot, size_t bytes);
     void finish_linear(CudaLinear& l);
     Buf<uint8_t> attn_scratch_, gdn_scratch_, sample_scratch_, synth_scratch_;

@@ -68,6 +68,13 @@ void det_gemm(const det_qlinear* L, const int8_t* xq, const float* sx, const uin
               cudaStream_t st);
 void det_gemm_ex(const det_qlinear* L, const int8_t* xq, const float* sx, const uint16_t* mx, int M, float* y,
                  int accumulate, int nparts, const int* offs, float* const* dsts, cudaStream_t st);
+/* Two linears over the same input rows as one launch (both in the det_linear_expand layout with the same K: otherwise
+ * two det_gemm_ex calls): the row tiles of L2 follow those of L1 in the grid.  Outputs as det_gemm_ex's nparts / offs /
+ * dsts form (nparts >= 1).  A small linear beside a wide one — the Gated DeltaNet a|b projection beside qkv|z — otherwise
+ * pays a launch of its own.  Same values as the two separate calls.                                                   */
+void det_gemm_pair(const det_qlinear* L1, const det_qlinear* L2, const int8_t* xq, const float* sx, const uint16_t* mx, int M,
+                   int nparts1, const int* offs1, float* const* dsts1, int nparts2, const int* offs2, float* const* dsts2,
+                   cudaStream_t st);
 /* Scratch protocol of the reference's large-M path (det_cuda.h:52-57).  Kept so that callers that follow it link and
  * run: this backend's kernels need no such scratch, so the registration is accepted and ignored.                    */
 size_t det_gemm_scratch_bytes(int M, int K);

@@ -155,3 +155,67 @@ def test_large_batch_gemm_matches_oracle(n, k, bits, ms, libs, oracle):
     finally:
         for p in (wq, cc, mm, w8):
             d.det_free(p)
+
+
+def _expanded(d, libs, rng, n, k, bits):
+    rows, c, m, nc = _det_rows(rng, n, k, bits)
+    g = k // 128
+    wq, cc, mm = d.det_malloc(n * nc), d.det_malloc(n * 4), d.det_malloc(n * g * 2)
+    codes = np.ascontiguousarray(rows[:, :nc])
+    d.det_memcpy(wq, codes.ctypes.data, codes.nbytes, None)
+    d.det_memcpy(cc, c.ctypes.data, c.nbytes, None)
+    d.det_memcpy(mm, m.ctypes.data, m.nbytes, None)
+    src = libs.QLinear(wq, cc, mm, n, k, bits)
+    w8 = d.det_malloc(d.det_linear_expand_bytes(n, k))
+    d.det_linear_expand(C.byref(src), w8, None)
+    d.det_sync()
+    return libs.QLinear(w8, cc, mm, n, k, bits | libs.DET_LAYOUT_INT8), [wq, cc, mm, w8]
+
+
+@pytest.mark.parametrize("n1,n2,k,mtok", [(1000, 96, 1024, 32), (16384, 96, 5120, 32), (640, 300, 2560, 100), (5120, 96, 6144, 20),
+                                          (2048, 96, 5120, 512)])
+def test_pair_launch_equals_two_launches(n1, n2, k, mtok, libs):
+    """det_gemm_pair — a W6 linear and a small W8 linear over the same rows in one tensor-core launch, each with two
+    routed parts — against two det_gemm_ex calls, bit for bit (ragged last row tiles, the K split, every token tile)."""
+    d = libs.cuda()
+    rng = np.random.default_rng(n1 + n2 + k + mtok)
+    g = k // 128
+    l1, b1 = _expanded(d, libs, rng, n1, k, 6)
+    l2, b2 = _expanded(d, libs, rng, n2, k, 8)
+    xq = rng.integers(-127, 128, (mtok, k)).astype(np.int8)
+    sx = (1e-3 * (0.5 + rng.random(mtok))).astype(np.float32)
+    mx = rng.integers(1, 65536, (mtok, g)).astype(np.uint16)
+    dx, ds, dm = d.det_malloc(xq.nbytes), d.det_malloc(sx.nbytes), d.det_malloc(mx.nbytes)
+    d.det_memcpy(dx, xq.ctypes.data, xq.nbytes, None)
+    d.det_memcpy(ds, sx.ctypes.data, sx.nbytes, None)
+    d.det_memcpy(dm, mx.ctypes.data, mx.nbytes, None)
+    d.det_debug_set_tc_variant(0x100)
+    cut1, cut2 = n1 // 2 // 4 * 4, n2 // 3
+    widths = [(cut1, n1 - cut1), (cut2, n2 - cut2)]
+    outs = []
+    for pair in (False, True):
+        bufs = [[d.det_malloc(mtok * w * 4) for w in ws] for ws in widths]
+        for ws, bs in zip(widths, bufs):
+            for w, b in zip(ws, bs):
+                d.det_memset(b, 0xFF, mtok * w * 4, None)
+        offs = [(C.c_int * 2)(0, ws[0]) for ws in widths]
+        dsts = [(C.c_void_p * 2)(*bs) for bs in bufs]
+        if pair:
+            d.det_gemm_pair(C.byref(l1), C.byref(l2), dx, ds, dm, mtok, 2, offs[0], dsts[0], 2, offs[1], dsts[1], None)
+        else:
+            d.det_gemm_ex(C.byref(l1), dx, ds, dm, mtok, None, 0, 2, offs[0], dsts[0], None)
+            d.det_gemm_ex(C.byref(l2), dx, ds, dm, mtok, None, 0, 2, offs[1], dsts[1], None)
+        got = []
+        for ws, bs in zip(widths, bufs):
+            for w, b in zip(ws, bs):
+                a = np.zeros((mtok, w), np.float32)
+                d.det_memcpy(a.ctypes.data, b, a.nbytes, None)
+                d.det_sync()
+                got.append(a.view(np.uint32))
+                d.det_free(b)
+        outs.append(got)
+    for i, (u, f) in enumerate(zip(*outs)):
+        assert np.isfinite(u.view(np.float32)).all() and np.array_equal(u, f), f"part {i}: {(u != f).sum()} of {u.size} differ"
+    assert d.det_last_error() == 0
+    for p in b1 + b2 + [dx, ds, dm]:
+        d.det_free(p)
