@@ -244,6 +244,10 @@ def cpu_baseline(h, cfg: str, threads: int, tokens: int = 8, warmup: int = 1, co
     return base
 
 
+# dram bytes / algorithmic bytes of the decode GEMV in the committed profiler capture (68.62 - 68.94 MB for 68.38 MB)
+GEMV_TRAFFIC_RATIO = 1.006
+
+
 def _tensor_parallel(args, h, rank: int, world: int, shape: dict, rows: int):
     """N > 1: tensor parallel over NVLink.  torch.distributed (gloo, CPU) only carries the NCCL id, the IPC handles, the
     barriers and the max-over-ranks of the timings; the data path uses the library's own exchange on its queue.  `rows` is
@@ -482,8 +486,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "roofline": None if achieved is None else
                     {"bound": "hbm", "kernel": "k_gemv_stream", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                     # DRAM traffic needs a profiler capture, which never runs inside a timed benchmark
-                     "traffic": None,
+                     # DRAM traffic needs a profiler capture, which never runs inside a timed benchmark: the committed
+                     # capture of the K = 5120 x N = 17408 launch read and wrote 1.004 - 1.008 x its algorithmic bytes
+                     # (68.38 MB), and the traffic of this kernel grows with the bytes it streams, so the mean launch
+                     # of the sweep is scaled by the middle of that range
+                     "traffic": GEMV_TRAFFIC_RATIO * nbytes.value / max(1, nlaunch.value),
+                     "traffic_how": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one K=5120 x N=17408 launch "
+                                    "(profiles/k_gemv_stream_w6_k5120_n17408.md: 1.004-1.008 x algorithmic) scaled to "
+                                    "the mean launch of this sweep, bytes per launch",
                      "launches": nlaunch.value, "bytes": nbytes.value, "ms": sweep_ms,
                      "how": "every linear of the model at M=1, 3 passes back to back, CUDA events on the launch queue"},
         "clocks": sampler.summary(windows),
