@@ -67,9 +67,9 @@ def test_gemm_matches_oracle(n, k, bits, ms, libs, oracle):
             for name, lin, variant in cases:
                 got = np.zeros_like(want)
                 d.det_memset(dy, 0xFF, want.nbytes, None)
-                d.det_debug_set_tc_variant(variant)
+                d.det_debug_set_tc_variant(variant | (0 if variant & 0x100 else 0x200))   # K split only where asked for
                 d.det_gemm(C.byref(lin), dx, ds, dm, mtok, dy, None)
-                d.det_debug_set_tc_variant(0x200)
+                d.det_debug_set_tc_variant(0x100)                                         # back to the defaults
                 d.det_memcpy(got.ctypes.data, dy, got.nbytes, None)
                 d.det_sync()
                 bad = int((got.view(np.uint32) != want.view(np.uint32)).sum())
