@@ -58,3 +58,36 @@ def test_size_queries_need_no_device(libs):
 def test_host_library_loads(libs):
     h = libs.host()
     assert h.dh_det_row_bytes(6, 5120) == 5120 // 32 * 24 + 4 + 40 * 2
+
+
+def test_ctypes_mirror_has_the_layout_the_c_compiler_gives_the_header(libs, tmp_path):
+    """Every struct of include/det_b200.h: size and the offset of every field as gcc lays them out, against the ctypes
+    mirror in det_b200/capi.py (a field added to one side only, or out of order, shows here and not as a wrong pointer
+    on the GPU)."""
+    import os
+    import shutil
+    import subprocess
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    cuda_inc = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
+    if shutil.which("gcc") is None or not (cuda_inc / "cuda_runtime.h").exists():
+        pytest.skip("needs gcc and the CUDA headers")
+    pairs = {"det_qlinear": libs.QLinear, "det_attn_layer": libs.AttnLayer, "det_kv_cache": libs.KvCache,
+             "det_gdn_layer": libs.GdnLayer, "det_gdn_state": libs.GdnState, "det_act_source": libs.ActSource,
+             "det_gemv_op": libs.GemvOp}
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "det_b200.h"', "int main(void) {"]
+    for cname, mirror in pairs.items():
+        lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
+        for field, _ in mirror._fields_:
+            lines.append(f'  printf("{cname}.{field} %zu\\n", offsetof({cname}, {field}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(root / "include"), "-I", str(cuda_inc), str(src), "-o", str(exe)], check=True)
+    got = dict(line.split() for line in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for cname, mirror in pairs.items():
+        assert int(got[cname]) == C.sizeof(mirror), cname
+        for field, _ in mirror._fields_:
+            assert int(got[f"{cname}.{field}"]) == getattr(mirror, field).offset, f"{cname}.{field}"
