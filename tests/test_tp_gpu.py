@@ -104,3 +104,91 @@ def test_sharded_model_equals_single_gpu(world, exchange, libs, tmp_path):
     r = np.load(tmp_path / "result.npz")
     assert int(r["logit_diff"]) == 0, f"{int(r['logit_diff'])} logits differ between {world} GPUs and 1"
     assert np.array_equal(r["toks"], r["want"]), (r["toks"], r["want"])
+
+
+def _run_rank_serving(rank, world, port, out_dir):
+    """Three sequences with prompts of several ragged chunks advance together on a sharded model (every rank holds its
+    heads' caches and states of every sequence); rank 0 also produces every stream alone on the unsharded model."""
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, str(ROOT))
+    from det_b200 import capi
+    rt = C.CDLL("libcudart.so.12")
+    assert rt.cudaSetDevice(rank) == 0
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    h, d = capi.host(), capi.cuda()
+    backend = h.dh_cuda_backend_new(1, 1)
+    assert backend, h.dh_last_error()
+    nid = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        buf = np.zeros(128, np.uint8)
+        h.dh_nccl_unique_id(buf.ctypes.data)
+        nid = torch.from_numpy(buf)
+    dist.broadcast(nid, 0)
+    nid_np = nid.numpy().copy()
+    chunk, ctx, n_new = 128, 1024, 6
+    comm = h.dh_peer_comm_new(nid_np.ctypes.data, rank, world, 16 * max(chunk * 3072, VOCAB) + 4096)
+    assert comm, h.dh_last_error()
+    mine = np.zeros(64, np.uint8)
+    h.dh_peer_comm_handle(comm, mine.ctypes.data)
+    every = [torch.zeros(64, dtype=torch.uint8) for _ in range(world)]
+    dist.all_gather(every, torch.from_numpy(mine))
+    handles = np.concatenate([e.numpy() for e in every]).copy()
+    h.dh_peer_comm_open(comm, handles.ctypes.data)
+    dist.barrier()
+    prompts = [700, 333, 41]            # five chunks + 60 tokens, two + 77, one ragged chunk
+    sampling = (0, 1.0 / 0.7, 40, 0.95)
+
+    def prompt(i, n):
+        ids = np.zeros(n, np.int32)
+        h.dh_synth_prompt(300 + i, n, VOCAB, ids.ctypes.data)
+        return ids
+
+    shard = h.dh_model_new_synth_tp(backend, b"tiny", 4, SEED, ctx, chunk, comm)
+    assert shard, h.dh_last_error()
+    batch = h.dh_batch_new(shard, len(prompts), ctx)
+    assert batch, h.dh_last_error()
+    for i, n in enumerate(prompts):
+        assert h.dh_batch_prefill(batch, i, prompt(i, n).ctypes.data, n, *sampling, 7000 + i) == 0, h.dh_last_error()
+    assert h.dh_batch_step(batch, n_new - 1) == 0, h.dh_last_error()
+    together = []
+    for i in range(len(prompts)):
+        out = np.zeros(n_new, np.int32)
+        assert h.dh_batch_tokens(batch, i, out.ctypes.data, n_new) == n_new
+        together.append(out)
+    assert d.det_last_error() == 0
+    if rank == 0:
+        full = h.dh_model_new_synth(backend, b"tiny", 4, SEED, ctx, chunk)
+        assert full, h.dh_last_error()
+        solo = []
+        for i, n in enumerate(prompts):
+            out = np.zeros(n_new, np.int32)
+            cnt = C.c_size_t(0)
+            assert h.dh_model_reset(full) == 0
+            assert h.dh_model_generate(full, prompt(i, n).ctypes.data, n, n_new, *sampling, 7000 + i, out.ctypes.data,
+                                       C.byref(cnt)) == 0, h.dh_last_error()
+            assert cnt.value == n_new
+            solo.append(out)
+        np.savez(Path(out_dir) / "serving.npz", together=np.stack(together), solo=np.stack(solo))
+    d.det_sync()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [
+    2,
+    # the 27B serving line's first sampled tokens differ between 1 - 2 GPUs and 4 - 8 GPUs (ranks agree with each other):
+    # an unlocated defect of the sharded batched path; whether this reduced case shows it is not known
+    pytest.param(4, marks=pytest.mark.xfail(strict=False, reason="open defect of the sharded batched step at 4+ GPUs")),
+])
+def test_sharded_serving_streams_equal_solo_streams(world, libs, tmp_path):
+    """A BatchDecoder on shards against the unsharded model serving each sequence alone, sampled tokens bit for bit:
+    prompts longer than a chunk (tensor-core attention behind a filled cache, ragged last chunks, NCCL chunk exchanges),
+    then batched steps (row exchanges with several rows, det_attention_rows / det_gdn_rows on a shard)."""
+    if _gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_run_rank_serving, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    r = np.load(tmp_path / "serving.npz")
+    assert np.array_equal(r["together"], r["solo"]), (r["together"], r["solo"])
