@@ -112,7 +112,8 @@ def _run_rank_serving(rank, world, port, out_dir):
     batch = h.dh_batch_new(shard, len(prompts), 48)
     assert batch, h.dh_last_error()
     for i, n in enumerate(prompts):
-        assert h.dh_batch_prefill(batch, i, prompt(i, n).ctypes.data, n, *sampling, 7000 + i) == 0, h.dh_last_error()
+        ids = prompt(i, n)          # held in a name: the pointer of a temporary dies with it
+        assert h.dh_batch_prefill(batch, i, ids.ctypes.data, n, *sampling, 7000 + i) == 0, h.dh_last_error()
     assert h.dh_batch_step(batch, n_new - 1) == 0, h.dh_last_error()
     together = []
     for i in range(len(prompts)):
@@ -126,7 +127,8 @@ def _run_rank_serving(rank, world, port, out_dir):
             out = np.zeros(n_new, np.int32)
             cnt = C.c_size_t(0)
             assert h.dh_model_reset(full) == 0
-            assert h.dh_model_generate(full, prompt(i, n).ctypes.data, n, n_new, *sampling, 7000 + i, out.ctypes.data,
+            ids = prompt(i, n)
+            assert h.dh_model_generate(full, ids.ctypes.data, n, n_new, *sampling, 7000 + i, out.ctypes.data,
                                        C.byref(cnt)) == 0, h.dh_last_error()
             ok = ok and cnt.value == n_new and np.array_equal(out, together[i])
         np.savez(Path(out_dir) / "serving.npz", ok=ok, streams=np.stack(together))
